@@ -1,0 +1,237 @@
+/*
+ * tritium_b200 — C ABI of the B200 (sm_100a) backend for Tritium's packed additive-ternary
+ * linear layer  Y = X · Σ_p diag(s_p)·T_p.
+ *
+ * Conventions follow the reference project's own C ABI (crates/tritium-ffi/src/lib.rs:8-26,
+ * 42-75,82-100,362-376): every fallible call returns a tb_status (TB_OK == 0); the message of
+ * the last failure on the calling thread is kept in thread-local storage and returned by
+ * tb_last_error() until the next call on that thread; handles are opaque, owned by the caller
+ * and released by a null-safe *_free; every pointer is null-checked; nothing unwinds across
+ * the boundary.  A handle may move between threads but must not be used from two threads at
+ * once.  Status codes mirror BackendError (crates/tritium-spec/src/lib.rs:384-405).
+ *
+ * There is no CPU fallback: every compute entry point fails with TB_BACKEND when no CUDA
+ * device is present.  Host-side format helpers (tb_fmt_*) run anywhere.
+ */
+#ifndef TRITIUM_B200_H
+#define TRITIUM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TB_ABI_VERSION 1u
+
+typedef enum tb_status {
+  TB_OK = 0,
+  TB_NULL_ARG = 1,
+  TB_SHAPE_MISMATCH = 2,     /* BackendError::ShapeMismatch */
+  TB_UNSUPPORTED_FORMAT = 3, /* BackendError::UnsupportedFormat */
+  TB_OUT_OF_MEMORY = 4,      /* BackendError::OutOfMemory */
+  TB_INVALID_INPUT = 5,      /* BackendError::InvalidInput */
+  TB_BACKEND = 6,            /* BackendError::Backend (driver / device failure) */
+  TB_TIMEOUT = 7             /* a bounded device-side wait gave up; the context stays usable */
+} tb_status;
+
+/* Codec tags as written in a package header (crates/tritium-format/src/salt_v2_package.rs:2747-2762). */
+typedef enum tb_codec { TB_CODEC_D2 = 1, TB_CODEC_B3 = 2, TB_CODEC_S34 = 3 } tb_codec;
+
+typedef enum tb_dtype { TB_F32 = 0, TB_BF16 = 1, TB_I8 = 2 } tb_dtype;
+
+typedef struct tb_backend tb_backend;
+typedef struct tb_weights tb_weights;
+typedef struct tb_stack tb_stack;
+
+/* DeviceCaps (crates/tritium-spec/src/caps.rs:7-68). */
+typedef struct tb_caps {
+  char backend[16];      /* "b200" */
+  char device_name[128];
+  char device_id[32];    /* "b200:<ordinal>" */
+  char physical_id[96];  /* "b200:<ordinal>:GPU-<uuid>" */
+  char features[192];    /* comma separated: sm_100a,salt_v2_d2,salt_v2_b3,salt_v2_s34,tq2_0,int8_tcgen05 */
+  uint64_t total_memory_bytes;
+  uint32_t sm_count;
+  uint32_t supports_imma;
+  uint32_t supports_fp8;
+} tb_caps;
+
+/* Byte receipt of one forward call: the algorithmic bytes the call had to move
+ * (SaltV2ForwardReceipt, crates/tritium-cuda/src/cuda/backend.rs:321-405).  dense_weight_bytes
+ * is always 0: no dequantised weight copy exists on the device. */
+typedef struct tb_receipt {
+  uint64_t payload_bytes, scale_bytes, map_bytes, rank_prefix_bytes;
+  uint64_t activation_bytes, output_bytes, dense_weight_bytes;
+  uint32_t kernel; /* 0 exact, 1 decode (mma.sync), 2 prefill (tcgen05) */
+  uint32_t launches;
+} tb_receipt;
+
+typedef struct tb_weights_info {
+  uint32_t codec, group, planes_uniform; /* planes_uniform: 1..3, or 0 when plane counts vary */
+  uint64_t n, k, tiles, present_planes;
+  uint64_t payload_bytes, scale_bytes, map_bytes, rank_prefix_bytes;
+  uint64_t source_len_bytes; /* DeviceBuffer::len_bytes(): the caller's packed input length */
+  uint32_t fast_path;        /* 1 when the decode/prefill kernels accept this layout */
+} tb_weights_info;
+
+/* ------------------------------------------------------------------ library */
+uint32_t tb_abi_version(void);
+const char* tb_last_error(void);
+
+/* ------------------------------------------------------------------ backend
+ * Replaces CudaBackend::new / the BackendEntry init function
+ * (crates/tritium-cuda/src/cuda/backend.rs:9087-9100, crates/tritium-runtime/src/lib.rs:74-86).
+ * Returns TB_BACKEND (never aborts) when no device exists. */
+tb_status tb_backend_create(int ordinal, tb_backend** out);
+void tb_backend_free(tb_backend* backend);
+/* TernaryBackend::capabilities (crates/tritium-spec/src/lib.rs:166-185). */
+tb_status tb_backend_caps(const tb_backend* backend, tb_caps* out);
+tb_status tb_backend_synchronize(tb_backend* backend);
+
+/* ------------------------------------------------------------------ weights
+ * TernaryBackend::upload_weights for TernaryFormat::Tq2_0 (crates/tritium-spec/src/lib.rs:186-199,
+ * crates/tritium-cuda/src/cuda/backend.rs:8581-8650).  `len` must equal n*ceil(k/256)*66. */
+tb_status tb_tq2_upload(tb_backend* backend, const uint8_t* packed, size_t len, uint32_t n,
+                        uint32_t k, tb_weights** out);
+/* CudaBackend::upload_salt_v2 (crates/tritium-cuda/src/cuda/backend.rs:7463-7651), taking the
+ * resident arenas: payload (tile-major then plane), f16 scale bits, the runtime plane map
+ * (2 bits per tile, value planes-1) and its terminal partial byte.  Sizes are re-derived from
+ * (n, k, group, map) and compared. */
+tb_status tb_salt_v2_upload(tb_backend* backend, tb_codec codec, uint32_t group, uint32_t n,
+                            uint32_t k, const uint8_t* payload, size_t payload_len,
+                            const uint16_t* scales, size_t scale_count, const uint8_t* plane_map,
+                            size_t map_len, uint32_t terminal_map_value, tb_weights** out);
+/* CudaBackend::upload_salt_v2_from_reader (crates/tritium-cuda/src/cuda/backend/salt_v2_reader_upload.rs:32):
+ * whole package bytes plus a tensor name. */
+tb_status tb_salt_v2_upload_package(tb_backend* backend, const uint8_t* package, size_t len,
+                                    const char* tensor_name, tb_weights** out);
+tb_status tb_weights_info_get(const tb_weights* weights, tb_weights_info* out);
+void tb_weights_free(tb_weights* weights);
+
+/* ------------------------------------------------------------------ forward, host pointers
+ * CudaBackend::salt_v2_forward_exact_into (crates/tritium-cuda/src/cuda/backend/salt_v2_runtime.rs:212-381):
+ * fp32 activations [m,k] -> fp32 [m,n], bit-identical to the CPU reference order
+ * (crates/tritium-cpu/src/salt_v2.rs:316-423).  Non-finite activations and outputs are rejected
+ * as TB_INVALID_INPUT and `y` is left untouched on any error. */
+tb_status tb_salt_v2_forward_exact(tb_backend* backend, const tb_weights* weights, const float* x,
+                                   uint32_t m, float* y, tb_receipt* receipt);
+/* CudaBackend::salt_v2_forward_fast (backend.rs:7672-7687): same contract, reassociated sums. */
+tb_status tb_linear_forward_f32(tb_backend* backend, const tb_weights* weights, const float* x,
+                                uint32_t m, float* y, tb_receipt* receipt);
+/* The fused W1.58A8 path (TernaryBackend::mpgemm_with_act_quant, crates/tritium-spec/src/lib.rs:266-318,
+ * applied to the SALT V2 contraction): per-token absmax int8 quantisation, exact int32
+ * contraction per (scale group, plane), fold of f16 group scales and the token scale.
+ * `x` is [m,k] of x_dtype; `y` is [m,n] of y_dtype (TB_F32 or TB_BF16).  `acc_dump`, when not
+ * NULL, receives the int32 accumulators as [m][n][k/group][planes]. */
+tb_status tb_linear_forward_a8(tb_backend* backend, const tb_weights* weights, const void* x,
+                               tb_dtype x_dtype, uint32_t m, void* y, tb_dtype y_dtype,
+                               int32_t* acc_dump, tb_receipt* receipt);
+/* CudaBackend::salt_v2_gather_rows (backend.rs:7689-7701, kernels/salt_v2.cu:221-304). */
+tb_status tb_salt_v2_gather_rows(tb_backend* backend, const tb_weights* weights,
+                                 const uint32_t* rows, size_t row_count, float* out);
+
+/* ------------------------------------------------------------------ forward, device pointers
+ * Same operators on device memory, launched on `stream` (a cudaStream_t, NULL = the backend's
+ * stream) without any host synchronisation or allocation beyond the backend's own scratch.
+ * flags: */
+#define TB_FWD_A8 1u          /* int8-quantise activations (x_dtype F32 or BF16), or consume int8 */
+#define TB_FWD_EXACT 2u       /* force the bit-exact kernel (fp32 activations only) */
+#define TB_FWD_PDL 4u         /* launch with programmatic dependent launch (weights prefetch early) */
+#define TB_FWD_FORCE_DECODE 8u
+#define TB_FWD_FORCE_PREFILL 16u
+typedef struct tb_forward_args {
+  const void* x;            /* [m,k] device */
+  tb_dtype x_dtype;
+  const float* act_scale;   /* [m] device; dequantisation multiplier, required when x_dtype == TB_I8 */
+  const float* act_absmax;  /* [m] device, nullable: per-token max|x| over the FULL row; a
+                               row-parallel shard passes the global value so that its int8
+                               codes equal the unsharded ones */
+  uint32_t m;
+  void* y;                  /* [m,n] device */
+  tb_dtype y_dtype;
+  int32_t* acc_dump;        /* device, nullable */
+  const float* row_scale;   /* [n] device, nullable: per-output-channel scale (trait path) */
+  uint32_t flags;
+  void* stream;
+} tb_forward_args;
+tb_status tb_linear_forward_dev(tb_backend* backend, const tb_weights* weights,
+                                const tb_forward_args* args, tb_receipt* receipt);
+/* Reserves the backend's device scratch for `weights` at up to `max_m` tokens, so that later
+ * tb_linear_forward_dev calls allocate nothing. */
+tb_status tb_backend_reserve(tb_backend* backend, const tb_weights* weights, uint32_t max_m);
+/* Reads and clears the device status word written by bounded waits / finite checks. */
+tb_status tb_backend_check(tb_backend* backend, void* stream);
+
+/* ------------------------------------------------------------------ trait path (1 plane, per-channel scale)
+ * TernaryBackend::mpgemm (crates/tritium-spec/src/lib.rs:200-215; host crates/tritium-cuda/src/cuda/backend.rs:7175-7315)
+ * out[m,n] = scales[n] · Σ_k act[m,k]·w[n,k].  Integer-valued activations in [-128,127] take the
+ * exact int8 kernel (as crates/tritium-cpu/src/kernel.rs:833-837 does); others the fp32 kernel. */
+tb_status tb_mpgemm(tb_backend* backend, const tb_weights* weights, const float* act,
+                    const float* scales, uint32_t m, uint32_t n, uint32_t k, float* out);
+/* TernaryBackend::mpgemm_with_act_quant (lib.rs:216-318; CUDA override backend.rs:8868-8954). */
+tb_status tb_mpgemm_with_act_quant(tb_backend* backend, const tb_weights* weights,
+                                   const float* act, const float* scales, uint32_t m, uint32_t n,
+                                   uint32_t k, float* out);
+
+/* ------------------------------------------------------------------ layer stack (decoder linears)
+ * A sequence of resident linears run back to back on one stream, each layer's weight stream
+ * overlapping the previous layer's tail.  `weights[i]` consumes the output of layer i-1 when
+ * chain[i] != 0, else the stack input.  Used by the 2B / 27B stack configurations. */
+tb_status tb_stack_create(tb_backend* backend, const tb_weights* const* weights,
+                          const uint8_t* chain, uint32_t layers, uint32_t max_m, tb_stack** out);
+tb_status tb_stack_forward_dev(tb_stack* stack, const void* x, tb_dtype x_dtype, uint32_t m,
+                               void* y_last, tb_dtype y_dtype, uint32_t flags, void* stream);
+uint64_t tb_stack_bytes_per_step(const tb_stack* stack, uint32_t m);
+void tb_stack_free(tb_stack* stack);
+
+/* ------------------------------------------------------------------ tensor-parallel sharding (host)
+ * Cuts one tensor's resident arenas into the shard for `rank` of `world`:
+ * column-parallel (split n; QKV, gate/up) or row-parallel (split k; O, down).  Row-parallel
+ * shards are re-encoded so that each shard is itself a valid [n, k/world] tensor.  Output
+ * buffers are sized by tb_tp_shard_sizes. */
+typedef struct tb_shard_sizes {
+  uint32_t n, k;
+  uint64_t payload_bytes, scale_count, map_bytes;
+} tb_shard_sizes;
+tb_status tb_tp_shard_sizes(tb_codec codec, uint32_t group, uint32_t n, uint32_t k, uint32_t planes,
+                            int row_parallel, uint32_t world, uint32_t rank, tb_shard_sizes* out);
+tb_status tb_tp_shard(tb_codec codec, uint32_t group, uint32_t n, uint32_t k, uint32_t planes,
+                      const uint8_t* payload, const uint16_t* scales, int row_parallel,
+                      uint32_t world, uint32_t rank, uint8_t* shard_payload,
+                      uint16_t* shard_scales, uint8_t* shard_map, uint32_t* shard_terminal);
+
+/* ------------------------------------------------------------------ host format helpers
+ * Byte-for-byte the tritium-format layouts; no device needed. */
+/* pack_d2/pack_b3/pack_s34 and unpack_* (crates/tritium-format/src/salt_v2.rs:268-482).
+ * tb_fmt_pack returns bytes written (negative tb_status on error; out may be NULL to size). */
+int64_t tb_fmt_pack(tb_codec codec, const int8_t* trits, size_t n, uint8_t* out, size_t cap);
+tb_status tb_fmt_unpack(tb_codec codec, const uint8_t* packed, size_t len, size_t n, int8_t* trits);
+size_t tb_fmt_plane_bytes(tb_codec codec, size_t logical_len);
+/* Builds the resident arenas from dense planes: trits[(tile*3+p)*256+e], scales[(tile*3+p)*4+g]
+ * (f16 bits), plane_count[tile]; validates the semantic rules of
+ * salt_v2_package.rs:130-187,222-251,582-641.  Sizes come from tb_fmt_resident_sizes. */
+typedef struct tb_resident_sizes {
+  uint64_t payload_bytes, scale_count, map_bytes, rank_prefix_bytes, tiles, present_planes;
+} tb_resident_sizes;
+tb_status tb_fmt_resident_sizes(tb_codec codec, uint32_t group, uint64_t n, uint64_t k,
+                                const uint8_t* plane_count, tb_resident_sizes* out);
+tb_status tb_fmt_resident_build(tb_codec codec, uint32_t group, uint64_t n, uint64_t k,
+                                const uint8_t* plane_count, const int8_t* trits,
+                                const uint16_t* scales, uint8_t* payload, uint16_t* scale_out,
+                                uint8_t* plane_map, uint32_t* terminal_map_value);
+/* write_salt_v2_package for one matrix tensor (salt_v2_package.rs:1526-1668); returns total
+ * bytes (negative tb_status on error; out may be NULL to size). */
+int64_t tb_fmt_package_write(tb_codec codec, const char* name, uint32_t group, uint64_t n,
+                             uint64_t k, const uint8_t* plane_count, const int8_t* trits,
+                             const uint16_t* scales, uint8_t* out, size_t cap);
+/* pack_tq2_0_row (crates/tritium-format/src/rows.rs:61-77) with unit block scales. */
+tb_status tb_fmt_tq2_pack_rows(const int8_t* trits, uint64_t n, uint64_t k, uint8_t* out);
+/* quantize_act_int8 (crates/tritium-spec/src/lib.rs:351-378), host. */
+void tb_fmt_quantize_act_int8(const float* act, uint64_t m, uint64_t k, float* q, float* scale);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,189 @@
+"""Host logic of the product library against the oracle: byte layouts must be identical."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+
+from oracle import oracle as orc
+from tritium_b200 import _lib, errors
+from tritium_b200 import format as fmt
+from tritium_b200.format import SaltV2Codec, SaltV2Tensor
+from tritium_b200.synth import make_planes
+
+CODECS = [(SaltV2Codec.D2, orc.D2), (SaltV2Codec.B3, orc.B3), (SaltV2Codec.S34, orc.S34)]
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "tritium_b200.h")).read()
+    declared = set(re.findall(r"\b(tb_[a-z0-9_]+)\s*\(", header))
+    declared -= {"tb_status"}
+    L = _lib.load()
+    assert L.tb_abi_version() == 1
+    missing = [name for name in sorted(declared) if not hasattr(L, name)]
+    assert not missing, missing
+    assert set(_lib.EXPORTS) <= declared
+
+
+def s34_trits(rng, n):
+    t = rng.choice([-1, 1], n).astype(np.int8)
+    t[np.arange(0, n, 4) + rng.integers(0, 4, n // 4)] = 0
+    return t
+
+
+@pytest.mark.parametrize("codec,ocodec", CODECS)
+def test_codecs_match_oracle_bytes(codec, ocodec):
+    rng = np.random.default_rng(11)
+    for n in (4, 8, 20, 100, 256, 1024):
+        trits = s34_trits(rng, n) if codec == SaltV2Codec.S34 else rng.integers(-1, 2, n).astype(np.int8)
+        packed = fmt.pack(codec, trits)
+        assert packed == orc.pack(ocodec, trits)
+        assert np.array_equal(fmt.unpack(codec, packed, n), trits)
+    if codec != SaltV2Codec.S34:
+        for n in (1, 5, 6, 7, 87, 173, 255):
+            trits = rng.integers(-1, 2, n).astype(np.int8)
+            assert fmt.pack(codec, trits) == orc.pack(ocodec, trits)
+
+
+def test_codec_rejections():
+    with pytest.raises(errors.InvalidInput):
+        fmt.unpack(SaltV2Codec.D2, bytes([0b01010111]), 1)
+    with pytest.raises(errors.InvalidInput):
+        fmt.unpack(SaltV2Codec.D2, bytes([0x00]), 1)
+    with pytest.raises(errors.InvalidInput):
+        fmt.unpack(SaltV2Codec.B3, bytes([243]), 5)
+    with pytest.raises(errors.InvalidInput):
+        fmt.unpack(SaltV2Codec.B3, bytes([0]), 1)
+    with pytest.raises(errors.InvalidInput):
+        fmt.unpack(SaltV2Codec.B3, bytes([121, 121]), 1)
+    with pytest.raises(errors.InvalidInput):
+        fmt.unpack(SaltV2Codec.S34, bytes([0xC9, 0x82]), 8)
+    with pytest.raises(errors.InvalidInput):
+        fmt.pack(SaltV2Codec.S34, [-1, 1, -1, 1])
+    with pytest.raises(errors.InvalidInput):
+        fmt.pack(SaltV2Codec.D2, [2])
+
+
+def ragged_pair(rows, cols, counts, group=128, s34=False, seed=0):
+    """The same ragged tensor as a product SaltV2Tensor and as an oracle Tensor."""
+    rng = np.random.default_rng(seed)
+    tiles = (rows * cols + 255) // 256
+    pc = np.array(counts, np.uint8)
+    tr = np.zeros((tiles, 3, 256), np.int8)
+    sc = np.zeros((tiles, 3, 4), np.uint16)
+    for t in range(tiles):
+        length = min(256, rows * cols - t * 256)
+        for p in range(pc[t]):
+            if s34:
+                full = (length // 4) * 4
+                tr[t, p, :full] = s34_trits(rng, full) if full else []
+                tr[t, p, full:length] = rng.choice([-1, 1], length - full)
+            else:
+                tr[t, p, :length] = rng.integers(-1, 2, length)
+            groups = (length + group - 1) // group
+            sc[t, p, :groups] = fmt.f16_bits(0.05 + rng.random(groups, dtype=np.float32))
+    prod = SaltV2Tensor("w", rows, cols, pc.copy(), tr.copy(), sc.copy(), group)
+    orac = orc.Tensor(rows, cols, group, pc.copy(), tr.copy(), sc.copy())
+    return prod, orac
+
+
+@pytest.mark.parametrize("codec,ocodec", CODECS)
+@pytest.mark.parametrize("shape", [(3, 173, [1, 3, 2], 128), (2, 3, [3], 128), (1, 1, [1], 128),
+                                   (4, 576, [1, 2, 3, 1, 2, 3, 1, 2, 3], 64), (1, 513 * 256, None, 128)])
+def test_resident_arenas_and_package_bytes_match_oracle(codec, ocodec, shape):
+    rows, cols, counts, group = shape
+    if counts is None:
+        counts = [1 + i % 3 for i in range(rows * cols // 256)]
+    prod, orac = ragged_pair(rows, cols, counts, group, s34=(codec == SaltV2Codec.S34))
+    payload, scales, pmap, terminal, sizes = prod.resident(codec)
+    o_payload, o_scales, o_meta, o_terminal, plan = orc.resident_build(orac, ocodec)
+    assert payload.tobytes() == o_payload.tobytes()
+    assert scales.tobytes() == o_scales.tobytes()
+    assert pmap.tobytes() == o_meta[: plan["map_bytes"]].tobytes()
+    assert terminal == o_terminal
+    assert sizes["rank_prefix_bytes"] == plan["rank_prefix_bytes"]
+    assert fmt.write_salt_v2_package(prod, codec) == orc.package_write(ocodec, [("w", orac)])
+
+
+def test_semantic_validation_matches_reference_rules():
+    prod, _ = ragged_pair(1, 256, [1])
+    for bits in (0x7C00, 0x7E00, 0xBC00, 0x8000):
+        bad = SaltV2Tensor("w", 1, 256, prod.plane_count, prod.trits, prod.scales.copy())
+        bad.scales[0, 0, 1] = bits
+        with pytest.raises(errors.InvalidInput):
+            bad.resident(SaltV2Codec.B3)
+    bad = SaltV2Tensor("w", 1, 256, prod.plane_count, prod.trits.copy(), prod.scales.copy())
+    bad.scales[0, 0, 0] = 0
+    bad.trits[0, 0, 5] = 1
+    with pytest.raises(errors.InvalidInput):
+        bad.resident(SaltV2Codec.B3)
+    bad.trits[0, 0, :128] = 0
+    bad.resident(SaltV2Codec.B3)  # zero scale over an all-zero group is allowed
+    bad = SaltV2Tensor("w", 1, 256, np.array([4], np.uint8), prod.trits, prod.scales)
+    with pytest.raises(errors.InvalidInput):
+        bad.resident(SaltV2Codec.B3)
+    bad = SaltV2Tensor("w", 1, 256, prod.plane_count, prod.trits, prod.scales, 32)
+    with pytest.raises(errors.InvalidInput):
+        bad.resident(SaltV2Codec.B3)
+
+
+def test_host_quantiser_matches_oracle():
+    rng = np.random.default_rng(2)
+    x = (rng.standard_normal((5, 300)) * 3).astype(np.float32)
+    x[2] = 0
+    q, s = fmt.quantize_act_int8(x, 5, 300)
+    oq, os_ = orc.quantize_act_int8(x, 5, 300)
+    assert np.array_equal(q, oq) and np.array_equal(s, os_)
+    q, s = fmt.quantize_act_int8(np.array([1, -2, 0.5, -0.5, 2, -1], np.float32), 1, 6)
+    assert list(q[0]) == [64, -127, 32, -32, 127, -64]
+
+
+def test_tq2_rows_match_oracle():
+    rng = np.random.default_rng(4)
+    w = rng.integers(-1, 2, (7, 768)).astype(np.int8)
+    assert fmt.pack_tq2_0_rows(w) == orc.tq2_pack_rows(w)
+
+
+@pytest.mark.parametrize("codec,ocodec", CODECS[:2])
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_tensor_parallel_shards_reassemble(codec, ocodec, world):
+    n, k, planes = 16, 1024, 2
+    trits, scales = make_planes(n, k, planes, seed=3, densities=(0.66, 0.10, 0.03))
+    full = SaltV2Tensor.from_matrix_planes("w", trits, scales)
+    payload, sc, _, _, _ = full.resident(codec)
+    ofull = orc.Tensor(n, k, 128, full.plane_count, full.trits, full.scales)
+    x = np.random.default_rng(9).integers(-127, 128, k).astype(np.float32)
+    want = orc.matvec(ofull, x)
+    # column-parallel: output rows are split, results concatenate
+    outs = []
+    for r in range(world):
+        sn, sk, sp, ss, sm, term = fmt.tp_shard(codec, 128, n, k, planes, payload, sc, False, world, r)
+        assert (sn, sk) == (n // world, k)
+        outs.append(orc.forward_packed(ocodec, 128, sn, sk, sp, ss, sm, len(sm), term, x)[0])
+    assert np.array_equal(np.concatenate(outs), want)
+    # row-parallel: k is split (padded to whole tiles with zero trits), partial sums add up.
+    # Integer activations keep every partial sum exact, so the total is exact as well.
+    dense = np.zeros((n, k), np.float64)
+    for p in range(planes):
+        dense += trits[p].astype(np.float64) * np.repeat(fmt.f16_bits(scales[p]).view(np.float16).astype(np.float64), 128, axis=1)
+    total = np.zeros(n, np.float64)
+    for r in range(world):
+        sn, sk, sp, ss, sm, term = fmt.tp_shard(codec, 128, n, k, planes, payload, sc, True, world, r)
+        kv = k // world
+        assert sn == n and sk == (kv + 255) // 256 * 256
+        xs = np.zeros(sk, np.float32)
+        xs[:kv] = x[r * kv:(r + 1) * kv]
+        total += orc.forward_packed(ocodec, 128, sn, sk, sp, ss, sm, len(sm), term, xs)[0].astype(np.float64)
+    assert np.allclose(total, dense @ x.astype(np.float64), rtol=1e-5, atol=1e-3)
+
+
+def test_backend_reports_missing_device_without_aborting():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a device is present")
+    from tritium_b200 import B200Backend, Registry
+    with pytest.raises(errors.Backend):
+        B200Backend(0)
+    assert Registry.init().names() == []

@@ -1,0 +1,101 @@
+"""ctypes binding of ``libtritium_b200.so`` (the C ABI declared in ``include/tritium_b200.h``).
+
+The library is the product; there is no Python or CPU fallback for any compute entry point.
+Loading fails loudly when the shared object is missing and cannot be built.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "_lib", "libtritium_b200.so")
+
+TB_OK, TB_NULL_ARG, TB_SHAPE_MISMATCH, TB_UNSUPPORTED_FORMAT, TB_OUT_OF_MEMORY, TB_INVALID_INPUT, TB_BACKEND, TB_TIMEOUT = range(8)
+TB_CODEC_D2, TB_CODEC_B3, TB_CODEC_S34 = 1, 2, 3
+TB_F32, TB_BF16, TB_I8 = 0, 1, 2
+TB_FWD_A8, TB_FWD_EXACT, TB_FWD_PDL, TB_FWD_FORCE_DECODE, TB_FWD_FORCE_PREFILL = 1, 2, 4, 8, 16
+
+EXPORTS = [
+    "tb_abi_version", "tb_last_error", "tb_backend_create", "tb_backend_free", "tb_backend_caps",
+    "tb_backend_synchronize", "tb_backend_reserve", "tb_backend_check", "tb_tq2_upload",
+    "tb_salt_v2_upload", "tb_salt_v2_upload_package", "tb_weights_info_get", "tb_weights_free",
+    "tb_salt_v2_forward_exact", "tb_linear_forward_f32", "tb_linear_forward_a8",
+    "tb_salt_v2_gather_rows", "tb_linear_forward_dev", "tb_mpgemm", "tb_mpgemm_with_act_quant",
+    "tb_stack_create", "tb_stack_forward_dev", "tb_stack_bytes_per_step", "tb_stack_free",
+    "tb_tp_shard_sizes", "tb_tp_shard", "tb_fmt_pack", "tb_fmt_unpack", "tb_fmt_plane_bytes",
+    "tb_fmt_resident_sizes", "tb_fmt_resident_build", "tb_fmt_package_write", "tb_fmt_tq2_pack_rows",
+    "tb_fmt_quantize_act_int8",
+]
+
+
+class Caps(C.Structure):
+    _fields_ = [("backend", C.c_char * 16), ("device_name", C.c_char * 128), ("device_id", C.c_char * 32),
+                ("physical_id", C.c_char * 96), ("features", C.c_char * 192),
+                ("total_memory_bytes", C.c_uint64), ("sm_count", C.c_uint32),
+                ("supports_imma", C.c_uint32), ("supports_fp8", C.c_uint32)]
+
+
+class Receipt(C.Structure):
+    _fields_ = [("payload_bytes", C.c_uint64), ("scale_bytes", C.c_uint64), ("map_bytes", C.c_uint64),
+                ("rank_prefix_bytes", C.c_uint64), ("activation_bytes", C.c_uint64),
+                ("output_bytes", C.c_uint64), ("dense_weight_bytes", C.c_uint64),
+                ("kernel", C.c_uint32), ("launches", C.c_uint32)]
+
+
+class WeightsInfo(C.Structure):
+    _fields_ = [("codec", C.c_uint32), ("group", C.c_uint32), ("planes_uniform", C.c_uint32),
+                ("n", C.c_uint64), ("k", C.c_uint64), ("tiles", C.c_uint64), ("present_planes", C.c_uint64),
+                ("payload_bytes", C.c_uint64), ("scale_bytes", C.c_uint64), ("map_bytes", C.c_uint64),
+                ("rank_prefix_bytes", C.c_uint64), ("source_len_bytes", C.c_uint64), ("fast_path", C.c_uint32)]
+
+
+class ForwardArgs(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("x_dtype", C.c_int), ("act_scale", C.c_void_p), ("act_absmax", C.c_void_p),
+                ("m", C.c_uint32), ("y", C.c_void_p), ("y_dtype", C.c_int), ("acc_dump", C.c_void_p),
+                ("row_scale", C.c_void_p), ("flags", C.c_uint32), ("stream", C.c_void_p)]
+
+
+class ShardSizes(C.Structure):
+    _fields_ = [("n", C.c_uint32), ("k", C.c_uint32), ("payload_bytes", C.c_uint64),
+                ("scale_count", C.c_uint64), ("map_bytes", C.c_uint64)]
+
+
+class ResidentSizes(C.Structure):
+    _fields_ = [("payload_bytes", C.c_uint64), ("scale_count", C.c_uint64), ("map_bytes", C.c_uint64),
+                ("rank_prefix_bytes", C.c_uint64), ("tiles", C.c_uint64), ("present_planes", C.c_uint64)]
+
+
+_lib = None
+
+
+def load(build_if_missing: bool = True) -> C.CDLL:
+    """Load the shared library, building it in-tree first when it is absent."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        if not build_if_missing:
+            raise RuntimeError(f"{LIB_PATH} is missing: run tritium_b200/build.py (there is no fallback path)")
+        from . import build as _build
+        _build.build()
+    L = C.CDLL(LIB_PATH)
+    L.tb_abi_version.restype = C.c_uint32
+    L.tb_last_error.restype = C.c_char_p
+    L.tb_fmt_pack.restype = C.c_int64
+    L.tb_fmt_package_write.restype = C.c_int64
+    L.tb_fmt_plane_bytes.restype = C.c_size_t
+    L.tb_stack_bytes_per_step.restype = C.c_uint64
+    L.tb_backend_free.restype = None
+    L.tb_weights_free.restype = None
+    L.tb_stack_free.restype = None
+    L.tb_backend_free.argtypes = [C.c_void_p]
+    L.tb_weights_free.argtypes = [C.c_void_p]
+    L.tb_stack_free.argtypes = [C.c_void_p]
+    _lib = L
+    return L
+
+
+def last_error() -> str:
+    msg = load().tb_last_error()
+    return msg.decode() if msg else ""

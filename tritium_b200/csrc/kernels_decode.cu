@@ -1,0 +1,523 @@
+// Decode GEMV (1..4 tokens) straight from the packed B3 / D2 arenas, sm_100a.
+//
+// Data movement: a CTA owns blocks of R consecutive output rows.  A row's tile-planes are
+// contiguous in the payload arena and rows follow one another, so a block is ONE contiguous byte
+// range; a producer warp streams it (and the matching f16 scale range) into a shared-memory ring
+// with cp.async.bulk + mbarrier transaction counts.  Weights are read from HBM exactly once.
+//
+// Arithmetic: activations are int8 (per-token absmax quantisation fused into the prologue).
+// B3 bytes are never expanded to trits.  For a byte b = sum d_i 3^i the five floor quotients
+// q_i = floor(b / 3^i) come from half-precision FMAs on (1024 + b) (round-to-nearest of the FMA
+// does the floor; constants verified exhaustively for b in [0,243)), and
+//     sum_i d_i x_i = sum_i q_i (x_i - 3 x_{i-1})
+// so the quotient bytes feed mma.sync.m16n8k32 (u8 x s8 -> s32) against pre-transformed
+// activations z_i = x_i - 3 x_{i-1}, split as z = 4*zh + zl to fit int8 (two MMA columns per
+// token).  q_0 is the raw byte: the packed word itself is an MMA operand.  Sums are exact int32
+// per (row, 128-group, plane); the f16 group scale is applied once per sum in fp32.
+// D2 words feed the MMA as unsigned 2-bit codes (t = code - 1) with z = x.
+//
+// Fragment roles (m16n8k32): MMA rows are 16 consecutive row-planes; lane (g = lane/4, c = lane%4)
+// supplies rows g and g+8 from packed words c, 4+c, 8+c (and half of word 12 for B3).  The B
+// operand (activations) is laid out in shared memory in exactly that k-slot order.  Trits that
+// belong to the other scale group of a straddling byte, and B3 padding digits, are removed on
+// the activation side (their z entries are zero), never by masking weights.
+//
+// Every wait is bounded; on timeout the kernel records TBF_WAIT_TIMEOUT and returns.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "tb_internal.h"
+
+namespace {
+
+constexpr int kConsumerWarps = 8;
+constexpr int kThreads = (kConsumerWarps + 1) * 32;
+constexpr int kMaxStages = 4;
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+struct DecodeParams {
+  const uint8_t* payload; const uint16_t* scales;
+  const void* x; const float* act_scale_in; const float* act_absmax_in;
+  void* y; int32_t* acc_dump; const float* row_scale;
+  uint32_t* status;
+  uint32_t m, n, k, planes, tpr;            // tpr = k / 256
+  uint32_t rows_per_stage, row_bytes, stage_bytes, scale_stage_bytes, blocks;
+  uint32_t stages, x_dtype, y_dtype, y_row_stride;
+  uint32_t dump_token_offset, dump_tokens_total;
+  uint32_t pdl;
+  // shared memory offsets (bytes)
+  uint32_t off_ring, off_scale_ring, off_xq, off_z, off_cinit, off_part, off_actscale;
+};
+
+template <int CODEC> struct Traits;
+template <> struct Traits<tbf::kB3> { static constexpr int kMmas = 15, kWords = 13, kPlaneBytes = 52; };
+template <> struct Traits<tbf::kD2> { static constexpr int kMmas = 8, kWords = 16, kPlaneBytes = 64; };
+
+// ---------------------------------------------------------------- PTX helpers
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false after kSpinLimit polls or when another thread flagged an abort.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 255u) == 255u && *abort_flag) return false;
+  }
+  return false;
+}
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_addr(dst)), "l"(src), "r"(bytes), "r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory"); }
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+  return r;
+}
+__device__ __forceinline__ uint32_t hfma2_bits(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t r;
+  asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+  return r;
+}
+__device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// ---------------------------------------------------------------- B3 quotients
+// Half constants (bit patterns, both halves).  For V = 1024 + v:
+//   fma(V, 0x3553, 0x6156) = 1024 + floor(v/3)   for v in [0,242]
+//   fma(V, 0x2f19, 0x631e) = 1025 + floor(v/9)   for v in [0,242]   (and for v in [0,80])
+//   fma(1025+v, 0x2f1f, 0x631d) = 1025 + floor(v/9) for v in [0,26]
+// so with Q1 = 1024+q1, Q2 = 1025+q2, Q3 = fma(Q1, ./9) = 1025+q3, Q4 = fma(Q2, ./9) = 1025+q4
+// the low bytes are q1, 1+q2, 1+q3, 1+q4.  The "+1" offsets are folded into the accumulator
+// start value on the activation side.
+constexpr uint32_t kC3 = 0x35533553u, kK3 = 0x61566156u;
+constexpr uint32_t kC9 = 0x2f192f19u, kK9 = 0x631e631eu;
+constexpr uint32_t kC9b = 0x2f1f2f1fu, kK9b = 0x631d631du;
+__device__ __forceinline__ void b3_quads(uint32_t w, uint32_t (&q)[5]) {
+  const uint32_t h01 = prmt(w, 0x64646464u, 0x4140u);  // halves 1024+b0, 1024+b1
+  const uint32_t h23 = prmt(w, 0x64646464u, 0x4342u);  // halves 1024+b2, 1024+b3
+  const uint32_t a1 = hfma2_bits(h01, kC3, kK3), b1 = hfma2_bits(h23, kC3, kK3);
+  const uint32_t a2 = hfma2_bits(h01, kC9, kK9), b2 = hfma2_bits(h23, kC9, kK9);
+  const uint32_t a3 = hfma2_bits(a1, kC9, kK9), b3 = hfma2_bits(b1, kC9, kK9);
+  const uint32_t a4 = hfma2_bits(a2, kC9b, kK9b), b4 = hfma2_bits(b2, kC9b, kK9b);
+  q[0] = w;
+  q[1] = prmt(a1, b1, 0x6420u);
+  q[2] = prmt(a2, b2, 0x6420u);
+  q[3] = prmt(a3, b3, 0x6420u);
+  q[4] = prmt(a4, b4, 0x6420u);
+}
+__host__ __device__ constexpr int b3_delta(int i) { return i >= 2 ? 1 : 0; }  // operand = q_i + delta_i
+
+// ---------------------------------------------------------------- activation-side tables
+// Which packed word / digits / scale-group variant MMA number `mma` of a tile-plane consumes for
+// the lane column c (0..3).
+template <int CODEC> struct Slot { int word, variant, d0, d1, lane_lo, lane_hi; };
+template <int CODEC> __device__ __forceinline__ Slot<CODEC> slot_of(int mma, int c);
+template <> __device__ __forceinline__ Slot<tbf::kB3> slot_of<tbf::kB3>(int mma, int c) {
+  // mma 0-2: words c (group 0); 3-5: words 4+c into group 0; 6-8: words 4+c into group 1;
+  // 9-11: words 8+c (group 1); 12-14: word 12, bytes 48,49 for c=0 and 50,51 for c=1 (group 1).
+  const int slot = mma < 3 ? 0 : mma < 9 ? 1 : mma < 12 ? 2 : 3;
+  const int pair = mma % 3;
+  Slot<tbf::kB3> s;
+  s.variant = mma < 6 ? 0 : 1;
+  s.d0 = pair * 2; s.d1 = pair == 2 ? -1 : pair * 2 + 1;
+  s.word = slot < 3 ? slot * 4 + c : 12;
+  s.lane_lo = 0; s.lane_hi = 4;
+  if (slot == 3) { if (c == 0) s.lane_hi = 2; else if (c == 1) s.lane_lo = 2; else s.lane_hi = 0; }
+  return s;
+}
+template <> __device__ __forceinline__ Slot<tbf::kD2> slot_of<tbf::kD2>(int mma, int c) {
+  const int slot = mma >> 1;  // words c, 4+c (group 0), 8+c, 12+c (group 1)
+  Slot<tbf::kD2> s;
+  s.variant = slot >> 1;
+  s.d0 = (mma & 1) * 2; s.d1 = s.d0 + 1;
+  s.word = slot * 4 + c;
+  s.lane_lo = 0; s.lane_hi = 4;
+  return s;
+}
+
+// z value of (byte-lane e of packed word `word`, digit/slot i) for scale-group `variant`.
+template <int CODEC>
+__device__ __forceinline__ int z_value(const int8_t* xq_tile, int word, int e, int i, int variant) {
+  if (CODEC == tbf::kB3) {
+    const int t = 5 * (4 * word + e) + i;
+    const int cur = (t < 256 && (t >> 7) == variant) ? xq_tile[t] : 0;
+    const int prev = (i > 0 && t - 1 < 256 && ((t - 1) >> 7) == variant) ? xq_tile[t - 1] : 0;
+    return cur - 3 * prev;
+  } else {
+    const int t = 16 * word + 4 * e + i;
+    return ((t >> 7) == variant) ? xq_tile[t] : 0;
+  }
+}
+
+template <int CODEC>
+__device__ __forceinline__ uint32_t z_quad(const int8_t* xq_tile, const Slot<CODEC>& s, int digit, int hl) {
+  if (digit < 0) return 0;
+  uint32_t out = 0;
+  for (int e = s.lane_lo; e < s.lane_hi; ++e) {
+    const int z = z_value<CODEC>(xq_tile, s.word, e, digit, s.variant);
+    const int v = hl == 0 ? (z >> 2) : (z & 3);
+    out |= uint32_t(v & 0xff) << (8 * e);
+  }
+  return out;
+}
+
+// ---------------------------------------------------------------- the kernel
+template <int CODEC>
+__global__ void __launch_bounds__(kThreads, 1) decode_kernel(const DecodeParams p) {
+  using T = Traits<CODEC>;
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ uint64_t full_bar[kMaxStages], empty_bar[kMaxStages];
+  __shared__ uint32_t abort_flag;
+  __shared__ float red_max[kConsumerWarps];
+
+  const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  uint8_t* ring = smem + p.off_ring;
+  uint8_t* scale_ring = smem + p.off_scale_ring;
+  int8_t* xq = reinterpret_cast<int8_t*>(smem + p.off_xq);
+  uint2* ztab = reinterpret_cast<uint2*>(smem + p.off_z);
+  int* cinit = reinterpret_cast<int*>(smem + p.off_cinit);
+  float* part = reinterpret_cast<float*>(smem + p.off_part);
+  float* act_scale = reinterpret_cast<float*>(smem + p.off_actscale);
+
+  if (tid == 0) {
+    abort_flag = 0;
+    for (uint32_t s = 0; s < p.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], kConsumerWarps); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (p.pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  const uint32_t my_blocks = blockIdx.x < p.blocks ? (p.blocks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+
+  if (warp == kConsumerWarps) {
+    // ------------------------------------------------ producer: weights do not depend on the
+    // previous kernel, so the stream starts before griddepcontrol.wait.
+    if (lane == 0) {
+      uint32_t fills[kMaxStages] = {0, 0, 0, 0};
+      for (uint32_t it = 0; it < my_blocks; ++it) {
+        const uint32_t s = it % p.stages, round = it / p.stages;
+        if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1, &abort_flag)) {
+          abort_flag = 1;
+          if (atomicOr(&p.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) { p.status[TBS_INFO0] = it; p.status[TBS_INFO1] = 100 + s; }
+          break;
+        }
+        const uint64_t blk = blockIdx.x + uint64_t(it) * gridDim.x;
+        mbar_expect_tx(&full_bar[s], p.stage_bytes + p.scale_stage_bytes);
+        bulk_g2s(ring + size_t(s) * p.stage_bytes, p.payload + blk * p.stage_bytes, p.stage_bytes, &full_bar[s]);
+        bulk_g2s(scale_ring + size_t(s) * p.scale_stage_bytes,
+                 reinterpret_cast<const uint8_t*>(p.scales) + blk * p.scale_stage_bytes, p.scale_stage_bytes, &full_bar[s]);
+        ++fills[s];
+      }
+      // Do not leave the CTA while a copy may still be landing in its shared memory: wait
+      // (bounded) for the latest fill of every slot.  In the normal path these have all
+      // completed already, because the consumers waited on them.
+      for (uint32_t s = 0; s < p.stages; ++s)
+        if (fills[s])
+          for (uint32_t i = 0; i < kSpinLimit && !mbar_try_wait(&full_bar[s], (fills[s] - 1) & 1); ++i) {}
+    }
+    return;
+  }
+
+  // -------------------------------------------------- consumers: prologue
+  const uint32_t ctid = tid;  // 0 .. kConsumerWarps*32-1
+  constexpr uint32_t kCT = kConsumerWarps * 32;
+  if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  for (uint32_t t = 0; t < p.m; ++t) {
+    float scale_q = 0.f;  // 127/gamma
+    if (p.x_dtype == TB_I8) {
+      const int8_t* xr = static_cast<const int8_t*>(p.x) + size_t(t) * p.k;
+      for (uint32_t i = ctid; i < p.k; i += kCT) xq[t * p.k + i] = xr[i];
+      if (ctid == 0) act_scale[t] = p.act_scale_in[t];
+    } else {
+      float gamma;
+      if (p.act_absmax_in) {
+        gamma = p.act_absmax_in[t];  // absmax over the full (unsharded) row, supplied by the caller
+      } else {
+        float mx = 0.f;
+        for (uint32_t i = ctid; i < p.k; i += kCT) {
+          const float v = p.x_dtype == TB_F32 ? static_cast<const float*>(p.x)[size_t(t) * p.k + i]
+                                              : __bfloat162float(static_cast<const __nv_bfloat16*>(p.x)[size_t(t) * p.k + i]);
+          mx = fmaxf(mx, fabsf(v));
+        }
+        for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        if (lane == 0) red_max[warp] = mx;
+        consumer_sync();
+        gamma = 0.f;
+        for (int w2 = 0; w2 < kConsumerWarps; ++w2) gamma = fmaxf(gamma, red_max[w2]);
+        consumer_sync();
+      }
+      scale_q = gamma > 0.f ? __fdiv_rn(127.0f, gamma) : 0.f;
+      if (ctid == 0) act_scale[t] = __fdiv_rn(gamma, 127.0f);
+      for (uint32_t i = ctid; i < p.k; i += kCT) {
+        const float v = p.x_dtype == TB_F32 ? static_cast<const float*>(p.x)[size_t(t) * p.k + i]
+                                            : __bfloat162float(static_cast<const __nv_bfloat16*>(p.x)[size_t(t) * p.k + i]);
+        const float r = fminf(127.f, fmaxf(-128.f, rintf(__fmul_rn(v, scale_q))));
+        xq[t * p.k + i] = int8_t(int(r));
+      }
+    }
+  }
+  consumer_sync();
+
+  // z tables: entry (tile column j, mma, column col = 2*token + hl, lane column c) -> (b0, b1)
+  const uint32_t ncol = 2 * p.m;
+  {
+    const uint32_t entries = p.tpr * T::kMmas * ncol * 4;
+    for (uint32_t e = ctid; e < entries; e += kCT) {
+      const uint32_t c = e & 3, col = (e >> 2) % ncol, rest = (e >> 2) / ncol;
+      const uint32_t mma = rest % T::kMmas, j = rest / T::kMmas;
+      const int8_t* xt = xq + (col >> 1) * p.k + j * 256;
+      const Slot<CODEC> s = slot_of<CODEC>(int(mma), int(c));
+      ztab[e] = make_uint2(z_quad<CODEC>(xt, s, s.d0, int(col & 1)), z_quad<CODEC>(xt, s, s.d1, int(col & 1)));
+    }
+    // accumulator start values: -(sum of operand offsets * z) - (sum of activations of the group)
+    const uint32_t cells = p.m * p.tpr * 2;
+    for (uint32_t e = ctid; e < cells; e += kCT) {
+      const uint32_t v = e & 1, j = (e >> 1) % p.tpr, t = (e >> 1) / p.tpr;
+      const int8_t* xt = xq + t * p.k + j * 256;
+      int sum = 0;
+      for (int i = 0; i < 128; ++i) sum += xt[v * 128 + i];
+      if (CODEC == tbf::kB3) {
+        for (int byte = 0; byte < 52; ++byte)
+          for (int i = 2; i < 5; ++i) sum += z_value<CODEC>(xt, byte >> 2, byte & 3, i, int(v));
+      }
+      cinit[e] = -sum;
+    }
+  }
+  consumer_sync();
+
+  // -------------------------------------------------- consumers: main loop
+  const uint32_t g = lane >> 2, c = lane & 3;
+  const uint32_t rp_per_stage = p.rows_per_stage * p.planes;      // multiple of 16
+  const uint32_t sets = rp_per_stage >> 4;
+  const uint32_t items = p.tpr * sets;
+  const uint32_t per_warp = (items + kConsumerWarps - 1) / kConsumerWarps;
+  const uint32_t item_lo = warp * per_warp, item_hi = min(items, item_lo + per_warp);
+  const uint32_t part_stride = rp_per_stage * p.m;                // floats per warp slice
+  const bool lane_has_token = c < p.m;
+  const uint32_t groups_per_row = p.tpr * 2;
+
+  for (uint32_t it = 0; it < my_blocks; ++it) {
+    const uint32_t s = it % p.stages;
+    float* my_part = part + ((it & 1) * kConsumerWarps + warp) * part_stride;
+    for (uint32_t i = lane; i < part_stride; i += 32) my_part[i] = 0.f;
+    __syncwarp();
+    const bool landed = mbar_wait(&full_bar[s], (it / p.stages) & 1, &abort_flag);
+    if (!landed) {
+      abort_flag = 1;
+      if (lane == 0 && atomicOr(&p.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) { p.status[TBS_INFO0] = it; p.status[TBS_INFO1] = s; }
+    }
+    const uint32_t* words = reinterpret_cast<const uint32_t*>(ring + size_t(s) * p.stage_bytes);
+    const uint32_t* scl = reinterpret_cast<const uint32_t*>(scale_ring + size_t(s) * p.scale_stage_bytes);
+    const uint64_t blk = blockIdx.x + uint64_t(it) * gridDim.x;
+    const uint32_t row0 = uint32_t(blk) * p.rows_per_stage;
+
+    uint32_t cur_j = 0xffffffffu;
+    uint2 breg[T::kMmas];
+    for (uint32_t item = item_lo; landed && item < item_hi; ++item) {
+      const uint32_t j = item / sets, set = item - j * sets;
+      if (j != cur_j) {
+        cur_j = j;
+        const uint2* zrow = ztab + size_t(j) * T::kMmas * ncol * 4;
+#pragma unroll
+        for (int mm = 0; mm < T::kMmas; ++mm)
+          breg[mm] = g < ncol ? zrow[(mm * ncol + g) * 4 + c] : make_uint2(0u, 0u);
+      }
+      const uint32_t rpa = set * 16 + g, rpb = rpa + 8;
+      const uint32_t na = rpa / p.planes, pa = rpa - na * p.planes;
+      const uint32_t nb = rpb / p.planes, pb = rpb - nb * p.planes;
+      const uint32_t tpa = (na * p.tpr + j) * p.planes + pa, tpb = (nb * p.tpr + j) * p.planes + pb;
+      const uint32_t* wa = words + size_t(tpa) * (T::kPlaneBytes / 4);
+      const uint32_t* wb = words + size_t(tpb) * (T::kPlaneBytes / 4);
+      int acc0[4] = {0, 0, 0, 0}, acc1[4] = {0, 0, 0, 0};
+
+      if (CODEC == tbf::kB3) {
+        uint32_t qa[5], qb[5];
+        b3_quads(wa[c], qa); b3_quads(wb[c], qb);
+        mma_u8s8(acc0, qa[0], qb[0], qa[1], qb[1], breg[0].x, breg[0].y);
+        mma_u8s8(acc0, qa[2], qb[2], qa[3], qb[3], breg[1].x, breg[1].y);
+        mma_u8s8(acc0, qa[4], qb[4], 0u, 0u, breg[2].x, breg[2].y);
+        b3_quads(wa[4 + c], qa); b3_quads(wb[4 + c], qb);
+        mma_u8s8(acc0, qa[0], qb[0], qa[1], qb[1], breg[3].x, breg[3].y);
+        mma_u8s8(acc0, qa[2], qb[2], qa[3], qb[3], breg[4].x, breg[4].y);
+        mma_u8s8(acc0, qa[4], qb[4], 0u, 0u, breg[5].x, breg[5].y);
+        mma_u8s8(acc1, qa[0], qb[0], qa[1], qb[1], breg[6].x, breg[6].y);
+        mma_u8s8(acc1, qa[2], qb[2], qa[3], qb[3], breg[7].x, breg[7].y);
+        mma_u8s8(acc1, qa[4], qb[4], 0u, 0u, breg[8].x, breg[8].y);
+        b3_quads(wa[8 + c], qa); b3_quads(wb[8 + c], qb);
+        mma_u8s8(acc1, qa[0], qb[0], qa[1], qb[1], breg[9].x, breg[9].y);
+        mma_u8s8(acc1, qa[2], qb[2], qa[3], qb[3], breg[10].x, breg[10].y);
+        mma_u8s8(acc1, qa[4], qb[4], 0u, 0u, breg[11].x, breg[11].y);
+        b3_quads(wa[12], qa); b3_quads(wb[12], qb);
+        mma_u8s8(acc1, qa[0], qb[0], qa[1], qb[1], breg[12].x, breg[12].y);
+        mma_u8s8(acc1, qa[2], qb[2], qa[3], qb[3], breg[13].x, breg[13].y);
+        mma_u8s8(acc1, qa[4], qb[4], 0u, 0u, breg[14].x, breg[14].y);
+      } else {
+#pragma unroll
+        for (int sl = 0; sl < 4; ++sl) {
+          const uint32_t va = wa[sl * 4 + c], vb = wb[sl * 4 + c];
+          int (&acc)[4] = sl < 2 ? acc0 : acc1;
+          mma_u8s8(acc, va & 0x03030303u, vb & 0x03030303u, (va >> 2) & 0x03030303u, (vb >> 2) & 0x03030303u,
+                   breg[sl * 2].x, breg[sl * 2].y);
+          mma_u8s8(acc, (va >> 4) & 0x03030303u, (vb >> 4) & 0x03030303u, (va >> 6) & 0x03030303u,
+                   (vb >> 6) & 0x03030303u, breg[sl * 2 + 1].x, breg[sl * 2 + 1].y);
+        }
+      }
+
+      // flush: lane (g,c) holds token c (columns 2c = high part, 2c+1 = low part) for rows g, g+8
+      if (lane_has_token) {
+        const int ci0 = cinit[(c * p.tpr + j) * 2], ci1 = cinit[(c * p.tpr + j) * 2 + 1];
+        const int ia0 = 4 * acc0[0] + acc0[1] + ci0, ia1 = 4 * acc1[0] + acc1[1] + ci1;
+        const int ib0 = 4 * acc0[2] + acc0[3] + ci0, ib1 = 4 * acc1[2] + acc1[3] + ci1;
+        const __half2 sa = *reinterpret_cast<const __half2*>(&scl[tpa]);
+        const __half2 sb = *reinterpret_cast<const __half2*>(&scl[tpb]);
+        const float va = __fadd_rn(__fmul_rn(float(ia0), __low2float(sa)), __fmul_rn(float(ia1), __high2float(sa)));
+        const float vb = __fadd_rn(__fmul_rn(float(ib0), __low2float(sb)), __fmul_rn(float(ib1), __high2float(sb)));
+        my_part[rpa * p.m + c] += va;
+        my_part[rpb * p.m + c] += vb;
+        if (p.acc_dump) {
+          const uint32_t tok = p.dump_token_offset + c;
+          if (row0 + na < p.n) {
+            int32_t* d = p.acc_dump + ((size_t(tok) * p.n + row0 + na) * groups_per_row + 2 * j) * p.planes + pa;
+            d[0] = ia0; d[p.planes] = ia1;
+          }
+          if (row0 + nb < p.n) {
+            int32_t* d = p.acc_dump + ((size_t(tok) * p.n + row0 + nb) * groups_per_row + 2 * j) * p.planes + pb;
+            d[0] = ib0; d[p.planes] = ib1;
+          }
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty_bar[s]);   // slot may be refilled
+
+    // combine the warps' partial sums (fixed order: plane ascending, warp ascending).  Every
+    // consumer warp reaches this barrier, also after a failed wait, and all leave together.
+    consumer_sync();
+    if (abort_flag) return;
+    const float* stage_part = part + (it & 1) * kConsumerWarps * part_stride;
+    for (uint32_t e = ctid; e < p.rows_per_stage * p.m; e += kCT) {
+      const uint32_t t = e / p.rows_per_stage, r = e - t * p.rows_per_stage;
+      if (row0 + r >= p.n) continue;
+      float sum = 0.f;
+      for (uint32_t q = 0; q < p.planes; ++q)
+        for (int w2 = 0; w2 < kConsumerWarps; ++w2)
+          sum = __fadd_rn(sum, stage_part[w2 * part_stride + (r * p.planes + q) * p.m + t]);
+      float out = __fmul_rn(sum, act_scale[t]);
+      if (p.row_scale) out = __fmul_rn(out, p.row_scale[row0 + r]);
+      const size_t idx = size_t(t) * p.y_row_stride + row0 + r;
+      if (p.y_dtype == TB_F32) static_cast<float*>(p.y)[idx] = out;
+      else static_cast<__nv_bfloat16*>(p.y)[idx] = __float2bfloat16_rn(out);
+    }
+  }
+}
+
+uint32_t round_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
+
+// Shared-memory layout for (weights, m); returns total bytes or 0 when it cannot fit.
+size_t layout(const tb_weights* w, uint32_t m, int max_smem, DecodeParams* p) {
+  const DecodePlan& pl = w->plan;
+  const uint32_t tpr = uint32_t(w->k / 256), planes = w->uniform_planes;
+  const uint32_t mmas = w->codec == tbf::kB3 ? 15 : 8;
+  uint32_t off = 0;
+  const uint32_t xq = round_up(m * uint32_t(w->k), 16);
+  const uint32_t z = tpr * mmas * (2 * m) * 4 * 8;
+  const uint32_t ci = round_up(m * tpr * 2 * 4, 16);
+  const uint32_t part = round_up(2 * kConsumerWarps * pl.rows_per_stage * planes * m * 4, 16);
+  const uint32_t fixed = xq + z + ci + part + 64;
+  const uint32_t per_stage = pl.stage_bytes + pl.scale_stage_bytes;
+  if (fixed + 2 * per_stage > uint32_t(max_smem)) return 0;
+  uint32_t stages = std::min<uint32_t>(kMaxStages, (uint32_t(max_smem) - fixed) / per_stage);
+  if (p) {
+    p->stages = stages;
+    p->off_ring = off; off += stages * pl.stage_bytes;
+    p->off_scale_ring = off; off += stages * pl.scale_stage_bytes;
+    p->off_xq = off; off += xq;
+    p->off_z = off; off += z;
+    p->off_cinit = off; off += ci;
+    p->off_part = off; off += part;
+    p->off_actscale = off; off += 64;
+  }
+  return size_t(fixed) + size_t(stages) * per_stage;
+}
+
+}  // namespace
+
+void tb_make_decode_plan(tb_weights* w, int max_smem) {
+  DecodePlan pl{};
+  if (!w->fast) { w->plan = pl; return; }
+  const uint32_t planes = w->uniform_planes, tpr = uint32_t(w->k / 256);
+  const uint32_t pb = w->codec == tbf::kB3 ? 52 : 64;
+  pl.row_bytes = tpr * planes * pb;
+  const uint32_t base = planes == 2 ? 8 : 16;   // R % 4 == 0 and R*planes % 16 == 0
+  const uint32_t target = 40 * 1024;
+  uint32_t r = std::max(base, (target / pl.row_bytes) / base * base);
+  r = std::min<uint32_t>(r, 128);
+  // keep enough blocks to cover every SM at least three times when the tensor allows it
+  while (r > base && (w->n + r - 1) / r < 444) r -= base;
+  pl.rows_per_stage = r;
+  pl.stage_bytes = r * pl.row_bytes;
+  pl.scale_stage_bytes = r * tpr * planes * 4;
+  pl.blocks = uint32_t((w->n + r - 1) / r);
+  (void)max_smem;
+  w->plan = pl;
+}
+
+bool tb_decode_supported(const tb_weights* w, uint32_t m, int max_smem, size_t* smem_bytes) {
+  if (!w->fast || m < 1 || m > 4) return false;
+  const size_t bytes = layout(w, m, max_smem, nullptr);
+  if (!bytes) return false;
+  if (smem_bytes) *smem_bytes = bytes;
+  return true;
+}
+
+cudaError_t tb_launch_decode(const DecodeArgs& a, int sm_count, int max_smem, cudaStream_t stream) {
+  const tb_weights* w = a.w;
+  DecodeParams p{};
+  const size_t smem = layout(w, a.m, max_smem, &p);
+  if (!smem) return cudaErrorInvalidConfiguration;
+  p.payload = w->d_payload; p.scales = w->d_scales;
+  p.x = a.x; p.act_scale_in = a.act_scale_in; p.act_absmax_in = a.act_absmax_in; p.y = a.y; p.acc_dump = a.acc_dump; p.row_scale = a.row_scale;
+  p.status = a.status;
+  p.m = a.m; p.n = uint32_t(w->n); p.k = uint32_t(w->k); p.planes = w->uniform_planes; p.tpr = uint32_t(w->k / 256);
+  p.rows_per_stage = w->plan.rows_per_stage; p.row_bytes = w->plan.row_bytes;
+  p.stage_bytes = w->plan.stage_bytes; p.scale_stage_bytes = w->plan.scale_stage_bytes; p.blocks = w->plan.blocks;
+  p.x_dtype = uint32_t(a.x_dtype); p.y_dtype = uint32_t(a.y_dtype); p.y_row_stride = a.y_row_stride;
+  p.dump_token_offset = a.dump_token_offset; p.dump_tokens_total = a.dump_tokens_total;
+  p.pdl = a.pdl ? 1u : 0u;
+  auto kernel = w->codec == tbf::kB3 ? decode_kernel<tbf::kB3> : decode_kernel<tbf::kD2>;
+  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+  if (err != cudaSuccess) return err;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(std::min<uint32_t>(p.blocks, uint32_t(sm_count)));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = a.pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, p);
+}

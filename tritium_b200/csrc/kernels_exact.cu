@@ -1,0 +1,239 @@
+// Bit-exact SALT V2 forward for any valid layout (ragged plane counts, g64/g128, rows that
+// straddle tiles, D2/B3/S34), plus row gather.
+//
+// Arithmetic contract (crates/tritium-cpu/src/salt_v2.rs:10-23,316-423): per output row, walk
+// the scale-group segments in ascending coefficient order; per segment and per plane (ascending)
+// fold ga = ga ± x[col] sequentially in fp32, multiply once by the f16 scale, add to the row
+// accumulator.  No FMA, no reassociation.  Here one warp owns one output row: each lane folds
+// whole (segment, plane) sums on its own — the sequential order inside a sum is kept — and the
+// contributions are then added in segment/plane order, so the result is bit-identical.
+//
+// Compiled with --fmad=false; the explicit _rn intrinsics pin the rounding as well.
+#include <cuda_fp16.h>
+
+#include "tb_internal.h"
+
+namespace {
+
+constexpr int kWarpsPerBlock = 8;
+constexpr int kTokens = 4;  // tokens folded per decode pass
+
+struct ExactParams {
+  const uint8_t* payload; const uint16_t* scales; const uint8_t* meta; const uint32_t* tile_rank;
+  uint64_t map_bytes, coeffs, tiles;
+  uint32_t terminal, uniform_planes, codec, group, m, n, k;
+  const float* x; float* y; const float* row_scale;
+  uint32_t* status;
+};
+
+__device__ __forceinline__ uint32_t plane_bytes_dev(uint32_t codec, uint32_t len) {
+  if (codec == tbf::kD2) return (len + 3u) >> 2;
+  if (codec == tbf::kB3) return (len + 4u) / 5u;
+  return (((len + 3u) >> 2) * 5u + 7u) >> 3;
+}
+
+__device__ __forceinline__ uint32_t planes_of(const ExactParams& p, uint64_t tile) {
+  if (p.uniform_planes) return p.uniform_planes;
+  const uint64_t bit = tile * 2;
+  const uint32_t code = bit < p.map_bytes * 8 ? (p.meta[bit >> 3] >> (bit & 7)) & 3u
+                                              : (p.terminal >> (bit - p.map_bytes * 8)) & 3u;
+  return code + 1;
+}
+
+__device__ __forceinline__ uint64_t rank_of(const ExactParams& p, uint64_t tile) {
+  return p.uniform_planes ? tile * p.uniform_planes : p.tile_rank[tile];
+}
+
+// One trit of a plane whose bytes start at `base`.  `lut` maps a B3 byte to five 2-bit digits.
+__device__ __forceinline__ int trit_at(const uint8_t* base, uint32_t codec, uint32_t local,
+                                       const uint16_t* lut) {
+  if (codec == tbf::kD2) return int((base[local >> 2] >> (2 * (local & 3))) & 3u) - 1;
+  if (codec == tbf::kB3) {
+    const uint32_t byte = local / 5u;
+    return int((lut[base[byte]] >> (2 * (local - byte * 5u))) & 3u) - 1;
+  }
+  const uint32_t bit = (local >> 2) * 5u, byte = bit >> 3;
+  const uint32_t word = base[byte] | (uint32_t(base[byte + 1]) << 8);  // arena is padded by one byte
+  const uint32_t code = (word >> (bit & 7)) & 31u, slot = local & 3u, zero = code & 3u;
+  if (slot == zero) return 0;
+  return (code >> (2 + slot - (slot > zero))) & 1u ? 1 : -1;
+}
+
+__global__ void __launch_bounds__(kWarpsPerBlock * 32) salt_v2_exact_kernel(const ExactParams p) {
+  __shared__ uint16_t lut[243];
+  for (int b = threadIdx.x; b < 243; b += blockDim.x) {
+    int v = b; uint32_t packed = 0;
+    for (int i = 0; i < 5; ++i) { packed |= uint32_t(v % 3) << (2 * i); v /= 3; }
+    lut[b] = uint16_t(packed);
+  }
+  __syncthreads();
+  const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t row = blockIdx.x * kWarpsPerBlock + warp;
+  const uint32_t m0 = blockIdx.y * kTokens;
+  if (row >= p.n) return;
+  const uint32_t tokens = min(uint32_t(kTokens), p.m - m0);
+  const uint64_t row_base = uint64_t(row) * p.k, row_end = row_base + p.k;
+  const uint32_t full_bytes = plane_bytes_dev(p.codec, 256), full_scales = 256u / p.group;
+
+  float acc[kTokens];
+#pragma unroll
+  for (int t = 0; t < kTokens; ++t) acc[t] = 0.f;
+  bool bad = false;
+  uint32_t bad_col = 0;
+
+  // Segment s of this row: boundaries are the row start, every tile-local group boundary, and
+  // the row end.  first_boundary = distance from the row start to the next group boundary.
+  const uint32_t head = p.group - uint32_t(row_base % p.group);  // group divides 256
+  const uint32_t first_len = min(head, p.k);
+  const uint32_t segments = 1 + (p.k > first_len ? (p.k - first_len + p.group - 1) / p.group : 0);
+
+  for (uint32_t seg0 = 0; seg0 < segments; seg0 += 32) {
+    const uint32_t seg = seg0 + lane;
+    float contrib[3][kTokens];
+    uint32_t planes = 0;
+#pragma unroll
+    for (int q = 0; q < 3; ++q)
+#pragma unroll
+      for (int t = 0; t < kTokens; ++t) contrib[q][t] = 0.f;
+    if (seg < segments) {
+      const uint32_t col0 = seg == 0 ? 0 : first_len + (seg - 1) * p.group;
+      const uint32_t len = seg == 0 ? first_len : min(p.group, p.k - col0);
+      const uint64_t c = row_base + col0, tile = c >> 8;
+      const uint32_t local0 = uint32_t(c & 255);
+      const uint32_t tlen = uint32_t(min(uint64_t(256), p.coeffs - (tile << 8)));
+      const uint32_t g = local0 / p.group;
+      planes = planes_of(p, tile);
+      const uint64_t rank = rank_of(p, tile);
+      const uint32_t cur_bytes = plane_bytes_dev(p.codec, tlen);
+      const uint32_t cur_scales = (tlen + p.group - 1) / p.group;
+      for (uint32_t q = 0; q < planes; ++q) {
+        const uint8_t* base = p.payload + rank * full_bytes + uint64_t(q) * cur_bytes;
+        const float scale = __half2float(__ushort_as_half(p.scales[rank * full_scales + q * cur_scales + g]));
+        float ga[kTokens];
+#pragma unroll
+        for (int t = 0; t < kTokens; ++t) ga[t] = 0.f;
+        for (uint32_t e = 0; e < len; ++e) {
+          const int trit = trit_at(base, p.codec, local0 + e, lut);
+          if (trit == 0) continue;
+#pragma unroll
+          for (int t = 0; t < kTokens; ++t)
+            if (t < int(tokens)) {
+              const float xv = p.x[uint64_t(m0 + t) * p.k + col0 + e];
+              ga[t] = trit > 0 ? __fadd_rn(ga[t], xv) : __fsub_rn(ga[t], xv);
+              if (!isfinite(ga[t]) && !bad) { bad = true; bad_col = col0 + e; }
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < kTokens; ++t) {
+          contrib[q][t] = __fmul_rn(ga[t], scale);
+          if (!isfinite(contrib[q][t]) && !bad) { bad = true; bad_col = col0 + len - 1; }
+        }
+      }
+      (void)row_end;
+    }
+    // ordered fold: segment ascending, plane ascending
+    for (int l = 0; l < 32; ++l) {
+      const uint32_t lp = __shfl_sync(0xffffffffu, planes, l);
+      if (lp == 0) break;  // uniform: lanes past the last segment hold zero planes
+#pragma unroll
+      for (int q = 0; q < 3; ++q) {
+        if (uint32_t(q) < lp) {
+#pragma unroll
+          for (int t = 0; t < kTokens; ++t) {
+            const float v = __shfl_sync(0xffffffffu, contrib[q][t], l);
+            acc[t] = __fadd_rn(acc[t], v);
+          }
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < kTokens; ++t)
+    if (!isfinite(acc[t]) && !bad) { bad = true; bad_col = p.k - 1; }
+  if (__any_sync(0xffffffffu, bad)) {
+    if (bad && atomicOr(&p.status[TBS_FLAGS], TBF_NONFINITE_OUT) == 0) {
+      p.status[TBS_INFO0] = row;
+      p.status[TBS_INFO1] = bad_col;
+    }
+  }
+  if (lane == 0) {
+#pragma unroll
+    for (int t = 0; t < kTokens; ++t)
+      if (t < int(tokens)) {
+        float v = acc[t];
+        if (p.row_scale) v = __fmul_rn(v, p.row_scale[row]);
+        p.y[uint64_t(m0 + t) * p.n + row] = v;
+      }
+  }
+}
+
+__global__ void gather_rows_kernel(const ExactParams p, const uint32_t* rows, uint32_t count, float* out) {
+  __shared__ uint16_t lut[243];
+  for (int b = threadIdx.x; b < 243; b += blockDim.x) {
+    int v = b; uint32_t packed = 0;
+    for (int i = 0; i < 5; ++i) { packed |= uint32_t(v % 3) << (2 * i); v /= 3; }
+    lut[b] = uint16_t(packed);
+  }
+  __syncthreads();
+  const uint64_t idx = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= uint64_t(count) * p.k) return;
+  const uint32_t which = uint32_t(idx / p.k), col = uint32_t(idx % p.k);
+  const uint64_t c = uint64_t(rows[which]) * p.k + col, tile = c >> 8;
+  const uint32_t local = uint32_t(c & 255);
+  const uint32_t tlen = uint32_t(min(uint64_t(256), p.coeffs - (tile << 8)));
+  const uint32_t full_bytes = plane_bytes_dev(p.codec, 256), cur_bytes = plane_bytes_dev(p.codec, tlen);
+  const uint32_t full_scales = 256u / p.group, cur_scales = (tlen + p.group - 1) / p.group;
+  const uint64_t rank = rank_of(p, tile);
+  float w = 0.f;
+  for (uint32_t q = 0; q < planes_of(p, tile); ++q) {
+    const int trit = trit_at(p.payload + rank * full_bytes + uint64_t(q) * cur_bytes, p.codec, local, lut);
+    const float scale = __half2float(__ushort_as_half(p.scales[rank * full_scales + q * cur_scales + local / p.group]));
+    w = __fadd_rn(w, __fmul_rn(float(trit), scale));
+  }
+  out[idx] = w;
+}
+
+__global__ void check_finite_kernel(const float* x, uint64_t count, uint32_t* status) {
+  const uint64_t stride = uint64_t(gridDim.x) * blockDim.x;
+  for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += stride)
+    if (!isfinite(x[i]) && atomicOr(&status[TBS_FLAGS], TBF_NONFINITE_ACT) == 0) {
+      status[TBS_INFO0] = uint32_t(i);
+      status[TBS_INFO1] = __float_as_uint(x[i]);
+    }
+}
+
+ExactParams make_params(const tb_weights* w) {
+  ExactParams p{};
+  p.payload = w->d_payload; p.scales = w->d_scales; p.meta = w->d_meta; p.tile_rank = w->d_tile_rank;
+  p.map_bytes = w->map_bytes; p.coeffs = w->n * w->k; p.tiles = w->tiles;
+  p.terminal = w->terminal_map; p.uniform_planes = w->uniform_planes;
+  p.codec = uint32_t(w->codec); p.group = w->group; p.n = uint32_t(w->n); p.k = uint32_t(w->k);
+  return p;
+}
+
+}  // namespace
+
+cudaError_t tb_launch_exact(const ExactArgs& a, cudaStream_t stream) {
+  ExactParams p = make_params(a.w);
+  p.x = a.x; p.y = a.y; p.m = a.m; p.row_scale = a.row_scale; p.status = a.status;
+  if (a.m == 0 || p.n == 0) return cudaSuccess;
+  const dim3 grid((p.n + kWarpsPerBlock - 1) / kWarpsPerBlock, (a.m + kTokens - 1) / kTokens);
+  salt_v2_exact_kernel<<<grid, kWarpsPerBlock * 32, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
+cudaError_t tb_launch_gather_rows(const tb_weights* w, const uint32_t* rows, uint32_t count, float* out,
+                                  cudaStream_t stream) {
+  ExactParams p = make_params(w);
+  const uint64_t total = uint64_t(count) * p.k;
+  if (!total) return cudaSuccess;
+  gather_rows_kernel<<<unsigned((total + 255) / 256), 256, 0, stream>>>(p, rows, count, out);
+  return cudaGetLastError();
+}
+
+cudaError_t tb_launch_check_finite(const float* x, uint64_t count, uint32_t* status, cudaStream_t stream) {
+  if (!count) return cudaSuccess;
+  const unsigned blocks = unsigned(std::min<uint64_t>((count + 255) / 256, 1184));
+  check_finite_kernel<<<blocks, 256, 0, stream>>>(x, count, status);
+  return cudaGetLastError();
+}

@@ -1,0 +1,671 @@
+// C ABI of the B200 backend: handles, uploads, forward entry points, stack driver, host format
+// helpers.  Host logic only; kernels live in kernels_*.cu.
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "tb_internal.h"
+
+// ---------------------------------------------------------------- errors
+namespace {
+thread_local std::string g_last_error;
+thread_local bool g_has_error = false;
+}  // namespace
+
+void tb_set_error(const std::string& message) { g_last_error = message; g_has_error = true; }
+static void clear_error() { g_has_error = false; }
+tb_status tb_fail(tb_status code, const std::string& message) { tb_set_error(message); return code; }
+tb_status tb_cuda_fail(cudaError_t err, const char* what) {
+  const tb_status code = err == cudaErrorMemoryAllocation ? TB_OUT_OF_MEMORY : TB_BACKEND;
+  return tb_fail(code, std::string(what) + ": " + cudaGetErrorName(err) + " (" + cudaGetErrorString(err) + ")");
+}
+static tb_status from_fmt(const tbf::Err& e) {
+  const tb_status code = e.code == 2 ? TB_SHAPE_MISMATCH : e.code == 3 ? TB_UNSUPPORTED_FORMAT : TB_INVALID_INPUT;
+  return tb_fail(code, e.msg);
+}
+#define TB_CUDA(call, what)                                   \
+  do {                                                        \
+    cudaError_t err__ = (call);                               \
+    if (err__ != cudaSuccess) return tb_cuda_fail(err__, what); \
+  } while (0)
+
+extern "C" uint32_t tb_abi_version(void) { return TB_ABI_VERSION; }
+extern "C" const char* tb_last_error(void) { return g_has_error ? g_last_error.c_str() : nullptr; }
+
+// ---------------------------------------------------------------- backend
+namespace {
+
+tb_status ensure(void** ptr, size_t* cap, size_t need, bool pinned_host = false) {
+  if (*cap >= need) return TB_OK;
+  if (*ptr) { if (pinned_host) cudaFreeHost(*ptr); else cudaFree(*ptr); *ptr = nullptr; *cap = 0; }
+  const size_t want = std::max<size_t>(need, 4096);
+  cudaError_t err = pinned_host ? cudaMallocHost(ptr, want) : cudaMalloc(ptr, want);
+  if (err != cudaSuccess) { *ptr = nullptr; return tb_cuda_fail(err, "allocate staging buffer"); }
+  *cap = want;
+  return TB_OK;
+}
+
+tb_status use_device(const tb_backend* b) {
+  TB_CUDA(cudaSetDevice(b->ordinal), "select device");
+  return TB_OK;
+}
+
+}  // namespace
+
+extern "C" tb_status tb_backend_create(int ordinal, tb_backend** out) {
+  clear_error();
+  if (!out) return tb_fail(TB_NULL_ARG, "out is null");
+  *out = nullptr;
+  int count = 0;
+  cudaError_t err = cudaGetDeviceCount(&count);
+  if (err != cudaSuccess || count == 0) {
+    cudaGetLastError();
+    return tb_fail(TB_BACKEND, std::string("no CUDA device available") +
+                                   (err != cudaSuccess ? std::string(": ") + cudaGetErrorString(err) : ""));
+  }
+  if (ordinal < 0 || ordinal >= count) return tb_fail(TB_INVALID_INPUT, "device ordinal out of range");
+  tb_backend* b = new (std::nothrow) tb_backend();
+  if (!b) return tb_fail(TB_OUT_OF_MEMORY, "host allocation failed");
+  b->ordinal = ordinal;
+  auto bail = [&](cudaError_t e, const char* what) { tb_backend_free(b); return tb_cuda_fail(e, what); };
+  if ((err = cudaSetDevice(ordinal)) != cudaSuccess) return bail(err, "select device");
+  if ((err = cudaGetDeviceProperties(&b->prop, ordinal)) != cudaSuccess) return bail(err, "query device");
+  if (b->prop.major != 10) {
+    const std::string msg = "device " + std::string(b->prop.name) + " is sm_" + std::to_string(b->prop.major) +
+                            std::to_string(b->prop.minor) + "; this backend carries sm_100a code only";
+    tb_backend_free(b);
+    return tb_fail(TB_BACKEND, msg);
+  }
+  if ((err = cudaStreamCreateWithFlags(&b->stream, cudaStreamNonBlocking)) != cudaSuccess) return bail(err, "create stream");
+  if ((err = cudaMalloc(&b->d_status, 8 * sizeof(uint32_t))) != cudaSuccess) return bail(err, "allocate status");
+  if ((err = cudaMemset(b->d_status, 0, 8 * sizeof(uint32_t))) != cudaSuccess) return bail(err, "clear status");
+  if ((err = cudaMallocHost(&b->h_status, 8 * sizeof(uint32_t))) != cudaSuccess) return bail(err, "allocate status mirror");
+  cudaDeviceGetAttribute(&b->max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, ordinal);
+  const unsigned char* u = reinterpret_cast<const unsigned char*>(b->prop.uuid.bytes);
+  std::snprintf(b->physical_id, sizeof b->physical_id,
+                "b200:%d:GPU-%02x%02x%02x%02x-%02x%02x-%02x%02x-%02x%02x-%02x%02x%02x%02x%02x%02x", ordinal, u[0], u[1],
+                u[2], u[3], u[4], u[5], u[6], u[7], u[8], u[9], u[10], u[11], u[12], u[13], u[14], u[15]);
+  *out = b;
+  return TB_OK;
+}
+
+extern "C" void tb_backend_free(tb_backend* b) {
+  if (!b) return;
+  cudaSetDevice(b->ordinal);
+  if (b->stream) { cudaStreamSynchronize(b->stream); cudaStreamDestroy(b->stream); }
+  cudaFree(b->d_status); cudaFreeHost(b->h_status);
+  cudaFree(b->d_x); cudaFree(b->d_y); cudaFree(b->d_aux); cudaFree(b->d_q); cudaFreeHost(b->h_pin);
+  delete b;
+}
+
+extern "C" tb_status tb_backend_caps(const tb_backend* b, tb_caps* out) {
+  clear_error();
+  if (!b || !out) return tb_fail(TB_NULL_ARG, "null argument");
+  std::memset(out, 0, sizeof *out);
+  std::snprintf(out->backend, sizeof out->backend, "b200");
+  std::snprintf(out->device_name, sizeof out->device_name, "%s", b->prop.name);
+  std::snprintf(out->device_id, sizeof out->device_id, "b200:%d", b->ordinal);
+  std::snprintf(out->physical_id, sizeof out->physical_id, "%s", b->physical_id);
+  std::snprintf(out->features, sizeof out->features, "sm_100a,salt_v2_d2,salt_v2_b3,salt_v2_s34,tq2_0,int8_tcgen05");
+  out->total_memory_bytes = b->prop.totalGlobalMem;
+  out->sm_count = uint32_t(b->prop.multiProcessorCount);
+  out->supports_imma = 1;
+  out->supports_fp8 = 1;
+  return TB_OK;
+}
+
+extern "C" tb_status tb_backend_synchronize(tb_backend* b) {
+  clear_error();
+  if (!b) return tb_fail(TB_NULL_ARG, "backend is null");
+  if (tb_status s = use_device(b)) return s;
+  TB_CUDA(cudaStreamSynchronize(b->stream), "synchronize stream");
+  return TB_OK;
+}
+
+extern "C" tb_status tb_backend_check(tb_backend* b, void* stream) {
+  clear_error();
+  if (!b) return tb_fail(TB_NULL_ARG, "backend is null");
+  if (tb_status s = use_device(b)) return s;
+  cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : b->stream;
+  TB_CUDA(cudaMemcpyAsync(b->h_status, b->d_status, 8 * sizeof(uint32_t), cudaMemcpyDeviceToHost, st), "read status");
+  TB_CUDA(cudaMemsetAsync(b->d_status, 0, 8 * sizeof(uint32_t), st), "clear status");
+  TB_CUDA(cudaStreamSynchronize(st), "synchronize stream");
+  const uint32_t flags = b->h_status[TBS_FLAGS];
+  if (!flags) return TB_OK;
+  char msg[192];
+  if (flags & TBF_WAIT_TIMEOUT) {
+    std::snprintf(msg, sizeof msg, "a bounded device wait gave up (stage %u, barrier %u)", b->h_status[TBS_INFO0], b->h_status[TBS_INFO1]);
+    return tb_fail(TB_TIMEOUT, msg);
+  }
+  if (flags & TBF_NONFINITE_ACT) {
+    std::snprintf(msg, sizeof msg, "SALT V2 activation %u is non-finite (%#010x)", b->h_status[TBS_INFO0], b->h_status[TBS_INFO1]);
+    return tb_fail(TB_INVALID_INPUT, msg);
+  }
+  if (flags & TBF_NONFINITE_OUT) {
+    std::snprintf(msg, sizeof msg, "SALT V2 output row %u became non-finite at column %u", b->h_status[TBS_INFO0], b->h_status[TBS_INFO1]);
+    return tb_fail(TB_INVALID_INPUT, msg);
+  }
+  return tb_fail(TB_BACKEND, "kernel reported an invalid configuration");
+}
+
+// ---------------------------------------------------------------- weights
+namespace {
+
+tb_status upload_resident(tb_backend* b, const tbf::Resident& r, uint64_t source_len, bool is_tq2, uint64_t logical_k,
+                          tb_weights** out) {
+  if (tb_status s = use_device(b)) return s;
+  tb_weights* w = new (std::nothrow) tb_weights();
+  if (!w) return tb_fail(TB_OUT_OF_MEMORY, "host allocation failed");
+  w->owner = b; w->codec = r.codec; w->group = r.group; w->uniform_planes = r.uniform_planes;
+  w->n = r.n; w->k = r.k; w->tiles = r.tiles; w->present_planes = r.present_planes;
+  w->payload_bytes = r.payload.size(); w->scale_count = r.scales.size();
+  w->map_bytes = r.map.size(); w->rank_prefix_bytes = r.rank_prefix.size() * 4;
+  w->terminal_map = r.terminal_map; w->source_len = source_len; w->is_tq2 = is_tq2; w->logical_k = logical_k;
+  w->fast = r.uniform_planes != 0 && r.k % 256 == 0 && r.group == 128 && (r.codec == tbf::kB3 || r.codec == tbf::kD2);
+  tb_make_decode_plan(w, b->max_smem_optin);
+  // Arenas are padded so that the last row block is a full, valid stage: zero-trit bytes
+  // (B3 121, D2 0x55) and zero scales.  The padding is never stored to an output.
+  size_t pay_alloc = r.payload.size() + 64, sc_alloc = r.scales.size() * 2 + 64;
+  if (w->fast) {
+    pay_alloc = std::max<size_t>(pay_alloc, size_t(w->plan.blocks) * w->plan.stage_bytes + 64);
+    sc_alloc = std::max<size_t>(sc_alloc, size_t(w->plan.blocks) * w->plan.scale_stage_bytes + 64);
+  }
+  auto bail = [&](cudaError_t e, const char* what) { tb_weights_free(w); return tb_cuda_fail(e, what); };
+  cudaError_t err;
+  if ((err = cudaMalloc(&w->d_payload, pay_alloc)) != cudaSuccess) return bail(err, "upload SALT V2 payload");
+  if ((err = cudaMalloc(&w->d_scales, sc_alloc)) != cudaSuccess) return bail(err, "upload SALT V2 scales");
+  const int fill = r.codec == tbf::kB3 ? 121 : r.codec == tbf::kD2 ? 0x55 : 0;
+  if ((err = cudaMemsetAsync(w->d_payload, fill, pay_alloc, b->stream)) != cudaSuccess) return bail(err, "pad payload");
+  if ((err = cudaMemsetAsync(w->d_scales, 0, sc_alloc, b->stream)) != cudaSuccess) return bail(err, "pad scales");
+  if ((err = cudaMemcpyAsync(w->d_payload, r.payload.data(), r.payload.size(), cudaMemcpyHostToDevice, b->stream)) != cudaSuccess)
+    return bail(err, "upload SALT V2 payload");
+  if ((err = cudaMemcpyAsync(w->d_scales, r.scales.data(), r.scales.size() * 2, cudaMemcpyHostToDevice, b->stream)) != cudaSuccess)
+    return bail(err, "upload SALT V2 scales");
+  std::vector<uint8_t> meta(r.map);
+  for (uint32_t v : r.rank_prefix) for (int i = 0; i < 4; ++i) meta.push_back(uint8_t(v >> (8 * i)));
+  if ((err = cudaMalloc(&w->d_meta, meta.size() + 16)) != cudaSuccess) return bail(err, "upload SALT V2 compact index");
+  if (!meta.empty() && (err = cudaMemcpyAsync(w->d_meta, meta.data(), meta.size(), cudaMemcpyHostToDevice, b->stream)) != cudaSuccess)
+    return bail(err, "upload SALT V2 compact index");
+  std::vector<uint32_t> ranks;
+  if (!r.uniform_planes) {
+    ranks.resize(size_t(r.tiles));
+    uint32_t acc = 0;
+    for (uint64_t t = 0; t < r.tiles; ++t) { ranks[t] = acc; acc += r.planes_of(t); }
+    if ((err = cudaMalloc(&w->d_tile_rank, ranks.size() * 4)) != cudaSuccess) return bail(err, "upload tile ranks");
+    if ((err = cudaMemcpyAsync(w->d_tile_rank, ranks.data(), ranks.size() * 4, cudaMemcpyHostToDevice, b->stream)) != cudaSuccess)
+      return bail(err, "upload tile ranks");
+  }
+  if ((err = cudaStreamSynchronize(b->stream)) != cudaSuccess) return bail(err, "finish upload");
+  *out = w;
+  return TB_OK;
+}
+
+}  // namespace
+
+extern "C" tb_status tb_tq2_upload(tb_backend* b, const uint8_t* packed, size_t len, uint32_t n, uint32_t k, tb_weights** out) {
+  clear_error();
+  if (!b || !out || (!packed && len)) return tb_fail(TB_NULL_ARG, "null argument");
+  *out = nullptr;
+  if (n == 0 || k == 0) return tb_fail(TB_INVALID_INPUT, "packed len 0: shape must be positive");
+  tbf::Resident r;
+  if (tbf::Err e = tbf::resident_from_tq2(packed, len, n, k, &r)) return from_fmt(e);
+  return upload_resident(b, r, len, true, k, out);
+}
+
+extern "C" tb_status tb_salt_v2_upload(tb_backend* b, tb_codec codec, uint32_t group, uint32_t n, uint32_t k,
+                                       const uint8_t* payload, size_t payload_len, const uint16_t* scales, size_t scale_count,
+                                       const uint8_t* plane_map, size_t map_len, uint32_t terminal, tb_weights** out) {
+  clear_error();
+  if (!b || !out || !payload || !scales || (!plane_map && map_len)) return tb_fail(TB_NULL_ARG, "null argument");
+  *out = nullptr;
+  tbf::Resident r;
+  if (tbf::Err e = tbf::resident_from_arenas(int(codec), group, n, k, payload, payload_len, scales, scale_count, plane_map, map_len, terminal, &r))
+    return from_fmt(e);
+  return upload_resident(b, r, payload_len, false, k, out);
+}
+
+extern "C" tb_status tb_salt_v2_upload_package(tb_backend* b, const uint8_t* package, size_t len, const char* name, tb_weights** out) {
+  clear_error();
+  if (!b || !out || !package || !name) return tb_fail(TB_NULL_ARG, "null argument");
+  *out = nullptr;
+  tbf::Resident r;
+  if (tbf::Err e = tbf::resident_from_package(package, len, name, &r)) return from_fmt(e);
+  return upload_resident(b, r, r.payload.size(), false, r.k, out);
+}
+
+extern "C" tb_status tb_weights_info_get(const tb_weights* w, tb_weights_info* out) {
+  clear_error();
+  if (!w || !out) return tb_fail(TB_NULL_ARG, "null argument");
+  std::memset(out, 0, sizeof *out);
+  out->codec = uint32_t(w->codec); out->group = w->group; out->planes_uniform = w->uniform_planes;
+  out->n = w->n; out->k = w->k; out->tiles = w->tiles; out->present_planes = w->present_planes;
+  out->payload_bytes = w->payload_bytes; out->scale_bytes = w->scale_count * 2; out->map_bytes = w->map_bytes;
+  out->rank_prefix_bytes = w->rank_prefix_bytes; out->source_len_bytes = w->source_len; out->fast_path = w->fast;
+  return TB_OK;
+}
+
+extern "C" void tb_weights_free(tb_weights* w) {
+  if (!w) return;
+  if (w->owner) cudaSetDevice(w->owner->ordinal);
+  cudaFree(w->d_payload); cudaFree(w->d_scales); cudaFree(w->d_meta); cudaFree(w->d_tile_rank);
+  delete w;
+}
+
+// ---------------------------------------------------------------- forward
+namespace {
+
+void fill_receipt(const tb_weights* w, uint32_t m, size_t x_elem, size_t y_elem, uint32_t kernel, uint32_t launches, tb_receipt* r) {
+  if (!r) return;
+  std::memset(r, 0, sizeof *r);
+  r->payload_bytes = w->payload_bytes; r->scale_bytes = w->scale_count * 2; r->map_bytes = w->map_bytes;
+  r->rank_prefix_bytes = w->rank_prefix_bytes;
+  r->activation_bytes = uint64_t(m) * w->k * x_elem; r->output_bytes = uint64_t(m) * w->n * y_elem;
+  r->kernel = kernel; r->launches = launches;
+}
+
+size_t dtype_size(tb_dtype t) { return t == TB_F32 ? 4 : t == TB_BF16 ? 2 : 1; }
+
+tb_status check_handles(const tb_backend* b, const tb_weights* w) {
+  if (!b || !w) return tb_fail(TB_NULL_ARG, "null argument");
+  if (w->owner != b) return tb_fail(TB_INVALID_INPUT, "weights handle belongs to another backend context");
+  return TB_OK;
+}
+
+// Device-pointer dispatch shared by every entry point.  Returns the kernel family used.
+tb_status forward_dev(tb_backend* b, const tb_weights* w, const tb_forward_args& a, cudaStream_t st, tb_receipt* receipt) {
+  if (a.m == 0 || w->n == 0) { fill_receipt(w, 0, 0, 0, 0, 0, receipt); return TB_OK; }
+  if (!a.x || !a.y) return tb_fail(TB_NULL_ARG, "null activation or output pointer");
+  const bool a8 = (a.flags & TB_FWD_A8) != 0 || a.x_dtype == TB_I8;
+  if (!a8) {
+    if (a.x_dtype != TB_F32 || a.y_dtype != TB_F32) return tb_fail(TB_INVALID_INPUT, "the fp32 path takes fp32 activations and outputs");
+    ExactArgs e{w, static_cast<const float*>(a.x), static_cast<float*>(a.y), a.m, a.row_scale, b->d_status};
+    TB_CUDA(tb_launch_check_finite(e.x, uint64_t(a.m) * w->k, b->d_status, st), "launch finite check");
+    TB_CUDA(tb_launch_exact(e, st), "launch salt_v2_exact");
+    fill_receipt(w, a.m, 4, 4, 0, 2, receipt);
+    return TB_OK;
+  }
+  if (a.x_dtype == TB_I8 && !a.act_scale) return tb_fail(TB_NULL_ARG, "int8 activations need act_scale");
+  if (a.y_dtype == TB_I8) return tb_fail(TB_INVALID_INPUT, "output dtype must be fp32 or bf16");
+  if (!w->fast) return tb_fail(TB_UNSUPPORTED_FORMAT, "the int8 path needs uniform plane counts, k % 256 == 0, group 128 and codec D2 or B3");
+  const bool want_prefill = (a.flags & TB_FWD_FORCE_PREFILL) || (a.m > 8 && !(a.flags & TB_FWD_FORCE_DECODE));
+  if (want_prefill && tb_prefill_supported(w, a.m)) {
+    const size_t need = tb_prefill_scratch_bytes(w, a.m);
+    if (b->d_q_cap < need) return tb_fail(TB_OUT_OF_MEMORY, "prefill scratch is not reserved; call through a host entry point or tb_stack first");
+    const uint32_t m_pad = (a.m + 255) / 256 * 256;
+    PrefillArgs pa{w, a.x, a.x_dtype, a.act_scale, a.act_absmax, a.m, a.y, a.y_dtype, a.acc_dump, a.row_scale,
+                   static_cast<int8_t*>(b->d_q), reinterpret_cast<float*>(static_cast<uint8_t*>(b->d_q) + size_t(m_pad) * w->k),
+                   b->d_status};
+    TB_CUDA(tb_launch_prefill(pa, b->prop.multiProcessorCount, st), "launch prefill");
+    fill_receipt(w, a.m, dtype_size(a.x_dtype), dtype_size(a.y_dtype), 2, 2, receipt);
+    return TB_OK;
+  }
+  if (a.flags & TB_FWD_FORCE_PREFILL) return tb_fail(TB_UNSUPPORTED_FORMAT, "the prefill kernel does not take this shape");
+  uint32_t launches = 0;
+  for (uint32_t m0 = 0; m0 < a.m; m0 += 4) {
+    const uint32_t mc = std::min<uint32_t>(4, a.m - m0);
+    if (!tb_decode_supported(w, mc, b->max_smem_optin, nullptr))
+      return tb_fail(TB_UNSUPPORTED_FORMAT, "the decode kernel's shared-memory plan does not fit this shape");
+    DecodeArgs d{};
+    d.w = w; d.x_dtype = a.x_dtype; d.m = mc; d.y_dtype = a.y_dtype; d.y_row_stride = uint32_t(w->n);
+    d.x = static_cast<const uint8_t*>(a.x) + size_t(m0) * w->k * dtype_size(a.x_dtype);
+    d.act_scale_in = a.act_scale ? a.act_scale + m0 : nullptr;
+    d.act_absmax_in = a.act_absmax ? a.act_absmax + m0 : nullptr;
+    d.y = static_cast<uint8_t*>(a.y) + size_t(m0) * w->n * dtype_size(a.y_dtype);
+    d.acc_dump = a.acc_dump; d.dump_token_offset = m0; d.dump_tokens_total = a.m;
+    d.row_scale = a.row_scale; d.status = b->d_status; d.pdl = (a.flags & TB_FWD_PDL) != 0;
+    TB_CUDA(tb_launch_decode(d, b->prop.multiProcessorCount, b->max_smem_optin, st), "launch decode");
+    ++launches;
+  }
+  fill_receipt(w, a.m, dtype_size(a.x_dtype), dtype_size(a.y_dtype), 1, launches, receipt);
+  return TB_OK;
+}
+
+tb_status reserve_prefill(tb_backend* b, const tb_weights* w, uint32_t m) {
+  if (!w->fast || !tb_prefill_supported(w, m)) return TB_OK;
+  return ensure(&b->d_q, &b->d_q_cap, tb_prefill_scratch_bytes(w, m));
+}
+
+// Host-pointer wrapper: stage in, run, check, stage out.  `y` is written only on success.
+tb_status forward_host(tb_backend* b, const tb_weights* w, const void* x, tb_dtype xd, uint32_t m, void* y, tb_dtype yd,
+                       int32_t* acc_dump, const float* row_scale_host, uint32_t flags, tb_receipt* receipt) {
+  if (tb_status s = check_handles(b, w)) return s;
+  if (m == 0 || w->n == 0) { fill_receipt(w, 0, 0, 0, 0, 0, receipt); return TB_OK; }
+  if (!x || !y) return tb_fail(TB_NULL_ARG, "null activation or output pointer");
+  if (tb_status s = use_device(b)) return s;
+  const size_t xb = size_t(m) * w->k * dtype_size(xd), yb = size_t(m) * w->n * dtype_size(yd);
+  const size_t groups = w->k / w->group;
+  const size_t dump_b = acc_dump ? size_t(m) * w->n * groups * w->uniform_planes * 4 : 0;
+  const size_t rs_b = row_scale_host ? w->n * 4 : 0;
+  if (tb_status s = ensure(&b->d_x, &b->d_x_cap, xb)) return s;
+  if (tb_status s = ensure(&b->d_y, &b->d_y_cap, yb)) return s;
+  if (tb_status s = ensure(&b->d_aux, &b->d_aux_cap, dump_b + rs_b + 256)) return s;
+  if (flags & TB_FWD_A8) if (tb_status s = reserve_prefill(b, w, m)) return s;
+  uint8_t* aux = static_cast<uint8_t*>(b->d_aux);
+  TB_CUDA(cudaMemcpyAsync(b->d_x, x, xb, cudaMemcpyHostToDevice, b->stream), "copy activations to device");
+  if (rs_b) TB_CUDA(cudaMemcpyAsync(aux + dump_b, row_scale_host, rs_b, cudaMemcpyHostToDevice, b->stream), "copy scales to device");
+  tb_forward_args a{};
+  a.x = b->d_x; a.x_dtype = xd; a.m = m; a.y = b->d_y; a.y_dtype = yd; a.flags = flags;
+  a.acc_dump = acc_dump ? reinterpret_cast<int32_t*>(aux) : nullptr;
+  a.row_scale = rs_b ? reinterpret_cast<const float*>(aux + dump_b) : nullptr;
+  if (tb_status s = forward_dev(b, w, a, b->stream, receipt)) return s;
+  if (tb_status s = tb_backend_check(b, b->stream)) return s;
+  TB_CUDA(cudaMemcpyAsync(y, b->d_y, yb, cudaMemcpyDeviceToHost, b->stream), "copy output to host");
+  if (dump_b) TB_CUDA(cudaMemcpyAsync(acc_dump, aux, dump_b, cudaMemcpyDeviceToHost, b->stream), "copy accumulators to host");
+  TB_CUDA(cudaStreamSynchronize(b->stream), "synchronize stream");
+  return TB_OK;
+}
+
+tb_status preflight_finite(const float* x, size_t count) {
+  for (size_t i = 0; i < count; ++i)
+    if (!std::isfinite(x[i])) {
+      uint32_t bits;
+      std::memcpy(&bits, &x[i], 4);
+      char msg[96];
+      std::snprintf(msg, sizeof msg, "SALT V2 activation %zu is non-finite (%#010x)", i, bits);
+      return tb_fail(TB_INVALID_INPUT, msg);
+    }
+  return TB_OK;
+}
+
+}  // namespace
+
+extern "C" tb_status tb_salt_v2_forward_exact(tb_backend* b, const tb_weights* w, const float* x, uint32_t m, float* y, tb_receipt* receipt) {
+  clear_error();
+  if (tb_status s = check_handles(b, w)) return s;
+  if (m && w->n && x) if (tb_status s = preflight_finite(x, size_t(m) * w->k)) return s;
+  return forward_host(b, w, x, TB_F32, m, y, TB_F32, nullptr, nullptr, TB_FWD_EXACT, receipt);
+}
+
+extern "C" tb_status tb_linear_forward_f32(tb_backend* b, const tb_weights* w, const float* x, uint32_t m, float* y, tb_receipt* receipt) {
+  clear_error();
+  if (tb_status s = check_handles(b, w)) return s;
+  if (m && w->n && x) if (tb_status s = preflight_finite(x, size_t(m) * w->k)) return s;
+  return forward_host(b, w, x, TB_F32, m, y, TB_F32, nullptr, nullptr, 0, receipt);
+}
+
+extern "C" tb_status tb_linear_forward_a8(tb_backend* b, const tb_weights* w, const void* x, tb_dtype xd, uint32_t m, void* y,
+                                          tb_dtype yd, int32_t* acc_dump, tb_receipt* receipt) {
+  clear_error();
+  if (tb_status s = check_handles(b, w)) return s;
+  if (xd == TB_I8) return tb_fail(TB_INVALID_INPUT, "host int8 activations are not accepted here; pass fp32 or bf16");
+  if (xd == TB_F32 && m && w->n && x) if (tb_status s = preflight_finite(static_cast<const float*>(x), size_t(m) * w->k)) return s;
+  return forward_host(b, w, x, xd, m, y, yd, acc_dump, nullptr, TB_FWD_A8, receipt);
+}
+
+extern "C" tb_status tb_linear_forward_dev(tb_backend* b, const tb_weights* w, const tb_forward_args* args, tb_receipt* receipt) {
+  clear_error();
+  if (tb_status s = check_handles(b, w)) return s;
+  if (!args) return tb_fail(TB_NULL_ARG, "args is null");
+  if (tb_status s = use_device(b)) return s;
+  cudaStream_t st = args->stream ? static_cast<cudaStream_t>(args->stream) : b->stream;
+  return forward_dev(b, w, *args, st, receipt);
+}
+
+extern "C" tb_status tb_backend_reserve(tb_backend* b, const tb_weights* w, uint32_t max_m) {
+  clear_error();
+  if (tb_status s = check_handles(b, w)) return s;
+  if (tb_status s = use_device(b)) return s;
+  return reserve_prefill(b, w, max_m);
+}
+
+extern "C" tb_status tb_salt_v2_gather_rows(tb_backend* b, const tb_weights* w, const uint32_t* rows, size_t count, float* out) {
+  clear_error();
+  if (tb_status s = check_handles(b, w)) return s;
+  if (count == 0) return TB_OK;
+  if (!rows || !out) return tb_fail(TB_NULL_ARG, "null argument");
+  for (size_t i = 0; i < count; ++i)
+    if (rows[i] >= w->n) return tb_fail(TB_INVALID_INPUT, "token_embd row " + std::to_string(rows[i]) + " is out of range");
+  if (tb_status s = use_device(b)) return s;
+  const size_t ob = count * w->k * 4;
+  if (tb_status s = ensure(&b->d_x, &b->d_x_cap, count * 4)) return s;
+  if (tb_status s = ensure(&b->d_y, &b->d_y_cap, ob)) return s;
+  TB_CUDA(cudaMemcpyAsync(b->d_x, rows, count * 4, cudaMemcpyHostToDevice, b->stream), "copy row ids");
+  TB_CUDA(tb_launch_gather_rows(w, static_cast<const uint32_t*>(b->d_x), uint32_t(count), static_cast<float*>(b->d_y), b->stream), "launch gather");
+  TB_CUDA(cudaMemcpyAsync(out, b->d_y, ob, cudaMemcpyDeviceToHost, b->stream), "copy rows to host");
+  TB_CUDA(cudaStreamSynchronize(b->stream), "synchronize stream");
+  return TB_OK;
+}
+
+// ---------------------------------------------------------------- trait path
+namespace {
+tb_status check_trait_shape(const tb_weights* w, uint32_t n, uint32_t k) {
+  if (!w->is_tq2) return tb_fail(TB_INVALID_INPUT, "buffer is not a TQ2_0 upload");
+  if (w->n != n || w->logical_k != k)
+    return tb_fail(TB_SHAPE_MISMATCH, "shape mismatch: expected " + std::to_string(w->n * w->logical_k) + ", got " + std::to_string(uint64_t(n) * k));
+  return TB_OK;
+}
+// Rows are stored padded to whole 256-trit blocks; widen [m,k] to [m,kp] with zeros.
+void pad_rows(const float* src, uint32_t m, uint32_t k, uint64_t kp, std::vector<float>* dst) {
+  dst->assign(size_t(m) * kp, 0.f);
+  for (uint32_t r = 0; r < m; ++r) std::copy(src + size_t(r) * k, src + size_t(r + 1) * k, dst->begin() + size_t(r) * kp);
+}
+}  // namespace
+
+extern "C" tb_status tb_mpgemm(tb_backend* b, const tb_weights* w, const float* act, const float* scales, uint32_t m, uint32_t n,
+                               uint32_t k, float* out) {
+  clear_error();
+  if (tb_status s = check_handles(b, w)) return s;
+  if (tb_status s = check_trait_shape(w, n, k)) return s;
+  if (m == 0 || n == 0) return TB_OK;
+  if (!act || !scales || !out) return tb_fail(TB_NULL_ARG, "null argument");
+  // Integer-valued activations in [-128,127] (what TernaryLinear::forward hands over after its
+  // host quantisation) take the exact int8 kernel with a unit token scale.
+  bool a8 = true;
+  for (size_t i = 0; i < size_t(m) * k && a8; ++i) a8 = act[i] >= -128.f && act[i] <= 127.f && act[i] == std::trunc(act[i]);
+  std::vector<float> padded;
+  const float* x = act;
+  if (w->k != k) { pad_rows(act, m, k, w->k, &padded); x = padded.data(); }
+  if (!a8) return forward_host(b, w, x, TB_F32, m, out, TB_F32, nullptr, scales, 0, nullptr);
+  // int8 path: quantising integers with absmax 127 reproduces them exactly only when the row
+  // maximum is 127, so feed the codes directly as int8 with act_scale = 1.
+  if (tb_status s = use_device(b)) return s;
+  std::vector<int8_t> q(size_t(m) * w->k);
+  for (size_t i = 0; i < q.size(); ++i) q[i] = int8_t(int(x[i]));
+  const size_t yb = size_t(m) * n * 4;
+  if (tb_status s = ensure(&b->d_x, &b->d_x_cap, q.size())) return s;
+  if (tb_status s = ensure(&b->d_y, &b->d_y_cap, yb)) return s;
+  if (tb_status s = ensure(&b->d_aux, &b->d_aux_cap, size_t(n) * 4 + size_t(m) * 4 + 256)) return s;
+  if (tb_status s = reserve_prefill(b, w, m)) return s;
+  float* d_rs = static_cast<float*>(b->d_aux);
+  float* d_as = d_rs + n;
+  std::vector<float> ones(m, 1.0f);
+  TB_CUDA(cudaMemcpyAsync(b->d_x, q.data(), q.size(), cudaMemcpyHostToDevice, b->stream), "copy activations to device");
+  TB_CUDA(cudaMemcpyAsync(d_rs, scales, size_t(n) * 4, cudaMemcpyHostToDevice, b->stream), "copy scales to device");
+  TB_CUDA(cudaMemcpyAsync(d_as, ones.data(), size_t(m) * 4, cudaMemcpyHostToDevice, b->stream), "copy token scales to device");
+  tb_forward_args a{};
+  a.x = b->d_x; a.x_dtype = TB_I8; a.act_scale = d_as; a.m = m; a.y = b->d_y; a.y_dtype = TB_F32; a.row_scale = d_rs; a.flags = TB_FWD_A8;
+  if (tb_status s = forward_dev(b, w, a, b->stream, nullptr)) return s;
+  if (tb_status s = tb_backend_check(b, b->stream)) return s;
+  TB_CUDA(cudaMemcpyAsync(out, b->d_y, yb, cudaMemcpyDeviceToHost, b->stream), "copy output to host");
+  TB_CUDA(cudaStreamSynchronize(b->stream), "synchronize stream");
+  return TB_OK;
+}
+
+extern "C" tb_status tb_mpgemm_with_act_quant(tb_backend* b, const tb_weights* w, const float* act, const float* scales, uint32_t m,
+                                              uint32_t n, uint32_t k, float* out) {
+  clear_error();
+  if (tb_status s = check_handles(b, w)) return s;
+  if (tb_status s = check_trait_shape(w, n, k)) return s;
+  if (m == 0 || n == 0) return TB_OK;
+  if (!act || !scales || !out) return tb_fail(TB_NULL_ARG, "null argument");
+  std::vector<float> padded;
+  const float* x = act;
+  if (w->k != k) { pad_rows(act, m, k, w->k, &padded); x = padded.data(); }
+  return forward_host(b, w, x, TB_F32, m, out, TB_F32, nullptr, scales, TB_FWD_A8, nullptr);
+}
+
+// ---------------------------------------------------------------- layer stack
+struct tb_stack {
+  tb_backend* backend = nullptr;
+  std::vector<const tb_weights*> layers;
+  std::vector<uint8_t> chain;
+  uint32_t max_m = 0;
+  void* buf[2] = {nullptr, nullptr};   // ping-pong activations (bf16)
+  size_t buf_bytes = 0;
+};
+
+extern "C" tb_status tb_stack_create(tb_backend* b, const tb_weights* const* weights, const uint8_t* chain, uint32_t layers,
+                                     uint32_t max_m, tb_stack** out) {
+  clear_error();
+  if (!b || !weights || !out) return tb_fail(TB_NULL_ARG, "null argument");
+  *out = nullptr;
+  if (!layers || !max_m) return tb_fail(TB_INVALID_INPUT, "a stack needs at least one layer and one token");
+  if (tb_status s = use_device(b)) return s;
+  tb_stack* st = new (std::nothrow) tb_stack();
+  if (!st) return tb_fail(TB_OUT_OF_MEMORY, "host allocation failed");
+  st->backend = b; st->max_m = max_m;
+  uint64_t widest = 0;
+  for (uint32_t i = 0; i < layers; ++i) {
+    const tb_weights* w = weights[i];
+    if (!w || w->owner != b || !w->fast) { delete st; return tb_fail(TB_INVALID_INPUT, "stack layers must be fast-path weights of this backend"); }
+    const bool chained = chain && chain[i];
+    if (chained && (i == 0 || weights[i - 1]->n != w->k)) { delete st; return tb_fail(TB_SHAPE_MISMATCH, "chained layer input width differs from the previous output width"); }
+    if (!chained && i > 0 && w->k != weights[0]->k) { delete st; return tb_fail(TB_SHAPE_MISMATCH, "unchained layers read the stack input and must share its width"); }
+    st->layers.push_back(w);
+    st->chain.push_back(chained ? 1 : 0);
+    widest = std::max<uint64_t>(widest, w->n);
+    if (tb_status s = reserve_prefill(b, w, max_m)) { delete st; return s; }
+  }
+  st->buf_bytes = size_t(max_m) * widest * 2;
+  for (int i = 0; i < 2; ++i) {
+    cudaError_t err = cudaMalloc(&st->buf[i], st->buf_bytes);
+    if (err != cudaSuccess) { tb_stack_free(st); return tb_cuda_fail(err, "allocate stack activations"); }
+  }
+  *out = st;
+  return TB_OK;
+}
+
+extern "C" tb_status tb_stack_forward_dev(tb_stack* st, const void* x, tb_dtype xd, uint32_t m, void* y_last, tb_dtype yd,
+                                          uint32_t flags, void* stream) {
+  clear_error();
+  if (!st || !x) return tb_fail(TB_NULL_ARG, "null argument");
+  if (m == 0) return TB_OK;
+  if (m > st->max_m) return tb_fail(TB_SHAPE_MISMATCH, "token count exceeds the stack's max_m");
+  tb_backend* b = st->backend;
+  if (tb_status s = use_device(b)) return s;
+  cudaStream_t cs = stream ? static_cast<cudaStream_t>(stream) : b->stream;
+  const size_t n_layers = st->layers.size();
+  for (size_t i = 0; i < n_layers; ++i) {
+    tb_forward_args a{};
+    const bool chained = st->chain[i] != 0, last = i + 1 == n_layers;
+    a.x = chained ? st->buf[(i + 1) & 1] : x;
+    a.x_dtype = chained ? TB_BF16 : xd;
+    a.m = m;
+    a.y = (last && y_last) ? y_last : st->buf[i & 1];
+    a.y_dtype = (last && y_last) ? yd : TB_BF16;
+    a.flags = TB_FWD_A8 | (flags & (TB_FWD_PDL | TB_FWD_FORCE_DECODE | TB_FWD_FORCE_PREFILL));
+    a.stream = cs;
+    if (tb_status s = forward_dev(b, st->layers[i], a, cs, nullptr)) return s;
+  }
+  return TB_OK;
+}
+
+extern "C" uint64_t tb_stack_bytes_per_step(const tb_stack* st, uint32_t m) {
+  if (!st) return 0;
+  uint64_t total = 0;
+  for (const tb_weights* w : st->layers)
+    total += w->payload_bytes + w->scale_count * 2 + w->map_bytes + w->rank_prefix_bytes + uint64_t(m) * (w->k + w->n) * 2;
+  return total;
+}
+
+extern "C" void tb_stack_free(tb_stack* st) {
+  if (!st) return;
+  if (st->backend) cudaSetDevice(st->backend->ordinal);
+  cudaFree(st->buf[0]); cudaFree(st->buf[1]);
+  delete st;
+}
+
+// ---------------------------------------------------------------- tensor-parallel shards (host)
+extern "C" tb_status tb_tp_shard_sizes(tb_codec codec, uint32_t group, uint32_t n, uint32_t k, uint32_t planes, int row_parallel,
+                                       uint32_t world, uint32_t rank, tb_shard_sizes* out) {
+  clear_error();
+  if (!out) return tb_fail(TB_NULL_ARG, "out is null");
+  tbf::ShardSizes s;
+  if (tbf::Err e = tbf::shard_sizes(int(codec), group, n, k, planes, row_parallel != 0, world, rank, &s)) return from_fmt(e);
+  out->n = s.n; out->k = s.k; out->payload_bytes = s.payload_bytes; out->scale_count = s.scale_count; out->map_bytes = s.map_bytes;
+  return TB_OK;
+}
+
+extern "C" tb_status tb_tp_shard(tb_codec codec, uint32_t group, uint32_t n, uint32_t k, uint32_t planes, const uint8_t* payload,
+                                 const uint16_t* scales, int row_parallel, uint32_t world, uint32_t rank, uint8_t* sp, uint16_t* ss,
+                                 uint8_t* smap, uint32_t* terminal) {
+  clear_error();
+  if (!payload || !scales || !sp || !ss || !terminal) return tb_fail(TB_NULL_ARG, "null argument");
+  uint8_t dummy = 0;
+  if (tbf::Err e = tbf::shard(int(codec), group, n, k, planes, payload, scales, row_parallel != 0, world, rank, sp, ss,
+                              smap ? smap : &dummy, terminal))
+    return from_fmt(e);
+  return TB_OK;
+}
+
+// ---------------------------------------------------------------- host format helpers
+extern "C" int64_t tb_fmt_pack(tb_codec codec, const int8_t* trits, size_t n, uint8_t* out, size_t cap) {
+  clear_error();
+  if (!trits && n) { tb_fail(TB_NULL_ARG, "trits is null"); return -TB_NULL_ARG; }
+  if (codec == TB_CODEC_S34 && n % 4) { tb_fail(TB_INVALID_INPUT, "S34 requires a multiple of four trits"); return -TB_INVALID_INPUT; }
+  const size_t bytes = tbf::codec_bytes(int(codec), n);
+  if (!out) return int64_t(bytes);
+  if (cap < bytes) { tb_fail(TB_SHAPE_MISMATCH, "output buffer too small"); return -TB_SHAPE_MISMATCH; }
+  if (tbf::Err e = tbf::pack(int(codec), trits, n, out)) return -int64_t(from_fmt(e));
+  return int64_t(bytes);
+}
+
+extern "C" tb_status tb_fmt_unpack(tb_codec codec, const uint8_t* packed, size_t len, size_t n, int8_t* trits) {
+  clear_error();
+  if ((!packed && len) || (!trits && n)) return tb_fail(TB_NULL_ARG, "null argument");
+  if (tbf::Err e = tbf::unpack(int(codec), packed, len, n, trits)) return from_fmt(e);
+  return TB_OK;
+}
+
+extern "C" size_t tb_fmt_plane_bytes(tb_codec codec, size_t logical_len) { return tbf::plane_bytes(int(codec), logical_len); }
+
+extern "C" tb_status tb_fmt_resident_sizes(tb_codec codec, uint32_t group, uint64_t n, uint64_t k, const uint8_t* pc, tb_resident_sizes* out) {
+  clear_error();
+  if (!pc || !out) return tb_fail(TB_NULL_ARG, "null argument");
+  tbf::Sizes s;
+  if (tbf::Err e = tbf::resident_sizes(int(codec), group, n, k, pc, &s)) return from_fmt(e);
+  out->payload_bytes = s.payload_bytes; out->scale_count = s.scale_count; out->map_bytes = s.map_bytes;
+  out->rank_prefix_bytes = s.rank_prefix_bytes; out->tiles = s.tiles; out->present_planes = s.present_planes;
+  return TB_OK;
+}
+
+extern "C" tb_status tb_fmt_resident_build(tb_codec codec, uint32_t group, uint64_t n, uint64_t k, const uint8_t* pc, const int8_t* trits,
+                                           const uint16_t* scales, uint8_t* payload, uint16_t* scale_out, uint8_t* plane_map,
+                                           uint32_t* terminal) {
+  clear_error();
+  if (!pc || !trits || !scales || !payload || !scale_out || !terminal) return tb_fail(TB_NULL_ARG, "null argument");
+  tbf::Resident r;
+  if (tbf::Err e = tbf::resident_from_planes(int(codec), group, n, k, pc, trits, scales, &r)) return from_fmt(e);
+  std::copy(r.payload.begin(), r.payload.end(), payload);
+  std::copy(r.scales.begin(), r.scales.end(), scale_out);
+  if (plane_map) std::copy(r.map.begin(), r.map.end(), plane_map);
+  *terminal = r.terminal_map;
+  return TB_OK;
+}
+
+extern "C" int64_t tb_fmt_package_write(tb_codec codec, const char* name, uint32_t group, uint64_t n, uint64_t k, const uint8_t* pc,
+                                        const int8_t* trits, const uint16_t* scales, uint8_t* out, size_t cap) {
+  clear_error();
+  if (!name || !pc || !trits || !scales) { tb_fail(TB_NULL_ARG, "null argument"); return -TB_NULL_ARG; }
+  std::vector<uint8_t> bytes;
+  if (tbf::Err e = tbf::package_write(int(codec), name, group, n, k, pc, trits, scales, &bytes)) return -int64_t(from_fmt(e));
+  if (!out) return int64_t(bytes.size());
+  if (cap < bytes.size()) { tb_fail(TB_SHAPE_MISMATCH, "output buffer too small"); return -TB_SHAPE_MISMATCH; }
+  std::copy(bytes.begin(), bytes.end(), out);
+  return int64_t(bytes.size());
+}
+
+extern "C" tb_status tb_fmt_tq2_pack_rows(const int8_t* trits, uint64_t n, uint64_t k, uint8_t* out) {
+  clear_error();
+  if (!trits || !out) return tb_fail(TB_NULL_ARG, "null argument");
+  if (tbf::Err e = tbf::tq2_pack_rows(trits, n, k, out)) return from_fmt(e);
+  return TB_OK;
+}
+
+extern "C" void tb_fmt_quantize_act_int8(const float* act, uint64_t m, uint64_t k, float* q, float* scale) {
+  if (!act || !q || !scale) return;
+  tbf::quantize_act_int8(act, m, k, q, scale);
+}

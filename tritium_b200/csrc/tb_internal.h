@@ -1,0 +1,113 @@
+// Internal declarations shared by the C-ABI layer and the kernel translation units.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <string>
+
+#include "../../include/tritium_b200.h"
+#include "tb_format.h"
+
+// Device status word layout (uint32 x 8), written by kernels, read by tb_backend_check.
+enum : uint32_t {
+  TBS_FLAGS = 0,       // bit mask below
+  TBS_INFO0 = 1,       // row / stage
+  TBS_INFO1 = 2,       // column / barrier id
+  TBS_INFO2 = 3,
+};
+enum : uint32_t {
+  TBF_NONFINITE_ACT = 1u,
+  TBF_NONFINITE_OUT = 2u,
+  TBF_WAIT_TIMEOUT = 4u,
+  TBF_BAD_CONFIG = 8u,
+};
+
+struct tb_backend {
+  int ordinal = 0;
+  cudaStream_t stream = nullptr;
+  cudaDeviceProp prop{};
+  char physical_id[96]{};
+  uint32_t* d_status = nullptr;   // 8 words
+  uint32_t* h_status = nullptr;   // pinned mirror
+  // grow-on-demand staging for the host-pointer entry points
+  void* d_x = nullptr; size_t d_x_cap = 0;
+  void* d_y = nullptr; size_t d_y_cap = 0;
+  void* d_aux = nullptr; size_t d_aux_cap = 0;   // act scales / row scales / acc dump
+  void* h_pin = nullptr; size_t h_pin_cap = 0;   // pinned bounce buffer
+  // scratch for the prefill path: quantised activations (permuted int8) + token scales
+  void* d_q = nullptr; size_t d_q_cap = 0;
+  int max_smem_optin = 0;
+};
+
+// How the decode kernel walks one weight tensor (fixed at upload).
+struct DecodePlan {
+  uint32_t rows_per_stage = 0;   // R: multiple of 4 (16-byte chunks) with R*planes % 16 == 0
+  uint32_t row_bytes = 0;        // tiles_per_row * planes * plane_bytes
+  uint32_t stage_bytes = 0;      // R * row_bytes
+  uint32_t scale_stage_bytes = 0;
+  uint32_t blocks = 0;           // ceil(n / R)
+};
+
+struct tb_weights {
+  tb_backend* owner = nullptr;
+  int codec = 0;                 // tbf::Codec
+  uint32_t group = 128, uniform_planes = 0;
+  uint64_t n = 0, k = 0, tiles = 0, present_planes = 0;
+  uint64_t payload_bytes = 0, scale_count = 0, map_bytes = 0, rank_prefix_bytes = 0;
+  uint32_t terminal_map = 0;
+  uint64_t source_len = 0;
+  uint64_t logical_k = 0;        // k the caller sees (TQ2_0 rows are padded to whole blocks)
+  bool is_tq2 = false;
+  bool fast = false;             // uniform planes, k % 256 == 0, group 128, codec D2/B3
+  uint8_t* d_payload = nullptr;  // padded to whole decode stages with zero-trit bytes
+  uint16_t* d_scales = nullptr;
+  uint8_t* d_meta = nullptr;     // map bytes followed by LE u32 rank prefixes
+  uint32_t* d_tile_rank = nullptr;  // planes before each tile (ragged tensors only)
+  DecodePlan plan;
+};
+
+void tb_set_error(const std::string& message);
+tb_status tb_fail(tb_status code, const std::string& message);
+tb_status tb_cuda_fail(cudaError_t err, const char* what);
+
+// ---- kernel launchers (each returns a cudaError_t from the launch) ----
+struct ExactArgs {
+  const tb_weights* w;
+  const float* x; float* y; uint32_t m;
+  const float* row_scale;   // nullable
+  uint32_t* status;
+};
+cudaError_t tb_launch_exact(const ExactArgs& a, cudaStream_t stream);
+cudaError_t tb_launch_gather_rows(const tb_weights* w, const uint32_t* rows, uint32_t count, float* out,
+                                  cudaStream_t stream);
+cudaError_t tb_launch_check_finite(const float* x, uint64_t count, uint32_t* status, cudaStream_t stream);
+
+struct DecodeArgs {
+  const tb_weights* w;
+  const void* x; tb_dtype x_dtype; const float* act_scale_in; const float* act_absmax_in;
+  uint32_t m;                 // 1..4 tokens per launch
+  void* y; tb_dtype y_dtype; uint32_t y_row_stride;  // elements between tokens in y
+  int32_t* acc_dump; uint32_t dump_token_offset, dump_tokens_total;
+  const float* row_scale;
+  uint32_t* status;
+  bool pdl;
+};
+// Returns false (and leaves *err untouched) when the layout/shape does not fit the kernel.
+bool tb_decode_supported(const tb_weights* w, uint32_t m, int max_smem, size_t* smem_bytes);
+cudaError_t tb_launch_decode(const DecodeArgs& a, int sm_count, int max_smem, cudaStream_t stream);
+void tb_make_decode_plan(tb_weights* w, int max_smem);
+
+struct PrefillArgs {
+  const tb_weights* w;
+  const void* x; tb_dtype x_dtype; const float* act_scale_in; const float* act_absmax_in;
+  uint32_t m;
+  void* y; tb_dtype y_dtype;
+  int32_t* acc_dump;
+  const float* row_scale;
+  int8_t* q_scratch; float* token_scale_scratch;   // [m_pad, k] permuted int8, [m_pad]
+  uint32_t* status;
+};
+bool tb_prefill_supported(const tb_weights* w, uint32_t m);
+size_t tb_prefill_scratch_bytes(const tb_weights* w, uint32_t m);
+cudaError_t tb_launch_prefill(const PrefillArgs& a, int sm_count, cudaStream_t stream);
