@@ -1,0 +1,302 @@
+#!/usr/bin/env python
+"""Benchmark of the packed additive-ternary linear layer on B200.
+
+Workload (N=1): BASELINE config 2 — 3-plane additive ternary linear, K=2560, N=6912, B3 packed,
+per-128-group f16 scales, bf16 activations with outlier channels, int8-quantised per token,
+decode M=1.  One "step" is one forward of every layer copy in a rotating set of distinct weight
+buffers that is larger than L2, so every step streams its weights from HBM.
+
+The metric is HBM GB/s: algorithmic bytes (resident arenas read once + activations in + outputs
+out) divided by device time.  `value` is timed with inputs resident in HBM; `e2e` goes through the
+host-pointer C ABI call with host buffers, copies included.
+
+`--impl reference` times the CPU restatement of the reference's scalar algorithm (the oracle) on
+the host cores for the same configuration.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+N_ROWS, K_COLS, PLANES = 6912, 2560, 3
+METRIC = "ternary linear HBM GB/s (M=1)"
+UNIT = "GB/s"
+PLANE_BYTES = {"b3": 52, "d2": 64}
+
+
+def algorithmic_bytes(codec: str, m: int, x_size: int = 2, y_size: int = 2) -> int:
+    from tritium_b200.synth import algorithmic_bytes as ab
+    return ab(N_ROWS, K_COLS, PLANES, PLANE_BYTES[codec], m, x_size, y_size)
+
+
+def measured_peaks() -> tuple[float, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                      "-i", str(self.index)], capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.samples.append([f.strip() for f in out.split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._thread.join(timeout=6)
+
+    def summary(self) -> dict:
+        sm = [int(s[0]) for s in self.samples if s and s[0].isdigit()]
+        mx = [int(s[1]) for s in self.samples if len(s) > 1 and s[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(s) > 2 + i and s[2 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": int(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def build_inputs(m: int):
+    from tritium_b200 import SaltV2Tensor
+    from tritium_b200.synth import f32_to_bf16_bits, make_activations, make_planes
+    trits, scales = make_planes(N_ROWS, K_COLS, PLANES, seed=0)
+    tensor = SaltV2Tensor.from_matrix_planes("ffn_up", trits, scales)
+    x = make_activations(m, K_COLS, seed=0, bf16=True)
+    return tensor, x, f32_to_bf16_bits(x)
+
+
+# ---------------------------------------------------------------------------------------- CPU arm
+def cpu_forward_time(tensor, x: np.ndarray, threads: int, repeats: int) -> float:
+    """Seconds per forward of the oracle: quantise, contract row by row, fold scales."""
+    from oracle import oracle as orc
+    orac = orc.Tensor(tensor.rows, tensor.cols, 128, tensor.plane_count, tensor.trits, tensor.scales)
+    m = x.shape[0]
+    best = float("inf")
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        if threads <= 1:
+            orc.a8_linear(orac, x, dump=False)
+        else:
+            q, s = orc.quantize_act_int8(x, m, tensor.cols)
+            y = orc.matmul(orac, q, threads=threads)
+            y *= s[:, None]
+        best = min(best, time.perf_counter() - t0)
+    return best
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    tensor, x, _ = build_inputs(1)
+    cores = os.cpu_count() or 1
+    for _ in range(max(args.warmup, 1)):
+        cpu_forward_time(tensor, x, cores, 1)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_forward_time(tensor, x, cores, 1)
+    dt = (time.perf_counter() - t0) / args.steps
+    value = algorithmic_bytes("b3", 1) / dt / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "config": {"workload": "c2_3plane_k2560_n6912_b3_m1", "sample": "one layer forward per step"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": "one C2 layer forward (M=1) per step; oracle rows split over POSIX threads"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------- GPU arm
+def time_graph(torch, stream, launch, steps: int, warmup: int, sampler=None):
+    """Capture one step in a CUDA graph, replay it `warmup` + `steps` times, time with events on `stream`."""
+    with torch.cuda.stream(stream):
+        launch()                      # eager once: module load, attribute setup
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            launch()
+        for _ in range(warmup):
+            graph.replay()
+        stream.synchronize()
+    return graph
+
+
+def run_b200(args) -> None:
+    import torch
+    import torch.distributed as dist
+    from tritium_b200 import B200Backend, LinearStack, SaltV2Codec, _lib
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    codec_name = args.codec
+    codec = SaltV2Codec.B3 if codec_name == "b3" else SaltV2Codec.D2
+    m = args.m
+    tensor, x, x_bits = build_inputs(m)
+    backend = B200Backend(local)
+    payload, scales, pmap, terminal, _ = tensor.resident(codec)
+    layer_bytes = algorithmic_bytes(codec_name, m)
+    copies = args.copies or max(2, int(np.ceil(300e6 / layer_bytes)))   # rotating set > 126 MB L2
+    weights = [backend.upload_salt_v2_arenas(codec, 128, N_ROWS, K_COLS, payload, scales, pmap, terminal)
+               for _ in range(copies)]
+    stack = LinearStack(backend, weights, [0] * copies, max_m=max(m, 1))
+
+    stream = torch.cuda.Stream()
+    x_dev = torch.from_numpy(x_bits.view(np.int16).copy()).cuda().view(torch.bfloat16).reshape(m, K_COLS)
+    flags = _lib.TB_FWD_PDL if not args.no_pdl else 0
+
+    def launch():
+        stack.forward_dev(x_dev, flags=flags, stream=stream)
+
+    with torch.cuda.stream(stream):
+        launch()
+        stream.synchronize()
+        backend.check(stream)
+        graph = None
+        if not args.no_graph:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                launch()
+        step = graph.replay if graph is not None else launch
+        for _ in range(max(args.warmup, 3)):
+            step()
+        stream.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local) as clocks:
+            start.record(stream)
+            for _ in range(args.steps):
+                step()
+            stop.record(stream)
+            stream.synchronize()
+            if args.steps * 1.0 < 0:  # pragma: no cover
+                pass
+            elapsed_ms = start.elapsed_time(stop)
+            # keep the sampler alive long enough to see the clocks under load on short runs
+            t_end = time.time() + 0.6
+            while time.time() < t_end and len(clocks.samples) < 2:
+                step()
+            stream.synchronize()
+        backend.check(stream)
+    t = torch.tensor([elapsed_ms], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    elapsed_ms = float(t.item())
+    ms_per_step = elapsed_ms / args.steps
+    bytes_per_step = layer_bytes * copies
+    value = world * bytes_per_step / (ms_per_step * 1e-3) / 1e9
+    per_launch_us = ms_per_step * 1e3 / copies
+    peak, peak_kind = measured_peaks()
+    achieved = layer_bytes / (per_launch_us * 1e-6) / 1e9
+
+    # ---- end to end through the host-pointer C ABI call: H2D of x and D2H of y inside the region
+    y_dtype = "bf16"
+    e2e_steps = max(3, min(args.steps, 20))
+    for w in weights[:3]:
+        backend.linear_forward_a8(w, x_bits, m, y_dtype=y_dtype, x_is_bf16=True)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        for w in weights:
+            backend.linear_forward_a8(w, x_bits, m, y_dtype=y_dtype, x_is_bf16=True)
+    e2e_dt = (time.perf_counter() - t0) / e2e_steps
+    e2e_t = torch.tensor([e2e_dt], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
+    e2e_value = world * bytes_per_step / float(e2e_t.item()) / 1e9
+
+    if rank == 0:
+        cpu = None
+        if world == 1 and not args.skip_cpu:
+            reps = 3
+            sec = cpu_forward_time(tensor, x, 1, reps)
+            cpu = {"value": layer_bytes / sec / 1e9, "unit": UNIT, "cores": 1, "kind": "port",
+                   "sample": f"best of {reps} single-thread oracle forwards of one C2 layer (M={m}), {sec * 1e3:.0f} ms each"}
+        line = {
+            "metric": METRIC if m == 1 else f"ternary linear HBM GB/s (M={m})", "value": value, "unit": UNIT,
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": {"workload": f"c2_3plane_k2560_n6912_{codec_name}_m{m}", "layer_copies_per_step": copies,
+                       "l2_policy": f"rotating set of {copies} distinct weight buffers ({bytes_per_step / 1e6:.0f} MB > 126 MB L2)",
+                       "launch": ("cuda graph" if graph is not None else "eager") + (" + programmatic dependent launch" if flags else "")},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
+                         "traffic": None, "peak_kind": peak_kind, "kernel": "decode_kernel", "us_per_launch": per_launch_us,
+                         "algorithmic_bytes_per_launch": layer_bytes},
+            "cpu_baseline": cpu,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": copies * m * K_COLS * 2,
+                    "d2h_bytes_per_step": copies * m * N_ROWS * 2},
+            "gpu_launches": args.steps * copies,
+            "clocks": clocks.summary(),
+        }
+        print(json.dumps(line), flush=True)
+    stack.close()
+    for w in weights:
+        w.free()
+    backend.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--codec", default="b3", choices=["b3", "d2"])
+    ap.add_argument("--m", type=int, default=1)
+    ap.add_argument("--copies", type=int, default=0)
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-pdl", action="store_true")
+    ap.add_argument("--skip-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -59,6 +59,19 @@ __device__ __forceinline__ int trit_at(const uint8_t* base, uint32_t codec, uint
   return (code >> (2 + slot - (slot > zero))) & 1u ? 1 : -1;
 }
 
+// Acc = float reproduces the reference order bit for bit.  Acc = double is the trait path's
+// accumulator (the reference's own CUDA kernel for that path folds in f64,
+// crates/tritium-cuda/kernels/tq2_0_add.cu:107-175): the only rounding left is the final one.
+template <typename Acc> __device__ __forceinline__ Acc acc_add(Acc a, float b);
+template <> __device__ __forceinline__ float acc_add<float>(float a, float b) { return __fadd_rn(a, b); }
+template <> __device__ __forceinline__ double acc_add<double>(double a, float b) { return __dadd_rn(a, double(b)); }
+template <typename Acc> __device__ __forceinline__ Acc acc_mul(Acc a, float b);
+template <> __device__ __forceinline__ float acc_mul<float>(float a, float b) { return __fmul_rn(a, b); }
+template <> __device__ __forceinline__ double acc_mul<double>(double a, float b) { return __dmul_rn(a, double(b)); }
+__device__ __forceinline__ float shfl_acc(float v, int l) { return __shfl_sync(0xffffffffu, v, l); }
+__device__ __forceinline__ double shfl_acc(double v, int l) { return __shfl_sync(0xffffffffu, v, l); }
+
+template <typename Acc>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32) salt_v2_exact_kernel(const ExactParams p) {
   __shared__ uint16_t lut[243];
   for (int b = threadIdx.x; b < 243; b += blockDim.x) {
@@ -75,9 +88,9 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) salt_v2_exact_kernel(cons
   const uint64_t row_base = uint64_t(row) * p.k, row_end = row_base + p.k;
   const uint32_t full_bytes = plane_bytes_dev(p.codec, 256), full_scales = 256u / p.group;
 
-  float acc[kTokens];
+  Acc acc[kTokens];
 #pragma unroll
-  for (int t = 0; t < kTokens; ++t) acc[t] = 0.f;
+  for (int t = 0; t < kTokens; ++t) acc[t] = Acc(0);
   bool bad = false;
   uint32_t bad_col = 0;
 
@@ -89,12 +102,12 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) salt_v2_exact_kernel(cons
 
   for (uint32_t seg0 = 0; seg0 < segments; seg0 += 32) {
     const uint32_t seg = seg0 + lane;
-    float contrib[3][kTokens];
+    Acc contrib[3][kTokens];
     uint32_t planes = 0;
 #pragma unroll
     for (int q = 0; q < 3; ++q)
 #pragma unroll
-      for (int t = 0; t < kTokens; ++t) contrib[q][t] = 0.f;
+      for (int t = 0; t < kTokens; ++t) contrib[q][t] = Acc(0);
     if (seg < segments) {
       const uint32_t col0 = seg == 0 ? 0 : first_len + (seg - 1) * p.group;
       const uint32_t len = seg == 0 ? first_len : min(p.group, p.k - col0);
@@ -109,9 +122,9 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) salt_v2_exact_kernel(cons
       for (uint32_t q = 0; q < planes; ++q) {
         const uint8_t* base = p.payload + rank * full_bytes + uint64_t(q) * cur_bytes;
         const float scale = __half2float(__ushort_as_half(p.scales[rank * full_scales + q * cur_scales + g]));
-        float ga[kTokens];
+        Acc ga[kTokens];
 #pragma unroll
-        for (int t = 0; t < kTokens; ++t) ga[t] = 0.f;
+        for (int t = 0; t < kTokens; ++t) ga[t] = Acc(0);
         for (uint32_t e = 0; e < len; ++e) {
           const int trit = trit_at(base, p.codec, local0 + e, lut);
           if (trit == 0) continue;
@@ -119,13 +132,13 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) salt_v2_exact_kernel(cons
           for (int t = 0; t < kTokens; ++t)
             if (t < int(tokens)) {
               const float xv = p.x[uint64_t(m0 + t) * p.k + col0 + e];
-              ga[t] = trit > 0 ? __fadd_rn(ga[t], xv) : __fsub_rn(ga[t], xv);
+              ga[t] = acc_add<Acc>(ga[t], trit > 0 ? xv : -xv);
               if (!isfinite(ga[t]) && !bad) { bad = true; bad_col = col0 + e; }
             }
         }
 #pragma unroll
         for (int t = 0; t < kTokens; ++t) {
-          contrib[q][t] = __fmul_rn(ga[t], scale);
+          contrib[q][t] = acc_mul<Acc>(ga[t], scale);
           if (!isfinite(contrib[q][t]) && !bad) { bad = true; bad_col = col0 + len - 1; }
         }
       }
@@ -140,8 +153,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) salt_v2_exact_kernel(cons
         if (uint32_t(q) < lp) {
 #pragma unroll
           for (int t = 0; t < kTokens; ++t) {
-            const float v = __shfl_sync(0xffffffffu, contrib[q][t], l);
-            acc[t] = __fadd_rn(acc[t], v);
+            const Acc v = shfl_acc(contrib[q][t], l);
+            acc[t] = acc[t] + v;
           }
         }
       }
@@ -160,7 +173,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) salt_v2_exact_kernel(cons
 #pragma unroll
     for (int t = 0; t < kTokens; ++t)
       if (t < int(tokens)) {
-        float v = acc[t];
+        float v = float(acc[t]);
         if (p.row_scale) v = __fmul_rn(v, p.row_scale[row]);
         p.y[uint64_t(m0 + t) * p.n + row] = v;
       }
@@ -218,7 +231,8 @@ cudaError_t tb_launch_exact(const ExactArgs& a, cudaStream_t stream) {
   p.x = a.x; p.y = a.y; p.m = a.m; p.row_scale = a.row_scale; p.status = a.status;
   if (a.m == 0 || p.n == 0) return cudaSuccess;
   const dim3 grid((p.n + kWarpsPerBlock - 1) / kWarpsPerBlock, (a.m + kTokens - 1) / kTokens);
-  salt_v2_exact_kernel<<<grid, kWarpsPerBlock * 32, 0, stream>>>(p);
+  if (a.w->is_tq2) salt_v2_exact_kernel<double><<<grid, kWarpsPerBlock * 32, 0, stream>>>(p);
+  else salt_v2_exact_kernel<float><<<grid, kWarpsPerBlock * 32, 0, stream>>>(p);
   return cudaGetLastError();
 }
 
