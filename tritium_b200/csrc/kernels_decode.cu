@@ -37,16 +37,16 @@ constexpr uint32_t kSpinLimit = 1u << 22;
 
 struct DecodeParams {
   const uint8_t* payload; const uint16_t* scales;
-  const void* x; const float* act_scale_in; const float* act_absmax_in;
+  const uint8_t* tables; uint32_t table_bytes;   // z tables | accumulator start values | token scales
   void* y; int32_t* acc_dump; const float* row_scale;
   uint32_t* status;
   uint32_t m, n, k, planes, tpr;            // tpr = k / 256
   uint32_t rows_per_stage, row_bytes, stage_bytes, scale_stage_bytes, blocks;
-  uint32_t stages, x_dtype, y_dtype, y_row_stride;
+  uint32_t stages, y_dtype, y_row_stride;
   uint32_t dump_token_offset, dump_tokens_total;
   uint32_t pdl;
   // shared memory offsets (bytes)
-  uint32_t off_ring, off_scale_ring, off_xq, off_z, off_cinit, off_part, off_actscale;
+  uint32_t off_ring, off_scale_ring, off_z, off_cinit, off_part, off_actscale;
 };
 
 template <int CODEC> struct Traits;
@@ -182,19 +182,93 @@ __device__ __forceinline__ uint32_t z_quad(const int8_t* xq_tile, const Slot<COD
   return out;
 }
 
+// ---------------------------------------------------------------- activation preparation
+// One CTA per (tile column j, token t): per-token absmax int8 quantisation of the 256
+// activations of column j (each CTA re-reduces the whole row for the absmax: the row is a few
+// KB), then the B-fragment table entries and accumulator start values of that column.
+// Table layout in global scratch (bytes): z entries uint2[tpr][mmas][ncol][4] | start values
+// int[m][tpr][2] (padded to 16) | token scales float[m] (padded to 16).
+struct PrepareParams {
+  const void* x; const float* act_scale_in; const float* act_absmax_in;
+  uint8_t* tables;
+  uint32_t m, k, tpr, x_dtype, off_cinit, off_actscale, pdl;
+};
+
+__device__ __forceinline__ float load_act(const void* x, uint32_t dtype, size_t i) {
+  return dtype == TB_F32 ? static_cast<const float*>(x)[i] : __bfloat162float(static_cast<const __nv_bfloat16*>(x)[i]);
+}
+
+template <int CODEC>
+__global__ void __launch_bounds__(256) prepare_kernel(const PrepareParams p) {
+  using T = Traits<CODEC>;
+  __shared__ int8_t xq[256];
+  __shared__ float red[8];
+  if (p.pdl) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+  }
+  const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t j = blockIdx.x, t = blockIdx.y, ncol = 2 * p.m;
+  float scale_out;
+  if (p.x_dtype == TB_I8) {
+    xq[tid] = static_cast<const int8_t*>(p.x)[size_t(t) * p.k + j * 256 + tid];
+    scale_out = p.act_scale_in[t];
+  } else {
+    float gamma;
+    if (p.act_absmax_in) {
+      gamma = p.act_absmax_in[t];   // absmax over the full (unsharded) row, supplied by the caller
+    } else {
+      float mx = 0.f;
+      for (uint32_t i = tid; i < p.k; i += 256) mx = fmaxf(mx, fabsf(load_act(p.x, p.x_dtype, size_t(t) * p.k + i)));
+      for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      if (lane == 0) red[warp] = mx;
+      __syncthreads();
+      gamma = 0.f;
+      for (int w2 = 0; w2 < 8; ++w2) gamma = fmaxf(gamma, red[w2]);
+    }
+    const float scale_q = gamma > 0.f ? __fdiv_rn(127.0f, gamma) : 0.f;
+    scale_out = __fdiv_rn(gamma, 127.0f);
+    const float v = load_act(p.x, p.x_dtype, size_t(t) * p.k + j * 256 + tid);
+    xq[tid] = int8_t(int(fminf(127.f, fmaxf(-128.f, rintf(__fmul_rn(v, scale_q))))));
+  }
+  __syncthreads();
+  uint2* ztab = reinterpret_cast<uint2*>(p.tables);
+  // entries of this (column, token): mma x {high, low part} x lane column
+  if (tid < T::kMmas * 8) {
+    const uint32_t c = tid & 3, hl = (tid >> 2) & 1, mma = tid >> 3;
+    const Slot<CODEC> s = slot_of<CODEC>(int(mma), int(c));
+    const uint32_t col = 2 * t + hl;
+    ztab[((size_t(j) * T::kMmas + mma) * ncol + col) * 4 + c] =
+        make_uint2(z_quad<CODEC>(xq, s, s.d0, int(hl)), z_quad<CODEC>(xq, s, s.d1, int(hl)));
+  }
+  // accumulator start value of (token, column, group v):
+  //   B3: -(sum over the group of x_t * c5[t mod 5]), c5 = {1,-2,-1,-1,2}: the group sum of x plus
+  //       the operand offsets (q2,q3,q4 carry +1) times z = x_i - 3 x_{i-1};   D2: -(sum of x_t).
+  if (warp < 2) {
+    int sum = 0;
+    for (int e = 0; e < 4; ++e) {
+      const int tt = int(warp) * 128 + int(lane) * 4 + e;
+      int coef = 1;
+      if (CODEC == tbf::kB3) { const int d = tt % 5; coef = d == 0 ? 1 : d == 1 ? -2 : d == 4 ? 2 : -1; }
+      sum += int(xq[tt]) * coef;
+    }
+    for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane == 0) reinterpret_cast<int*>(p.tables + p.off_cinit)[(t * p.tpr + j) * 2 + warp] = -sum;
+  }
+  if (j == 0 && tid == 0) reinterpret_cast<float*>(p.tables + p.off_actscale)[t] = scale_out;
+}
+
 // ---------------------------------------------------------------- the kernel
 template <int CODEC>
 __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const DecodeParams p) {
   using T = Traits<CODEC>;
   extern __shared__ __align__(128) uint8_t smem[];
-  __shared__ uint64_t full_bar[kMaxStages], empty_bar[kMaxStages];
+  __shared__ uint64_t full_bar[kMaxStages], empty_bar[kMaxStages], table_bar;
   __shared__ uint32_t abort_flag;
-  __shared__ float red_max[kConsumerWarps];
 
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   uint8_t* ring = smem + p.off_ring;
   uint8_t* scale_ring = smem + p.off_scale_ring;
-  int8_t* xq = reinterpret_cast<int8_t*>(smem + p.off_xq);
   uint2* ztab = reinterpret_cast<uint2*>(smem + p.off_z);
   int* cinit = reinterpret_cast<int*>(smem + p.off_cinit);
   float* part = reinterpret_cast<float*>(smem + p.off_part);
@@ -203,6 +277,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const DecodeParams 
   if (tid == 0) {
     abort_flag = 0;
     for (uint32_t s = 0; s < p.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], kConsumerWarps); }
+    mbar_init(&table_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
@@ -239,73 +314,26 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const DecodeParams 
     return;
   }
 
-  // -------------------------------------------------- consumers: prologue
+  // -------------------------------------------------- consumers: fetch the activation tables
+  // The prepare kernel (previous launch on this stream) wrote z tables, accumulator start values
+  // and token scales to global scratch; one bulk copy brings them in.
   const uint32_t ctid = tid;  // 0 .. kConsumerWarps*32-1
   constexpr uint32_t kCT = kConsumerWarps * 32;
   if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
-
-  for (uint32_t t = 0; t < p.m; ++t) {
-    float scale_q = 0.f;  // 127/gamma
-    if (p.x_dtype == TB_I8) {
-      const int8_t* xr = static_cast<const int8_t*>(p.x) + size_t(t) * p.k;
-      for (uint32_t i = ctid; i < p.k; i += kCT) xq[t * p.k + i] = xr[i];
-      if (ctid == 0) act_scale[t] = p.act_scale_in[t];
-    } else {
-      float gamma;
-      if (p.act_absmax_in) {
-        gamma = p.act_absmax_in[t];  // absmax over the full (unsharded) row, supplied by the caller
-      } else {
-        float mx = 0.f;
-        for (uint32_t i = ctid; i < p.k; i += kCT) {
-          const float v = p.x_dtype == TB_F32 ? static_cast<const float*>(p.x)[size_t(t) * p.k + i]
-                                              : __bfloat162float(static_cast<const __nv_bfloat16*>(p.x)[size_t(t) * p.k + i]);
-          mx = fmaxf(mx, fabsf(v));
-        }
-        for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        if (lane == 0) red_max[warp] = mx;
-        consumer_sync();
-        gamma = 0.f;
-        for (int w2 = 0; w2 < kConsumerWarps; ++w2) gamma = fmaxf(gamma, red_max[w2]);
-        consumer_sync();
-      }
-      scale_q = gamma > 0.f ? __fdiv_rn(127.0f, gamma) : 0.f;
-      if (ctid == 0) act_scale[t] = __fdiv_rn(gamma, 127.0f);
-      for (uint32_t i = ctid; i < p.k; i += kCT) {
-        const float v = p.x_dtype == TB_F32 ? static_cast<const float*>(p.x)[size_t(t) * p.k + i]
-                                            : __bfloat162float(static_cast<const __nv_bfloat16*>(p.x)[size_t(t) * p.k + i]);
-        const float r = fminf(127.f, fmaxf(-128.f, rintf(__fmul_rn(v, scale_q))));
-        xq[t * p.k + i] = int8_t(int(r));
-      }
-    }
-  }
-  consumer_sync();
-
-  // z tables: entry (tile column j, mma, column col = 2*token + hl, lane column c) -> (b0, b1)
   const uint32_t ncol = 2 * p.m;
-  {
-    const uint32_t entries = p.tpr * T::kMmas * ncol * 4;
-    for (uint32_t e = ctid; e < entries; e += kCT) {
-      const uint32_t c = e & 3, col = (e >> 2) % ncol, rest = (e >> 2) / ncol;
-      const uint32_t mma = rest % T::kMmas, j = rest / T::kMmas;
-      const int8_t* xt = xq + (col >> 1) * p.k + j * 256;
-      const Slot<CODEC> s = slot_of<CODEC>(int(mma), int(c));
-      ztab[e] = make_uint2(z_quad<CODEC>(xt, s, s.d0, int(col & 1)), z_quad<CODEC>(xt, s, s.d1, int(col & 1)));
-    }
-    // accumulator start values: -(sum of operand offsets * z) - (sum of activations of the group)
-    const uint32_t cells = p.m * p.tpr * 2;
-    for (uint32_t e = ctid; e < cells; e += kCT) {
-      const uint32_t v = e & 1, j = (e >> 1) % p.tpr, t = (e >> 1) / p.tpr;
-      const int8_t* xt = xq + t * p.k + j * 256;
-      int sum = 0;
-      for (int i = 0; i < 128; ++i) sum += xt[v * 128 + i];
-      if (CODEC == tbf::kB3) {
-        for (int byte = 0; byte < 52; ++byte)
-          for (int i = 2; i < 5; ++i) sum += z_value<CODEC>(xt, byte >> 2, byte & 3, i, int(v));
-      }
-      cinit[e] = -sum;
-    }
+  if (ctid == 0) {
+    mbar_expect_tx(&table_bar, p.table_bytes);
+    bulk_g2s(smem + p.off_z, p.tables, p.table_bytes, &table_bar);
   }
-  consumer_sync();
+  {
+    const bool tables_ok = mbar_wait(&table_bar, 0, &abort_flag);
+    if (!tables_ok) {
+      abort_flag = 1;
+      if (lane == 0 && atomicOr(&p.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) { p.status[TBS_INFO0] = 0; p.status[TBS_INFO1] = 200; }
+    }
+    consumer_sync();
+    if (abort_flag) return;
+  }
 
   // -------------------------------------------------- consumers: main loop
   const uint32_t g = lane >> 2, c = lane & 3;
@@ -435,17 +463,26 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const DecodeParams 
 
 uint32_t round_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
 
+// Byte layout of the activation tables (identical in global scratch and in shared memory).
+struct TableLayout { uint32_t z_bytes, off_cinit, off_actscale, total; };
+TableLayout table_layout(const tb_weights* w, uint32_t m) {
+  const uint32_t tpr = uint32_t(w->k / 256), mmas = w->codec == tbf::kB3 ? 15 : 8;
+  TableLayout t;
+  t.z_bytes = tpr * mmas * (2 * m) * 4 * 8;
+  t.off_cinit = t.z_bytes;
+  t.off_actscale = t.off_cinit + round_up(m * tpr * 2 * 4, 16);
+  t.total = t.off_actscale + 16;
+  return t;
+}
+
 // Shared-memory layout for (weights, m); returns total bytes or 0 when it cannot fit.
 size_t layout(const tb_weights* w, uint32_t m, int max_smem, DecodeParams* p) {
   const DecodePlan& pl = w->plan;
-  const uint32_t tpr = uint32_t(w->k / 256), planes = w->uniform_planes;
-  const uint32_t mmas = w->codec == tbf::kB3 ? 15 : 8;
+  const uint32_t planes = w->uniform_planes;
+  const TableLayout tl = table_layout(w, m);
   uint32_t off = 0;
-  const uint32_t xq = round_up(m * uint32_t(w->k), 16);
-  const uint32_t z = tpr * mmas * (2 * m) * 4 * 8;
-  const uint32_t ci = round_up(m * tpr * 2 * 4, 16);
   const uint32_t part = round_up(2 * kConsumerWarps * pl.rows_per_stage * planes * m * 4, 16);
-  const uint32_t fixed = xq + z + ci + part + 64;
+  const uint32_t fixed = tl.total + part;
   const uint32_t per_stage = pl.stage_bytes + pl.scale_stage_bytes;
   if (fixed + 2 * per_stage > uint32_t(max_smem)) return 0;
   uint32_t stages = std::min<uint32_t>(kMaxStages, (uint32_t(max_smem) - fixed) / per_stage);
@@ -453,11 +490,12 @@ size_t layout(const tb_weights* w, uint32_t m, int max_smem, DecodeParams* p) {
     p->stages = stages;
     p->off_ring = off; off += stages * pl.stage_bytes;
     p->off_scale_ring = off; off += stages * pl.scale_stage_bytes;
-    p->off_xq = off; off += xq;
-    p->off_z = off; off += z;
-    p->off_cinit = off; off += ci;
+    p->off_z = off;
+    p->off_cinit = off + tl.off_cinit;
+    p->off_actscale = off + tl.off_actscale;
+    off += tl.total;
     p->off_part = off; off += part;
-    p->off_actscale = off; off += 64;
+    p->table_bytes = tl.total;
   }
   return size_t(fixed) + size_t(stages) * per_stage;
 }
@@ -492,18 +530,47 @@ bool tb_decode_supported(const tb_weights* w, uint32_t m, int max_smem, size_t* 
   return true;
 }
 
+size_t tb_decode_scratch_bytes(const tb_weights* w, uint32_t m) { return table_layout(w, m).total; }
+
 cudaError_t tb_launch_decode(const DecodeArgs& a, int sm_count, int max_smem, cudaStream_t stream) {
   const tb_weights* w = a.w;
   DecodeParams p{};
   const size_t smem = layout(w, a.m, max_smem, &p);
   if (!smem) return cudaErrorInvalidConfiguration;
+  const TableLayout tl = table_layout(w, a.m);
+  if (!a.scratch || a.scratch_bytes < tl.total) return cudaErrorInvalidValue;
+
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+
+  // 1. activation tables
+  PrepareParams pp{};
+  pp.x = a.x; pp.act_scale_in = a.act_scale_in; pp.act_absmax_in = a.act_absmax_in;
+  pp.tables = static_cast<uint8_t*>(a.scratch);
+  pp.m = a.m; pp.k = uint32_t(w->k); pp.tpr = uint32_t(w->k / 256); pp.x_dtype = uint32_t(a.x_dtype);
+  pp.off_cinit = tl.off_cinit; pp.off_actscale = tl.off_actscale; pp.pdl = a.pdl ? 1u : 0u;
+  {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(pp.tpr, a.m);
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = a.pdl ? 1 : 0;
+    cudaError_t err = w->codec == tbf::kB3 ? cudaLaunchKernelEx(&cfg, prepare_kernel<tbf::kB3>, pp)
+                                           : cudaLaunchKernelEx(&cfg, prepare_kernel<tbf::kD2>, pp);
+    if (err != cudaSuccess) return err;
+  }
+
+  // 2. the weight stream
   p.payload = w->d_payload; p.scales = w->d_scales;
-  p.x = a.x; p.act_scale_in = a.act_scale_in; p.act_absmax_in = a.act_absmax_in; p.y = a.y; p.acc_dump = a.acc_dump; p.row_scale = a.row_scale;
+  p.tables = static_cast<const uint8_t*>(a.scratch);
+  p.y = a.y; p.acc_dump = a.acc_dump; p.row_scale = a.row_scale;
   p.status = a.status;
   p.m = a.m; p.n = uint32_t(w->n); p.k = uint32_t(w->k); p.planes = w->uniform_planes; p.tpr = uint32_t(w->k / 256);
   p.rows_per_stage = w->plan.rows_per_stage; p.row_bytes = w->plan.row_bytes;
   p.stage_bytes = w->plan.stage_bytes; p.scale_stage_bytes = w->plan.scale_stage_bytes; p.blocks = w->plan.blocks;
-  p.x_dtype = uint32_t(a.x_dtype); p.y_dtype = uint32_t(a.y_dtype); p.y_row_stride = a.y_row_stride;
+  p.y_dtype = uint32_t(a.y_dtype); p.y_row_stride = a.y_row_stride;
   p.dump_token_offset = a.dump_token_offset; p.dump_tokens_total = a.dump_tokens_total;
   p.pdl = a.pdl ? 1u : 0u;
   auto kernel = w->codec == tbf::kB3 ? decode_kernel<tbf::kB3> : decode_kernel<tbf::kD2>;
@@ -514,9 +581,6 @@ cudaError_t tb_launch_decode(const DecodeArgs& a, int sm_count, int max_smem, cu
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = a.pdl ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, p);

@@ -84,6 +84,8 @@ extern "C" tb_status tb_backend_create(int ordinal, tb_backend** out) {
   if ((err = cudaMemset(b->d_status, 0, 8 * sizeof(uint32_t))) != cudaSuccess) return bail(err, "clear status");
   if ((err = cudaMallocHost(&b->h_status, 8 * sizeof(uint32_t))) != cudaSuccess) return bail(err, "allocate status mirror");
   cudaDeviceGetAttribute(&b->max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, ordinal);
+  b->d_prep_cap = 2u << 20;   // activation tables of the decode path: up to 4 tokens x k = 32768
+  if ((err = cudaMalloc(&b->d_prep, b->d_prep_cap)) != cudaSuccess) return bail(err, "allocate decode scratch");
   const unsigned char* u = reinterpret_cast<const unsigned char*>(b->prop.uuid.bytes);
   std::snprintf(b->physical_id, sizeof b->physical_id,
                 "b200:%d:GPU-%02x%02x%02x%02x-%02x%02x-%02x%02x-%02x%02x-%02x%02x%02x%02x%02x%02x", ordinal, u[0], u[1],
@@ -97,7 +99,7 @@ extern "C" void tb_backend_free(tb_backend* b) {
   cudaSetDevice(b->ordinal);
   if (b->stream) { cudaStreamSynchronize(b->stream); cudaStreamDestroy(b->stream); }
   cudaFree(b->d_status); cudaFreeHost(b->h_status);
-  cudaFree(b->d_x); cudaFree(b->d_y); cudaFree(b->d_aux); cudaFree(b->d_q); cudaFreeHost(b->h_pin);
+  cudaFree(b->d_x); cudaFree(b->d_y); cudaFree(b->d_aux); cudaFree(b->d_q); cudaFree(b->d_prep); cudaFreeHost(b->h_pin);
   delete b;
 }
 
@@ -316,6 +318,7 @@ tb_status forward_dev(tb_backend* b, const tb_weights* w, const tb_forward_args&
     d.y = static_cast<uint8_t*>(a.y) + size_t(m0) * w->n * dtype_size(a.y_dtype);
     d.acc_dump = a.acc_dump; d.dump_token_offset = m0; d.dump_tokens_total = a.m;
     d.row_scale = a.row_scale; d.status = b->d_status; d.pdl = (a.flags & TB_FWD_PDL) != 0;
+    d.scratch = b->d_prep; d.scratch_bytes = b->d_prep_cap;
     TB_CUDA(tb_launch_decode(d, b->prop.multiProcessorCount, b->max_smem_optin, st), "launch decode");
     ++launches;
   }

@@ -37,6 +37,8 @@ struct tb_backend {
   void* h_pin = nullptr; size_t h_pin_cap = 0;   // pinned bounce buffer
   // scratch for the prefill path: quantised activations (permuted int8) + token scales
   void* d_q = nullptr; size_t d_q_cap = 0;
+  // scratch for the decode path: activation tables built by the prepare kernel
+  void* d_prep = nullptr; size_t d_prep_cap = 0;
   int max_smem_optin = 0;
 };
 
@@ -92,7 +94,9 @@ struct DecodeArgs {
   const float* row_scale;
   uint32_t* status;
   bool pdl;
+  void* scratch; size_t scratch_bytes;   // activation tables (written by the prepare kernel)
 };
+size_t tb_decode_scratch_bytes(const tb_weights* w, uint32_t m);
 // Returns false (and leaves *err untouched) when the layout/shape does not fit the kernel.
 bool tb_decode_supported(const tb_weights* w, uint32_t m, int max_smem, size_t* smem_bytes);
 cudaError_t tb_launch_decode(const DecodeArgs& a, int sm_count, int max_smem, cudaStream_t stream);
