@@ -44,7 +44,7 @@ struct DecodeParams {
   uint32_t rows_per_stage, row_bytes, stage_bytes, scale_stage_bytes, blocks;
   uint32_t stages, y_dtype, y_row_stride;
   uint32_t dump_token_offset, dump_tokens_total;
-  uint32_t pdl;
+  uint32_t pdl, wait_tables;
   // shared memory offsets (bytes)
   uint32_t off_ring, off_scale_ring, off_z, off_cinit, off_part, off_actscale;
 };
@@ -260,7 +260,7 @@ __global__ void __launch_bounds__(256) prepare_kernel(const PrepareParams p) {
 
 // ---------------------------------------------------------------- the kernel
 template <int CODEC>
-__global__ void __launch_bounds__(kThreads, 1) decode_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams p) {
   using T = Traits<CODEC>;
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ uint64_t full_bar[kMaxStages], empty_bar[kMaxStages], table_bar;
@@ -281,7 +281,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const DecodeParams 
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  if (p.pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // The next kernel on the stream may begin once every CTA has passed this point.  When this
+  // launch has to wait for its tables, the trigger is raised only after that wait, so that a
+  // later launch which shares the tables (and therefore does not wait) cannot outrun them.
+  if (p.pdl && !p.wait_tables) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   const uint32_t my_blocks = blockIdx.x < p.blocks ? (p.blocks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
 
@@ -319,7 +322,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const DecodeParams 
   // and token scales to global scratch; one bulk copy brings them in.
   const uint32_t ctid = tid;  // 0 .. kConsumerWarps*32-1
   constexpr uint32_t kCT = kConsumerWarps * 32;
-  if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (p.pdl && p.wait_tables) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  }
   const uint32_t ncol = 2 * p.m;
   if (ctid == 0) {
     mbar_expect_tx(&table_bar, p.table_bytes);
@@ -361,17 +367,14 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const DecodeParams 
     const uint64_t blk = blockIdx.x + uint64_t(it) * gridDim.x;
     const uint32_t row0 = uint32_t(blk) * p.rows_per_stage;
 
-    uint32_t cur_j = 0xffffffffu;
-    uint2 breg[T::kMmas];
     for (uint32_t item = item_lo; landed && item < item_hi; ++item) {
       const uint32_t j = item / sets, set = item - j * sets;
-      if (j != cur_j) {
-        cur_j = j;
-        const uint2* zrow = ztab + size_t(j) * T::kMmas * ncol * 4;
-#pragma unroll
-        for (int mm = 0; mm < T::kMmas; ++mm)
-          breg[mm] = g < ncol ? zrow[(mm * ncol + g) * 4 + c] : make_uint2(0u, 0u);
-      }
+      // B fragments (activation tables) of tile column j for this lane; lanes whose MMA column
+      // is beyond the token columns contribute zeros.
+      const uint2* zlane = ztab + (size_t(j) * T::kMmas * ncol + g) * 4 + c;
+      const uint32_t zstep = ncol * 4;
+      const bool has_b = g < ncol;
+#define TB_BFRAG(mm) (has_b ? zlane[(mm) * zstep] : make_uint2(0u, 0u))
       const uint32_t rpa = set * 16 + g, rpb = rpa + 8;
       const uint32_t na = rpa / p.planes, pa = rpa - na * p.planes;
       const uint32_t nb = rpb / p.planes, pb = rpb - nb * p.planes;
@@ -381,37 +384,46 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const DecodeParams 
       int acc0[4] = {0, 0, 0, 0}, acc1[4] = {0, 0, 0, 0};
 
       if (CODEC == tbf::kB3) {
+        // One short accumulation chain per packed word keeps dependent MMAs three deep.
+        int s0[4] = {0, 0, 0, 0}, s1a[4] = {0, 0, 0, 0}, s1b[4] = {0, 0, 0, 0}, s2[4] = {0, 0, 0, 0}, s3[4] = {0, 0, 0, 0};
         uint32_t qa[5], qb[5];
+        uint2 b;
         b3_quads(wa[c], qa); b3_quads(wb[c], qb);
-        mma_u8s8(acc0, qa[0], qb[0], qa[1], qb[1], breg[0].x, breg[0].y);
-        mma_u8s8(acc0, qa[2], qb[2], qa[3], qb[3], breg[1].x, breg[1].y);
-        mma_u8s8(acc0, qa[4], qb[4], 0u, 0u, breg[2].x, breg[2].y);
+        b = TB_BFRAG(0); mma_u8s8(s0, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
+        b = TB_BFRAG(1); mma_u8s8(s0, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
+        b = TB_BFRAG(2); mma_u8s8(s0, qa[4], qb[4], 0u, 0u, b.x, b.y);
         b3_quads(wa[4 + c], qa); b3_quads(wb[4 + c], qb);
-        mma_u8s8(acc0, qa[0], qb[0], qa[1], qb[1], breg[3].x, breg[3].y);
-        mma_u8s8(acc0, qa[2], qb[2], qa[3], qb[3], breg[4].x, breg[4].y);
-        mma_u8s8(acc0, qa[4], qb[4], 0u, 0u, breg[5].x, breg[5].y);
-        mma_u8s8(acc1, qa[0], qb[0], qa[1], qb[1], breg[6].x, breg[6].y);
-        mma_u8s8(acc1, qa[2], qb[2], qa[3], qb[3], breg[7].x, breg[7].y);
-        mma_u8s8(acc1, qa[4], qb[4], 0u, 0u, breg[8].x, breg[8].y);
+        b = TB_BFRAG(3); mma_u8s8(s1a, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
+        b = TB_BFRAG(6); mma_u8s8(s1b, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
+        b = TB_BFRAG(4); mma_u8s8(s1a, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
+        b = TB_BFRAG(7); mma_u8s8(s1b, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
+        b = TB_BFRAG(5); mma_u8s8(s1a, qa[4], qb[4], 0u, 0u, b.x, b.y);
+        b = TB_BFRAG(8); mma_u8s8(s1b, qa[4], qb[4], 0u, 0u, b.x, b.y);
         b3_quads(wa[8 + c], qa); b3_quads(wb[8 + c], qb);
-        mma_u8s8(acc1, qa[0], qb[0], qa[1], qb[1], breg[9].x, breg[9].y);
-        mma_u8s8(acc1, qa[2], qb[2], qa[3], qb[3], breg[10].x, breg[10].y);
-        mma_u8s8(acc1, qa[4], qb[4], 0u, 0u, breg[11].x, breg[11].y);
+        b = TB_BFRAG(9); mma_u8s8(s2, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
+        b = TB_BFRAG(10); mma_u8s8(s2, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
+        b = TB_BFRAG(11); mma_u8s8(s2, qa[4], qb[4], 0u, 0u, b.x, b.y);
         b3_quads(wa[12], qa); b3_quads(wb[12], qb);
-        mma_u8s8(acc1, qa[0], qb[0], qa[1], qb[1], breg[12].x, breg[12].y);
-        mma_u8s8(acc1, qa[2], qb[2], qa[3], qb[3], breg[13].x, breg[13].y);
-        mma_u8s8(acc1, qa[4], qb[4], 0u, 0u, breg[14].x, breg[14].y);
+        b = TB_BFRAG(12); mma_u8s8(s3, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
+        b = TB_BFRAG(13); mma_u8s8(s3, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
+        b = TB_BFRAG(14); mma_u8s8(s3, qa[4], qb[4], 0u, 0u, b.x, b.y);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { acc0[e] = s0[e] + s1a[e]; acc1[e] = s1b[e] + s2[e] + s3[e]; }
       } else {
+        int s[4][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}, {0, 0, 0, 0}, {0, 0, 0, 0}};
 #pragma unroll
         for (int sl = 0; sl < 4; ++sl) {
           const uint32_t va = wa[sl * 4 + c], vb = wb[sl * 4 + c];
-          int (&acc)[4] = sl < 2 ? acc0 : acc1;
-          mma_u8s8(acc, va & 0x03030303u, vb & 0x03030303u, (va >> 2) & 0x03030303u, (vb >> 2) & 0x03030303u,
-                   breg[sl * 2].x, breg[sl * 2].y);
-          mma_u8s8(acc, (va >> 4) & 0x03030303u, (vb >> 4) & 0x03030303u, (va >> 6) & 0x03030303u,
-                   (vb >> 6) & 0x03030303u, breg[sl * 2 + 1].x, breg[sl * 2 + 1].y);
+          uint2 b = TB_BFRAG(sl * 2);
+          mma_u8s8(s[sl], va & 0x03030303u, vb & 0x03030303u, (va >> 2) & 0x03030303u, (vb >> 2) & 0x03030303u, b.x, b.y);
+          b = TB_BFRAG(sl * 2 + 1);
+          mma_u8s8(s[sl], (va >> 4) & 0x03030303u, (vb >> 4) & 0x03030303u, (va >> 6) & 0x03030303u,
+                   (vb >> 6) & 0x03030303u, b.x, b.y);
         }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { acc0[e] = s[0][e] + s[1][e]; acc1[e] = s[2][e] + s[3][e]; }
       }
+#undef TB_BFRAG
 
       // flush: lane (g,c) holds token c (columns 2c = high part, 2c+1 = low part) for rows g, g+8
       if (lane_has_token) {
@@ -485,7 +497,11 @@ size_t layout(const tb_weights* w, uint32_t m, int max_smem, DecodeParams* p) {
   const uint32_t fixed = tl.total + part;
   const uint32_t per_stage = pl.stage_bytes + pl.scale_stage_bytes;
   if (fixed + 2 * per_stage > uint32_t(max_smem)) return 0;
-  uint32_t stages = std::min<uint32_t>(kMaxStages, (uint32_t(max_smem) - fixed) / per_stage);
+  // Prefer a footprint that lets two CTAs share an SM (one of this launch, one of the next launch
+  // on the stream, whose weight stream then starts under this launch's tail).
+  const uint32_t half_sm = 113u * 1024u;
+  const uint32_t budget = fixed + 2 * per_stage <= half_sm ? half_sm : uint32_t(max_smem);
+  uint32_t stages = std::min<uint32_t>(kMaxStages, (budget - fixed) / per_stage);
   if (p) {
     p->stages = stages;
     p->off_ring = off; off += stages * pl.stage_bytes;
@@ -532,6 +548,28 @@ bool tb_decode_supported(const tb_weights* w, uint32_t m, int max_smem, size_t* 
 
 size_t tb_decode_scratch_bytes(const tb_weights* w, uint32_t m) { return table_layout(w, m).total; }
 
+cudaError_t tb_launch_prepare(const DecodeArgs& a, cudaStream_t stream) {
+  const tb_weights* w = a.w;
+  const TableLayout tl = table_layout(w, a.m);
+  if (!a.scratch || a.scratch_bytes < tl.total) return cudaErrorInvalidValue;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  PrepareParams pp{};
+  pp.x = a.x; pp.act_scale_in = a.act_scale_in; pp.act_absmax_in = a.act_absmax_in;
+  pp.tables = static_cast<uint8_t*>(a.scratch);
+  pp.m = a.m; pp.k = uint32_t(w->k); pp.tpr = uint32_t(w->k / 256); pp.x_dtype = uint32_t(a.x_dtype);
+  pp.off_cinit = tl.off_cinit; pp.off_actscale = tl.off_actscale; pp.pdl = a.pdl ? 1u : 0u;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(pp.tpr, a.m);
+  cfg.blockDim = dim3(256);
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = a.pdl ? 1 : 0;
+  return w->codec == tbf::kB3 ? cudaLaunchKernelEx(&cfg, prepare_kernel<tbf::kB3>, pp)
+                              : cudaLaunchKernelEx(&cfg, prepare_kernel<tbf::kD2>, pp);
+}
+
 cudaError_t tb_launch_decode(const DecodeArgs& a, int sm_count, int max_smem, cudaStream_t stream) {
   const tb_weights* w = a.w;
   DecodeParams p{};
@@ -539,30 +577,9 @@ cudaError_t tb_launch_decode(const DecodeArgs& a, int sm_count, int max_smem, cu
   if (!smem) return cudaErrorInvalidConfiguration;
   const TableLayout tl = table_layout(w, a.m);
   if (!a.scratch || a.scratch_bytes < tl.total) return cudaErrorInvalidValue;
-
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
-
-  // 1. activation tables
-  PrepareParams pp{};
-  pp.x = a.x; pp.act_scale_in = a.act_scale_in; pp.act_absmax_in = a.act_absmax_in;
-  pp.tables = static_cast<uint8_t*>(a.scratch);
-  pp.m = a.m; pp.k = uint32_t(w->k); pp.tpr = uint32_t(w->k / 256); pp.x_dtype = uint32_t(a.x_dtype);
-  pp.off_cinit = tl.off_cinit; pp.off_actscale = tl.off_actscale; pp.pdl = a.pdl ? 1u : 0u;
-  {
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(pp.tpr, a.m);
-    cfg.blockDim = dim3(256);
-    cfg.stream = stream;
-    cfg.attrs = attr;
-    cfg.numAttrs = a.pdl ? 1 : 0;
-    cudaError_t err = w->codec == tbf::kB3 ? cudaLaunchKernelEx(&cfg, prepare_kernel<tbf::kB3>, pp)
-                                           : cudaLaunchKernelEx(&cfg, prepare_kernel<tbf::kD2>, pp);
-    if (err != cudaSuccess) return err;
-  }
-
-  // 2. the weight stream
   p.payload = w->d_payload; p.scales = w->d_scales;
   p.tables = static_cast<const uint8_t*>(a.scratch);
   p.y = a.y; p.acc_dump = a.acc_dump; p.row_scale = a.row_scale;
@@ -573,6 +590,7 @@ cudaError_t tb_launch_decode(const DecodeArgs& a, int sm_count, int max_smem, cu
   p.y_dtype = uint32_t(a.y_dtype); p.y_row_stride = a.y_row_stride;
   p.dump_token_offset = a.dump_token_offset; p.dump_tokens_total = a.dump_tokens_total;
   p.pdl = a.pdl ? 1u : 0u;
+  p.wait_tables = a.tables_shared ? 0u : 1u;
   auto kernel = w->codec == tbf::kB3 ? decode_kernel<tbf::kB3> : decode_kernel<tbf::kD2>;
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
   if (err != cudaSuccess) return err;

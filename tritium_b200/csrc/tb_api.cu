@@ -277,7 +277,8 @@ tb_status check_handles(const tb_backend* b, const tb_weights* w) {
 }
 
 // Device-pointer dispatch shared by every entry point.  Returns the kernel family used.
-tb_status forward_dev(tb_backend* b, const tb_weights* w, const tb_forward_args& a, cudaStream_t st, tb_receipt* receipt) {
+tb_status forward_dev(tb_backend* b, const tb_weights* w, const tb_forward_args& a, cudaStream_t st, tb_receipt* receipt,
+                      bool reuse_tables = false) {
   if (a.m == 0 || w->n == 0) { fill_receipt(w, 0, 0, 0, 0, 0, receipt); return TB_OK; }
   if (!a.x || !a.y) return tb_fail(TB_NULL_ARG, "null activation or output pointer");
   const bool a8 = (a.flags & TB_FWD_A8) != 0 || a.x_dtype == TB_I8;
@@ -319,6 +320,8 @@ tb_status forward_dev(tb_backend* b, const tb_weights* w, const tb_forward_args&
     d.acc_dump = a.acc_dump; d.dump_token_offset = m0; d.dump_tokens_total = a.m;
     d.row_scale = a.row_scale; d.status = b->d_status; d.pdl = (a.flags & TB_FWD_PDL) != 0;
     d.scratch = b->d_prep; d.scratch_bytes = b->d_prep_cap;
+    d.tables_shared = reuse_tables && a.m <= 4;
+    if (!d.tables_shared) { TB_CUDA(tb_launch_prepare(d, st), "launch prepare"); ++launches; }
     TB_CUDA(tb_launch_decode(d, b->prop.multiProcessorCount, b->max_smem_optin, st), "launch decode");
     ++launches;
   }
@@ -561,7 +564,11 @@ extern "C" tb_status tb_stack_forward_dev(tb_stack* st, const void* x, tb_dtype 
     a.y_dtype = (last && y_last) ? yd : TB_BF16;
     a.flags = TB_FWD_A8 | (flags & (TB_FWD_PDL | TB_FWD_FORCE_DECODE | TB_FWD_FORCE_PREFILL));
     a.stream = cs;
-    if (tb_status s = forward_dev(b, st->layers[i], a, cs, nullptr)) return s;
+    // Consecutive layers that read the stack input with the same width and codec share one set
+    // of activation tables: quantisation and table building run once for the group.
+    const bool reuse = i > 0 && !chained && !st->chain[i - 1] && st->layers[i - 1]->k == st->layers[i]->k &&
+                       st->layers[i - 1]->codec == st->layers[i]->codec;
+    if (tb_status s = forward_dev(b, st->layers[i], a, cs, nullptr, reuse)) return s;
   }
   return TB_OK;
 }

@@ -95,7 +95,9 @@ struct DecodeArgs {
   uint32_t* status;
   bool pdl;
   void* scratch; size_t scratch_bytes;   // activation tables (written by the prepare kernel)
+  bool tables_shared;   // the tables in scratch were prepared for an earlier launch of the same input
 };
+cudaError_t tb_launch_prepare(const DecodeArgs& a, cudaStream_t stream);
 size_t tb_decode_scratch_bytes(const tb_weights* w, uint32_t m);
 // Returns false (and leaves *err untouched) when the layout/shape does not fit the kernel.
 bool tb_decode_supported(const tb_weights* w, uint32_t m, int max_smem, size_t* smem_bytes);
