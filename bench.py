@@ -227,9 +227,10 @@ def run_b200(args) -> None:
     ms_per_step = elapsed_ms / args.steps
     bytes_per_step = layer_bytes * copies
     value = world * bytes_per_step / (ms_per_step * 1e-3) / 1e9
-    per_launch_us = ms_per_step * 1e3 / copies
+    # One step = one prepare launch + ONE grouped decode launch that streams every layer copy.
+    per_launch_us = ms_per_step * 1e3
     peak, peak_kind = measured_peaks()
-    achieved = layer_bytes / (per_launch_us * 1e-6) / 1e9
+    achieved = bytes_per_step / (per_launch_us * 1e-6) / 1e9
 
     # ---- end to end through the host-pointer C ABI call: H2D of x and D2H of y inside the region
     y_dtype = "bf16"
@@ -263,11 +264,12 @@ def run_b200(args) -> None:
                        "launch": ("cuda graph" if graph is not None else "eager") + (" + programmatic dependent launch" if flags else "")},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
                          "traffic": None, "peak_kind": peak_kind, "kernel": "decode_kernel", "us_per_launch": per_launch_us,
-                         "algorithmic_bytes_per_launch": layer_bytes},
+                         "algorithmic_bytes_per_launch": bytes_per_step, "layers_per_launch": copies,
+                         "algorithmic_bytes_per_layer": layer_bytes},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": copies * m * K_COLS * 2,
                     "d2h_bytes_per_step": copies * m * N_ROWS * 2},
-            "gpu_launches": args.steps * copies,
+            "gpu_launches": args.steps * 2,
             "clocks": clocks.summary(),
         }
         print(json.dumps(line), flush=True)

@@ -184,6 +184,9 @@ tb_status tb_stack_create(tb_backend* backend, const tb_weights* const* weights,
 tb_status tb_stack_forward_dev(tb_stack* stack, const void* x, tb_dtype x_dtype, uint32_t m,
                                void* y_last, tb_dtype y_dtype, uint32_t flags, void* stream);
 uint64_t tb_stack_bytes_per_step(const tb_stack* stack, uint32_t m);
+/* Consecutive unchained layers of one geometry form a group that runs as a single launch;
+ * their bf16 outputs ([m][n] per layer) are read back with this call (synchronises). */
+tb_status tb_stack_read_output(tb_stack* stack, uint32_t layer, uint32_t m, void* out_bf16);
 void tb_stack_free(tb_stack* stack);
 
 /* ------------------------------------------------------------------ tensor-parallel sharding (host)

@@ -315,3 +315,28 @@ def test_trait_path_errors(backend):
     caps = backend.capabilities()
     assert caps.backend == "b200" and "sm_100a" in caps.features and backend.device_id() == "b200:0"
     assert backend.physical_device_id().startswith("b200:0:GPU-")
+
+
+# ------------------------------------------------------------------ grouped stack (one launch, many layers)
+@pytest.mark.parametrize("codec", [SaltV2Codec.B3, SaltV2Codec.D2])
+@pytest.mark.parametrize("m", [1, 3])
+def test_grouped_stack_matches_per_layer_oracle(backend, codec, m):
+    import torch
+    from tritium_b200 import LinearStack
+    n, k, planes = 96, 1024, 2
+    pairs = [uniform_pair(n, k, planes, seed=100 + i) for i in range(5)]
+    weights = [backend.upload_salt_v2(prod, codec) for prod, _ in pairs]
+    stack = LinearStack(backend, weights, [0] * len(weights), max_m=4)
+    x = make_activations(m, k, seed=17, bf16=True)
+    x_dev = torch.from_numpy(f32_to_bf16_bits(x).view(np.int16).copy()).cuda().view(torch.bfloat16).reshape(m, k)
+    stream = torch.cuda.Stream()
+    for flags in (0, 4):          # plain stream order, then programmatic dependent launch
+        with torch.cuda.stream(stream):
+            stack.forward_dev(x_dev, flags=flags, stream=stream)
+        stream.synchronize()
+        backend.check(stream)
+        for i, (_, orac) in enumerate(pairs):
+            want, _, _ = orc.a8_linear(orac, x, dump=False)
+            got = bf16_bits_to_f32(stack.read_output(i, m))
+            assert rel_l2(got, want) <= 1e-2, (i, flags)
+    stack.close()

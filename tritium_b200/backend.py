@@ -341,6 +341,12 @@ class LinearStack:
             C.c_void_p(y_last.data_ptr()) if y_last is not None else None,
             dt[y_last.dtype] if y_last is not None else _lib.TB_BF16, C.c_uint32(flags), C.c_void_p(s.cuda_stream)))
 
+    def read_output(self, layer: int, m: int) -> np.ndarray:
+        """bf16 bit patterns [m, n] of a grouped layer's output (synchronises)."""
+        out = np.zeros((m, self._weights[layer].rows), np.uint16)
+        check(self._backend._L.tb_stack_read_output(self._h, C.c_uint32(layer), C.c_uint32(m), out.ctypes.data_as(C.c_void_p)))
+        return out
+
     def bytes_per_step(self, m: int) -> int:
         return int(self._backend._L.tb_stack_bytes_per_step(self._h, C.c_uint32(m)))
 

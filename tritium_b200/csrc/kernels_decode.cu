@@ -36,7 +36,8 @@ constexpr int kMaxStages = 4;
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 struct DecodeParams {
-  const uint8_t* payload; const uint16_t* scales;
+  const uint8_t* payload; const uint16_t* scales;   // single layer (layers == nullptr)
+  const TbLayerDesc* layers; uint32_t layer_count; uint32_t y_layer_stride;   // grouped launch: outputs [layer][m][n]
   const uint8_t* tables; uint32_t table_bytes;   // z tables | accumulator start values | token scales
   void* y; int32_t* acc_dump; const float* row_scale;
   uint32_t* status;
@@ -46,7 +47,7 @@ struct DecodeParams {
   uint32_t dump_token_offset, dump_tokens_total;
   uint32_t pdl, wait_tables;
   // shared memory offsets (bytes)
-  uint32_t off_ring, off_scale_ring, off_z, off_cinit, off_part, off_actscale;
+  uint32_t off_ring, off_scale_ring, off_z, off_cinit, off_part, off_actscale, off_zero;
 };
 
 template <int CODEC> struct Traits;
@@ -100,6 +101,19 @@ __device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, 
       "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// D = A*B with a zero accumulator (starts a chain without clearing four registers first).
+__device__ __forceinline__ void mma_u8s8_first(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+// v / planes for planes in {1,2,3} and v < 65536, without an integer division.
+__device__ __forceinline__ uint32_t div_planes(uint32_t v, uint32_t planes) {
+  return planes == 1 ? v : planes == 2 ? v >> 1 : (v * 0xAAABu) >> 17;
 }
 
 // ---------------------------------------------------------------- B3 quotients
@@ -256,6 +270,7 @@ __global__ void __launch_bounds__(256) prepare_kernel(const PrepareParams p) {
     if (lane == 0) reinterpret_cast<int*>(p.tables + p.off_cinit)[(t * p.tpr + j) * 2 + warp] = -sum;
   }
   if (j == 0 && tid == 0) reinterpret_cast<float*>(p.tables + p.off_actscale)[t] = scale_out;
+  if (j == 0 && t == 0 && tid < 4) reinterpret_cast<uint32_t*>(p.tables + p.off_actscale + 16)[tid] = 0u;
 }
 
 // ---------------------------------------------------------------- the kernel
@@ -286,7 +301,8 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
   // later launch which shares the tables (and therefore does not wait) cannot outrun them.
   if (p.pdl && !p.wait_tables) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-  const uint32_t my_blocks = blockIdx.x < p.blocks ? (p.blocks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const uint32_t total_blocks = p.blocks * p.layer_count;
+  const uint32_t my_blocks = blockIdx.x < total_blocks ? (total_blocks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
 
   if (warp == kConsumerWarps) {
     // ------------------------------------------------ producer: weights do not depend on the
@@ -300,11 +316,14 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
           if (atomicOr(&p.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) { p.status[TBS_INFO0] = it; p.status[TBS_INFO1] = 100 + s; }
           break;
         }
-        const uint64_t blk = blockIdx.x + uint64_t(it) * gridDim.x;
+        const uint32_t gblk = blockIdx.x + it * gridDim.x;
+        const uint32_t layer = gblk / p.blocks, blk = gblk - layer * p.blocks;
+        const uint8_t* pay = p.layers ? p.layers[layer].payload : p.payload;
+        const uint8_t* scs = reinterpret_cast<const uint8_t*>(p.layers ? p.layers[layer].scales : p.scales);
         mbar_expect_tx(&full_bar[s], p.stage_bytes + p.scale_stage_bytes);
-        bulk_g2s(ring + size_t(s) * p.stage_bytes, p.payload + blk * p.stage_bytes, p.stage_bytes, &full_bar[s]);
-        bulk_g2s(scale_ring + size_t(s) * p.scale_stage_bytes,
-                 reinterpret_cast<const uint8_t*>(p.scales) + blk * p.scale_stage_bytes, p.scale_stage_bytes, &full_bar[s]);
+        bulk_g2s(ring + size_t(s) * p.stage_bytes, pay + size_t(blk) * p.stage_bytes, p.stage_bytes, &full_bar[s]);
+        bulk_g2s(scale_ring + size_t(s) * p.scale_stage_bytes, scs + size_t(blk) * p.scale_stage_bytes,
+                 p.scale_stage_bytes, &full_bar[s]);
         ++fills[s];
       }
       // Do not leave the CTA while a copy may still be landing in its shared memory: wait
@@ -350,6 +369,9 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
   const uint32_t item_lo = warp * per_warp, item_hi = min(items, item_lo + per_warp);
   const uint32_t part_stride = rp_per_stage * p.m;                // floats per warp slice
   const bool lane_has_token = c < p.m;
+  const bool has_b = g < ncol;
+  const uint32_t zstep = has_b ? ncol * 4 : 0;
+  const uint2* zero_entry = reinterpret_cast<const uint2*>(smem + p.off_zero);
   const uint32_t groups_per_row = p.tpr * 2;
 
   for (uint32_t it = 0; it < my_blocks; ++it) {
@@ -364,58 +386,58 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
     }
     const uint32_t* words = reinterpret_cast<const uint32_t*>(ring + size_t(s) * p.stage_bytes);
     const uint32_t* scl = reinterpret_cast<const uint32_t*>(scale_ring + size_t(s) * p.scale_stage_bytes);
-    const uint64_t blk = blockIdx.x + uint64_t(it) * gridDim.x;
-    const uint32_t row0 = uint32_t(blk) * p.rows_per_stage;
+    const uint32_t gblk = blockIdx.x + it * gridDim.x;
+    const uint32_t layer = gblk / p.blocks, blk = gblk - layer * p.blocks;
+    const uint32_t row0 = blk * p.rows_per_stage;
 
-    for (uint32_t item = item_lo; landed && item < item_hi; ++item) {
-      const uint32_t j = item / sets, set = item - j * sets;
+    uint32_t j = item_lo / sets, set = item_lo - j * sets;
+    for (uint32_t item = item_lo; landed && item < item_hi; ++item, ++set) {
+      if (set == sets) { set = 0; ++j; }
       // B fragments (activation tables) of tile column j for this lane; lanes whose MMA column
-      // is beyond the token columns contribute zeros.
-      const uint2* zlane = ztab + (size_t(j) * T::kMmas * ncol + g) * 4 + c;
-      const uint32_t zstep = ncol * 4;
-      const bool has_b = g < ncol;
-#define TB_BFRAG(mm) (has_b ? zlane[(mm) * zstep] : make_uint2(0u, 0u))
+      // is beyond the token columns read a zero entry.
+      const uint2* zlane = has_b ? ztab + (size_t(j) * T::kMmas * ncol + g) * 4 + c : zero_entry;
+#define TB_BFRAG(mm) (zlane[(mm) * zstep])
       const uint32_t rpa = set * 16 + g, rpb = rpa + 8;
-      const uint32_t na = rpa / p.planes, pa = rpa - na * p.planes;
-      const uint32_t nb = rpb / p.planes, pb = rpb - nb * p.planes;
+      const uint32_t na = div_planes(rpa, p.planes), pa = rpa - na * p.planes;
+      const uint32_t nb = div_planes(rpb, p.planes), pb = rpb - nb * p.planes;
       const uint32_t tpa = (na * p.tpr + j) * p.planes + pa, tpb = (nb * p.tpr + j) * p.planes + pb;
       const uint32_t* wa = words + size_t(tpa) * (T::kPlaneBytes / 4);
       const uint32_t* wb = words + size_t(tpb) * (T::kPlaneBytes / 4);
-      int acc0[4] = {0, 0, 0, 0}, acc1[4] = {0, 0, 0, 0};
+      int acc0[4], acc1[4];
 
       if (CODEC == tbf::kB3) {
         // One short accumulation chain per packed word keeps dependent MMAs three deep.
-        int s0[4] = {0, 0, 0, 0}, s1a[4] = {0, 0, 0, 0}, s1b[4] = {0, 0, 0, 0}, s2[4] = {0, 0, 0, 0}, s3[4] = {0, 0, 0, 0};
+        int s0[4], s1a[4], s1b[4], s2[4], s3[4];
         uint32_t qa[5], qb[5];
         uint2 b;
         b3_quads(wa[c], qa); b3_quads(wb[c], qb);
-        b = TB_BFRAG(0); mma_u8s8(s0, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
+        b = TB_BFRAG(0); mma_u8s8_first(s0, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
         b = TB_BFRAG(1); mma_u8s8(s0, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
         b = TB_BFRAG(2); mma_u8s8(s0, qa[4], qb[4], 0u, 0u, b.x, b.y);
         b3_quads(wa[4 + c], qa); b3_quads(wb[4 + c], qb);
-        b = TB_BFRAG(3); mma_u8s8(s1a, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
-        b = TB_BFRAG(6); mma_u8s8(s1b, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
+        b = TB_BFRAG(3); mma_u8s8_first(s1a, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
+        b = TB_BFRAG(6); mma_u8s8_first(s1b, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
         b = TB_BFRAG(4); mma_u8s8(s1a, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
         b = TB_BFRAG(7); mma_u8s8(s1b, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
         b = TB_BFRAG(5); mma_u8s8(s1a, qa[4], qb[4], 0u, 0u, b.x, b.y);
         b = TB_BFRAG(8); mma_u8s8(s1b, qa[4], qb[4], 0u, 0u, b.x, b.y);
         b3_quads(wa[8 + c], qa); b3_quads(wb[8 + c], qb);
-        b = TB_BFRAG(9); mma_u8s8(s2, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
+        b = TB_BFRAG(9); mma_u8s8_first(s2, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
         b = TB_BFRAG(10); mma_u8s8(s2, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
         b = TB_BFRAG(11); mma_u8s8(s2, qa[4], qb[4], 0u, 0u, b.x, b.y);
         b3_quads(wa[12], qa); b3_quads(wb[12], qb);
-        b = TB_BFRAG(12); mma_u8s8(s3, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
+        b = TB_BFRAG(12); mma_u8s8_first(s3, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
         b = TB_BFRAG(13); mma_u8s8(s3, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
         b = TB_BFRAG(14); mma_u8s8(s3, qa[4], qb[4], 0u, 0u, b.x, b.y);
 #pragma unroll
         for (int e = 0; e < 4; ++e) { acc0[e] = s0[e] + s1a[e]; acc1[e] = s1b[e] + s2[e] + s3[e]; }
       } else {
-        int s[4][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}, {0, 0, 0, 0}, {0, 0, 0, 0}};
+        int s[4][4];
 #pragma unroll
         for (int sl = 0; sl < 4; ++sl) {
           const uint32_t va = wa[sl * 4 + c], vb = wb[sl * 4 + c];
           uint2 b = TB_BFRAG(sl * 2);
-          mma_u8s8(s[sl], va & 0x03030303u, vb & 0x03030303u, (va >> 2) & 0x03030303u, (vb >> 2) & 0x03030303u, b.x, b.y);
+          mma_u8s8_first(s[sl], va & 0x03030303u, vb & 0x03030303u, (va >> 2) & 0x03030303u, (vb >> 2) & 0x03030303u, b.x, b.y);
           b = TB_BFRAG(sl * 2 + 1);
           mma_u8s8(s[sl], (va >> 4) & 0x03030303u, (vb >> 4) & 0x03030303u, (va >> 6) & 0x03030303u,
                    (vb >> 6) & 0x03030303u, b.x, b.y);
@@ -466,7 +488,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
           sum = __fadd_rn(sum, stage_part[w2 * part_stride + (r * p.planes + q) * p.m + t]);
       float out = __fmul_rn(sum, act_scale[t]);
       if (p.row_scale) out = __fmul_rn(out, p.row_scale[row0 + r]);
-      const size_t idx = size_t(t) * p.y_row_stride + row0 + r;
+      const size_t idx = size_t(layer) * p.y_layer_stride + size_t(t) * p.y_row_stride + row0 + r;
       if (p.y_dtype == TB_F32) static_cast<float*>(p.y)[idx] = out;
       else static_cast<__nv_bfloat16*>(p.y)[idx] = __float2bfloat16_rn(out);
     }
@@ -483,7 +505,7 @@ TableLayout table_layout(const tb_weights* w, uint32_t m) {
   t.z_bytes = tpr * mmas * (2 * m) * 4 * 8;
   t.off_cinit = t.z_bytes;
   t.off_actscale = t.off_cinit + round_up(m * tpr * 2 * 4, 16);
-  t.total = t.off_actscale + 16;
+  t.total = t.off_actscale + 32;   // token scales (16 bytes) then a zero entry read by idle MMA columns
   return t;
 }
 
@@ -509,6 +531,7 @@ size_t layout(const tb_weights* w, uint32_t m, int max_smem, DecodeParams* p) {
     p->off_z = off;
     p->off_cinit = off + tl.off_cinit;
     p->off_actscale = off + tl.off_actscale;
+    p->off_zero = off + tl.off_actscale + 16;
     off += tl.total;
     p->off_part = off; off += part;
     p->table_bytes = tl.total;
@@ -581,6 +604,7 @@ cudaError_t tb_launch_decode(const DecodeArgs& a, int sm_count, int max_smem, cu
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   p.payload = w->d_payload; p.scales = w->d_scales;
+  p.layers = a.layers; p.layer_count = a.layers ? a.layer_count : 1; p.y_layer_stride = a.y_layer_stride;
   p.tables = static_cast<const uint8_t*>(a.scratch);
   p.y = a.y; p.acc_dump = a.acc_dump; p.row_scale = a.row_scale;
   p.status = a.status;
@@ -595,7 +619,7 @@ cudaError_t tb_launch_decode(const DecodeArgs& a, int sm_count, int max_smem, cu
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
   if (err != cudaSuccess) return err;
   cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(std::min<uint32_t>(p.blocks, uint32_t(sm_count)));
+  cfg.gridDim = dim3(std::min<uint32_t>(p.blocks * p.layer_count, uint32_t(sm_count)));
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;

@@ -277,8 +277,7 @@ tb_status check_handles(const tb_backend* b, const tb_weights* w) {
 }
 
 // Device-pointer dispatch shared by every entry point.  Returns the kernel family used.
-tb_status forward_dev(tb_backend* b, const tb_weights* w, const tb_forward_args& a, cudaStream_t st, tb_receipt* receipt,
-                      bool reuse_tables = false) {
+tb_status forward_dev(tb_backend* b, const tb_weights* w, const tb_forward_args& a, cudaStream_t st, tb_receipt* receipt) {
   if (a.m == 0 || w->n == 0) { fill_receipt(w, 0, 0, 0, 0, 0, receipt); return TB_OK; }
   if (!a.x || !a.y) return tb_fail(TB_NULL_ARG, "null activation or output pointer");
   const bool a8 = (a.flags & TB_FWD_A8) != 0 || a.x_dtype == TB_I8;
@@ -320,7 +319,7 @@ tb_status forward_dev(tb_backend* b, const tb_weights* w, const tb_forward_args&
     d.acc_dump = a.acc_dump; d.dump_token_offset = m0; d.dump_tokens_total = a.m;
     d.row_scale = a.row_scale; d.status = b->d_status; d.pdl = (a.flags & TB_FWD_PDL) != 0;
     d.scratch = b->d_prep; d.scratch_bytes = b->d_prep_cap;
-    d.tables_shared = reuse_tables && a.m <= 4;
+    d.tables_shared = false;
     if (!d.tables_shared) { TB_CUDA(tb_launch_prepare(d, st), "launch prepare"); ++launches; }
     TB_CUDA(tb_launch_decode(d, b->prop.multiProcessorCount, b->max_smem_optin, st), "launch decode");
     ++launches;
@@ -504,10 +503,22 @@ extern "C" tb_status tb_mpgemm_with_act_quant(tb_backend* b, const tb_weights* w
 }
 
 // ---------------------------------------------------------------- layer stack
+namespace {
+// A run of consecutive layers that all read the stack input and share one geometry: launched
+// as ONE grouped decode (a single persistent grid streams every layer's weights back to back).
+struct StackGroup {
+  size_t first = 0, count = 0;
+  TbLayerDesc* d_descs = nullptr;
+  void* y = nullptr;          // [count][max_m][n] bf16
+};
+}  // namespace
+
 struct tb_stack {
   tb_backend* backend = nullptr;
   std::vector<const tb_weights*> layers;
   std::vector<uint8_t> chain;
+  std::vector<StackGroup> groups;
+  std::vector<int> group_of;           // layer -> group index or -1
   uint32_t max_m = 0;
   void* buf[2] = {nullptr, nullptr};   // ping-pong activations (bf16)
   size_t buf_bytes = 0;
@@ -535,6 +546,31 @@ extern "C" tb_status tb_stack_create(tb_backend* b, const tb_weights* const* wei
     widest = std::max<uint64_t>(widest, w->n);
     if (tb_status s = reserve_prefill(b, w, max_m)) { delete st; return s; }
   }
+  st->group_of.assign(layers, -1);
+  auto same_geometry = [](const tb_weights* p, const tb_weights* q) {
+    return p->k == q->k && p->n == q->n && p->codec == q->codec && p->uniform_planes == q->uniform_planes &&
+           p->plan.rows_per_stage == q->plan.rows_per_stage;
+  };
+  for (uint32_t i = 0; i < layers;) {
+    uint32_t e = i + 1;
+    // a grouped run must not feed a chained successor (its outputs live in the group buffer)
+    if (!st->chain[i])
+      while (e < layers && !st->chain[e] && same_geometry(st->layers[i], st->layers[e])) ++e;
+    const bool feeds_chain = e < layers && st->chain[e];
+    if (e - i >= 2 && !feeds_chain) {
+      StackGroup g;
+      g.first = i; g.count = e - i;
+      std::vector<TbLayerDesc> descs;
+      for (uint32_t l = i; l < e; ++l) descs.push_back(TbLayerDesc{st->layers[l]->d_payload, st->layers[l]->d_scales});
+      cudaError_t err = cudaMalloc(&g.d_descs, descs.size() * sizeof(TbLayerDesc));
+      if (err == cudaSuccess) err = cudaMemcpy(g.d_descs, descs.data(), descs.size() * sizeof(TbLayerDesc), cudaMemcpyHostToDevice);
+      if (err == cudaSuccess) err = cudaMalloc(&g.y, g.count * size_t(max_m) * st->layers[i]->n * 2);
+      if (err != cudaSuccess) { cudaFree(g.d_descs); cudaFree(g.y); tb_stack_free(st); return tb_cuda_fail(err, "allocate layer group"); }
+      for (uint32_t l = i; l < e; ++l) st->group_of[l] = int(st->groups.size());
+      st->groups.push_back(g);
+    }
+    i = e;
+  }
   st->buf_bytes = size_t(max_m) * widest * 2;
   for (int i = 0; i < 2; ++i) {
     cudaError_t err = cudaMalloc(&st->buf[i], st->buf_bytes);
@@ -555,6 +591,22 @@ extern "C" tb_status tb_stack_forward_dev(tb_stack* st, const void* x, tb_dtype 
   cudaStream_t cs = stream ? static_cast<cudaStream_t>(stream) : b->stream;
   const size_t n_layers = st->layers.size();
   for (size_t i = 0; i < n_layers; ++i) {
+    const int gi = st->group_of[i];
+    if (gi >= 0 && m <= 4 && !(flags & TB_FWD_FORCE_PREFILL)) {
+      // one prepare + one grouped decode for the whole run
+      const StackGroup& g = st->groups[gi];
+      const tb_weights* w = st->layers[i];
+      DecodeArgs d{};
+      d.w = w; d.x = x; d.x_dtype = xd; d.m = m; d.y = g.y; d.y_dtype = TB_BF16; d.y_row_stride = uint32_t(w->n);
+      d.status = b->d_status; d.pdl = (flags & TB_FWD_PDL) != 0; d.scratch = b->d_prep; d.scratch_bytes = b->d_prep_cap;
+      d.layers = g.d_descs; d.layer_count = uint32_t(g.count); d.y_layer_stride = uint32_t(size_t(m) * w->n);
+      if (!tb_decode_supported(w, m, b->max_smem_optin, nullptr))
+        return tb_fail(TB_UNSUPPORTED_FORMAT, "the decode kernel's shared-memory plan does not fit this shape");
+      TB_CUDA(tb_launch_prepare(d, cs), "launch prepare");
+      TB_CUDA(tb_launch_decode(d, b->prop.multiProcessorCount, b->max_smem_optin, cs), "launch grouped decode");
+      i += g.count - 1;
+      continue;
+    }
     tb_forward_args a{};
     const bool chained = st->chain[i] != 0, last = i + 1 == n_layers;
     a.x = chained ? st->buf[(i + 1) & 1] : x;
@@ -564,12 +616,22 @@ extern "C" tb_status tb_stack_forward_dev(tb_stack* st, const void* x, tb_dtype 
     a.y_dtype = (last && y_last) ? yd : TB_BF16;
     a.flags = TB_FWD_A8 | (flags & (TB_FWD_PDL | TB_FWD_FORCE_DECODE | TB_FWD_FORCE_PREFILL));
     a.stream = cs;
-    // Consecutive layers that read the stack input with the same width and codec share one set
-    // of activation tables: quantisation and table building run once for the group.
-    const bool reuse = i > 0 && !chained && !st->chain[i - 1] && st->layers[i - 1]->k == st->layers[i]->k &&
-                       st->layers[i - 1]->codec == st->layers[i]->codec;
-    if (tb_status s = forward_dev(b, st->layers[i], a, cs, nullptr, reuse)) return s;
+    if (tb_status s = forward_dev(b, st->layers[i], a, cs, nullptr)) return s;
   }
+  return TB_OK;
+}
+
+/* Copies the bf16 outputs of grouped layer `layer` (as [m][n]) to `out` on the host; used by
+ * tests and by callers that consume every projection of a group. */
+extern "C" tb_status tb_stack_read_output(tb_stack* st, uint32_t layer, uint32_t m, void* out_bf16) {
+  clear_error();
+  if (!st || !out_bf16) return tb_fail(TB_NULL_ARG, "null argument");
+  if (layer >= st->layers.size() || st->group_of[layer] < 0) return tb_fail(TB_INVALID_INPUT, "layer is not part of a grouped run");
+  if (tb_status s = use_device(st->backend)) return s;
+  const StackGroup& g = st->groups[st->group_of[layer]];
+  const size_t per_layer = size_t(m) * st->layers[layer]->n * 2;
+  TB_CUDA(cudaStreamSynchronize(st->backend->stream), "synchronize stream");
+  TB_CUDA(cudaMemcpy(out_bf16, static_cast<const uint8_t*>(g.y) + (layer - g.first) * per_layer, per_layer, cudaMemcpyDeviceToHost), "copy group output");
   return TB_OK;
 }
 
@@ -584,6 +646,7 @@ extern "C" uint64_t tb_stack_bytes_per_step(const tb_stack* st, uint32_t m) {
 extern "C" void tb_stack_free(tb_stack* st) {
   if (!st) return;
   if (st->backend) cudaSetDevice(st->backend->ordinal);
+  for (StackGroup& g : st->groups) { cudaFree(g.d_descs); cudaFree(g.y); }
   cudaFree(st->buf[0]); cudaFree(st->buf[1]);
   delete st;
 }

@@ -85,6 +85,9 @@ cudaError_t tb_launch_gather_rows(const tb_weights* w, const uint32_t* rows, uin
                                   cudaStream_t stream);
 cudaError_t tb_launch_check_finite(const float* x, uint64_t count, uint32_t* status, cudaStream_t stream);
 
+// Device-resident descriptor of one layer of a grouped launch.
+struct TbLayerDesc { const uint8_t* payload; const uint16_t* scales; };
+
 struct DecodeArgs {
   const tb_weights* w;
   const void* x; tb_dtype x_dtype; const float* act_scale_in; const float* act_absmax_in;
@@ -96,6 +99,9 @@ struct DecodeArgs {
   bool pdl;
   void* scratch; size_t scratch_bytes;   // activation tables (written by the prepare kernel)
   bool tables_shared;   // the tables in scratch were prepared for an earlier launch of the same input
+  // grouped launch: `layer_count` layers shaped like `w` read the same activations; outputs are
+  // written as [layer][m][n] with `y_layer_stride` elements between layers
+  const TbLayerDesc* layers; uint32_t layer_count; uint32_t y_layer_stride;
 };
 cudaError_t tb_launch_prepare(const DecodeArgs& a, cudaStream_t stream);
 size_t tb_decode_scratch_bytes(const tb_weights* w, uint32_t m);
