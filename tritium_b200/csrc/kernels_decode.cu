@@ -45,14 +45,17 @@ struct DecodeParams {
   uint32_t rows_per_stage, row_bytes, stage_bytes, scale_stage_bytes, blocks;
   uint32_t stages, y_dtype, y_row_stride;
   uint32_t dump_token_offset, dump_tokens_total;
-  uint32_t pdl, wait_tables;
+  uint32_t pdl, wait_tables, ctas_per_sm;
   // shared memory offsets (bytes)
   uint32_t off_ring, off_scale_ring, off_z, off_cinit, off_part, off_actscale, off_zero;
 };
 
 template <int CODEC> struct Traits;
-template <> struct Traits<tbf::kB3> { static constexpr int kMmas = 15, kWords = 13, kPlaneBytes = 52; };
-template <> struct Traits<tbf::kD2> { static constexpr int kMmas = 8, kWords = 16, kPlaneBytes = 64; };
+// kMmas: MMAs per (16 row-planes x tile-plane) when the two scale groups use separate
+// accumulators; kMmasDual: when they use separate MMA columns instead (1 or 2 tokens).
+template <> struct Traits<tbf::kB3> { static constexpr int kMmas = 15, kMmasDual = 12, kPlaneBytes = 52; };
+template <> struct Traits<tbf::kD2> { static constexpr int kMmas = 8, kMmasDual = 8, kPlaneBytes = 64; };
+template <int CODEC, bool DUAL> struct MmaCount { static constexpr int value = DUAL ? Traits<CODEC>::kMmasDual : Traits<CODEC>::kMmas; };
 
 // ---------------------------------------------------------------- PTX helpers
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
@@ -146,8 +149,8 @@ __host__ __device__ constexpr int b3_delta(int i) { return i >= 2 ? 1 : 0; }  //
 // Which packed word / digits / scale-group variant MMA number `mma` of a tile-plane consumes for
 // the lane column c (0..3).
 template <int CODEC> struct Slot { int word, variant, d0, d1, lane_lo, lane_hi; };
-template <int CODEC> __device__ __forceinline__ Slot<CODEC> slot_of(int mma, int c);
-template <> __device__ __forceinline__ Slot<tbf::kB3> slot_of<tbf::kB3>(int mma, int c) {
+template <int CODEC, bool DUAL> __device__ __forceinline__ Slot<CODEC> slot_of(int mma, int c);
+template <> __device__ __forceinline__ Slot<tbf::kB3> slot_of<tbf::kB3, false>(int mma, int c) {
   // mma 0-2: words c (group 0); 3-5: words 4+c into group 0; 6-8: words 4+c into group 1;
   // 9-11: words 8+c (group 1); 12-14: word 12, bytes 48,49 for c=0 and 50,51 for c=1 (group 1).
   const int slot = mma < 3 ? 0 : mma < 9 ? 1 : mma < 12 ? 2 : 3;
@@ -160,13 +163,29 @@ template <> __device__ __forceinline__ Slot<tbf::kB3> slot_of<tbf::kB3>(int mma,
   if (slot == 3) { if (c == 0) s.lane_hi = 2; else if (c == 1) s.lane_lo = 2; else s.lane_hi = 0; }
   return s;
 }
-template <> __device__ __forceinline__ Slot<tbf::kD2> slot_of<tbf::kD2>(int mma, int c) {
+template <> __device__ __forceinline__ Slot<tbf::kB3> slot_of<tbf::kB3, true>(int mma, int c) {
+  // three MMAs per packed word; the scale group is chosen by the MMA column, not by the MMA
+  const int slot = mma / 3, pair = mma % 3;
+  Slot<tbf::kB3> s;
+  s.variant = -1;
+  s.d0 = pair * 2; s.d1 = pair == 2 ? -1 : pair * 2 + 1;
+  s.word = slot < 3 ? slot * 4 + c : 12;
+  s.lane_lo = 0; s.lane_hi = 4;
+  if (slot == 3) { if (c == 0) s.lane_hi = 2; else if (c == 1) s.lane_lo = 2; else s.lane_hi = 0; }
+  return s;
+}
+template <> __device__ __forceinline__ Slot<tbf::kD2> slot_of<tbf::kD2, false>(int mma, int c) {
   const int slot = mma >> 1;  // words c, 4+c (group 0), 8+c, 12+c (group 1)
   Slot<tbf::kD2> s;
   s.variant = slot >> 1;
   s.d0 = (mma & 1) * 2; s.d1 = s.d0 + 1;
   s.word = slot * 4 + c;
   s.lane_lo = 0; s.lane_hi = 4;
+  return s;
+}
+template <> __device__ __forceinline__ Slot<tbf::kD2> slot_of<tbf::kD2, true>(int mma, int c) {
+  Slot<tbf::kD2> s = slot_of<tbf::kD2, false>(mma, c);
+  s.variant = -1;
   return s;
 }
 
@@ -185,11 +204,11 @@ __device__ __forceinline__ int z_value(const int8_t* xq_tile, int word, int e, i
 }
 
 template <int CODEC>
-__device__ __forceinline__ uint32_t z_quad(const int8_t* xq_tile, const Slot<CODEC>& s, int digit, int hl) {
+__device__ __forceinline__ uint32_t z_quad(const int8_t* xq_tile, const Slot<CODEC>& s, int digit, int hl, int variant) {
   if (digit < 0) return 0;
   uint32_t out = 0;
   for (int e = s.lane_lo; e < s.lane_hi; ++e) {
-    const int z = z_value<CODEC>(xq_tile, s.word, e, digit, s.variant);
+    const int z = z_value<CODEC>(xq_tile, s.word, e, digit, variant);
     const int v = hl == 0 ? (z >> 2) : (z & 3);
     out |= uint32_t(v & 0xff) << (8 * e);
   }
@@ -212,9 +231,9 @@ __device__ __forceinline__ float load_act(const void* x, uint32_t dtype, size_t 
   return dtype == TB_F32 ? static_cast<const float*>(x)[i] : __bfloat162float(static_cast<const __nv_bfloat16*>(x)[i]);
 }
 
-template <int CODEC>
+template <int CODEC, bool DUAL>
 __global__ void __launch_bounds__(256) prepare_kernel(const PrepareParams p) {
-  using T = Traits<CODEC>;
+  constexpr int kNM = MmaCount<CODEC, DUAL>::value;
   __shared__ int8_t xq[256];
   __shared__ float red[8];
   if (p.pdl) {
@@ -222,7 +241,7 @@ __global__ void __launch_bounds__(256) prepare_kernel(const PrepareParams p) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
   }
   const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const uint32_t j = blockIdx.x, t = blockIdx.y, ncol = 2 * p.m;
+  const uint32_t j = blockIdx.x, t = blockIdx.y, ncol = (DUAL ? 4 : 2) * p.m;
   float scale_out;
   if (p.x_dtype == TB_I8) {
     xq[tid] = static_cast<const int8_t*>(p.x)[size_t(t) * p.k + j * 256 + tid];
@@ -247,13 +266,16 @@ __global__ void __launch_bounds__(256) prepare_kernel(const PrepareParams p) {
   }
   __syncthreads();
   uint2* ztab = reinterpret_cast<uint2*>(p.tables);
-  // entries of this (column, token): mma x {high, low part} x lane column
-  if (tid < T::kMmas * 8) {
-    const uint32_t c = tid & 3, hl = (tid >> 2) & 1, mma = tid >> 3;
-    const Slot<CODEC> s = slot_of<CODEC>(int(mma), int(c));
-    const uint32_t col = 2 * t + hl;
-    ztab[((size_t(j) * T::kMmas + mma) * ncol + col) * 4 + c] =
-        make_uint2(z_quad<CODEC>(xq, s, s.d0, int(hl)), z_quad<CODEC>(xq, s, s.d1, int(hl)));
+  // entries of this (tile column, token): mma x [scale group] x {high, low part} x lane column.
+  // MMA column = 2*token + hl, plus 2*m for the second scale group in the dual layout.
+  constexpr uint32_t kPerMma = DUAL ? 16 : 8;
+  if (tid < kNM * kPerMma) {
+    const uint32_t c = tid & 3, hl = (tid >> 2) & 1, v = DUAL ? (tid >> 3) & 1 : 0, mma = tid / kPerMma;
+    const Slot<CODEC> s = slot_of<CODEC, DUAL>(int(mma), int(c));
+    const int variant = DUAL ? int(v) : s.variant;
+    const uint32_t col = v * 2 * p.m + 2 * t + hl;
+    ztab[((size_t(j) * kNM + mma) * ncol + col) * 4 + c] =
+        make_uint2(z_quad<CODEC>(xq, s, s.d0, int(hl), variant), z_quad<CODEC>(xq, s, s.d1, int(hl), variant));
   }
   // accumulator start value of (token, column, group v):
   //   B3: -(sum over the group of x_t * c5[t mod 5]), c5 = {1,-2,-1,-1,2}: the group sum of x plus
@@ -274,9 +296,10 @@ __global__ void __launch_bounds__(256) prepare_kernel(const PrepareParams p) {
 }
 
 // ---------------------------------------------------------------- the kernel
-template <int CODEC>
+template <int CODEC, int PLANES, bool DUAL>
 __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams p) {
   using T = Traits<CODEC>;
+  constexpr int kNM = MmaCount<CODEC, DUAL>::value;
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ uint64_t full_bar[kMaxStages], empty_bar[kMaxStages], table_bar;
   __shared__ uint32_t abort_flag;
@@ -345,7 +368,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   }
-  const uint32_t ncol = 2 * p.m;
+  const uint32_t ncol = (DUAL ? 4 : 2) * p.m;
   if (ctid == 0) {
     mbar_expect_tx(&table_bar, p.table_bytes);
     bulk_g2s(smem + p.off_z, p.tables, p.table_bytes, &table_bar);
@@ -362,13 +385,18 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
 
   // -------------------------------------------------- consumers: main loop
   const uint32_t g = lane >> 2, c = lane & 3;
-  const uint32_t rp_per_stage = p.rows_per_stage * p.planes;      // multiple of 16
+  const uint32_t rp_per_stage = p.rows_per_stage * PLANES;        // multiple of 16
   const uint32_t sets = rp_per_stage >> 4;
   const uint32_t items = p.tpr * sets;
   const uint32_t per_warp = (items + kConsumerWarps - 1) / kConsumerWarps;
   const uint32_t item_lo = warp * per_warp, item_hi = min(items, item_lo + per_warp);
   const uint32_t part_stride = rp_per_stage * p.m;                // floats per warp slice
-  const bool lane_has_token = c < p.m;
+  // Which (scale group, token) cell of the C fragment this lane finishes.
+  //   separate accumulators: lane column c holds token c, both groups;
+  //   dual columns:          lane column c holds group c / m, token c % m.
+  const bool lane_has_cell = DUAL ? c < 2 * p.m : c < p.m;
+  const uint32_t cell_group = DUAL ? (c >= p.m ? 1u : 0u) : 0u;
+  const uint32_t cell_token = DUAL ? c - cell_group * p.m : c;
   const bool has_b = g < ncol;
   const uint32_t zstep = has_b ? ncol * 4 : 0;
   const uint2* zero_entry = reinterpret_cast<const uint2*>(smem + p.off_zero);
@@ -394,20 +422,20 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
     for (uint32_t item = item_lo; landed && item < item_hi; ++item, ++set) {
       if (set == sets) { set = 0; ++j; }
       // B fragments (activation tables) of tile column j for this lane; lanes whose MMA column
-      // is beyond the token columns read a zero entry.
-      const uint2* zlane = has_b ? ztab + (size_t(j) * T::kMmas * ncol + g) * 4 + c : zero_entry;
+      // is beyond the used columns read a zero entry.
+      const uint2* zlane = has_b ? ztab + (size_t(j) * kNM * ncol + g) * 4 + c : zero_entry;
 #define TB_BFRAG(mm) (zlane[(mm) * zstep])
       const uint32_t rpa = set * 16 + g, rpb = rpa + 8;
-      const uint32_t na = div_planes(rpa, p.planes), pa = rpa - na * p.planes;
-      const uint32_t nb = div_planes(rpb, p.planes), pb = rpb - nb * p.planes;
-      const uint32_t tpa = (na * p.tpr + j) * p.planes + pa, tpb = (nb * p.tpr + j) * p.planes + pb;
+      const uint32_t na = rpa / PLANES, pa = rpa - na * PLANES;
+      const uint32_t nb = rpb / PLANES, pb = rpb - nb * PLANES;
+      const uint32_t tpa = (na * p.tpr + j) * PLANES + pa, tpb = (nb * p.tpr + j) * PLANES + pb;
       const uint32_t* wa = words + size_t(tpa) * (T::kPlaneBytes / 4);
       const uint32_t* wb = words + size_t(tpb) * (T::kPlaneBytes / 4);
-      int acc0[4], acc1[4];
+      int acc0[4], acc1[4];   // group 0 / group 1 sums (dual layout: acc0 holds this lane's group)
 
       if (CODEC == tbf::kB3) {
         // One short accumulation chain per packed word keeps dependent MMAs three deep.
-        int s0[4], s1a[4], s1b[4], s2[4], s3[4];
+        int s0[4], s1[4], s2[4], s3[4];
         uint32_t qa[5], qb[5];
         uint2 b;
         b3_quads(wa[c], qa); b3_quads(wb[c], qb);
@@ -415,40 +443,81 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
         b = TB_BFRAG(1); mma_u8s8(s0, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
         b = TB_BFRAG(2); mma_u8s8(s0, qa[4], qb[4], 0u, 0u, b.x, b.y);
         b3_quads(wa[4 + c], qa); b3_quads(wb[4 + c], qb);
-        b = TB_BFRAG(3); mma_u8s8_first(s1a, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
-        b = TB_BFRAG(6); mma_u8s8_first(s1b, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
-        b = TB_BFRAG(4); mma_u8s8(s1a, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
-        b = TB_BFRAG(7); mma_u8s8(s1b, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
-        b = TB_BFRAG(5); mma_u8s8(s1a, qa[4], qb[4], 0u, 0u, b.x, b.y);
-        b = TB_BFRAG(8); mma_u8s8(s1b, qa[4], qb[4], 0u, 0u, b.x, b.y);
-        b3_quads(wa[8 + c], qa); b3_quads(wb[8 + c], qb);
-        b = TB_BFRAG(9); mma_u8s8_first(s2, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
-        b = TB_BFRAG(10); mma_u8s8(s2, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
-        b = TB_BFRAG(11); mma_u8s8(s2, qa[4], qb[4], 0u, 0u, b.x, b.y);
-        b3_quads(wa[12], qa); b3_quads(wb[12], qb);
-        b = TB_BFRAG(12); mma_u8s8_first(s3, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
-        b = TB_BFRAG(13); mma_u8s8(s3, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
-        b = TB_BFRAG(14); mma_u8s8(s3, qa[4], qb[4], 0u, 0u, b.x, b.y);
+        if (DUAL) {
+          b = TB_BFRAG(3); mma_u8s8_first(s1, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
+          b = TB_BFRAG(4); mma_u8s8(s1, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
+          b = TB_BFRAG(5); mma_u8s8(s1, qa[4], qb[4], 0u, 0u, b.x, b.y);
+        } else {
+          // the words 4..7 straddle the two scale groups: once per group, masked on the B side
+          int s1b[4];
+          b = TB_BFRAG(3); mma_u8s8_first(s1, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
+          b = TB_BFRAG(6); mma_u8s8_first(s1b, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
+          b = TB_BFRAG(4); mma_u8s8(s1, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
+          b = TB_BFRAG(7); mma_u8s8(s1b, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
+          b = TB_BFRAG(5); mma_u8s8(s1, qa[4], qb[4], 0u, 0u, b.x, b.y);
+          b = TB_BFRAG(8); mma_u8s8(s1b, qa[4], qb[4], 0u, 0u, b.x, b.y);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) { acc0[e] = s0[e] + s1a[e]; acc1[e] = s1b[e] + s2[e] + s3[e]; }
+          for (int e = 0; e < 4; ++e) acc1[e] = s1b[e];
+        }
+        constexpr int o2 = DUAL ? 6 : 9, o3 = DUAL ? 9 : 12;
+        b3_quads(wa[8 + c], qa); b3_quads(wb[8 + c], qb);
+        b = TB_BFRAG(o2); mma_u8s8_first(s2, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
+        b = TB_BFRAG(o2 + 1); mma_u8s8(s2, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
+        b = TB_BFRAG(o2 + 2); mma_u8s8(s2, qa[4], qb[4], 0u, 0u, b.x, b.y);
+        b3_quads(wa[12], qa); b3_quads(wb[12], qb);
+        b = TB_BFRAG(o3); mma_u8s8_first(s3, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
+        b = TB_BFRAG(o3 + 1); mma_u8s8(s3, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
+        b = TB_BFRAG(o3 + 2); mma_u8s8(s3, qa[4], qb[4], 0u, 0u, b.x, b.y);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          if (DUAL) acc0[e] = (s0[e] + s1[e]) + (s2[e] + s3[e]);
+          else { acc0[e] = s0[e] + s1[e]; acc1[e] = acc1[e] + s2[e] + s3[e]; }
+        }
       } else {
-        int s[4][4];
+        int sq[4][4];
 #pragma unroll
         for (int sl = 0; sl < 4; ++sl) {
           const uint32_t va = wa[sl * 4 + c], vb = wb[sl * 4 + c];
           uint2 b = TB_BFRAG(sl * 2);
-          mma_u8s8_first(s[sl], va & 0x03030303u, vb & 0x03030303u, (va >> 2) & 0x03030303u, (vb >> 2) & 0x03030303u, b.x, b.y);
+          mma_u8s8_first(sq[sl], va & 0x03030303u, vb & 0x03030303u, (va >> 2) & 0x03030303u, (vb >> 2) & 0x03030303u, b.x, b.y);
           b = TB_BFRAG(sl * 2 + 1);
-          mma_u8s8(s[sl], (va >> 4) & 0x03030303u, (vb >> 4) & 0x03030303u, (va >> 6) & 0x03030303u,
+          mma_u8s8(sq[sl], (va >> 4) & 0x03030303u, (vb >> 4) & 0x03030303u, (va >> 6) & 0x03030303u,
                    (vb >> 6) & 0x03030303u, b.x, b.y);
         }
 #pragma unroll
-        for (int e = 0; e < 4; ++e) { acc0[e] = s[0][e] + s[1][e]; acc1[e] = s[2][e] + s[3][e]; }
+        for (int e = 0; e < 4; ++e) {
+          if (DUAL) acc0[e] = (sq[0][e] + sq[1][e]) + (sq[2][e] + sq[3][e]);
+          else { acc0[e] = sq[0][e] + sq[1][e]; acc1[e] = sq[2][e] + sq[3][e]; }
+        }
       }
 #undef TB_BFRAG
 
-      // flush: lane (g,c) holds token c (columns 2c = high part, 2c+1 = low part) for rows g, g+8
-      if (lane_has_token) {
+      // finish the cells: columns (2c, 2c+1) are the high / low activation parts of one cell
+      if (DUAL) {
+        float va = 0.f, vb = 0.f;
+        if (lane_has_cell) {
+          const int ci = cinit[(cell_token * p.tpr + j) * 2 + cell_group];
+          const int ia = 4 * acc0[0] + acc0[1] + ci, ib = 4 * acc0[2] + acc0[3] + ci;
+          const __half2 sa = *reinterpret_cast<const __half2*>(&scl[tpa]);
+          const __half2 sb = *reinterpret_cast<const __half2*>(&scl[tpb]);
+          va = __fmul_rn(float(ia), cell_group ? __high2float(sa) : __low2float(sa));
+          vb = __fmul_rn(float(ib), cell_group ? __high2float(sb) : __low2float(sb));
+          if (p.acc_dump) {
+            const uint32_t tok = p.dump_token_offset + cell_token;
+            if (row0 + na < p.n)
+              p.acc_dump[((size_t(tok) * p.n + row0 + na) * groups_per_row + 2 * j + cell_group) * PLANES + pa] = ia;
+            if (row0 + nb < p.n)
+              p.acc_dump[((size_t(tok) * p.n + row0 + nb) * groups_per_row + 2 * j + cell_group) * PLANES + pb] = ib;
+          }
+        }
+        // the two scale groups of a (row, token) sit p.m lanes apart: group 0 + group 1
+        va = __fadd_rn(va, __shfl_xor_sync(0xffffffffu, va, p.m));
+        vb = __fadd_rn(vb, __shfl_xor_sync(0xffffffffu, vb, p.m));
+        if (lane_has_cell && cell_group == 0) {
+          my_part[rpa * p.m + cell_token] += va;
+          my_part[rpb * p.m + cell_token] += vb;
+        }
+      } else if (lane_has_cell) {
         const int ci0 = cinit[(c * p.tpr + j) * 2], ci1 = cinit[(c * p.tpr + j) * 2 + 1];
         const int ia0 = 4 * acc0[0] + acc0[1] + ci0, ia1 = 4 * acc1[0] + acc1[1] + ci1;
         const int ib0 = 4 * acc0[2] + acc0[3] + ci0, ib1 = 4 * acc1[2] + acc1[3] + ci1;
@@ -461,12 +530,12 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
         if (p.acc_dump) {
           const uint32_t tok = p.dump_token_offset + c;
           if (row0 + na < p.n) {
-            int32_t* d = p.acc_dump + ((size_t(tok) * p.n + row0 + na) * groups_per_row + 2 * j) * p.planes + pa;
-            d[0] = ia0; d[p.planes] = ia1;
+            int32_t* d = p.acc_dump + ((size_t(tok) * p.n + row0 + na) * groups_per_row + 2 * j) * PLANES + pa;
+            d[0] = ia0; d[PLANES] = ia1;
           }
           if (row0 + nb < p.n) {
-            int32_t* d = p.acc_dump + ((size_t(tok) * p.n + row0 + nb) * groups_per_row + 2 * j) * p.planes + pb;
-            d[0] = ib0; d[p.planes] = ib1;
+            int32_t* d = p.acc_dump + ((size_t(tok) * p.n + row0 + nb) * groups_per_row + 2 * j) * PLANES + pb;
+            d[0] = ib0; d[PLANES] = ib1;
           }
         }
       }
@@ -483,9 +552,10 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
       const uint32_t t = e / p.rows_per_stage, r = e - t * p.rows_per_stage;
       if (row0 + r >= p.n) continue;
       float sum = 0.f;
-      for (uint32_t q = 0; q < p.planes; ++q)
+#pragma unroll
+      for (uint32_t q = 0; q < PLANES; ++q)
         for (int w2 = 0; w2 < kConsumerWarps; ++w2)
-          sum = __fadd_rn(sum, stage_part[w2 * part_stride + (r * p.planes + q) * p.m + t]);
+          sum = __fadd_rn(sum, stage_part[w2 * part_stride + (r * PLANES + q) * p.m + t]);
       float out = __fmul_rn(sum, act_scale[t]);
       if (p.row_scale) out = __fmul_rn(out, p.row_scale[row0 + r]);
       const size_t idx = size_t(layer) * p.y_layer_stride + size_t(t) * p.y_row_stride + row0 + r;
@@ -499,10 +569,13 @@ uint32_t round_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
 
 // Byte layout of the activation tables (identical in global scratch and in shared memory).
 struct TableLayout { uint32_t z_bytes, off_cinit, off_actscale, total; };
+bool use_dual(uint32_t m) { return m <= 2; }
 TableLayout table_layout(const tb_weights* w, uint32_t m) {
-  const uint32_t tpr = uint32_t(w->k / 256), mmas = w->codec == tbf::kB3 ? 15 : 8;
+  const bool dual = use_dual(m);
+  const uint32_t tpr = uint32_t(w->k / 256);
+  const uint32_t mmas = w->codec == tbf::kB3 ? (dual ? 12 : 15) : 8;
   TableLayout t;
-  t.z_bytes = tpr * mmas * (2 * m) * 4 * 8;
+  t.z_bytes = tpr * mmas * ((dual ? 4 : 2) * m) * 4 * 8;
   t.off_cinit = t.z_bytes;
   t.off_actscale = t.off_cinit + round_up(m * tpr * 2 * 4, 16);
   t.total = t.off_actscale + 32;   // token scales (16 bytes) then a zero entry read by idle MMA columns
@@ -535,6 +608,7 @@ size_t layout(const tb_weights* w, uint32_t m, int max_smem, DecodeParams* p) {
     off += tl.total;
     p->off_part = off; off += part;
     p->table_bytes = tl.total;
+    p->ctas_per_sm = budget == half_sm ? 2 : 1;
   }
   return size_t(fixed) + size_t(stages) * per_stage;
 }
@@ -589,8 +663,18 @@ cudaError_t tb_launch_prepare(const DecodeArgs& a, cudaStream_t stream) {
   cfg.stream = stream;
   cfg.attrs = attr;
   cfg.numAttrs = a.pdl ? 1 : 0;
-  return w->codec == tbf::kB3 ? cudaLaunchKernelEx(&cfg, prepare_kernel<tbf::kB3>, pp)
-                              : cudaLaunchKernelEx(&cfg, prepare_kernel<tbf::kD2>, pp);
+  const bool dual = use_dual(a.m);
+  if (w->codec == tbf::kB3)
+    return dual ? cudaLaunchKernelEx(&cfg, prepare_kernel<tbf::kB3, true>, pp) : cudaLaunchKernelEx(&cfg, prepare_kernel<tbf::kB3, false>, pp);
+  return dual ? cudaLaunchKernelEx(&cfg, prepare_kernel<tbf::kD2, true>, pp) : cudaLaunchKernelEx(&cfg, prepare_kernel<tbf::kD2, false>, pp);
+}
+
+using DecodeKernel = void (*)(const DecodeParams);
+template <int CODEC, int PLANES> DecodeKernel pick_dual(bool dual) {
+  return dual ? decode_kernel<CODEC, PLANES, true> : decode_kernel<CODEC, PLANES, false>;
+}
+template <int CODEC> DecodeKernel pick_planes(uint32_t planes, bool dual) {
+  return planes == 1 ? pick_dual<CODEC, 1>(dual) : planes == 2 ? pick_dual<CODEC, 2>(dual) : pick_dual<CODEC, 3>(dual);
 }
 
 cudaError_t tb_launch_decode(const DecodeArgs& a, int sm_count, int max_smem, cudaStream_t stream) {
@@ -615,11 +699,15 @@ cudaError_t tb_launch_decode(const DecodeArgs& a, int sm_count, int max_smem, cu
   p.dump_token_offset = a.dump_token_offset; p.dump_tokens_total = a.dump_tokens_total;
   p.pdl = a.pdl ? 1u : 0u;
   p.wait_tables = a.tables_shared ? 0u : 1u;
-  auto kernel = w->codec == tbf::kB3 ? decode_kernel<tbf::kB3> : decode_kernel<tbf::kD2>;
+  const bool dual = use_dual(a.m);
+  DecodeKernel kernel = w->codec == tbf::kB3 ? pick_planes<tbf::kB3>(w->uniform_planes, dual) : pick_planes<tbf::kD2>(w->uniform_planes, dual);
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
   if (err != cudaSuccess) return err;
   cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(std::min<uint32_t>(p.blocks * p.layer_count, uint32_t(sm_count)));
+  // A grouped launch keeps two CTAs per SM busy; a single layer keeps one, so that the next
+  // launch on the stream can move in beside it.
+  const uint32_t resident = uint32_t(sm_count) * (a.layers ? p.ctas_per_sm : 1u);
+  cfg.gridDim = dim3(std::min<uint32_t>(p.blocks * p.layer_count, resident));
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
