@@ -34,6 +34,7 @@ constexpr int kConsumerWarps = 8;
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
 constexpr int kMaxStages = 4;
 constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr int kMaxGroupLayers = 128;   // layers of one grouped launch (descriptors live in shared memory)
 
 struct DecodeParams {
   const uint8_t* payload; const uint16_t* scales;   // single layer (layers == nullptr)
@@ -79,6 +80,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (i >= 4) __nanosleep(100);   // waiting warps should not take issue slots from working ones
     if ((i & 255u) == 255u && *abort_flag) return false;
   }
   return false;
@@ -296,13 +298,16 @@ __global__ void __launch_bounds__(256) prepare_kernel(const PrepareParams p) {
 }
 
 // ---------------------------------------------------------------- the kernel
-template <int CODEC, int PLANES, bool DUAL>
+template <int CODEC, int PLANES, int M>
 __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams p) {
   using T = Traits<CODEC>;
+  constexpr bool DUAL = M <= 2;
   constexpr int kNM = MmaCount<CODEC, DUAL>::value;
+  constexpr uint32_t ncol = (DUAL ? 4 : 2) * M;   // MMA columns in use
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ uint64_t full_bar[kMaxStages], empty_bar[kMaxStages], table_bar;
   __shared__ uint32_t abort_flag;
+  __shared__ TbLayerDesc layer_desc[kMaxGroupLayers];
 
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   uint8_t* ring = smem + p.off_ring;
@@ -317,6 +322,10 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
     for (uint32_t s = 0; s < p.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], kConsumerWarps); }
     mbar_init(&table_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  for (uint32_t l = tid; l < p.layer_count; l += kThreads) {
+    if (p.layers) { layer_desc[l].payload = p.layers[l].payload; layer_desc[l].scales = p.layers[l].scales; }
+    else { layer_desc[l].payload = p.payload; layer_desc[l].scales = p.scales; }
   }
   __syncthreads();
   // The next kernel on the stream may begin once every CTA has passed this point.  When this
@@ -341,8 +350,8 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
         }
         const uint32_t gblk = blockIdx.x + it * gridDim.x;
         const uint32_t layer = gblk / p.blocks, blk = gblk - layer * p.blocks;
-        const uint8_t* pay = p.layers ? p.layers[layer].payload : p.payload;
-        const uint8_t* scs = reinterpret_cast<const uint8_t*>(p.layers ? p.layers[layer].scales : p.scales);
+        const uint8_t* pay = layer_desc[layer].payload;
+        const uint8_t* scs = reinterpret_cast<const uint8_t*>(layer_desc[layer].scales);
         mbar_expect_tx(&full_bar[s], p.stage_bytes + p.scale_stage_bytes);
         bulk_g2s(ring + size_t(s) * p.stage_bytes, pay + size_t(blk) * p.stage_bytes, p.stage_bytes, &full_bar[s]);
         bulk_g2s(scale_ring + size_t(s) * p.scale_stage_bytes, scs + size_t(blk) * p.scale_stage_bytes,
@@ -368,7 +377,6 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   }
-  const uint32_t ncol = (DUAL ? 4 : 2) * p.m;
   if (ctid == 0) {
     mbar_expect_tx(&table_bar, p.table_bytes);
     bulk_g2s(smem + p.off_z, p.tables, p.table_bytes, &table_bar);
@@ -387,19 +395,21 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
   const uint32_t g = lane >> 2, c = lane & 3;
   const uint32_t rp_per_stage = p.rows_per_stage * PLANES;        // multiple of 16
   const uint32_t sets = rp_per_stage >> 4;
-  const uint32_t items = p.tpr * sets;
+  const uint32_t items = p.tpr * sets;   // (set, tile column) pairs, set-major
   const uint32_t per_warp = (items + kConsumerWarps - 1) / kConsumerWarps;
   const uint32_t item_lo = warp * per_warp, item_hi = min(items, item_lo + per_warp);
-  const uint32_t part_stride = rp_per_stage * p.m;                // floats per warp slice
+  const uint32_t first_set = item_lo / p.tpr, first_j = item_lo - first_set * p.tpr;
+  const uint32_t part_stride = rp_per_stage * M;                  // floats per warp slice
   // Which (scale group, token) cell of the C fragment this lane finishes.
   //   separate accumulators: lane column c holds token c, both groups;
   //   dual columns:          lane column c holds group c / m, token c % m.
-  const bool lane_has_cell = DUAL ? c < 2 * p.m : c < p.m;
-  const uint32_t cell_group = DUAL ? (c >= p.m ? 1u : 0u) : 0u;
-  const uint32_t cell_token = DUAL ? c - cell_group * p.m : c;
-  const bool has_b = g < ncol;
-  const uint32_t zstep = has_b ? ncol * 4 : 0;
-  const uint2* zero_entry = reinterpret_cast<const uint2*>(smem + p.off_zero);
+  const bool lane_has_cell = DUAL ? c < 2 * M : c < M;
+  const uint32_t cell_group = DUAL ? (c >= M ? 1u : 0u) : 0u;
+  const uint32_t cell_token = DUAL ? c - cell_group * M : c;
+  // MMA columns beyond `ncol` produce sums nobody reads, so their lanes may load any valid
+  // table entry: fold them onto the used columns instead of masking.
+  const uint32_t bcol = g % ncol;
+  constexpr uint32_t zstep = ncol * 4;
   const uint32_t groups_per_row = p.tpr * 2;
 
   for (uint32_t it = 0; it < my_blocks; ++it) {
@@ -418,126 +428,137 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
     const uint32_t layer = gblk / p.blocks, blk = gblk - layer * p.blocks;
     const uint32_t row0 = blk * p.rows_per_stage;
 
-    uint32_t j = item_lo / sets, set = item_lo - j * sets;
-    for (uint32_t item = item_lo; landed && item < item_hi; ++item, ++set) {
-      if (set == sets) { set = 0; ++j; }
-      // B fragments (activation tables) of tile column j for this lane; lanes whose MMA column
-      // is beyond the used columns read a zero entry.
-      const uint2* zlane = has_b ? ztab + (size_t(j) * kNM * ncol + g) * 4 + c : zero_entry;
-#define TB_BFRAG(mm) (zlane[(mm) * zstep])
+    // Items are (row set, tile column) pairs in set-major order; a warp's range is contiguous, so
+    // it walks the columns of one set with running pointers and keeps the two rows' partial
+    // sums in registers until the set changes.
+    uint32_t item = item_lo, set = first_set, j = first_j;
+    for (; landed && item < item_hi; ++set, j = 0) {
+      const uint32_t j_end = min(p.tpr, j + (item_hi - item));
+      item += j_end - j;
       const uint32_t rpa = set * 16 + g, rpb = rpa + 8;
       const uint32_t na = rpa / PLANES, pa = rpa - na * PLANES;
       const uint32_t nb = rpb / PLANES, pb = rpb - nb * PLANES;
-      const uint32_t tpa = (na * p.tpr + j) * PLANES + pa, tpb = (nb * p.tpr + j) * PLANES + pb;
-      const uint32_t* wa = words + size_t(tpa) * (T::kPlaneBytes / 4);
-      const uint32_t* wb = words + size_t(tpb) * (T::kPlaneBytes / 4);
-      int acc0[4], acc1[4];   // group 0 / group 1 sums (dual layout: acc0 holds this lane's group)
+      constexpr uint32_t kWordsPerPlane = T::kPlaneBytes / 4, kColStride = PLANES * kWordsPerPlane;
+      const uint32_t* wa = words + ((na * p.tpr + j) * PLANES + pa) * kWordsPerPlane + c;
+      const uint32_t* wb = words + ((nb * p.tpr + j) * PLANES + pb) * kWordsPerPlane + c;
+      // f16 scales of (row-plane, tile): two per u32, [group 0 | group 1]
+      const uint16_t* sca = reinterpret_cast<const uint16_t*>(scl + (na * p.tpr + j) * PLANES + pa) + (DUAL ? cell_group : 0);
+      const uint16_t* scb = reinterpret_cast<const uint16_t*>(scl + (nb * p.tpr + j) * PLANES + pb) + (DUAL ? cell_group : 0);
+      const int* cin = cinit + ((DUAL ? cell_token : c) * p.tpr + j) * 2 + (DUAL ? cell_group : 0);
+      const uint2* zlane = ztab + (size_t(j) * kNM * ncol + bcol) * 4 + c;
+      constexpr uint32_t zcol = kNM * ncol * 4;
+#define TB_BFRAG(mm) (zlane[(mm) * zstep])
+      float ya = 0.f, yb = 0.f;
 
-      if (CODEC == tbf::kB3) {
-        // One short accumulation chain per packed word keeps dependent MMAs three deep.
-        int s0[4], s1[4], s2[4], s3[4];
-        uint32_t qa[5], qb[5];
-        uint2 b;
-        b3_quads(wa[c], qa); b3_quads(wb[c], qb);
-        b = TB_BFRAG(0); mma_u8s8_first(s0, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
-        b = TB_BFRAG(1); mma_u8s8(s0, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
-        b = TB_BFRAG(2); mma_u8s8(s0, qa[4], qb[4], 0u, 0u, b.x, b.y);
-        b3_quads(wa[4 + c], qa); b3_quads(wb[4 + c], qb);
-        if (DUAL) {
-          b = TB_BFRAG(3); mma_u8s8_first(s1, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
-          b = TB_BFRAG(4); mma_u8s8(s1, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
-          b = TB_BFRAG(5); mma_u8s8(s1, qa[4], qb[4], 0u, 0u, b.x, b.y);
+      for (; j < j_end; ++j, wa += kColStride, wb += kColStride, sca += 2 * PLANES, scb += 2 * PLANES, cin += 2, zlane += zcol) {
+        int acc0[4], acc1[4];   // group 0 / group 1 sums (dual layout: acc0 holds this lane's group)
+        if (CODEC == tbf::kB3) {
+          // One short accumulation chain per packed word keeps dependent MMAs three deep.
+          int s0[4], s1[4], s2[4], s3[4];
+          uint32_t qa[5], qb[5];
+          uint2 b;
+          b3_quads(wa[0], qa); b3_quads(wb[0], qb);
+          b = TB_BFRAG(0); mma_u8s8_first(s0, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
+          b = TB_BFRAG(1); mma_u8s8(s0, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
+          b = TB_BFRAG(2); mma_u8s8(s0, qa[4], qb[4], 0u, 0u, b.x, b.y);
+          b3_quads(wa[4], qa); b3_quads(wb[4], qb);
+          if (DUAL) {
+            b = TB_BFRAG(3); mma_u8s8_first(s1, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
+            b = TB_BFRAG(4); mma_u8s8(s1, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
+            b = TB_BFRAG(5); mma_u8s8(s1, qa[4], qb[4], 0u, 0u, b.x, b.y);
+          } else {
+            // the words 4..7 straddle the two scale groups: once per group, masked on the B side
+            int s1b[4];
+            b = TB_BFRAG(3); mma_u8s8_first(s1, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
+            b = TB_BFRAG(6); mma_u8s8_first(s1b, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
+            b = TB_BFRAG(4); mma_u8s8(s1, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
+            b = TB_BFRAG(7); mma_u8s8(s1b, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
+            b = TB_BFRAG(5); mma_u8s8(s1, qa[4], qb[4], 0u, 0u, b.x, b.y);
+            b = TB_BFRAG(8); mma_u8s8(s1b, qa[4], qb[4], 0u, 0u, b.x, b.y);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc1[e] = s1b[e];
+          }
+          constexpr int o2 = DUAL ? 6 : 9, o3 = DUAL ? 9 : 12;
+          b3_quads(wa[8], qa); b3_quads(wb[8], qb);
+          b = TB_BFRAG(o2); mma_u8s8_first(s2, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
+          b = TB_BFRAG(o2 + 1); mma_u8s8(s2, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
+          b = TB_BFRAG(o2 + 2); mma_u8s8(s2, qa[4], qb[4], 0u, 0u, b.x, b.y);
+          b3_quads(wa[12 - c], qa); b3_quads(wb[12 - c], qb);   // word 12 for every lane column
+          b = TB_BFRAG(o3); mma_u8s8_first(s3, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
+          b = TB_BFRAG(o3 + 1); mma_u8s8(s3, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
+          b = TB_BFRAG(o3 + 2); mma_u8s8(s3, qa[4], qb[4], 0u, 0u, b.x, b.y);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            if (DUAL) acc0[e] = (s0[e] + s1[e]) + (s2[e] + s3[e]);
+            else { acc0[e] = s0[e] + s1[e]; acc1[e] = acc1[e] + s2[e] + s3[e]; }
+          }
         } else {
-          // the words 4..7 straddle the two scale groups: once per group, masked on the B side
-          int s1b[4];
-          b = TB_BFRAG(3); mma_u8s8_first(s1, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
-          b = TB_BFRAG(6); mma_u8s8_first(s1b, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
-          b = TB_BFRAG(4); mma_u8s8(s1, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
-          b = TB_BFRAG(7); mma_u8s8(s1b, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
-          b = TB_BFRAG(5); mma_u8s8(s1, qa[4], qb[4], 0u, 0u, b.x, b.y);
-          b = TB_BFRAG(8); mma_u8s8(s1b, qa[4], qb[4], 0u, 0u, b.x, b.y);
+          int sq[4][4];
 #pragma unroll
-          for (int e = 0; e < 4; ++e) acc1[e] = s1b[e];
+          for (int sl = 0; sl < 4; ++sl) {
+            const uint32_t va = wa[sl * 4], vb = wb[sl * 4];
+            uint2 b = TB_BFRAG(sl * 2);
+            mma_u8s8_first(sq[sl], va & 0x03030303u, vb & 0x03030303u, (va >> 2) & 0x03030303u, (vb >> 2) & 0x03030303u, b.x, b.y);
+            b = TB_BFRAG(sl * 2 + 1);
+            mma_u8s8(sq[sl], (va >> 4) & 0x03030303u, (vb >> 4) & 0x03030303u, (va >> 6) & 0x03030303u,
+                     (vb >> 6) & 0x03030303u, b.x, b.y);
+          }
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            if (DUAL) acc0[e] = (sq[0][e] + sq[1][e]) + (sq[2][e] + sq[3][e]);
+            else { acc0[e] = sq[0][e] + sq[1][e]; acc1[e] = sq[2][e] + sq[3][e]; }
+          }
         }
-        constexpr int o2 = DUAL ? 6 : 9, o3 = DUAL ? 9 : 12;
-        b3_quads(wa[8 + c], qa); b3_quads(wb[8 + c], qb);
-        b = TB_BFRAG(o2); mma_u8s8_first(s2, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
-        b = TB_BFRAG(o2 + 1); mma_u8s8(s2, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
-        b = TB_BFRAG(o2 + 2); mma_u8s8(s2, qa[4], qb[4], 0u, 0u, b.x, b.y);
-        b3_quads(wa[12], qa); b3_quads(wb[12], qb);
-        b = TB_BFRAG(o3); mma_u8s8_first(s3, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
-        b = TB_BFRAG(o3 + 1); mma_u8s8(s3, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
-        b = TB_BFRAG(o3 + 2); mma_u8s8(s3, qa[4], qb[4], 0u, 0u, b.x, b.y);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          if (DUAL) acc0[e] = (s0[e] + s1[e]) + (s2[e] + s3[e]);
-          else { acc0[e] = s0[e] + s1[e]; acc1[e] = acc1[e] + s2[e] + s3[e]; }
-        }
-      } else {
-        int sq[4][4];
-#pragma unroll
-        for (int sl = 0; sl < 4; ++sl) {
-          const uint32_t va = wa[sl * 4 + c], vb = wb[sl * 4 + c];
-          uint2 b = TB_BFRAG(sl * 2);
-          mma_u8s8_first(sq[sl], va & 0x03030303u, vb & 0x03030303u, (va >> 2) & 0x03030303u, (vb >> 2) & 0x03030303u, b.x, b.y);
-          b = TB_BFRAG(sl * 2 + 1);
-          mma_u8s8(sq[sl], (va >> 4) & 0x03030303u, (vb >> 4) & 0x03030303u, (va >> 6) & 0x03030303u,
-                   (vb >> 6) & 0x03030303u, b.x, b.y);
-        }
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          if (DUAL) acc0[e] = (sq[0][e] + sq[1][e]) + (sq[2][e] + sq[3][e]);
-          else { acc0[e] = sq[0][e] + sq[1][e]; acc1[e] = sq[2][e] + sq[3][e]; }
+
+        // finish the cells: columns (2c, 2c+1) are the high / low activation parts of one cell
+        if (DUAL) {
+          if (lane_has_cell) {
+            const int ci = cin[0];
+            const int ia = 4 * acc0[0] + acc0[1] + ci, ib = 4 * acc0[2] + acc0[3] + ci;
+            ya = __fadd_rn(ya, __fmul_rn(float(ia), __half2float(__ushort_as_half(sca[0]))));
+            yb = __fadd_rn(yb, __fmul_rn(float(ib), __half2float(__ushort_as_half(scb[0]))));
+            if (p.acc_dump) {
+              const uint32_t tok = p.dump_token_offset + cell_token;
+              if (row0 + na < p.n)
+                p.acc_dump[((size_t(tok) * p.n + row0 + na) * groups_per_row + 2 * j + cell_group) * PLANES + pa] = ia;
+              if (row0 + nb < p.n)
+                p.acc_dump[((size_t(tok) * p.n + row0 + nb) * groups_per_row + 2 * j + cell_group) * PLANES + pb] = ib;
+            }
+          }
+        } else if (lane_has_cell) {
+          const int ci0 = cin[0], ci1 = cin[1];
+          const int ia0 = 4 * acc0[0] + acc0[1] + ci0, ia1 = 4 * acc1[0] + acc1[1] + ci1;
+          const int ib0 = 4 * acc0[2] + acc0[3] + ci0, ib1 = 4 * acc1[2] + acc1[3] + ci1;
+          ya = __fadd_rn(ya, __fadd_rn(__fmul_rn(float(ia0), __half2float(__ushort_as_half(sca[0]))),
+                                       __fmul_rn(float(ia1), __half2float(__ushort_as_half(sca[1])))));
+          yb = __fadd_rn(yb, __fadd_rn(__fmul_rn(float(ib0), __half2float(__ushort_as_half(scb[0]))),
+                                       __fmul_rn(float(ib1), __half2float(__ushort_as_half(scb[1])))));
+          if (p.acc_dump) {
+            const uint32_t tok = p.dump_token_offset + c;
+            if (row0 + na < p.n) {
+              int32_t* d = p.acc_dump + ((size_t(tok) * p.n + row0 + na) * groups_per_row + 2 * j) * PLANES + pa;
+              d[0] = ia0; d[PLANES] = ia1;
+            }
+            if (row0 + nb < p.n) {
+              int32_t* d = p.acc_dump + ((size_t(tok) * p.n + row0 + nb) * groups_per_row + 2 * j) * PLANES + pb;
+              d[0] = ib0; d[PLANES] = ib1;
+            }
+          }
         }
       }
 #undef TB_BFRAG
-
-      // finish the cells: columns (2c, 2c+1) are the high / low activation parts of one cell
+      // hand the set's partial sums to the stage combine
       if (DUAL) {
-        float va = 0.f, vb = 0.f;
-        if (lane_has_cell) {
-          const int ci = cinit[(cell_token * p.tpr + j) * 2 + cell_group];
-          const int ia = 4 * acc0[0] + acc0[1] + ci, ib = 4 * acc0[2] + acc0[3] + ci;
-          const __half2 sa = *reinterpret_cast<const __half2*>(&scl[tpa]);
-          const __half2 sb = *reinterpret_cast<const __half2*>(&scl[tpb]);
-          va = __fmul_rn(float(ia), cell_group ? __high2float(sa) : __low2float(sa));
-          vb = __fmul_rn(float(ib), cell_group ? __high2float(sb) : __low2float(sb));
-          if (p.acc_dump) {
-            const uint32_t tok = p.dump_token_offset + cell_token;
-            if (row0 + na < p.n)
-              p.acc_dump[((size_t(tok) * p.n + row0 + na) * groups_per_row + 2 * j + cell_group) * PLANES + pa] = ia;
-            if (row0 + nb < p.n)
-              p.acc_dump[((size_t(tok) * p.n + row0 + nb) * groups_per_row + 2 * j + cell_group) * PLANES + pb] = ib;
-          }
-        }
         // the two scale groups of a (row, token) sit p.m lanes apart: group 0 + group 1
-        va = __fadd_rn(va, __shfl_xor_sync(0xffffffffu, va, p.m));
-        vb = __fadd_rn(vb, __shfl_xor_sync(0xffffffffu, vb, p.m));
+        ya = __fadd_rn(ya, __shfl_xor_sync(0xffffffffu, ya, M));
+        yb = __fadd_rn(yb, __shfl_xor_sync(0xffffffffu, yb, M));
         if (lane_has_cell && cell_group == 0) {
-          my_part[rpa * p.m + cell_token] += va;
-          my_part[rpb * p.m + cell_token] += vb;
+          my_part[rpa * M + cell_token] += ya;
+          my_part[rpb * M + cell_token] += yb;
         }
       } else if (lane_has_cell) {
-        const int ci0 = cinit[(c * p.tpr + j) * 2], ci1 = cinit[(c * p.tpr + j) * 2 + 1];
-        const int ia0 = 4 * acc0[0] + acc0[1] + ci0, ia1 = 4 * acc1[0] + acc1[1] + ci1;
-        const int ib0 = 4 * acc0[2] + acc0[3] + ci0, ib1 = 4 * acc1[2] + acc1[3] + ci1;
-        const __half2 sa = *reinterpret_cast<const __half2*>(&scl[tpa]);
-        const __half2 sb = *reinterpret_cast<const __half2*>(&scl[tpb]);
-        const float va = __fadd_rn(__fmul_rn(float(ia0), __low2float(sa)), __fmul_rn(float(ia1), __high2float(sa)));
-        const float vb = __fadd_rn(__fmul_rn(float(ib0), __low2float(sb)), __fmul_rn(float(ib1), __high2float(sb)));
-        my_part[rpa * p.m + c] += va;
-        my_part[rpb * p.m + c] += vb;
-        if (p.acc_dump) {
-          const uint32_t tok = p.dump_token_offset + c;
-          if (row0 + na < p.n) {
-            int32_t* d = p.acc_dump + ((size_t(tok) * p.n + row0 + na) * groups_per_row + 2 * j) * PLANES + pa;
-            d[0] = ia0; d[PLANES] = ia1;
-          }
-          if (row0 + nb < p.n) {
-            int32_t* d = p.acc_dump + ((size_t(tok) * p.n + row0 + nb) * groups_per_row + 2 * j) * PLANES + pb;
-            d[0] = ib0; d[PLANES] = ib1;
-          }
-        }
+        my_part[rpa * M + c] += ya;
+        my_part[rpb * M + c] += yb;
       }
     }
     __syncwarp();
@@ -548,14 +569,14 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
     consumer_sync();
     if (abort_flag) return;
     const float* stage_part = part + (it & 1) * kConsumerWarps * part_stride;
-    for (uint32_t e = ctid; e < p.rows_per_stage * p.m; e += kCT) {
+    for (uint32_t e = ctid; e < p.rows_per_stage * M; e += kCT) {
       const uint32_t t = e / p.rows_per_stage, r = e - t * p.rows_per_stage;
       if (row0 + r >= p.n) continue;
       float sum = 0.f;
 #pragma unroll
       for (uint32_t q = 0; q < PLANES; ++q)
         for (int w2 = 0; w2 < kConsumerWarps; ++w2)
-          sum = __fadd_rn(sum, stage_part[w2 * part_stride + (r * PLANES + q) * p.m + t]);
+          sum = __fadd_rn(sum, stage_part[w2 * part_stride + (r * PLANES + q) * M + t]);
       float out = __fmul_rn(sum, act_scale[t]);
       if (p.row_scale) out = __fmul_rn(out, p.row_scale[row0 + r]);
       const size_t idx = size_t(layer) * p.y_layer_stride + size_t(t) * p.y_row_stride + row0 + r;
@@ -594,7 +615,7 @@ size_t layout(const tb_weights* w, uint32_t m, int max_smem, DecodeParams* p) {
   if (fixed + 2 * per_stage > uint32_t(max_smem)) return 0;
   // Prefer a footprint that lets two CTAs share an SM (one of this launch, one of the next launch
   // on the stream, whose weight stream then starts under this launch's tail).
-  const uint32_t half_sm = 113u * 1024u;
+  const uint32_t half_sm = 110u * 1024u;   // two CTAs (dynamic + static + 1 KB reserved each) within 228 KB
   const uint32_t budget = fixed + 2 * per_stage <= half_sm ? half_sm : uint32_t(max_smem);
   uint32_t stages = std::min<uint32_t>(kMaxStages, (budget - fixed) / per_stage);
   if (p) {
@@ -670,11 +691,12 @@ cudaError_t tb_launch_prepare(const DecodeArgs& a, cudaStream_t stream) {
 }
 
 using DecodeKernel = void (*)(const DecodeParams);
-template <int CODEC, int PLANES> DecodeKernel pick_dual(bool dual) {
-  return dual ? decode_kernel<CODEC, PLANES, true> : decode_kernel<CODEC, PLANES, false>;
+template <int CODEC, int PLANES> DecodeKernel pick_tokens(uint32_t m) {
+  return m == 1 ? decode_kernel<CODEC, PLANES, 1> : m == 2 ? decode_kernel<CODEC, PLANES, 2>
+       : m == 3 ? decode_kernel<CODEC, PLANES, 3> : decode_kernel<CODEC, PLANES, 4>;
 }
-template <int CODEC> DecodeKernel pick_planes(uint32_t planes, bool dual) {
-  return planes == 1 ? pick_dual<CODEC, 1>(dual) : planes == 2 ? pick_dual<CODEC, 2>(dual) : pick_dual<CODEC, 3>(dual);
+template <int CODEC> DecodeKernel pick_planes(uint32_t planes, uint32_t m) {
+  return planes == 1 ? pick_tokens<CODEC, 1>(m) : planes == 2 ? pick_tokens<CODEC, 2>(m) : pick_tokens<CODEC, 3>(m);
 }
 
 cudaError_t tb_launch_decode(const DecodeArgs& a, int sm_count, int max_smem, cudaStream_t stream) {
@@ -699,8 +721,8 @@ cudaError_t tb_launch_decode(const DecodeArgs& a, int sm_count, int max_smem, cu
   p.dump_token_offset = a.dump_token_offset; p.dump_tokens_total = a.dump_tokens_total;
   p.pdl = a.pdl ? 1u : 0u;
   p.wait_tables = a.tables_shared ? 0u : 1u;
-  const bool dual = use_dual(a.m);
-  DecodeKernel kernel = w->codec == tbf::kB3 ? pick_planes<tbf::kB3>(w->uniform_planes, dual) : pick_planes<tbf::kD2>(w->uniform_planes, dual);
+  DecodeKernel kernel = w->codec == tbf::kB3 ? pick_planes<tbf::kB3>(w->uniform_planes, a.m) : pick_planes<tbf::kD2>(w->uniform_planes, a.m);
+  if (a.layers && a.layer_count > uint32_t(kMaxGroupLayers)) return cudaErrorInvalidValue;
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
   if (err != cudaSuccess) return err;
   cudaLaunchConfig_t cfg{};

@@ -557,6 +557,7 @@ extern "C" tb_status tb_stack_create(tb_backend* b, const tb_weights* const* wei
     if (!st->chain[i])
       while (e < layers && !st->chain[e] && same_geometry(st->layers[i], st->layers[e])) ++e;
     const bool feeds_chain = e < layers && st->chain[e];
+    if (e - i > 128) e = i + 128;   // descriptor capacity of one grouped launch
     if (e - i >= 2 && !feeds_chain) {
       StackGroup g;
       g.first = i; g.count = e - i;
