@@ -158,6 +158,25 @@ typedef struct tb_forward_args {
 } tb_forward_args;
 tb_status tb_linear_forward_dev(tb_backend* backend, const tb_weights* weights,
                                 const tb_forward_args* args, tb_receipt* receipt);
+/* No counterpart in the reference: an int8-path forward (1..4 tokens, device pointers) for
+ * callers that are not allowed to allocate device memory while they run — a serving loop whose
+ * memory is fully planned up front, a latency-critical thread that must not enter the driver's
+ * allocator (cudaMalloc and cudaFree serialise the whole device), or code that runs while every
+ * byte of HBM is already spoken for.  This call performs no cudaMalloc, cudaFree or any other
+ * allocating call: its only working memory, the activation tables, sits in a fixed 256 KiB array
+ * that is part of the library image on every GPU that loads it (held until the process exits).
+ *   - Shapes whose tables do not fit (roughly m * k above 40k elements for B3, m <= 4 always) are
+ *     refused with TB_INVALID_INPUT and a message that states both sizes.
+ *   - The first call on a device looks up the array's device address; make that first call
+ *     before starting any stream capture, and from one thread.
+ *   - All calls share the one array.  Each call rewrites every table entry it later reads, so
+ *     nothing has to be cleared, but two calls that overlap on the GPU (different streams, or the
+ *     same stream with programmatic overlap) race on it: keep them ordered.
+ * `act_scale` is needed only for int8 activations.  Results equal tb_linear_forward_dev with
+ * TB_FWD_A8.  Timeouts and finite checks are reported by tb_backend_check as usual. */
+tb_status tb_linear_forward_a8_static(tb_backend* backend, const tb_weights* weights, const void* x,
+                                      tb_dtype x_dtype, const float* act_scale, uint32_t m, void* y,
+                                      tb_dtype y_dtype, void* stream);
 /* Reserves the backend's device scratch for `weights` at up to `max_m` tokens, so that later
  * tb_linear_forward_dev calls allocate nothing. */
 tb_status tb_backend_reserve(tb_backend* backend, const tb_weights* weights, uint32_t max_m);

@@ -25,7 +25,7 @@ EXPORTS = [
     "tb_stack_create", "tb_stack_forward_dev", "tb_stack_bytes_per_step", "tb_stack_read_output", "tb_stack_free",
     "tb_tp_shard_sizes", "tb_tp_shard", "tb_fmt_pack", "tb_fmt_unpack", "tb_fmt_plane_bytes",
     "tb_fmt_resident_sizes", "tb_fmt_resident_build", "tb_fmt_package_write", "tb_fmt_tq2_pack_rows",
-    "tb_fmt_quantize_act_int8",
+    "tb_fmt_quantize_act_int8", "tb_linear_forward_a8_static",
 ]
 
 

@@ -26,6 +26,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <string>
+
 #include "tb_internal.h"
 
 namespace {
@@ -736,4 +738,58 @@ cudaError_t tb_launch_decode(const DecodeArgs& a, int sm_count, int max_smem, cu
   cfg.attrs = attr;
   cfg.numAttrs = a.pdl ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, p);
+}
+
+// ---------------------------------------------------------------- allocation-free entry point
+// Scratch for callers that must not allocate: the activation tables normally live in a buffer the
+// backend obtained from cudaMalloc; here they live in this fixed array, which every GPU that loads
+// the library carries until the process exits.
+constexpr size_t kStaticTableBytes = 256u * 1024u;
+static __device__ __align__(256) uint8_t g_static_tables[kStaticTableBytes];
+
+namespace {
+// Device address of g_static_tables per device ordinal, resolved on the first call on that device.
+// In host code the array's name is only a handle for the runtime, never a device pointer.
+void* g_static_tables_ptr[64] = {};
+}  // namespace
+
+extern "C" tb_status tb_linear_forward_a8_static(tb_backend* backend, const tb_weights* weights, const void* x,
+                                                 tb_dtype x_dtype, const float* act_scale, uint32_t m, void* y,
+                                                 tb_dtype y_dtype, void* stream) {
+  if (!backend || !weights) return tb_fail(TB_NULL_ARG, "null argument");
+  if (weights->owner != backend) return tb_fail(TB_INVALID_INPUT, "weights handle belongs to another backend context");
+  if (m == 0 || weights->n == 0) return TB_OK;
+  if (!x || !y) return tb_fail(TB_NULL_ARG, "null activation or output pointer");
+  if (x_dtype == TB_I8 && !act_scale) return tb_fail(TB_NULL_ARG, "int8 activations need act_scale");
+  if (y_dtype == TB_I8) return tb_fail(TB_INVALID_INPUT, "output dtype must be fp32 or bf16");
+  if (m > 4) return tb_fail(TB_INVALID_INPUT, "the allocation-free entry point takes at most 4 tokens per call, got " + std::to_string(m));
+  if (!weights->fast) return tb_fail(TB_UNSUPPORTED_FORMAT, "the int8 path needs uniform plane counts, k % 256 == 0, group 128 and codec D2 or B3");
+  if (backend->ordinal < 0 || backend->ordinal >= 64) return tb_fail(TB_INVALID_INPUT, "device ordinal out of range");
+  const TableLayout tl = table_layout(weights, m);
+  if (tl.total > kStaticTableBytes)
+    return tb_fail(TB_INVALID_INPUT, "activation tables need " + std::to_string(tl.total) + " bytes but the fixed scratch holds " +
+                                         std::to_string(kStaticTableBytes) + " (k = " + std::to_string(weights->k) + ", m = " + std::to_string(m) + ")");
+  if (!tb_decode_supported(weights, m, backend->max_smem_optin, nullptr))
+    return tb_fail(TB_UNSUPPORTED_FORMAT, "the decode kernel's shared-memory plan does not fit this shape");
+  cudaError_t err = cudaSetDevice(backend->ordinal);
+  if (err != cudaSuccess) return tb_cuda_fail(err, "select device");
+  void*& tables = g_static_tables_ptr[backend->ordinal];
+  if (!tables) {
+    // once per device, with that device current
+    err = cudaGetSymbolAddress(&tables, g_static_tables);
+    if (err != cudaSuccess) { tables = nullptr; return tb_cuda_fail(err, "resolve the fixed scratch array"); }
+  }
+  cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : backend->stream;
+  DecodeArgs d{};
+  d.w = weights; d.x = x; d.x_dtype = x_dtype; d.act_scale_in = act_scale; d.m = m;
+  d.y = y; d.y_dtype = y_dtype; d.y_row_stride = uint32_t(weights->n);
+  d.status = backend->d_status; d.pdl = false;
+  d.scratch = tables; d.scratch_bytes = kStaticTableBytes;
+  // Nothing in the tables has to start at zero: the prepare kernel rewrites every entry the decode
+  // kernel of the same call reads (z entries, start values, token scales) before it is read.
+  err = tb_launch_prepare(d, st);
+  if (err != cudaSuccess) return tb_cuda_fail(err, "launch prepare");
+  err = tb_launch_decode(d, backend->prop.multiProcessorCount, backend->max_smem_optin, st);
+  if (err != cudaSuccess) return tb_cuda_fail(err, "launch decode");
+  return TB_OK;
 }
