@@ -177,6 +177,13 @@ tb_status tb_linear_forward_dev(tb_backend* backend, const tb_weights* weights,
 tb_status tb_linear_forward_a8_static(tb_backend* backend, const tb_weights* weights, const void* x,
                                       tb_dtype x_dtype, const float* act_scale, uint32_t m, void* y,
                                       tb_dtype y_dtype, void* stream);
+/* Per-token max|x| of `x` [m,k] (fp32 or bf16, device) into `out` [m] (fp32, device).  A
+ * row-parallel shard runs this on its slice of the activations, takes the maximum over the
+ * tensor-parallel group and passes the result as `act_absmax`, which reproduces the
+ * quantisation scale of quantize_act_int8 over the whole row
+ * (crates/tritium-spec/src/lib.rs:351-378; no sharded counterpart exists in the reference). */
+tb_status tb_act_absmax_dev(tb_backend* backend, const void* x, tb_dtype x_dtype, uint32_t m, uint32_t k,
+                            float* out, void* stream);
 /* Reserves the backend's device scratch for `weights` at up to `max_m` tokens, so that later
  * tb_linear_forward_dev calls allocate nothing. */
 tb_status tb_backend_reserve(tb_backend* backend, const tb_weights* weights, uint32_t max_m);

@@ -241,6 +241,71 @@ def test_a8_decode_full_size_configs(backend, name, codec):
             assert rel_l2(total, want_y) <= 1e-5
 
 
+# ------------------------------------------------------------------ int8 path (prefill kernel, tcgen05)
+@pytest.mark.parametrize("codec", [SaltV2Codec.B3, SaltV2Codec.D2])
+@pytest.mark.parametrize("planes", [1, 2, 3])
+@pytest.mark.parametrize("m,n,k", [(9, 40, 768), (16, 128, 256), (130, 200, 1024), (257, 129, 512)])
+def test_a8_prefill_small_shapes(backend, codec, planes, m, n, k):
+    prod, orac = uniform_pair(n, k, planes, seed=planes * 100 + m)
+    x = make_activations(m, k, seed=m)
+    want_y, want_acc, _ = orc.a8_linear(orac, x)
+    resident = backend.upload_salt_v2(prod, codec)
+    y, acc, receipt = backend.linear_forward_a8(resident, x, m, dump=True)
+    assert receipt.kernel == 2                                  # the tensor-core kernel ran
+    assert np.array_equal(acc, want_acc[:, :, :, :planes])      # int32 accumulators: bit exact
+    assert rel_l2(y, want_y) <= 1e-5
+    # two calls in a row give identical bits (no state left behind in the scratch or in TMEM)
+    y2, _, _ = backend.linear_forward_a8(resident, x, m)
+    assert np.array_equal(y, y2)
+
+
+def test_a8_prefill_extreme_activations_stay_exact(backend):
+    n, k, m = 130, 512, 32
+    prod, orac = uniform_pair(n, k, 3, seed=5)
+    prod.trits[:, 0, :] = 1
+    orac.trits[:, 0, :] = 1
+    x = np.ones((m, k), np.float32)
+    x[1::2] = -1.0                                      # every code is +-127: largest group sums
+    x[5] = 0.0                                          # a zero row: zero codes, zero scale
+    want_y, want_acc, _ = orc.a8_linear(orac, x)
+    for codec in (SaltV2Codec.B3, SaltV2Codec.D2):
+        y, acc, _ = backend.linear_forward_a8(backend.upload_salt_v2(prod, codec), x, m, dump=True)
+        assert np.array_equal(acc, want_acc) and np.all(y[5] == 0) and rel_l2(y, want_y) <= 1e-5
+
+
+@pytest.mark.parametrize("codec", [SaltV2Codec.B3, SaltV2Codec.D2])
+def test_a8_prefill_bf16_in_and_out(backend, codec):
+    n, k, planes, m = 192, 1024, 3, 48
+    prod, orac = uniform_pair(n, k, planes, seed=22)
+    x = make_activations(m, k, seed=4, bf16=True)
+    want_y, want_acc, _ = orc.a8_linear(orac, x)
+    resident = backend.upload_salt_v2(prod, codec)
+    y_bits, acc, _ = backend.linear_forward_a8(resident, f32_to_bf16_bits(x), m, y_dtype="bf16", dump=True, x_is_bf16=True)
+    assert np.array_equal(acc, want_acc)
+    assert rel_l2(bf16_bits_to_f32(y_bits), want_y) <= 1e-2
+
+
+@pytest.mark.parametrize("codec", [SaltV2Codec.B3, SaltV2Codec.D2])
+def test_a8_prefill_full_size_config(backend, codec):
+    """K=2560, N=6912, three planes, 2048 tokens: sampled rows against the CPU reference, and the
+    first tokens against the (already pinned) decode kernel on every row."""
+    n, k, planes, m = 6912, 2560, 3, 2048
+    prod, _ = uniform_pair(n, k, planes, seed=0)
+    x = make_activations(m, k, seed=1, bf16=True)
+    resident = backend.upload_salt_v2(prod, codec)
+    y, _, receipt = backend.linear_forward_a8(resident, x, m)
+    assert receipt.kernel == 2
+    rows = np.r_[0:8, 3451:3459, n - 8:n]
+    sub = orc.Tensor(len(rows), k, 128, prod.plane_count.reshape(n, -1)[rows].reshape(-1).copy(),
+                     prod.trits.reshape(n, k // 256, 3, 256)[rows].reshape(-1, 3, 256).copy(),
+                     prod.scales.reshape(n, k // 256, 3, -1)[rows].reshape(-1, 3, prod.scales.shape[-1]).copy())
+    tokens = np.r_[0:4, 1021:1027, m - 4:m]
+    want_y, _, _ = orc.a8_linear(sub, x[tokens])
+    assert rel_l2(y[np.ix_(tokens, rows)], want_y) <= 1e-5
+    y_dec, _, r_dec = backend.linear_forward_a8(resident, x[:4], 4)
+    assert r_dec.kernel == 1 and rel_l2(y[:4], y_dec) <= 1e-5
+
+
 # ------------------------------------------------------------------ trait path (TQ2_0 conformance)
 def conformance_vectors(seed=0xC0FFEE, count=12):
     """generate_vectors (crates/tritium-testkit/src/generate.rs:203-233), TQ2_0 cases only."""

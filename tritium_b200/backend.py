@@ -298,6 +298,14 @@ class B200Backend:
         args.stream = s.cuda_stream
         check(self._L.tb_linear_forward_dev(self._h, t._h, C.byref(args), None))
 
+    def act_absmax_dev(self, x, out, stream=None) -> None:
+        """Per-token max|x| of a [m, k] fp32/bf16 CUDA tensor into ``out`` (fp32 [m]); no sync."""
+        import torch
+        dt = {torch.float32: _lib.TB_F32, torch.bfloat16: _lib.TB_BF16}
+        s = stream if stream is not None else torch.cuda.current_stream()
+        check(self._L.tb_act_absmax_dev(self._h, C.c_void_p(x.data_ptr()), dt[x.dtype], C.c_uint32(x.shape[0]),
+                                        C.c_uint32(x.shape[1]), C.c_void_p(out.data_ptr()), C.c_void_p(s.cuda_stream)))
+
     def reserve(self, t, max_m: int) -> None:
         check(self._L.tb_backend_reserve(self._h, t._h, C.c_uint32(max_m)))
 

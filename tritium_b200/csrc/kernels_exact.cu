@@ -11,6 +11,8 @@
 // Compiled with --fmad=false; the explicit _rn intrinsics pin the rounding as well.
 #include <cuda_fp16.h>
 
+#include <cuda_bf16.h>
+
 #include "tb_internal.h"
 
 namespace {
@@ -215,6 +217,26 @@ __global__ void check_finite_kernel(const float* x, uint64_t count, uint32_t* st
     }
 }
 
+// max |x| of each token's row: one CTA per token
+__global__ void __launch_bounds__(256) row_absmax_kernel(const void* x, uint32_t dtype, uint32_t k, float* out) {
+  __shared__ float red[8];
+  const uint32_t t = blockIdx.x, tid = threadIdx.x;
+  float mx = 0.f;
+  for (uint32_t i = tid; i < k; i += 256) {
+    const size_t idx = size_t(t) * k + i;
+    const float v = dtype == TB_F32 ? static_cast<const float*>(x)[idx]
+                                    : __bfloat162float(static_cast<const __nv_bfloat16*>(x)[idx]);
+    mx = fmaxf(mx, fabsf(v));
+  }
+  for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if ((tid & 31) == 0) red[tid >> 5] = mx;
+  __syncthreads();
+  if (tid == 0) {
+    for (int w = 1; w < 8; ++w) mx = fmaxf(mx, red[w]);
+    out[t] = mx;
+  }
+}
+
 ExactParams make_params(const tb_weights* w) {
   ExactParams p{};
   p.payload = w->d_payload; p.scales = w->d_scales; p.meta = w->d_meta; p.tile_rank = w->d_tile_rank;
@@ -242,6 +264,12 @@ cudaError_t tb_launch_gather_rows(const tb_weights* w, const uint32_t* rows, uin
   const uint64_t total = uint64_t(count) * p.k;
   if (!total) return cudaSuccess;
   gather_rows_kernel<<<unsigned((total + 255) / 256), 256, 0, stream>>>(p, rows, count, out);
+  return cudaGetLastError();
+}
+
+cudaError_t tb_launch_row_absmax(const void* x, tb_dtype dtype, uint32_t m, uint32_t k, float* out, cudaStream_t stream) {
+  if (!m) return cudaSuccess;
+  row_absmax_kernel<<<m, 256, 0, stream>>>(x, uint32_t(dtype), k, out);
   return cudaGetLastError();
 }
 

@@ -1,6 +1,617 @@
-// Prefill GEMM placeholder translation unit (replaced by the tcgen05 kernel).
+// Prefill GEMM (many tokens) from the packed B3 / D2 arenas on the tcgen05 INT8 tensor cores.
+//
+//   Y[m,n] = a[m] * sum over (tile column j, plane p, group g) of s[n,j,p,g] * I[m,n,j,p,g],
+//   I = sum over the 128 trits of the group of t * q          (exact int32)
+//
+// One CTA owns a 128 (weight rows) x 128 (tokens) output tile and walks the K dimension in slabs
+// of one (tile column, plane, scale group) = 128 trits:
+//   * expander warps read each row's packed words, turn them into int8 operands with the
+//     half-precision-FMA digit trick (no table, no division) and write the slab as a K-major,
+//     128-byte-swizzled tile in shared memory (A operand, UMMA M = 128);
+//   * a TMA warp loads the int8 activations of the tile column (B operand, N = 128 tokens) from
+//     the scratch written by the quantisation pre-pass, already in the expander's k-slot order;
+//   * one thread issues four tcgen05.mma (kind::i8, K = 32 each) per slab into a TMEM accumulator
+//     that the epilogue pre-loaded with 0x4B400000 +/- (sum of the slab's activations): after the
+//     MMAs the accumulator's bits ARE the float 12582912 -/+ I, so int->float costs one FADD;
+//   * epilogue warps (one TMEM lane = one weight row per thread) drain the accumulator, multiply
+//     by the row's f16 group scale and add into an fp32 running sum that also lives in TMEM.
+// Operand signs: B3 digits come out of the FMA chain as -d (digits 0..3) / +d (digit 4), so the
+// activations of digit-4 slots are stored negated and the start value carries +sum(q); the
+// accumulator then holds magic - I.  D2 codes are used as unsigned c = t+1 with start value
+// magic - sum(q); the accumulator holds magic + I.
+//
+// TMEM columns: [0,128) accumulator 0, [128,256) accumulator 1, [256,384) fp32 running sums.
+// All waits are bounded; a timeout sets TBF_WAIT_TIMEOUT and every role leaves its loop, the
+// allocating warp frees TMEM, and the kernel returns.  No TMA multicast is used.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <algorithm>
+
 #include "tb_internal.h"
 
-bool tb_prefill_supported(const tb_weights*, uint32_t) { return false; }
-size_t tb_prefill_scratch_bytes(const tb_weights*, uint32_t) { return 0; }
-cudaError_t tb_launch_prefill(const PrefillArgs&, int, cudaStream_t) { return cudaErrorNotSupported; }
+namespace {
+
+constexpr int kRows = 128;        // weight rows per tile (UMMA M)
+constexpr int kTokens = 128;      // tokens per tile (UMMA N)
+constexpr int kStagesA = 4;       // expanded slabs in flight
+constexpr int kStagesB = 2;       // tile columns of activations in flight (two slabs each)
+constexpr int kThreads = 384;     // warps: 0 TMA, 1 MMA, 2 TMEM owner, 3 idle, 4-7 epilogue, 8-11 expanders
+constexpr uint32_t kSpin = 1u << 22;
+constexpr uint32_t kMagicBits = 0x4B400000u;   // float 12582912 = 2^23 + 2^22
+constexpr uint32_t kTileABytes = kRows * 128, kTileBBytes = kTokens * 128;
+
+struct PrefillParams {
+  const uint8_t* payload; const uint16_t* scales;
+  const int8_t* qperm; const int32_t* qinit; const float* ascale;   // scratch from the pre-pass
+  void* y; int32_t* acc_dump; const float* row_scale;
+  uint32_t* status;
+  uint32_t m, m_pad, n, k, tpr, y_dtype;
+  uint32_t n_tiles, m_tiles;
+};
+
+// ---------------------------------------------------------------- PTX helpers
+__device__ __forceinline__ uint32_t saddr(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint64_t* b, uint32_t c) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(saddr(b)), "r"(c)); }
+__device__ __forceinline__ void mbar_arrive(uint64_t* b) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(saddr(b)) : "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* b, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(saddr(b)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t* b, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(ok) : "r"(saddr(b)), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, volatile uint32_t* abort_flag) {
+  for (uint32_t i = 0; i < kSpin; ++i) {
+    if (mbar_try(b, parity)) return true;
+    if (i >= 8) __nanosleep(64);
+    if ((i & 127u) == 127u && *abort_flag) return false;
+  }
+  return false;
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t r; asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel)); return r;
+}
+__device__ __forceinline__ uint32_t hfma2(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t r; asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c)); return r;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(saddr(dst)), "l"(map), "r"(x), "r"(y), "r"(saddr(bar)) : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(saddr(dst)), "l"(src), "r"(bytes), "r"(saddr(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(saddr(bar)) : "memory");
+}
+// D[tmem] += A[smem] * B[smem], int8 operands, int32 accumulate (accumulate flag always set: the
+// accumulator was pre-loaded by the epilogue).
+__device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(1u), "r"(0u) : "memory");
+}
+#define TB_R32(a, o) "=r"(a[o+0]), "=r"(a[o+1]), "=r"(a[o+2]), "=r"(a[o+3]), "=r"(a[o+4]), "=r"(a[o+5]), "=r"(a[o+6]), "=r"(a[o+7]), \
+                     "=r"(a[o+8]), "=r"(a[o+9]), "=r"(a[o+10]), "=r"(a[o+11]), "=r"(a[o+12]), "=r"(a[o+13]), "=r"(a[o+14]), "=r"(a[o+15])
+#define TB_S32(a, o) "r"(a[o+0]), "r"(a[o+1]), "r"(a[o+2]), "r"(a[o+3]), "r"(a[o+4]), "r"(a[o+5]), "r"(a[o+6]), "r"(a[o+7]), \
+                     "r"(a[o+8]), "r"(a[o+9]), "r"(a[o+10]), "r"(a[o+11]), "r"(a[o+12]), "r"(a[o+13]), "r"(a[o+14]), "r"(a[o+15])
+// 32 lanes x 16 columns of 32 bits: this thread's lane, 16 consecutive columns
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+               : TB_R32(r, 0) : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+               ::"r"(taddr), TB_S32(r, 0) : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major tile of 128-byte rows, 128-byte swizzle, 8-row groups
+// 1024 bytes apart; `k_chunk` selects the 32-byte K slice of one MMA inside the swizzled row.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t k_chunk) {
+  uint64_t d = 0;
+  d |= uint64_t(((addr + k_chunk * 32u) & 0x3ffffu) >> 4);   // start address
+  d |= uint64_t(1) << 16;                                    // leading byte offset (unused for swizzled K-major)
+  d |= uint64_t(1024 >> 4) << 32;                            // stride byte offset
+  d |= uint64_t(1) << 46;                                    // descriptor version
+  d |= uint64_t(2) << 61;                                    // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor: s32 accumulate, A/B formats, K-major both, N, M.
+constexpr uint32_t kInstrDesc = (2u << 4)                       // s32 accumulator
+                                | (1u << 7) | (1u << 10)        // A and B are signed 8-bit
+                                | ((uint32_t(kTokens) >> 3) << 17) | ((uint32_t(kRows) >> 4) << 24);
+
+// ---------------------------------------------------------------- k-slot order of a slab
+// slot (0..127) of trit t (0..255 of the tile) inside its group's slab: packed words are expanded
+// digit-major (quad = 5*word + digit, byte lane = byte of the word); the word that straddles the
+// group boundary (bytes 24..27) and the last word (bytes 48..51, four padding digits) are laid
+// out in natural trit order.
+__host__ __device__ inline uint32_t b3_slot(uint32_t t) {
+  if (t < 120) { const uint32_t w = t / 20, r = t % 20; return 4 * (5 * w + r % 5) + r / 5; }
+  if (t < 128) return t;
+  if (t < 140) return t - 128;
+  if (t < 240) { const uint32_t w = t / 20, r = t % 20; return 4 * (3 + 5 * (w - 7) + r % 5) + r / 5; }
+  return 112 + (t - 240);
+}
+__host__ __device__ inline uint32_t d2_slot(uint32_t t) {
+  const uint32_t u = t & 127, w = u >> 4, e = (u & 15) >> 2, s = u & 3;
+  return 4 * (4 * w + s) + e;
+}
+
+// ---------------------------------------------------------------- quantisation pre-pass
+struct QuantParams {
+  const void* x; const float* act_scale_in; const float* act_absmax_in;
+  int8_t* qperm; int32_t* qinit; float* ascale;
+  uint32_t m, m_pad, k, x_dtype, codec;
+};
+
+__global__ void __launch_bounds__(256) prefill_quant_kernel(const QuantParams p) {
+  __shared__ float red[8];
+  const uint32_t t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t slabs = p.k / 128;
+  int8_t* qrow = p.qperm + size_t(t) * p.k;
+  if (t >= p.m) {   // padding tokens: zero codes, neutral start values
+    for (uint32_t i = tid; i < p.k; i += 256) qrow[i] = 0;
+    for (uint32_t s = tid; s < slabs; s += 256) p.qinit[size_t(s) * p.m_pad + t] = int(kMagicBits);
+    if (tid == 0) p.ascale[t] = 0.f;
+    return;
+  }
+  float scale_q = 0.f;
+  if (p.x_dtype != TB_I8) {
+    float gamma;
+    if (p.act_absmax_in) gamma = p.act_absmax_in[t];
+    else {
+      float mx = 0.f;
+      for (uint32_t i = tid; i < p.k; i += 256) {
+        const float v = p.x_dtype == TB_F32 ? static_cast<const float*>(p.x)[size_t(t) * p.k + i]
+                                            : __bfloat162float(static_cast<const __nv_bfloat16*>(p.x)[size_t(t) * p.k + i]);
+        mx = fmaxf(mx, fabsf(v));
+      }
+      for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      if (lane == 0) red[warp] = mx;
+      __syncthreads();
+      gamma = 0.f;
+      for (int w = 0; w < 8; ++w) gamma = fmaxf(gamma, red[w]);
+    }
+    scale_q = gamma > 0.f ? __fdiv_rn(127.0f, gamma) : 0.f;
+    if (tid == 0) p.ascale[t] = __fdiv_rn(gamma, 127.0f);
+  } else if (tid == 0) {
+    p.ascale[t] = p.act_scale_in[t];
+  }
+  // one warp per 128-trit group: quantise, scatter into slot order, sum
+  for (uint32_t grp = warp; grp < slabs; grp += 8) {
+    int sum = 0;
+    for (uint32_t e = 0; e < 4; ++e) {
+      const uint32_t u = lane * 4 + e, i = grp * 128 + u, tt = (grp & 1) * 128 + u;   // tt: trit index in its tile
+      int q;
+      if (p.x_dtype == TB_I8) q = static_cast<const int8_t*>(p.x)[size_t(t) * p.k + i];
+      else {
+        const float v = p.x_dtype == TB_F32 ? static_cast<const float*>(p.x)[size_t(t) * p.k + i]
+                                            : __bfloat162float(static_cast<const __nv_bfloat16*>(p.x)[size_t(t) * p.k + i]);
+        q = int(fminf(127.f, fmaxf(-128.f, rintf(__fmul_rn(v, scale_q)))));
+      }
+      sum += q;
+      if (p.codec == tbf::kB3) qrow[grp * 128 + b3_slot(tt)] = int8_t((tt % 5 == 4) ? -q : q);
+      else qrow[grp * 128 + d2_slot(tt)] = int8_t(q);
+    }
+    for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane == 0) p.qinit[size_t(grp) * p.m_pad + t] = int(kMagicBits) + (p.codec == tbf::kB3 ? sum : -sum);
+  }
+}
+
+// ---------------------------------------------------------------- weight expansion
+// B3 word (four bytes) -> five registers of int8 operands: digit i of bytes 0..3 in byte lanes
+// 0..3; digits 0..3 are stored as -d, digit 4 as +d.
+__device__ __forceinline__ void b3_digits(uint32_t w, uint32_t (&r)[5]) {
+  constexpr uint32_t c1 = 0x35533553u, k1 = 0x61566156u;   // 1024+v -> 1024+floor(v/3), v <= 242
+  constexpr uint32_t c2 = 0x354d354du, k2 = 0x61596159u;   // v <= 80
+  constexpr uint32_t c3 = 0x354b354bu, k3 = 0x615a615au;   // v <= 26
+  constexpr uint32_t m3 = 0xc200c200u;                     // -3.0
+  const uint32_t h01 = prmt(w, 0x64646464u, 0x4140u), h23 = prmt(w, 0x64646464u, 0x4342u);
+  const uint32_t a1 = hfma2(h01, c1, k1), b1 = hfma2(h23, c1, k1);
+  const uint32_t a2 = hfma2(a1, c2, k2), b2 = hfma2(b1, c2, k2);
+  const uint32_t a3 = hfma2(a2, c3, k3), b3 = hfma2(b2, c3, k3);
+  const uint32_t a4 = hfma2(a3, c3, k3), b4 = hfma2(b3, c3, k3);
+  r[0] = prmt(hfma2(a1, m3, h01), hfma2(b1, m3, h23), 0x6420u);   // d0 - 2048 -> low byte -d0
+  r[1] = prmt(hfma2(a2, m3, a1), hfma2(b2, m3, b1), 0x6420u);
+  r[2] = prmt(hfma2(a3, m3, a2), hfma2(b3, m3, b2), 0x6420u);
+  r[3] = prmt(hfma2(a4, m3, a3), hfma2(b4, m3, b3), 0x6420u);
+  r[4] = prmt(a4, b4, 0x6420u);                                   // 1024 + d4 -> low byte +d4
+}
+// (a.byte[ea], b.byte[eb], c.byte[ec], d.byte[ed])
+__device__ __forceinline__ uint32_t pack4(uint32_t a, uint32_t ea, uint32_t b, uint32_t eb, uint32_t c, uint32_t ec, uint32_t d, uint32_t ed) {
+  return prmt(prmt(a, b, ea | ((4u + eb) << 4)), prmt(c, d, ec | ((4u + ed) << 4)), 0x5410u);
+}
+// natural-order trit quad number `nq` of a word whose digit registers are r[0..4]: trits 4nq..4nq+3
+// of the sequence T[5*byte + digit]
+__device__ __forceinline__ uint32_t natural_quad(const uint32_t (&r)[5], int nq) {
+  const int t0 = 4 * nq;
+  return pack4(r[t0 % 5], t0 / 5, r[(t0 + 1) % 5], (t0 + 1) / 5, r[(t0 + 2) % 5], (t0 + 2) / 5, r[(t0 + 3) % 5], (t0 + 3) / 5);
+}
+// store 16 bytes = quads 4*chunk .. 4*chunk+3 of row `row` into a swizzled K-major tile
+__device__ __forceinline__ void store_chunk(uint8_t* tile, uint32_t row, uint32_t chunk, uint32_t q0, uint32_t q1, uint32_t q2, uint32_t q3) {
+  *reinterpret_cast<uint4*>(tile + row * 128u + ((chunk ^ (row & 7u)) << 4)) = make_uint4(q0, q1, q2, q3);
+}
+
+template <int CODEC, int PLANES>
+__global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map_q) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* tile_a = smem;                                       // kStagesA * 16 KB
+  uint8_t* tile_b = tile_a + kStagesA * kTileABytes;            // kStagesB * 2 * 16 KB
+  int32_t* qinit_s = reinterpret_cast<int32_t*>(tile_b + kStagesB * 2 * kTileBBytes);   // kStagesB * 2 * 128 ints
+  __shared__ uint64_t a_full[kStagesA], a_empty[kStagesA], b_full[kStagesB], b_empty[kStagesB], acc_full[2], acc_empty[2];
+  __shared__ uint32_t tmem_base_s, abort_flag;
+
+  const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < kStagesA; ++s) { mbar_init(&a_full[s], 4); mbar_init(&a_empty[s], 1); }
+    for (int s = 0; s < kStagesB; ++s) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 1 + 4); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 4); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(saddr(&tmem_base_s)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+  constexpr uint32_t kSlabsPerCol = 2 * PLANES;
+  const uint32_t tiles = p.n_tiles * p.m_tiles;
+  constexpr uint32_t kPlaneBytes = CODEC == tbf::kB3 ? 52 : 64;
+
+  if (warp == 0) {
+    // ------------------------------------------------ TMA: activations + start values of a tile column
+    if (lane == 0) {
+      uint32_t fill = 0;
+      bool ok = true;
+      for (uint32_t tile = blockIdx.x; ok && tile < tiles; tile += gridDim.x) {
+        const uint32_t mt = tile % p.m_tiles;
+        for (uint32_t j = 0; j < p.tpr; ++j, ++fill) {
+          const uint32_t s = fill % kStagesB, round = fill / kStagesB;
+          if (round > 0 && !mbar_wait(&b_empty[s], (round - 1) & 1, &abort_flag)) { ok = false; break; }
+          mbar_expect_tx(&b_full[s], 2 * kTileBBytes + 2 * kTokens * 4);
+          for (int gsel = 0; gsel < 2; ++gsel) {
+            tma_load_2d(tile_b + (s * 2 + gsel) * kTileBBytes, &map_q, int((2 * j + gsel) * 128), int(mt * kTokens), &b_full[s]);
+            bulk_g2s(qinit_s + (s * 2 + gsel) * kTokens, p.qinit + size_t(2 * j + gsel) * p.m_pad + mt * kTokens, kTokens * 4, &b_full[s]);
+          }
+        }
+      }
+      if (!ok) {
+        abort_flag = 1;
+        if (atomicOr(&p.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) { p.status[TBS_INFO0] = fill; p.status[TBS_INFO1] = 300; }
+      }
+      // copies in flight must land before the CTA's shared memory goes away
+      for (uint32_t back = 0; back < kStagesB && back < fill; ++back) {
+        const uint32_t f = fill - 1 - back;
+        for (uint32_t i = 0; i < kSpin && !mbar_try(&b_full[f % kStagesB], (f / kStagesB) & 1); ++i) {}
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      uint32_t slab = 0, colfill = 0;
+      bool ok = true;
+      for (uint32_t tile = blockIdx.x; ok && tile < tiles; tile += gridDim.x) {
+        for (uint32_t j = 0; ok && j < p.tpr; ++j, ++colfill) {
+          const uint32_t sb = colfill % kStagesB;
+          if (!mbar_wait(&b_full[sb], (colfill / kStagesB) & 1, &abort_flag)) { ok = false; break; }
+          for (uint32_t q = 0; q < kSlabsPerCol; ++q, ++slab) {
+            const uint32_t sa = slab % kStagesA, acc = slab & 1, gsel = q & 1;
+            if (!mbar_wait(&a_full[sa], (slab / kStagesA) & 1, &abort_flag) ||
+                !mbar_wait(&acc_empty[acc], (slab >> 1) & 1, &abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t a_addr = saddr(tile_a + sa * kTileABytes);
+            const uint32_t b_addr = saddr(tile_b + (sb * 2 + gsel) * kTileBBytes);
+#pragma unroll
+            for (uint32_t kc = 0; kc < 4; ++kc)
+              tc_mma_i8(tmem_base + acc * kTokens, smem_desc(a_addr, kc), smem_desc(b_addr, kc), kInstrDesc);
+            tc_commit(&a_empty[sa]);
+            tc_commit(&acc_full[acc]);
+          }
+          if (ok) tc_commit(&b_empty[sb]);
+        }
+      }
+      if (!ok) {
+        abort_flag = 1;
+        if (atomicOr(&p.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) { p.status[TBS_INFO0] = slab; p.status[TBS_INFO1] = 301; }
+      }
+    }
+  } else if (warp >= 8) {
+    // ------------------------------------------------ expanders: one weight row per thread
+    const uint32_t r = (warp - 8) * 32 + lane;
+    uint32_t slab = 0;
+    bool ok = true;
+    for (uint32_t tile = blockIdx.x; ok && tile < tiles; tile += gridDim.x) {
+      const uint32_t nt = tile / p.m_tiles;
+      const uint32_t n = min(nt * kRows + r, p.n - 1);   // rows past the end repeat the last row; never stored
+      const uint32_t* row_words = reinterpret_cast<const uint32_t*>(p.payload + size_t(n) * p.tpr * PLANES * kPlaneBytes);
+      for (uint32_t j = 0; ok && j < p.tpr; ++j) {
+        for (uint32_t pl = 0; pl < PLANES; ++pl, slab += 2) {
+          const uint32_t* wsrc = row_words + (j * PLANES + pl) * (kPlaneBytes / 4);
+          uint32_t w[kPlaneBytes / 4];
+#pragma unroll
+          for (uint32_t i = 0; i < kPlaneBytes / 4; ++i) w[i] = __ldg(wsrc + i);
+          const uint32_t s0 = slab % kStagesA, s1 = (slab + 1) % kStagesA;
+          if (slab >= kStagesA && !mbar_wait(&a_empty[s0], ((slab / kStagesA) - 1) & 1, &abort_flag)) { ok = false; break; }
+          uint8_t* t0 = tile_a + s0 * kTileABytes;
+          if (CODEC == tbf::kB3) {
+            uint32_t d[5], e[5], f[5], g2[5];
+            // group 0: words 0..5 digit-major (quads 0..29), then trits 120..127 in natural order
+            b3_digits(w[0], d); b3_digits(w[1], e); b3_digits(w[2], f); b3_digits(w[3], g2);
+            store_chunk(t0, r, 0, d[0], d[1], d[2], d[3]);
+            store_chunk(t0, r, 1, d[4], e[0], e[1], e[2]);
+            store_chunk(t0, r, 2, e[3], e[4], f[0], f[1]);
+            store_chunk(t0, r, 3, f[2], f[3], f[4], g2[0]);
+            b3_digits(w[4], d); b3_digits(w[5], e); b3_digits(w[6], f);
+            store_chunk(t0, r, 4, g2[1], g2[2], g2[3], g2[4]);
+            store_chunk(t0, r, 5, d[0], d[1], d[2], d[3]);
+            store_chunk(t0, r, 6, d[4], e[0], e[1], e[2]);
+            store_chunk(t0, r, 7, e[3], e[4], natural_quad(f, 0), natural_quad(f, 1));
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&a_full[s0]);
+            if (slab + 1 >= kStagesA && !mbar_wait(&a_empty[s1], (((slab + 1) / kStagesA) - 1) & 1, &abort_flag)) { ok = false; break; }
+            uint8_t* t1 = tile_a + s1 * kTileABytes;
+            // group 1: trits 128..139 in natural order (quads 0..2), words 7..11, trits 240..255
+            b3_digits(w[7], d); b3_digits(w[8], e);
+            store_chunk(t1, r, 0, natural_quad(f, 2), natural_quad(f, 3), natural_quad(f, 4), d[0]);
+            store_chunk(t1, r, 1, d[1], d[2], d[3], d[4]);
+            b3_digits(w[9], f); b3_digits(w[10], g2);
+            store_chunk(t1, r, 2, e[0], e[1], e[2], e[3]);
+            store_chunk(t1, r, 3, e[4], f[0], f[1], f[2]);
+            store_chunk(t1, r, 4, f[3], f[4], g2[0], g2[1]);
+            b3_digits(w[11], d); b3_digits(w[12], e);
+            store_chunk(t1, r, 5, g2[2], g2[3], g2[4], d[0]);
+            store_chunk(t1, r, 6, d[1], d[2], d[3], d[4]);
+            store_chunk(t1, r, 7, natural_quad(e, 0), natural_quad(e, 1), natural_quad(e, 2), natural_quad(e, 3));
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&a_full[s1]);
+          } else {
+            // D2: word i of the tile-plane holds trits 16i..16i+15; quad (4w + s) = slot s of its bytes
+#pragma unroll
+            for (uint32_t c = 0; c < 8; ++c) {
+              const uint32_t v = w[c];
+              store_chunk(t0, r, c, v & 0x03030303u, (v >> 2) & 0x03030303u, (v >> 4) & 0x03030303u, (v >> 6) & 0x03030303u);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&a_full[s0]);
+            if (slab + 1 >= kStagesA && !mbar_wait(&a_empty[s1], (((slab + 1) / kStagesA) - 1) & 1, &abort_flag)) { ok = false; break; }
+            uint8_t* t1 = tile_a + s1 * kTileABytes;
+#pragma unroll
+            for (uint32_t c = 0; c < 8; ++c) {
+              const uint32_t v = w[8 + c];
+              store_chunk(t1, r, c, v & 0x03030303u, (v >> 2) & 0x03030303u, (v >> 4) & 0x03030303u, (v >> 6) & 0x03030303u);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&a_full[s1]);
+          }
+        }
+      }
+    }
+    if (!ok) {
+      abort_flag = 1;
+      if (lane == 0 && atomicOr(&p.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) { p.status[TBS_INFO0] = slab; p.status[TBS_INFO1] = 302; }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------ epilogue: TMEM lane = weight row
+    const uint32_t quad = warp & 3, r = quad * 32 + lane;
+    const uint32_t lane_addr = tmem_base + ((quad * 32u) << 16);
+    const uint32_t y_addr = lane_addr + 2 * kTokens;
+    constexpr float kMagic = 12582912.0f;
+    uint32_t slab = 0, colfill = 0;
+    bool ok = true;
+    // start values of the first two slabs of the first tile column
+    for (uint32_t tile = blockIdx.x; ok && tile < tiles; tile += gridDim.x) {
+      const uint32_t nt = tile / p.m_tiles, mt = tile % p.m_tiles;
+      const uint32_t n = nt * kRows + r;
+      const uint32_t nc = min(n, p.n - 1);
+      const uint16_t* srow = p.scales + size_t(nc) * p.tpr * PLANES * 2;
+      for (uint32_t j = 0; ok && j < p.tpr; ++j, ++colfill) {
+        const uint32_t sb = colfill % kStagesB;
+        // start values come with the tile column's activations
+        if (!mbar_wait(&b_full[sb], (colfill / kStagesB) & 1, &abort_flag)) { ok = false; break; }
+        for (uint32_t q = 0; q < kSlabsPerCol; ++q, ++slab) {
+          const uint32_t acc = slab & 1, gsel = q & 1, pl = q >> 1;
+          const uint32_t d_addr = lane_addr + acc * kTokens;
+          // The accumulator must hold the slab's start values before its MMAs run.  Buffers are
+          // filled two slabs ahead (below); the first two slabs of the whole kernel are filled here.
+          if (slab == 0) {
+            // slabs 0 and 1 are the two groups of the first tile column and plane
+#pragma unroll 1
+            for (uint32_t both = 0; both < 2; ++both) {
+              const int32_t* qi = qinit_s + (sb * 2 + both) * kTokens;
+#pragma unroll 1
+              for (uint32_t c = 0; c < kTokens; c += 16) {
+                uint32_t v[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[i] = uint32_t(qi[c + i]);
+                tmem_st16(lane_addr + both * kTokens + c, v);
+              }
+              tmem_wait_st();
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&acc_empty[both]);
+            }
+          }
+          if (!mbar_wait(&acc_full[acc], (slab >> 1) & 1, &abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const float s = __half2float(__ushort_as_half(srow[(j * PLANES + pl) * 2 + gsel]));
+          const float sgn_scale = CODEC == tbf::kB3 ? -s : s;
+          const bool first = (j == 0 && q == 0), last = (j + 1 == p.tpr && q + 1 == kSlabsPerCol);
+          // where the NEXT user of this accumulator (slab + 2) finds its start values
+          uint32_t nq = q + 2, nj = j, ncol = colfill;
+          if (nq >= kSlabsPerCol) { nq -= kSlabsPerCol; ++nj; ++ncol; }
+          const bool has_next = !(nj >= p.tpr && tile + gridDim.x >= tiles);
+          bool next_ready = true;
+          if (has_next && ncol != colfill) next_ready = mbar_wait(&b_full[ncol % kStagesB], (ncol / kStagesB) & 1, &abort_flag);
+          if (!next_ready) { ok = false; break; }
+          const int32_t* qnext = qinit_s + ((ncol % kStagesB) * 2 + (nq & 1)) * kTokens;
+#pragma unroll 1
+          for (uint32_t c = 0; c < kTokens; c += 16) {
+            uint32_t dv[16], yv[16];
+            tmem_ld16(d_addr + c, dv);
+            if (!first) tmem_ld16(y_addr + c, yv);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float f = __fsub_rn(__uint_as_float(dv[i]), kMagic);   // -I (B3) or +I (D2), exact
+              const float prev = first ? 0.f : __uint_as_float(yv[i]);
+              yv[i] = __float_as_uint(__fmaf_rn(f, sgn_scale, prev));
+            }
+            if (p.acc_dump && n < p.n) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                const uint32_t mtok = mt * kTokens + c + i;
+                if (mtok < p.m) {
+                  const int v = CODEC == tbf::kB3 ? int(kMagicBits) - int(dv[i]) : int(dv[i]) - int(kMagicBits);
+                  p.acc_dump[((size_t(mtok) * p.n + n) * (p.tpr * 2) + 2 * j + gsel) * PLANES + pl] = v;
+                }
+              }
+            }
+            if (!last) tmem_st16(y_addr + c, yv);
+            else if (n < p.n) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                const uint32_t mtok = mt * kTokens + c + i;
+                if (mtok < p.m) {
+                  float out = __fmul_rn(__uint_as_float(yv[i]), p.ascale[mtok]);
+                  if (p.row_scale) out = __fmul_rn(out, p.row_scale[n]);
+                  const size_t idx = size_t(mtok) * p.n + n;
+                  if (p.y_dtype == TB_F32) static_cast<float*>(p.y)[idx] = out;
+                  else static_cast<__nv_bfloat16*>(p.y)[idx] = __float2bfloat16_rn(out);
+                }
+              }
+            }
+            if (has_next) {
+              uint32_t v[16];
+#pragma unroll
+              for (int i = 0; i < 16; ++i) v[i] = uint32_t(qnext[c + i]);
+              tmem_st16(d_addr + c, v);
+            }
+          }
+          tmem_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0 && has_next) mbar_arrive(&acc_empty[acc]);
+          // this column's start values are no longer needed once its last two slabs' successors are filled
+          if (lane == 0 && q + 1 == kSlabsPerCol) mbar_arrive(&b_empty[sb]);
+        }
+      }
+    }
+    if (!ok) {
+      abort_flag = 1;
+      if (lane == 0 && atomicOr(&p.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) { p.status[TBS_INFO0] = slab; p.status[TBS_INFO1] = 303; }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+}
+
+// ---------------------------------------------------------------- host side
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiled encode_tiled_fn() {
+  static EncodeTiled fn = [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult res;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &res) != cudaSuccess ||
+        res != cudaDriverEntryPointSuccess)
+      sym = nullptr;
+    return reinterpret_cast<EncodeTiled>(sym);
+  }();
+  return fn;
+}
+
+uint32_t pad_tokens(uint32_t m) { return (m + kTokens - 1) / kTokens * kTokens; }
+
+struct Scratch { int8_t* qperm; int32_t* qinit; float* ascale; };
+Scratch carve(void* base, uint32_t m_pad, uint32_t k) {
+  uint8_t* b = static_cast<uint8_t*>(base);
+  Scratch s;
+  s.qperm = reinterpret_cast<int8_t*>(b);
+  size_t off = (size_t(m_pad) * k + 255) & ~size_t(255);
+  s.qinit = reinterpret_cast<int32_t*>(b + off);
+  off += (size_t(k / 128) * m_pad * 4 + 255) & ~size_t(255);
+  s.ascale = reinterpret_cast<float*>(b + off);
+  return s;
+}
+
+template <int CODEC>
+cudaError_t launch_planes(uint32_t planes, dim3 grid, size_t smem, cudaStream_t st, const PrefillParams& pp, const CUtensorMap& map) {
+  auto go = [&](auto kernel) -> cudaError_t {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e != cudaSuccess) return e;
+    kernel<<<grid, kThreads, smem, st>>>(pp, map);
+    return cudaGetLastError();
+  };
+  if (planes == 1) return go(prefill_kernel<CODEC, 1>);
+  if (planes == 2) return go(prefill_kernel<CODEC, 2>);
+  return go(prefill_kernel<CODEC, 3>);
+}
+
+}  // namespace
+
+bool tb_prefill_supported(const tb_weights* w, uint32_t m) {
+  return w->fast && m >= 1 && w->k >= 256 && encode_tiled_fn() != nullptr;
+}
+
+size_t tb_prefill_scratch_bytes(const tb_weights* w, uint32_t m) {
+  const uint32_t m_pad = pad_tokens(m);
+  return ((size_t(m_pad) * w->k + 255) & ~size_t(255)) + ((size_t(w->k / 128) * m_pad * 4 + 255) & ~size_t(255)) +
+         size_t(m_pad) * 4 + 256;
+}
+
+cudaError_t tb_launch_prefill(const PrefillArgs& a, int sm_count, cudaStream_t stream) {
+  const tb_weights* w = a.w;
+  const uint32_t m_pad = pad_tokens(a.m), k = uint32_t(w->k);
+  if (!a.scratch || a.scratch_bytes < tb_prefill_scratch_bytes(w, a.m)) return cudaErrorInvalidValue;
+  const Scratch sc = carve(a.scratch, m_pad, k);
+
+  QuantParams qp{};
+  qp.x = a.x; qp.act_scale_in = a.act_scale_in; qp.act_absmax_in = a.act_absmax_in;
+  qp.qperm = sc.qperm; qp.qinit = sc.qinit; qp.ascale = sc.ascale;
+  qp.m = a.m; qp.m_pad = m_pad; qp.k = k; qp.x_dtype = uint32_t(a.x_dtype); qp.codec = uint32_t(w->codec);
+  prefill_quant_kernel<<<m_pad, 256, 0, stream>>>(qp);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return err;
+
+  // activations as a 2-D int8 tensor [m_pad rows][k bytes]; a box is one slab of one token tile
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {k, m_pad};
+  const cuuint64_t strides[1] = {k};
+  const cuuint32_t box[2] = {128, kTokens};
+  const cuuint32_t elem[2] = {1, 1};
+  if (encode_tiled_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, sc.qperm, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return cudaErrorInvalidValue;
+
+  PrefillParams pp{};
+  pp.payload = w->d_payload; pp.scales = w->d_scales;
+  pp.qperm = sc.qperm; pp.qinit = sc.qinit; pp.ascale = sc.ascale;
+  pp.y = a.y; pp.acc_dump = a.acc_dump; pp.row_scale = a.row_scale; pp.status = a.status;
+  pp.m = a.m; pp.m_pad = m_pad; pp.n = uint32_t(w->n); pp.k = k; pp.tpr = k / 256; pp.y_dtype = uint32_t(a.y_dtype);
+  pp.n_tiles = (pp.n + kRows - 1) / kRows; pp.m_tiles = m_pad / kTokens;
+  const size_t smem = 1024 + size_t(kStagesA) * kTileABytes + size_t(kStagesB) * 2 * kTileBBytes + size_t(kStagesB) * 2 * kTokens * 4;
+  const dim3 grid(std::min<uint32_t>(pp.n_tiles * pp.m_tiles, uint32_t(sm_count)));
+  return w->codec == tbf::kB3 ? launch_planes<tbf::kB3>(w->uniform_planes, grid, smem, stream, pp, map)
+                              : launch_planes<tbf::kD2>(w->uniform_planes, grid, smem, stream, pp, map);
+}

@@ -296,10 +296,8 @@ tb_status forward_dev(tb_backend* b, const tb_weights* w, const tb_forward_args&
   if (want_prefill && tb_prefill_supported(w, a.m)) {
     const size_t need = tb_prefill_scratch_bytes(w, a.m);
     if (b->d_q_cap < need) return tb_fail(TB_OUT_OF_MEMORY, "prefill scratch is not reserved; call through a host entry point or tb_stack first");
-    const uint32_t m_pad = (a.m + 255) / 256 * 256;
     PrefillArgs pa{w, a.x, a.x_dtype, a.act_scale, a.act_absmax, a.m, a.y, a.y_dtype, a.acc_dump, a.row_scale,
-                   static_cast<int8_t*>(b->d_q), reinterpret_cast<float*>(static_cast<uint8_t*>(b->d_q) + size_t(m_pad) * w->k),
-                   b->d_status};
+                   b->d_q, b->d_q_cap, b->d_status};
     TB_CUDA(tb_launch_prefill(pa, b->prop.multiProcessorCount, st), "launch prefill");
     fill_receipt(w, a.m, dtype_size(a.x_dtype), dtype_size(a.y_dtype), 2, 2, receipt);
     return TB_OK;
@@ -407,6 +405,18 @@ extern "C" tb_status tb_linear_forward_dev(tb_backend* b, const tb_weights* w, c
   if (tb_status s = use_device(b)) return s;
   cudaStream_t st = args->stream ? static_cast<cudaStream_t>(args->stream) : b->stream;
   return forward_dev(b, w, *args, st, receipt);
+}
+
+extern "C" tb_status tb_act_absmax_dev(tb_backend* b, const void* x, tb_dtype x_dtype, uint32_t m, uint32_t k, float* out, void* stream) {
+  clear_error();
+  if (!b) return tb_fail(TB_NULL_ARG, "null argument");
+  if (m == 0) return TB_OK;
+  if (!x || !out) return tb_fail(TB_NULL_ARG, "null activation or output pointer");
+  if (x_dtype != TB_F32 && x_dtype != TB_BF16) return tb_fail(TB_INVALID_INPUT, "activations must be fp32 or bf16");
+  if (tb_status s = use_device(b)) return s;
+  cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : b->stream;
+  TB_CUDA(tb_launch_row_absmax(x, x_dtype, m, k, out, st), "launch row absmax");
+  return TB_OK;
 }
 
 extern "C" tb_status tb_backend_reserve(tb_backend* b, const tb_weights* w, uint32_t max_m) {

@@ -83,6 +83,7 @@ struct ExactArgs {
 cudaError_t tb_launch_exact(const ExactArgs& a, cudaStream_t stream);
 cudaError_t tb_launch_gather_rows(const tb_weights* w, const uint32_t* rows, uint32_t count, float* out,
                                   cudaStream_t stream);
+cudaError_t tb_launch_row_absmax(const void* x, tb_dtype dtype, uint32_t m, uint32_t k, float* out, cudaStream_t stream);
 cudaError_t tb_launch_check_finite(const float* x, uint64_t count, uint32_t* status, cudaStream_t stream);
 
 // Device-resident descriptor of one layer of a grouped launch.
@@ -117,7 +118,7 @@ struct PrefillArgs {
   void* y; tb_dtype y_dtype;
   int32_t* acc_dump;
   const float* row_scale;
-  int8_t* q_scratch; float* token_scale_scratch;   // [m_pad, k] permuted int8, [m_pad]
+  void* scratch; size_t scratch_bytes;   // permuted int8 activations, slab start values, token scales
   uint32_t* status;
 };
 bool tb_prefill_supported(const tb_weights* w, uint32_t m);

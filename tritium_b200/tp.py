@@ -1,0 +1,212 @@
+"""Tensor-parallel ternary linears over the GPUs of one node (one process per GPU).
+
+The reference has no tensor-parallel inference path; its only collective is the training
+gradient all-reduce (crates/tritium-cuda/src/nccl.rs:530-625).  The sharding rules here follow
+the artifact layout (crates/tritium-format/src/salt_v2_package.rs:607-631: tiles cut the flattened
+row-major index, so rows may straddle tiles) and the per-token quantiser
+(crates/tritium-spec/src/lib.rs:351-378):
+
+* column-parallel (QKV, gate/up): output rows are split.  A rank's shard is a byte slice of the
+  arenas; no communication; outputs stay sharded.
+* row-parallel (O, down): K is split.  A rank's shard is a re-encoded [N, K/world] tensor whose K
+  is padded to whole tiles with zero trits.  The int8 quantiser must see the absmax of the whole
+  row, so the ranks take one small MAX all-reduce over their local absmax, run the contraction
+  on their slice, and SUM all-reduce the fp32 partial outputs.
+
+`ShardExecutor` is the seam between the collective logic and the device.  `CudaExecutor` is the
+only executor this package ships (B200 kernels through the C ABI, NCCL on CUDA tensors); tests
+of the collective logic run the same classes over `gloo` with an executor of their own.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import format as fmt
+from .format import SaltV2Codec, SaltV2Tensor
+
+
+@dataclass(frozen=True)
+class ShardGeometry:
+    """Shape of one rank's shard of an [n, k] linear."""
+    mode: str          # "column" | "row"
+    n: int             # output rows held by this rank
+    k: int             # K of the shard tensor (row-parallel: padded to whole tiles)
+    k_valid: int       # activations of the unsharded row that this rank consumes
+    k_offset: int      # first activation column of the unsharded row
+    n_offset: int      # first output row of the unsharded tensor
+
+    @staticmethod
+    def of(mode: str, n: int, k: int, world: int, rank: int) -> "ShardGeometry":
+        if mode == "column":
+            if n % world:
+                raise ValueError(f"column-parallel: {n} rows do not split over {world} ranks")
+            return ShardGeometry(mode, n // world, k, k, 0, rank * (n // world))
+        if mode == "row":
+            if k % (128 * world):
+                raise ValueError(f"row-parallel: K={k} over {world} ranks breaks the 128-wide scale groups")
+            kv = k // world
+            return ShardGeometry(mode, n, (kv + 255) // 256 * 256, kv, rank * kv, 0)
+        raise ValueError(f"unknown mode {mode!r}")
+
+
+class ShardExecutor:
+    """What a TP linear needs from the device.  Tensors are torch tensors on the executor's device."""
+
+    def upload(self, codec, group, n, k, payload, scales, plane_map, terminal):
+        raise NotImplementedError
+
+    def alloc(self, shape, dtype):
+        raise NotImplementedError
+
+    def row_absmax(self, x, out) -> None:
+        raise NotImplementedError
+
+    def linear(self, handle, x, y, act_absmax) -> None:
+        raise NotImplementedError
+
+
+class CudaExecutor(ShardExecutor):
+    """B200 kernels through the C ABI; every call is asynchronous on the current torch stream."""
+
+    def __init__(self, backend, flags: int = 0):
+        self.backend = backend
+        self.flags = flags
+
+    def upload(self, codec, group, n, k, payload, scales, plane_map, terminal):
+        return self.backend.upload_salt_v2_arenas(codec, group, n, k, payload, scales, plane_map, terminal)
+
+    def alloc(self, shape, dtype):
+        import torch
+        return torch.zeros(shape, dtype=dtype, device=f"cuda:{self.backend.ordinal}")
+
+    def reserve(self, handle, max_m: int) -> None:
+        self.backend.reserve(handle, max_m)
+
+    def row_absmax(self, x, out) -> None:
+        self.backend.act_absmax_dev(x, out)
+
+    def linear(self, handle, x, y, act_absmax) -> None:
+        self.backend.forward_dev(handle, x, y, a8=True, act_absmax=act_absmax, flags=self.flags)
+
+
+class TPLinear:
+    """One rank's share of a tensor-parallel ternary linear."""
+
+    def __init__(self, executor: ShardExecutor, tensor: SaltV2Tensor, codec: SaltV2Codec, mode: str, rank: int, world: int,
+                 group=None, max_m: int = 1, act_dtype=None):
+        import torch
+        self.executor, self.rank, self.world, self.group, self.max_m = executor, rank, world, group, max_m
+        n, k = tensor.rows, tensor.cols
+        planes = int(tensor.plane_count[0])
+        if np.any(tensor.plane_count != planes):
+            raise ValueError("tensor-parallel sharding needs the same plane count in every tile")
+        self.geometry = ShardGeometry.of(mode, n, k, world, rank)
+        payload, scales, _, _, _ = tensor.resident(codec)
+        sn, sk, sp, ss, sm, term = fmt.tp_shard(codec, tensor.scale_group_size, n, k, planes, payload, scales,
+                                                mode == "row", world, rank)
+        assert (sn, sk) == (self.geometry.n, self.geometry.k)
+        self.handle = executor.upload(codec, tensor.scale_group_size, sn, sk, sp, ss, sm, term)
+        if hasattr(executor, "reserve"):
+            executor.reserve(self.handle, max_m)
+        act_dtype = act_dtype or torch.bfloat16
+        # activations live in a buffer as wide as the shard tensor's (padded) K: the padding
+        # columns stay zero and meet zero trits
+        self.x = executor.alloc((max_m, self.geometry.k), act_dtype)
+        self.y = executor.alloc((max_m, self.geometry.n), torch.float32)
+        self.absmax = executor.alloc((max_m,), torch.float32) if mode == "row" else None
+
+    @property
+    def mode(self) -> str:
+        return self.geometry.mode
+
+    def input_view(self, m: int):
+        """[m, k_valid] view of the activation buffer: write this rank's slice of the row here."""
+        return self.x[:m, : self.geometry.k_valid]
+
+    def forward(self, m: int):
+        """Runs on the first ``m`` rows of the activation buffer.  Returns the fp32 output:
+        column-parallel [m, n / world] (this rank's rows), row-parallel [m, n] (reduced)."""
+        import torch.distributed as dist
+        x, y = self.x[:m], self.y[:m]
+        if self.mode == "column":
+            self.executor.linear(self.handle, x, y, None)
+            return y
+        absmax = self.absmax[:m]
+        self.executor.row_absmax(x, absmax)
+        if self.world > 1:
+            dist.all_reduce(absmax, op=dist.ReduceOp.MAX, group=self.group)
+        self.executor.linear(self.handle, x, y, absmax)
+        if self.world > 1:
+            dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
+        return y
+
+
+@dataclass(frozen=True)
+class DecoderShape:
+    """Linear shapes of one decoder layer: QKV, O, gate+up (fused), down."""
+    hidden: int
+    q_heads: int
+    kv_heads: int
+    head_dim: int
+    ffn: int
+    planes: int
+    layers: int
+
+    def linears(self):
+        qkv = (self.q_heads + 2 * self.kv_heads) * self.head_dim
+        return [("qkv", "column", qkv, self.hidden), ("o", "row", self.hidden, self.q_heads * self.head_dim),
+                ("gate_up", "column", 2 * self.ffn, self.hidden), ("down", "row", self.hidden, self.ffn)]
+
+
+DECODER_2B = DecoderShape(hidden=2560, q_heads=20, kv_heads=5, head_dim=128, ffn=6912, planes=1, layers=30)
+DECODER_27B = DecoderShape(hidden=5120, q_heads=40, kv_heads=8, head_dim=128, ffn=17408, planes=2, layers=64)
+
+
+class TPDecoderStack:
+    """The linears of a decoder, layer by layer, each fed its own fixed input (no attention,
+    norm or activation function between them): QKV and gate/up column-parallel, O and down
+    row-parallel with the all-reduce behind them."""
+
+    def __init__(self, executor: ShardExecutor, shape: DecoderShape, codec: SaltV2Codec, rank: int, world: int, group=None,
+                 max_m: int = 1, make_tensor=None, distinct_layers: int | None = None, act_dtype=None):
+        from .synth import make_tensor as synth_tensor
+        make_tensor = make_tensor or synth_tensor
+        self.shape, self.rank, self.world = shape, rank, world
+        built = distinct_layers or shape.layers
+        self.layers = []
+        for layer in range(built):
+            row = []
+            for idx, (name, mode, n, k) in enumerate(shape.linears()):
+                t = make_tensor(f"l{layer}.{name}", n, k, shape.planes, seed=layer * 4 + idx)
+                row.append(TPLinear(executor, t, codec, mode, rank, world, group, max_m, act_dtype))
+            self.layers.append(row)
+
+    def fill_inputs(self, m: int, seed: int = 0) -> None:
+        """Seeded activations, identical on every rank before slicing (a rank keeps its K slice)."""
+        import torch
+        from .synth import make_activations
+        for li, row in enumerate(self.layers):
+            for idx, lin in enumerate(row):
+                g = lin.geometry
+                k_full = g.k_valid * (self.world if lin.mode == "row" else 1)
+                full = make_activations(m, k_full, seed=seed + li * 4 + idx, bf16=True)
+                part = full[:, g.k_offset:g.k_offset + g.k_valid]
+                lin.input_view(m).copy_(torch.from_numpy(np.ascontiguousarray(part)).to(lin.x.dtype))
+
+    def forward(self, m: int) -> list:
+        """One pass over every layer; returns the outputs of the last layer's four linears."""
+        out = []
+        for row in self.layers:
+            out = [lin.forward(m) for lin in row]
+        return out
+
+    def weight_bytes(self) -> int:
+        """Resident arena bytes this rank streams per pass."""
+        total = 0
+        for row in self.layers:
+            for lin in row:
+                r = lin.handle.allocation_receipt()
+                total += int(r["steady_resident_bytes"])
+        return total
