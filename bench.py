@@ -157,6 +157,41 @@ def time_graph(torch, stream, launch, steps: int, warmup: int, sampler=None):
     return graph
 
 
+def measure_prefill(torch, backend, weights, m: int, codec_name: str, steps: int, warmup: int, stream) -> dict:
+    """INT8 tensor-core leg: Y[m, N] for m tokens through the tcgen05 kernel (quantisation pre-pass
+    included), one weight copy per iteration out of the rotating set, CUDA events on `stream`."""
+    from tritium_b200.synth import f32_to_bf16_bits, make_activations
+    x = make_activations(m, K_COLS, seed=1, bf16=True)
+    x_dev = torch.from_numpy(f32_to_bf16_bits(x).view(np.int16).copy()).cuda().view(torch.bfloat16).reshape(m, K_COLS)
+    y_dev = torch.zeros((m, N_ROWS), dtype=torch.bfloat16, device="cuda")
+    backend.reserve(weights[0], m)
+    with torch.cuda.stream(stream):
+        for i in range(max(warmup, 3)):
+            backend.forward_dev(weights[i % len(weights)], x_dev, y_dev, stream=stream)
+        stream.synchronize()
+        backend.check(stream)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(stream)
+        for i in range(steps):
+            backend.forward_dev(weights[i % len(weights)], x_dev, y_dev, stream=stream)
+        stop.record(stream)
+        stream.synchronize()
+        backend.check(stream)
+    ms = start.elapsed_time(stop) / steps
+    ops = 2.0 * m * N_ROWS * K_COLS * PLANES
+    tops = ops / (ms * 1e-3) / 1e12
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peak, kind = 2.0 * float(json.load(f)["bf16_tflops"]), "2 x measured cuBLAS bf16 burst (INT8 issues at twice the bf16 rate)"
+    except Exception:
+        peak, kind = 2.0 * 1590.0, "2 x fallback bf16 figure"
+    return {"metric": f"INT8 TOPS (M={m})", "value": tops, "unit": "TOPS", "ms_per_call": ms, "launches_per_call": 2,
+            "ops_per_call": ops, "workload": f"c2_3plane_k2560_n6912_{codec_name}_m{m}", "out_dtype": "bf16",
+            "l2_policy": f"weights rotate over {len(weights)} copies; activations stay L2-resident as they would after the previous layer",
+            "roofline": {"bound": "tensor", "achieved": tops, "peak": peak, "unit": "TOPS", "frac": tops / peak,
+                         "peak_kind": kind, "frac_of_nominal_4500": tops / 4500.0, "kernel": "prefill_kernel"}}
+
+
 def run_b200(args) -> None:
     import torch
     import torch.distributed as dist
@@ -182,6 +217,10 @@ def run_b200(args) -> None:
     stack = LinearStack(backend, weights, [0] * copies, max_m=max(m, 1))
 
     stream = torch.cuda.Stream()
+    if args.only_prefill:
+        # profiling aid: the tensor-core leg alone (no decode leg, no CPU leg)
+        print(json.dumps(measure_prefill(torch, backend, weights[:2], args.prefill_m, codec_name, args.steps, args.warmup, stream)), flush=True)
+        return
     x_dev = torch.from_numpy(x_bits.view(np.int16).copy()).cuda().view(torch.bfloat16).reshape(m, K_COLS)
     flags = _lib.TB_FWD_PDL if not args.no_pdl else 0
 
@@ -248,6 +287,19 @@ def run_b200(args) -> None:
         dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
     e2e_value = world * bytes_per_step / float(e2e_t.item()) / 1e9
 
+    prefill = None
+    if args.prefill_m > 0:
+        prefill = measure_prefill(torch, backend, weights, args.prefill_m, codec_name, max(5, min(args.steps, 20)), args.warmup, stream)
+        pt = torch.tensor([prefill["ms_per_call"]], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(pt, op=dist.ReduceOp.MAX)
+            scale = prefill["ms_per_call"] / float(pt.item())
+            prefill["ms_per_call"] = float(pt.item())
+            prefill["value"] *= scale * world
+            prefill["roofline"]["achieved"] *= scale
+            prefill["roofline"]["frac"] *= scale
+            prefill["roofline"]["frac_of_nominal_4500"] *= scale
+
     if rank == 0:
         cpu = None
         if world == 1 and not args.skip_cpu:
@@ -271,6 +323,7 @@ def run_b200(args) -> None:
                     "d2h_bytes_per_step": copies * m * N_ROWS * 2},
             "gpu_launches": args.steps * 2,
             "clocks": clocks.summary(),
+            "prefill": prefill,
         }
         print(json.dumps(line), flush=True)
     stack.close()
@@ -293,6 +346,8 @@ def main() -> None:
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")
+    ap.add_argument("--prefill-m", type=int, default=2048, help="tokens of the tensor-core leg (0 = skip)")
+    ap.add_argument("--only-prefill", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -34,13 +34,15 @@
 namespace {
 
 constexpr int kRows = 128;        // weight rows per tile (UMMA M)
-constexpr int kTokens = 128;      // tokens per tile (UMMA N)
 constexpr int kStagesA = 4;       // expanded slabs in flight
 constexpr int kStagesB = 2;       // tile columns of activations in flight (two slabs each)
-constexpr int kThreads = 384;     // warps: 0 TMA, 1 MMA, 2 TMEM owner, 3 idle, 4-7 epilogue, 8-11 expanders
+constexpr int kEpilogueWarps = 8, kExpandWarps = 4;
+constexpr int kFirstEpilogueWarp = 4, kFirstExpandWarp = kFirstEpilogueWarp + kEpilogueWarps;
+constexpr int kThreads = 32 * (kFirstExpandWarp + kExpandWarps);   // warps: 0 TMA, 1 MMA + TMEM owner, 2-3 idle, 4-11 epilogue, 12-15 expanders
 constexpr uint32_t kSpin = 1u << 22;
+constexpr long long kWaitCycles = 2000000000ll;
 constexpr uint32_t kMagicBits = 0x4B400000u;   // float 12582912 = 2^23 + 2^22
-constexpr uint32_t kTileABytes = kRows * 128, kTileBBytes = kTokens * 128;
+constexpr uint32_t kTileABytes = kRows * 128;
 
 struct PrefillParams {
   const uint8_t* payload; const uint16_t* scales;
@@ -64,13 +66,20 @@ __device__ __forceinline__ bool mbar_try(uint64_t* b, uint32_t parity) {
                : "=r"(ok) : "r"(saddr(b)), "r"(parity) : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, volatile uint32_t* abort_flag) {
-  for (uint32_t i = 0; i < kSpin; ++i) {
+// Bounded wait: gives up after kWaitCycles SM clocks (about a second) or when another role has
+// raised the abort flag.  `backoff_ns` > 0 sleeps between polls: roles that run ahead of the
+// pipeline (copy producer, expanders) must not take issue slots from the warps that bound it.
+__device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, volatile uint32_t* abort_flag, uint32_t backoff_ns = 0) {
+  if (mbar_try(b, parity)) return true;
+  const long long t0 = clock64();
+  for (uint32_t i = 0;; ++i) {
+    if (backoff_ns) __nanosleep(backoff_ns);
     if (mbar_try(b, parity)) return true;
-    if (i >= 8) __nanosleep(64);
-    if ((i & 127u) == 127u && *abort_flag) return false;
+    if ((i & 63u) == 63u) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitCycles) return false;
+    }
   }
-  return false;
 }
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
   uint32_t r; asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel)); return r;
@@ -86,6 +95,11 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(saddr(dst)), "l"(src), "r"(bytes), "r"(saddr(bar)) : "memory");
 }
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n .reg .pred p;\n elect.sync _|p, 0xffffffff;\n selp.u32 %0, 1, 0, p;\n}\n" : "=r"(pred));
+  return pred != 0;
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
@@ -99,18 +113,29 @@ __device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t adesc, uint6
       " tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n"
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(1u), "r"(0u) : "memory");
 }
-#define TB_R32(a, o) "=r"(a[o+0]), "=r"(a[o+1]), "=r"(a[o+2]), "=r"(a[o+3]), "=r"(a[o+4]), "=r"(a[o+5]), "=r"(a[o+6]), "=r"(a[o+7]), \
+#define TB_R16(a, o) "=r"(a[o+0]), "=r"(a[o+1]), "=r"(a[o+2]), "=r"(a[o+3]), "=r"(a[o+4]), "=r"(a[o+5]), "=r"(a[o+6]), "=r"(a[o+7]), \
                      "=r"(a[o+8]), "=r"(a[o+9]), "=r"(a[o+10]), "=r"(a[o+11]), "=r"(a[o+12]), "=r"(a[o+13]), "=r"(a[o+14]), "=r"(a[o+15])
-#define TB_S32(a, o) "r"(a[o+0]), "r"(a[o+1]), "r"(a[o+2]), "r"(a[o+3]), "r"(a[o+4]), "r"(a[o+5]), "r"(a[o+6]), "r"(a[o+7]), \
+#define TB_S16(a, o) "r"(a[o+0]), "r"(a[o+1]), "r"(a[o+2]), "r"(a[o+3]), "r"(a[o+4]), "r"(a[o+5]), "r"(a[o+6]), "r"(a[o+7]), \
                      "r"(a[o+8]), "r"(a[o+9]), "r"(a[o+10]), "r"(a[o+11]), "r"(a[o+12]), "r"(a[o+13]), "r"(a[o+14]), "r"(a[o+15])
 // 32 lanes x 16 columns of 32 bits: this thread's lane, 16 consecutive columns
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-               : TB_R32(r, 0) : "r"(taddr) : "memory");
+               : TB_R16(r, 0) : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
-               ::"r"(taddr), TB_S32(r, 0) : "memory");
+               ::"r"(taddr), TB_S16(r, 0) : "memory");
+}
+// 32 lanes x 32 columns of 32 bits: this thread's lane, 32 consecutive columns
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+               "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+               : TB_R16(r, 0), TB_R16(r, 16) : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+               "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+               ::"r"(taddr), TB_S16(r, 0), TB_S16(r, 16) : "memory");
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
@@ -127,9 +152,11 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t k_chunk) {
   return d;
 }
 // Instruction descriptor: s32 accumulate, A/B formats, K-major both, N, M.
-constexpr uint32_t kInstrDesc = (2u << 4)                       // s32 accumulator
-                                | (1u << 7) | (1u << 10)        // A and B are signed 8-bit
-                                | ((uint32_t(kTokens) >> 3) << 17) | ((uint32_t(kRows) >> 4) << 24);
+__host__ __device__ constexpr uint32_t instr_desc_n(uint32_t n) {
+  return (2u << 4)                    // s32 accumulator
+         | (1u << 7) | (1u << 10)     // A and B are signed 8-bit
+         | ((n >> 3) << 17) | ((uint32_t(kRows) >> 4) << 24);
+}
 
 // ---------------------------------------------------------------- k-slot order of a slab
 // slot (0..127) of trit t (0..255 of the tile) inside its group's slab: packed words are expanded
@@ -201,32 +228,33 @@ __global__ void __launch_bounds__(256) prefill_quant_kernel(const QuantParams p)
         q = int(fminf(127.f, fmaxf(-128.f, rintf(__fmul_rn(v, scale_q)))));
       }
       sum += q;
-      if (p.codec == tbf::kB3) qrow[grp * 128 + b3_slot(tt)] = int8_t((tt % 5 == 4) ? -q : q);
-      else qrow[grp * 128 + d2_slot(tt)] = int8_t(q);
+      qrow[grp * 128 + (p.codec == tbf::kB3 ? b3_slot(tt) : d2_slot(tt))] = int8_t(q);
     }
     for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    if (lane == 0) p.qinit[size_t(grp) * p.m_pad + t] = int(kMagicBits) + (p.codec == tbf::kB3 ? sum : -sum);
+    if (lane == 0) p.qinit[size_t(grp) * p.m_pad + t] = int(kMagicBits) - sum;
   }
 }
 
 // ---------------------------------------------------------------- weight expansion
-// B3 word (four bytes) -> five registers of int8 operands: digit i of bytes 0..3 in byte lanes
-// 0..3; digits 0..3 are stored as -d, digit 4 as +d.
+// B3 word (four bytes) -> five registers of operand bytes: digit i (0..2, i.e. trit + 1) of bytes
+// 0..3 in byte lanes 0..3.  The quotients q_i = floor(b / 3^i) come from a half-precision FMA
+// chain on 1024 + b (exact: every intermediate is an integer below 2048); packed as bytes,
+// d_i = q_i - 3 q_(i+1) is one 32-bit multiply-add for all four lanes (no lane ever borrows).
 __device__ __forceinline__ void b3_digits(uint32_t w, uint32_t (&r)[5]) {
   constexpr uint32_t c1 = 0x35533553u, k1 = 0x61566156u;   // 1024+v -> 1024+floor(v/3), v <= 242
   constexpr uint32_t c2 = 0x354d354du, k2 = 0x61596159u;   // v <= 80
   constexpr uint32_t c3 = 0x354b354bu, k3 = 0x615a615au;   // v <= 26
-  constexpr uint32_t m3 = 0xc200c200u;                     // -3.0
   const uint32_t h01 = prmt(w, 0x64646464u, 0x4140u), h23 = prmt(w, 0x64646464u, 0x4342u);
   const uint32_t a1 = hfma2(h01, c1, k1), b1 = hfma2(h23, c1, k1);
   const uint32_t a2 = hfma2(a1, c2, k2), b2 = hfma2(b1, c2, k2);
   const uint32_t a3 = hfma2(a2, c3, k3), b3 = hfma2(b2, c3, k3);
   const uint32_t a4 = hfma2(a3, c3, k3), b4 = hfma2(b3, c3, k3);
-  r[0] = prmt(hfma2(a1, m3, h01), hfma2(b1, m3, h23), 0x6420u);   // d0 - 2048 -> low byte -d0
-  r[1] = prmt(hfma2(a2, m3, a1), hfma2(b2, m3, b1), 0x6420u);
-  r[2] = prmt(hfma2(a3, m3, a2), hfma2(b3, m3, b2), 0x6420u);
-  r[3] = prmt(hfma2(a4, m3, a3), hfma2(b4, m3, b3), 0x6420u);
-  r[4] = prmt(a4, b4, 0x6420u);                                   // 1024 + d4 -> low byte +d4
+  const uint32_t q1 = prmt(a1, b1, 0x6420u), q2 = prmt(a2, b2, 0x6420u), q3 = prmt(a3, b3, 0x6420u), q4 = prmt(a4, b4, 0x6420u);
+  r[0] = w - 3u * q1;
+  r[1] = q1 - 3u * q2;
+  r[2] = q2 - 3u * q3;
+  r[3] = q3 - 3u * q4;
+  r[4] = q4;
 }
 // (a.byte[ea], b.byte[eb], c.byte[ec], d.byte[ed])
 __device__ __forceinline__ uint32_t pack4(uint32_t a, uint32_t ea, uint32_t b, uint32_t eb, uint32_t c, uint32_t ec, uint32_t d, uint32_t ed) {
@@ -243,35 +271,50 @@ __device__ __forceinline__ void store_chunk(uint8_t* tile, uint32_t row, uint32_
   *reinterpret_cast<uint4*>(tile + row * 128u + ((chunk ^ (row & 7u)) << 4)) = make_uint4(q0, q1, q2, q3);
 }
 
-template <int CODEC, int PLANES>
+// y{0,1} += (as_float(d{0,1}) - 12582912) * s, two lanes per instruction
+__device__ __forceinline__ void scale_add2(uint32_t d0, uint32_t d1, float2 neg_magic, float2 scale, uint32_t& y0, uint32_t& y1) {
+  const float2 d = __fadd2_rn(make_float2(__uint_as_float(d0), __uint_as_float(d1)), neg_magic);
+  const float2 y = __ffma2_rn(d, scale, make_float2(__uint_as_float(y0), __uint_as_float(y1)));
+  y0 = __float_as_uint(y.x); y1 = __float_as_uint(y.y);
+}
+__device__ __forceinline__ void lds128(uint32_t addr, uint32_t* v) {
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "r"(addr));
+}
+
+// HW = tokens per accumulator half (64 or 128); a CTA tile is 128 weight rows x 2*HW tokens.
+template <int CODEC, int PLANES, int HW, bool DUMP>
 __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map_q) {
+  constexpr uint32_t kTileTokens = 2 * HW;
+  constexpr uint32_t kTileBBytes = kTileTokens * 128;          // one slab of activations
+  constexpr uint32_t kCW = HW;                                 // columns per epilogue thread: one whole half
+  constexpr uint32_t kSlabsPerCol = 2 * PLANES;
+  constexpr uint32_t kPlaneBytes = CODEC == tbf::kB3 ? 52 : 64;
+  constexpr uint32_t kIdesc = instr_desc_n(HW);
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* tile_a = smem;                                       // kStagesA * 16 KB
-  uint8_t* tile_b = tile_a + kStagesA * kTileABytes;            // kStagesB * 2 * 16 KB
-  int32_t* qinit_s = reinterpret_cast<int32_t*>(tile_b + kStagesB * 2 * kTileBBytes);   // kStagesB * 2 * 128 ints
+  uint8_t* tile_b = tile_a + kStagesA * kTileABytes;            // kStagesB * 2 slabs
+  int32_t* qinit_s = reinterpret_cast<int32_t*>(tile_b + kStagesB * 2 * kTileBBytes);   // kStagesB * 2 * kTileTokens
   __shared__ uint64_t a_full[kStagesA], a_empty[kStagesA], b_full[kStagesB], b_empty[kStagesB], acc_full[2], acc_empty[2];
   __shared__ uint32_t tmem_base_s, abort_flag;
 
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
     abort_flag = 0;
-    for (int s = 0; s < kStagesA; ++s) { mbar_init(&a_full[s], 4); mbar_init(&a_empty[s], 1); }
-    for (int s = 0; s < kStagesB; ++s) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 1 + 4); }
-    for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 4); }
+    for (int s = 0; s < kStagesA; ++s) { mbar_init(&a_full[s], kExpandWarps); mbar_init(&a_empty[s], 1); }
+    for (int s = 0; s < kStagesB; ++s) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 1 + kEpilogueWarps); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], kEpilogueWarps / 2); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 2) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(saddr(&tmem_base_s)) : "memory");
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(saddr(&tmem_base_s)), "r"(4u * HW) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_s;
-  constexpr uint32_t kSlabsPerCol = 2 * PLANES;
   const uint32_t tiles = p.n_tiles * p.m_tiles;
-  constexpr uint32_t kPlaneBytes = CODEC == tbf::kB3 ? 52 : 64;
 
   if (warp == 0) {
     // ------------------------------------------------ TMA: activations + start values of a tile column
@@ -282,11 +325,12 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
         const uint32_t mt = tile % p.m_tiles;
         for (uint32_t j = 0; j < p.tpr; ++j, ++fill) {
           const uint32_t s = fill % kStagesB, round = fill / kStagesB;
-          if (round > 0 && !mbar_wait(&b_empty[s], (round - 1) & 1, &abort_flag)) { ok = false; break; }
-          mbar_expect_tx(&b_full[s], 2 * kTileBBytes + 2 * kTokens * 4);
+          if (round > 0 && !mbar_wait(&b_empty[s], (round - 1) & 1, &abort_flag, 400)) { ok = false; break; }
+          mbar_expect_tx(&b_full[s], 2 * kTileBBytes + 2 * kTileTokens * 4);
           for (int gsel = 0; gsel < 2; ++gsel) {
-            tma_load_2d(tile_b + (s * 2 + gsel) * kTileBBytes, &map_q, int((2 * j + gsel) * 128), int(mt * kTokens), &b_full[s]);
-            bulk_g2s(qinit_s + (s * 2 + gsel) * kTokens, p.qinit + size_t(2 * j + gsel) * p.m_pad + mt * kTokens, kTokens * 4, &b_full[s]);
+            tma_load_2d(tile_b + (s * 2 + gsel) * kTileBBytes, &map_q, int((2 * j + gsel) * 128), int(mt * kTileTokens), &b_full[s]);
+            bulk_g2s(qinit_s + (s * 2 + gsel) * kTileTokens, p.qinit + size_t(2 * j + gsel) * p.m_pad + mt * kTileTokens,
+                     kTileTokens * 4, &b_full[s]);
           }
         }
       }
@@ -301,38 +345,48 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      uint32_t slab = 0, colfill = 0;
-      bool ok = true;
-      for (uint32_t tile = blockIdx.x; ok && tile < tiles; tile += gridDim.x) {
-        for (uint32_t j = 0; ok && j < p.tpr; ++j, ++colfill) {
-          const uint32_t sb = colfill % kStagesB;
-          if (!mbar_wait(&b_full[sb], (colfill / kStagesB) & 1, &abort_flag)) { ok = false; break; }
-          for (uint32_t q = 0; q < kSlabsPerCol; ++q, ++slab) {
-            const uint32_t sa = slab % kStagesA, acc = slab & 1, gsel = q & 1;
-            if (!mbar_wait(&a_full[sa], (slab / kStagesA) & 1, &abort_flag) ||
-                !mbar_wait(&acc_empty[acc], (slab >> 1) & 1, &abort_flag)) { ok = false; break; }
-            tc_fence_after();
-            const uint32_t a_addr = saddr(tile_a + sa * kTileABytes);
-            const uint32_t b_addr = saddr(tile_b + (sb * 2 + gsel) * kTileBBytes);
+    // ------------------------------------------------ MMA issuer: the whole warp walks the loop (so
+    // that addresses and descriptors stay in uniform registers); one elected lane issues
+    uint32_t slab = 0, colfill = 0;
+    bool ok = true;
+    const uint64_t a_desc0 = smem_desc(saddr(tile_a), 0), b_desc0 = smem_desc(saddr(tile_b), 0);
+    for (uint32_t tile = blockIdx.x; ok && tile < tiles; tile += gridDim.x) {
+      for (uint32_t j = 0; ok && j < p.tpr; ++j, ++colfill) {
+        const uint32_t sb = colfill % kStagesB;
+        if (!mbar_wait(&b_full[sb], (colfill / kStagesB) & 1, &abort_flag)) { ok = false; break; }
+        for (uint32_t q = 0; q < kSlabsPerCol; ++q, ++slab) {
+          const uint32_t sa = slab % kStagesA, gsel = q & 1;
+          if (!mbar_wait(&a_full[sa], (slab / kStagesA) & 1, &abort_flag)) { ok = false; break; }
+          // descriptor start addresses are in 16-byte units
+          const uint64_t a_desc = a_desc0 + uint64_t(sa * (kTileABytes >> 4));
+          const uint64_t b_desc = b_desc0 + uint64_t((sb * 2 + gsel) * (kTileBBytes >> 4));
 #pragma unroll
-            for (uint32_t kc = 0; kc < 4; ++kc)
-              tc_mma_i8(tmem_base + acc * kTokens, smem_desc(a_addr, kc), smem_desc(b_addr, kc), kInstrDesc);
-            tc_commit(&a_empty[sa]);
-            tc_commit(&acc_full[acc]);
+          for (uint32_t h = 0; h < 2; ++h) {
+            if (!mbar_wait(&acc_empty[h], slab & 1, &abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            if (elect_one()) {
+#pragma unroll
+              for (uint32_t kc = 0; kc < 4; ++kc)
+                tc_mma_i8(tmem_base + h * HW, a_desc + 2 * kc, b_desc + uint64_t(h * (HW * 128u >> 4)) + 2 * kc, kIdesc);
+              tc_commit(&acc_full[h]);
+            }
+            __syncwarp();
           }
-          if (ok) tc_commit(&b_empty[sb]);
+          if (!ok) break;
+          if (elect_one()) tc_commit(&a_empty[sa]);
+          __syncwarp();
         }
-      }
-      if (!ok) {
-        abort_flag = 1;
-        if (atomicOr(&p.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) { p.status[TBS_INFO0] = slab; p.status[TBS_INFO1] = 301; }
+        if (ok && elect_one()) tc_commit(&b_empty[sb]);
+        __syncwarp();
       }
     }
-  } else if (warp >= 8) {
+    if (!ok) {
+      abort_flag = 1;
+      if (lane == 0 && atomicOr(&p.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) { p.status[TBS_INFO0] = slab; p.status[TBS_INFO1] = 301; }
+    }
+  } else if (warp >= kFirstExpandWarp) {
     // ------------------------------------------------ expanders: one weight row per thread
-    const uint32_t r = (warp - 8) * 32 + lane;
+    const uint32_t r = (warp - kFirstExpandWarp) * 32 + lane;
     uint32_t slab = 0;
     bool ok = true;
     for (uint32_t tile = blockIdx.x; ok && tile < tiles; tile += gridDim.x) {
@@ -346,7 +400,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
 #pragma unroll
           for (uint32_t i = 0; i < kPlaneBytes / 4; ++i) w[i] = __ldg(wsrc + i);
           const uint32_t s0 = slab % kStagesA, s1 = (slab + 1) % kStagesA;
-          if (slab >= kStagesA && !mbar_wait(&a_empty[s0], ((slab / kStagesA) - 1) & 1, &abort_flag)) { ok = false; break; }
+          if (slab >= kStagesA && !mbar_wait(&a_empty[s0], ((slab / kStagesA) - 1) & 1, &abort_flag, 100)) { ok = false; break; }
           uint8_t* t0 = tile_a + s0 * kTileABytes;
           if (CODEC == tbf::kB3) {
             uint32_t d[5], e[5], f[5], g2[5];
@@ -364,7 +418,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&a_full[s0]);
-            if (slab + 1 >= kStagesA && !mbar_wait(&a_empty[s1], (((slab + 1) / kStagesA) - 1) & 1, &abort_flag)) { ok = false; break; }
+            if (slab + 1 >= kStagesA && !mbar_wait(&a_empty[s1], (((slab + 1) / kStagesA) - 1) & 1, &abort_flag, 100)) { ok = false; break; }
             uint8_t* t1 = tile_a + s1 * kTileABytes;
             // group 1: trits 128..139 in natural order (quads 0..2), words 7..11, trits 240..255
             b3_digits(w[7], d); b3_digits(w[8], e);
@@ -391,7 +445,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&a_full[s0]);
-            if (slab + 1 >= kStagesA && !mbar_wait(&a_empty[s1], (((slab + 1) / kStagesA) - 1) & 1, &abort_flag)) { ok = false; break; }
+            if (slab + 1 >= kStagesA && !mbar_wait(&a_empty[s1], (((slab + 1) / kStagesA) - 1) & 1, &abort_flag, 100)) { ok = false; break; }
             uint8_t* t1 = tile_a + s1 * kTileABytes;
 #pragma unroll
             for (uint32_t c = 0; c < 8; ++c) {
@@ -409,109 +463,111 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
       abort_flag = 1;
       if (lane == 0 && atomicOr(&p.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) { p.status[TBS_INFO0] = slab; p.status[TBS_INFO1] = 302; }
     }
-  } else if (warp >= 4) {
-    // ------------------------------------------------ epilogue: TMEM lane = weight row
-    const uint32_t quad = warp & 3, r = quad * 32 + lane;
+  } else if (warp >= kFirstEpilogueWarp) {
+    // ------------------------------------------------ epilogue: TMEM lane = weight row; two warps
+    // share a lane quadrant and split each accumulator half's columns
+    const uint32_t quad = warp & 3, wh = (warp - kFirstEpilogueWarp) >> 2, r = quad * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((quad * 32u) << 16);
-    const uint32_t y_addr = lane_addr + 2 * kTokens;
-    constexpr float kMagic = 12582912.0f;
     uint32_t slab = 0, colfill = 0;
     bool ok = true;
-    // start values of the first two slabs of the first tile column
+    // start values of slab 0 (first tile column, group 0) for both halves
+    if (mbar_wait(&b_full[0], 0, &abort_flag)) {
+      {
+        const uint32_t h = wh;
+        const uint32_t qi = saddr(qinit_s + h * HW);
+#pragma unroll 1
+        for (uint32_t c = 0; c < kCW; c += 32) {
+          uint32_t v[32];
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) lds128(qi + (c + i) * 4u, &v[i]);
+          tmem_st32(lane_addr + h * HW + c, v);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0u;
+          tmem_st32(lane_addr + (2 + h) * HW + c, v);       // running sums start at zero
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[h]);
+      }
+    } else ok = false;
     for (uint32_t tile = blockIdx.x; ok && tile < tiles; tile += gridDim.x) {
       const uint32_t nt = tile / p.m_tiles, mt = tile % p.m_tiles;
       const uint32_t n = nt * kRows + r;
       const uint32_t nc = min(n, p.n - 1);
       const uint16_t* srow = p.scales + size_t(nc) * p.tpr * PLANES * 2;
+      const bool more_tiles = tile + gridDim.x < tiles;
       for (uint32_t j = 0; ok && j < p.tpr; ++j, ++colfill) {
         const uint32_t sb = colfill % kStagesB;
-        // start values come with the tile column's activations
-        if (!mbar_wait(&b_full[sb], (colfill / kStagesB) & 1, &abort_flag)) { ok = false; break; }
-        for (uint32_t q = 0; q < kSlabsPerCol; ++q, ++slab) {
-          const uint32_t acc = slab & 1, gsel = q & 1, pl = q >> 1;
-          const uint32_t d_addr = lane_addr + acc * kTokens;
-          // The accumulator must hold the slab's start values before its MMAs run.  Buffers are
-          // filled two slabs ahead (below); the first two slabs of the whole kernel are filled here.
-          if (slab == 0) {
-            // slabs 0 and 1 are the two groups of the first tile column and plane
+        for (uint32_t q = 0; ok && q < kSlabsPerCol; ++q, ++slab) {
+          const uint32_t gsel = q & 1, pl = q >> 1;
+          const float sv = __half2float(__ushort_as_half(srow[(j * PLANES + pl) * 2 + gsel]));
+          const float2 scale2 = make_float2(sv, sv), neg_magic2 = make_float2(-12582912.0f, -12582912.0f);
+          const bool last = (j + 1 == p.tpr && q + 1 == kSlabsPerCol);
+          // where the next slab's start values are
+          const bool next_col = q + 1 == kSlabsPerCol;
+          const bool has_next = !(last && !more_tiles);
+          const uint32_t ncol = next_col ? colfill + 1 : colfill;
+          if (has_next && next_col && !mbar_wait(&b_full[ncol % kStagesB], (ncol / kStagesB) & 1, &abort_flag)) { ok = false; break; }
+          const uint32_t qnext = saddr(qinit_s + ((ncol % kStagesB) * 2 + (next_col ? 0u : (q + 1) & 1u)) * kTileTokens);
+          {
+            const uint32_t h = wh;
+            if (!mbar_wait(&acc_full[h], slab & 1, &abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t d_addr = lane_addr + h * HW, y_addr = lane_addr + (2 + h) * HW;
+            const uint32_t tok0 = mt * kTileTokens + h * HW;
 #pragma unroll 1
-            for (uint32_t both = 0; both < 2; ++both) {
-              const int32_t* qi = qinit_s + (sb * 2 + both) * kTokens;
-#pragma unroll 1
-              for (uint32_t c = 0; c < kTokens; c += 16) {
-                uint32_t v[16];
+            for (uint32_t c = 0; c < kCW; c += 32) {
+              uint32_t dv[32], yv[32];
+              tmem_ld32(d_addr + c, dv);
+              tmem_ld32(y_addr + c, yv);      // zero at the first slab of a tile (see below)
+              tmem_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 16; ++i) v[i] = uint32_t(qi[c + i]);
-                tmem_st16(lane_addr + both * kTokens + c, v);
-              }
-              tmem_wait_st();
-              tc_fence_before();
-              __syncwarp();
-              if (lane == 0) mbar_arrive(&acc_empty[both]);
-            }
-          }
-          if (!mbar_wait(&acc_full[acc], (slab >> 1) & 1, &abort_flag)) { ok = false; break; }
-          tc_fence_after();
-          const float s = __half2float(__ushort_as_half(srow[(j * PLANES + pl) * 2 + gsel]));
-          const float sgn_scale = CODEC == tbf::kB3 ? -s : s;
-          const bool first = (j == 0 && q == 0), last = (j + 1 == p.tpr && q + 1 == kSlabsPerCol);
-          // where the NEXT user of this accumulator (slab + 2) finds its start values
-          uint32_t nq = q + 2, nj = j, ncol = colfill;
-          if (nq >= kSlabsPerCol) { nq -= kSlabsPerCol; ++nj; ++ncol; }
-          const bool has_next = !(nj >= p.tpr && tile + gridDim.x >= tiles);
-          bool next_ready = true;
-          if (has_next && ncol != colfill) next_ready = mbar_wait(&b_full[ncol % kStagesB], (ncol / kStagesB) & 1, &abort_flag);
-          if (!next_ready) { ok = false; break; }
-          const int32_t* qnext = qinit_s + ((ncol % kStagesB) * 2 + (nq & 1)) * kTokens;
-#pragma unroll 1
-          for (uint32_t c = 0; c < kTokens; c += 16) {
-            uint32_t dv[16], yv[16];
-            tmem_ld16(d_addr + c, dv);
-            if (!first) tmem_ld16(y_addr + c, yv);
-            tmem_wait_ld();
+              for (int i = 0; i < 32; i += 2) scale_add2(dv[i], dv[i + 1], neg_magic2, scale2, yv[i], yv[i + 1]);
+              if (DUMP) {
+                if (n < p.n) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const float f = __fsub_rn(__uint_as_float(dv[i]), kMagic);   // -I (B3) or +I (D2), exact
-              const float prev = first ? 0.f : __uint_as_float(yv[i]);
-              yv[i] = __float_as_uint(__fmaf_rn(f, sgn_scale, prev));
-            }
-            if (p.acc_dump && n < p.n) {
-#pragma unroll
-              for (int i = 0; i < 16; ++i) {
-                const uint32_t mtok = mt * kTokens + c + i;
-                if (mtok < p.m) {
-                  const int v = CODEC == tbf::kB3 ? int(kMagicBits) - int(dv[i]) : int(dv[i]) - int(kMagicBits);
-                  p.acc_dump[((size_t(mtok) * p.n + n) * (p.tpr * 2) + 2 * j + gsel) * PLANES + pl] = v;
+                  for (int i = 0; i < 32; ++i) {
+                    const uint32_t mtok = tok0 + c + i;
+                    if (mtok < p.m)
+                      p.acc_dump[((size_t(mtok) * p.n + n) * (p.tpr * 2) + 2 * j + gsel) * PLANES + pl] = int(dv[i]) - int(kMagicBits);
+                  }
                 }
               }
-            }
-            if (!last) tmem_st16(y_addr + c, yv);
-            else if (n < p.n) {
+              if (has_next) {
 #pragma unroll
-              for (int i = 0; i < 16; ++i) {
-                const uint32_t mtok = mt * kTokens + c + i;
-                if (mtok < p.m) {
-                  float out = __fmul_rn(__uint_as_float(yv[i]), p.ascale[mtok]);
-                  if (p.row_scale) out = __fmul_rn(out, p.row_scale[n]);
-                  const size_t idx = size_t(mtok) * p.n + n;
-                  if (p.y_dtype == TB_F32) static_cast<float*>(p.y)[idx] = out;
-                  else static_cast<__nv_bfloat16*>(p.y)[idx] = __float2bfloat16_rn(out);
+                for (int i = 0; i < 32; i += 4) lds128(qnext + (h * HW + c + i) * 4u, &dv[i]);
+                tmem_st32(d_addr + c, dv);
+              }
+              if (!last) tmem_st32(y_addr + c, yv);
+              else {
+                if (n < p.n) {
+                  const float rs = p.row_scale ? p.row_scale[n] : 1.0f;
+#pragma unroll
+                  for (int i = 0; i < 32; ++i) {
+                    const uint32_t mtok = tok0 + c + i;
+                    if (mtok < p.m) {
+                      float out = __fmul_rn(__uint_as_float(yv[i]), __ldg(p.ascale + mtok));
+                      if (p.row_scale) out = __fmul_rn(out, rs);
+                      const size_t idx = size_t(mtok) * p.n + n;
+                      if (p.y_dtype == TB_F32) static_cast<float*>(p.y)[idx] = out;
+                      else static_cast<__nv_bfloat16*>(p.y)[idx] = __float2bfloat16_rn(out);
+                    }
+                  }
                 }
+                // the next tile starts from zero running sums
+#pragma unroll
+                for (int i = 0; i < 32; ++i) yv[i] = 0u;
+                tmem_st32(y_addr + c, yv);
               }
             }
-            if (has_next) {
-              uint32_t v[16];
-#pragma unroll
-              for (int i = 0; i < 16; ++i) v[i] = uint32_t(qnext[c + i]);
-              tmem_st16(d_addr + c, v);
-            }
+            tmem_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0 && has_next) mbar_arrive(&acc_empty[h]);
           }
-          tmem_wait_st();
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0 && has_next) mbar_arrive(&acc_empty[acc]);
-          // this column's start values are no longer needed once its last two slabs' successors are filled
-          if (lane == 0 && q + 1 == kSlabsPerCol) mbar_arrive(&b_empty[sb]);
+          // the column's start values and activations are no longer needed by this warp
+          if (ok && lane == 0 && next_col) mbar_arrive(&b_empty[sb]);
         }
       }
     }
@@ -522,7 +578,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 2) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(4u * HW) : "memory");
 }
 
 // ---------------------------------------------------------------- host side
@@ -541,7 +597,9 @@ EncodeTiled encode_tiled_fn() {
   return fn;
 }
 
-uint32_t pad_tokens(uint32_t m) { return (m + kTokens - 1) / kTokens * kTokens; }
+// tokens per accumulator half: 64 for up to 128 tokens (one 128-token tile), else 128
+uint32_t half_width(uint32_t m) { return m <= 128 ? 64 : 128; }
+uint32_t pad_tokens(uint32_t m) { const uint32_t t = 2 * half_width(m); return (m + t - 1) / t * t; }
 
 struct Scratch { int8_t* qperm; int32_t* qinit; float* ascale; };
 Scratch carve(void* base, uint32_t m_pad, uint32_t k) {
@@ -555,7 +613,7 @@ Scratch carve(void* base, uint32_t m_pad, uint32_t k) {
   return s;
 }
 
-template <int CODEC>
+template <int CODEC, int HW, bool DUMP>
 cudaError_t launch_planes(uint32_t planes, dim3 grid, size_t smem, cudaStream_t st, const PrefillParams& pp, const CUtensorMap& map) {
   auto go = [&](auto kernel) -> cudaError_t {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
@@ -563,9 +621,18 @@ cudaError_t launch_planes(uint32_t planes, dim3 grid, size_t smem, cudaStream_t 
     kernel<<<grid, kThreads, smem, st>>>(pp, map);
     return cudaGetLastError();
   };
-  if (planes == 1) return go(prefill_kernel<CODEC, 1>);
-  if (planes == 2) return go(prefill_kernel<CODEC, 2>);
-  return go(prefill_kernel<CODEC, 3>);
+  if (planes == 1) return go(prefill_kernel<CODEC, 1, HW, DUMP>);
+  if (planes == 2) return go(prefill_kernel<CODEC, 2, HW, DUMP>);
+  return go(prefill_kernel<CODEC, 3, HW, DUMP>);
+}
+
+template <int CODEC>
+cudaError_t launch_shape(uint32_t hw, bool dump, uint32_t planes, dim3 grid, size_t smem, cudaStream_t st, const PrefillParams& pp,
+                         const CUtensorMap& map) {
+  if (hw == 64) return dump ? launch_planes<CODEC, 64, true>(planes, grid, smem, st, pp, map)
+                            : launch_planes<CODEC, 64, false>(planes, grid, smem, st, pp, map);
+  return dump ? launch_planes<CODEC, 128, true>(planes, grid, smem, st, pp, map)
+              : launch_planes<CODEC, 128, false>(planes, grid, smem, st, pp, map);
 }
 
 }  // namespace
@@ -598,7 +665,8 @@ cudaError_t tb_launch_prefill(const PrefillArgs& a, int sm_count, cudaStream_t s
   CUtensorMap map;
   const cuuint64_t dims[2] = {k, m_pad};
   const cuuint64_t strides[1] = {k};
-  const cuuint32_t box[2] = {128, kTokens};
+  const uint32_t hw = half_width(a.m), tile_tokens = 2 * hw;
+  const cuuint32_t box[2] = {128, tile_tokens};
   const cuuint32_t elem[2] = {1, 1};
   if (encode_tiled_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, sc.qperm, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
@@ -609,9 +677,10 @@ cudaError_t tb_launch_prefill(const PrefillArgs& a, int sm_count, cudaStream_t s
   pp.qperm = sc.qperm; pp.qinit = sc.qinit; pp.ascale = sc.ascale;
   pp.y = a.y; pp.acc_dump = a.acc_dump; pp.row_scale = a.row_scale; pp.status = a.status;
   pp.m = a.m; pp.m_pad = m_pad; pp.n = uint32_t(w->n); pp.k = k; pp.tpr = k / 256; pp.y_dtype = uint32_t(a.y_dtype);
-  pp.n_tiles = (pp.n + kRows - 1) / kRows; pp.m_tiles = m_pad / kTokens;
-  const size_t smem = 1024 + size_t(kStagesA) * kTileABytes + size_t(kStagesB) * 2 * kTileBBytes + size_t(kStagesB) * 2 * kTokens * 4;
+  pp.n_tiles = (pp.n + kRows - 1) / kRows; pp.m_tiles = m_pad / tile_tokens;
+  const size_t smem = 1024 + size_t(kStagesA) * kTileABytes + size_t(kStagesB) * 2 * tile_tokens * 128 + size_t(kStagesB) * 2 * tile_tokens * 4;
   const dim3 grid(std::min<uint32_t>(pp.n_tiles * pp.m_tiles, uint32_t(sm_count)));
-  return w->codec == tbf::kB3 ? launch_planes<tbf::kB3>(w->uniform_planes, grid, smem, stream, pp, map)
-                              : launch_planes<tbf::kD2>(w->uniform_planes, grid, smem, stream, pp, map);
+  const bool dump = a.acc_dump != nullptr;
+  return w->codec == tbf::kB3 ? launch_shape<tbf::kB3>(hw, dump, w->uniform_planes, grid, smem, stream, pp, map)
+                              : launch_shape<tbf::kD2>(hw, dump, w->uniform_planes, grid, smem, stream, pp, map);
 }
