@@ -3,24 +3,26 @@
 //   Y[m,n] = a[m] * sum over (tile column j, plane p, group g) of s[n,j,p,g] * I[m,n,j,p,g],
 //   I = sum over the 128 trits of the group of t * q          (exact int32)
 //
-// One CTA owns a 128 (weight rows) x 128 (tokens) output tile and walks the K dimension in slabs
-// of one (tile column, plane, scale group) = 128 trits:
-//   * expander warps read each row's packed words, turn them into int8 operands with the
-//     half-precision-FMA digit trick (no table, no division) and write the slab as a K-major,
+// One CTA owns a 128 (weight rows) x 2*HW (tokens) output tile, HW = 128 (64 for up to 128 tokens),
+// and walks the K dimension in slabs of one (tile column, plane, scale group) = 128 trits:
+//   * expander warps read each row's packed words, turn them into int8 operands (B3: a
+//     half-precision-FMA chain gives the quotients floor(b / 3^i), one 32-bit multiply-add per
+//     digit gives the four lanes' digits; no table, no division) and write the slab as a K-major,
 //     128-byte-swizzled tile in shared memory (A operand, UMMA M = 128);
-//   * a TMA warp loads the int8 activations of the tile column (B operand, N = 128 tokens) from
-//     the scratch written by the quantisation pre-pass, already in the expander's k-slot order;
-//   * one thread issues four tcgen05.mma (kind::i8, K = 32 each) per slab into a TMEM accumulator
-//     that the epilogue pre-loaded with 0x4B400000 +/- (sum of the slab's activations): after the
-//     MMAs the accumulator's bits ARE the float 12582912 -/+ I, so int->float costs one FADD;
-//   * epilogue warps (one TMEM lane = one weight row per thread) drain the accumulator, multiply
-//     by the row's f16 group scale and add into an fp32 running sum that also lives in TMEM.
-// Operand signs: B3 digits come out of the FMA chain as -d (digits 0..3) / +d (digit 4), so the
-// activations of digit-4 slots are stored negated and the start value carries +sum(q); the
-// accumulator then holds magic - I.  D2 codes are used as unsigned c = t+1 with start value
-// magic - sum(q); the accumulator holds magic + I.
+//   * a TMA warp loads the int8 activations of the tile column (B operand) from the scratch
+//     written by the quantisation pre-pass, already in the expander's k-slot order, together with
+//     the per-token start values of its two slabs;
+//   * two MMA warps, one per half of the token tile, each issue four tcgen05.mma (kind::i8,
+//     N = HW, K = 32 each) per slab into their TMEM accumulator.  The accumulator was pre-loaded by
+//     the epilogue with 0x4B400000 - (sum of the slab's activations): operands are the unsigned
+//     codes c = trit + 1, so after the MMAs the accumulator's BITS are the float 12582912 + I and
+//     int -> float costs one FADD.  While one half is drained the tensor core works on the other;
+//   * epilogue warps (one TMEM lane = one weight row per thread; a warp owns one half and a
+//     column range of it) drain the accumulator, multiply by the row's f16 group scale, add into
+//     fp32 running sums that also live in TMEM (packed two-lane FADD2 / FFMA2), store the next
+//     slab's start values and hand the half back.
 //
-// TMEM columns: [0,128) accumulator 0, [128,256) accumulator 1, [256,384) fp32 running sums.
+// TMEM columns: [0,HW) and [HW,2HW) accumulator halves, [2HW,4HW) fp32 running sums.
 // All waits are bounded; a timeout sets TBF_WAIT_TIMEOUT and every role leaves its loop, the
 // allocating warp frees TMEM, and the kernel returns.  No TMA multicast is used.
 #include <cuda.h>
@@ -36,9 +38,9 @@ namespace {
 constexpr int kRows = 128;        // weight rows per tile (UMMA M)
 constexpr int kStagesA = 4;       // expanded slabs in flight
 constexpr int kStagesB = 2;       // tile columns of activations in flight (two slabs each)
-constexpr int kEpilogueWarps = 8, kExpandWarps = 4;
+constexpr int kEpilogueWarps = 16, kExpandWarps = 4;   // epilogue: two column parts per accumulator half and lane quadrant
 constexpr int kFirstEpilogueWarp = 4, kFirstExpandWarp = kFirstEpilogueWarp + kEpilogueWarps;
-constexpr int kThreads = 32 * (kFirstExpandWarp + kExpandWarps);   // warps: 0 TMA, 1 MMA + TMEM owner, 2-3 idle, 4-11 epilogue, 12-15 expanders
+constexpr int kThreads = 32 * (kFirstExpandWarp + kExpandWarps);   // warps: 0 TMA, 1-2 MMA issue (1 owns TMEM), 3 idle, then epilogue, then expanders
 constexpr uint32_t kSpin = 1u << 22;
 constexpr long long kWaitCycles = 2000000000ll;
 constexpr uint32_t kMagicBits = 0x4B400000u;   // float 12582912 = 2^23 + 2^22
@@ -69,12 +71,16 @@ __device__ __forceinline__ bool mbar_try(uint64_t* b, uint32_t parity) {
 // Bounded wait: gives up after kWaitCycles SM clocks (about a second) or when another role has
 // raised the abort flag.  `backoff_ns` > 0 sleeps between polls: roles that run ahead of the
 // pipeline (copy producer, expanders) must not take issue slots from the warps that bound it.
-__device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, volatile uint32_t* abort_flag, uint32_t backoff_ns = 0) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, volatile uint32_t* abort_flag, uint32_t backoff_ns = 0,
+                                          uint32_t expected_ns = 0) {
   if (mbar_try(b, parity)) return true;
+  // a wait that is known to take a while (the MMA that has just been started, a whole drain)
+  // sleeps through most of it instead of polling
+  if (expected_ns) __nanosleep(expected_ns);
   const long long t0 = clock64();
   for (uint32_t i = 0;; ++i) {
-    if (backoff_ns) __nanosleep(backoff_ns);
     if (mbar_try(b, parity)) return true;
+    if (backoff_ns) __nanosleep(backoff_ns);
     if ((i & 63u) == 63u) {
       if (*abort_flag) return false;
       if (clock64() - t0 > kWaitCycles) return false;
@@ -137,6 +143,10 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
                "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
                ::"r"(taddr), TB_S16(r, 0), TB_S16(r, 16) : "memory");
 }
+__device__ __forceinline__ void tmem_ldn(uint32_t taddr, uint32_t (&r)[16]) { tmem_ld16(taddr, r); }
+__device__ __forceinline__ void tmem_ldn(uint32_t taddr, uint32_t (&r)[32]) { tmem_ld32(taddr, r); }
+__device__ __forceinline__ void tmem_stn(uint32_t taddr, const uint32_t (&r)[16]) { tmem_st16(taddr, r); }
+__device__ __forceinline__ void tmem_stn(uint32_t taddr, const uint32_t (&r)[32]) { tmem_st32(taddr, r); }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -286,7 +296,9 @@ template <int CODEC, int PLANES, int HW, bool DUMP>
 __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map_q) {
   constexpr uint32_t kTileTokens = 2 * HW;
   constexpr uint32_t kTileBBytes = kTileTokens * 128;          // one slab of activations
-  constexpr uint32_t kCW = HW;                                 // columns per epilogue thread: one whole half
+  constexpr uint32_t kParts = kEpilogueWarps / 8;              // epilogue warps per (half, lane quadrant)
+  constexpr uint32_t kCW = HW / kParts;                        // columns per epilogue thread
+  constexpr int kChunk = 16;
   constexpr uint32_t kSlabsPerCol = 2 * PLANES;
   constexpr uint32_t kPlaneBytes = CODEC == tbf::kB3 ? 52 : 64;
   constexpr uint32_t kIdesc = instr_desc_n(HW);
@@ -301,8 +313,8 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
     abort_flag = 0;
-    for (int s = 0; s < kStagesA; ++s) { mbar_init(&a_full[s], kExpandWarps); mbar_init(&a_empty[s], 1); }
-    for (int s = 0; s < kStagesB; ++s) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 1 + kEpilogueWarps); }
+    for (int s = 0; s < kStagesA; ++s) { mbar_init(&a_full[s], kExpandWarps); mbar_init(&a_empty[s], 2); }
+    for (int s = 0; s < kStagesB; ++s) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 2 + kEpilogueWarps); }
     for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], kEpilogueWarps / 2); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -344,8 +356,10 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
         for (uint32_t i = 0; i < kSpin && !mbar_try(&b_full[f % kStagesB], (f / kStagesB) & 1); ++i) {}
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------ MMA issuer: the whole warp walks the loop (so
+  } else if (warp == 1 || warp == 2) {
+    // ------------------------------------------------ MMA issuers, one warp per accumulator half (issuing a
+    // tcgen05.mma keeps the thread busy for about as long as the MMA runs, so one thread cannot
+    // keep the tensor core fed and also do the waiting); the whole warp walks the loop (so
     // that addresses and descriptors stay in uniform registers); one elected lane issues
     uint32_t slab = 0, colfill = 0;
     bool ok = true;
@@ -360,9 +374,9 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
           // descriptor start addresses are in 16-byte units
           const uint64_t a_desc = a_desc0 + uint64_t(sa * (kTileABytes >> 4));
           const uint64_t b_desc = b_desc0 + uint64_t((sb * 2 + gsel) * (kTileBBytes >> 4));
-#pragma unroll
-          for (uint32_t h = 0; h < 2; ++h) {
-            if (!mbar_wait(&acc_empty[h], slab & 1, &abort_flag)) { ok = false; break; }
+          {
+            const uint32_t h = warp - 1;
+            if (!mbar_wait(&acc_empty[h], slab & 1, &abort_flag, 0, 250)) { ok = false; break; }
             tc_fence_after();
             if (elect_one()) {
 #pragma unroll
@@ -466,24 +480,24 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
   } else if (warp >= kFirstEpilogueWarp) {
     // ------------------------------------------------ epilogue: TMEM lane = weight row; two warps
     // share a lane quadrant and split each accumulator half's columns
-    const uint32_t quad = warp & 3, wh = (warp - kFirstEpilogueWarp) >> 2, r = quad * 32 + lane;
-    const uint32_t lane_addr = tmem_base + ((quad * 32u) << 16);
+    const uint32_t quad = warp & 3, sub = (warp - kFirstEpilogueWarp) >> 2, wh = sub & 1, part = sub >> 1, r = quad * 32 + lane;
+    const uint32_t lane_addr = tmem_base + ((quad * 32u) << 16) + part * kCW;
     uint32_t slab = 0, colfill = 0;
     bool ok = true;
     // start values of slab 0 (first tile column, group 0) for both halves
     if (mbar_wait(&b_full[0], 0, &abort_flag)) {
       {
         const uint32_t h = wh;
-        const uint32_t qi = saddr(qinit_s + h * HW);
+        const uint32_t qi = saddr(qinit_s + h * HW + part * kCW);
 #pragma unroll 1
-        for (uint32_t c = 0; c < kCW; c += 32) {
-          uint32_t v[32];
+        for (uint32_t c = 0; c < kCW; c += kChunk) {
+          uint32_t v[kChunk];
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) lds128(qi + (c + i) * 4u, &v[i]);
-          tmem_st32(lane_addr + h * HW + c, v);
+          for (int i = 0; i < kChunk; i += 4) lds128(qi + (c + i) * 4u, &v[i]);
+          tmem_stn(lane_addr + h * HW + c, v);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = 0u;
-          tmem_st32(lane_addr + (2 + h) * HW + c, v);       // running sums start at zero
+          for (int i = 0; i < kChunk; ++i) v[i] = 0u;
+          tmem_stn(lane_addr + (2 + h) * HW + c, v);       // running sums start at zero
         }
         tmem_wait_st();
         tc_fence_before();
@@ -509,25 +523,25 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
           const bool has_next = !(last && !more_tiles);
           const uint32_t ncol = next_col ? colfill + 1 : colfill;
           if (has_next && next_col && !mbar_wait(&b_full[ncol % kStagesB], (ncol / kStagesB) & 1, &abort_flag)) { ok = false; break; }
-          const uint32_t qnext = saddr(qinit_s + ((ncol % kStagesB) * 2 + (next_col ? 0u : (q + 1) & 1u)) * kTileTokens);
+          const uint32_t qnext = saddr(qinit_s + ((ncol % kStagesB) * 2 + (next_col ? 0u : (q + 1) & 1u)) * kTileTokens + part * kCW);
           {
             const uint32_t h = wh;
-            if (!mbar_wait(&acc_full[h], slab & 1, &abort_flag)) { ok = false; break; }
+            if (!mbar_wait(&acc_full[h], slab & 1, &abort_flag, 0, 80)) { ok = false; break; }
             tc_fence_after();
             const uint32_t d_addr = lane_addr + h * HW, y_addr = lane_addr + (2 + h) * HW;
-            const uint32_t tok0 = mt * kTileTokens + h * HW;
+            const uint32_t tok0 = mt * kTileTokens + h * HW + part * kCW;
 #pragma unroll 1
-            for (uint32_t c = 0; c < kCW; c += 32) {
-              uint32_t dv[32], yv[32];
-              tmem_ld32(d_addr + c, dv);
-              tmem_ld32(y_addr + c, yv);      // zero at the first slab of a tile (see below)
+            for (uint32_t c = 0; c < kCW; c += kChunk) {
+              uint32_t dv[kChunk], yv[kChunk];
+              tmem_ldn(d_addr + c, dv);
+              tmem_ldn(y_addr + c, yv);      // zero at the first slab of a tile (see below)
               tmem_wait_ld();
 #pragma unroll
-              for (int i = 0; i < 32; i += 2) scale_add2(dv[i], dv[i + 1], neg_magic2, scale2, yv[i], yv[i + 1]);
+              for (int i = 0; i < kChunk; i += 2) scale_add2(dv[i], dv[i + 1], neg_magic2, scale2, yv[i], yv[i + 1]);
               if (DUMP) {
                 if (n < p.n) {
 #pragma unroll
-                  for (int i = 0; i < 32; ++i) {
+                  for (int i = 0; i < kChunk; ++i) {
                     const uint32_t mtok = tok0 + c + i;
                     if (mtok < p.m)
                       p.acc_dump[((size_t(mtok) * p.n + n) * (p.tpr * 2) + 2 * j + gsel) * PLANES + pl] = int(dv[i]) - int(kMagicBits);
@@ -536,15 +550,15 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
               }
               if (has_next) {
 #pragma unroll
-                for (int i = 0; i < 32; i += 4) lds128(qnext + (h * HW + c + i) * 4u, &dv[i]);
-                tmem_st32(d_addr + c, dv);
+                for (int i = 0; i < kChunk; i += 4) lds128(qnext + (h * HW + c + i) * 4u, &dv[i]);
+                tmem_stn(d_addr + c, dv);
               }
-              if (!last) tmem_st32(y_addr + c, yv);
+              if (!last) tmem_stn(y_addr + c, yv);
               else {
                 if (n < p.n) {
                   const float rs = p.row_scale ? p.row_scale[n] : 1.0f;
 #pragma unroll
-                  for (int i = 0; i < 32; ++i) {
+                  for (int i = 0; i < kChunk; ++i) {
                     const uint32_t mtok = tok0 + c + i;
                     if (mtok < p.m) {
                       float out = __fmul_rn(__uint_as_float(yv[i]), __ldg(p.ascale + mtok));
@@ -557,8 +571,8 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
                 }
                 // the next tile starts from zero running sums
 #pragma unroll
-                for (int i = 0; i < 32; ++i) yv[i] = 0u;
-                tmem_st32(y_addr + c, yv);
+                for (int i = 0; i < kChunk; ++i) yv[i] = 0u;
+                tmem_stn(y_addr + c, yv);
               }
             }
             tmem_wait_st();
