@@ -33,6 +33,9 @@ N_ROWS, K_COLS, PLANES = 6912, 2560, 3
 METRIC = "ternary linear HBM GB/s (M=1)"
 UNIT = "GB/s"
 PLANE_BYTES = {"b3": 52, "d2": 64}
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE grouped decode launch, from the ncu capture
+# summarised in profiles/decode_kernel_c2_b3_m1.md; key = (codec, tokens, weight copies per launch)
+NCU_TRAFFIC_BYTES = {("b3", 1, 26): 301_976_064 + 5_391_616}
 
 
 def algorithmic_bytes(codec: str, m: int, x_size: int = 2, y_size: int = 2) -> int:
@@ -315,7 +318,7 @@ def run_b200(args) -> None:
                        "l2_policy": f"rotating set of {copies} distinct weight buffers ({bytes_per_step / 1e6:.0f} MB > 126 MB L2)",
                        "launch": ("cuda graph" if graph is not None else "eager") + (" + programmatic dependent launch" if flags else "")},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
-                         "traffic": None, "peak_kind": peak_kind, "kernel": "decode_kernel", "us_per_launch": per_launch_us,
+                         "traffic": NCU_TRAFFIC_BYTES.get((codec_name, m, copies)), "peak_kind": peak_kind, "kernel": "decode_kernel", "us_per_launch": per_launch_us,
                          "algorithmic_bytes_per_launch": bytes_per_step, "layers_per_launch": copies,
                          "algorithmic_bytes_per_layer": layer_bytes},
             "cpu_baseline": cpu,
