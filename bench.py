@@ -195,6 +195,78 @@ def measure_prefill(torch, backend, weights, m: int, codec_name: str, steps: int
                          "peak_kind": kind, "frac_of_nominal_4500": tops / 4500.0, "kernel": "prefill_kernel"}}
 
 
+def measure_tp(torch, dist, backend, rank: int, world: int, codec, codec_name: str, args, stream) -> dict:
+    """Tensor-parallel leg: the linears of the 27B-class decoder (64 layers x {QKV 5120->7168,
+    O 5120->5120, gate+up 5120->34816, down 17408->5120}, 2 planes) sharded over `world` GPUs:
+    QKV and gate/up column-parallel, O and down row-parallel with a MAX all-reduce of the per-token
+    absmax before and a SUM all-reduce of the fp32 partial outputs after.  `L` = 2 x world distinct
+    layers are built and timed (each rank streams 2 x 144 MB > L2 per step); the 64-layer step
+    time is L-layer time x 64 / L, stated in the output."""
+    from tritium_b200 import _lib, tp
+    shape = tp.DECODER_27B
+    built = 2 * world
+    out = {"workload": f"c5_27b_2plane_tp{world}_{codec_name}", "layers_timed": built, "layers_model": shape.layers,
+           "collective": "nccl all_reduce (fp32 sum after O and down; fp32 max of the row absmax before them)" if world > 1 else "none"}
+    m_prefill = args.tp_prefill_m
+    max_m = max(1, m_prefill)
+    ex = tp.CudaExecutor(backend, flags=0)
+    t0 = time.perf_counter()
+    stack = tp.TPDecoderStack(ex, shape, codec, rank, world, max_m=max_m, distinct_layers=built, synthetic_shards=True)
+    out["build_seconds"] = time.perf_counter() - t0
+    bytes_rank = stack.weight_bytes()
+    steps = max(3, min(args.steps, 20))
+
+    def timed(m: int, use_graph: bool):
+        stack.fill_inputs(m, seed=m)
+        with torch.cuda.stream(stream):
+            stack.forward(m)
+            stream.synchronize()
+            backend.check(stream)
+            step = lambda: stack.forward(m)
+            graph = None
+            if use_graph:
+                try:
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph, stream=stream):
+                        stack.forward(m)
+                    step = graph.replay
+                except Exception as exc:  # capture of a collective is refused on some setups: time eagerly
+                    out.setdefault("notes", []).append(f"graph capture failed ({type(exc).__name__}); eager launches")
+                    graph = None
+                    step = lambda: stack.forward(m)
+            for _ in range(3):
+                step()
+            stream.synchronize()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(steps):
+                step()
+            e1.record(stream)
+            stream.synchronize()
+            backend.check(stream)
+        t = torch.tensor([e0.elapsed_time(e1) / steps], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()), graph is not None
+
+    ms, graphed = timed(1, not args.no_graph)
+    full_ms = ms * shape.layers / built
+    out["decode_m1"] = {"ms_per_step_timed_layers": ms, "ms_per_64_layer_step": full_ms, "tokens_per_s": 1e3 / full_ms,
+                        "weight_gbs_all_ranks": world * bytes_rank / (ms * 1e-3) / 1e9, "cuda_graph": graphed,
+                        "all_reduces_per_timed_step": 4 * built if world > 1 else 0}
+    if m_prefill > 0:
+        ms, _ = timed(m_prefill, False)
+        full_ms = ms * shape.layers / built
+        ops = 2.0 * m_prefill * shape.planes * sum(n * k for _, _, n, k in shape.linears()) * built
+        out[f"prefill_m{m_prefill}"] = {"ms_per_step_timed_layers": ms, "ms_per_64_layer_step": full_ms,
+                                        "tokens_per_s": m_prefill * 1e3 / full_ms, "tops_all_ranks": ops / (ms * 1e-3) / 1e12}
+    del stack
+    return out
+
+
 def run_b200(args) -> None:
     import torch
     import torch.distributed as dist
@@ -303,6 +375,10 @@ def run_b200(args) -> None:
             prefill["roofline"]["frac"] *= scale
             prefill["roofline"]["frac_of_nominal_4500"] *= scale
 
+    tp_leg = None
+    if not args.no_tp:
+        tp_leg = measure_tp(torch, dist, backend, rank, world, codec, codec_name, args, stream)
+
     if rank == 0:
         cpu = None
         if world == 1 and not args.skip_cpu:
@@ -327,6 +403,7 @@ def run_b200(args) -> None:
             "gpu_launches": args.steps * 2,
             "clocks": clocks.summary(),
             "prefill": prefill,
+            "tp": tp_leg,
         }
         print(json.dumps(line), flush=True)
     stack.close()
@@ -351,6 +428,8 @@ def main() -> None:
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--prefill-m", type=int, default=2048, help="tokens of the tensor-core leg (0 = skip)")
     ap.add_argument("--only-prefill", action="store_true")
+    ap.add_argument("--no-tp", action="store_true", help="skip the tensor-parallel decoder-stack leg")
+    ap.add_argument("--tp-prefill-m", type=int, default=4096, help="tokens of the tensor-parallel prefill pass (0 = skip)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -97,6 +97,14 @@ def rank_main(rank, world, port, codec_value, results):
         dist.all_gather(gathered, o_full)
         same = all(torch.equal(gathered[0], t) for t in gathered)
         shapes = [tuple(o.shape) for o in outs]
+        # shards drawn directly by each rank (the benchmark's way) go through the same classes
+        direct = tp.TPDecoderStack(ex, shape, codec, rank, world, max_m=2, act_dtype=torch.float32, distinct_layers=1,
+                                   synthetic_shards=True)
+        direct.fill_inputs(2, seed=4)
+        d_outs = direct.forward(2)
+        gathered = [torch.zeros_like(d_outs[3]) for _ in range(world)]
+        dist.all_gather(gathered, d_outs[3].clone())
+        same = same and all(torch.equal(gathered[0], t) for t in gathered) and [tuple(o.shape) for o in d_outs] == shapes
         results[rank] = (err_col, err_row, absmax_ok, same, shapes)
     finally:
         dist.destroy_process_group()

@@ -1,0 +1,79 @@
+"""Tensor-parallel linears on two GPUs over NCCL: the reduced result equals the unsharded CPU
+reference; per-shard int8 codes use the absmax of the whole row."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+sys.path.insert(0, os.path.join(os.path.dirname(__file__), ".."))
+
+pytestmark = pytest.mark.gpu
+
+
+def free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def rel_l2(got, want):
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    return float(np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-30))
+
+
+def rank_main(rank, world, port, codec_value, results):
+    import torch.distributed as dist
+    from oracle import oracle as orc
+    from tritium_b200 import B200Backend, tp
+    from tritium_b200.format import SaltV2Codec
+    from tritium_b200.synth import make_activations, make_tensor
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        codec = SaltV2Codec(codec_value)
+        backend = B200Backend(rank)
+        ex = tp.CudaExecutor(backend)
+        stream = torch.cuda.Stream()
+        out = {}
+        for m, n, k, planes in [(3, 256, 1024, 2), (40, 384, 2048, 1)]:     # decode kernel, tensor-core kernel
+            tensor = make_tensor("w", n, k, planes, seed=11 + m)
+            x = make_activations(m, k, seed=5, bf16=True)
+            otensor = orc.Tensor(n, k, 128, tensor.plane_count.copy(), tensor.trits.copy(), tensor.scales.copy())
+            want = orc.a8_linear(otensor, x, dump=False)[0]
+            with torch.cuda.stream(stream):
+                col = tp.TPLinear(ex, tensor, codec, "column", rank, world, max_m=m)
+                col.input_view(m).copy_(torch.from_numpy(x).to(torch.bfloat16))
+                y_col = col.forward(m)
+                row = tp.TPLinear(ex, tensor, codec, "row", rank, world, max_m=m)
+                g = row.geometry
+                row.input_view(m).copy_(torch.from_numpy(np.ascontiguousarray(x[:, g.k_offset:g.k_offset + g.k_valid])).to(torch.bfloat16))
+                y_row = row.forward(m)
+                stream.synchronize()
+                backend.check(stream)
+            gc = col.geometry
+            out[m] = (rel_l2(y_col.cpu().numpy(), want[:, gc.n_offset:gc.n_offset + gc.n]), rel_l2(y_row.cpu().numpy(), want),
+                      bool(np.array_equal(row.absmax[:m].cpu().numpy(), np.abs(x).max(axis=1))))
+        results[rank] = out
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("codec", [2, 1], ids=["b3", "d2"])
+def test_two_gpu_tensor_parallel_matches_unsharded_reference(codec):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    world = 2
+    with mp.Manager() as manager:
+        results = manager.dict()
+        mp.spawn(rank_main, args=(world, free_port(), codec, results), nprocs=world, join=True)
+        assert sorted(results.keys()) == [0, 1]
+        for rank in range(world):
+            for m, (err_col, err_row, absmax_ok) in results[rank].items():
+                assert err_col <= 1e-5 and err_row <= 1e-5, (rank, m, err_col, err_row)
+                assert absmax_ok

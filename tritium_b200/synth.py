@@ -41,6 +41,24 @@ def make_tensor(name: str, n: int, k: int, planes: int, seed: int = 0, **kw) -> 
     return SaltV2Tensor.from_matrix_planes(name, trits, scales)
 
 
+def make_shard_tensor(name: str, n: int, k: int, planes: int, mode: str, rank: int, world: int, seed: int = 0, **kw) -> SaltV2Tensor:
+    """One rank's shard of a synthetic [n, k] tensor, generated directly (the full tensor is never
+    built): column-parallel -> [n / world, k]; row-parallel -> [n, k / world] padded with zero
+    trits and zero scales to whole 256-wide tiles.  Distribution as `make_planes`."""
+    if mode == "column":
+        return make_tensor(name, n // world, k, planes, seed=seed * 1009 + rank, **kw)
+    kv = k // world
+    kp = (kv + 255) // 256 * 256
+    trits, scales = make_planes(n, kv, planes, seed=seed * 1009 + rank, **kw)
+    if kp != kv:
+        tp_ = np.zeros((planes, n, kp), np.int8)
+        tp_[:, :, :kv] = trits
+        sp_ = np.zeros((planes, n, kp // 128), np.float32)
+        sp_[:, :, : kv // 128] = scales
+        trits, scales = tp_, sp_
+    return SaltV2Tensor.from_matrix_planes(name, trits, scales)
+
+
 def make_activations(m: int, k: int, seed: int = 0, outlier_fraction: float = 0.001, outlier_gain: float = 20.0,
                      bf16: bool = False) -> np.ndarray:
     """N(0,1) activations [m,k]; `outlier_fraction` of the channels (the same for every token) are

@@ -95,18 +95,26 @@ class TPLinear:
     """One rank's share of a tensor-parallel ternary linear."""
 
     def __init__(self, executor: ShardExecutor, tensor: SaltV2Tensor, codec: SaltV2Codec, mode: str, rank: int, world: int,
-                 group=None, max_m: int = 1, act_dtype=None):
+                 group=None, max_m: int = 1, act_dtype=None, full_shape=None):
+        """``tensor`` is the whole [n, k] tensor (it is sharded here), or, when ``full_shape`` =
+        (n, k) is given, this rank's shard already cut and padded as `ShardGeometry` says."""
         import torch
         self.executor, self.rank, self.world, self.group, self.max_m = executor, rank, world, group, max_m
-        n, k = tensor.rows, tensor.cols
         planes = int(tensor.plane_count[0])
         if np.any(tensor.plane_count != planes):
             raise ValueError("tensor-parallel sharding needs the same plane count in every tile")
-        self.geometry = ShardGeometry.of(mode, n, k, world, rank)
-        payload, scales, _, _, _ = tensor.resident(codec)
-        sn, sk, sp, ss, sm, term = fmt.tp_shard(codec, tensor.scale_group_size, n, k, planes, payload, scales,
-                                                mode == "row", world, rank)
-        assert (sn, sk) == (self.geometry.n, self.geometry.k)
+        if full_shape is None:
+            n, k = tensor.rows, tensor.cols
+            self.geometry = ShardGeometry.of(mode, n, k, world, rank)
+            payload, scales, _, _, _ = tensor.resident(codec)
+            sn, sk, sp, ss, sm, term = fmt.tp_shard(codec, tensor.scale_group_size, n, k, planes, payload, scales,
+                                                    mode == "row", world, rank)
+        else:
+            self.geometry = ShardGeometry.of(mode, full_shape[0], full_shape[1], world, rank)
+            sn, sk = tensor.rows, tensor.cols
+            sp, ss, sm, term, _ = tensor.resident(codec)
+        if (sn, sk) != (self.geometry.n, self.geometry.k):
+            raise ValueError(f"shard is [{sn}, {sk}], expected [{self.geometry.n}, {self.geometry.k}]")
         self.handle = executor.upload(codec, tensor.scale_group_size, sn, sk, sp, ss, sm, term)
         if hasattr(executor, "reserve"):
             executor.reserve(self.handle, max_m)
@@ -170,8 +178,11 @@ class TPDecoderStack:
     row-parallel with the all-reduce behind them."""
 
     def __init__(self, executor: ShardExecutor, shape: DecoderShape, codec: SaltV2Codec, rank: int, world: int, group=None,
-                 max_m: int = 1, make_tensor=None, distinct_layers: int | None = None, act_dtype=None):
-        from .synth import make_tensor as synth_tensor
+                 max_m: int = 1, make_tensor=None, distinct_layers: int | None = None, act_dtype=None,
+                 synthetic_shards: bool = False):
+        """``synthetic_shards`` draws each rank's shard directly from the seeded generator instead of
+        building and cutting the whole tensor (benchmarks: 1/world of the host work per rank)."""
+        from .synth import make_shard_tensor, make_tensor as synth_tensor
         make_tensor = make_tensor or synth_tensor
         self.shape, self.rank, self.world = shape, rank, world
         built = distinct_layers or shape.layers
@@ -179,8 +190,13 @@ class TPDecoderStack:
         for layer in range(built):
             row = []
             for idx, (name, mode, n, k) in enumerate(shape.linears()):
-                t = make_tensor(f"l{layer}.{name}", n, k, shape.planes, seed=layer * 4 + idx)
-                row.append(TPLinear(executor, t, codec, mode, rank, world, group, max_m, act_dtype))
+                if synthetic_shards:
+                    t = make_shard_tensor(f"l{layer}.{name}", n, k, shape.planes, mode, rank, world, seed=layer * 4 + idx)
+                    row.append(TPLinear(executor, t, codec, mode, rank, world, group, max_m, act_dtype, full_shape=(n, k)))
+                else:
+                    t = make_tensor(f"l{layer}.{name}", n, k, shape.planes, seed=layer * 4 + idx)
+                    row.append(TPLinear(executor, t, codec, mode, rank, world, group, max_m, act_dtype))
+                del t
             self.layers.append(row)
 
     def fill_inputs(self, m: int, seed: int = 0) -> None:
