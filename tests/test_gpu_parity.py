@@ -306,6 +306,36 @@ def test_a8_prefill_full_size_config(backend, codec):
     assert r_dec.kernel == 1 and rel_l2(y[:4], y_dec) <= 1e-5
 
 
+def test_a8_prefill_sweep_shape_full_accumulator_check(backend):
+    """Prefill sweep shape (K=2560, N=2560, one plane) at 512 tokens: every int32 group sum and
+    every output against the CPU reference, bf16 outputs."""
+    n, k, planes, m = 2560, 2560, 1, 512
+    prod, orac = uniform_pair(n, k, planes, seed=3)
+    x = make_activations(m, k, seed=2, bf16=True)
+    want_y, want_acc, _ = orc.a8_linear(orac, x)
+    resident = backend.upload_salt_v2(prod, SaltV2Codec.B3)
+    y_bits, acc, receipt = backend.linear_forward_a8(resident, f32_to_bf16_bits(x), m, y_dtype="bf16", dump=True, x_is_bf16=True)
+    assert receipt.kernel == 2
+    assert np.array_equal(acc, want_acc[:, :, :, :planes])
+    assert rel_l2(bf16_bits_to_f32(y_bits), want_y) <= 1e-2
+
+
+@pytest.mark.parametrize("n,k", [(3840, 2560), (13824, 2560), (2560, 6912)], ids=["qkv", "gate_up", "down"])
+def test_a8_decoder_stack_shapes_batch16(backend, n, k):
+    """2B-class decoder linears (one plane) at decode batch 16: sampled rows against the reference."""
+    planes, m = 1, 16
+    prod, _ = uniform_pair(n, k, planes, seed=n % 97)
+    x = make_activations(m, k, seed=6, bf16=True)
+    resident = backend.upload_salt_v2(prod, SaltV2Codec.B3)
+    y, _, _ = backend.linear_forward_a8(resident, x, m)
+    rows = np.r_[0:6, n // 2:n // 2 + 6, n - 6:n]
+    sub = orc.Tensor(len(rows), k, 128, prod.plane_count.reshape(n, -1)[rows].reshape(-1).copy(),
+                     prod.trits.reshape(n, k // 256, 3, 256)[rows].reshape(-1, 3, 256).copy(),
+                     prod.scales.reshape(n, k // 256, 3, -1)[rows].reshape(-1, 3, prod.scales.shape[-1]).copy())
+    want_y, _, _ = orc.a8_linear(sub, x)
+    assert rel_l2(y[:, rows], want_y) <= 1e-5
+
+
 # ------------------------------------------------------------------ trait path (TQ2_0 conformance)
 def conformance_vectors(seed=0xC0FFEE, count=12):
     """generate_vectors (crates/tritium-testkit/src/generate.rs:203-233), TQ2_0 cases only."""
