@@ -209,7 +209,11 @@ def measure_tp(torch, dist, backend, rank: int, world: int, codec, codec_name: s
            "collective": "nccl all_reduce (fp32 sum after O and down; fp32 max of the row absmax before them)" if world > 1 else "none"}
     m_prefill = args.tp_prefill_m
     max_m = max(1, m_prefill)
-    ex = tp.CudaExecutor(backend, flags=0)
+    comm = None
+    if world > 1:
+        # two slots (row absmax, partial outputs) per row-parallel linear, sized for decode batches up to 32
+        comm = tp.PeerComm(backend, rank, world, slot_bytes=32 * shape.hidden * 4, slots=4 * built)
+    ex = tp.CudaExecutor(backend, flags=0, comm=comm)
     t0 = time.perf_counter()
     stack = tp.TPDecoderStack(ex, shape, codec, rank, world, max_m=max_m, distinct_layers=built, synthetic_shards=True)
     out["build_seconds"] = time.perf_counter() - t0
@@ -252,11 +256,19 @@ def measure_tp(torch, dist, backend, rank: int, world: int, codec, codec_name: s
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item()), graph is not None
 
+    def decode_entry(ms, graphed, reduce_kind):
+        full_ms = ms * shape.layers / built
+        return {"ms_per_step_timed_layers": ms, "ms_per_64_layer_step": full_ms, "tokens_per_s": 1e3 / full_ms,
+                "weight_gbs_all_ranks": world * bytes_rank / (ms * 1e-3) / 1e9, "cuda_graph": graphed,
+                "all_reduces_per_timed_step": 4 * built if world > 1 else 0, "reduce": reduce_kind}
+
     ms, graphed = timed(1, not args.no_graph)
-    full_ms = ms * shape.layers / built
-    out["decode_m1"] = {"ms_per_step_timed_layers": ms, "ms_per_64_layer_step": full_ms, "tokens_per_s": 1e3 / full_ms,
-                        "weight_gbs_all_ranks": world * bytes_rank / (ms * 1e-3) / 1e9, "cuda_graph": graphed,
-                        "all_reduces_per_timed_step": 4 * built if world > 1 else 0}
+    out["decode_m1"] = decode_entry(ms, graphed, "one-shot kernel over peer memory" if world > 1 else "none")
+    if world > 1:
+        stack.use_peer_reduce(False)
+        ms, graphed = timed(1, not args.no_graph)
+        out["decode_m1_nccl"] = decode_entry(ms, graphed, "nccl all_reduce")
+        stack.use_peer_reduce(True)
     if m_prefill > 0:
         ms, _ = timed(m_prefill, False)
         full_ms = ms * shape.layers / built
@@ -264,6 +276,8 @@ def measure_tp(torch, dist, backend, rank: int, world: int, codec, codec_name: s
         out[f"prefill_m{m_prefill}"] = {"ms_per_step_timed_layers": ms, "ms_per_64_layer_step": full_ms,
                                         "tokens_per_s": m_prefill * 1e3 / full_ms, "tops_all_ranks": ops / (ms * 1e-3) / 1e12}
     del stack
+    if comm is not None:
+        comm.close()
     return out
 
 

@@ -215,6 +215,26 @@ uint64_t tb_stack_bytes_per_step(const tb_stack* stack, uint32_t m);
 tb_status tb_stack_read_output(tb_stack* stack, uint32_t layer, uint32_t m, void* out_bf16);
 void tb_stack_free(tb_stack* stack);
 
+/* ------------------------------------------------------------------ tensor-parallel reduce over peer memory
+ * No counterpart in the reference (its only collective is the host-staged NCCL gradient
+ * all-reduce, crates/tritium-cuda/src/nccl.rs:530-625).  A communicator owns `slots` buffers of
+ * `slot_bytes` on this rank's GPU; the ranks of one node exchange the 64-byte handles
+ * (tb_comm_export -> all-gather by any means -> tb_comm_connect) and then reduce a slot with one
+ * kernel launch that reads every rank's copy with plain peer loads: the row-parallel kernel
+ * writes its fp32 partial outputs straight into tb_comm_slot(), tb_comm_allreduce_f32 combines
+ * them in rank order into `out` (local device memory).  Waits on peers are bounded; a peer that
+ * does not arrive is reported as TB_TIMEOUT by tb_backend_check.  A slot's content may be
+ * rewritten only after a later reduce on the same communicator has been launched behind it. */
+#define TB_COMM_HANDLE_BYTES 64
+typedef struct tb_comm tb_comm;
+tb_status tb_comm_create(tb_backend* backend, uint32_t world, uint32_t rank, size_t slot_bytes, uint32_t slots,
+                         tb_comm** out);
+tb_status tb_comm_export(const tb_comm* comm, uint8_t* handle_out /* TB_COMM_HANDLE_BYTES */);
+tb_status tb_comm_connect(tb_comm* comm, const uint8_t* all_handles /* world x TB_COMM_HANDLE_BYTES */);
+void* tb_comm_slot(const tb_comm* comm, uint32_t slot);
+tb_status tb_comm_allreduce_f32(tb_comm* comm, uint32_t slot, uint32_t count, int op_max, float* out, void* stream);
+void tb_comm_free(tb_comm* comm);
+
 /* ------------------------------------------------------------------ tensor-parallel sharding (host)
  * Cuts one tensor's resident arenas into the shard for `rank` of `world`:
  * column-parallel (split n; QKV, gate/up) or row-parallel (split k; O, down).  Row-parallel

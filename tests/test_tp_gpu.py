@@ -24,7 +24,7 @@ def rel_l2(got, want):
     return float(np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-30))
 
 
-def rank_main(rank, world, port, codec_value, results):
+def rank_main(rank, world, port, codec_value, use_peer, results):
     import torch.distributed as dist
     from oracle import oracle as orc
     from tritium_b200 import B200Backend, tp
@@ -37,7 +37,8 @@ def rank_main(rank, world, port, codec_value, results):
     try:
         codec = SaltV2Codec(codec_value)
         backend = B200Backend(rank)
-        ex = tp.CudaExecutor(backend)
+        comm = tp.PeerComm(backend, rank, world, slot_bytes=64 * 384 * 4, slots=8) if use_peer else None
+        ex = tp.CudaExecutor(backend, comm=comm)
         stream = torch.cuda.Stream()
         out = {}
         for m, n, k, planes in [(3, 256, 1024, 2), (40, 384, 2048, 1)]:     # decode kernel, tensor-core kernel
@@ -52,7 +53,9 @@ def rank_main(rank, world, port, codec_value, results):
                 row = tp.TPLinear(ex, tensor, codec, "row", rank, world, max_m=m)
                 g = row.geometry
                 row.input_view(m).copy_(torch.from_numpy(np.ascontiguousarray(x[:, g.k_offset:g.k_offset + g.k_valid])).to(torch.bfloat16))
-                y_row = row.forward(m)
+                assert (row.comm is not None) == bool(use_peer)
+                for _ in range(3):          # repeated rounds on the same slots
+                    y_row = row.forward(m)
                 stream.synchronize()
                 backend.check(stream)
             gc = col.geometry
@@ -63,15 +66,16 @@ def rank_main(rank, world, port, codec_value, results):
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("use_peer", [0, 1], ids=["nccl", "peer_memory"])
 @pytest.mark.parametrize("codec", [2, 1], ids=["b3", "d2"])
-def test_two_gpu_tensor_parallel_matches_unsharded_reference(codec):
+def test_two_gpu_tensor_parallel_matches_unsharded_reference(codec, use_peer):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
     world = 2
     with mp.Manager() as manager:
         results = manager.dict()
-        mp.spawn(rank_main, args=(world, free_port(), codec, results), nprocs=world, join=True)
+        mp.spawn(rank_main, args=(world, free_port(), codec, use_peer, results), nprocs=world, join=True)
         assert sorted(results.keys()) == [0, 1]
         for rank in range(world):
             for m, (err_col, err_row, absmax_ok) in results[rank].items():

@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(_HERE, "_lib", "libtritium_b200.so")
 TB_OK, TB_NULL_ARG, TB_SHAPE_MISMATCH, TB_UNSUPPORTED_FORMAT, TB_OUT_OF_MEMORY, TB_INVALID_INPUT, TB_BACKEND, TB_TIMEOUT = range(8)
 TB_CODEC_D2, TB_CODEC_B3, TB_CODEC_S34 = 1, 2, 3
 TB_F32, TB_BF16, TB_I8 = 0, 1, 2
+TB_COMM_HANDLE_BYTES = 64
 TB_FWD_A8, TB_FWD_EXACT, TB_FWD_PDL, TB_FWD_FORCE_DECODE, TB_FWD_FORCE_PREFILL = 1, 2, 4, 8, 16
 
 EXPORTS = [
@@ -21,7 +22,8 @@ EXPORTS = [
     "tb_backend_synchronize", "tb_backend_reserve", "tb_backend_check", "tb_tq2_upload",
     "tb_salt_v2_upload", "tb_salt_v2_upload_package", "tb_weights_info_get", "tb_weights_free",
     "tb_salt_v2_forward_exact", "tb_linear_forward_f32", "tb_linear_forward_a8",
-    "tb_salt_v2_gather_rows", "tb_linear_forward_dev", "tb_act_absmax_dev", "tb_mpgemm", "tb_mpgemm_with_act_quant",
+    "tb_salt_v2_gather_rows", "tb_linear_forward_dev", "tb_act_absmax_dev",
+    "tb_comm_create", "tb_comm_export", "tb_comm_connect", "tb_comm_slot", "tb_comm_allreduce_f32", "tb_comm_free", "tb_mpgemm", "tb_mpgemm_with_act_quant",
     "tb_stack_create", "tb_stack_forward_dev", "tb_stack_bytes_per_step", "tb_stack_read_output", "tb_stack_free",
     "tb_tp_shard_sizes", "tb_tp_shard", "tb_fmt_pack", "tb_fmt_unpack", "tb_fmt_plane_bytes",
     "tb_fmt_resident_sizes", "tb_fmt_resident_build", "tb_fmt_package_write", "tb_fmt_tq2_pack_rows",
@@ -87,6 +89,10 @@ def load(build_if_missing: bool = True) -> C.CDLL:
     L.tb_fmt_plane_bytes.restype = C.c_size_t
     L.tb_stack_bytes_per_step.restype = C.c_uint64
     L.tb_backend_free.restype = None
+    L.tb_comm_free.restype = None
+    L.tb_comm_free.argtypes = [C.c_void_p]
+    L.tb_comm_slot.restype = C.c_void_p
+    L.tb_comm_slot.argtypes = [C.c_void_p, C.c_uint32]
     L.tb_weights_free.restype = None
     L.tb_stack_free.restype = None
     L.tb_backend_free.argtypes = [C.c_void_p]

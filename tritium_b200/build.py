@@ -11,7 +11,7 @@ CSRC = os.path.join(HERE, "csrc")
 OUT_DIR = os.path.join(HERE, "_lib")
 LIB = os.path.join(OUT_DIR, "libtritium_b200.so")
 
-CU_SOURCES = ["tb_api.cu", "kernels_exact.cu", "kernels_decode.cu", "kernels_prefill.cu"]
+CU_SOURCES = ["tb_api.cu", "kernels_exact.cu", "kernels_decode.cu", "kernels_prefill.cu", "kernels_comm.cu"]
 CPP_SOURCES = ["tb_format.cpp"]
 GENCODE = ["-gencode", "arch=compute_100a,code=sm_100a"]
 

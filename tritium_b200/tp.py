@@ -70,9 +70,10 @@ class ShardExecutor:
 class CudaExecutor(ShardExecutor):
     """B200 kernels through the C ABI; every call is asynchronous on the current torch stream."""
 
-    def __init__(self, backend, flags: int = 0):
+    def __init__(self, backend, flags: int = 0, comm=None):
         self.backend = backend
         self.flags = flags
+        self.comm = comm    # PeerComm or None (NCCL only)
 
     def upload(self, codec, group, n, k, payload, scales, plane_map, terminal):
         return self.backend.upload_salt_v2_arenas(codec, group, n, k, payload, scales, plane_map, terminal)
@@ -89,6 +90,67 @@ class CudaExecutor(ShardExecutor):
 
     def linear(self, handle, x, y, act_absmax) -> None:
         self.backend.forward_dev(handle, x, y, a8=True, act_absmax=act_absmax, flags=self.flags)
+
+
+class PeerComm:
+    """Slots of device memory that the ranks of one node map into each other (CUDA IPC) and reduce
+    with one kernel launch (`tb_comm_allreduce_f32`): the small-message all-reduce of decode."""
+
+    def __init__(self, backend, rank: int, world: int, slot_bytes: int, slots: int, group=None):
+        import ctypes as C
+        import torch.distributed as dist
+        from . import _lib
+        from .errors import check
+        self._L, self._check, self.backend = _lib.load(), check, backend
+        self.rank, self.world, self.slots, self.slot_bytes = rank, world, slots, (slot_bytes + 255) // 256 * 256
+        self._next = 0
+        h = C.c_void_p(None)
+        check(self._L.tb_comm_create(backend._h, C.c_uint32(world), C.c_uint32(rank), C.c_size_t(slot_bytes), C.c_uint32(slots), C.byref(h)))
+        self._h = h
+        if world > 1:
+            mine = (C.c_uint8 * _lib.TB_COMM_HANDLE_BYTES)()
+            check(self._L.tb_comm_export(self._h, mine))
+            gathered = [None] * world
+            dist.all_gather_object(gathered, bytes(mine), group=group)
+            blob = (C.c_uint8 * (_lib.TB_COMM_HANDLE_BYTES * world)).from_buffer_copy(b"".join(gathered))
+            check(self._L.tb_comm_connect(self._h, blob))
+            dist.barrier(group=group)
+
+    def take_slot(self) -> int:
+        if self._next >= self.slots:
+            raise RuntimeError("communicator has no free slot left")
+        self._next += 1
+        return self._next - 1
+
+    def slot_tensor(self, slot: int, shape):
+        """fp32 torch view of a slot (zero-copy)."""
+        import torch
+        ptr = self._L.tb_comm_slot(self._h, slot)
+        count = int(np.prod(shape))
+        if not ptr or count * 4 > self.slot_bytes:
+            raise ValueError("slot index or shape out of range")
+
+        class _Raw:
+            __cuda_array_interface__ = {"shape": (count,), "typestr": "<f4", "data": (int(ptr), False), "version": 2}
+        return torch.as_tensor(_Raw(), device=f"cuda:{self.backend.ordinal}").view(*shape)
+
+    def all_reduce(self, slot: int, count: int, out, op_max: bool = False, stream=None) -> None:
+        import ctypes as C
+        import torch
+        s = stream if stream is not None else torch.cuda.current_stream()
+        self._check(self._L.tb_comm_allreduce_f32(self._h, C.c_uint32(slot), C.c_uint32(count), int(op_max),
+                                                  C.c_void_p(out.data_ptr()), C.c_void_p(s.cuda_stream)))
+
+    def close(self) -> None:
+        if self._h:
+            self._L.tb_comm_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 class TPLinear:
@@ -124,6 +186,16 @@ class TPLinear:
         self.x = executor.alloc((max_m, self.geometry.k), act_dtype)
         self.y = executor.alloc((max_m, self.geometry.n), torch.float32)
         self.absmax = executor.alloc((max_m,), torch.float32) if mode == "row" else None
+        # small messages (decode) are reduced over peer memory when the executor carries a
+        # communicator: the kernels write their partials straight into its slots
+        comm = getattr(executor, "comm", None) if mode == "row" and world > 1 else None
+        self.comm, self.peer_m = comm, 0
+        if comm is not None:
+            self.peer_m = min(max_m, comm.slot_bytes // (4 * self.geometry.n))
+            if self.peer_m:
+                self.slot_absmax, self.slot_y = comm.take_slot(), comm.take_slot()
+                self.peer_absmax = comm.slot_tensor(self.slot_absmax, (self.peer_m,))
+                self.peer_y = comm.slot_tensor(self.slot_y, (self.peer_m, self.geometry.n))
 
     @property
     def mode(self) -> str:
@@ -142,6 +214,12 @@ class TPLinear:
             self.executor.linear(self.handle, x, y, None)
             return y
         absmax = self.absmax[:m]
+        if self.comm is not None and m <= self.peer_m:
+            self.executor.row_absmax(x, self.peer_absmax[:m])
+            self.comm.all_reduce(self.slot_absmax, m, absmax, op_max=True)
+            self.executor.linear(self.handle, x, self.peer_y[:m], absmax)
+            self.comm.all_reduce(self.slot_y, m * self.geometry.n, y)
+            return y
         self.executor.row_absmax(x, absmax)
         if self.world > 1:
             dist.all_reduce(absmax, op=dist.ReduceOp.MAX, group=self.group)
@@ -210,6 +288,14 @@ class TPDecoderStack:
                 full = make_activations(m, k_full, seed=seed + li * 4 + idx, bf16=True)
                 part = full[:, g.k_offset:g.k_offset + g.k_valid]
                 lin.input_view(m).copy_(torch.from_numpy(np.ascontiguousarray(part)).to(lin.x.dtype))
+
+    def use_peer_reduce(self, enabled: bool) -> None:
+        """Switches the row-parallel linears between the peer-memory reduce and NCCL."""
+        for row in self.layers:
+            for lin in row:
+                if lin.mode == "row" and getattr(lin, "_comm_built", lin.comm) is not None:
+                    lin._comm_built = getattr(lin, "_comm_built", lin.comm)
+                    lin.comm = lin._comm_built if enabled else None
 
     def forward(self, m: int) -> list:
         """One pass over every layer; returns the outputs of the last layer's four linears."""
