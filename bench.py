@@ -263,7 +263,7 @@ def measure_tp(torch, dist, backend, rank: int, world: int, codec, codec_name: s
                 "all_reduces_per_timed_step": 4 * built if world > 1 else 0, "reduce": reduce_kind}
 
     ms, graphed = timed(1, not args.no_graph)
-    out["decode_m1"] = decode_entry(ms, graphed, "one-shot kernel over peer memory" if world > 1 else "none")
+    out["decode_m1"] = decode_entry(ms, graphed, "inside the prepare and decode kernels, over peer memory" if world > 1 else "none")
     if world > 1:
         stack.use_peer_reduce(False)
         ms, graphed = timed(1, not args.no_graph)

@@ -228,11 +228,21 @@ void tb_stack_free(tb_stack* stack);
 #define TB_COMM_HANDLE_BYTES 64
 typedef struct tb_comm tb_comm;
 tb_status tb_comm_create(tb_backend* backend, uint32_t world, uint32_t rank, size_t slot_bytes, uint32_t slots,
-                         tb_comm** out);
+                         uint32_t counters_per_slot, tb_comm** out);
 tb_status tb_comm_export(const tb_comm* comm, uint8_t* handle_out /* TB_COMM_HANDLE_BYTES */);
 tb_status tb_comm_connect(tb_comm* comm, const uint8_t* all_handles /* world x TB_COMM_HANDLE_BYTES */);
 void* tb_comm_slot(const tb_comm* comm, uint32_t slot);
 tb_status tb_comm_allreduce_f32(tb_comm* comm, uint32_t slot, uint32_t count, int op_max, float* out, void* stream);
+/* Row-parallel int8 forward (1..8 tokens) that finishes the tensor-parallel all-reduce inside its
+ * own kernels: the activation-preparation kernel exchanges the per-token absmax through
+ * `slot_absmax` (so that every shard quantises with the scale of the whole row), the GEMV kernel
+ * writes its fp32 partial rows into `slot_y`, raises one arrival counter per row block on every
+ * peer and, one block later, adds the peers' rows in rank order into `y` (every rank ends with the
+ * full result).  `counters_per_slot` of the communicator must cover max(tokens, row blocks).
+ * The two slots belong to this linear alone. */
+tb_status tb_linear_forward_tp_dev(tb_backend* backend, const tb_weights* weights, tb_comm* comm, uint32_t slot_absmax,
+                                   uint32_t slot_y, const void* x, tb_dtype x_dtype, uint32_t m, void* y, tb_dtype y_dtype,
+                                   void* stream);
 void tb_comm_free(tb_comm* comm);
 
 /* ------------------------------------------------------------------ tensor-parallel sharding (host)

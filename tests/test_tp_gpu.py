@@ -41,7 +41,7 @@ def rank_main(rank, world, port, codec_value, use_peer, results):
         ex = tp.CudaExecutor(backend, comm=comm)
         stream = torch.cuda.Stream()
         out = {}
-        for m, n, k, planes in [(3, 256, 1024, 2), (40, 384, 2048, 1)]:     # decode kernel, tensor-core kernel
+        for m, n, k, planes in [(3, 256, 1024, 2), (7, 200, 1536, 3), (40, 384, 2048, 1)]:   # decode kernel (one and two passes), tensor-core kernel
             tensor = make_tensor("w", n, k, planes, seed=11 + m)
             x = make_activations(m, k, seed=5, bf16=True)
             otensor = orc.Tensor(n, k, 128, tensor.plane_count.copy(), tensor.trits.copy(), tensor.scales.copy())
@@ -54,19 +54,21 @@ def rank_main(rank, world, port, codec_value, use_peer, results):
                 g = row.geometry
                 row.input_view(m).copy_(torch.from_numpy(np.ascontiguousarray(x[:, g.k_offset:g.k_offset + g.k_valid])).to(torch.bfloat16))
                 assert (row.comm is not None) == bool(use_peer)
+                row.fused = use_peer == 2
                 for _ in range(3):          # repeated rounds on the same slots
                     y_row = row.forward(m)
                 stream.synchronize()
                 backend.check(stream)
             gc = col.geometry
-            out[m] = (rel_l2(y_col.cpu().numpy(), want[:, gc.n_offset:gc.n_offset + gc.n]), rel_l2(y_row.cpu().numpy(), want),
-                      bool(np.array_equal(row.absmax[:m].cpu().numpy(), np.abs(x).max(axis=1))))
+            # the in-kernel exchange keeps the row absmax to itself; the output parity covers it
+            absmax_ok = (use_peer == 2 and m <= 8) or bool(np.array_equal(row.absmax[:m].cpu().numpy(), np.abs(x).max(axis=1)))
+            out[m] = (rel_l2(y_col.cpu().numpy(), want[:, gc.n_offset:gc.n_offset + gc.n]), rel_l2(y_row.cpu().numpy(), want), absmax_ok)
         results[rank] = out
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("use_peer", [0, 1], ids=["nccl", "peer_memory"])
+@pytest.mark.parametrize("use_peer", [0, 1, 2], ids=["nccl", "peer_one_shot", "peer_fused_in_kernel"])
 @pytest.mark.parametrize("codec", [2, 1], ids=["b3", "d2"])
 def test_two_gpu_tensor_parallel_matches_unsharded_reference(codec, use_peer):
     if torch.cuda.device_count() < 2:
@@ -80,4 +82,4 @@ def test_two_gpu_tensor_parallel_matches_unsharded_reference(codec, use_peer):
         for rank in range(world):
             for m, (err_col, err_row, absmax_ok) in results[rank].items():
                 assert err_col <= 1e-5 and err_row <= 1e-5, (rank, m, err_col, err_row)
-                assert absmax_ok
+                assert absmax_ok, (rank, m)

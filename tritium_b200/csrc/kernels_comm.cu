@@ -113,21 +113,20 @@ __global__ void __launch_bounds__(256) oneshot_reduce_kernel(const ReduceParams 
 
 struct tb_comm {
   tb_backend* owner = nullptr;
-  uint32_t world = 1, rank = 0, slots = 0;
+  uint32_t world = 1, rank = 0, slots = 0, flag_words = 16;
   size_t slot_bytes = 0, data_bytes = 0, total_bytes = 0;
   uint8_t* base[kMaxWorld] = {};   // base[rank] is the local allocation, the others are IPC mappings
   bool connected = false;
 };
 
 namespace {
-// words per slot in the flag area: [world flags | epoch | done | padding] = 16
-constexpr size_t kFlagWords = 16;
 uint32_t* flag_row(uint8_t* base, const tb_comm* c, uint32_t slot) {
-  return reinterpret_cast<uint32_t*>(base + c->data_bytes) + size_t(slot) * kFlagWords;
+  return reinterpret_cast<uint32_t*>(base + c->data_bytes) + size_t(slot) * c->flag_words;
 }
 }  // namespace
 
-extern "C" tb_status tb_comm_create(tb_backend* b, uint32_t world, uint32_t rank, size_t slot_bytes, uint32_t slots, tb_comm** out) {
+extern "C" tb_status tb_comm_create(tb_backend* b, uint32_t world, uint32_t rank, size_t slot_bytes, uint32_t slots,
+                                    uint32_t counters_per_slot, tb_comm** out) {
   if (!b || !out) return tb_fail(TB_NULL_ARG, "null argument");
   *out = nullptr;
   if (world == 0 || world > kMaxWorld || rank >= world) return tb_fail(TB_INVALID_INPUT, "world must be 1..8 and rank below it");
@@ -138,7 +137,8 @@ extern "C" tb_status tb_comm_create(tb_backend* b, uint32_t world, uint32_t rank
   c->owner = b; c->world = world; c->rank = rank; c->slots = slots;
   c->slot_bytes = (slot_bytes + 255) / 256 * 256;
   c->data_bytes = c->slot_bytes * slots;
-  c->total_bytes = c->data_bytes + size_t(slots) * kFlagWords * 4;
+  c->flag_words = (kCommCounters + counters_per_slot + 15) / 16 * 16;
+  c->total_bytes = c->data_bytes + size_t(slots) * c->flag_words * 4;
   void* mem = nullptr;
   cudaError_t err = cudaMalloc(&mem, c->total_bytes);
   if (err != cudaSuccess) { delete c; return tb_cuda_fail(err, "allocate communicator memory"); }
@@ -206,6 +206,18 @@ extern "C" tb_status tb_comm_allreduce_f32(tb_comm* c, uint32_t slot, uint32_t c
   if (err != cudaSuccess) return tb_cuda_fail(err, "launch one-shot reduce");
   return TB_OK;
 }
+
+bool tb_comm_view(const tb_comm* c, uint32_t slot, TbCommView* out) {
+  if (!c || !c->connected || slot >= c->slots) return false;
+  for (uint32_t r = 0; r < c->world; ++r) {
+    out->data[r] = reinterpret_cast<float*>(c->base[r] + size_t(slot) * c->slot_bytes);
+    out->flags[r] = flag_row(c->base[r], c, slot);
+  }
+  out->world = c->world; out->rank = c->rank; out->counters = c->flag_words - kCommCounters;
+  return true;
+}
+size_t tb_comm_slot_bytes(const tb_comm* c) { return c ? c->slot_bytes : 0; }
+const tb_backend* tb_comm_owner(const tb_comm* c) { return c ? c->owner : nullptr; }
 
 extern "C" void tb_comm_free(tb_comm* c) {
   if (!c) return;

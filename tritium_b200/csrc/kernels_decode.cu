@@ -51,7 +51,32 @@ struct DecodeParams {
   uint32_t pdl, wait_tables, ctas_per_sm;
   // shared memory offsets (bytes)
   uint32_t off_ring, off_scale_ring, off_z, off_cinit, off_part, off_actscale, off_zero;
+  TbCommView comm;   // world > 1: write fp32 partial rows into the slot and finish the all-reduce here
 };
+
+// ---- peer-memory helpers (tensor-parallel row shards)
+constexpr long long kPeerWaitCycles = 4000000000ll;   // about two seconds of SM clocks
+__device__ __forceinline__ void peer_signal(uint32_t* counter) {
+  asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(counter) : "memory");
+}
+__device__ __forceinline__ uint32_t peer_poll(const uint32_t* counter) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+  return v;
+}
+__device__ __forceinline__ float peer_load(const float* p) {
+  float v;
+  asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  return v;
+}
+// Waits (bounded) until `counter` has received `target` arrivals since the slot was created.
+__device__ __forceinline__ bool peer_wait(const uint32_t* counter, uint32_t target) {
+  const long long t0 = clock64();
+  for (uint32_t i = 0;; ++i) {
+    if (int32_t(peer_poll(counter) - target) >= 0) return true;
+    if ((i & 255u) == 255u && clock64() - t0 > kPeerWaitCycles) return false;
+  }
+}
 
 template <int CODEC> struct Traits;
 // kMmas: MMAs per (16 row-planes x tile-plane) when the two scale groups use separate
@@ -227,8 +252,9 @@ __device__ __forceinline__ uint32_t z_quad(const int8_t* xq_tile, const Slot<COD
 // int[m][tpr][2] (padded to 16) | token scales float[m] (padded to 16).
 struct PrepareParams {
   const void* x; const float* act_scale_in; const float* act_absmax_in;
-  uint8_t* tables;
+  uint8_t* tables; uint32_t* status;
   uint32_t m, k, tpr, x_dtype, off_cinit, off_actscale, pdl;
+  TbCommView comm;   // world > 1: the per-token absmax is the maximum over the ranks' slices
 };
 
 __device__ __forceinline__ float load_act(const void* x, uint32_t dtype, size_t i) {
@@ -247,6 +273,7 @@ __global__ void __launch_bounds__(256) prepare_kernel(const PrepareParams p) {
   const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const uint32_t j = blockIdx.x, t = blockIdx.y, ncol = (DUAL ? 4 : 2) * p.m;
   float scale_out;
+  uint32_t comm_seq = 0;   // thread 0 only
   if (p.x_dtype == TB_I8) {
     xq[tid] = static_cast<const int8_t*>(p.x)[size_t(t) * p.k + j * 256 + tid];
     scale_out = p.act_scale_in[t];
@@ -262,6 +289,38 @@ __global__ void __launch_bounds__(256) prepare_kernel(const PrepareParams p) {
       __syncthreads();
       gamma = 0.f;
       for (int w2 = 0; w2 < 8; ++w2) gamma = fmaxf(gamma, red[w2]);
+    }
+    if (p.comm.world > 1) {
+      // every rank holds a slice of the row: publish this slice's absmax (tile column 0 does it),
+      // wait for the peers' arrivals, take the maximum
+      __shared__ float gamma_all;
+      __syncthreads();
+      if (tid == 0) {
+        uint32_t* mine = p.comm.flags[p.comm.rank];
+        comm_seq = *reinterpret_cast<volatile uint32_t*>(mine + kCommFusedEpoch) + 1u;
+        if (j == 0) {
+          p.comm.data[p.comm.rank][t] = gamma;
+          __threadfence_system();
+          // a launch of fewer than four tokens still advances all four token counters, so that
+          // "arrivals = peers x rounds" holds for every counter whatever the token counts were
+          for (uint32_t r = 0; r < p.comm.world; ++r)
+            if (r != p.comm.rank) {
+              peer_signal(p.comm.flags[r] + kCommCounters + t);
+              if (t == 0)
+                for (uint32_t unused = p.m; unused < 4; ++unused) peer_signal(p.comm.flags[r] + kCommCounters + unused);
+            }
+        }
+        float gmax = gamma;
+        if (peer_wait(mine + kCommCounters + t, (p.comm.world - 1) * comm_seq)) {
+          for (uint32_t r = 0; r < p.comm.world; ++r)
+            if (r != p.comm.rank) gmax = fmaxf(gmax, peer_load(p.comm.data[r] + t));
+        } else if (atomicOr(&p.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) {
+          p.status[TBS_INFO0] = t; p.status[TBS_INFO1] = 500;
+        }
+        gamma_all = gmax;
+      }
+      __syncthreads();
+      gamma = gamma_all;
     }
     const float scale_q = gamma > 0.f ? __fdiv_rn(127.0f, gamma) : 0.f;
     scale_out = __fdiv_rn(gamma, 127.0f);
@@ -297,6 +356,15 @@ __global__ void __launch_bounds__(256) prepare_kernel(const PrepareParams p) {
   }
   if (j == 0 && tid == 0) reinterpret_cast<float*>(p.tables + p.off_actscale)[t] = scale_out;
   if (j == 0 && t == 0 && tid < 4) reinterpret_cast<uint32_t*>(p.tables + p.off_actscale + 16)[tid] = 0u;
+  if (p.comm.world > 1 && tid == 0 && comm_seq) {
+    // the last CTA of the launch closes the round
+    uint32_t* mine = p.comm.flags[p.comm.rank];
+    __threadfence();
+    if (atomicAdd(mine + kCommFusedDone, 1u) == gridDim.x * gridDim.y - 1) {
+      mine[kCommFusedDone] = 0;
+      *reinterpret_cast<volatile uint32_t*>(mine + kCommFusedEpoch) = comm_seq;
+    }
+  }
 }
 
 // ---------------------------------------------------------------- the kernel
@@ -308,7 +376,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
   constexpr uint32_t ncol = (DUAL ? 4 : 2) * M;   // MMA columns in use
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ uint64_t full_bar[kMaxStages], empty_bar[kMaxStages], table_bar;
-  __shared__ uint32_t abort_flag;
+  __shared__ uint32_t abort_flag, comm_ok;
   __shared__ TbLayerDesc layer_desc[kMaxGroupLayers];
 
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -413,6 +481,37 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
   const uint32_t bcol = g % ncol;
   constexpr uint32_t zstep = ncol * 4;
   const uint32_t groups_per_row = p.tpr * 2;
+
+  // Tensor-parallel row shard: the block's fp32 partial rows go to the peer-visible slot, one
+  // arrival counter per row block is raised on every peer, and ONE BLOCK LATER (the peers have had a
+  // block's time to catch up) the block's rows are summed over the ranks in rank order.
+  const bool fused = p.comm.world > 1;
+  const uint32_t comm_seq = fused ? *reinterpret_cast<volatile uint32_t*>(p.comm.flags[p.comm.rank] + kCommFusedEpoch) + 1u : 0u;
+  auto reduce_rows = [&](uint32_t blk_done) -> bool {
+    if (ctid == 0) {
+      const bool arrived = peer_wait(p.comm.flags[p.comm.rank] + kCommCounters + blk_done, (p.comm.world - 1) * comm_seq);
+      if (!arrived) {
+        abort_flag = 1;
+        if (atomicOr(&p.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) { p.status[TBS_INFO0] = blk_done; p.status[TBS_INFO1] = 501; }
+      }
+      comm_ok = arrived ? 1u : 0u;
+    }
+    consumer_sync();
+    if (!comm_ok) return false;
+    const uint32_t r0 = blk_done * p.rows_per_stage;
+    for (uint32_t e = ctid; e < p.rows_per_stage * M; e += kCT) {
+      const uint32_t t = e / p.rows_per_stage, r = e - t * p.rows_per_stage;
+      if (r0 + r >= p.n) continue;
+      const size_t at = size_t(t) * p.n + r0 + r;
+      float sum = p.comm.rank == 0 ? p.comm.data[0][at] : peer_load(p.comm.data[0] + at);
+      for (uint32_t q = 1; q < p.comm.world; ++q)
+        sum = __fadd_rn(sum, q == p.comm.rank ? p.comm.data[q][at] : peer_load(p.comm.data[q] + at));
+      const size_t idx = size_t(t) * p.y_row_stride + r0 + r;
+      if (p.y_dtype == TB_F32) static_cast<float*>(p.y)[idx] = sum;
+      else static_cast<__nv_bfloat16*>(p.y)[idx] = __float2bfloat16_rn(sum);
+    }
+    return true;
+  };
 
   for (uint32_t it = 0; it < my_blocks; ++it) {
     const uint32_t s = it % p.stages;
@@ -581,9 +680,34 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
           sum = __fadd_rn(sum, stage_part[w2 * part_stride + (r * PLANES + q) * M + t]);
       float out = __fmul_rn(sum, act_scale[t]);
       if (p.row_scale) out = __fmul_rn(out, p.row_scale[row0 + r]);
+      if (fused) {
+        // this rank's partial row, peer-visible; the sum over ranks follows one block later
+        p.comm.data[p.comm.rank][size_t(t) * p.n + row0 + r] = out;
+        __threadfence_system();
+        continue;
+      }
       const size_t idx = size_t(layer) * p.y_layer_stride + size_t(t) * p.y_row_stride + row0 + r;
       if (p.y_dtype == TB_F32) static_cast<float*>(p.y)[idx] = out;
       else static_cast<__nv_bfloat16*>(p.y)[idx] = __float2bfloat16_rn(out);
+    }
+    if (fused) {
+      consumer_sync();   // every partial of this block is written and fenced
+      if (ctid == 0)
+        for (uint32_t r = 0; r < p.comm.world; ++r)
+          if (r != p.comm.rank) peer_signal(p.comm.flags[r] + kCommCounters + blk);
+      if (it > 0 && !reduce_rows(blockIdx.x + (it - 1) * gridDim.x)) return;
+    }
+  }
+  if (fused) {
+    if (my_blocks > 0 && !reduce_rows(blockIdx.x + (my_blocks - 1) * gridDim.x)) return;
+    if (ctid == 0) {
+      // the last CTA of the launch closes the round
+      uint32_t* mine = p.comm.flags[p.comm.rank];
+      __threadfence();
+      if (atomicAdd(mine + kCommFusedDone, 1u) == gridDim.x - 1) {
+        mine[kCommFusedDone] = 0;
+        *reinterpret_cast<volatile uint32_t*>(mine + kCommFusedEpoch) = comm_seq;
+      }
     }
   }
 }
@@ -680,6 +804,11 @@ cudaError_t tb_launch_prepare(const DecodeArgs& a, cudaStream_t stream) {
   pp.tables = static_cast<uint8_t*>(a.scratch);
   pp.m = a.m; pp.k = uint32_t(w->k); pp.tpr = uint32_t(w->k / 256); pp.x_dtype = uint32_t(a.x_dtype);
   pp.off_cinit = tl.off_cinit; pp.off_actscale = tl.off_actscale; pp.pdl = a.pdl ? 1u : 0u;
+  pp.status = a.status;
+  if (a.comm_absmax) {
+    if (a.comm_absmax->counters < a.m) return cudaErrorInvalidValue;
+    pp.comm = *a.comm_absmax;
+  }
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(pp.tpr, a.m);
   cfg.blockDim = dim3(256);
@@ -723,6 +852,11 @@ cudaError_t tb_launch_decode(const DecodeArgs& a, int sm_count, int max_smem, cu
   p.dump_token_offset = a.dump_token_offset; p.dump_tokens_total = a.dump_tokens_total;
   p.pdl = a.pdl ? 1u : 0u;
   p.wait_tables = a.tables_shared ? 0u : 1u;
+  if (a.comm_y) {
+    // one arrival counter per row block; single layer, fp32 partials of [m, n]
+    if (a.layers || a.comm_y->counters < p.blocks) return cudaErrorInvalidValue;
+    p.comm = *a.comm_y;
+  }
   DecodeKernel kernel = w->codec == tbf::kB3 ? pick_planes<tbf::kB3>(w->uniform_planes, a.m) : pick_planes<tbf::kD2>(w->uniform_planes, a.m);
   if (a.layers && a.layer_count > uint32_t(kMaxGroupLayers)) return cudaErrorInvalidValue;
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));

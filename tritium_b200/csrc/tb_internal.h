@@ -86,6 +86,17 @@ cudaError_t tb_launch_gather_rows(const tb_weights* w, const uint32_t* rows, uin
 cudaError_t tb_launch_row_absmax(const void* x, tb_dtype dtype, uint32_t m, uint32_t k, float* out, cudaStream_t stream);
 cudaError_t tb_launch_check_finite(const float* x, uint64_t count, uint32_t* status, cudaStream_t stream);
 
+// One slot of a peer-memory communicator as the kernels see it: every rank's copy of the slot and of
+// its flag words (this rank's own pointers at index `rank`).  world <= 1 means "no peers".
+// Flag words of a slot: [0,8) one-shot flags, 8 epoch, 9 block counter (one-shot reduce);
+// 10 epoch, 11 block counter (fused kernels); 16.. arrival counters, one per token or row block.
+constexpr uint32_t kCommMaxWorld = 8, kCommFusedEpoch = 10, kCommFusedDone = 11, kCommCounters = 16;
+struct TbCommView {
+  float* data[kCommMaxWorld];
+  uint32_t* flags[kCommMaxWorld];
+  uint32_t world, rank, counters;   // counters: arrival counters the slot's flag area holds
+};
+
 // Device-resident descriptor of one layer of a grouped launch.
 struct TbLayerDesc { const uint8_t* payload; const uint16_t* scales; };
 
@@ -103,6 +114,10 @@ struct DecodeArgs {
   // grouped launch: `layer_count` layers shaped like `w` read the same activations; outputs are
   // written as [layer][m][n] with `y_layer_stride` elements between layers
   const TbLayerDesc* layers; uint32_t layer_count; uint32_t y_layer_stride;
+  // tensor-parallel row shard (single layer): the prepare kernel exchanges the per-token absmax
+  // through `comm_absmax`, the decode kernel writes fp32 partial rows into `comm_y` and finishes
+  // the all-reduce itself.  Both null = no peers.
+  const TbCommView* comm_absmax; const TbCommView* comm_y;
 };
 cudaError_t tb_launch_prepare(const DecodeArgs& a, cudaStream_t stream);
 size_t tb_decode_scratch_bytes(const tb_weights* w, uint32_t m);
@@ -124,3 +139,9 @@ struct PrefillArgs {
 bool tb_prefill_supported(const tb_weights* w, uint32_t m);
 size_t tb_prefill_scratch_bytes(const tb_weights* w, uint32_t m);
 cudaError_t tb_launch_prefill(const PrefillArgs& a, int sm_count, cudaStream_t stream);
+
+// peer-memory communicator (kernels_comm.cu)
+struct tb_comm;
+bool tb_comm_view(const tb_comm* c, uint32_t slot, TbCommView* out);
+size_t tb_comm_slot_bytes(const tb_comm* c);
+const tb_backend* tb_comm_owner(const tb_comm* c);

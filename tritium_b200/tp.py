@@ -96,7 +96,7 @@ class PeerComm:
     """Slots of device memory that the ranks of one node map into each other (CUDA IPC) and reduce
     with one kernel launch (`tb_comm_allreduce_f32`): the small-message all-reduce of decode."""
 
-    def __init__(self, backend, rank: int, world: int, slot_bytes: int, slots: int, group=None):
+    def __init__(self, backend, rank: int, world: int, slot_bytes: int, slots: int, group=None, counters_per_slot: int = 1024):
         import ctypes as C
         import torch.distributed as dist
         from . import _lib
@@ -105,7 +105,8 @@ class PeerComm:
         self.rank, self.world, self.slots, self.slot_bytes = rank, world, slots, (slot_bytes + 255) // 256 * 256
         self._next = 0
         h = C.c_void_p(None)
-        check(self._L.tb_comm_create(backend._h, C.c_uint32(world), C.c_uint32(rank), C.c_size_t(slot_bytes), C.c_uint32(slots), C.byref(h)))
+        check(self._L.tb_comm_create(backend._h, C.c_uint32(world), C.c_uint32(rank), C.c_size_t(slot_bytes), C.c_uint32(slots),
+                                     C.c_uint32(counters_per_slot), C.byref(h)))
         self._h = h
         if world > 1:
             mine = (C.c_uint8 * _lib.TB_COMM_HANDLE_BYTES)()
@@ -140,6 +141,18 @@ class PeerComm:
         s = stream if stream is not None else torch.cuda.current_stream()
         self._check(self._L.tb_comm_allreduce_f32(self._h, C.c_uint32(slot), C.c_uint32(count), int(op_max),
                                                   C.c_void_p(out.data_ptr()), C.c_void_p(s.cuda_stream)))
+
+    def linear_fused(self, handle, slot_absmax: int, slot_y: int, x, y, stream=None) -> None:
+        """Row-parallel forward of up to 8 tokens whose kernels exchange the absmax and finish the
+        all-reduce themselves (`tb_linear_forward_tp_dev`)."""
+        import ctypes as C
+        import torch
+        from . import _lib
+        dt = {torch.float32: _lib.TB_F32, torch.bfloat16: _lib.TB_BF16}
+        s = stream if stream is not None else torch.cuda.current_stream()
+        self._check(self._L.tb_linear_forward_tp_dev(self.backend._h, handle._h, self._h, C.c_uint32(slot_absmax), C.c_uint32(slot_y),
+                                                     C.c_void_p(x.data_ptr()), dt[x.dtype], C.c_uint32(x.shape[0]),
+                                                     C.c_void_p(y.data_ptr()), dt[y.dtype], C.c_void_p(s.cuda_stream)))
 
     def close(self) -> None:
         if self._h:
@@ -189,7 +202,7 @@ class TPLinear:
         # small messages (decode) are reduced over peer memory when the executor carries a
         # communicator: the kernels write their partials straight into its slots
         comm = getattr(executor, "comm", None) if mode == "row" and world > 1 else None
-        self.comm, self.peer_m = comm, 0
+        self.comm, self.peer_m, self.fused = comm, 0, True
         if comm is not None:
             self.peer_m = min(max_m, comm.slot_bytes // (4 * self.geometry.n))
             if self.peer_m:
@@ -214,6 +227,9 @@ class TPLinear:
             self.executor.linear(self.handle, x, y, None)
             return y
         absmax = self.absmax[:m]
+        if self.comm is not None and m <= min(self.peer_m, 8) and self.fused:
+            self.comm.linear_fused(self.handle, self.slot_absmax, self.slot_y, x, y)
+            return y
         if self.comm is not None and m <= self.peer_m:
             self.executor.row_absmax(x, self.peer_absmax[:m])
             self.comm.all_reduce(self.slot_absmax, m, absmax, op_max=True)
