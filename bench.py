@@ -213,7 +213,7 @@ def measure_tp(torch, dist, backend, rank: int, world: int, codec, codec_name: s
     if world > 1:
         # two slots (row absmax, partial outputs) per row-parallel linear, sized for decode batches up to 32
         comm = tp.PeerComm(backend, rank, world, slot_bytes=32 * shape.hidden * 4, slots=4 * built)
-    ex = tp.CudaExecutor(backend, flags=0, comm=comm)
+    ex = tp.CudaExecutor(backend, flags=0 if args.no_pdl else _lib.TB_FWD_PDL, comm=comm)
     t0 = time.perf_counter()
     stack = tp.TPDecoderStack(ex, shape, codec, rank, world, max_m=max_m, distinct_layers=built, synthetic_shards=True)
     out["build_seconds"] = time.perf_counter() - t0
@@ -265,10 +265,14 @@ def measure_tp(torch, dist, backend, rank: int, world: int, codec, codec_name: s
     ms, graphed = timed(1, not args.no_graph)
     out["decode_m1"] = decode_entry(ms, graphed, "inside the prepare and decode kernels, over peer memory" if world > 1 else "none")
     if world > 1:
+        stack.use_fused_reduce(False)
+        ms, graphed = timed(1, not args.no_graph)
+        out["decode_m1_one_shot"] = decode_entry(ms, graphed, "one-shot reduce kernels over peer memory")
         stack.use_peer_reduce(False)
         ms, graphed = timed(1, not args.no_graph)
         out["decode_m1_nccl"] = decode_entry(ms, graphed, "nccl all_reduce")
         stack.use_peer_reduce(True)
+        stack.use_fused_reduce(True)
     if m_prefill > 0:
         ms, _ = timed(m_prefill, False)
         full_ms = ms * shape.layers / built

@@ -482,37 +482,10 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
   constexpr uint32_t zstep = ncol * 4;
   const uint32_t groups_per_row = p.tpr * 2;
 
-  // Tensor-parallel row shard: the block's fp32 partial rows go to the peer-visible slot, one
-  // arrival counter per row block is raised on every peer, and ONE BLOCK LATER (the peers have had a
-  // block's time to catch up) the block's rows are summed over the ranks in rank order.
+  // Tensor-parallel row shard: the fp32 partial rows go to the peer-visible slot and the
+  // all-reduce is finished at the end of this kernel.
   const bool fused = p.comm.world > 1;
   const uint32_t comm_seq = fused ? *reinterpret_cast<volatile uint32_t*>(p.comm.flags[p.comm.rank] + kCommFusedEpoch) + 1u : 0u;
-  auto reduce_rows = [&](uint32_t blk_done) -> bool {
-    if (ctid == 0) {
-      const bool arrived = peer_wait(p.comm.flags[p.comm.rank] + kCommCounters + blk_done, (p.comm.world - 1) * comm_seq);
-      if (!arrived) {
-        abort_flag = 1;
-        if (atomicOr(&p.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) { p.status[TBS_INFO0] = blk_done; p.status[TBS_INFO1] = 501; }
-      }
-      comm_ok = arrived ? 1u : 0u;
-    }
-    consumer_sync();
-    if (!comm_ok) return false;
-    const uint32_t r0 = blk_done * p.rows_per_stage;
-    for (uint32_t e = ctid; e < p.rows_per_stage * M; e += kCT) {
-      const uint32_t t = e / p.rows_per_stage, r = e - t * p.rows_per_stage;
-      if (r0 + r >= p.n) continue;
-      const size_t at = size_t(t) * p.n + r0 + r;
-      float sum = p.comm.rank == 0 ? p.comm.data[0][at] : peer_load(p.comm.data[0] + at);
-      for (uint32_t q = 1; q < p.comm.world; ++q)
-        sum = __fadd_rn(sum, q == p.comm.rank ? p.comm.data[q][at] : peer_load(p.comm.data[q] + at));
-      const size_t idx = size_t(t) * p.y_row_stride + r0 + r;
-      if (p.y_dtype == TB_F32) static_cast<float*>(p.y)[idx] = sum;
-      else static_cast<__nv_bfloat16*>(p.y)[idx] = __float2bfloat16_rn(sum);
-    }
-    return true;
-  };
-
   for (uint32_t it = 0; it < my_blocks; ++it) {
     const uint32_t s = it % p.stages;
     float* my_part = part + ((it & 1) * kConsumerWarps + warp) * part_stride;
@@ -683,23 +656,47 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
       if (fused) {
         // this rank's partial row, peer-visible; the sum over ranks follows one block later
         p.comm.data[p.comm.rank][size_t(t) * p.n + row0 + r] = out;
-        __threadfence_system();
         continue;
       }
       const size_t idx = size_t(layer) * p.y_layer_stride + size_t(t) * p.y_row_stride + row0 + r;
       if (p.y_dtype == TB_F32) static_cast<float*>(p.y)[idx] = out;
       else static_cast<__nv_bfloat16*>(p.y)[idx] = __float2bfloat16_rn(out);
     }
-    if (fused) {
-      consumer_sync();   // every partial of this block is written and fenced
-      if (ctid == 0)
-        for (uint32_t r = 0; r < p.comm.world; ++r)
-          if (r != p.comm.rank) peer_signal(p.comm.flags[r] + kCommCounters + blk);
-      if (it > 0 && !reduce_rows(blockIdx.x + (it - 1) * gridDim.x)) return;
-    }
   }
   if (fused) {
-    if (my_blocks > 0 && !reduce_rows(blockIdx.x + (my_blocks - 1) * gridDim.x)) return;
+    // Every rank's CTA number b walks the same row blocks.  Once all of this CTA's partial rows are
+    // written, ONE arrival is raised on every peer's counter b; when the peers' arrivals are in,
+    // the CTA's rows are summed over the ranks in rank order (one NVLink round trip per kernel).
+    consumer_sync();
+    if (ctid == 0) {
+      // the barrier orders the other threads' stores before this fence; the fence and the release
+      // additions publish them to the peers
+      __threadfence_system();
+      for (uint32_t r = 0; r < p.comm.world; ++r)
+        if (r != p.comm.rank) peer_signal(p.comm.flags[r] + kCommCounters + blockIdx.x);
+      const bool arrived = peer_wait(p.comm.flags[p.comm.rank] + kCommCounters + blockIdx.x, (p.comm.world - 1) * comm_seq);
+      if (!arrived) {
+        abort_flag = 1;
+        if (atomicOr(&p.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) { p.status[TBS_INFO0] = blockIdx.x; p.status[TBS_INFO1] = 501; }
+      }
+      comm_ok = arrived ? 1u : 0u;
+    }
+    consumer_sync();
+    if (!comm_ok) return;
+    const uint32_t per_block = p.rows_per_stage * M;
+    for (uint32_t e = ctid; e < my_blocks * per_block; e += kCT) {
+      const uint32_t it = e / per_block, rem = e - it * per_block;
+      const uint32_t t = rem / p.rows_per_stage, r = rem - t * p.rows_per_stage;
+      const uint32_t row = (blockIdx.x + it * gridDim.x) * p.rows_per_stage + r;
+      if (row >= p.n) continue;
+      const size_t at = size_t(t) * p.n + row;
+      float sum = p.comm.rank == 0 ? p.comm.data[0][at] : peer_load(p.comm.data[0] + at);
+      for (uint32_t q = 1; q < p.comm.world; ++q)
+        sum = __fadd_rn(sum, q == p.comm.rank ? p.comm.data[q][at] : peer_load(p.comm.data[q] + at));
+      const size_t idx = size_t(t) * p.y_row_stride + row;
+      if (p.y_dtype == TB_F32) static_cast<float*>(p.y)[idx] = sum;
+      else static_cast<__nv_bfloat16*>(p.y)[idx] = __float2bfloat16_rn(sum);
+    }
     if (ctid == 0) {
       // the last CTA of the launch closes the round
       uint32_t* mine = p.comm.flags[p.comm.rank];
@@ -853,8 +850,8 @@ cudaError_t tb_launch_decode(const DecodeArgs& a, int sm_count, int max_smem, cu
   p.pdl = a.pdl ? 1u : 0u;
   p.wait_tables = a.tables_shared ? 0u : 1u;
   if (a.comm_y) {
-    // one arrival counter per row block; single layer, fp32 partials of [m, n]
-    if (a.layers || a.comm_y->counters < p.blocks) return cudaErrorInvalidValue;
+    // one arrival counter per CTA; single layer, fp32 partials of [m, n]
+    if (a.layers || a.comm_y->counters < uint32_t(sm_count)) return cudaErrorInvalidValue;
     p.comm = *a.comm_y;
   }
   DecodeKernel kernel = w->codec == tbf::kB3 ? pick_planes<tbf::kB3>(w->uniform_planes, a.m) : pick_planes<tbf::kD2>(w->uniform_planes, a.m);

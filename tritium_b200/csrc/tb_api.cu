@@ -436,9 +436,9 @@ extern "C" tb_status tb_linear_forward_tp_dev(tb_backend* b, const tb_weights* w
   if (!tb_comm_view(comm, slot_absmax, &va) || !tb_comm_view(comm, slot_y, &vy))
     return tb_fail(TB_INVALID_INPUT, "communicator is not connected or a slot index is out of range");
   if (size_t(m) * w->n * 4 > tb_comm_slot_bytes(comm)) return tb_fail(TB_INVALID_INPUT, "the output slot is smaller than m x n fp32 values");
-  if (vy.counters < w->plan.blocks || va.counters < 4)
-    return tb_fail(TB_INVALID_INPUT, "the communicator holds " + std::to_string(vy.counters) + " arrival counters per slot, this tensor needs " +
-                                         std::to_string(w->plan.blocks));
+  if (vy.counters < uint32_t(b->prop.multiProcessorCount) || va.counters < 4)
+    return tb_fail(TB_INVALID_INPUT, "the communicator holds " + std::to_string(vy.counters) + " arrival counters per slot, one per SM (" +
+                                         std::to_string(b->prop.multiProcessorCount) + ") is needed");
   if (tb_status s = use_device(b)) return s;
   cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : b->stream;
   for (uint32_t m0 = 0; m0 < m; m0 += 4) {

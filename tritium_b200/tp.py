@@ -313,6 +313,12 @@ class TPDecoderStack:
                     lin._comm_built = getattr(lin, "_comm_built", lin.comm)
                     lin.comm = lin._comm_built if enabled else None
 
+    def use_fused_reduce(self, enabled: bool) -> None:
+        """Row-parallel decode: all-reduce inside the prepare/decode kernels, or separate one-shot kernels."""
+        for row in self.layers:
+            for lin in row:
+                lin.fused = enabled
+
     def forward(self, m: int) -> list:
         """One pass over every layer; returns the outputs of the last layer's four linears."""
         out = []
