@@ -42,6 +42,8 @@ constexpr int kEpilogueWarps = 16, kExpandWarps = 4;   // epilogue: two column p
 constexpr int kFirstEpilogueWarp = 4, kFirstExpandWarp = kFirstEpilogueWarp + kEpilogueWarps;
 constexpr int kThreads = 32 * (kFirstExpandWarp + kExpandWarps);   // warps: 0 TMA, 1-2 MMA issue (1 owns TMEM), 3 idle, then epilogue, then expanders
 constexpr uint32_t kSpin = 1u << 22;
+constexpr uint32_t kBarFull = 1, kBarEmpty = 3;                 // named barriers kBarFull + half, kBarEmpty + half
+constexpr uint32_t kHandoffThreads = 32 + 32 * kEpilogueWarps / 2;   // one MMA warp + the epilogue warps of its half
 constexpr long long kWaitCycles = 2000000000ll;
 constexpr uint32_t kMagicBits = 0x4B400000u;   // float 12582912 = 2^23 + 2^22
 constexpr uint32_t kTileABytes = kRows * 128;
@@ -68,25 +70,33 @@ __device__ __forceinline__ bool mbar_try(uint64_t* b, uint32_t parity) {
                : "=r"(ok) : "r"(saddr(b)), "r"(parity) : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after kWaitCycles SM clocks (about a second) or when another role has
-// raised the abort flag.  `backoff_ns` > 0 sleeps between polls: roles that run ahead of the
-// pipeline (copy producer, expanders) must not take issue slots from the warps that bound it.
-__device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, volatile uint32_t* abort_flag, uint32_t backoff_ns = 0,
-                                          uint32_t expected_ns = 0) {
-  if (mbar_try(b, parity)) return true;
-  // a wait that is known to take a while (the MMA that has just been started, a whole drain)
-  // sleeps through most of it instead of polling
-  if (expected_ns) __nanosleep(expected_ns);
+// Bounded wait.  After kWaitCycles SM clocks (about a second) it records TBF_WAIT_TIMEOUT and raises
+// the CTA's abort flag; from then on NO wait in this CTA blocks any more: every role runs its
+// loops to the end on whatever data is there (the host discards the result), so that all
+// barrier arrivals still happen and the kernel ends.  `backoff_ns` > 0 sleeps between polls:
+// roles that run ahead of the pipeline (copy producer, expanders) must not take issue slots from
+// the warps that bound it.
+struct WaitCtx { volatile uint32_t* abort_flag; uint32_t* status; };
+__device__ __forceinline__ void mbar_wait(uint64_t* b, uint32_t parity, const WaitCtx& ctx, uint32_t where, uint32_t backoff_ns = 0) {
+  if (mbar_try(b, parity) || *ctx.abort_flag) return;
   const long long t0 = clock64();
   for (uint32_t i = 0;; ++i) {
-    if (mbar_try(b, parity)) return true;
     if (backoff_ns) __nanosleep(backoff_ns);
+    if (mbar_try(b, parity)) return;
     if ((i & 63u) == 63u) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitCycles) return false;
+      if (*ctx.abort_flag) return;
+      if (clock64() - t0 > kWaitCycles) {
+        *ctx.abort_flag = 1;
+        if (atomicOr(&ctx.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) { ctx.status[TBS_INFO0] = parity; ctx.status[TBS_INFO1] = where; }
+        return;
+      }
     }
   }
 }
+// Named barriers hand an accumulator half back and forth between its MMA warp and its epilogue
+// warps without polling: every participant makes the same number of calls whatever happens.
+__device__ __forceinline__ void named_sync(uint32_t id, uint32_t count) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory"); }
+__device__ __forceinline__ void named_arrive(uint32_t id, uint32_t count) { asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory"); }
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
   uint32_t r; asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel)); return r;
 }
@@ -307,7 +317,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
   uint8_t* tile_a = smem;                                       // kStagesA * 16 KB
   uint8_t* tile_b = tile_a + kStagesA * kTileABytes;            // kStagesB * 2 slabs
   int32_t* qinit_s = reinterpret_cast<int32_t*>(tile_b + kStagesB * 2 * kTileBBytes);   // kStagesB * 2 * kTileTokens
-  __shared__ uint64_t a_full[kStagesA], a_empty[kStagesA], b_full[kStagesB], b_empty[kStagesB], acc_full[2], acc_empty[2];
+  __shared__ uint64_t a_full[kStagesA], a_empty[kStagesA], b_full[kStagesB], b_empty[kStagesB], acc_full[2];
   __shared__ uint32_t tmem_base_s, abort_flag;
 
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -315,7 +325,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
     abort_flag = 0;
     for (int s = 0; s < kStagesA; ++s) { mbar_init(&a_full[s], kExpandWarps); mbar_init(&a_empty[s], 2); }
     for (int s = 0; s < kStagesB; ++s) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 2 + kEpilogueWarps); }
-    for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], kEpilogueWarps / 2); }
+    for (int s = 0; s < 2; ++s) mbar_init(&acc_full[s], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -328,16 +338,16 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
   const uint32_t tmem_base = tmem_base_s;
   const uint32_t tiles = p.n_tiles * p.m_tiles;
 
+  const WaitCtx wctx{&abort_flag, p.status};
   if (warp == 0) {
     // ------------------------------------------------ TMA: activations + start values of a tile column
     if (lane == 0) {
       uint32_t fill = 0;
-      bool ok = true;
-      for (uint32_t tile = blockIdx.x; ok && tile < tiles; tile += gridDim.x) {
+      for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
         const uint32_t mt = tile % p.m_tiles;
         for (uint32_t j = 0; j < p.tpr; ++j, ++fill) {
           const uint32_t s = fill % kStagesB, round = fill / kStagesB;
-          if (round > 0 && !mbar_wait(&b_empty[s], (round - 1) & 1, &abort_flag, 400)) { ok = false; break; }
+          if (round > 0) mbar_wait(&b_empty[s], (round - 1) & 1, wctx, 300, 400);
           mbar_expect_tx(&b_full[s], 2 * kTileBBytes + 2 * kTileTokens * 4);
           for (int gsel = 0; gsel < 2; ++gsel) {
             tma_load_2d(tile_b + (s * 2 + gsel) * kTileBBytes, &map_q, int((2 * j + gsel) * 128), int(mt * kTileTokens), &b_full[s]);
@@ -345,10 +355,6 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
                      kTileTokens * 4, &b_full[s]);
           }
         }
-      }
-      if (!ok) {
-        abort_flag = 1;
-        if (atomicOr(&p.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) { p.status[TBS_INFO0] = fill; p.status[TBS_INFO1] = 300; }
       }
       // copies in flight must land before the CTA's shared memory goes away
       for (uint32_t back = 0; back < kStagesB && back < fill; ++back) {
@@ -361,60 +367,52 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
     // tcgen05.mma keeps the thread busy for about as long as the MMA runs, so one thread cannot
     // keep the tensor core fed and also do the waiting); the whole warp walks the loop (so
     // that addresses and descriptors stay in uniform registers); one elected lane issues
+    const uint32_t h = warp - 1;
     uint32_t slab = 0, colfill = 0;
-    bool ok = true;
     const uint64_t a_desc0 = smem_desc(saddr(tile_a), 0), b_desc0 = smem_desc(saddr(tile_b), 0);
-    for (uint32_t tile = blockIdx.x; ok && tile < tiles; tile += gridDim.x) {
-      for (uint32_t j = 0; ok && j < p.tpr; ++j, ++colfill) {
+    for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+      for (uint32_t j = 0; j < p.tpr; ++j, ++colfill) {
         const uint32_t sb = colfill % kStagesB;
-        if (!mbar_wait(&b_full[sb], (colfill / kStagesB) & 1, &abort_flag)) { ok = false; break; }
+        mbar_wait(&b_full[sb], (colfill / kStagesB) & 1, wctx, 301);
         for (uint32_t q = 0; q < kSlabsPerCol; ++q, ++slab) {
           const uint32_t sa = slab % kStagesA, gsel = q & 1;
-          if (!mbar_wait(&a_full[sa], (slab / kStagesA) & 1, &abort_flag)) { ok = false; break; }
+          mbar_wait(&a_full[sa], (slab / kStagesA) & 1, wctx, 301);
           // descriptor start addresses are in 16-byte units
           const uint64_t a_desc = a_desc0 + uint64_t(sa * (kTileABytes >> 4));
-          const uint64_t b_desc = b_desc0 + uint64_t((sb * 2 + gsel) * (kTileBBytes >> 4));
-          {
-            const uint32_t h = warp - 1;
-            if (!mbar_wait(&acc_empty[h], slab & 1, &abort_flag, 0, 250)) { ok = false; break; }
-            tc_fence_after();
-            if (elect_one()) {
+          const uint64_t b_desc = b_desc0 + uint64_t((sb * 2 + gsel) * (kTileBBytes >> 4)) + uint64_t(h * (HW * 128u >> 4));
+          named_sync(kBarEmpty + h, kHandoffThreads);   // the epilogue has stored the start values
+          tc_fence_after();
+          if (elect_one()) {
 #pragma unroll
-              for (uint32_t kc = 0; kc < 4; ++kc)
-                tc_mma_i8(tmem_base + h * HW, a_desc + 2 * kc, b_desc + uint64_t(h * (HW * 128u >> 4)) + 2 * kc, kIdesc);
-              tc_commit(&acc_full[h]);
-            }
-            __syncwarp();
+            for (uint32_t kc = 0; kc < 4; ++kc) tc_mma_i8(tmem_base + h * HW, a_desc + 2 * kc, b_desc + 2 * kc, kIdesc);
+            tc_commit(&acc_full[h]);
+            tc_commit(&a_empty[sa]);
           }
-          if (!ok) break;
-          if (elect_one()) tc_commit(&a_empty[sa]);
           __syncwarp();
+          mbar_wait(&acc_full[h], slab & 1, wctx, 301);
+          tc_fence_before();
+          named_arrive(kBarFull + h, kHandoffThreads);
         }
-        if (ok && elect_one()) tc_commit(&b_empty[sb]);
+        if (elect_one()) tc_commit(&b_empty[sb]);
         __syncwarp();
       }
-    }
-    if (!ok) {
-      abort_flag = 1;
-      if (lane == 0 && atomicOr(&p.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) { p.status[TBS_INFO0] = slab; p.status[TBS_INFO1] = 301; }
     }
   } else if (warp >= kFirstExpandWarp) {
     // ------------------------------------------------ expanders: one weight row per thread
     const uint32_t r = (warp - kFirstExpandWarp) * 32 + lane;
     uint32_t slab = 0;
-    bool ok = true;
-    for (uint32_t tile = blockIdx.x; ok && tile < tiles; tile += gridDim.x) {
+    for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
       const uint32_t nt = tile / p.m_tiles;
       const uint32_t n = min(nt * kRows + r, p.n - 1);   // rows past the end repeat the last row; never stored
       const uint32_t* row_words = reinterpret_cast<const uint32_t*>(p.payload + size_t(n) * p.tpr * PLANES * kPlaneBytes);
-      for (uint32_t j = 0; ok && j < p.tpr; ++j) {
+      for (uint32_t j = 0; j < p.tpr; ++j) {
         for (uint32_t pl = 0; pl < PLANES; ++pl, slab += 2) {
           const uint32_t* wsrc = row_words + (j * PLANES + pl) * (kPlaneBytes / 4);
           uint32_t w[kPlaneBytes / 4];
 #pragma unroll
           for (uint32_t i = 0; i < kPlaneBytes / 4; ++i) w[i] = __ldg(wsrc + i);
           const uint32_t s0 = slab % kStagesA, s1 = (slab + 1) % kStagesA;
-          if (slab >= kStagesA && !mbar_wait(&a_empty[s0], ((slab / kStagesA) - 1) & 1, &abort_flag, 100)) { ok = false; break; }
+          if (slab >= kStagesA) mbar_wait(&a_empty[s0], ((slab / kStagesA) - 1) & 1, wctx, 302, 100);
           uint8_t* t0 = tile_a + s0 * kTileABytes;
           if (CODEC == tbf::kB3) {
             uint32_t d[5], e[5], f[5], g2[5];
@@ -432,7 +430,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&a_full[s0]);
-            if (slab + 1 >= kStagesA && !mbar_wait(&a_empty[s1], (((slab + 1) / kStagesA) - 1) & 1, &abort_flag, 100)) { ok = false; break; }
+            if (slab + 1 >= kStagesA) mbar_wait(&a_empty[s1], (((slab + 1) / kStagesA) - 1) & 1, wctx, 302, 100);
             uint8_t* t1 = tile_a + s1 * kTileABytes;
             // group 1: trits 128..139 in natural order (quads 0..2), words 7..11, trits 240..255
             b3_digits(w[7], d); b3_digits(w[8], e);
@@ -459,7 +457,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&a_full[s0]);
-            if (slab + 1 >= kStagesA && !mbar_wait(&a_empty[s1], (((slab + 1) / kStagesA) - 1) & 1, &abort_flag, 100)) { ok = false; break; }
+            if (slab + 1 >= kStagesA) mbar_wait(&a_empty[s1], (((slab + 1) / kStagesA) - 1) & 1, wctx, 302, 100);
             uint8_t* t1 = tile_a + s1 * kTileABytes;
 #pragma unroll
             for (uint32_t c = 0; c < 8; ++c) {
@@ -473,19 +471,15 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
         }
       }
     }
-    if (!ok) {
-      abort_flag = 1;
-      if (lane == 0 && atomicOr(&p.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) { p.status[TBS_INFO0] = slab; p.status[TBS_INFO1] = 302; }
-    }
   } else if (warp >= kFirstEpilogueWarp) {
-    // ------------------------------------------------ epilogue: TMEM lane = weight row; two warps
-    // share a lane quadrant and split each accumulator half's columns
+    // ------------------------------------------------ epilogue: TMEM lane = weight row; a warp owns one
+    // accumulator half, one lane quadrant and a column range of it
     const uint32_t quad = warp & 3, sub = (warp - kFirstEpilogueWarp) >> 2, wh = sub & 1, part = sub >> 1, r = quad * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((quad * 32u) << 16) + part * kCW;
     uint32_t slab = 0, colfill = 0;
-    bool ok = true;
     // start values of slab 0 (first tile column, group 0) for both halves
-    if (mbar_wait(&b_full[0], 0, &abort_flag)) {
+    {
+      mbar_wait(&b_full[0], 0, wctx, 303);
       {
         const uint32_t h = wh;
         const uint32_t qi = saddr(qinit_s + h * HW + part * kCW);
@@ -502,18 +496,18 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&acc_empty[h]);
+        named_arrive(kBarEmpty + h, kHandoffThreads);
       }
-    } else ok = false;
-    for (uint32_t tile = blockIdx.x; ok && tile < tiles; tile += gridDim.x) {
+    }
+    for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
       const uint32_t nt = tile / p.m_tiles, mt = tile % p.m_tiles;
       const uint32_t n = nt * kRows + r;
       const uint32_t nc = min(n, p.n - 1);
       const uint16_t* srow = p.scales + size_t(nc) * p.tpr * PLANES * 2;
       const bool more_tiles = tile + gridDim.x < tiles;
-      for (uint32_t j = 0; ok && j < p.tpr; ++j, ++colfill) {
+      for (uint32_t j = 0; j < p.tpr; ++j, ++colfill) {
         const uint32_t sb = colfill % kStagesB;
-        for (uint32_t q = 0; ok && q < kSlabsPerCol; ++q, ++slab) {
+        for (uint32_t q = 0; q < kSlabsPerCol; ++q, ++slab) {
           const uint32_t gsel = q & 1, pl = q >> 1;
           const float sv = __half2float(__ushort_as_half(srow[(j * PLANES + pl) * 2 + gsel]));
           const float2 scale2 = make_float2(sv, sv), neg_magic2 = make_float2(-12582912.0f, -12582912.0f);
@@ -522,11 +516,11 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
           const bool next_col = q + 1 == kSlabsPerCol;
           const bool has_next = !(last && !more_tiles);
           const uint32_t ncol = next_col ? colfill + 1 : colfill;
-          if (has_next && next_col && !mbar_wait(&b_full[ncol % kStagesB], (ncol / kStagesB) & 1, &abort_flag)) { ok = false; break; }
+          if (has_next && next_col) mbar_wait(&b_full[ncol % kStagesB], (ncol / kStagesB) & 1, wctx, 303);
           const uint32_t qnext = saddr(qinit_s + ((ncol % kStagesB) * 2 + (next_col ? 0u : (q + 1) & 1u)) * kTileTokens + part * kCW);
           {
             const uint32_t h = wh;
-            if (!mbar_wait(&acc_full[h], slab & 1, &abort_flag, 0, 80)) { ok = false; break; }
+            named_sync(kBarFull + h, kHandoffThreads);   // the MMA warp saw this half's MMAs complete
             tc_fence_after();
             const uint32_t d_addr = lane_addr + h * HW, y_addr = lane_addr + (2 + h) * HW;
             const uint32_t tok0 = mt * kTileTokens + h * HW + part * kCW;
@@ -577,17 +571,12 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
             }
             tmem_wait_st();
             tc_fence_before();
-            __syncwarp();
-            if (lane == 0 && has_next) mbar_arrive(&acc_empty[h]);
+            if (has_next) named_arrive(kBarEmpty + h, kHandoffThreads);
           }
           // the column's start values and activations are no longer needed by this warp
-          if (ok && lane == 0 && next_col) mbar_arrive(&b_empty[sb]);
+          if (lane == 0 && next_col) mbar_arrive(&b_empty[sb]);
         }
       }
-    }
-    if (!ok) {
-      abort_flag = 1;
-      if (lane == 0 && atomicOr(&p.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) { p.status[TBS_INFO0] = slab; p.status[TBS_INFO1] = 303; }
     }
   }
   tc_fence_before();
