@@ -202,7 +202,9 @@ class TPLinear:
         # small messages (decode) are reduced over peer memory when the executor carries a
         # communicator: the kernels write their partials straight into its slots
         comm = getattr(executor, "comm", None) if mode == "row" and world > 1 else None
-        self.comm, self.peer_m, self.fused = comm, 0, True
+        # `fused`: exchange inside the prepare/decode kernels instead of separate one-shot reduce
+        # kernels (measured slower on 2 GPUs: every CTA then pays an NVLink round trip)
+        self.comm, self.peer_m, self.fused = comm, 0, False
         if comm is not None:
             self.peer_m = min(max_m, comm.slot_bytes // (4 * self.geometry.n))
             if self.peer_m:
