@@ -81,7 +81,7 @@ __device__ __forceinline__ bool peer_wait(const uint32_t* counter, uint32_t targ
 template <int CODEC> struct Traits;
 // kMmas: MMAs per (16 row-planes x tile-plane) when the two scale groups use separate
 // accumulators; kMmasDual: when they use separate MMA columns instead (1 or 2 tokens).
-template <> struct Traits<tbf::kB3> { static constexpr int kMmas = 15, kMmasDual = 12, kPlaneBytes = 52; };
+template <> struct Traits<tbf::kB3> { static constexpr int kMmas = 13, kMmasDual = 10, kPlaneBytes = 52; };
 template <> struct Traits<tbf::kD2> { static constexpr int kMmas = 8, kMmasDual = 8, kPlaneBytes = 64; };
 template <int CODEC, bool DUAL> struct MmaCount { static constexpr int value = DUAL ? Traits<CODEC>::kMmasDual : Traits<CODEC>::kMmas; };
 
@@ -177,11 +177,13 @@ __host__ __device__ constexpr int b3_delta(int i) { return i >= 2 ? 1 : 0; }  //
 // ---------------------------------------------------------------- activation-side tables
 // Which packed word / digits / scale-group variant MMA number `mma` of a tile-plane consumes for
 // the lane column c (0..3).
-template <int CODEC> struct Slot { int word, variant, d0, d1, lane_lo, lane_hi; };
+// bytewise: the MMA takes ONE packed byte per lane column (byte c of the word): register byte i of
+// the first operand quad is digit i (0..3), byte 0 of the second quad is digit 4.
+template <int CODEC> struct Slot { int word, variant, d0, d1, lane_lo, lane_hi; bool bytewise; };
 template <int CODEC, bool DUAL> __device__ __forceinline__ Slot<CODEC> slot_of(int mma, int c);
 template <> __device__ __forceinline__ Slot<tbf::kB3> slot_of<tbf::kB3, false>(int mma, int c) {
   // mma 0-2: words c (group 0); 3-5: words 4+c into group 0; 6-8: words 4+c into group 1;
-  // 9-11: words 8+c (group 1); 12-14: word 12, bytes 48,49 for c=0 and 50,51 for c=1 (group 1).
+  // 9-11: words 8+c (group 1); 12: byte c of word 12 (group 1).
   const int slot = mma < 3 ? 0 : mma < 9 ? 1 : mma < 12 ? 2 : 3;
   const int pair = mma % 3;
   Slot<tbf::kB3> s;
@@ -189,18 +191,19 @@ template <> __device__ __forceinline__ Slot<tbf::kB3> slot_of<tbf::kB3, false>(i
   s.d0 = pair * 2; s.d1 = pair == 2 ? -1 : pair * 2 + 1;
   s.word = slot < 3 ? slot * 4 + c : 12;
   s.lane_lo = 0; s.lane_hi = 4;
-  if (slot == 3) { if (c == 0) s.lane_hi = 2; else if (c == 1) s.lane_lo = 2; else s.lane_hi = 0; }
+  s.bytewise = slot == 3;
   return s;
 }
 template <> __device__ __forceinline__ Slot<tbf::kB3> slot_of<tbf::kB3, true>(int mma, int c) {
   // three MMAs per packed word; the scale group is chosen by the MMA column, not by the MMA
+  // (the tenth MMA takes byte c of word 12)
   const int slot = mma / 3, pair = mma % 3;
   Slot<tbf::kB3> s;
   s.variant = -1;
   s.d0 = pair * 2; s.d1 = pair == 2 ? -1 : pair * 2 + 1;
   s.word = slot < 3 ? slot * 4 + c : 12;
   s.lane_lo = 0; s.lane_hi = 4;
-  if (slot == 3) { if (c == 0) s.lane_hi = 2; else if (c == 1) s.lane_lo = 2; else s.lane_hi = 0; }
+  s.bytewise = slot == 3;
   return s;
 }
 template <> __device__ __forceinline__ Slot<tbf::kD2> slot_of<tbf::kD2, false>(int mma, int c) {
@@ -210,6 +213,7 @@ template <> __device__ __forceinline__ Slot<tbf::kD2> slot_of<tbf::kD2, false>(i
   s.d0 = (mma & 1) * 2; s.d1 = s.d0 + 1;
   s.word = slot * 4 + c;
   s.lane_lo = 0; s.lane_hi = 4;
+  s.bytewise = false;
   return s;
 }
 template <> __device__ __forceinline__ Slot<tbf::kD2> slot_of<tbf::kD2, true>(int mma, int c) {
@@ -242,6 +246,19 @@ __device__ __forceinline__ uint32_t z_quad(const int8_t* xq_tile, const Slot<COD
     out |= uint32_t(v & 0xff) << (8 * e);
   }
   return out;
+}
+
+// B operand of a bytewise MMA for lane column c: quad 0 = digits 0..3 of byte c of the word,
+// quad 1 = digit 4 in its first byte.
+template <int CODEC>
+__device__ __forceinline__ uint2 z_bytewise(const int8_t* xq_tile, const Slot<CODEC>& s, int c, int hl, int variant) {
+  uint32_t q0 = 0, q1 = 0;
+  for (int i = 0; i < 5; ++i) {
+    const int z = z_value<CODEC>(xq_tile, s.word, c, i, variant);
+    const uint32_t v = uint32_t((hl == 0 ? (z >> 2) : (z & 3)) & 0xff);
+    if (i < 4) q0 |= v << (8 * i); else q1 = v;
+  }
+  return make_uint2(q0, q1);
 }
 
 // ---------------------------------------------------------------- activation preparation
@@ -338,7 +355,8 @@ __global__ void __launch_bounds__(256) prepare_kernel(const PrepareParams p) {
     const int variant = DUAL ? int(v) : s.variant;
     const uint32_t col = v * 2 * p.m + 2 * t + hl;
     ztab[((size_t(j) * kNM + mma) * ncol + col) * 4 + c] =
-        make_uint2(z_quad<CODEC>(xq, s, s.d0, int(hl), variant), z_quad<CODEC>(xq, s, s.d1, int(hl), variant));
+        s.bytewise ? z_bytewise<CODEC>(xq, s, int(c), int(hl), variant)
+                   : make_uint2(z_quad<CODEC>(xq, s, s.d0, int(hl), variant), z_quad<CODEC>(xq, s, s.d1, int(hl), variant));
   }
   // accumulator start value of (token, column, group v):
   //   B3: -(sum over the group of x_t * c5[t mod 5]), c5 = {1,-2,-1,-1,2}: the group sum of x plus
@@ -479,6 +497,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
   // MMA columns beyond `ncol` produce sums nobody reads, so their lanes may load any valid
   // table entry: fold them onto the used columns instead of masking.
   const uint32_t bcol = g % ncol;
+  const uint32_t byte_sel = c | (c << 4) | ((4u + c) << 8) | ((4u + c) << 12);   // byte c of two words -> bytes 0 and 2
   constexpr uint32_t zstep = ncol * 4;
   const uint32_t groups_per_row = p.tpr * 2;
 
@@ -557,10 +576,16 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
           b = TB_BFRAG(o2); mma_u8s8_first(s2, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
           b = TB_BFRAG(o2 + 1); mma_u8s8(s2, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
           b = TB_BFRAG(o2 + 2); mma_u8s8(s2, qa[4], qb[4], 0u, 0u, b.x, b.y);
-          b3_quads(wa[12 - c], qa); b3_quads(wb[12 - c], qb);   // word 12 for every lane column
-          b = TB_BFRAG(o3); mma_u8s8_first(s3, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
-          b = TB_BFRAG(o3 + 1); mma_u8s8(s3, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
-          b = TB_BFRAG(o3 + 2); mma_u8s8(s3, qa[4], qb[4], 0u, 0u, b.x, b.y);
+          {
+            // word 12: lane column c takes byte c of both rows through one half2 chain; its five
+            // quotients fill the lane's eight k-slots of a single MMA
+            const uint32_t h = (prmt(wa[12 - c], wb[12 - c], byte_sel) & 0x00ff00ffu) | 0x64006400u;
+            const uint32_t q1 = hfma2_bits(h, kC3, kK3), q2 = hfma2_bits(h, kC9, kK9);
+            const uint32_t q3 = hfma2_bits(q1, kC9, kK9), q4 = hfma2_bits(q2, kC9b, kK9b);
+            const uint32_t u = prmt(h, q1, 0x6240u), v = prmt(q2, q3, 0x6240u);
+            b = TB_BFRAG(o3);
+            mma_u8s8_first(s3, prmt(u, v, 0x5410u), prmt(u, v, 0x7632u), prmt(q4, 0u, 0x4440u), prmt(q4, 0u, 0x4442u), b.x, b.y);
+          }
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             if (DUAL) acc0[e] = (s0[e] + s1[e]) + (s2[e] + s3[e]);
@@ -717,7 +742,7 @@ bool use_dual(uint32_t m) { return m <= 2; }
 TableLayout table_layout(const tb_weights* w, uint32_t m) {
   const bool dual = use_dual(m);
   const uint32_t tpr = uint32_t(w->k / 256);
-  const uint32_t mmas = w->codec == tbf::kB3 ? (dual ? 12 : 15) : 8;
+  const uint32_t mmas = w->codec == tbf::kB3 ? (dual ? 10 : 13) : 8;
   TableLayout t;
   t.z_bytes = tpr * mmas * ((dual ? 4 : 2) * m) * 4 * 8;
   t.off_cinit = t.z_bytes;
