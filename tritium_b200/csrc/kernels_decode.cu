@@ -546,36 +546,41 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
       for (; j < j_end; ++j, wa += kColStride, wb += kColStride, sca += 2 * PLANES, scb += 2 * PLANES, cin += 2, zlane += zcol) {
         int acc0[4], acc1[4];   // group 0 / group 1 sums (dual layout: acc0 holds this lane's group)
         if (CODEC == tbf::kB3) {
-          // One short accumulation chain per packed word keeps dependent MMAs three deep.
-          int s0[4], s1[4], s2[4], s3[4];
+          // Two accumulation chains, fed alternately, so that consecutive MMAs rarely depend on
+          // each other.  Dual layout: chain A takes words c and 8+c, chain B words 4+c and 12, and
+          // their sum is the cell.  Separate accumulators: chain A is scale group 0, chain B group 1.
+          int sA[4], sB[4];
           uint32_t qa[5], qb[5];
           uint2 b;
           b3_quads(wa[0], qa); b3_quads(wb[0], qb);
-          b = TB_BFRAG(0); mma_u8s8_first(s0, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
-          b = TB_BFRAG(1); mma_u8s8(s0, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
-          b = TB_BFRAG(2); mma_u8s8(s0, qa[4], qb[4], 0u, 0u, b.x, b.y);
+          b = TB_BFRAG(0); mma_u8s8_first(sA, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
+          b = TB_BFRAG(1); mma_u8s8(sA, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
+          b = TB_BFRAG(2); mma_u8s8(sA, qa[4], qb[4], 0u, 0u, b.x, b.y);
           b3_quads(wa[4], qa); b3_quads(wb[4], qb);
           if (DUAL) {
-            b = TB_BFRAG(3); mma_u8s8_first(s1, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
-            b = TB_BFRAG(4); mma_u8s8(s1, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
-            b = TB_BFRAG(5); mma_u8s8(s1, qa[4], qb[4], 0u, 0u, b.x, b.y);
+            b = TB_BFRAG(3); mma_u8s8_first(sB, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
+            b = TB_BFRAG(4); mma_u8s8(sB, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
+            b = TB_BFRAG(5); mma_u8s8(sB, qa[4], qb[4], 0u, 0u, b.x, b.y);
           } else {
             // the words 4..7 straddle the two scale groups: once per group, masked on the B side
-            int s1b[4];
-            b = TB_BFRAG(3); mma_u8s8_first(s1, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
-            b = TB_BFRAG(6); mma_u8s8_first(s1b, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
-            b = TB_BFRAG(4); mma_u8s8(s1, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
-            b = TB_BFRAG(7); mma_u8s8(s1b, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
-            b = TB_BFRAG(5); mma_u8s8(s1, qa[4], qb[4], 0u, 0u, b.x, b.y);
-            b = TB_BFRAG(8); mma_u8s8(s1b, qa[4], qb[4], 0u, 0u, b.x, b.y);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) acc1[e] = s1b[e];
+            b = TB_BFRAG(3); mma_u8s8(sA, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
+            b = TB_BFRAG(6); mma_u8s8_first(sB, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
+            b = TB_BFRAG(4); mma_u8s8(sA, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
+            b = TB_BFRAG(7); mma_u8s8(sB, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
+            b = TB_BFRAG(5); mma_u8s8(sA, qa[4], qb[4], 0u, 0u, b.x, b.y);
+            b = TB_BFRAG(8); mma_u8s8(sB, qa[4], qb[4], 0u, 0u, b.x, b.y);
           }
           constexpr int o2 = DUAL ? 6 : 9, o3 = DUAL ? 9 : 12;
           b3_quads(wa[8], qa); b3_quads(wb[8], qb);
-          b = TB_BFRAG(o2); mma_u8s8_first(s2, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
-          b = TB_BFRAG(o2 + 1); mma_u8s8(s2, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
-          b = TB_BFRAG(o2 + 2); mma_u8s8(s2, qa[4], qb[4], 0u, 0u, b.x, b.y);
+          if (DUAL) {
+            b = TB_BFRAG(o2); mma_u8s8(sA, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
+            b = TB_BFRAG(o2 + 1); mma_u8s8(sA, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
+            b = TB_BFRAG(o2 + 2); mma_u8s8(sA, qa[4], qb[4], 0u, 0u, b.x, b.y);
+          } else {
+            b = TB_BFRAG(o2); mma_u8s8(sB, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
+            b = TB_BFRAG(o2 + 1); mma_u8s8(sB, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
+            b = TB_BFRAG(o2 + 2); mma_u8s8(sB, qa[4], qb[4], 0u, 0u, b.x, b.y);
+          }
           {
             // word 12: lane column c takes byte c of both rows through one half2 chain; its five
             // quotients fill the lane's eight k-slots of a single MMA
@@ -584,12 +589,12 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
             const uint32_t q3 = hfma2_bits(q1, kC9, kK9), q4 = hfma2_bits(q2, kC9b, kK9b);
             const uint32_t u = prmt(h, q1, 0x6240u), v = prmt(q2, q3, 0x6240u);
             b = TB_BFRAG(o3);
-            mma_u8s8_first(s3, prmt(u, v, 0x5410u), prmt(u, v, 0x7632u), prmt(q4, 0u, 0x4440u), prmt(q4, 0u, 0x4442u), b.x, b.y);
+            mma_u8s8(sB, prmt(u, v, 0x5410u), prmt(u, v, 0x7632u), prmt(q4, 0u, 0x4440u), prmt(q4, 0u, 0x4442u), b.x, b.y);
           }
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            if (DUAL) acc0[e] = (s0[e] + s1[e]) + (s2[e] + s3[e]);
-            else { acc0[e] = s0[e] + s1[e]; acc1[e] = acc1[e] + s2[e] + s3[e]; }
+            if (DUAL) acc0[e] = sA[e] + sB[e];
+            else { acc0[e] = sA[e]; acc1[e] = sB[e]; }
           }
         } else {
           int sq[4][4];
