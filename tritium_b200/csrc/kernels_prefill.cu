@@ -317,6 +317,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
   uint8_t* tile_a = smem;                                       // kStagesA * 16 KB
   uint8_t* tile_b = tile_a + kStagesA * kTileABytes;            // kStagesB * 2 slabs
   int32_t* qinit_s = reinterpret_cast<int32_t*>(tile_b + kStagesB * 2 * kTileBBytes);   // kStagesB * 2 * kTileTokens
+  uint32_t* stage_s = reinterpret_cast<uint32_t*>(qinit_s + kStagesB * 2 * kTileTokens);   // kExpandWarps * 32 rows * 16 words
   __shared__ uint64_t a_full[kStagesA], a_empty[kStagesA], b_full[kStagesB], b_empty[kStagesB], acc_full[2];
   __shared__ uint32_t tmem_base_s, abort_flag;
 
@@ -399,18 +400,41 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
     }
   } else if (warp >= kFirstExpandWarp) {
     // ------------------------------------------------ expanders: one weight row per thread
-    const uint32_t r = (warp - kFirstExpandWarp) * 32 + lane;
+    // Rows are 1.5 KB apart in the arena, so a lane that fetched its own row word by word would
+    // touch one sector per load.  Instead the warp fetches its 32 rows' words of a tile-plane as a
+    // flattened (row, word) sequence -- consecutive lanes read consecutive words -- parks them in a
+    // per-warp staging area, and every lane picks up its own row from there (stride kWords words:
+    // odd for B3, conflict-free).  The next tile-plane's words are requested before the current
+    // one is expanded.
+    constexpr uint32_t kWords = kPlaneBytes / 4;
+    const uint32_t wexp = warp - kFirstExpandWarp, r = wexp * 32 + lane;
+    uint32_t* stage = stage_s + wexp * 32 * kWords;
+    const uint32_t row_stride = p.tpr * PLANES * kWords;   // words per weight row
     uint32_t slab = 0;
     for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
       const uint32_t nt = tile / p.m_tiles;
-      const uint32_t n = min(nt * kRows + r, p.n - 1);   // rows past the end repeat the last row; never stored
-      const uint32_t* row_words = reinterpret_cast<const uint32_t*>(p.payload + size_t(n) * p.tpr * PLANES * kPlaneBytes);
+      const uint32_t* tile_words = reinterpret_cast<const uint32_t*>(p.payload);
+      const uint32_t row0 = nt * kRows + wexp * 32;
+      uint32_t pf[kWords];
+      auto fetch = [&](uint32_t tp) {
+#pragma unroll
+        for (uint32_t it = 0; it < kWords; ++it) {
+          const uint32_t f = it * 32 + lane, rl = f / kWords, wd = f - rl * kWords;
+          const uint32_t n = min(row0 + rl, p.n - 1);   // rows past the end repeat the last row; never stored
+          pf[it] = __ldg(tile_words + size_t(n) * row_stride + tp * kWords + wd);
+        }
+      };
+      fetch(0);
       for (uint32_t j = 0; j < p.tpr; ++j) {
         for (uint32_t pl = 0; pl < PLANES; ++pl, slab += 2) {
-          const uint32_t* wsrc = row_words + (j * PLANES + pl) * (kPlaneBytes / 4);
-          uint32_t w[kPlaneBytes / 4];
+          uint32_t w[kWords];
 #pragma unroll
-          for (uint32_t i = 0; i < kPlaneBytes / 4; ++i) w[i] = __ldg(wsrc + i);
+          for (uint32_t it = 0; it < kWords; ++it) stage[it * 32 + lane] = pf[it];
+          __syncwarp();
+          if (j * PLANES + pl + 1 < p.tpr * PLANES) fetch(j * PLANES + pl + 1);
+#pragma unroll
+          for (uint32_t i = 0; i < kWords; ++i) w[i] = stage[lane * kWords + i];
+          __syncwarp();
           const uint32_t s0 = slab % kStagesA, s1 = (slab + 1) % kStagesA;
           if (slab >= kStagesA) mbar_wait(&a_empty[s0], ((slab / kStagesA) - 1) & 1, wctx, 302, 100);
           uint8_t* t0 = tile_a + s0 * kTileABytes;
@@ -681,7 +705,8 @@ cudaError_t tb_launch_prefill(const PrefillArgs& a, int sm_count, cudaStream_t s
   pp.y = a.y; pp.acc_dump = a.acc_dump; pp.row_scale = a.row_scale; pp.status = a.status;
   pp.m = a.m; pp.m_pad = m_pad; pp.n = uint32_t(w->n); pp.k = k; pp.tpr = k / 256; pp.y_dtype = uint32_t(a.y_dtype);
   pp.n_tiles = (pp.n + kRows - 1) / kRows; pp.m_tiles = m_pad / tile_tokens;
-  const size_t smem = 1024 + size_t(kStagesA) * kTileABytes + size_t(kStagesB) * 2 * tile_tokens * 128 + size_t(kStagesB) * 2 * tile_tokens * 4;
+  const size_t smem = 1024 + size_t(kStagesA) * kTileABytes + size_t(kStagesB) * 2 * tile_tokens * 128 + size_t(kStagesB) * 2 * tile_tokens * 4 +
+                      size_t(kExpandWarps) * 32 * 16 * 4;
   const dim3 grid(std::min<uint32_t>(pp.n_tiles * pp.m_tiles, uint32_t(sm_count)));
   const bool dump = a.acc_dump != nullptr;
   return w->codec == tbf::kB3 ? launch_shape<tbf::kB3>(hw, dump, w->uniform_planes, grid, smem, stream, pp, map)
