@@ -209,6 +209,11 @@ tb_status tb_stack_create(tb_backend* backend, const tb_weights* const* weights,
                           const uint8_t* chain, uint32_t layers, uint32_t max_m, tb_stack** out);
 tb_status tb_stack_forward_dev(tb_stack* stack, const void* x, tb_dtype x_dtype, uint32_t m,
                                void* y_last, tb_dtype y_dtype, uint32_t flags, void* stream);
+/* Host-pointer pass over a stack whose layers all read the stack input (up to 4 tokens): x in,
+ * every layer's bf16 output out as [layer][m][n]; one synchronisation; `y_bf16` is written only
+ * on success.  No counterpart in the reference: it replaces one tb_linear_forward_a8 call per
+ * projection when several projections (a QKV or gate/up group) read the same activations. */
+tb_status tb_stack_forward_host(tb_stack* stack, const void* x, tb_dtype x_dtype, uint32_t m, void* y_bf16, uint32_t flags);
 uint64_t tb_stack_bytes_per_step(const tb_stack* stack, uint32_t m);
 /* Consecutive unchained layers of one geometry form a group that runs as a single launch;
  * their bf16 outputs ([m][n] per layer) are read back with this call (synchronises). */

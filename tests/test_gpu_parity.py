@@ -435,3 +435,20 @@ def test_grouped_stack_matches_per_layer_oracle(backend, codec, m):
             got = bf16_bits_to_f32(stack.read_output(i, m))
             assert rel_l2(got, want) <= 1e-2, (i, flags)
     stack.close()
+
+
+def test_stack_host_call_matches_per_layer_calls(backend):
+    """One host-pointer call over a stack of projections that read the same activations returns
+    what one host-pointer call per projection returns."""
+    n, k, planes, m = 96, 512, 2, 3
+    tensors = [uniform_pair(n, k, planes, seed=70 + i)[0] for i in range(3)]
+    residents = [backend.upload_salt_v2(t, SaltV2Codec.B3) for t in tensors]
+    from tritium_b200 import LinearStack
+    stack = LinearStack(backend, residents, [0, 0, 0], max_m=4)
+    x = make_activations(m, k, seed=8, bf16=True)
+    got = stack.forward_host(f32_to_bf16_bits(x), m, x_is_bf16=True)
+    assert got.shape == (3, m, n)
+    for i, r in enumerate(residents):
+        want, _, _ = backend.linear_forward_a8(r, f32_to_bf16_bits(x), m, y_dtype="bf16", x_is_bf16=True)
+        assert np.array_equal(got[i], want)
+    stack.close()

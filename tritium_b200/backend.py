@@ -349,6 +349,16 @@ class LinearStack:
             C.c_void_p(y_last.data_ptr()) if y_last is not None else None,
             dt[y_last.dtype] if y_last is not None else _lib.TB_BF16, C.c_uint32(flags), C.c_void_p(s.cuda_stream)))
 
+    def forward_host(self, x: np.ndarray, m: int, x_is_bf16: bool = False, flags: int = 0) -> np.ndarray:
+        """Host buffers in and out: every layer's bf16 output bits as [layers, m, n] (uint16); the
+        layers must all read the stack input and share n."""
+        xa = np.ascontiguousarray(x, np.uint16 if x_is_bf16 else np.float32)
+        n = self._weights[0].rows
+        y = np.zeros((len(self._weights), m, n), np.uint16)
+        check(self._backend._L.tb_stack_forward_host(self._h, _ptr(xa), _lib.TB_BF16 if x_is_bf16 else _lib.TB_F32, C.c_uint32(m), _ptr(y),
+                                            C.c_uint32(flags)))
+        return y
+
     def read_output(self, layer: int, m: int) -> np.ndarray:
         """bf16 bit patterns [m, n] of a grouped layer's output (synchronises)."""
         out = np.zeros((m, self._weights[layer].rows), np.uint16)

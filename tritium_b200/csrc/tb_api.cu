@@ -347,17 +347,30 @@ tb_status forward_host(tb_backend* b, const tb_weights* w, const void* x, tb_dty
   if (tb_status s = ensure(&b->d_aux, &b->d_aux_cap, dump_b + rs_b + 256)) return s;
   if (flags & TB_FWD_A8) if (tb_status s = reserve_prefill(b, w, m)) return s;
   uint8_t* aux = static_cast<uint8_t*>(b->d_aux);
-  TB_CUDA(cudaMemcpyAsync(b->d_x, x, xb, cudaMemcpyHostToDevice, b->stream), "copy activations to device");
+  // Activations and outputs travel through one pinned bounce buffer, so that both copies are truly
+  // asynchronous and the call needs a single stream synchronisation: [x | y].
+  const size_t x_off = 0, y_off = (xb + 255) / 256 * 256;
+  if (tb_status s = ensure(&b->h_pin, &b->h_pin_cap, y_off + yb, true)) return s;
+  uint8_t* pin = static_cast<uint8_t*>(b->h_pin);
+  std::memcpy(pin + x_off, x, xb);
+  TB_CUDA(cudaMemcpyAsync(b->d_x, pin + x_off, xb, cudaMemcpyHostToDevice, b->stream), "copy activations to device");
   if (rs_b) TB_CUDA(cudaMemcpyAsync(aux + dump_b, row_scale_host, rs_b, cudaMemcpyHostToDevice, b->stream), "copy scales to device");
   tb_forward_args a{};
   a.x = b->d_x; a.x_dtype = xd; a.m = m; a.y = b->d_y; a.y_dtype = yd; a.flags = flags;
   a.acc_dump = acc_dump ? reinterpret_cast<int32_t*>(aux) : nullptr;
   a.row_scale = rs_b ? reinterpret_cast<const float*>(aux + dump_b) : nullptr;
   if (tb_status s = forward_dev(b, w, a, b->stream, receipt)) return s;
-  if (tb_status s = tb_backend_check(b, b->stream)) return s;
-  TB_CUDA(cudaMemcpyAsync(y, b->d_y, yb, cudaMemcpyDeviceToHost, b->stream), "copy output to host");
-  if (dump_b) TB_CUDA(cudaMemcpyAsync(acc_dump, aux, dump_b, cudaMemcpyDeviceToHost, b->stream), "copy accumulators to host");
+  // the device status word (bounded waits, finite checks) comes back with the output; the
+  // caller's buffers are written only when it is clean
+  TB_CUDA(cudaMemcpyAsync(pin + y_off, b->d_y, yb, cudaMemcpyDeviceToHost, b->stream), "copy output to host");
+  TB_CUDA(cudaMemcpyAsync(b->h_status, b->d_status, 8 * sizeof(uint32_t), cudaMemcpyDeviceToHost, b->stream), "read status");
   TB_CUDA(cudaStreamSynchronize(b->stream), "synchronize stream");
+  if (b->h_status[TBS_FLAGS]) return tb_backend_check(b, b->stream);   // reports and clears
+  std::memcpy(y, pin + y_off, yb);
+  if (dump_b) {
+    TB_CUDA(cudaMemcpyAsync(acc_dump, aux, dump_b, cudaMemcpyDeviceToHost, b->stream), "copy accumulators to host");
+    TB_CUDA(cudaStreamSynchronize(b->stream), "synchronize stream");
+  }
   return TB_OK;
 }
 
@@ -671,6 +684,43 @@ extern "C" tb_status tb_stack_forward_dev(tb_stack* st, const void* x, tb_dtype 
     a.stream = cs;
     if (tb_status s = forward_dev(b, st->layers[i], a, cs, nullptr)) return s;
   }
+  return TB_OK;
+}
+
+/* Host-pointer pass over a stack whose layers all read the stack input (every layer belongs to a
+ * grouped run, m <= 4): one copy of x to the device, one prepare + one grouped launch per run,
+ * one copy of every layer's bf16 output ([layer][m][n], layers in stack order) back, one
+ * synchronisation.  `y` is written only when the device status is clean. */
+extern "C" tb_status tb_stack_forward_host(tb_stack* st, const void* x, tb_dtype xd, uint32_t m, void* y_bf16, uint32_t flags) {
+  clear_error();
+  if (!st || !x || !y_bf16) return tb_fail(TB_NULL_ARG, "null argument");
+  if (m == 0) return TB_OK;
+  if (m > st->max_m || m > 4) return tb_fail(TB_SHAPE_MISMATCH, "token count exceeds the stack's max_m or the grouped kernel's four tokens");
+  if (xd == TB_I8) return tb_fail(TB_INVALID_INPUT, "host int8 activations are not accepted here; pass fp32 or bf16");
+  for (int gi : st->group_of)
+    if (gi < 0) return tb_fail(TB_INVALID_INPUT, "every layer of the stack must belong to a grouped run");
+  tb_backend* b = st->backend;
+  if (tb_status s = use_device(b)) return s;
+  const size_t xb = size_t(m) * st->layers[0]->k * dtype_size(xd);
+  size_t yb = 0;
+  for (const tb_weights* w : st->layers) yb += size_t(m) * w->n * 2;
+  const size_t y_off = (xb + 255) / 256 * 256;
+  if (tb_status s = ensure(&b->d_x, &b->d_x_cap, xb)) return s;
+  if (tb_status s = ensure(&b->h_pin, &b->h_pin_cap, y_off + yb, true)) return s;
+  uint8_t* pin = static_cast<uint8_t*>(b->h_pin);
+  std::memcpy(pin, x, xb);
+  TB_CUDA(cudaMemcpyAsync(b->d_x, pin, xb, cudaMemcpyHostToDevice, b->stream), "copy activations to device");
+  if (tb_status s = tb_stack_forward_dev(st, b->d_x, xd, m, nullptr, TB_BF16, flags, b->stream)) return s;
+  size_t off = y_off;
+  for (const StackGroup& g : st->groups) {
+    const size_t bytes = g.count * size_t(m) * st->layers[g.first]->n * 2;
+    TB_CUDA(cudaMemcpyAsync(pin + off, g.y, bytes, cudaMemcpyDeviceToHost, b->stream), "copy group outputs to host");
+    off += bytes;
+  }
+  TB_CUDA(cudaMemcpyAsync(b->h_status, b->d_status, 8 * sizeof(uint32_t), cudaMemcpyDeviceToHost, b->stream), "read status");
+  TB_CUDA(cudaStreamSynchronize(b->stream), "synchronize stream");
+  if (b->h_status[TBS_FLAGS]) return tb_backend_check(b, b->stream);
+  std::memcpy(y_bf16, pin + y_off, yb);
   return TB_OK;
 }
 
