@@ -203,12 +203,15 @@ def measure_tp(torch, dist, backend, rank: int, world: int, codec, codec_name: s
     layers are built and timed (each rank streams 2 x 144 MB > L2 per step); the 64-layer step
     time is L-layer time x 64 / L, stated in the output."""
     from tritium_b200 import _lib, tp
-    shape = tp.DECODER_27B
-    built = 2 * world
-    out = {"workload": f"c5_27b_2plane_tp{world}_{codec_name}", "layers_timed": built, "layers_model": shape.layers,
+    shape = tp.DECODER_27B if args.tp_shape == "27b" else tp.DECODER_2B
+    # enough distinct layers that one rank's weights of a timed step exceed L2 (126 MB)
+    built = 2 * world if args.tp_shape == "27b" else 12 * world
+    out = {"workload": f"{'c5_27b_2plane' if args.tp_shape == '27b' else 'c4_2b_1plane'}_tp{world}_{codec_name}", "layers_timed": built,
+           "layers_model": shape.layers,
            "collective": "nccl all_reduce (fp32 sum after O and down; fp32 max of the row absmax before them)" if world > 1 else "none"}
     m_prefill = args.tp_prefill_m
-    max_m = max(1, m_prefill)
+    batches = [int(v) for v in args.tp_batches.split(",") if v]
+    max_m = max([1, m_prefill] + batches)
     comm = None
     if world > 1:
         # two slots (row absmax, partial outputs) per row-parallel linear, sized for decode batches up to 32
@@ -258,26 +261,36 @@ def measure_tp(torch, dist, backend, rank: int, world: int, codec, codec_name: s
 
     def decode_entry(ms, graphed, reduce_kind):
         full_ms = ms * shape.layers / built
-        return {"ms_per_step_timed_layers": ms, "ms_per_64_layer_step": full_ms, "tokens_per_s": 1e3 / full_ms,
+        return {"ms_per_step_timed_layers": ms, "ms_per_model_step": full_ms, "tokens_per_s": 1e3 / full_ms,
                 "weight_gbs_all_ranks": world * bytes_rank / (ms * 1e-3) / 1e9, "cuda_graph": graphed,
                 "all_reduces_per_timed_step": 4 * built if world > 1 else 0, "reduce": reduce_kind}
 
     ms, graphed = timed(1, not args.no_graph)
-    out["decode_m1"] = decode_entry(ms, graphed, "one-shot reduce kernels over peer memory" if world > 1 else "none")
+    out["decode_m1"] = decode_entry(ms, graphed, "absmax exchange inside the prepare kernel + one reduce kernel over peer memory" if world > 1 else "none")
     if world > 1:
         stack.use_fused_reduce(True)
         ms, graphed = timed(1, not args.no_graph)
         out["decode_m1_in_kernel"] = decode_entry(ms, graphed, "inside the prepare and decode kernels, over peer memory")
+        stack.use_fused_reduce(None)
+        ms, graphed = timed(1, not args.no_graph)
+        out["decode_m1_one_shot"] = decode_entry(ms, graphed, "separate absmax and one-shot reduce kernels over peer memory")
         stack.use_fused_reduce(False)
         stack.use_peer_reduce(False)
         ms, graphed = timed(1, not args.no_graph)
         out["decode_m1_nccl"] = decode_entry(ms, graphed, "nccl all_reduce")
         stack.use_peer_reduce(True)
+    for mb in batches:
+        if mb == 1:
+            continue
+        ms, graphed = timed(mb, not args.no_graph)
+        full_ms = ms * shape.layers / built
+        out[f"decode_m{mb}"] = {"ms_per_step_timed_layers": ms, "ms_per_model_step": full_ms, "tokens_per_s": mb * 1e3 / full_ms,
+                                "weight_gbs_all_ranks": world * bytes_rank / (ms * 1e-3) / 1e9, "cuda_graph": graphed}
     if m_prefill > 0:
         ms, _ = timed(m_prefill, False)
         full_ms = ms * shape.layers / built
         ops = 2.0 * m_prefill * shape.planes * sum(n * k for _, _, n, k in shape.linears()) * built
-        out[f"prefill_m{m_prefill}"] = {"ms_per_step_timed_layers": ms, "ms_per_64_layer_step": full_ms,
+        out[f"prefill_m{m_prefill}"] = {"ms_per_step_timed_layers": ms, "ms_per_model_step": full_ms,
                                         "tokens_per_s": m_prefill * 1e3 / full_ms, "tops_all_ranks": ops / (ms * 1e-3) / 1e12}
     del stack
     if comm is not None:
@@ -449,6 +462,8 @@ def main() -> None:
     ap.add_argument("--only-prefill", action="store_true")
     ap.add_argument("--no-tp", action="store_true", help="skip the tensor-parallel decoder-stack leg")
     ap.add_argument("--tp-prefill-m", type=int, default=4096, help="tokens of the tensor-parallel prefill pass (0 = skip)")
+    ap.add_argument("--tp-shape", default="27b", choices=["27b", "2b"], help="decoder whose linears the tensor-parallel leg runs")
+    ap.add_argument("--tp-batches", default="1", help="comma-separated decode batch sizes of the tensor-parallel leg")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -241,14 +241,15 @@ tb_status tb_comm_allreduce_f32(tb_comm* comm, uint32_t slot, uint32_t count, in
 /* Row-parallel int8 forward (1..8 tokens) that finishes the tensor-parallel all-reduce inside its
  * own kernels: the activation-preparation kernel exchanges the per-token absmax through
  * `slot_absmax` (so that every shard quantises with the scale of the whole row), the GEMV kernel
- * writes its fp32 partial rows into `slot_y`; each CTA then raises one arrival counter on every
+ * writes its fp32 partial rows into `slot_y`; with TB_TP_REDUCE_IN_KERNEL each CTA then raises one arrival counter on every
  * peer, waits (bounded) for the peers' arrivals and adds the peers' rows in rank order into `y`
  * (every rank ends with the full result).  `counters_per_slot` of the communicator must be at
- * least the SM count.
+ * least twice the SM count.
  * The two slots belong to this linear alone. */
+#define TB_TP_REDUCE_IN_KERNEL 1u   /* else: partial rows into `slot_y`, then one tb_comm_allreduce_f32 launch (fp32 y) */
 tb_status tb_linear_forward_tp_dev(tb_backend* backend, const tb_weights* weights, tb_comm* comm, uint32_t slot_absmax,
                                    uint32_t slot_y, const void* x, tb_dtype x_dtype, uint32_t m, void* y, tb_dtype y_dtype,
-                                   void* stream);
+                                   uint32_t flags, void* stream);
 void tb_comm_free(tb_comm* comm);
 
 /* ------------------------------------------------------------------ tensor-parallel sharding (host)

@@ -54,21 +54,21 @@ def rank_main(rank, world, port, codec_value, use_peer, results):
                 g = row.geometry
                 row.input_view(m).copy_(torch.from_numpy(np.ascontiguousarray(x[:, g.k_offset:g.k_offset + g.k_valid])).to(torch.bfloat16))
                 assert (row.comm is not None) == bool(use_peer)
-                row.fused = use_peer == 2
+                row.fused = {1: None, 2: True, 3: False}.get(use_peer, None)
                 for _ in range(3):          # repeated rounds on the same slots
                     y_row = row.forward(m)
                 stream.synchronize()
                 backend.check(stream)
             gc = col.geometry
             # the in-kernel exchange keeps the row absmax to itself; the output parity covers it
-            absmax_ok = (use_peer == 2 and m <= 8) or bool(np.array_equal(row.absmax[:m].cpu().numpy(), np.abs(x).max(axis=1)))
+            absmax_ok = (use_peer >= 2 and m <= 8) or bool(np.array_equal(row.absmax[:m].cpu().numpy(), np.abs(x).max(axis=1)))
             out[m] = (rel_l2(y_col.cpu().numpy(), want[:, gc.n_offset:gc.n_offset + gc.n]), rel_l2(y_row.cpu().numpy(), want), absmax_ok)
         results[rank] = out
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("use_peer", [0, 1, 2], ids=["nccl", "peer_one_shot", "peer_fused_in_kernel"])
+@pytest.mark.parametrize("use_peer", [0, 1, 2, 3], ids=["nccl", "peer_one_shot", "peer_in_kernel", "peer_absmax_in_kernel"])
 @pytest.mark.parametrize("codec", [2, 1], ids=["b3", "d2"])
 def test_two_gpu_tensor_parallel_matches_unsharded_reference(codec, use_peer):
     if torch.cuda.device_count() < 2:

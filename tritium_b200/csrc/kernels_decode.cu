@@ -880,8 +880,8 @@ cudaError_t tb_launch_decode(const DecodeArgs& a, int sm_count, int max_smem, cu
   p.pdl = a.pdl ? 1u : 0u;
   p.wait_tables = a.tables_shared ? 0u : 1u;
   if (a.comm_y) {
-    // one arrival counter per CTA; single layer, fp32 partials of [m, n]
-    if (a.layers || a.comm_y->counters < uint32_t(sm_count)) return cudaErrorInvalidValue;
+    // one arrival counter per CTA (up to two CTAs per SM); single layer, fp32 partials of [m, n]
+    if (a.layers || a.comm_y->counters < 2u * uint32_t(sm_count)) return cudaErrorInvalidValue;
     p.comm = *a.comm_y;
   }
   DecodeKernel kernel = w->codec == tbf::kB3 ? pick_planes<tbf::kB3>(w->uniform_planes, a.m) : pick_planes<tbf::kD2>(w->uniform_planes, a.m);
@@ -889,9 +889,11 @@ cudaError_t tb_launch_decode(const DecodeArgs& a, int sm_count, int max_smem, cu
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
   if (err != cudaSuccess) return err;
   cudaLaunchConfig_t cfg{};
-  // A grouped launch keeps two CTAs per SM busy; a single layer keeps one, so that the next
-  // launch on the stream can move in beside it.
-  const uint32_t resident = uint32_t(sm_count) * (a.layers ? p.ctas_per_sm : 1u);
+  // A grouped launch keeps two CTAs per SM busy.  A single small layer keeps one, so that the next
+  // launch on the stream can move in beside it; a layer with many row blocks per SM is better
+  // served by two CTAs per SM of its own.
+  const bool wide = a.layers != nullptr || p.blocks >= 3u * uint32_t(sm_count);
+  const uint32_t resident = uint32_t(sm_count) * (wide ? p.ctas_per_sm : 1u);
   cfg.gridDim = dim3(std::min<uint32_t>(p.blocks * p.layer_count, resident));
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = smem;

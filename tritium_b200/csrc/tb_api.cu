@@ -434,7 +434,8 @@ extern "C" tb_status tb_act_absmax_dev(tb_backend* b, const void* x, tb_dtype x_
 }
 
 extern "C" tb_status tb_linear_forward_tp_dev(tb_backend* b, const tb_weights* w, tb_comm* comm, uint32_t slot_absmax, uint32_t slot_y,
-                                               const void* x, tb_dtype x_dtype, uint32_t m, void* y, tb_dtype y_dtype, void* stream) {
+                                               const void* x, tb_dtype x_dtype, uint32_t m, void* y, tb_dtype y_dtype, uint32_t flags,
+                                               void* stream) {
   clear_error();
   if (tb_status s = check_handles(b, w)) return s;
   if (!comm) return tb_fail(TB_NULL_ARG, "communicator is null");
@@ -444,15 +445,17 @@ extern "C" tb_status tb_linear_forward_tp_dev(tb_backend* b, const tb_weights* w
   if (x_dtype == TB_I8) return tb_fail(TB_INVALID_INPUT, "the tensor-parallel path quantises fp32 or bf16 activations itself");
   if (y_dtype == TB_I8) return tb_fail(TB_INVALID_INPUT, "output dtype must be fp32 or bf16");
   if (m > 8) return tb_fail(TB_INVALID_INPUT, "the fused tensor-parallel path takes at most 8 tokens per call");
+  const bool in_kernel = (flags & TB_TP_REDUCE_IN_KERNEL) != 0;
+  if (!in_kernel && y_dtype != TB_F32) return tb_fail(TB_INVALID_INPUT, "the one-shot reduce writes fp32 outputs");
   if (!w->fast) return tb_fail(TB_UNSUPPORTED_FORMAT, "the int8 path needs uniform plane counts, k % 256 == 0, group 128 and codec D2 or B3");
   if (slot_absmax == slot_y) return tb_fail(TB_INVALID_INPUT, "the absmax and the output slot must differ");
   TbCommView va{}, vy{};
   if (!tb_comm_view(comm, slot_absmax, &va) || !tb_comm_view(comm, slot_y, &vy))
     return tb_fail(TB_INVALID_INPUT, "communicator is not connected or a slot index is out of range");
   if (size_t(m) * w->n * 4 > tb_comm_slot_bytes(comm)) return tb_fail(TB_INVALID_INPUT, "the output slot is smaller than m x n fp32 values");
-  if (vy.counters < uint32_t(b->prop.multiProcessorCount) || va.counters < 4)
-    return tb_fail(TB_INVALID_INPUT, "the communicator holds " + std::to_string(vy.counters) + " arrival counters per slot, one per SM (" +
-                                         std::to_string(b->prop.multiProcessorCount) + ") is needed");
+  if (vy.counters < 2u * uint32_t(b->prop.multiProcessorCount) || va.counters < 4)
+    return tb_fail(TB_INVALID_INPUT, "the communicator holds " + std::to_string(vy.counters) + " arrival counters per slot, two per SM (" +
+                                         std::to_string(2 * b->prop.multiProcessorCount) + ") are needed");
   if (tb_status s = use_device(b)) return s;
   cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : b->stream;
   for (uint32_t m0 = 0; m0 < m; m0 += 4) {
@@ -464,14 +467,21 @@ extern "C" tb_status tb_linear_forward_tp_dev(tb_backend* b, const tb_weights* w
     DecodeArgs d{};
     d.w = w; d.x_dtype = x_dtype; d.m = mc; d.y_dtype = y_dtype; d.y_row_stride = uint32_t(w->n);
     d.x = static_cast<const uint8_t*>(x) + size_t(m0) * w->k * dtype_size(x_dtype);
-    d.y = static_cast<uint8_t*>(y) + size_t(m0) * w->n * dtype_size(y_dtype);
     d.status = b->d_status; d.pdl = false;
     d.scratch = b->d_prep; d.scratch_bytes = b->d_prep_cap;
     d.comm_absmax = va.world > 1 ? &ca : nullptr;
-    d.comm_y = vy.world > 1 ? &cy : nullptr;
+    if (in_kernel) {
+      d.y = static_cast<uint8_t*>(y) + size_t(m0) * w->n * dtype_size(y_dtype);
+      d.comm_y = vy.world > 1 ? &cy : nullptr;
+    } else {
+      // fp32 partial rows straight into this rank's slot; one reduce kernel after the last pass
+      d.y = vy.data[vy.rank] + size_t(m0) * w->n;
+      d.y_dtype = TB_F32;
+    }
     TB_CUDA(tb_launch_prepare(d, st), "launch prepare");
     TB_CUDA(tb_launch_decode(d, b->prop.multiProcessorCount, b->max_smem_optin, st), "launch decode");
   }
+  if (!in_kernel) return tb_comm_allreduce_f32(comm, slot_y, uint32_t(size_t(m) * w->n), 0, static_cast<float*>(y), st);
   return TB_OK;
 }
 

@@ -142,9 +142,10 @@ class PeerComm:
         self._check(self._L.tb_comm_allreduce_f32(self._h, C.c_uint32(slot), C.c_uint32(count), int(op_max),
                                                   C.c_void_p(out.data_ptr()), C.c_void_p(s.cuda_stream)))
 
-    def linear_fused(self, handle, slot_absmax: int, slot_y: int, x, y, stream=None) -> None:
-        """Row-parallel forward of up to 8 tokens whose kernels exchange the absmax and finish the
-        all-reduce themselves (`tb_linear_forward_tp_dev`)."""
+    def linear_fused(self, handle, slot_absmax: int, slot_y: int, x, y, reduce_in_kernel: bool = False, stream=None) -> None:
+        """Row-parallel forward of up to 8 tokens (`tb_linear_forward_tp_dev`): the prepare kernel
+        exchanges the row absmax; the output all-reduce is one reduce kernel behind the decode
+        kernel, or (``reduce_in_kernel``) done by the decode kernel's CTAs themselves."""
         import ctypes as C
         import torch
         from . import _lib
@@ -152,7 +153,8 @@ class PeerComm:
         s = stream if stream is not None else torch.cuda.current_stream()
         self._check(self._L.tb_linear_forward_tp_dev(self.backend._h, handle._h, self._h, C.c_uint32(slot_absmax), C.c_uint32(slot_y),
                                                      C.c_void_p(x.data_ptr()), dt[x.dtype], C.c_uint32(x.shape[0]),
-                                                     C.c_void_p(y.data_ptr()), dt[y.dtype], C.c_void_p(s.cuda_stream)))
+                                                     C.c_void_p(y.data_ptr()), dt[y.dtype], C.c_uint32(1 if reduce_in_kernel else 0),
+                                                     C.c_void_p(s.cuda_stream)))
 
     def close(self) -> None:
         if self._h:
@@ -202,8 +204,10 @@ class TPLinear:
         # small messages (decode) are reduced over peer memory when the executor carries a
         # communicator: the kernels write their partials straight into its slots
         comm = getattr(executor, "comm", None) if mode == "row" and world > 1 else None
-        # `fused`: exchange inside the prepare/decode kernels instead of separate one-shot reduce
-        # kernels (measured slower on 2 GPUs: every CTA then pays an NVLink round trip)
+        # `fused` (decode-sized batches): False = the prepare kernel exchanges the row absmax and one
+        # reduce kernel follows the decode kernel; True = the decode kernel's CTAs also do the output
+        # reduce (measured slower: every CTA then pays an NVLink round trip); None = separate absmax
+        # and reduce kernels around the ordinary forward
         self.comm, self.peer_m, self.fused = comm, 0, False
         if comm is not None:
             self.peer_m = min(max_m, comm.slot_bytes // (4 * self.geometry.n))
@@ -229,8 +233,8 @@ class TPLinear:
             self.executor.linear(self.handle, x, y, None)
             return y
         absmax = self.absmax[:m]
-        if self.comm is not None and m <= min(self.peer_m, 8) and self.fused:
-            self.comm.linear_fused(self.handle, self.slot_absmax, self.slot_y, x, y)
+        if self.comm is not None and m <= min(self.peer_m, 8) and self.fused is not None:
+            self.comm.linear_fused(self.handle, self.slot_absmax, self.slot_y, x, y, reduce_in_kernel=bool(self.fused))
             return y
         if self.comm is not None and m <= self.peer_m:
             self.executor.row_absmax(x, self.peer_absmax[:m])
