@@ -266,15 +266,15 @@ def measure_tp(torch, dist, backend, rank: int, world: int, codec, codec_name: s
                 "all_reduces_per_timed_step": 4 * built if world > 1 else 0, "reduce": reduce_kind}
 
     ms, graphed = timed(1, not args.no_graph)
-    out["decode_m1"] = decode_entry(ms, graphed, "absmax exchange inside the prepare kernel + one reduce kernel over peer memory" if world > 1 else "none")
+    out["decode_m1"] = decode_entry(ms, graphed, "separate absmax and one-shot reduce kernels over peer memory" if world > 1 else "none")
     if world > 1:
+        stack.use_fused_reduce(False)
+        ms, graphed = timed(1, not args.no_graph)
+        out["decode_m1_absmax_in_kernel"] = decode_entry(ms, graphed, "absmax exchange inside the prepare kernel + one reduce kernel over peer memory")
         stack.use_fused_reduce(True)
         ms, graphed = timed(1, not args.no_graph)
         out["decode_m1_in_kernel"] = decode_entry(ms, graphed, "inside the prepare and decode kernels, over peer memory")
         stack.use_fused_reduce(None)
-        ms, graphed = timed(1, not args.no_graph)
-        out["decode_m1_one_shot"] = decode_entry(ms, graphed, "separate absmax and one-shot reduce kernels over peer memory")
-        stack.use_fused_reduce(False)
         stack.use_peer_reduce(False)
         ms, graphed = timed(1, not args.no_graph)
         out["decode_m1_nccl"] = decode_entry(ms, graphed, "nccl all_reduce")
