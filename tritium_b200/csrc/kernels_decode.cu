@@ -143,11 +143,6 @@ __device__ __forceinline__ void mma_u8s8_first(int (&d)[4], uint32_t a0, uint32_
       : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
-// v / planes for planes in {1,2,3} and v < 65536, without an integer division.
-__device__ __forceinline__ uint32_t div_planes(uint32_t v, uint32_t planes) {
-  return planes == 1 ? v : planes == 2 ? v >> 1 : (v * 0xAAABu) >> 17;
-}
-
 // ---------------------------------------------------------------- B3 quotients
 // Half constants (bit patterns, both halves).  For V = 1024 + v:
 //   fma(V, 0x3553, 0x6156) = 1024 + floor(v/3)   for v in [0,242]
@@ -172,7 +167,6 @@ __device__ __forceinline__ void b3_quads(uint32_t w, uint32_t (&q)[5]) {
   q[3] = prmt(a3, b3, 0x6420u);
   q[4] = prmt(a4, b4, 0x6420u);
 }
-__host__ __device__ constexpr int b3_delta(int i) { return i >= 2 ? 1 : 0; }  // operand = q_i + delta_i
 
 // ---------------------------------------------------------------- activation-side tables
 // Which packed word / digits / scale-group variant MMA number `mma` of a tile-plane consumes for

@@ -108,7 +108,7 @@ extern "C" tb_status tb_backend_caps(const tb_backend* b, tb_caps* out) {
   if (!b || !out) return tb_fail(TB_NULL_ARG, "null argument");
   std::memset(out, 0, sizeof *out);
   std::snprintf(out->backend, sizeof out->backend, "b200");
-  std::snprintf(out->device_name, sizeof out->device_name, "%s", b->prop.name);
+  std::snprintf(out->device_name, sizeof out->device_name, "%.*s", int(sizeof out->device_name) - 1, b->prop.name);
   std::snprintf(out->device_id, sizeof out->device_id, "b200:%d", b->ordinal);
   std::snprintf(out->physical_id, sizeof out->physical_id, "%s", b->physical_id);
   std::snprintf(out->features, sizeof out->features, "sm_100a,salt_v2_d2,salt_v2_b3,salt_v2_s34,tq2_0,int8_tcgen05");
