@@ -34,7 +34,7 @@ METRIC = "ternary linear HBM GB/s (M=1)"
 UNIT = "GB/s"
 PLANE_BYTES = {"b3": 52, "d2": 64}
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE grouped decode launch, from the ncu capture
-# summarised in profiles/decode_kernel_c2_b3_m1.md; key = (codec, tokens, weight copies per launch)
+# summarised under profiles/ (decode kernel, C2, B3, M=1); key = (codec, tokens, weight copies per launch)
 NCU_TRAFFIC_BYTES = {("b3", 1, 26): 301_977_600 + 4_381_440}
 
 
