@@ -143,6 +143,12 @@ __device__ __forceinline__ void mma_u8s8_first(int (&d)[4], uint32_t a0, uint32_
       : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
+// int -> float for |v| < 2^22 without the conversion unit: the integer is added into the mantissa
+// of 1.5 * 2^23 and the constant is subtracted again (both steps exact).
+__device__ __forceinline__ float group_sum_to_float(int v) {
+  return __fsub_rn(__int_as_float(0x4B400000 + v), 12582912.0f);
+}
+
 // ---------------------------------------------------------------- B3 quotients
 // Half constants (bit patterns, both halves).  For V = 1024 + v:
 //   fma(V, 0x3553, 0x6156) = 1024 + floor(v/3)   for v in [0,242]
@@ -613,8 +619,8 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
           if (lane_has_cell) {
             const int ci = cin[0];
             const int ia = 4 * acc0[0] + acc0[1] + ci, ib = 4 * acc0[2] + acc0[3] + ci;
-            ya = __fadd_rn(ya, __fmul_rn(float(ia), __half2float(__ushort_as_half(sca[0]))));
-            yb = __fadd_rn(yb, __fmul_rn(float(ib), __half2float(__ushort_as_half(scb[0]))));
+            ya = __fmaf_rn(group_sum_to_float(ia), __half2float(__ushort_as_half(sca[0])), ya);
+            yb = __fmaf_rn(group_sum_to_float(ib), __half2float(__ushort_as_half(scb[0])), yb);
             if (p.acc_dump) {
               const uint32_t tok = p.dump_token_offset + cell_token;
               if (row0 + na < p.n)
@@ -627,10 +633,10 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
           const int ci0 = cin[0], ci1 = cin[1];
           const int ia0 = 4 * acc0[0] + acc0[1] + ci0, ia1 = 4 * acc1[0] + acc1[1] + ci1;
           const int ib0 = 4 * acc0[2] + acc0[3] + ci0, ib1 = 4 * acc1[2] + acc1[3] + ci1;
-          ya = __fadd_rn(ya, __fadd_rn(__fmul_rn(float(ia0), __half2float(__ushort_as_half(sca[0]))),
-                                       __fmul_rn(float(ia1), __half2float(__ushort_as_half(sca[1])))));
-          yb = __fadd_rn(yb, __fadd_rn(__fmul_rn(float(ib0), __half2float(__ushort_as_half(scb[0]))),
-                                       __fmul_rn(float(ib1), __half2float(__ushort_as_half(scb[1])))));
+          ya = __fmaf_rn(group_sum_to_float(ia1), __half2float(__ushort_as_half(sca[1])),
+                         __fmaf_rn(group_sum_to_float(ia0), __half2float(__ushort_as_half(sca[0])), ya));
+          yb = __fmaf_rn(group_sum_to_float(ib1), __half2float(__ushort_as_half(scb[1])),
+                         __fmaf_rn(group_sum_to_float(ib0), __half2float(__ushort_as_half(scb[0])), yb));
           if (p.acc_dump) {
             const uint32_t tok = p.dump_token_offset + c;
             if (row0 + na < p.n) {
