@@ -244,7 +244,7 @@ def test_a8_decode_full_size_configs(backend, name, codec):
 # ------------------------------------------------------------------ int8 path (prefill kernel, tcgen05)
 @pytest.mark.parametrize("codec", [SaltV2Codec.B3, SaltV2Codec.D2])
 @pytest.mark.parametrize("planes", [1, 2, 3])
-@pytest.mark.parametrize("m,n,k", [(13, 40, 768), (16, 128, 256), (130, 200, 1024), (257, 129, 512)])
+@pytest.mark.parametrize("m,n,k", [(17, 40, 768), (20, 128, 256), (130, 200, 1024), (257, 129, 512)])
 def test_a8_prefill_small_shapes(backend, codec, planes, m, n, k):
     prod, orac = uniform_pair(n, k, planes, seed=planes * 100 + m)
     x = make_activations(m, k, seed=m)

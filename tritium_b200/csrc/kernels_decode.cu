@@ -892,7 +892,7 @@ cudaError_t tb_launch_decode(const DecodeArgs& a, int sm_count, int max_smem, cu
   // A grouped launch keeps two CTAs per SM busy.  A single small layer keeps one, so that the next
   // launch on the stream can move in beside it; a layer with many row blocks per SM is better
   // served by two CTAs per SM of its own.
-  const bool wide = a.layers != nullptr || p.blocks >= 3u * uint32_t(sm_count);
+  const bool wide = a.layers != nullptr || p.blocks >= 2u * uint32_t(sm_count);
   const uint32_t resident = uint32_t(sm_count) * (wide ? p.ctas_per_sm : 1u);
   cfg.gridDim = dim3(std::min<uint32_t>(p.blocks * p.layer_count, resident));
   cfg.blockDim = dim3(kThreads);

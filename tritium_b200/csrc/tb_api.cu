@@ -292,8 +292,8 @@ tb_status forward_dev(tb_backend* b, const tb_weights* w, const tb_forward_args&
   if (a.x_dtype == TB_I8 && !a.act_scale) return tb_fail(TB_NULL_ARG, "int8 activations need act_scale");
   if (a.y_dtype == TB_I8) return tb_fail(TB_INVALID_INPUT, "output dtype must be fp32 or bf16");
   if (!w->fast) return tb_fail(TB_UNSUPPORTED_FORMAT, "the int8 path needs uniform plane counts, k % 256 == 0, group 128 and codec D2 or B3");
-  // measured crossover on C2: three 4-token decode passes (about 52 us) still beat one tensor-core call (65 us)
-  const bool want_prefill = (a.flags & TB_FWD_FORCE_PREFILL) || (a.m > 12 && !(a.flags & TB_FWD_FORCE_DECODE));
+  // measured crossover on C2: four chained 4-token decode passes (about 51 us) still beat one tensor-core call (67 us)
+  const bool want_prefill = (a.flags & TB_FWD_FORCE_PREFILL) || (a.m > 16 && !(a.flags & TB_FWD_FORCE_DECODE));
   if (want_prefill && tb_prefill_supported(w, a.m)) {
     const size_t need = tb_prefill_scratch_bytes(w, a.m);
     if (b->d_q_cap < need) return tb_fail(TB_OUT_OF_MEMORY, "prefill scratch is not reserved; call through a host entry point or tb_stack first");
@@ -316,7 +316,9 @@ tb_status forward_dev(tb_backend* b, const tb_weights* w, const tb_forward_args&
     d.act_absmax_in = a.act_absmax ? a.act_absmax + m0 : nullptr;
     d.y = static_cast<uint8_t*>(a.y) + size_t(m0) * w->n * dtype_size(a.y_dtype);
     d.acc_dump = a.acc_dump; d.dump_token_offset = m0; d.dump_tokens_total = a.m;
-    d.row_scale = a.row_scale; d.status = b->d_status; d.pdl = (a.flags & TB_FWD_PDL) != 0;
+    // passes after the first always chain with programmatic dependent launch: their weight
+    // stream starts under the previous pass's tail (every consumer still waits for its own tables)
+    d.row_scale = a.row_scale; d.status = b->d_status; d.pdl = (a.flags & TB_FWD_PDL) != 0 || m0 > 0;
     d.scratch = b->d_prep; d.scratch_bytes = b->d_prep_cap;
     d.tables_shared = false;
     if (!d.tables_shared) { TB_CUDA(tb_launch_prepare(d, st), "launch prepare"); ++launches; }
