@@ -238,15 +238,11 @@ tb_status tb_comm_export(const tb_comm* comm, uint8_t* handle_out /* TB_COMM_HAN
 tb_status tb_comm_connect(tb_comm* comm, const uint8_t* all_handles /* world x TB_COMM_HANDLE_BYTES */);
 void* tb_comm_slot(const tb_comm* comm, uint32_t slot);
 tb_status tb_comm_allreduce_f32(tb_comm* comm, uint32_t slot, uint32_t count, int op_max, float* out, void* stream);
-/* Row-parallel int8 forward (1..8 tokens) that finishes the tensor-parallel all-reduce inside its
- * own kernels: the activation-preparation kernel exchanges the per-token absmax through
- * `slot_absmax` (so that every shard quantises with the scale of the whole row), the GEMV kernel
- * writes its fp32 partial rows into `slot_y`; with TB_TP_REDUCE_IN_KERNEL each CTA then raises one arrival counter on every
- * peer, waits (bounded) for the peers' arrivals and adds the peers' rows in rank order into `y`
- * (every rank ends with the full result).  `counters_per_slot` of the communicator must be at
- * least twice the SM count.
- * The two slots belong to this linear alone. */
-#define TB_TP_REDUCE_IN_KERNEL 1u   /* else: partial rows into `slot_y`, then one tb_comm_allreduce_f32 launch (fp32 y) */
+/* Row-parallel int8 forward (1..8 tokens): the activation-preparation kernel exchanges the
+ * per-token absmax through `slot_absmax` (so that every shard quantises with the scale of the whole
+ * row), the GEMV kernel writes its fp32 partial rows into `slot_y`, and one tb_comm_allreduce_f32
+ * launch adds the ranks' rows in rank order into `y` (fp32; every rank ends with the full
+ * result).  `flags` must be 0.  The two slots belong to this linear alone. */
 tb_status tb_linear_forward_tp_dev(tb_backend* backend, const tb_weights* weights, tb_comm* comm, uint32_t slot_absmax,
                                    uint32_t slot_y, const void* x, tb_dtype x_dtype, uint32_t m, void* y, tb_dtype y_dtype,
                                    uint32_t flags, void* stream);

@@ -48,6 +48,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
             cmd += ["--fmad=false"]
         if verbose:
             cmd += ["-Xptxas", "-v"]
+        cmd += os.environ.get("TB_NVCC_FLAGS", "").split()
         subprocess.check_call(cmd)
     if force or _stale(LIB, objects):
         subprocess.check_call([nvcc, "-shared", "-o", LIB] + objects + ["-cudart", "static"] + GENCODE)

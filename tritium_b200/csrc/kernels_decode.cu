@@ -1,4 +1,4 @@
-// Decode GEMV (1..4 tokens) straight from the packed B3 / D2 arenas, sm_100a.
+// Decode GEMV (1..4 tokens per pass) straight from the packed B3 / D2 arenas, sm_100a.
 //
 // Data movement: a CTA owns blocks of R consecutive output rows.  A row's tile-planes are
 // contiguous in the payload arena and rows follow one another, so a block is ONE contiguous byte
@@ -22,37 +22,55 @@
 // belong to the other scale group of a straddling byte, and B3 padding digits, are removed on
 // the activation side (their z entries are zero), never by masking weights.
 //
+// Roles inside a CTA: eight consumer warps share every row block (each takes a run of
+// (tile column, 16 row-planes) items, tile column outermost, so that the B fragments of a column
+// stay in registers while the row-planes change), one producer warp feeds the ring, one combiner
+// warp adds the consumers' partial sums of a finished block in a fixed order and stores the
+// outputs.  The hand-offs are mbarriers: no warp waits for another consumer warp.
+//
+// The activation tables (B fragments, accumulator start values, token scales) are either built by
+// the CTA itself from the activations (one launch per linear) or copied from global scratch that
+// prepare_kernel filled (tensor-parallel shards that exchange the absmax, callers that supply
+// their own scratch).
+//
 // Every wait is bounded; on timeout the kernel records TBF_WAIT_TIMEOUT and returns.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cfloat>
+#include <cstdlib>
 #include <string>
 
 #include "tb_internal.h"
 
 namespace {
 
-constexpr int kConsumerWarps = 8;
-constexpr int kThreads = (kConsumerWarps + 1) * 32;
+constexpr int kWarps = 8;                       // consumer warps; then one producer and one combiner warp
+constexpr int kThreads = (kWarps + 2) * 32;
+constexpr int kConsumerThreads = kWarps * 32;
 constexpr int kMaxStages = 4;
-constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr int kPartBufs = 4;   // row blocks whose partial sums may wait for the combiner
 constexpr int kMaxGroupLayers = 128;   // layers of one grouped launch (descriptors live in shared memory)
+constexpr uint32_t kStageBytesPerWarp = 256 + 16;   // fused prologue: one quantised tile column + absmax partials
 
 struct DecodeParams {
   const uint8_t* payload; const uint16_t* scales;   // single layer (layers == nullptr)
   const TbLayerDesc* layers; uint32_t layer_count; uint32_t y_layer_stride;   // grouped launch: outputs [layer][m][n]
   const uint8_t* tables; uint32_t table_bytes;   // z tables | accumulator start values | token scales
+  // fused prologue (fused != 0): the CTA quantises x and builds its tables itself
+  const void* x; const float* act_scale_in; const float* act_absmax_in; uint32_t x_dtype, fused;
   void* y; int32_t* acc_dump; const float* row_scale;
   uint32_t* status;
-  uint32_t m, n, k, planes, tpr;            // tpr = k / 256
+  uint32_t m, n, k, planes, tpr;            // m: valid tokens; tpr = k / 256
   uint32_t rows_per_stage, row_bytes, stage_bytes, scale_stage_bytes, blocks;
   uint32_t stages, y_dtype, y_row_stride;
   uint32_t dump_token_offset, dump_tokens_total;
   uint32_t pdl, wait_tables, ctas_per_sm;
+  uint32_t inject_missing_tx;   // test hook: bytes the table barrier expects but nobody copies
   // shared memory offsets (bytes)
-  uint32_t off_ring, off_scale_ring, off_z, off_cinit, off_part, off_actscale, off_zero;
-  TbCommView comm;   // world > 1: write fp32 partial rows into the slot and finish the all-reduce here
+  uint32_t off_ring, off_scale_ring, off_z, off_cinit, off_part, off_actscale, off_xq;
 };
+
 
 // ---- peer-memory helpers (tensor-parallel row shards)
 constexpr long long kPeerWaitCycles = 4000000000ll;   // about two seconds of SM clocks
@@ -103,20 +121,53 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
   return ok != 0;
 }
-// Bounded wait.  Returns false after kSpinLimit polls or when another thread flagged an abort.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (i >= 4) __nanosleep(100);   // waiting warps should not take issue slots from working ones
-    if ((i & 255u) == 255u && *abort_flag) return false;
-  }
-  return false;
+// The same with a time hint: the hardware may keep the thread suspended for up to `ns` nanoseconds
+// before it reports "not yet", which keeps a waiting warp out of the issue slots.
+__device__ __forceinline__ bool mbar_try_wait_for(uint64_t* bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity), "r"(ns) : "memory");
+  return ok != 0;
 }
+// Bounded wait: gives up after about two seconds of SM clocks or when another thread flagged an
+// abort.  Returns false in both cases.
+constexpr uint32_t kWaitHintNs = 20000;
+constexpr long long kWaitLimitCycles = 4000000000ll;   // about two seconds of SM clocks
+constexpr long long kDrainLimitCycles = 4000000ll;     // about two milliseconds: copies in flight after an abort
+__device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, long long limit) {
+  const long long t0 = clock64();
+  for (;;) {
+    if (mbar_try_wait_for(bar, parity, kWaitHintNs)) return true;
+    if ((abort_flag && *abort_flag) || clock64() - t0 > limit) return false;
+  }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, long long limit = kWaitLimitCycles) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, abort_flag, limit);
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory"); }
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(smem_addr(dst)), "l"(src), "r"(bytes), "r"(smem_addr(bar)) : "memory");
 }
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory"); }
+// Shared-memory loads through 32-bit addresses (the generic 64-bit pointer arithmetic otherwise
+// doubles every address computation in the inner loop).
+template <int OFF = 0> __device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(OFF));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint2 lds_u64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
   uint32_t r;
   asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
@@ -143,12 +194,6 @@ __device__ __forceinline__ void mma_u8s8_first(int (&d)[4], uint32_t a0, uint32_
       : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
-// int -> float for |v| < 2^22 without the conversion unit: the integer is added into the mantissa
-// of 1.5 * 2^23 and the constant is subtracted again (both steps exact).
-__device__ __forceinline__ float group_sum_to_float(int v) {
-  return __fsub_rn(__int_as_float(0x4B400000 + v), 12582912.0f);
-}
-
 // ---------------------------------------------------------------- B3 quotients
 // Half constants (bit patterns, both halves).  For V = 1024 + v:
 //   fma(V, 0x3553, 0x6156) = 1024 + floor(v/3)   for v in [0,242]
@@ -172,6 +217,27 @@ __device__ __forceinline__ void b3_quads(uint32_t w, uint32_t (&q)[5]) {
   q[2] = prmt(a2, b2, 0x6420u);
   q[3] = prmt(a3, b3, 0x6420u);
   q[4] = prmt(a4, b4, 0x6420u);
+}
+
+// The same for the packed words of two rows, in MMA operand order: A[2i] = q_i of row a,
+// A[2i+1] = q_i of row b.  A[10] and A[11] pad the third MMA; they meet zero B entries, so their
+// value does not matter and they are left unwritten.
+__device__ __forceinline__ void b3_quads2(uint32_t wa, uint32_t wb, uint32_t (&A)[12]) {
+  const uint32_t ha01 = prmt(wa, 0x64646464u, 0x4140u), ha23 = prmt(wa, 0x64646464u, 0x4342u);
+  const uint32_t hb01 = prmt(wb, 0x64646464u, 0x4140u), hb23 = prmt(wb, 0x64646464u, 0x4342u);
+  const uint32_t a1 = hfma2_bits(ha01, kC3, kK3), a1h = hfma2_bits(ha23, kC3, kK3);
+  const uint32_t b1 = hfma2_bits(hb01, kC3, kK3), b1h = hfma2_bits(hb23, kC3, kK3);
+  const uint32_t a2 = hfma2_bits(ha01, kC9, kK9), a2h = hfma2_bits(ha23, kC9, kK9);
+  const uint32_t b2 = hfma2_bits(hb01, kC9, kK9), b2h = hfma2_bits(hb23, kC9, kK9);
+  const uint32_t a3 = hfma2_bits(a1, kC9, kK9), a3h = hfma2_bits(a1h, kC9, kK9);
+  const uint32_t b3 = hfma2_bits(b1, kC9, kK9), b3h = hfma2_bits(b1h, kC9, kK9);
+  const uint32_t a4 = hfma2_bits(a2, kC9b, kK9b), a4h = hfma2_bits(a2h, kC9b, kK9b);
+  const uint32_t b4 = hfma2_bits(b2, kC9b, kK9b), b4h = hfma2_bits(b2h, kC9b, kK9b);
+  A[0] = wa; A[1] = wb;
+  A[2] = prmt(a1, a1h, 0x6420u); A[3] = prmt(b1, b1h, 0x6420u);
+  A[4] = prmt(a2, a2h, 0x6420u); A[5] = prmt(b2, b2h, 0x6420u);
+  A[6] = prmt(a3, a3h, 0x6420u); A[7] = prmt(b3, b3h, 0x6420u);
+  A[8] = prmt(a4, a4h, 0x6420u); A[9] = prmt(b4, b4h, 0x6420u);
 }
 
 // ---------------------------------------------------------------- activation-side tables
@@ -270,7 +336,7 @@ __device__ __forceinline__ uint2 z_bytewise(const int8_t* xq_tile, const Slot<CO
 struct PrepareParams {
   const void* x; const float* act_scale_in; const float* act_absmax_in;
   uint8_t* tables; uint32_t* status;
-  uint32_t m, k, tpr, x_dtype, off_cinit, off_actscale, pdl;
+  uint32_t m, mk, k, tpr, x_dtype, off_cinit, off_actscale, pdl;   // m valid tokens (grid.y), tables laid out for mk
   TbCommView comm;   // world > 1: the per-token absmax is the maximum over the ranks' slices
 };
 
@@ -288,7 +354,7 @@ __global__ void __launch_bounds__(256) prepare_kernel(const PrepareParams p) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
   }
   const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const uint32_t j = blockIdx.x, t = blockIdx.y, ncol = (DUAL ? 4 : 2) * p.m;
+  const uint32_t j = blockIdx.x, t = blockIdx.y, ncol = (DUAL ? 4 : 2) * p.mk;
   float scale_out;
   uint32_t comm_seq = 0;   // thread 0 only
   if (p.x_dtype == TB_I8) {
@@ -342,6 +408,9 @@ __global__ void __launch_bounds__(256) prepare_kernel(const PrepareParams p) {
     const float scale_q = gamma > 0.f ? __fdiv_rn(127.0f, gamma) : 0.f;
     scale_out = __fdiv_rn(gamma, 127.0f);
     const float v = load_act(p.x, p.x_dtype, size_t(t) * p.k + j * 256 + tid);
+    if (!(fabsf(v) <= FLT_MAX) && atomicOr(&p.status[TBS_FLAGS], TBF_NONFINITE_ACT) == 0) {
+      p.status[TBS_INFO0] = t * p.k + j * 256 + tid; p.status[TBS_INFO1] = __float_as_uint(v);
+    }
     xq[tid] = int8_t(int(fminf(127.f, fmaxf(-128.f, rintf(__fmul_rn(v, scale_q))))));
   }
   __syncthreads();
@@ -353,7 +422,7 @@ __global__ void __launch_bounds__(256) prepare_kernel(const PrepareParams p) {
     const uint32_t c = tid & 3, hl = (tid >> 2) & 1, v = DUAL ? (tid >> 3) & 1 : 0, mma = tid / kPerMma;
     const Slot<CODEC> s = slot_of<CODEC, DUAL>(int(mma), int(c));
     const int variant = DUAL ? int(v) : s.variant;
-    const uint32_t col = v * 2 * p.m + 2 * t + hl;
+    const uint32_t col = v * 2 * p.mk + 2 * t + hl;
     ztab[((size_t(j) * kNM + mma) * ncol + col) * 4 + c] =
         s.bytewise ? z_bytewise<CODEC>(xq, s, int(c), int(hl), variant)
                    : make_uint2(z_quad<CODEC>(xq, s, s.d0, int(hl), variant), z_quad<CODEC>(xq, s, s.d1, int(hl), variant));
@@ -384,31 +453,154 @@ __global__ void __launch_bounds__(256) prepare_kernel(const PrepareParams p) {
     }
   }
 }
+// ---------------------------------------------------------------- fused prologue
+// Eight elements of a row starting at element `idx` (a multiple of 8; rows are 16-byte aligned).
+__device__ __forceinline__ void load8(const void* x, uint32_t dtype, size_t idx, float (&v)[8]) {
+  if (dtype == TB_F32) {
+    const float4 a = reinterpret_cast<const float4*>(x)[idx / 4], b = reinterpret_cast<const float4*>(x)[idx / 4 + 1];
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  } else if (dtype == TB_BF16) {
+    const uint4 u = reinterpret_cast<const uint4*>(x)[idx / 8];
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { v[2 * i] = __uint_as_float(w[i] << 16); v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+  } else {
+    const uint2 u = reinterpret_cast<const uint2*>(x)[idx / 8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[i] = float(int(int8_t(u.x >> (8 * i))));
+      v[4 + i] = float(int(int8_t(u.y >> (8 * i))));
+    }
+  }
+}
+
+// Builds this CTA's activation tables in shared memory (same contents as prepare_kernel writes to
+// global scratch): per-token absmax int8 quantisation of x, B-fragment entries, accumulator start
+// values, token scales.  Called by the eight consumer warps (tid 0..255).
+template <int CODEC, bool DUAL, int M>
+__device__ __forceinline__ void build_tables(const DecodeParams& p, uint8_t* smem, uint32_t tid) {
+  constexpr int kNM = MmaCount<CODEC, DUAL>::value;
+  constexpr uint32_t ncol = (DUAL ? 4 : 2) * M, kPerMma = DUAL ? 16 : 8;
+  const uint32_t warp = tid >> 5, lane = tid & 31;
+  int8_t* xq = reinterpret_cast<int8_t*>(smem + p.off_xq) + warp * kStageBytesPerWarp;
+  float* red = reinterpret_cast<float*>(smem + p.off_xq + 256);   // [warp] at stride kStageBytesPerWarp: four floats
+  uint2* ztab = reinterpret_cast<uint2*>(smem + p.off_z);
+  int* cinit = reinterpret_cast<int*>(smem + p.off_cinit);
+  float* act_scale = reinterpret_cast<float*>(smem + p.off_actscale);
+  float scale_q[M], scale_out[M];
+  if (p.x_dtype == TB_I8) {
+#pragma unroll
+    for (int t = 0; t < M; ++t) { scale_q[t] = 1.f; scale_out[t] = uint32_t(t) < p.m ? p.act_scale_in[t] : 0.f; }
+  } else {
+    if (!p.act_absmax_in) {
+#pragma unroll
+      for (int t = 0; t < M; ++t) {
+        float mx = 0.f;
+        for (uint32_t i = tid * 8; i < p.k && uint32_t(t) < p.m; i += kConsumerThreads * 8) {
+          float v[8];
+          load8(p.x, p.x_dtype, size_t(t) * p.k + i, v);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) mx = fmaxf(mx, fabsf(v[e]));
+        }
+        for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        if (lane == 0) red[warp * (kStageBytesPerWarp / 4) + t] = mx;
+      }
+      consumer_sync();
+    }
+#pragma unroll
+    for (int t = 0; t < M; ++t) {
+      float gamma = 0.f;
+      if (p.act_absmax_in) gamma = uint32_t(t) < p.m ? p.act_absmax_in[t] : 0.f;   // absmax over the full (unsharded) row, supplied by the caller
+      else
+        for (uint32_t w2 = 0; w2 < uint32_t(kWarps); ++w2) gamma = fmaxf(gamma, red[w2 * (kStageBytesPerWarp / 4) + t]);
+      scale_q[t] = gamma > 0.f ? __fdiv_rn(127.0f, gamma) : 0.f;
+      scale_out[t] = __fdiv_rn(gamma, 127.0f);
+    }
+  }
+  for (uint32_t pr = warp; pr < p.tpr * M; pr += kWarps) {
+    const uint32_t j = pr / M, t = pr - j * M;
+    if (t >= p.m) continue;   // table entries of absent tokens are never read for an output
+    float v[8];
+    load8(p.x, p.x_dtype, size_t(t) * p.k + j * 256 + lane * 8, v);
+    float sq = scale_q[0];
+#pragma unroll
+    for (int tt = 1; tt < M; ++tt) sq = t == uint32_t(tt) ? scale_q[tt] : sq;
+    int q[8];
+    bool bad = false;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      bad |= !(fabsf(v[e]) <= FLT_MAX);
+      q[e] = p.x_dtype == TB_I8 ? int(v[e]) : int(fminf(127.f, fmaxf(-128.f, rintf(__fmul_rn(v[e], sq)))));
+    }
+    if (bad && atomicOr(&p.status[TBS_FLAGS], TBF_NONFINITE_ACT) == 0) {
+      p.status[TBS_INFO0] = t * p.k + j * 256 + lane * 8; p.status[TBS_INFO1] = 0x7fc00000u;
+    }
+    uint2 packed;
+    packed.x = uint32_t(q[0] & 0xff) | (uint32_t(q[1] & 0xff) << 8) | (uint32_t(q[2] & 0xff) << 16) | (uint32_t(q[3] & 0xff) << 24);
+    packed.y = uint32_t(q[4] & 0xff) | (uint32_t(q[5] & 0xff) << 8) | (uint32_t(q[6] & 0xff) << 16) | (uint32_t(q[7] & 0xff) << 24);
+    reinterpret_cast<uint2*>(xq)[lane] = packed;
+    __syncwarp();
+    // entries of this (tile column, token): mma x [scale group] x {high, low part} x lane column
+    for (uint32_t idx = lane; idx < kNM * kPerMma; idx += 32) {
+      const uint32_t c = idx & 3, hl = (idx >> 2) & 1, v2 = DUAL ? (idx >> 3) & 1 : 0, mma = idx / kPerMma;
+      const Slot<CODEC> s = slot_of<CODEC, DUAL>(int(mma), int(c));
+      const int variant = DUAL ? int(v2) : s.variant;
+      const uint32_t col = v2 * 2 * M + 2 * t + hl;
+      ztab[((size_t(j) * kNM + mma) * ncol + col) * 4 + c] =
+          s.bytewise ? z_bytewise<CODEC>(xq, s, int(c), int(hl), variant)
+                     : make_uint2(z_quad<CODEC>(xq, s, s.d0, int(hl), variant), z_quad<CODEC>(xq, s, s.d1, int(hl), variant));
+    }
+    // accumulator start values (see prepare_kernel): lanes 0..15 hold scale group 0, 16..31 group 1
+    int sum = 0;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      int coef = 1;
+      if (CODEC == tbf::kB3) { const int d = int(lane * 8 + e) % 5; coef = d == 0 ? 1 : d == 1 ? -2 : d == 4 ? 2 : -1; }
+      sum += q[e] * coef;
+    }
+    for (int o = 8; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if ((lane & 15) == 0) cinit[(t * p.tpr + j) * 2 + (lane >> 4)] = -sum;
+    __syncwarp();
+  }
+  if (tid < uint32_t(M)) {
+    float so = scale_out[0];
+#pragma unroll
+    for (int tt = 1; tt < M; ++tt) so = tid == uint32_t(tt) ? scale_out[tt] : so;
+    act_scale[tid] = so;
+  }
+}
 
 // ---------------------------------------------------------------- the kernel
-template <int CODEC, int PLANES, int M>
+// M: token columns the tables are laid out for (1, 2 or 4; p.m <= M tokens are valid).
+// SETS: blocks of 16 row-planes in one row block (rows_per_stage * PLANES / 16).
+template <int CODEC, int PLANES, int M, int SETS>
 __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams p) {
   using T = Traits<CODEC>;
   constexpr bool DUAL = M <= 2;
   constexpr int kNM = MmaCount<CODEC, DUAL>::value;
   constexpr uint32_t ncol = (DUAL ? 4 : 2) * M;   // MMA columns in use
+  constexpr uint32_t NC = DUAL ? 2 * M : M;       // (scale group, token) cells a lane quad finishes
+  constexpr bool kPlaneSets = PLANES == 3;        // a set is one plane of 16 rows: the lane adds a row's planes itself
+  constexpr int YN = kPlaneSets ? 1 : SETS;       // partial sums a lane keeps for each of its two rows
+  constexpr uint32_t kSliceFloats = YN * 16 * NC;   // one consumer warp's partial sums of a row block
   extern __shared__ __align__(128) uint8_t smem[];
-  __shared__ uint64_t full_bar[kMaxStages], empty_bar[kMaxStages], table_bar;
-  __shared__ uint32_t abort_flag, comm_ok;
+  __shared__ uint64_t full_bar[kMaxStages], empty_bar[kMaxStages], table_bar, part_full[kPartBufs], part_empty[kPartBufs];
+  __shared__ uint32_t abort_flag;
   __shared__ TbLayerDesc layer_desc[kMaxGroupLayers];
 
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   uint8_t* ring = smem + p.off_ring;
   uint8_t* scale_ring = smem + p.off_scale_ring;
-  uint2* ztab = reinterpret_cast<uint2*>(smem + p.off_z);
-  int* cinit = reinterpret_cast<int*>(smem + p.off_cinit);
+  const uint2* ztab = reinterpret_cast<const uint2*>(smem + p.off_z);
+  const int* cinit = reinterpret_cast<const int*>(smem + p.off_cinit);
   float* part = reinterpret_cast<float*>(smem + p.off_part);
-  float* act_scale = reinterpret_cast<float*>(smem + p.off_actscale);
+  const float* act_scale = reinterpret_cast<const float*>(smem + p.off_actscale);
 
   if (tid == 0) {
     abort_flag = 0;
-    for (uint32_t s = 0; s < p.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], kConsumerWarps); }
+    for (uint32_t s = 0; s < p.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], kWarps); }
     mbar_init(&table_bar, 1);
+    for (int b = 0; b < kPartBufs; ++b) { mbar_init(&part_full[b], kWarps); mbar_init(&part_empty[b], 1); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   for (uint32_t l = tid; l < p.layer_count; l += kThreads) {
@@ -416,28 +608,28 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
     else { layer_desc[l].payload = p.payload; layer_desc[l].scales = p.scales; }
   }
   __syncthreads();
-  // The next kernel on the stream may begin once every CTA has passed this point.  When this
-  // launch has to wait for its tables, the trigger is raised only after that wait, so that a
-  // later launch which shares the tables (and therefore does not wait) cannot outrun them.
-  if (p.pdl && !p.wait_tables) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // The next kernel on the stream may begin once every CTA has passed this point.  A launch that
+  // builds its own tables shares no scratch with its neighbours, so it raises the trigger at
+  // once.  A launch that waits for tables in global scratch raises it only after that wait, so
+  // that a later launch which shares the tables (and does not wait) cannot outrun them.
+  if (p.pdl && (p.fused || !p.wait_tables)) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   const uint32_t total_blocks = p.blocks * p.layer_count;
   const uint32_t my_blocks = blockIdx.x < total_blocks ? (total_blocks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
 
-  if (warp == kConsumerWarps) {
+  if (warp == kWarps) {
     // ------------------------------------------------ producer: weights do not depend on the
     // previous kernel, so the stream starts before griddepcontrol.wait.
     if (lane == 0) {
       uint32_t fills[kMaxStages] = {0, 0, 0, 0};
+      uint32_t s = 0, round = 0;
+      uint32_t layer = blockIdx.x / p.blocks, blk = blockIdx.x - layer * p.blocks;
       for (uint32_t it = 0; it < my_blocks; ++it) {
-        const uint32_t s = it % p.stages, round = it / p.stages;
         if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1, &abort_flag)) {
           abort_flag = 1;
           if (atomicOr(&p.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) { p.status[TBS_INFO0] = it; p.status[TBS_INFO1] = 100 + s; }
           break;
         }
-        const uint32_t gblk = blockIdx.x + it * gridDim.x;
-        const uint32_t layer = gblk / p.blocks, blk = gblk - layer * p.blocks;
         const uint8_t* pay = layer_desc[layer].payload;
         const uint8_t* scs = reinterpret_cast<const uint8_t*>(layer_desc[layer].scales);
         mbar_expect_tx(&full_bar[s], p.stage_bytes + p.scale_stage_bytes);
@@ -445,151 +637,194 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
         bulk_g2s(scale_ring + size_t(s) * p.scale_stage_bytes, scs + size_t(blk) * p.scale_stage_bytes,
                  p.scale_stage_bytes, &full_bar[s]);
         ++fills[s];
+        if (++s == p.stages) { s = 0; ++round; }
+        for (blk += gridDim.x; blk >= p.blocks; blk -= p.blocks) ++layer;
       }
       // Do not leave the CTA while a copy may still be landing in its shared memory: wait
       // (bounded) for the latest fill of every slot.  In the normal path these have all
       // completed already, because the consumers waited on them.
-      for (uint32_t s = 0; s < p.stages; ++s)
-        if (fills[s])
-          for (uint32_t i = 0; i < kSpinLimit && !mbar_try_wait(&full_bar[s], (fills[s] - 1) & 1); ++i) {}
+      for (uint32_t sl = 0; sl < p.stages; ++sl)
+        if (fills[sl]) mbar_wait(&full_bar[sl], (fills[sl] - 1) & 1, nullptr, kDrainLimitCycles);
     }
     return;
   }
 
-  // -------------------------------------------------- consumers: fetch the activation tables
-  // The prepare kernel (previous launch on this stream) wrote z tables, accumulator start values
-  // and token scales to global scratch; one bulk copy brings them in.
-  const uint32_t ctid = tid;  // 0 .. kConsumerWarps*32-1
-  constexpr uint32_t kCT = kConsumerWarps * 32;
-  if (p.pdl && p.wait_tables) {
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (warp == kWarps + 1) {
+    // ------------------------------------------------ combiner: adds the eight consumer warps'
+    // partial sums of a finished row block (fixed order: plane, scale-group cell, warp), applies
+    // the token scale and stores the outputs, while the consumers work on later blocks.
+    if (!mbar_wait(&table_bar, 0, &abort_flag)) return;   // token scales live in the tables
+    uint32_t buf = 0, parity = 0;
+    uint32_t layer = blockIdx.x / p.blocks, blk = blockIdx.x - layer * p.blocks;
+    for (uint32_t it = 0; it < my_blocks; ++it) {
+      if (!mbar_wait(&part_full[buf], parity, &abort_flag)) {
+        abort_flag = 1;
+        if (lane == 0 && atomicOr(&p.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) { p.status[TBS_INFO0] = it; p.status[TBS_INFO1] = 300 + buf; }
+        return;
+      }
+      const uint32_t row0 = blk * p.rows_per_stage;
+      const float* stage_part = part + size_t(buf) * kWarps * kSliceFloats;
+      for (uint32_t e = lane; e < p.rows_per_stage * p.m; e += 32) {
+        const uint32_t t = e / p.rows_per_stage, r = e - t * p.rows_per_stage;
+        if (row0 + r >= p.n) continue;
+        float sum = 0.f;
+        constexpr uint32_t kSplit = PLANES == 2 ? 2 : 1;   // planes that arrive as separate partial sums
+#pragma unroll
+        for (uint32_t q = 0; q < kSplit; ++q) {
+#pragma unroll
+          for (uint32_t grp = 0; grp < (DUAL ? 2u : 1u); ++grp) {
+            const float* src = stage_part + (r * kSplit + q) * NC + grp * M + t;
+            float v[kWarps];
+#pragma unroll
+            for (int w2 = 0; w2 < kWarps; ++w2) v[w2] = src[w2 * kSliceFloats];
+#pragma unroll
+            for (int w2 = 0; w2 < kWarps; ++w2) sum = __fadd_rn(sum, v[w2]);
+          }
+        }
+        float out = __fmul_rn(sum, act_scale[t]);
+        if (p.row_scale) out = __fmul_rn(out, p.row_scale[row0 + r]);
+        const size_t idx = size_t(layer) * p.y_layer_stride + size_t(t) * p.y_row_stride + row0 + r;
+        if (p.y_dtype == TB_F32) static_cast<float*>(p.y)[idx] = out;
+        else static_cast<__nv_bfloat16*>(p.y)[idx] = __float2bfloat16_rn(out);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&part_empty[buf]);
+      if (++buf == kPartBufs) { buf = 0; parity ^= 1; }
+      for (blk += gridDim.x; blk >= p.blocks; blk -= p.blocks) ++layer;
+    }
+    return;
   }
-  if (ctid == 0) {
-    mbar_expect_tx(&table_bar, p.table_bytes);
-    bulk_g2s(smem + p.off_z, p.tables, p.table_bytes, &table_bar);
-  }
-  {
-    const bool tables_ok = mbar_wait(&table_bar, 0, &abort_flag);
-    if (!tables_ok) {
+
+  // -------------------------------------------------- consumers: activation tables
+  if (p.fused) {
+    // x may be the previous kernel's output: wait for it (the weight stream is already running)
+    if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
+    build_tables<CODEC, DUAL, M>(p, smem, tid);
+    consumer_sync();
+    if (tid == 0) mbar_arrive(&table_bar);   // releases the combiner
+  } else {
+    // The prepare kernel (previous launch on this stream) wrote the tables to global scratch; one
+    // bulk copy brings them in.
+    if (p.pdl && p.wait_tables) {
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    }
+    if (tid == 0) {
+      mbar_expect_tx(&table_bar, p.table_bytes + p.inject_missing_tx);
+      bulk_g2s(smem + p.off_z, p.tables, p.table_bytes, &table_bar);
+    }
+    if (!mbar_wait(&table_bar, 0, &abort_flag)) {
       abort_flag = 1;
       if (lane == 0 && atomicOr(&p.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) { p.status[TBS_INFO0] = 0; p.status[TBS_INFO1] = 200; }
+      return;
     }
-    consumer_sync();
-    if (abort_flag) return;
   }
 
   // -------------------------------------------------- consumers: main loop
   const uint32_t g = lane >> 2, c = lane & 3;
-  const uint32_t rp_per_stage = p.rows_per_stage * PLANES;        // multiple of 16
-  const uint32_t sets = rp_per_stage >> 4;
-  const uint32_t items = p.tpr * sets;   // (set, tile column) pairs, set-major
-  const uint32_t per_warp = (items + kConsumerWarps - 1) / kConsumerWarps;
-  const uint32_t item_lo = warp * per_warp, item_hi = min(items, item_lo + per_warp);
-  const uint32_t first_set = item_lo / p.tpr, first_j = item_lo - first_set * p.tpr;
-  const uint32_t part_stride = rp_per_stage * M;                  // floats per warp slice
   // Which (scale group, token) cell of the C fragment this lane finishes.
   //   separate accumulators: lane column c holds token c, both groups;
-  //   dual columns:          lane column c holds group c / m, token c % m.
-  const bool lane_has_cell = DUAL ? c < 2 * M : c < M;
-  const uint32_t cell_group = DUAL ? (c >= M ? 1u : 0u) : 0u;
-  const uint32_t cell_token = DUAL ? c - cell_group * M : c;
+  //   dual columns:          lane column c holds group c / M, token c % M.
+  // Lane columns beyond the cells in use compute sums that nobody reads.
+  const bool lane_has_cell = c < NC;
+  const uint32_t cell_group = DUAL ? ((c >= M && lane_has_cell) ? 1u : 0u) : 0u;
+  const uint32_t cell_token = lane_has_cell ? (DUAL ? c - cell_group * M : c) : 0u;
   // MMA columns beyond `ncol` produce sums nobody reads, so their lanes may load any valid
   // table entry: fold them onto the used columns instead of masking.
   const uint32_t bcol = g % ncol;
   const uint32_t byte_sel = c | (c << 4) | ((4u + c) << 8) | ((4u + c) << 12);   // byte c of two words -> bytes 0 and 2
   constexpr uint32_t zstep = ncol * 4;
   const uint32_t groups_per_row = p.tpr * 2;
+  const bool dump = p.acc_dump != nullptr;
+  constexpr uint32_t kPlaneBytes = T::kPlaneBytes;
+  constexpr int kMagic = 0x4B400000;   // bits of 1.5 * 2^23: an integer added here reads as float 12582912 + v
 
-  // Tensor-parallel row shard: the fp32 partial rows go to the peer-visible slot and the
-  // all-reduce is finished at the end of this kernel.
-  const bool fused = p.comm.world > 1;
-  const uint32_t comm_seq = fused ? *reinterpret_cast<volatile uint32_t*>(p.comm.flags[p.comm.rank] + kCommFusedEpoch) + 1u : 0u;
+  // Lane -> weights.  A set is 16 MMA rows (row-planes) of one tile column:
+  //   one plane:    set q = rows 16q .. 16q+15              (the lane holds rows g and g+8)
+  //   two planes:   set q = rows 8q .. 8q+7, both planes    (the lane holds (row g/2, plane g%2) and row + 4)
+  //   three planes: set q = plane q of the block's 16 rows  (rows g and g+8; the planes of a row add up in the lane)
+  // so that every address is lane base + set stride + half stride, the same for every block.
+  const uint32_t row_bytes = p.tpr * PLANES * kPlaneBytes, srow_bytes = p.tpr * PLANES * 4;
+  const uint32_t lrow = PLANES == 2 ? g >> 1 : g, lplane = PLANES == 2 ? g & 1 : 0;
+  const uint32_t lane_w = lrow * row_bytes + lplane * kPlaneBytes + c * 4;             // word c of the lane's first tile-plane
+  const uint32_t lane_s = lrow * srow_bytes + lplane * 4 + (DUAL ? cell_group * 2 : 0);
+  constexpr uint32_t kHalfRows = PLANES == 2 ? 4 : 8;
+  const uint32_t db_w = kHalfRows * row_bytes, db_s = kHalfRows * srow_bytes;           // first -> second row of the lane
+  const uint32_t dq_w = kPlaneSets ? kPlaneBytes : 2 * kHalfRows * row_bytes;           // set q -> set q + 1
+  const uint32_t dq_s = kPlaneSets ? 4u : 2 * kHalfRows * srow_bytes;
+  const uint32_t w12 = 48 - 4 * c;   // from word c to word 12 of a tile-plane
+  const uint32_t zlane0 = smem_addr(ztab + bcol * 4 + c);
+  const uint32_t cin0 = smem_addr(cinit + cell_token * p.tpr * 2 + cell_group);
+  const uint32_t ring_addr = smem_addr(ring), scale_ring_addr = smem_addr(scale_ring);
+
+  uint32_t s = 0, full_parity = 0, buf = 0, part_round = 0, vw = warp;
   for (uint32_t it = 0; it < my_blocks; ++it) {
-    const uint32_t s = it % p.stages;
-    float* my_part = part + ((it & 1) * kConsumerWarps + warp) * part_stride;
-    for (uint32_t i = lane; i < part_stride; i += 32) my_part[i] = 0.f;
-    __syncwarp();
-    const bool landed = mbar_wait(&full_bar[s], (it / p.stages) & 1, &abort_flag);
-    if (!landed) {
+    if (!mbar_wait(&full_bar[s], full_parity, &abort_flag)) {
       abort_flag = 1;
       if (lane == 0 && atomicOr(&p.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) { p.status[TBS_INFO0] = it; p.status[TBS_INFO1] = s; }
+      return;
     }
-    const uint32_t* words = reinterpret_cast<const uint32_t*>(ring + size_t(s) * p.stage_bytes);
-    const uint32_t* scl = reinterpret_cast<const uint32_t*>(scale_ring + size_t(s) * p.scale_stage_bytes);
-    const uint32_t gblk = blockIdx.x + it * gridDim.x;
-    const uint32_t layer = gblk / p.blocks, blk = gblk - layer * p.blocks;
-    const uint32_t row0 = blk * p.rows_per_stage;
+    const uint32_t wstage = ring_addr + s * p.stage_bytes + lane_w;
+    const uint32_t sstage = scale_ring_addr + s * p.scale_stage_bytes + lane_s;
 
-    // Items are (row set, tile column) pairs in set-major order; a warp's range is contiguous, so
-    // it walks the columns of one set with running pointers and keeps the two rows' partial
-    // sums in registers until the set changes.
-    uint32_t item = item_lo, set = first_set, j = first_j;
-    for (; landed && item < item_hi; ++set, j = 0) {
-      const uint32_t j_end = min(p.tpr, j + (item_hi - item));
-      item += j_end - j;
-      const uint32_t rpa = set * 16 + g, rpb = rpa + 8;
-      const uint32_t na = rpa / PLANES, pa = rpa - na * PLANES;
-      const uint32_t nb = rpb / PLANES, pb = rpb - nb * PLANES;
-      constexpr uint32_t kWordsPerPlane = T::kPlaneBytes / 4, kColStride = PLANES * kWordsPerPlane;
-      const uint32_t* wa = words + ((na * p.tpr + j) * PLANES + pa) * kWordsPerPlane + c;
-      const uint32_t* wb = words + ((nb * p.tpr + j) * PLANES + pb) * kWordsPerPlane + c;
-      // f16 scales of (row-plane, tile): two per u32, [group 0 | group 1]
-      const uint16_t* sca = reinterpret_cast<const uint16_t*>(scl + (na * p.tpr + j) * PLANES + pa) + (DUAL ? cell_group : 0);
-      const uint16_t* scb = reinterpret_cast<const uint16_t*>(scl + (nb * p.tpr + j) * PLANES + pb) + (DUAL ? cell_group : 0);
-      const int* cin = cinit + ((DUAL ? cell_token : c) * p.tpr + j) * 2 + (DUAL ? cell_group : 0);
-      const uint2* zlane = ztab + (size_t(j) * kNM * ncol + bcol) * 4 + c;
-      constexpr uint32_t zcol = kNM * ncol * 4;
-#define TB_BFRAG(mm) (zlane[(mm) * zstep])
-      float ya = 0.f, yb = 0.f;
+    float ya[YN], yb[YN];
+#pragma unroll
+    for (int q = 0; q < YN; ++q) { ya[q] = 0.f; yb[q] = 0.f; }
 
-      for (; j < j_end; ++j, wa += kColStride, wb += kColStride, sca += 2 * PLANES, scb += 2 * PLANES, cin += 2, zlane += zcol) {
+    // This warp takes the tile columns vw, vw + 8, ...  The assignment rotates from block to
+    // block, so that one-column differences between warps even out.
+    for (uint32_t j = vw; j < p.tpr; j += kWarps) {
+      // B fragments of tile column j stay in registers while the row-planes change
+      uint2 bf[kNM];
+      {
+        const uint32_t zlane = zlane0 + j * (kNM * ncol * 4 * 8);
+#pragma unroll
+        for (int mm = 0; mm < kNM; ++mm) bf[mm] = lds_u64(zlane + mm * (zstep * 8));
+      }
+      const int ci0 = int(lds_u32(cin0 + j * 8)) + kMagic, ci1 = DUAL ? 0 : int(lds_u32<4>(cin0 + j * 8)) + kMagic;
+      const uint32_t wcol = wstage + j * (PLANES * kPlaneBytes);
+      const uint32_t scol = sstage + j * (PLANES * 4);
+#pragma unroll
+      for (int q = 0; q < SETS; ++q) {
+        const uint32_t wa = wcol + q * dq_w, wb = wa + db_w;
         int acc0[4], acc1[4];   // group 0 / group 1 sums (dual layout: acc0 holds this lane's group)
-        if (CODEC == tbf::kB3) {
+        if constexpr (CODEC == tbf::kB3) {
           // Two accumulation chains, fed alternately, so that consecutive MMAs rarely depend on
           // each other.  Dual layout: chain A takes words c and 8+c, chain B words 4+c and 12, and
           // their sum is the cell.  Separate accumulators: chain A is scale group 0, chain B group 1.
           int sA[4], sB[4];
-          uint32_t qa[5], qb[5];
-          uint2 b;
-          b3_quads(wa[0], qa); b3_quads(wb[0], qb);
-          b = TB_BFRAG(0); mma_u8s8_first(sA, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
-          b = TB_BFRAG(1); mma_u8s8(sA, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
-          b = TB_BFRAG(2); mma_u8s8(sA, qa[4], qb[4], 0u, 0u, b.x, b.y);
-          b3_quads(wa[4], qa); b3_quads(wb[4], qb);
-          if (DUAL) {
-            b = TB_BFRAG(3); mma_u8s8_first(sB, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
-            b = TB_BFRAG(4); mma_u8s8(sB, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
-            b = TB_BFRAG(5); mma_u8s8(sB, qa[4], qb[4], 0u, 0u, b.x, b.y);
+          uint32_t A[12];
+#define TB_MMA3(first, acc, i0)                                                          \
+  first(acc, A[0], A[1], A[2], A[3], bf[i0].x, bf[i0].y);                                \
+  mma_u8s8(acc, A[4], A[5], A[6], A[7], bf[(i0) + 1].x, bf[(i0) + 1].y);                 \
+  mma_u8s8(acc, A[8], A[9], A[10], A[11], bf[(i0) + 2].x, bf[(i0) + 2].y)
+          b3_quads2(lds_u32(wa), lds_u32(wb), A);
+          TB_MMA3(mma_u8s8_first, sA, 0);
+          b3_quads2(lds_u32(wa + 16), lds_u32(wb + 16), A);
+          if constexpr (DUAL) {
+            TB_MMA3(mma_u8s8_first, sB, 3);
           } else {
             // the words 4..7 straddle the two scale groups: once per group, masked on the B side
-            b = TB_BFRAG(3); mma_u8s8(sA, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
-            b = TB_BFRAG(6); mma_u8s8_first(sB, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
-            b = TB_BFRAG(4); mma_u8s8(sA, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
-            b = TB_BFRAG(7); mma_u8s8(sB, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
-            b = TB_BFRAG(5); mma_u8s8(sA, qa[4], qb[4], 0u, 0u, b.x, b.y);
-            b = TB_BFRAG(8); mma_u8s8(sB, qa[4], qb[4], 0u, 0u, b.x, b.y);
+            TB_MMA3(mma_u8s8, sA, 3);
+            TB_MMA3(mma_u8s8_first, sB, 6);
           }
           constexpr int o2 = DUAL ? 6 : 9, o3 = DUAL ? 9 : 12;
-          b3_quads(wa[8], qa); b3_quads(wb[8], qb);
-          if (DUAL) {
-            b = TB_BFRAG(o2); mma_u8s8(sA, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
-            b = TB_BFRAG(o2 + 1); mma_u8s8(sA, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
-            b = TB_BFRAG(o2 + 2); mma_u8s8(sA, qa[4], qb[4], 0u, 0u, b.x, b.y);
+          b3_quads2(lds_u32(wa + 32), lds_u32(wb + 32), A);
+          if constexpr (DUAL) {
+            TB_MMA3(mma_u8s8, sA, o2);
           } else {
-            b = TB_BFRAG(o2); mma_u8s8(sB, qa[0], qb[0], qa[1], qb[1], b.x, b.y);
-            b = TB_BFRAG(o2 + 1); mma_u8s8(sB, qa[2], qb[2], qa[3], qb[3], b.x, b.y);
-            b = TB_BFRAG(o2 + 2); mma_u8s8(sB, qa[4], qb[4], 0u, 0u, b.x, b.y);
+            TB_MMA3(mma_u8s8, sB, o2);
           }
+#undef TB_MMA3
           {
             // word 12: lane column c takes byte c of both rows through one half2 chain; its five
             // quotients fill the lane's eight k-slots of a single MMA
-            const uint32_t h = (prmt(wa[12 - c], wb[12 - c], byte_sel) & 0x00ff00ffu) | 0x64006400u;
+            const uint32_t w12a = lds_u32(wa + w12), w12b = lds_u32(wb + w12);
+            const uint32_t h = (prmt(w12a, w12b, byte_sel) & 0x00ff00ffu) | 0x64006400u;
             const uint32_t q1 = hfma2_bits(h, kC3, kK3), q2 = hfma2_bits(h, kC9, kK9);
             const uint32_t q3 = hfma2_bits(q1, kC9, kK9), q4 = hfma2_bits(q2, kC9b, kK9b);
             const uint32_t u = prmt(h, q1, 0x6240u), v = prmt(q2, q3, 0x6240u);
-            b = TB_BFRAG(o3);
-            mma_u8s8(sB, prmt(u, v, 0x5410u), prmt(u, v, 0x7632u), prmt(q4, 0u, 0x4440u), prmt(q4, 0u, 0x4442u), b.x, b.y);
+            mma_u8s8(sB, prmt(u, v, 0x5410u), prmt(u, v, 0x7632u), prmt(q4, 0u, 0x4440u), prmt(q4, 0u, 0x4442u), bf[o3].x, bf[o3].y);
           }
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
@@ -600,12 +835,11 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
           int sq[4][4];
 #pragma unroll
           for (int sl = 0; sl < 4; ++sl) {
-            const uint32_t va = wa[sl * 4], vb = wb[sl * 4];
-            uint2 b = TB_BFRAG(sl * 2);
-            mma_u8s8_first(sq[sl], va & 0x03030303u, vb & 0x03030303u, (va >> 2) & 0x03030303u, (vb >> 2) & 0x03030303u, b.x, b.y);
-            b = TB_BFRAG(sl * 2 + 1);
+            const uint32_t va = lds_u32(wa + sl * 16), vb = lds_u32(wb + sl * 16);
+            mma_u8s8_first(sq[sl], va & 0x03030303u, vb & 0x03030303u, (va >> 2) & 0x03030303u, (vb >> 2) & 0x03030303u,
+                           bf[sl * 2].x, bf[sl * 2].y);
             mma_u8s8(sq[sl], (va >> 4) & 0x03030303u, (vb >> 4) & 0x03030303u, (va >> 6) & 0x03030303u,
-                     (vb >> 6) & 0x03030303u, b.x, b.y);
+                     (vb >> 6) & 0x03030303u, bf[sl * 2 + 1].x, bf[sl * 2 + 1].y);
           }
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
@@ -614,128 +848,70 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
           }
         }
 
-        // finish the cells: columns (2c, 2c+1) are the high / low activation parts of one cell
-        if (DUAL) {
-          if (lane_has_cell) {
-            const int ci = cin[0];
-            const int ia = 4 * acc0[0] + acc0[1] + ci, ib = 4 * acc0[2] + acc0[3] + ci;
-            ya = __fmaf_rn(group_sum_to_float(ia), __half2float(__ushort_as_half(sca[0])), ya);
-            yb = __fmaf_rn(group_sum_to_float(ib), __half2float(__ushort_as_half(scb[0])), yb);
-            if (p.acc_dump) {
-              const uint32_t tok = p.dump_token_offset + cell_token;
-              if (row0 + na < p.n)
-                p.acc_dump[((size_t(tok) * p.n + row0 + na) * groups_per_row + 2 * j + cell_group) * PLANES + pa] = ia;
-              if (row0 + nb < p.n)
-                p.acc_dump[((size_t(tok) * p.n + row0 + nb) * groups_per_row + 2 * j + cell_group) * PLANES + pb] = ib;
-            }
-          }
-        } else if (lane_has_cell) {
-          const int ci0 = cin[0], ci1 = cin[1];
-          const int ia0 = 4 * acc0[0] + acc0[1] + ci0, ia1 = 4 * acc1[0] + acc1[1] + ci1;
-          const int ib0 = 4 * acc0[2] + acc0[3] + ci0, ib1 = 4 * acc1[2] + acc1[3] + ci1;
-          ya = __fmaf_rn(group_sum_to_float(ia1), __half2float(__ushort_as_half(sca[1])),
-                         __fmaf_rn(group_sum_to_float(ia0), __half2float(__ushort_as_half(sca[0])), ya));
-          yb = __fmaf_rn(group_sum_to_float(ib1), __half2float(__ushort_as_half(scb[1])),
-                         __fmaf_rn(group_sum_to_float(ib0), __half2float(__ushort_as_half(scb[0])), yb));
-          if (p.acc_dump) {
-            const uint32_t tok = p.dump_token_offset + c;
+        // finish the cells: columns (2c, 2c+1) are the high / low activation parts of one cell.
+        // Every lane runs this code (lanes without a cell produce values that are never read).
+        const int yi = kPlaneSets ? 0 : q;
+        const uint32_t sa_addr = scol + q * dq_s, sb_addr = sa_addr + db_s;
+        int da0, da1 = 0, db0, db1 = 0;   // exact group sums + kMagic
+        if constexpr (DUAL) {
+          da0 = 4 * acc0[0] + acc0[1] + ci0; db0 = 4 * acc0[2] + acc0[3] + ci0;
+          const float sa = __half2float(__ushort_as_half(uint16_t(lds_u16(sa_addr))));
+          const float sb = __half2float(__ushort_as_half(uint16_t(lds_u16(sb_addr))));
+          ya[yi] = __fmaf_rn(__fsub_rn(__int_as_float(da0), 12582912.0f), sa, ya[yi]);
+          yb[yi] = __fmaf_rn(__fsub_rn(__int_as_float(db0), 12582912.0f), sb, yb[yi]);
+        } else {
+          da0 = 4 * acc0[0] + acc0[1] + ci0; da1 = 4 * acc1[0] + acc1[1] + ci1;
+          db0 = 4 * acc0[2] + acc0[3] + ci0; db1 = 4 * acc1[2] + acc1[3] + ci1;
+          const uint32_t s2a = lds_u32(sa_addr), s2b = lds_u32(sb_addr);   // f16 scales [group 0 | group 1]
+          ya[yi] = __fmaf_rn(__fsub_rn(__int_as_float(da0), 12582912.0f), __half2float(__ushort_as_half(uint16_t(s2a & 0xffffu))), ya[yi]);
+          ya[yi] = __fmaf_rn(__fsub_rn(__int_as_float(da1), 12582912.0f), __half2float(__ushort_as_half(uint16_t(s2a >> 16))), ya[yi]);
+          yb[yi] = __fmaf_rn(__fsub_rn(__int_as_float(db0), 12582912.0f), __half2float(__ushort_as_half(uint16_t(s2b & 0xffffu))), yb[yi]);
+          yb[yi] = __fmaf_rn(__fsub_rn(__int_as_float(db1), 12582912.0f), __half2float(__ushort_as_half(uint16_t(s2b >> 16))), yb[yi]);
+        }
+        if (dump) {
+          if (lane_has_cell && cell_token < p.m) {
+            const uint32_t gblk = blockIdx.x + it * gridDim.x;
+            const uint32_t row0 = (gblk % p.blocks) * p.rows_per_stage;
+            // (row, plane) of the lane's first row-plane in set q; the second one is kHalfRows rows further
+            const uint32_t na = kPlaneSets ? g : q * 2 * kHalfRows + lrow, nb = na + kHalfRows;
+            const uint32_t pl = kPlaneSets ? uint32_t(q) : lplane;
+            const uint32_t tok = p.dump_token_offset + cell_token;
             if (row0 + na < p.n) {
-              int32_t* d = p.acc_dump + ((size_t(tok) * p.n + row0 + na) * groups_per_row + 2 * j) * PLANES + pa;
-              d[0] = ia0; d[PLANES] = ia1;
+              int32_t* d = p.acc_dump + ((size_t(tok) * p.n + row0 + na) * groups_per_row + 2 * j + cell_group) * PLANES + pl;
+              d[0] = da0 - kMagic;
+              if (!DUAL) d[PLANES] = da1 - kMagic;
             }
             if (row0 + nb < p.n) {
-              int32_t* d = p.acc_dump + ((size_t(tok) * p.n + row0 + nb) * groups_per_row + 2 * j) * PLANES + pb;
-              d[0] = ib0; d[PLANES] = ib1;
+              int32_t* d = p.acc_dump + ((size_t(tok) * p.n + row0 + nb) * groups_per_row + 2 * j + cell_group) * PLANES + pl;
+              d[0] = db0 - kMagic;
+              if (!DUAL) d[PLANES] = db1 - kMagic;
             }
           }
         }
-      }
-#undef TB_BFRAG
-      // hand the set's partial sums to the stage combine
-      if (DUAL) {
-        // the two scale groups of a (row, token) sit p.m lanes apart: group 0 + group 1
-        ya = __fadd_rn(ya, __shfl_xor_sync(0xffffffffu, ya, M));
-        yb = __fadd_rn(yb, __shfl_xor_sync(0xffffffffu, yb, M));
-        if (lane_has_cell && cell_group == 0) {
-          my_part[rpa * M + cell_token] += ya;
-          my_part[rpb * M + cell_token] += yb;
-        }
-      } else if (lane_has_cell) {
-        my_part[rpa * M + c] += ya;
-        my_part[rpb * M + c] += yb;
       }
     }
     __syncwarp();
-    if (lane == 0) mbar_arrive(&empty_bar[s]);   // slot may be refilled
+    if (lane == 0) mbar_arrive(&empty_bar[s]);      // slot may be refilled
 
-    // combine the warps' partial sums (fixed order: plane ascending, warp ascending).  Every
-    // consumer warp reaches this barrier, also after a failed wait, and all leave together.
-    consumer_sync();
-    if (abort_flag) return;
-    const float* stage_part = part + (it & 1) * kConsumerWarps * part_stride;
-    for (uint32_t e = ctid; e < p.rows_per_stage * M; e += kCT) {
-      const uint32_t t = e / p.rows_per_stage, r = e - t * p.rows_per_stage;
-      if (row0 + r >= p.n) continue;
-      float sum = 0.f;
+    // hand this warp's partial sums of the block to the combiner: [row-plane (three planes: row)][cell]
+    if (part_round > 0 && !mbar_wait(&part_empty[buf], (part_round - 1) & 1, &abort_flag)) {
+      abort_flag = 1;
+      if (lane == 0 && atomicOr(&p.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) { p.status[TBS_INFO0] = it; p.status[TBS_INFO1] = 400 + buf; }
+      return;
+    }
+    float* my_part = part + (size_t(buf) * kWarps + warp) * kSliceFloats;
+    if (lane_has_cell) {
 #pragma unroll
-      for (uint32_t q = 0; q < PLANES; ++q)
-        for (int w2 = 0; w2 < kConsumerWarps; ++w2)
-          sum = __fadd_rn(sum, stage_part[w2 * part_stride + (r * PLANES + q) * M + t]);
-      float out = __fmul_rn(sum, act_scale[t]);
-      if (p.row_scale) out = __fmul_rn(out, p.row_scale[row0 + r]);
-      if (fused) {
-        // this rank's partial row, peer-visible; the sum over ranks follows one block later
-        p.comm.data[p.comm.rank][size_t(t) * p.n + row0 + r] = out;
-        continue;
-      }
-      const size_t idx = size_t(layer) * p.y_layer_stride + size_t(t) * p.y_row_stride + row0 + r;
-      if (p.y_dtype == TB_F32) static_cast<float*>(p.y)[idx] = out;
-      else static_cast<__nv_bfloat16*>(p.y)[idx] = __float2bfloat16_rn(out);
-    }
-  }
-  if (fused) {
-    // Every rank's CTA number b walks the same row blocks.  Once all of this CTA's partial rows are
-    // written, ONE arrival is raised on every peer's counter b; when the peers' arrivals are in,
-    // the CTA's rows are summed over the ranks in rank order (one NVLink round trip per kernel).
-    consumer_sync();
-    if (ctid == 0) {
-      // the barrier orders the other threads' stores before this fence; the fence and the release
-      // additions publish them to the peers
-      __threadfence_system();
-      for (uint32_t r = 0; r < p.comm.world; ++r)
-        if (r != p.comm.rank) peer_signal(p.comm.flags[r] + kCommCounters + blockIdx.x);
-      const bool arrived = peer_wait(p.comm.flags[p.comm.rank] + kCommCounters + blockIdx.x, (p.comm.world - 1) * comm_seq);
-      if (!arrived) {
-        abort_flag = 1;
-        if (atomicOr(&p.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) { p.status[TBS_INFO0] = blockIdx.x; p.status[TBS_INFO1] = 501; }
-      }
-      comm_ok = arrived ? 1u : 0u;
-    }
-    consumer_sync();
-    if (!comm_ok) return;
-    const uint32_t per_block = p.rows_per_stage * M;
-    for (uint32_t e = ctid; e < my_blocks * per_block; e += kCT) {
-      const uint32_t it = e / per_block, rem = e - it * per_block;
-      const uint32_t t = rem / p.rows_per_stage, r = rem - t * p.rows_per_stage;
-      const uint32_t row = (blockIdx.x + it * gridDim.x) * p.rows_per_stage + r;
-      if (row >= p.n) continue;
-      const size_t at = size_t(t) * p.n + row;
-      float sum = p.comm.rank == 0 ? p.comm.data[0][at] : peer_load(p.comm.data[0] + at);
-      for (uint32_t q = 1; q < p.comm.world; ++q)
-        sum = __fadd_rn(sum, q == p.comm.rank ? p.comm.data[q][at] : peer_load(p.comm.data[q] + at));
-      const size_t idx = size_t(t) * p.y_row_stride + row;
-      if (p.y_dtype == TB_F32) static_cast<float*>(p.y)[idx] = sum;
-      else static_cast<__nv_bfloat16*>(p.y)[idx] = __float2bfloat16_rn(sum);
-    }
-    if (ctid == 0) {
-      // the last CTA of the launch closes the round
-      uint32_t* mine = p.comm.flags[p.comm.rank];
-      __threadfence();
-      if (atomicAdd(mine + kCommFusedDone, 1u) == gridDim.x - 1) {
-        mine[kCommFusedDone] = 0;
-        *reinterpret_cast<volatile uint32_t*>(mine + kCommFusedEpoch) = comm_seq;
+      for (int q = 0; q < YN; ++q) {
+        my_part[(q * 16 + g) * NC + c] = ya[q];
+        my_part[(q * 16 + 8 + g) * NC + c] = yb[q];
       }
     }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&part_full[buf]);
+    if (++s == p.stages) { s = 0; full_parity ^= 1; }
+    if (++buf == kPartBufs) { buf = 0; ++part_round; }
+    if (++vw == kWarps) vw = 0;
   }
 }
 
@@ -743,8 +919,11 @@ uint32_t round_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
 
 // Byte layout of the activation tables (identical in global scratch and in shared memory).
 struct TableLayout { uint32_t z_bytes, off_cinit, off_actscale, total; };
+// Token columns the tables and the kernel are laid out for: three tokens run in the four-token kernel.
+uint32_t layout_tokens(uint32_t m) { return m == 3 ? 4u : m; }
 bool use_dual(uint32_t m) { return m <= 2; }
-TableLayout table_layout(const tb_weights* w, uint32_t m) {
+TableLayout table_layout(const tb_weights* w, uint32_t m_valid) {
+  const uint32_t m = layout_tokens(m_valid);
   const bool dual = use_dual(m);
   const uint32_t tpr = uint32_t(w->k / 256);
   const uint32_t mmas = w->codec == tbf::kB3 ? (dual ? 10 : 13) : 8;
@@ -761,15 +940,21 @@ size_t layout(const tb_weights* w, uint32_t m, int max_smem, DecodeParams* p) {
   const DecodePlan& pl = w->plan;
   const uint32_t planes = w->uniform_planes;
   const TableLayout tl = table_layout(w, m);
+  const uint32_t cw = kWarps;
   uint32_t off = 0;
-  const uint32_t part = round_up(2 * kConsumerWarps * pl.rows_per_stage * planes * m * 4, 16);
-  const uint32_t fixed = tl.total + part;
+  const uint32_t mk = layout_tokens(m), cells = use_dual(mk) ? 2 * mk : mk;
+  // a consumer warp's partial sums per row block: one per row-plane (three planes: one per row)
+  const uint32_t part = kPartBufs * cw * pl.rows_per_stage * (planes == 3 ? 1 : planes) * cells * 4;
+  const uint32_t xq = cw * kStageBytesPerWarp;   // fused prologue staging
+  const uint32_t fixed = tl.total + part + xq;
   const uint32_t per_stage = pl.stage_bytes + pl.scale_stage_bytes;
   if (fixed + 2 * per_stage > uint32_t(max_smem)) return 0;
-  // Prefer a footprint that lets two CTAs share an SM (one of this launch, one of the next launch
-  // on the stream, whose weight stream then starts under this launch's tail).
-  const uint32_t half_sm = 110u * 1024u;   // two CTAs (dynamic + static + 1 KB reserved each) within 228 KB
-  const uint32_t budget = fixed + 2 * per_stage <= half_sm ? half_sm : uint32_t(max_smem);
+  // Prefer a footprint that lets two CTAs share an SM (of this launch, or one of this launch and
+  // one of the next launch on the stream, whose weight stream then starts under this launch's
+  // tail).  Each CTA adds its static shared memory and 1 KB of reserved space to the 228 KB of an SM.
+  const uint32_t half_sm = 110u * 1024u;
+  uint32_t budget = uint32_t(max_smem), ctas = 1;
+  if (fixed + 2 * per_stage <= half_sm) { budget = half_sm; ctas = 2; }
   uint32_t stages = std::min<uint32_t>(kMaxStages, (budget - fixed) / per_stage);
   if (p) {
     p->stages = stages;
@@ -778,11 +963,11 @@ size_t layout(const tb_weights* w, uint32_t m, int max_smem, DecodeParams* p) {
     p->off_z = off;
     p->off_cinit = off + tl.off_cinit;
     p->off_actscale = off + tl.off_actscale;
-    p->off_zero = off + tl.off_actscale + 16;
     off += tl.total;
     p->off_part = off; off += part;
+    p->off_xq = off; off += xq;
     p->table_bytes = tl.total;
-    p->ctas_per_sm = budget == half_sm ? 2 : 1;
+    p->ctas_per_sm = ctas;
   }
   return size_t(fixed) + size_t(stages) * per_stage;
 }
@@ -795,12 +980,17 @@ void tb_make_decode_plan(tb_weights* w, int max_smem) {
   const uint32_t planes = w->uniform_planes, tpr = uint32_t(w->k / 256);
   const uint32_t pb = w->codec == tbf::kB3 ? 52 : 64;
   pl.row_bytes = tpr * planes * pb;
-  const uint32_t base = planes == 2 ? 8 : 16;   // R % 4 == 0 and R*planes % 16 == 0
+  // A row block is `sets` blocks of 16 row-planes: 16*sets/planes rows (1, 2 or 4 sets for one and
+  // two planes, 3 sets = 16 rows for three), so that R % 4 == 0 (16-byte chunks).  Take the
+  // largest block up to about 40 KB that still leaves every SM three blocks when the tensor allows it.
   const uint32_t target = 40 * 1024;
-  uint32_t r = std::max(base, (target / pl.row_bytes) / base * base);
-  r = std::min<uint32_t>(r, 128);
-  // keep enough blocks to cover every SM at least three times when the tensor allows it
-  while (r > base && (w->n + r - 1) / r < 444) r -= base;
+  uint32_t sets = planes == 3 ? 3 : 1;
+  if (planes != 3)
+    for (uint32_t cand : {2u, 4u}) {
+      const uint32_t r = 16 * cand / planes;
+      if (r * pl.row_bytes <= target && (w->n + r - 1) / r >= 444) sets = cand;
+    }
+  const uint32_t r = 16 * sets / planes;
   pl.rows_per_stage = r;
   pl.stage_bytes = r * pl.row_bytes;
   pl.scale_stage_bytes = r * tpr * planes * 4;
@@ -829,7 +1019,7 @@ cudaError_t tb_launch_prepare(const DecodeArgs& a, cudaStream_t stream) {
   PrepareParams pp{};
   pp.x = a.x; pp.act_scale_in = a.act_scale_in; pp.act_absmax_in = a.act_absmax_in;
   pp.tables = static_cast<uint8_t*>(a.scratch);
-  pp.m = a.m; pp.k = uint32_t(w->k); pp.tpr = uint32_t(w->k / 256); pp.x_dtype = uint32_t(a.x_dtype);
+  pp.m = a.m; pp.mk = layout_tokens(a.m); pp.k = uint32_t(w->k); pp.tpr = uint32_t(w->k / 256); pp.x_dtype = uint32_t(a.x_dtype);
   pp.off_cinit = tl.off_cinit; pp.off_actscale = tl.off_actscale; pp.pdl = a.pdl ? 1u : 0u;
   pp.status = a.status;
   if (a.comm_absmax) {
@@ -842,20 +1032,28 @@ cudaError_t tb_launch_prepare(const DecodeArgs& a, cudaStream_t stream) {
   cfg.stream = stream;
   cfg.attrs = attr;
   cfg.numAttrs = a.pdl ? 1 : 0;
-  const bool dual = use_dual(a.m);
+  const bool dual = use_dual(layout_tokens(a.m));
   if (w->codec == tbf::kB3)
     return dual ? cudaLaunchKernelEx(&cfg, prepare_kernel<tbf::kB3, true>, pp) : cudaLaunchKernelEx(&cfg, prepare_kernel<tbf::kB3, false>, pp);
   return dual ? cudaLaunchKernelEx(&cfg, prepare_kernel<tbf::kD2, true>, pp) : cudaLaunchKernelEx(&cfg, prepare_kernel<tbf::kD2, false>, pp);
 }
 
 using DecodeKernel = void (*)(const DecodeParams);
-template <int CODEC, int PLANES> DecodeKernel pick_tokens(uint32_t m) {
-  return m == 1 ? decode_kernel<CODEC, PLANES, 1> : m == 2 ? decode_kernel<CODEC, PLANES, 2>
-       : m == 3 ? decode_kernel<CODEC, PLANES, 3> : decode_kernel<CODEC, PLANES, 4>;
+#ifdef TB_DECODE_MINIMAL
+template <int CODEC> DecodeKernel pick_planes(uint32_t planes, uint32_t sets, uint32_t mk) {
+  return (CODEC == tbf::kB3 && planes == 3 && sets == 3 && mk == 1) ? decode_kernel<tbf::kB3, 3, 1, 3> : nullptr;
 }
-template <int CODEC> DecodeKernel pick_planes(uint32_t planes, uint32_t m) {
-  return planes == 1 ? pick_tokens<CODEC, 1>(m) : planes == 2 ? pick_tokens<CODEC, 2>(m) : pick_tokens<CODEC, 3>(m);
+#else
+template <int CODEC, int PLANES, int SETS> DecodeKernel pick_tokens(uint32_t mk) {
+  return mk == 1 ? decode_kernel<CODEC, PLANES, 1, SETS> : mk == 2 ? decode_kernel<CODEC, PLANES, 2, SETS> : decode_kernel<CODEC, PLANES, 4, SETS>;
 }
+template <int CODEC, int PLANES> DecodeKernel pick_sets(uint32_t sets, uint32_t mk) {
+  return sets == 1 ? pick_tokens<CODEC, PLANES, 1>(mk) : sets == 2 ? pick_tokens<CODEC, PLANES, 2>(mk) : pick_tokens<CODEC, PLANES, 4>(mk);
+}
+template <int CODEC> DecodeKernel pick_planes(uint32_t planes, uint32_t sets, uint32_t mk) {
+  return planes == 1 ? pick_sets<CODEC, 1>(sets, mk) : planes == 2 ? pick_sets<CODEC, 2>(sets, mk) : pick_tokens<CODEC, 3, 3>(mk);
+}
+#endif
 
 cudaError_t tb_launch_decode(const DecodeArgs& a, int sm_count, int max_smem, cudaStream_t stream) {
   const tb_weights* w = a.w;
@@ -863,7 +1061,14 @@ cudaError_t tb_launch_decode(const DecodeArgs& a, int sm_count, int max_smem, cu
   const size_t smem = layout(w, a.m, max_smem, &p);
   if (!smem) return cudaErrorInvalidConfiguration;
   const TableLayout tl = table_layout(w, a.m);
-  if (!a.scratch || a.scratch_bytes < tl.total) return cudaErrorInvalidValue;
+  if (a.fused) {
+    // the prologue reads x with 16-byte loads
+    if (!a.x || (reinterpret_cast<uintptr_t>(a.x) & 15u) || a.comm_absmax) return cudaErrorInvalidValue;
+    if (a.x_dtype == TB_I8 && !a.act_scale_in) return cudaErrorInvalidValue;
+    p.fused = 1; p.x = a.x; p.act_scale_in = a.act_scale_in; p.act_absmax_in = a.act_absmax_in; p.x_dtype = uint32_t(a.x_dtype);
+  } else if (!a.scratch || a.scratch_bytes < tl.total) {
+    return cudaErrorInvalidValue;
+  }
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
@@ -879,12 +1084,10 @@ cudaError_t tb_launch_decode(const DecodeArgs& a, int sm_count, int max_smem, cu
   p.dump_token_offset = a.dump_token_offset; p.dump_tokens_total = a.dump_tokens_total;
   p.pdl = a.pdl ? 1u : 0u;
   p.wait_tables = a.tables_shared ? 0u : 1u;
-  if (a.comm_y) {
-    // one arrival counter per CTA (up to two CTAs per SM); single layer, fp32 partials of [m, n]
-    if (a.layers || a.comm_y->counters < 2u * uint32_t(sm_count)) return cudaErrorInvalidValue;
-    p.comm = *a.comm_y;
-  }
-  DecodeKernel kernel = w->codec == tbf::kB3 ? pick_planes<tbf::kB3>(w->uniform_planes, a.m) : pick_planes<tbf::kD2>(w->uniform_planes, a.m);
+  p.inject_missing_tx = a.inject_missing_tx;
+  const uint32_t sets = w->plan.rows_per_stage * w->uniform_planes / 16, mk = layout_tokens(a.m);
+  DecodeKernel kernel = w->codec == tbf::kB3 ? pick_planes<tbf::kB3>(w->uniform_planes, sets, mk) : pick_planes<tbf::kD2>(w->uniform_planes, sets, mk);
+  if (!kernel) return cudaErrorInvalidConfiguration;
   if (a.layers && a.layer_count > uint32_t(kMaxGroupLayers)) return cudaErrorInvalidValue;
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
   if (err != cudaSuccess) return err;
@@ -919,6 +1122,7 @@ void* g_static_tables_ptr[64] = {};
 extern "C" tb_status tb_linear_forward_a8_static(tb_backend* backend, const tb_weights* weights, const void* x,
                                                  tb_dtype x_dtype, const float* act_scale, uint32_t m, void* y,
                                                  tb_dtype y_dtype, void* stream) {
+  tb_clear_error();
   if (!backend || !weights) return tb_fail(TB_NULL_ARG, "null argument");
   if (weights->owner != backend) return tb_fail(TB_INVALID_INPUT, "weights handle belongs to another backend context");
   if (m == 0 || weights->n == 0) return TB_OK;
@@ -956,3 +1160,4 @@ extern "C" tb_status tb_linear_forward_a8_static(tb_backend* backend, const tb_w
   if (err != cudaSuccess) return tb_cuda_fail(err, "launch decode");
   return TB_OK;
 }
+

@@ -16,7 +16,8 @@ thread_local bool g_has_error = false;
 }  // namespace
 
 void tb_set_error(const std::string& message) { g_last_error = message; g_has_error = true; }
-static void clear_error() { g_has_error = false; }
+void tb_clear_error() { g_has_error = false; }
+static void clear_error() { tb_clear_error(); }
 tb_status tb_fail(tb_status code, const std::string& message) { tb_set_error(message); return code; }
 tb_status tb_cuda_fail(cudaError_t err, const char* what) {
   const tb_status code = err == cudaErrorMemoryAllocation ? TB_OUT_OF_MEMORY : TB_BACKEND;
@@ -305,6 +306,10 @@ tb_status forward_dev(tb_backend* b, const tb_weights* w, const tb_forward_args&
   }
   if (a.flags & TB_FWD_FORCE_PREFILL) return tb_fail(TB_UNSUPPORTED_FORMAT, "the prefill kernel does not take this shape");
   uint32_t launches = 0;
+  // One launch per pass of up to four tokens: the kernel quantises the activations and builds its
+  // tables itself.  Activations that are not 16-byte aligned go through the separate
+  // preparation kernel and the backend's scratch instead.
+  const bool fused = (reinterpret_cast<uintptr_t>(a.x) & 15u) == 0;
   for (uint32_t m0 = 0; m0 < a.m; m0 += 4) {
     const uint32_t mc = std::min<uint32_t>(4, a.m - m0);
     if (!tb_decode_supported(w, mc, b->max_smem_optin, nullptr))
@@ -317,11 +322,12 @@ tb_status forward_dev(tb_backend* b, const tb_weights* w, const tb_forward_args&
     d.y = static_cast<uint8_t*>(a.y) + size_t(m0) * w->n * dtype_size(a.y_dtype);
     d.acc_dump = a.acc_dump; d.dump_token_offset = m0; d.dump_tokens_total = a.m;
     // passes after the first always chain with programmatic dependent launch: their weight
-    // stream starts under the previous pass's tail (every consumer still waits for its own tables)
+    // stream starts under the previous pass's tail
     d.row_scale = a.row_scale; d.status = b->d_status; d.pdl = (a.flags & TB_FWD_PDL) != 0 || m0 > 0;
+    d.fused = fused;
     d.scratch = b->d_prep; d.scratch_bytes = b->d_prep_cap;
     d.tables_shared = false;
-    if (!d.tables_shared) { TB_CUDA(tb_launch_prepare(d, st), "launch prepare"); ++launches; }
+    if (!fused) { TB_CUDA(tb_launch_prepare(d, st), "launch prepare"); ++launches; }
     TB_CUDA(tb_launch_decode(d, b->prop.multiProcessorCount, b->max_smem_optin, st), "launch decode");
     ++launches;
   }
@@ -447,44 +453,37 @@ extern "C" tb_status tb_linear_forward_tp_dev(tb_backend* b, const tb_weights* w
   if (x_dtype == TB_I8) return tb_fail(TB_INVALID_INPUT, "the tensor-parallel path quantises fp32 or bf16 activations itself");
   if (y_dtype == TB_I8) return tb_fail(TB_INVALID_INPUT, "output dtype must be fp32 or bf16");
   if (m > 8) return tb_fail(TB_INVALID_INPUT, "the fused tensor-parallel path takes at most 8 tokens per call");
-  const bool in_kernel = (flags & TB_TP_REDUCE_IN_KERNEL) != 0;
-  if (!in_kernel && y_dtype != TB_F32) return tb_fail(TB_INVALID_INPUT, "the one-shot reduce writes fp32 outputs");
+  if (flags != 0) return tb_fail(TB_INVALID_INPUT, "unknown flag bits");
+  if (y_dtype != TB_F32) return tb_fail(TB_INVALID_INPUT, "the one-shot reduce writes fp32 outputs");
   if (!w->fast) return tb_fail(TB_UNSUPPORTED_FORMAT, "the int8 path needs uniform plane counts, k % 256 == 0, group 128 and codec D2 or B3");
   if (slot_absmax == slot_y) return tb_fail(TB_INVALID_INPUT, "the absmax and the output slot must differ");
   TbCommView va{}, vy{};
   if (!tb_comm_view(comm, slot_absmax, &va) || !tb_comm_view(comm, slot_y, &vy))
     return tb_fail(TB_INVALID_INPUT, "communicator is not connected or a slot index is out of range");
   if (size_t(m) * w->n * 4 > tb_comm_slot_bytes(comm)) return tb_fail(TB_INVALID_INPUT, "the output slot is smaller than m x n fp32 values");
-  if (vy.counters < 2u * uint32_t(b->prop.multiProcessorCount) || va.counters < 4)
-    return tb_fail(TB_INVALID_INPUT, "the communicator holds " + std::to_string(vy.counters) + " arrival counters per slot, two per SM (" +
-                                         std::to_string(2 * b->prop.multiProcessorCount) + ") are needed");
+  if (va.counters < 4)
+    return tb_fail(TB_INVALID_INPUT, "the communicator holds " + std::to_string(va.counters) + " arrival counters per slot, four are needed");
   if (tb_status s = use_device(b)) return s;
   cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : b->stream;
   for (uint32_t m0 = 0; m0 < m; m0 += 4) {
     const uint32_t mc = std::min<uint32_t>(4, m - m0);
     if (!tb_decode_supported(w, mc, b->max_smem_optin, nullptr))
       return tb_fail(TB_UNSUPPORTED_FORMAT, "the decode kernel's shared-memory plan does not fit this shape");
-    TbCommView ca = va, cy = vy;
-    for (uint32_t r = 0; r < va.world; ++r) { ca.data[r] += m0; cy.data[r] += size_t(m0) * w->n; }
+    TbCommView ca = va;
+    for (uint32_t r = 0; r < va.world; ++r) ca.data[r] += m0;
     DecodeArgs d{};
-    d.w = w; d.x_dtype = x_dtype; d.m = mc; d.y_dtype = y_dtype; d.y_row_stride = uint32_t(w->n);
+    d.w = w; d.x_dtype = x_dtype; d.m = mc; d.y_row_stride = uint32_t(w->n);
     d.x = static_cast<const uint8_t*>(x) + size_t(m0) * w->k * dtype_size(x_dtype);
     d.status = b->d_status; d.pdl = false;
     d.scratch = b->d_prep; d.scratch_bytes = b->d_prep_cap;
     d.comm_absmax = va.world > 1 ? &ca : nullptr;
-    if (in_kernel) {
-      d.y = static_cast<uint8_t*>(y) + size_t(m0) * w->n * dtype_size(y_dtype);
-      d.comm_y = vy.world > 1 ? &cy : nullptr;
-    } else {
-      // fp32 partial rows straight into this rank's slot; one reduce kernel after the last pass
-      d.y = vy.data[vy.rank] + size_t(m0) * w->n;
-      d.y_dtype = TB_F32;
-    }
+    // fp32 partial rows straight into this rank's slot; one reduce kernel after the last pass
+    d.y = vy.data[vy.rank] + size_t(m0) * w->n;
+    d.y_dtype = TB_F32;
     TB_CUDA(tb_launch_prepare(d, st), "launch prepare");
     TB_CUDA(tb_launch_decode(d, b->prop.multiProcessorCount, b->max_smem_optin, st), "launch decode");
   }
-  if (!in_kernel) return tb_comm_allreduce_f32(comm, slot_y, uint32_t(size_t(m) * w->n), 0, static_cast<float*>(y), st);
-  return TB_OK;
+  return tb_comm_allreduce_f32(comm, slot_y, uint32_t(size_t(m) * w->n), 0, static_cast<float*>(y), st);
 }
 
 extern "C" tb_status tb_backend_reserve(tb_backend* b, const tb_weights* w, uint32_t max_m) {
@@ -669,20 +668,44 @@ extern "C" tb_status tb_stack_forward_dev(tb_stack* st, const void* x, tb_dtype 
   if (tb_status s = use_device(b)) return s;
   cudaStream_t cs = stream ? static_cast<cudaStream_t>(stream) : b->stream;
   const size_t n_layers = st->layers.size();
+  if (y_last && st->group_of[n_layers - 1] >= 0)
+    return tb_fail(TB_INVALID_INPUT, "the last layer belongs to a grouped run: its output is read with tb_stack_read_output, y_last must be NULL");
+  const bool x_aligned = (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
   for (size_t i = 0; i < n_layers; ++i) {
     const int gi = st->group_of[i];
-    if (gi >= 0 && m <= 4 && !(flags & TB_FWD_FORCE_PREFILL)) {
-      // one prepare + one grouped decode for the whole run
+    if (gi >= 0) {
+      // A run of layers that read the stack input.  Outputs go to the group buffer as
+      // [layer][m][n] bf16, whichever kernel family runs.
       const StackGroup& g = st->groups[gi];
       const tb_weights* w = st->layers[i];
-      DecodeArgs d{};
-      d.w = w; d.x = x; d.x_dtype = xd; d.m = m; d.y = g.y; d.y_dtype = TB_BF16; d.y_row_stride = uint32_t(w->n);
-      d.status = b->d_status; d.pdl = (flags & TB_FWD_PDL) != 0; d.scratch = b->d_prep; d.scratch_bytes = b->d_prep_cap;
-      d.layers = g.d_descs; d.layer_count = uint32_t(g.count); d.y_layer_stride = uint32_t(size_t(m) * w->n);
-      if (!tb_decode_supported(w, m, b->max_smem_optin, nullptr))
-        return tb_fail(TB_UNSUPPORTED_FORMAT, "the decode kernel's shared-memory plan does not fit this shape");
-      TB_CUDA(tb_launch_prepare(d, cs), "launch prepare");
-      TB_CUDA(tb_launch_decode(d, b->prop.multiProcessorCount, b->max_smem_optin, cs), "launch grouped decode");
+      const bool prefill = (flags & TB_FWD_FORCE_PREFILL) || (m > 16 && !(flags & TB_FWD_FORCE_DECODE));
+      if (prefill) {
+        for (size_t l = 0; l < g.count; ++l) {
+          tb_forward_args a{};
+          a.x = x; a.x_dtype = xd; a.m = m;
+          a.y = static_cast<uint8_t*>(g.y) + l * size_t(m) * w->n * 2; a.y_dtype = TB_BF16;
+          a.flags = TB_FWD_A8 | (flags & (TB_FWD_PDL | TB_FWD_FORCE_DECODE | TB_FWD_FORCE_PREFILL));
+          a.stream = cs;
+          if (tb_status s = forward_dev(b, st->layers[i + l], a, cs, nullptr)) return s;
+        }
+      } else {
+        // one grouped decode launch per pass of up to four tokens
+        for (uint32_t m0 = 0; m0 < m; m0 += 4) {
+          const uint32_t mc = std::min<uint32_t>(4, m - m0);
+          DecodeArgs d{};
+          d.w = w; d.x_dtype = xd; d.m = mc; d.y_dtype = TB_BF16; d.y_row_stride = uint32_t(w->n);
+          d.x = static_cast<const uint8_t*>(x) + size_t(m0) * w->k * dtype_size(xd);
+          d.y = static_cast<uint8_t*>(g.y) + size_t(m0) * w->n * 2;
+          d.status = b->d_status; d.pdl = (flags & TB_FWD_PDL) != 0 || m0 > 0;
+          d.fused = x_aligned;
+          d.scratch = b->d_prep; d.scratch_bytes = b->d_prep_cap;
+          d.layers = g.d_descs; d.layer_count = uint32_t(g.count); d.y_layer_stride = uint32_t(size_t(m) * w->n);
+          if (!tb_decode_supported(w, mc, b->max_smem_optin, nullptr))
+            return tb_fail(TB_UNSUPPORTED_FORMAT, "the decode kernel's shared-memory plan does not fit this shape");
+          if (!d.fused) TB_CUDA(tb_launch_prepare(d, cs), "launch prepare");
+          TB_CUDA(tb_launch_decode(d, b->prop.multiProcessorCount, b->max_smem_optin, cs), "launch grouped decode");
+        }
+      }
       i += g.count - 1;
       continue;
     }
@@ -708,7 +731,7 @@ extern "C" tb_status tb_stack_forward_host(tb_stack* st, const void* x, tb_dtype
   clear_error();
   if (!st || !x || !y_bf16) return tb_fail(TB_NULL_ARG, "null argument");
   if (m == 0) return TB_OK;
-  if (m > st->max_m || m > 4) return tb_fail(TB_SHAPE_MISMATCH, "token count exceeds the stack's max_m or the grouped kernel's four tokens");
+  if (m > st->max_m) return tb_fail(TB_SHAPE_MISMATCH, "token count exceeds the stack's max_m");
   if (xd == TB_I8) return tb_fail(TB_INVALID_INPUT, "host int8 activations are not accepted here; pass fp32 or bf16");
   for (int gi : st->group_of)
     if (gi < 0) return tb_fail(TB_INVALID_INPUT, "every layer of the stack must belong to a grouped run");
@@ -743,6 +766,7 @@ extern "C" tb_status tb_stack_read_output(tb_stack* st, uint32_t layer, uint32_t
   clear_error();
   if (!st || !out_bf16) return tb_fail(TB_NULL_ARG, "null argument");
   if (layer >= st->layers.size() || st->group_of[layer] < 0) return tb_fail(TB_INVALID_INPUT, "layer is not part of a grouped run");
+  if (m == 0 || m > st->max_m) return tb_fail(TB_SHAPE_MISMATCH, "token count exceeds the stack's max_m");
   if (tb_status s = use_device(st->backend)) return s;
   const StackGroup& g = st->groups[st->group_of[layer]];
   const size_t per_layer = size_t(m) * st->layers[layer]->n * 2;

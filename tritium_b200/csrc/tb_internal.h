@@ -70,6 +70,7 @@ struct tb_weights {
 };
 
 void tb_set_error(const std::string& message);
+void tb_clear_error();
 tb_status tb_fail(tb_status code, const std::string& message);
 tb_status tb_cuda_fail(cudaError_t err, const char* what);
 
@@ -109,15 +110,19 @@ struct DecodeArgs {
   const float* row_scale;
   uint32_t* status;
   bool pdl;
+  // fused: the decode kernel quantises x and builds its activation tables itself (x 16-byte
+  // aligned; no scratch, no prepare launch).  Otherwise the tables come from `scratch`, which
+  // tb_launch_prepare filled on the same stream.
+  bool fused;
   void* scratch; size_t scratch_bytes;   // activation tables (written by the prepare kernel)
   bool tables_shared;   // the tables in scratch were prepared for an earlier launch of the same input
   // grouped launch: `layer_count` layers shaped like `w` read the same activations; outputs are
   // written as [layer][m][n] with `y_layer_stride` elements between layers
   const TbLayerDesc* layers; uint32_t layer_count; uint32_t y_layer_stride;
   // tensor-parallel row shard (single layer): the prepare kernel exchanges the per-token absmax
-  // through `comm_absmax`, the decode kernel writes fp32 partial rows into `comm_y` and finishes
-  // the all-reduce itself.  Both null = no peers.
-  const TbCommView* comm_absmax; const TbCommView* comm_y;
+  // through `comm_absmax`.  Null = no peers.
+  const TbCommView* comm_absmax;
+  uint32_t inject_missing_tx;   // test hook (non-fused launches): the table barrier expects this many bytes too many
 };
 cudaError_t tb_launch_prepare(const DecodeArgs& a, cudaStream_t stream);
 size_t tb_decode_scratch_bytes(const tb_weights* w, uint32_t m);

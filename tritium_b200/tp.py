@@ -142,10 +142,10 @@ class PeerComm:
         self._check(self._L.tb_comm_allreduce_f32(self._h, C.c_uint32(slot), C.c_uint32(count), int(op_max),
                                                   C.c_void_p(out.data_ptr()), C.c_void_p(s.cuda_stream)))
 
-    def linear_fused(self, handle, slot_absmax: int, slot_y: int, x, y, reduce_in_kernel: bool = False, stream=None) -> None:
+    def linear_fused(self, handle, slot_absmax: int, slot_y: int, x, y, stream=None) -> None:
         """Row-parallel forward of up to 8 tokens (`tb_linear_forward_tp_dev`): the prepare kernel
         exchanges the row absmax; the output all-reduce is one reduce kernel behind the decode
-        kernel, or (``reduce_in_kernel``) done by the decode kernel's CTAs themselves."""
+        kernel."""
         import ctypes as C
         import torch
         from . import _lib
@@ -153,7 +153,7 @@ class PeerComm:
         s = stream if stream is not None else torch.cuda.current_stream()
         self._check(self._L.tb_linear_forward_tp_dev(self.backend._h, handle._h, self._h, C.c_uint32(slot_absmax), C.c_uint32(slot_y),
                                                      C.c_void_p(x.data_ptr()), dt[x.dtype], C.c_uint32(x.shape[0]),
-                                                     C.c_void_p(y.data_ptr()), dt[y.dtype], C.c_uint32(1 if reduce_in_kernel else 0),
+                                                     C.c_void_p(y.data_ptr()), dt[y.dtype], C.c_uint32(0),
                                                      C.c_void_p(s.cuda_stream)))
 
     def close(self) -> None:
@@ -204,11 +204,10 @@ class TPLinear:
         # small messages (decode) are reduced over peer memory when the executor carries a
         # communicator: the kernels write their partials straight into its slots
         comm = getattr(executor, "comm", None) if mode == "row" and world > 1 else None
-        # `fused` (decode-sized batches): None = separate absmax and one-shot reduce kernels around the
-        # ordinary forward (fastest measured on 2 and 8 GPUs); False = the prepare kernel exchanges
-        # the row absmax itself and one reduce kernel follows the decode kernel; True = the decode
-        # kernel's CTAs also do the output reduce (every CTA then pays an NVLink round trip)
-        self.comm, self.peer_m, self.fused = comm, 0, None
+        # `fused` (decode-sized batches): False = separate absmax and one-shot reduce kernels around
+        # the ordinary forward; True = the prepare kernel exchanges the row absmax itself and one
+        # reduce kernel follows the decode kernel
+        self.comm, self.peer_m, self.fused = comm, 0, False
         if comm is not None:
             self.peer_m = min(max_m, comm.slot_bytes // (4 * self.geometry.n))
             if self.peer_m:
@@ -233,8 +232,8 @@ class TPLinear:
             self.executor.linear(self.handle, x, y, None)
             return y
         absmax = self.absmax[:m]
-        if self.comm is not None and m <= min(self.peer_m, 8) and self.fused is not None:
-            self.comm.linear_fused(self.handle, self.slot_absmax, self.slot_y, x, y, reduce_in_kernel=bool(self.fused))
+        if self.comm is not None and m <= min(self.peer_m, 8) and self.fused:
+            self.comm.linear_fused(self.handle, self.slot_absmax, self.slot_y, x, y)
             return y
         if self.comm is not None and m <= self.peer_m:
             self.executor.row_absmax(x, self.peer_absmax[:m])
@@ -320,7 +319,7 @@ class TPDecoderStack:
                     lin.comm = lin._comm_built if enabled else None
 
     def use_fused_reduce(self, enabled: bool) -> None:
-        """Row-parallel decode: all-reduce inside the prepare/decode kernels, or separate one-shot kernels."""
+        """Row-parallel decode: absmax exchange inside the prepare kernel, or separate one-shot kernels."""
         for row in self.layers:
             for lin in row:
                 lin.fused = enabled
