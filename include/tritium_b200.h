@@ -189,6 +189,12 @@ tb_status tb_act_absmax_dev(tb_backend* backend, const void* x, tb_dtype x_dtype
 tb_status tb_backend_reserve(tb_backend* backend, const tb_weights* weights, uint32_t max_m);
 /* Reads and clears the device status word written by bounded waits / finite checks. */
 tb_status tb_backend_check(tb_backend* backend, void* stream);
+/* Test hook, no counterpart in the reference: when `enable` is non-zero, the NEXT
+ * tb_linear_forward_a8_static call makes its kernel wait for table bytes that nobody sends.  The
+ * bounded wait runs out (about two seconds), the kernel returns by itself, tb_backend_check
+ * reports TB_TIMEOUT, and the context stays usable.  Nothing faults, traps or spins without a
+ * limit.  The hook disarms itself after that one call. */
+tb_status tb_backend_inject_wait_timeout(tb_backend* backend, uint32_t enable);
 
 /* ------------------------------------------------------------------ trait path (1 plane, per-channel scale)
  * TernaryBackend::mpgemm (crates/tritium-spec/src/lib.rs:200-215; host crates/tritium-cuda/src/cuda/backend.rs:7175-7315)

@@ -1,0 +1,185 @@
+"""GPU tests of the paths around the kernels: chained and grouped layer stacks, non-finite
+activations on the device-pointer entry points, activations that are not 16-byte aligned, and a
+bounded device wait that is made to run out (the kernel returns by itself, the call reports
+TB_TIMEOUT, the next call works)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from oracle import oracle as orc
+from tritium_b200 import _lib, errors
+from tritium_b200.format import SaltV2Codec
+from tritium_b200.synth import bf16_bits_to_f32, f32_to_bf16_bits, make_activations
+
+from gpu_common import rel_l2, uniform_pair
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def backend():
+    import torch
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device: there is no CPU path to fall back to")
+    from tritium_b200 import B200Backend
+    b = B200Backend(0)
+    yield b
+    b.close()
+
+
+def to_dev_bf16(x):
+    import torch
+    return torch.from_numpy(f32_to_bf16_bits(x).view(np.int16).copy()).cuda().view(torch.bfloat16).reshape(x.shape)
+
+
+def bf16_round(v):
+    return bf16_bits_to_f32(f32_to_bf16_bits(np.ascontiguousarray(v, np.float32)))
+
+
+# ------------------------------------------------------------------ layer stacks
+@pytest.mark.parametrize("chain", [[0, 0, 1], [0, 1, 1]], ids=["group_then_chain", "chain_of_three"])
+@pytest.mark.parametrize("m", [2, 6, 20])
+def test_chained_stack_matches_layer_by_layer_oracle(backend, chain, m):
+    """chain[i] = 1 feeds layer i with the bf16 output of layer i-1; the others read the stack input.
+    Decode kernel (one and two passes) and tensor-core kernel."""
+    import torch
+    from tritium_b200 import LinearStack
+    k = 512
+    pairs = [uniform_pair(k, k, 2, seed=200 + i) for i in range(3)]
+    weights = [backend.upload_salt_v2(prod, SaltV2Codec.B3) for prod, _ in pairs]
+    stack = LinearStack(backend, weights, chain, max_m=m)
+    x = make_activations(m, k, seed=23, bf16=True)
+    y_last = torch.zeros(m, k, dtype=torch.float32, device="cuda")
+    stream = torch.cuda.Stream()
+    for flags in (0, _lib.TB_FWD_PDL):
+        y_last.zero_()
+        with torch.cuda.stream(stream):
+            stack.forward_dev(to_dev_bf16(x), y_last=y_last, flags=flags, stream=stream)
+        stream.synchronize()
+        backend.check(stream)
+        prev, want = None, None
+        for i, (_, orac) in enumerate(pairs):
+            want = orc.a8_linear(orac, bf16_round(prev) if chain[i] else x, dump=False)[0]
+            prev = want
+        assert rel_l2(y_last.cpu().numpy(), want) <= 2e-2, flags   # two bf16 hand-offs on the way
+    stack.close()
+
+
+@pytest.mark.parametrize("m,flags", [(6, 0), (6, _lib.TB_FWD_PDL), (20, 0)], ids=["m6", "m6_pdl", "m20_tensor_core"])
+def test_grouped_stack_beyond_four_tokens(backend, m, flags):
+    """A grouped run (layers that read the stack input) takes more than four tokens: the grouped
+    launch is repeated per pass of four tokens; above sixteen the tensor-core kernel runs per layer.
+    Every layer's output is read back from the group buffer."""
+    import torch
+    from tritium_b200 import LinearStack
+    n, k, planes = 96, 1024, 2
+    pairs = [uniform_pair(n, k, planes, seed=300 + i) for i in range(4)]
+    weights = [backend.upload_salt_v2(prod, SaltV2Codec.B3) for prod, _ in pairs]
+    stack = LinearStack(backend, weights, [0] * 4, max_m=max(m, 8))
+    x = make_activations(m, k, seed=29, bf16=True)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        stack.forward_dev(to_dev_bf16(x), flags=flags, stream=stream)
+    stream.synchronize()
+    backend.check(stream)
+    for i, (_, orac) in enumerate(pairs):
+        want = orc.a8_linear(orac, x, dump=False)[0]
+        assert rel_l2(bf16_bits_to_f32(stack.read_output(i, m)), want) <= 1e-2, i
+    got = stack.forward_host(f32_to_bf16_bits(x), m, x_is_bf16=True)
+    for i, (_, orac) in enumerate(pairs):
+        assert rel_l2(bf16_bits_to_f32(got[i]), orc.a8_linear(orac, x, dump=False)[0]) <= 1e-2, i
+    # the last layer belongs to a group: a y_last pointer is refused, not ignored
+    with pytest.raises(errors.InvalidInput):
+        stack.forward_dev(to_dev_bf16(x), y_last=torch.zeros(m, n, dtype=torch.float32, device="cuda"), stream=stream)
+    stack.close()
+
+
+# ------------------------------------------------------------------ input checks on device pointers
+@pytest.mark.parametrize("bad", [float("nan"), float("inf")], ids=["nan", "inf"])
+@pytest.mark.parametrize("m", [2, 24], ids=["decode", "tensor_core"])
+def test_nonfinite_bf16_activation_is_reported(backend, bad, m):
+    """quantize_act_int8 (crates/tritium-spec/src/lib.rs:351-378) would carry a NaN through to the
+    output; the device paths report it instead of returning clamped codes."""
+    import torch
+    n, k = 64, 512
+    prod, _ = uniform_pair(n, k, 1, seed=9)
+    resident = backend.upload_salt_v2(prod, SaltV2Codec.B3)
+    backend.reserve(resident, m)
+    x = make_activations(m, k, seed=3, bf16=True)
+    x[m - 1, 77] = bad
+    x_dev = torch.from_numpy(x).cuda().to(torch.bfloat16)
+    y_dev = torch.zeros(m, n, dtype=torch.float32, device="cuda")
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        backend.forward_dev(resident, x_dev, y_dev, a8=True, stream=stream)
+    with pytest.raises(errors.InvalidInput, match="non-finite"):
+        backend.check(stream)
+    if m <= 4:
+        L = _lib.load()
+        errors.check(L.tb_linear_forward_a8_static(backend._h, resident._h, C.c_void_p(x_dev.data_ptr()), _lib.TB_BF16, None,
+                                                   C.c_uint32(m), C.c_void_p(y_dev.data_ptr()), _lib.TB_F32, C.c_void_p(stream.cuda_stream)))
+        with pytest.raises(errors.InvalidInput, match="non-finite"):
+            backend.check(stream)
+    # the status word is clear again and the next call is clean
+    x[m - 1, 77] = 1.0
+    with torch.cuda.stream(stream):
+        backend.forward_dev(resident, torch.from_numpy(x).cuda().to(torch.bfloat16), y_dev, a8=True, stream=stream)
+    backend.check(stream)
+
+
+def test_unaligned_activation_pointer_takes_the_scratch_path(backend):
+    """The one-launch path reads activations with 16-byte loads; a pointer that is only 2-byte
+    aligned goes through the preparation kernel and gives the same bits."""
+    import torch
+    n, k, m = 80, 768, 3
+    prod, orac = uniform_pair(n, k, 3, seed=13)
+    resident = backend.upload_salt_v2(prod, SaltV2Codec.B3)
+    x = make_activations(m, k, seed=4, bf16=True)
+    flat = torch.zeros(m * k + 8, dtype=torch.bfloat16, device="cuda")
+    aligned, shifted = flat[:m * k].view(m, k), flat[1:m * k + 1].view(m, k)
+    want_dev = torch.zeros(m, n, dtype=torch.float32, device="cuda")
+    got_dev = torch.zeros(m, n, dtype=torch.float32, device="cuda")
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        aligned.copy_(torch.from_numpy(x))
+        backend.forward_dev(resident, aligned, want_dev, a8=True, stream=stream)
+        stream.synchronize()
+        shifted.copy_(torch.from_numpy(x))
+        assert shifted.data_ptr() % 16 != 0
+        backend.forward_dev(resident, shifted, got_dev, a8=True, stream=stream)
+    stream.synchronize()
+    backend.check(stream)
+    assert torch.equal(want_dev, got_dev)
+    assert rel_l2(got_dev.cpu().numpy(), orc.a8_linear(orac, x, dump=False)[0]) <= 1e-5
+
+
+# ------------------------------------------------------------------ a bounded wait that runs out
+def test_bounded_wait_runs_out_and_the_context_stays_usable(backend):
+    """The hook makes one kernel wait for bytes that nobody copies.  The wait has a limit: the kernel
+    returns by itself (no trap, no fault), the status word says so, tb_backend_check turns it into
+    TB_TIMEOUT, and the same backend computes correct results right after."""
+    import torch
+    L = _lib.load()
+    n, k, m = 64, 512, 2
+    prod, orac = uniform_pair(n, k, 2, seed=17)
+    resident = backend.upload_salt_v2(prod, SaltV2Codec.B3)
+    x = make_activations(m, k, seed=5, bf16=True)
+    x_dev = to_dev_bf16(x)
+    y_dev = torch.zeros(m, n, dtype=torch.float32, device="cuda")
+    stream = torch.cuda.Stream()
+
+    def static_call():
+        errors.check(L.tb_linear_forward_a8_static(backend._h, resident._h, C.c_void_p(x_dev.data_ptr()), _lib.TB_BF16, None,
+                                                   C.c_uint32(m), C.c_void_p(y_dev.data_ptr()), _lib.TB_F32, C.c_void_p(stream.cuda_stream)))
+
+    static_call()                       # resolves the scratch address; clean
+    backend.check(stream)
+    errors.check(L.tb_backend_inject_wait_timeout(backend._h, 1))
+    static_call()
+    with pytest.raises(errors.Timeout, match="bounded device wait"):
+        backend.check(stream)
+    y_dev.zero_()
+    static_call()                       # the hook disarmed itself
+    backend.check(stream)
+    assert rel_l2(y_dev.cpu().numpy(), orc.a8_linear(orac, x, dump=False)[0]) <= 1e-5

@@ -1,10 +1,11 @@
-"""The allocation-free forward entry point against the regular device-pointer entry point.
+"""The allocation-free forward entry point against the regular device-pointer entry point and the CPU oracle.
 
 Some users of this library may not allocate device memory while they run (a serving loop with a
 fixed memory plan, a thread that must stay out of the driver's allocator).  For them the library
 offers one call whose scratch is a fixed array inside the library image.  This file checks, through
-the C ABI, that the call gives the same result as the regular path, twice in a row (the array is
-shared and keeps the previous call's contents), and that oversize shapes are refused.
+the C ABI, that the call gives the same bits as the regular path (both run the same arithmetic on
+the same codes) and agrees with the CPU oracle, twice in a row (the array is shared and keeps the
+previous call's contents), and that oversize shapes are refused.
 
 Collected last on purpose: a failure here must not hide the result of any other test.
 """
@@ -13,6 +14,7 @@ import ctypes as C
 import numpy as np
 import pytest
 
+from oracle import oracle as orc
 from tritium_b200 import _lib, errors
 from tritium_b200.format import SaltV2Codec, SaltV2Tensor
 from tritium_b200.synth import f32_to_bf16_bits, make_activations, make_planes
@@ -35,7 +37,9 @@ def test_static_scratch_forward_matches_regular_path_twice(codec):
     L = _lib.load()
     n, k, planes = 200, 1536, 3
     trits, scales = make_planes(n, k, planes, seed=31)
-    resident = backend.upload_salt_v2(SaltV2Tensor.from_matrix_planes("w", trits, scales), codec)
+    tensor = SaltV2Tensor.from_matrix_planes("w", trits, scales)
+    oracle_tensor = orc.Tensor(n, k, 128, tensor.plane_count.copy(), tensor.trits.copy(), tensor.scales.copy())
+    resident = backend.upload_salt_v2(tensor, codec)
     stream = torch.cuda.Stream()
     for call, m in enumerate((1, 3)):                      # two calls in a row, different inputs
         x = make_activations(m, k, seed=50 + call, bf16=True)
@@ -51,7 +55,8 @@ def test_static_scratch_forward_matches_regular_path_twice(codec):
                                                    C.c_void_p(stream.cuda_stream)))
         stream.synchronize()
         backend.check(stream)
-        assert rel_l2(got.cpu().numpy(), want.cpu().numpy()) <= 1e-5, (call, m)
+        assert torch.equal(got, want), (call, m)                                  # same bits as the regular path
+        assert rel_l2(got.cpu().numpy(), orc.a8_linear(oracle_tensor, x, dump=False)[0]) <= 1e-5, (call, m)
     # shapes beyond the fixed scratch, or beyond four tokens, are refused with a clear message
     x_dev = torch.zeros(5, k, dtype=torch.bfloat16, device="cuda")
     y_dev = torch.zeros(5, n, dtype=torch.float32, device="cuda")

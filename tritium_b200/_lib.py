@@ -27,7 +27,7 @@ EXPORTS = [
     "tb_stack_create", "tb_stack_forward_dev", "tb_stack_forward_host", "tb_stack_bytes_per_step", "tb_stack_read_output", "tb_stack_free",
     "tb_tp_shard_sizes", "tb_tp_shard", "tb_fmt_pack", "tb_fmt_unpack", "tb_fmt_plane_bytes",
     "tb_fmt_resident_sizes", "tb_fmt_resident_build", "tb_fmt_package_write", "tb_fmt_tq2_pack_rows",
-    "tb_fmt_quantize_act_int8", "tb_linear_forward_a8_static",
+    "tb_fmt_quantize_act_int8", "tb_linear_forward_a8_static", "tb_backend_inject_wait_timeout",
 ]
 
 
@@ -70,6 +70,70 @@ class ResidentSizes(C.Structure):
 
 _lib = None
 
+# (restype, argtypes) of every export, in the order of include/tritium_b200.h.  Pointers to
+# opaque handles, structs and buffers are all c_void_p: ctypes then accepts byref(), arrays,
+# c_void_p values, ints and None alike, and checks the argument count and the integer widths.
+_P, _U32, _U64, _SZ, _I = C.c_void_p, C.c_uint32, C.c_uint64, C.c_size_t, C.c_int
+_ST = C.c_int
+_SIGNATURES = {
+    "tb_abi_version": (C.c_uint32, []),
+    "tb_last_error": (C.c_char_p, []),
+    "tb_backend_create": (_ST, [_I, _P]),
+    "tb_backend_free": (None, [_P]),
+    "tb_backend_caps": (_ST, [_P, _P]),
+    "tb_backend_synchronize": (_ST, [_P]),
+    "tb_tq2_upload": (_ST, [_P, _P, _SZ, _U32, _U32, _P]),
+    "tb_salt_v2_upload": (_ST, [_P, _I, _U32, _U32, _U32, _P, _SZ, _P, _SZ, _P, _SZ, _U32, _P]),
+    "tb_salt_v2_upload_package": (_ST, [_P, _P, _SZ, C.c_char_p, _P]),
+    "tb_weights_info_get": (_ST, [_P, _P]),
+    "tb_weights_free": (None, [_P]),
+    "tb_salt_v2_forward_exact": (_ST, [_P, _P, _P, _U32, _P, _P]),
+    "tb_linear_forward_f32": (_ST, [_P, _P, _P, _U32, _P, _P]),
+    "tb_linear_forward_a8": (_ST, [_P, _P, _P, _I, _U32, _P, _I, _P, _P]),
+    "tb_salt_v2_gather_rows": (_ST, [_P, _P, _P, _SZ, _P]),
+    "tb_linear_forward_dev": (_ST, [_P, _P, _P, _P]),
+    "tb_linear_forward_a8_static": (_ST, [_P, _P, _P, _I, _P, _U32, _P, _I, _P]),
+    "tb_act_absmax_dev": (_ST, [_P, _P, _I, _U32, _U32, _P, _P]),
+    "tb_backend_reserve": (_ST, [_P, _P, _U32]),
+    "tb_backend_check": (_ST, [_P, _P]),
+    "tb_backend_inject_wait_timeout": (_ST, [_P, _U32]),
+    "tb_mpgemm": (_ST, [_P, _P, _P, _P, _U32, _U32, _U32, _P]),
+    "tb_mpgemm_with_act_quant": (_ST, [_P, _P, _P, _P, _U32, _U32, _U32, _P]),
+    "tb_stack_create": (_ST, [_P, _P, _P, _U32, _U32, _P]),
+    "tb_stack_forward_dev": (_ST, [_P, _P, _I, _U32, _P, _I, _U32, _P]),
+    "tb_stack_forward_host": (_ST, [_P, _P, _I, _U32, _P, _U32]),
+    "tb_stack_bytes_per_step": (C.c_uint64, [_P, _U32]),
+    "tb_stack_read_output": (_ST, [_P, _U32, _U32, _P]),
+    "tb_stack_free": (None, [_P]),
+    "tb_comm_create": (_ST, [_P, _U32, _U32, _SZ, _U32, _U32, _P]),
+    "tb_comm_export": (_ST, [_P, _P]),
+    "tb_comm_connect": (_ST, [_P, _P]),
+    "tb_comm_slot": (C.c_void_p, [_P, _U32]),
+    "tb_comm_allreduce_f32": (_ST, [_P, _U32, _U32, _I, _P, _P]),
+    "tb_linear_forward_tp_dev": (_ST, [_P, _P, _P, _U32, _U32, _P, _I, _U32, _P, _I, _U32, _P]),
+    "tb_comm_free": (None, [_P]),
+    "tb_tp_shard_sizes": (_ST, [_I, _U32, _U32, _U32, _U32, _I, _U32, _U32, _P]),
+    "tb_tp_shard": (_ST, [_I, _U32, _U32, _U32, _U32, _P, _P, _I, _U32, _U32, _P, _P, _P, _P]),
+    "tb_fmt_pack": (C.c_int64, [_I, _P, _SZ, _P, _SZ]),
+    "tb_fmt_unpack": (_ST, [_I, _P, _SZ, _SZ, _P]),
+    "tb_fmt_plane_bytes": (C.c_size_t, [_I, _SZ]),
+    "tb_fmt_resident_sizes": (_ST, [_I, _U32, _U64, _U64, _P, _P]),
+    "tb_fmt_resident_build": (_ST, [_I, _U32, _U64, _U64, _P, _P, _P, _P, _P, _P, _P]),
+    "tb_fmt_package_write": (C.c_int64, [_I, C.c_char_p, _U32, _U64, _U64, _P, _P, _P, _P, _SZ]),
+    "tb_fmt_tq2_pack_rows": (_ST, [_P, _U64, _U64, _P]),
+    "tb_fmt_quantize_act_int8": (None, [_P, _U64, _U64, _P, _P]),
+}
+
+
+def _declare(L: C.CDLL) -> None:
+    missing = [name for name in EXPORTS if name not in _SIGNATURES]
+    if missing:
+        raise RuntimeError(f"no signature recorded for {missing}")
+    for name, (restype, argtypes) in _SIGNATURES.items():
+        fn = getattr(L, name)
+        fn.restype = restype
+        fn.argtypes = argtypes
+
 
 def load(build_if_missing: bool = True) -> C.CDLL:
     """Load the shared library, building it in-tree first when it is absent."""
@@ -82,22 +146,7 @@ def load(build_if_missing: bool = True) -> C.CDLL:
         from . import build as _build
         _build.build()
     L = C.CDLL(LIB_PATH)
-    L.tb_abi_version.restype = C.c_uint32
-    L.tb_last_error.restype = C.c_char_p
-    L.tb_fmt_pack.restype = C.c_int64
-    L.tb_fmt_package_write.restype = C.c_int64
-    L.tb_fmt_plane_bytes.restype = C.c_size_t
-    L.tb_stack_bytes_per_step.restype = C.c_uint64
-    L.tb_backend_free.restype = None
-    L.tb_comm_free.restype = None
-    L.tb_comm_free.argtypes = [C.c_void_p]
-    L.tb_comm_slot.restype = C.c_void_p
-    L.tb_comm_slot.argtypes = [C.c_void_p, C.c_uint32]
-    L.tb_weights_free.restype = None
-    L.tb_stack_free.restype = None
-    L.tb_backend_free.argtypes = [C.c_void_p]
-    L.tb_weights_free.argtypes = [C.c_void_p]
-    L.tb_stack_free.argtypes = [C.c_void_p]
+    _declare(L)
     _lib = L
     return L
 

@@ -1152,6 +1152,8 @@ extern "C" tb_status tb_linear_forward_a8_static(tb_backend* backend, const tb_w
   d.y = y; d.y_dtype = y_dtype; d.y_row_stride = uint32_t(weights->n);
   d.status = backend->d_status; d.pdl = false;
   d.scratch = tables; d.scratch_bytes = kStaticTableBytes;
+  d.inject_missing_tx = backend->inject_missing_tx;   // test hook, one call only
+  backend->inject_missing_tx = 0;
   // Nothing in the tables has to start at zero: the prepare kernel rewrites every entry the decode
   // kernel of the same call reads (z entries, start values, token scales) before it is read.
   err = tb_launch_prepare(d, st);

@@ -187,6 +187,7 @@ struct QuantParams {
   const void* x; const float* act_scale_in; const float* act_absmax_in;
   int8_t* qperm; int32_t* qinit; float* ascale;
   uint32_t m, m_pad, k, x_dtype, codec;
+  uint32_t* status;
 };
 
 __global__ void __launch_bounds__(256) prefill_quant_kernel(const QuantParams p) {
@@ -232,6 +233,10 @@ __global__ void __launch_bounds__(256) prefill_quant_kernel(const QuantParams p)
       else {
         const float v = p.x_dtype == TB_F32 ? static_cast<const float*>(p.x)[size_t(t) * p.k + i]
                                             : __bfloat162float(static_cast<const __nv_bfloat16*>(p.x)[size_t(t) * p.k + i]);
+        // a NaN would clamp to a finite code: report non-finite activations instead
+        if (!(fabsf(v) <= 3.402823466e+38f) && atomicOr(&p.status[TBS_FLAGS], TBF_NONFINITE_ACT) == 0) {
+          p.status[TBS_INFO0] = t * p.k + i; p.status[TBS_INFO1] = __float_as_uint(v);
+        }
         q = int(fminf(127.f, fmaxf(-128.f, rintf(__fmul_rn(v, scale_q)))));
       }
       sum += q;
@@ -670,7 +675,7 @@ cudaError_t tb_launch_prefill(const PrefillArgs& a, int sm_count, cudaStream_t s
   QuantParams qp{};
   qp.x = a.x; qp.act_scale_in = a.act_scale_in; qp.act_absmax_in = a.act_absmax_in;
   qp.qperm = sc.qperm; qp.qinit = sc.qinit; qp.ascale = sc.ascale;
-  qp.m = a.m; qp.m_pad = m_pad; qp.k = k; qp.x_dtype = uint32_t(a.x_dtype); qp.codec = uint32_t(w->codec);
+  qp.m = a.m; qp.m_pad = m_pad; qp.k = k; qp.x_dtype = uint32_t(a.x_dtype); qp.codec = uint32_t(w->codec); qp.status = a.status;
   prefill_quant_kernel<<<m_pad, 256, 0, stream>>>(qp);
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return err;

@@ -154,6 +154,13 @@ extern "C" tb_status tb_backend_check(tb_backend* b, void* stream) {
   return tb_fail(TB_BACKEND, "kernel reported an invalid configuration");
 }
 
+extern "C" tb_status tb_backend_inject_wait_timeout(tb_backend* b, uint32_t enable) {
+  clear_error();
+  if (!b) return tb_fail(TB_NULL_ARG, "backend is null");
+  b->inject_missing_tx = enable ? 16u : 0u;
+  return TB_OK;
+}
+
 // ---------------------------------------------------------------- weights
 namespace {
 

@@ -40,6 +40,7 @@ struct tb_backend {
   // scratch for the decode path: activation tables built by the prepare kernel
   void* d_prep = nullptr; size_t d_prep_cap = 0;
   int max_smem_optin = 0;
+  uint32_t inject_missing_tx = 0;   // test hook: armed by tb_backend_inject_wait_timeout, used once
 };
 
 // How the decode kernel walks one weight tensor (fixed at upload).
