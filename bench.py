@@ -33,9 +33,11 @@ N_ROWS, K_COLS, PLANES = 6912, 2560, 3
 METRIC = "ternary linear HBM GB/s (M=1)"
 UNIT = "GB/s"
 PLANE_BYTES = {"b3": 52, "d2": 64}
-# dram__bytes_read.sum + dram__bytes_write.sum of ONE grouped decode launch, from the ncu capture
-# summarised under profiles/ (decode kernel, C2, B3, M=1); key = (codec, tokens, weight copies per launch)
-NCU_TRAFFIC_BYTES = {("b3", 1, 26): 301_977_600 + 4_381_440}
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE grouped decode launch, from an ncu capture of
+# this command (decode kernel, C2, B3, M=1); key = (codec, tokens, weight copies per launch).  The
+# figure belongs to the kernel it was captured on; `traffic_source` in the output says so.
+NCU_TRAFFIC_BYTES = {("b3", 1, 26): 302_004_224 + 3_978_496}
+NCU_TRAFFIC_SOURCE = "ncu capture of one grouped launch of this command (dram__bytes_read.sum + dram__bytes_write.sum); constant, not re-measured per run"
 
 
 def algorithmic_bytes(codec: str, m: int, x_size: int = 2, y_size: int = 2) -> int:
@@ -137,9 +139,10 @@ def run_reference(args) -> None:
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-        "config": {"workload": "c2_3plane_k2560_n6912_b3_m1", "sample": "one layer forward per step"},
+        "config": {"workload": "c2_3plane_k2560_n6912_b3_m1"},
+        "setup": {"sample": "one layer forward per step"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
-                         "sample": "one C2 layer forward (M=1) per step; oracle rows split over POSIX threads"},
+                         "sample": f"one C2 layer forward (M=1) per step; scalar port of salt_v2_matvec_into, rows split over {cores} POSIX threads"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -195,7 +198,82 @@ def measure_prefill(torch, backend, weights, m: int, codec_name: str, steps: int
                          "peak_kind": kind, "frac_of_nominal_4500": tops / 4500.0, "kernel": "prefill_kernel"}}
 
 
-def measure_tp(torch, dist, backend, rank: int, world: int, codec, codec_name: str, args, stream) -> dict:
+def measure_single_layer(torch, backend, weights, x_dev, m: int, layer_bytes: int, steps: int, stream, pdl_flag: int) -> dict:
+    """One linear per launch (the call shape of a decoder's ModelRunner): every layer of the rotating
+    set through tb_linear_forward_dev, eagerly and as a CUDA graph whose launches chain with
+    programmatic dependent launch.  GB/s = algorithmic bytes of one layer / time per launch."""
+    y_dev = torch.zeros((m, N_ROWS), dtype=torch.bfloat16, device="cuda")
+    out = {"workload": f"c2_3plane_k2560_n6912_m{m}, one linear per launch over {len(weights)} weight copies", "launches_per_linear": 1}
+
+    def sweep(flags):
+        for w in weights:
+            backend.forward_dev(w, x_dev, y_dev, flags=flags, stream=stream)
+
+    with torch.cuda.stream(stream):
+        for name, flags, use_graph in (("eager", 0, False), ("graph_pdl", pdl_flag, True)):
+            sweep(flags)
+            stream.synchronize()
+            run = lambda: sweep(flags)
+            if use_graph:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    sweep(flags)
+                run = graph.replay
+            for _ in range(3):
+                run()
+            stream.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(steps):
+                run()
+            e1.record(stream)
+            stream.synchronize()
+            backend.check(stream)
+            us = e0.elapsed_time(e1) * 1e3 / (steps * len(weights))
+            out[name] = {"us_per_linear": us, "gbs": layer_bytes / (us * 1e-6) / 1e9}
+    return out
+
+
+def measure_e2e_per_linear(torch, backend, weights, x_bits, m: int, layer_bytes: int, rounds: int) -> dict:
+    """The reference's call shape: one host-pointer call per linear (tb_linear_forward_a8: x host ->
+    device, kernel, y device -> host, one synchronisation), over the rotating weight set."""
+    for w in weights[:3]:
+        backend.linear_forward_a8(w, x_bits, m, y_dtype="bf16", x_is_bf16=True)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(rounds):
+        for w in weights:
+            backend.linear_forward_a8(w, x_bits, m, y_dtype="bf16", x_is_bf16=True)
+    dt = (time.perf_counter() - t0) / (rounds * len(weights))
+    return {"value": layer_bytes / dt / 1e9, "unit": UNIT, "us_per_call": dt * 1e6, "api": "tb_linear_forward_a8 (one call per linear)",
+            "h2d_bytes_per_call": m * K_COLS * 2, "d2h_bytes_per_call": m * N_ROWS * 2}
+
+
+def measure_int8_peak(torch) -> dict | None:
+    """Dense INT8 GEMM rate of the library GEMM on this GPU (torch._int_mm, 8192^3, best of 10):
+    the denominator SURVEY-style rooflines ask for when no INT8 figure was measured beforehand."""
+    try:
+        n = 8192
+        a = torch.randint(-8, 8, (n, n), dtype=torch.int8, device="cuda")
+        bm = torch.randint(-8, 8, (n, n), dtype=torch.int8, device="cuda")
+        for _ in range(3):
+            torch._int_mm(a, bm)
+        torch.cuda.synchronize()
+        best = float("inf")
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch._int_mm(a, bm)
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        return {"tops": 2.0 * n ** 3 / (best * 1e-3) / 1e12, "how": "torch._int_mm int8 8192^3, best of 10, CUDA events"}
+    except Exception as exc:  # the library GEMM may not offer int8 on this build
+        return {"tops": None, "how": f"torch._int_mm unavailable: {type(exc).__name__}: {exc}"[:200]}
+
+
+def measure_tp(torch, dist, backend, rank: int, world: int, codec, codec_name: str, args, stream,
+               shape_name: str = "27b", batches=(1,), m_prefill: int = 0, reduce_variants: bool = True) -> dict:
     """Tensor-parallel leg: the linears of the 27B-class decoder (64 layers x {QKV 5120->7168,
     O 5120->5120, gate+up 5120->34816, down 17408->5120}, 2 planes) sharded over `world` GPUs:
     QKV and gate/up column-parallel, O and down row-parallel with a MAX all-reduce of the per-token
@@ -203,14 +281,13 @@ def measure_tp(torch, dist, backend, rank: int, world: int, codec, codec_name: s
     layers are built and timed (each rank streams 2 x 144 MB > L2 per step); the 64-layer step
     time is L-layer time x 64 / L, stated in the output."""
     from tritium_b200 import _lib, tp
-    shape = tp.DECODER_27B if args.tp_shape == "27b" else tp.DECODER_2B
+    shape = tp.DECODER_27B if shape_name == "27b" else tp.DECODER_2B
     # enough distinct layers that one rank's weights of a timed step exceed L2 (126 MB)
-    built = 2 * world if args.tp_shape == "27b" else 12 * world
-    out = {"workload": f"{'c5_27b_2plane' if args.tp_shape == '27b' else 'c4_2b_1plane'}_tp{world}_{codec_name}", "layers_timed": built,
+    built = 2 * world if shape_name == "27b" else 12 * world
+    out = {"workload": f"{'c5_27b_2plane' if shape_name == '27b' else 'c4_2b_1plane'}_tp{world}_{codec_name}", "layers_timed": built,
            "layers_model": shape.layers,
            "collective": "nccl all_reduce (fp32 sum after O and down; fp32 max of the row absmax before them)" if world > 1 else "none"}
-    m_prefill = args.tp_prefill_m
-    batches = [int(v) for v in args.tp_batches.split(",") if v]
+    batches = list(batches)
     max_m = max([1, m_prefill] + batches)
     comm = None
     if world > 1:
@@ -267,7 +344,7 @@ def measure_tp(torch, dist, backend, rank: int, world: int, codec, codec_name: s
 
     ms, graphed = timed(1, not args.no_graph)
     out["decode_m1"] = decode_entry(ms, graphed, "separate absmax and one-shot reduce kernels over peer memory" if world > 1 else "none")
-    if world > 1:
+    if world > 1 and reduce_variants:
         stack.use_fused_reduce(True)
         ms, graphed = timed(1, not args.no_graph)
         out["decode_m1_absmax_in_kernel"] = decode_entry(ms, graphed, "absmax exchange inside the prepare kernel + one reduce kernel over peer memory")
@@ -353,8 +430,6 @@ def run_b200(args) -> None:
                 step()
             stop.record(stream)
             stream.synchronize()
-            if args.steps * 1.0 < 0:  # pragma: no cover
-                pass
             elapsed_ms = start.elapsed_time(stop)
             # keep the sampler alive long enough to see the clocks under load on short runs
             t_end = time.time() + 0.6
@@ -404,9 +479,36 @@ def run_b200(args) -> None:
             prefill["roofline"]["frac"] *= scale
             prefill["roofline"]["frac_of_nominal_4500"] *= scale
 
-    tp_leg = None
+    single = e2e_linear = int8_peak = None
+    if not args.quick:
+        single = measure_single_layer(torch, backend, weights, x_dev, m, layer_bytes, max(3, min(args.steps, 10)), stream, _lib.TB_FWD_PDL)
+        e2e_linear = measure_e2e_per_linear(torch, backend, weights, x_bits, m, layer_bytes, 3)
+        if prefill is not None:
+            int8_peak = measure_int8_peak(torch)
+            if int8_peak and int8_peak.get("tops"):
+                prefill["roofline"]["int8_gemm_peak_measured"] = int8_peak
+                prefill["roofline"]["frac_of_measured_int8_gemm"] = prefill["roofline"]["achieved"] / int8_peak["tops"]
+
+    tp_leg = stack_2b = None
     if not args.no_tp:
-        tp_leg = measure_tp(torch, dist, backend, rank, world, codec, codec_name, args, stream)
+        batches = [int(v) for v in args.tp_batches.split(",") if v]
+        if world > 1:
+            # the same decoder unsharded on this rank's GPU: the baseline of the efficiency figures below
+            base = measure_tp(torch, None, backend, 0, 1, codec, codec_name, args, stream, shape_name=args.tp_shape, batches=batches,
+                              m_prefill=args.tp_prefill_m, reduce_variants=False)
+        tp_leg = measure_tp(torch, dist, backend, rank, world, codec, codec_name, args, stream, shape_name=args.tp_shape,
+                            batches=batches, m_prefill=args.tp_prefill_m)
+        if world > 1:
+            eff = {}
+            for key, entry in tp_leg.items():
+                if isinstance(entry, dict) and "tokens_per_s" in entry:
+                    ref = base.get(key if key in base else "decode_m1")
+                    if ref:
+                        eff[key] = entry["tokens_per_s"] / (world * ref["tokens_per_s"])
+            tp_leg["one_gpu_same_run"] = {k2: v for k2, v in base.items() if isinstance(v, dict) and "tokens_per_s" in v}
+            tp_leg["efficiency_vs_one_gpu"] = eff
+        if world == 1 and not args.quick and args.tp_shape == "27b":
+            stack_2b = measure_tp(torch, dist, backend, rank, world, codec, codec_name, args, stream, shape_name="2b", batches=[1, 16, 64])
 
     if rank == 0:
         cpu = None
@@ -419,11 +521,13 @@ def run_b200(args) -> None:
             "metric": METRIC if m == 1 else f"ternary linear HBM GB/s (M={m})", "value": value, "unit": UNIT,
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-            "config": {"workload": f"c2_3plane_k2560_n6912_{codec_name}_m{m}", "layer_copies_per_step": copies,
-                       "l2_policy": f"rotating set of {copies} distinct weight buffers ({bytes_per_step / 1e6:.0f} MB > 126 MB L2)",
-                       "launch": ("cuda graph" if graph is not None else "eager") + (" + programmatic dependent launch" if flags else "")},
+            "config": {"workload": f"c2_3plane_k2560_n6912_{codec_name}_m{m}"},
+            "setup": {"layer_copies_per_step": copies,
+                      "l2_policy": f"rotating set of {copies} distinct weight buffers ({bytes_per_step / 1e6:.0f} MB > 126 MB L2)",
+                      "launch": ("cuda graph" if graph is not None else "eager") + (" + programmatic dependent launch" if flags else "")},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
-                         "traffic": NCU_TRAFFIC_BYTES.get((codec_name, m, copies)), "peak_kind": peak_kind, "kernel": "decode_kernel", "us_per_launch": per_launch_us,
+                         "traffic": NCU_TRAFFIC_BYTES.get((codec_name, m, copies)),
+                         "traffic_source": NCU_TRAFFIC_SOURCE if (codec_name, m, copies) in NCU_TRAFFIC_BYTES else None, "peak_kind": peak_kind, "kernel": "decode_kernel", "us_per_launch": per_launch_us,
                          "algorithmic_bytes_per_launch": bytes_per_step, "layers_per_launch": copies,
                          "algorithmic_bytes_per_layer": layer_bytes},
             "cpu_baseline": cpu,
@@ -431,8 +535,11 @@ def run_b200(args) -> None:
                     "d2h_bytes_per_step": copies * m * N_ROWS * 2, "api": "tb_stack_forward_host (one call per step)"},
             "gpu_launches": args.steps,
             "clocks": clocks.summary(),
+            "single_layer": single,
+            "e2e_per_linear": e2e_linear,
             "prefill": prefill,
             "tp": tp_leg,
+            "stack_2b": stack_2b,
         }
         print(json.dumps(line), flush=True)
     stack.close()
@@ -460,7 +567,8 @@ def main() -> None:
     ap.add_argument("--no-tp", action="store_true", help="skip the tensor-parallel decoder-stack leg")
     ap.add_argument("--tp-prefill-m", type=int, default=4096, help="tokens of the tensor-parallel prefill pass (0 = skip)")
     ap.add_argument("--tp-shape", default="27b", choices=["27b", "2b"], help="decoder whose linears the tensor-parallel leg runs")
-    ap.add_argument("--tp-batches", default="1", help="comma-separated decode batch sizes of the tensor-parallel leg")
+    ap.add_argument("--tp-batches", default="1,32", help="comma-separated decode batch sizes of the tensor-parallel leg")
+    ap.add_argument("--quick", action="store_true", help="headline legs only (no single-layer, per-linear, INT8-peak and 2B-stack legs)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

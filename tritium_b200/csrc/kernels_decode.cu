@@ -51,7 +51,7 @@ constexpr int kConsumerThreads = kWarps * 32;
 constexpr int kMaxStages = 4;
 constexpr int kPartBufs = 4;   // row blocks whose partial sums may wait for the combiner
 constexpr int kMaxGroupLayers = 128;   // layers of one grouped launch (descriptors live in shared memory)
-constexpr uint32_t kStageBytesPerWarp = 256 + 16;   // fused prologue: one quantised tile column + absmax partials
+constexpr uint32_t kBuildStagingBytes = 32 * 272 + 8 * 16;   // fused prologue: quantised activations of one pass of pairs, absmax partials
 
 struct DecodeParams {
   const uint8_t* payload; const uint16_t* scales;   // single layer (layers == nullptr)
@@ -474,20 +474,50 @@ __device__ __forceinline__ void load8(const void* x, uint32_t dtype, size_t idx,
   }
 }
 
+// MMA number that consumes digit pair `pair` of the packed words of `slot` (words 4*slot .. 4*slot+3;
+// slot 3 of B3 is the bytewise MMA on word 12) for scale group `v`, or -1 when that combination holds
+// only zeros (the inverse of slot_of).
+template <int CODEC, bool DUAL> __device__ __forceinline__ int mma_of(uint32_t slot, uint32_t pair, uint32_t v) {
+  if (CODEC == tbf::kB3) {
+    if (DUAL) return slot < 3 ? int(slot * 3 + pair) : 9;
+    if (slot == 0) return v == 0 ? int(pair) : -1;
+    if (slot == 1) return int((v == 0 ? 3 : 6) + pair);
+    if (slot == 2) return v == 1 ? int(9 + pair) : -1;
+    return v == 1 ? 12 : -1;
+  }
+  if (DUAL) return int(slot * 2 + pair);
+  return (slot >> 1) == v ? int(slot * 2 + pair) : -1;
+}
+
+constexpr uint32_t kChunkPairs = 32;    // (tile column, token) pairs quantised per pass of the table builder
+constexpr uint32_t kPairStride = 272;   // staged bytes per pair: 256 codes + zero padding (B3 digits 256..259)
+
+__device__ __forceinline__ int sbyte(uint32_t w, int b) { return int(int8_t(w >> (8 * b))); }
+
 // Builds this CTA's activation tables in shared memory (same contents as prepare_kernel writes to
 // global scratch): per-token absmax int8 quantisation of x, B-fragment entries, accumulator start
 // values, token scales.  Called by the eight consumer warps (tid 0..255).
+//
+// Work item of the entry construction = one packed word position w of one (tile column, token,
+// scale group): the 20 (B3) or 16 (D2) activations that meet the word's digits are five (four)
+// aligned 32-bit words of the staged codes, every one of them inside a single scale group; their
+// transformed values z = x_t - 3 x_(t-1) (B3; x_t for D2), split as 4*high + low, are the table
+// words of that position.  Items are independent, so the whole CTA works on them at once.
 template <int CODEC, bool DUAL, int M>
 __device__ __forceinline__ void build_tables(const DecodeParams& p, uint8_t* smem, uint32_t tid) {
   constexpr int kNM = MmaCount<CODEC, DUAL>::value;
-  constexpr uint32_t ncol = (DUAL ? 4 : 2) * M, kPerMma = DUAL ? 16 : 8;
+  constexpr uint32_t ncol = (DUAL ? 4 : 2) * M;
+  constexpr bool B3 = CODEC == tbf::kB3;
+  constexpr uint32_t kDigits = B3 ? 5 : 4, kWords = B3 ? 13 : 16;   // digits per packed byte, packed words per tile-plane
   const uint32_t warp = tid >> 5, lane = tid & 31;
-  int8_t* xq = reinterpret_cast<int8_t*>(smem + p.off_xq) + warp * kStageBytesPerWarp;
-  float* red = reinterpret_cast<float*>(smem + p.off_xq + 256);   // [warp] at stride kStageBytesPerWarp: four floats
-  uint2* ztab = reinterpret_cast<uint2*>(smem + p.off_z);
+  uint8_t* xq = smem + p.off_xq;                                                             // [kChunkPairs][kPairStride]
+  float* red = reinterpret_cast<float*>(smem + p.off_xq + kChunkPairs * kPairStride);       // [warp][4]
+  uint32_t* ztab = reinterpret_cast<uint32_t*>(smem + p.off_z);
   int* cinit = reinterpret_cast<int*>(smem + p.off_cinit);
   float* act_scale = reinterpret_cast<float*>(smem + p.off_actscale);
+  if (tid < kChunkPairs) *reinterpret_cast<uint4*>(xq + tid * kPairStride + 256) = make_uint4(0, 0, 0, 0);
   float scale_q[M], scale_out[M];
+  const uint32_t pairs = p.tpr * M;
   if (p.x_dtype == TB_I8) {
 #pragma unroll
     for (int t = 0; t < M; ++t) { scale_q[t] = 1.f; scale_out[t] = uint32_t(t) < p.m ? p.act_scale_in[t] : 0.f; }
@@ -503,7 +533,7 @@ __device__ __forceinline__ void build_tables(const DecodeParams& p, uint8_t* sme
           for (int e = 0; e < 8; ++e) mx = fmaxf(mx, fabsf(v[e]));
         }
         for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        if (lane == 0) red[warp * (kStageBytesPerWarp / 4) + t] = mx;
+        if (lane == 0) red[warp * 4 + t] = mx;
       }
       consumer_sync();
     }
@@ -512,55 +542,105 @@ __device__ __forceinline__ void build_tables(const DecodeParams& p, uint8_t* sme
       float gamma = 0.f;
       if (p.act_absmax_in) gamma = uint32_t(t) < p.m ? p.act_absmax_in[t] : 0.f;   // absmax over the full (unsharded) row, supplied by the caller
       else
-        for (uint32_t w2 = 0; w2 < uint32_t(kWarps); ++w2) gamma = fmaxf(gamma, red[w2 * (kStageBytesPerWarp / 4) + t]);
+        for (uint32_t w2 = 0; w2 < uint32_t(kWarps); ++w2) gamma = fmaxf(gamma, red[w2 * 4 + t]);
       scale_q[t] = gamma > 0.f ? __fdiv_rn(127.0f, gamma) : 0.f;
       scale_out[t] = __fdiv_rn(gamma, 127.0f);
     }
   }
-  for (uint32_t pr = warp; pr < p.tpr * M; pr += kWarps) {
-    const uint32_t j = pr / M, t = pr - j * M;
-    if (t >= p.m) continue;   // table entries of absent tokens are never read for an output
-    float v[8];
-    load8(p.x, p.x_dtype, size_t(t) * p.k + j * 256 + lane * 8, v);
-    float sq = scale_q[0];
+  for (uint32_t base = 0; base < pairs; base += kChunkPairs) {
+    const uint32_t chunk = min(kChunkPairs, pairs - base);
+    // ---- quantise: a warp takes whole pairs (lane = eight consecutive activations), and adds up
+    // the accumulator start values of the pair's two scale groups on the way
 #pragma unroll
-    for (int tt = 1; tt < M; ++tt) sq = t == uint32_t(tt) ? scale_q[tt] : sq;
-    int q[8];
-    bool bad = false;
+    for (uint32_t r = 0; r < kChunkPairs / kWarps; ++r) {
+      const uint32_t lp = warp + r * kWarps;
+      if (lp >= chunk) continue;
+      const uint32_t pr = base + lp, j = pr / M, t = pr - j * M;
+      if (t >= p.m) continue;   // table entries of absent tokens are never read for an output
+      float v[8];
+      load8(p.x, p.x_dtype, size_t(t) * p.k + j * 256 + lane * 8, v);
+      float sq = scale_q[0];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      bad |= !(fabsf(v[e]) <= FLT_MAX);
-      q[e] = p.x_dtype == TB_I8 ? int(v[e]) : int(fminf(127.f, fmaxf(-128.f, rintf(__fmul_rn(v[e], sq)))));
-    }
-    if (bad && atomicOr(&p.status[TBS_FLAGS], TBF_NONFINITE_ACT) == 0) {
-      p.status[TBS_INFO0] = t * p.k + j * 256 + lane * 8; p.status[TBS_INFO1] = 0x7fc00000u;
-    }
-    uint2 packed;
-    packed.x = uint32_t(q[0] & 0xff) | (uint32_t(q[1] & 0xff) << 8) | (uint32_t(q[2] & 0xff) << 16) | (uint32_t(q[3] & 0xff) << 24);
-    packed.y = uint32_t(q[4] & 0xff) | (uint32_t(q[5] & 0xff) << 8) | (uint32_t(q[6] & 0xff) << 16) | (uint32_t(q[7] & 0xff) << 24);
-    reinterpret_cast<uint2*>(xq)[lane] = packed;
-    __syncwarp();
-    // entries of this (tile column, token): mma x [scale group] x {high, low part} x lane column
-    for (uint32_t idx = lane; idx < kNM * kPerMma; idx += 32) {
-      const uint32_t c = idx & 3, hl = (idx >> 2) & 1, v2 = DUAL ? (idx >> 3) & 1 : 0, mma = idx / kPerMma;
-      const Slot<CODEC> s = slot_of<CODEC, DUAL>(int(mma), int(c));
-      const int variant = DUAL ? int(v2) : s.variant;
-      const uint32_t col = v2 * 2 * M + 2 * t + hl;
-      ztab[((size_t(j) * kNM + mma) * ncol + col) * 4 + c] =
-          s.bytewise ? z_bytewise<CODEC>(xq, s, int(c), int(hl), variant)
-                     : make_uint2(z_quad<CODEC>(xq, s, s.d0, int(hl), variant), z_quad<CODEC>(xq, s, s.d1, int(hl), variant));
-    }
-    // accumulator start values (see prepare_kernel): lanes 0..15 hold scale group 0, 16..31 group 1
-    int sum = 0;
+      for (int tt = 1; tt < M; ++tt) sq = t == uint32_t(tt) ? scale_q[tt] : sq;
+      int q[8];
+      bool bad = false;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      int coef = 1;
-      if (CODEC == tbf::kB3) { const int d = int(lane * 8 + e) % 5; coef = d == 0 ? 1 : d == 1 ? -2 : d == 4 ? 2 : -1; }
-      sum += q[e] * coef;
+      for (int e = 0; e < 8; ++e) {
+        bad |= !(fabsf(v[e]) <= FLT_MAX);
+        q[e] = p.x_dtype == TB_I8 ? int(v[e]) : int(fminf(127.f, fmaxf(-128.f, rintf(__fmul_rn(v[e], sq)))));
+      }
+      if (bad && atomicOr(&p.status[TBS_FLAGS], TBF_NONFINITE_ACT) == 0) {
+        p.status[TBS_INFO0] = t * p.k + j * 256 + lane * 8; p.status[TBS_INFO1] = 0x7fc00000u;
+      }
+      uint2 packed;
+      packed.x = uint32_t(q[0] & 0xff) | (uint32_t(q[1] & 0xff) << 8) | (uint32_t(q[2] & 0xff) << 16) | (uint32_t(q[3] & 0xff) << 24);
+      packed.y = uint32_t(q[4] & 0xff) | (uint32_t(q[5] & 0xff) << 8) | (uint32_t(q[6] & 0xff) << 16) | (uint32_t(q[7] & 0xff) << 24);
+      reinterpret_cast<uint2*>(xq + lp * kPairStride)[lane] = packed;
+      // accumulator start values (see prepare_kernel): lanes 0..15 hold scale group 0, 16..31 group 1
+      int sum = 0;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        int coef = 1;
+        if (B3) { const int d = int(lane * 8 + e) % 5; coef = d == 0 ? 1 : d == 1 ? -2 : d == 4 ? 2 : -1; }
+        sum += q[e] * coef;
+      }
+      for (int o = 8; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      if ((lane & 15) == 0) cinit[(t * p.tpr + j) * 2 + (lane >> 4)] = -sum;
     }
-    for (int o = 8; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    if ((lane & 15) == 0) cinit[(t * p.tpr + j) * 2 + (lane >> 4)] = -sum;
-    __syncwarp();
+    consumer_sync();
+    // ---- entries: item = (pair of the chunk, scale group, packed word position)
+    for (uint32_t item = tid; item < chunk * 2 * kWords; item += kConsumerThreads) {
+      const uint32_t lp = item / (2 * kWords), rem = item - lp * (2 * kWords), v = rem / kWords, w = rem - v * kWords;
+      const uint32_t pr = base + lp, j = pr / M, t = pr - j * M;
+      if (t >= p.m) continue;
+      const uint32_t slot = w >> 2, c = w & 3;
+      const bool bytewise = B3 && slot == 3;
+      if (!DUAL && mma_of<CODEC, false>(slot, 0, v) < 0) continue;   // no MMA reads this word for this scale group
+      // the activations that meet the digits of packed word w: words of four, each inside one scale group
+      const uint32_t t0 = 4 * kDigits * w;
+      const uint32_t* src = reinterpret_cast<const uint32_t*>(xq + lp * kPairStride + t0);
+      int a[4 * 5];
+#pragma unroll
+      for (uint32_t kw = 0; kw < kDigits; ++kw) {
+        const uint32_t word = (((t0 + 4 * kw) >> 7) == v) ? src[kw] : 0u;   // trits 256..259 read the zero padding
+#pragma unroll
+        for (int b = 0; b < 4; ++b) a[4 * kw + b] = sbyte(word, b);
+      }
+      // z of (byte e, digit i) and its parts
+      uint32_t hi[5][4], lo[5][4];   // [digit][byte]
+#pragma unroll
+      for (uint32_t e = 0; e < 4; ++e) {
+#pragma unroll
+        for (uint32_t i = 0; i < kDigits; ++i) {
+          const int cur = a[kDigits * e + i];
+          const int z = (B3 && i > 0) ? cur - 3 * a[kDigits * e + i - 1] : cur;
+          hi[i][e] = uint32_t(z >> 2) & 0xffu;
+          lo[i][e] = uint32_t(z) & 3u;
+        }
+      }
+      const uint32_t col0 = (DUAL ? v * 2 * M : 0) + 2 * t;
+      if (bytewise) {
+        // byte e of word 12 belongs to lane column e: operand quad 0 = digits 0..3, quad 1 byte 0 = digit 4
+        const uint32_t mma = uint32_t(mma_of<CODEC, DUAL>(3, 0, v));
+#pragma unroll
+        for (uint32_t e = 0; e < 4; ++e) {
+          uint32_t* at = ztab + (((j * kNM + mma) * ncol + col0) * 4 + e) * 2;
+          at[0] = hi[0][e] | (hi[1][e] << 8) | (hi[2][e] << 16) | (hi[3][e] << 24); at[1] = hi[4][e];
+          at[8] = lo[0][e] | (lo[1][e] << 8) | (lo[2][e] << 16) | (lo[3][e] << 24); at[9] = lo[4][e];
+        }
+      } else {
+#pragma unroll
+        for (uint32_t i = 0; i < kDigits; ++i) {
+          // digit i: MMA of (slot, digit pair i/2), operand quad i%2; bytes e = 0..3
+          const uint32_t mma = uint32_t(mma_of<CODEC, DUAL>(slot, i >> 1, v));
+          uint32_t* at = ztab + (((j * kNM + mma) * ncol + col0) * 4 + c) * 2 + (i & 1);
+          at[0] = hi[i][0] | (hi[i][1] << 8) | (hi[i][2] << 16) | (hi[i][3] << 24);
+          at[8] = lo[i][0] | (lo[i][1] << 8) | (lo[i][2] << 16) | (lo[i][3] << 24);   // low part: the next column
+          if (B3 && i == 4) { at[1] = 0u; at[9] = 0u; }                                 // the fifth digit has no partner
+        }
+      }
+    }
+    consumer_sync();
   }
   if (tid < uint32_t(M)) {
     float so = scale_out[0];
@@ -620,32 +700,31 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
   if (warp == kWarps) {
     // ------------------------------------------------ producer: weights do not depend on the
     // previous kernel, so the stream starts before griddepcontrol.wait.
-    if (lane == 0) {
-      uint32_t fills[kMaxStages] = {0, 0, 0, 0};
-      uint32_t s = 0, round = 0;
-      uint32_t layer = blockIdx.x / p.blocks, blk = blockIdx.x - layer * p.blocks;
-      for (uint32_t it = 0; it < my_blocks; ++it) {
-        if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1, &abort_flag)) {
-          abort_flag = 1;
-          if (atomicOr(&p.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) { p.status[TBS_INFO0] = it; p.status[TBS_INFO1] = 100 + s; }
-          break;
-        }
-        const uint8_t* pay = layer_desc[layer].payload;
-        const uint8_t* scs = reinterpret_cast<const uint8_t*>(layer_desc[layer].scales);
-        mbar_expect_tx(&full_bar[s], p.stage_bytes + p.scale_stage_bytes);
-        bulk_g2s(ring + size_t(s) * p.stage_bytes, pay + size_t(blk) * p.stage_bytes, p.stage_bytes, &full_bar[s]);
-        bulk_g2s(scale_ring + size_t(s) * p.scale_stage_bytes, scs + size_t(blk) * p.scale_stage_bytes,
-                 p.scale_stage_bytes, &full_bar[s]);
-        ++fills[s];
-        if (++s == p.stages) { s = 0; ++round; }
-        for (blk += gridDim.x; blk >= p.blocks; blk -= p.blocks) ++layer;
+    if (lane != 0) return;
+    uint32_t fills[kMaxStages] = {0, 0, 0, 0};
+    uint32_t s = 0, round = 0;
+    uint32_t layer = blockIdx.x / p.blocks, blk = blockIdx.x - layer * p.blocks;
+    for (uint32_t it = 0; it < my_blocks; ++it) {
+      if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1, &abort_flag)) {
+        abort_flag = 1;
+        if (atomicOr(&p.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) { p.status[TBS_INFO0] = it; p.status[TBS_INFO1] = 100 + s; }
+        break;
       }
-      // Do not leave the CTA while a copy may still be landing in its shared memory: wait
-      // (bounded) for the latest fill of every slot.  In the normal path these have all
-      // completed already, because the consumers waited on them.
-      for (uint32_t sl = 0; sl < p.stages; ++sl)
-        if (fills[sl]) mbar_wait(&full_bar[sl], (fills[sl] - 1) & 1, nullptr, kDrainLimitCycles);
+      const uint8_t* pay = layer_desc[layer].payload;
+      const uint8_t* scs = reinterpret_cast<const uint8_t*>(layer_desc[layer].scales);
+      mbar_expect_tx(&full_bar[s], p.stage_bytes + p.scale_stage_bytes);
+      bulk_g2s(ring + size_t(s) * p.stage_bytes, pay + size_t(blk) * p.stage_bytes, p.stage_bytes, &full_bar[s]);
+      bulk_g2s(scale_ring + size_t(s) * p.scale_stage_bytes, scs + size_t(blk) * p.scale_stage_bytes,
+               p.scale_stage_bytes, &full_bar[s]);
+      ++fills[s];
+      if (++s == p.stages) { s = 0; ++round; }
+      for (blk += gridDim.x; blk >= p.blocks; blk -= p.blocks) ++layer;
     }
+    // Do not leave the CTA while a copy may still be landing in its shared memory: wait
+    // (bounded) for the latest fill of every slot.  In the normal path these have all
+    // completed already, because the consumers waited on them.
+    for (uint32_t sl = 0; sl < p.stages; ++sl)
+      if (fills[sl]) mbar_wait(&full_bar[sl], (fills[sl] - 1) & 1, nullptr, kDrainLimitCycles);
     return;
   }
 
@@ -945,7 +1024,7 @@ size_t layout(const tb_weights* w, uint32_t m, int max_smem, DecodeParams* p) {
   const uint32_t mk = layout_tokens(m), cells = use_dual(mk) ? 2 * mk : mk;
   // a consumer warp's partial sums per row block: one per row-plane (three planes: one per row)
   const uint32_t part = kPartBufs * cw * pl.rows_per_stage * (planes == 3 ? 1 : planes) * cells * 4;
-  const uint32_t xq = cw * kStageBytesPerWarp;   // fused prologue staging
+  const uint32_t xq = kBuildStagingBytes;   // fused prologue staging
   const uint32_t fixed = tl.total + part + xq;
   const uint32_t per_stage = pl.stage_bytes + pl.scale_stage_bytes;
   if (fixed + 2 * per_stage > uint32_t(max_smem)) return 0;
@@ -1009,6 +1088,13 @@ bool tb_decode_supported(const tb_weights* w, uint32_t m, int max_smem, size_t* 
 
 size_t tb_decode_scratch_bytes(const tb_weights* w, uint32_t m) { return table_layout(w, m).total; }
 
+bool tb_decode_builds_tables(const tb_weights* w, uint32_t m, const void* x) {
+  // (tile column, token) pairs every CTA would have to quantise and lay out; measured on B200: up
+  // to about a dozen pairs the single launch wins, beyond that the separate kernel
+  const uint32_t pairs = uint32_t(w->k / 256) * layout_tokens(m);
+  return pairs <= 12 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
+}
+
 cudaError_t tb_launch_prepare(const DecodeArgs& a, cudaStream_t stream) {
   const tb_weights* w = a.w;
   const TableLayout tl = table_layout(w, a.m);
@@ -1039,11 +1125,6 @@ cudaError_t tb_launch_prepare(const DecodeArgs& a, cudaStream_t stream) {
 }
 
 using DecodeKernel = void (*)(const DecodeParams);
-#ifdef TB_DECODE_MINIMAL
-template <int CODEC> DecodeKernel pick_planes(uint32_t planes, uint32_t sets, uint32_t mk) {
-  return (CODEC == tbf::kB3 && planes == 3 && sets == 3 && mk == 1) ? decode_kernel<tbf::kB3, 3, 1, 3> : nullptr;
-}
-#else
 template <int CODEC, int PLANES, int SETS> DecodeKernel pick_tokens(uint32_t mk) {
   return mk == 1 ? decode_kernel<CODEC, PLANES, 1, SETS> : mk == 2 ? decode_kernel<CODEC, PLANES, 2, SETS> : decode_kernel<CODEC, PLANES, 4, SETS>;
 }
@@ -1053,7 +1134,6 @@ template <int CODEC, int PLANES> DecodeKernel pick_sets(uint32_t sets, uint32_t 
 template <int CODEC> DecodeKernel pick_planes(uint32_t planes, uint32_t sets, uint32_t mk) {
   return planes == 1 ? pick_sets<CODEC, 1>(sets, mk) : planes == 2 ? pick_sets<CODEC, 2>(sets, mk) : pick_tokens<CODEC, 3, 3>(mk);
 }
-#endif
 
 cudaError_t tb_launch_decode(const DecodeArgs& a, int sm_count, int max_smem, cudaStream_t stream) {
   const tb_weights* w = a.w;
@@ -1069,9 +1149,13 @@ cudaError_t tb_launch_decode(const DecodeArgs& a, int sm_count, int max_smem, cu
   } else if (!a.scratch || a.scratch_bytes < tl.total) {
     return cudaErrorInvalidValue;
   }
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  unsigned num_attrs = 0;
+  if (a.pdl) {
+    attr[num_attrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[num_attrs].val.programmaticStreamSerializationAllowed = 1;
+    ++num_attrs;
+  }
   p.payload = w->d_payload; p.scales = w->d_scales;
   p.layers = a.layers; p.layer_count = a.layers ? a.layer_count : 1; p.y_layer_stride = a.y_layer_stride;
   p.tables = static_cast<const uint8_t*>(a.scratch);
@@ -1097,12 +1181,13 @@ cudaError_t tb_launch_decode(const DecodeArgs& a, int sm_count, int max_smem, cu
   // served by two CTAs per SM of its own.
   const bool wide = a.layers != nullptr || p.blocks >= 2u * uint32_t(sm_count);
   const uint32_t resident = uint32_t(sm_count) * (wide ? p.ctas_per_sm : 1u);
-  cfg.gridDim = dim3(std::min<uint32_t>(p.blocks * p.layer_count, resident));
+  uint32_t grid = std::min<uint32_t>(p.blocks * p.layer_count, resident);
+  cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cfg.attrs = attr;
-  cfg.numAttrs = a.pdl ? 1 : 0;
+  cfg.numAttrs = num_attrs;
   return cudaLaunchKernelEx(&cfg, kernel, p);
 }
 

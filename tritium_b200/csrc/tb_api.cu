@@ -313,12 +313,12 @@ tb_status forward_dev(tb_backend* b, const tb_weights* w, const tb_forward_args&
   }
   if (a.flags & TB_FWD_FORCE_PREFILL) return tb_fail(TB_UNSUPPORTED_FORMAT, "the prefill kernel does not take this shape");
   uint32_t launches = 0;
-  // One launch per pass of up to four tokens: the kernel quantises the activations and builds its
-  // tables itself.  Activations that are not 16-byte aligned go through the separate
-  // preparation kernel and the backend's scratch instead.
-  const bool fused = (reinterpret_cast<uintptr_t>(a.x) & 15u) == 0;
+  // One pass per four tokens.  Small activation tables are built inside the decode kernel (one
+  // launch); large ones, and activations that are not 16-byte aligned, by the separate preparation
+  // kernel into the backend's scratch (see tb_decode_builds_tables).
   for (uint32_t m0 = 0; m0 < a.m; m0 += 4) {
     const uint32_t mc = std::min<uint32_t>(4, a.m - m0);
+    const bool fused = tb_decode_builds_tables(w, mc, a.x);
     if (!tb_decode_supported(w, mc, b->max_smem_optin, nullptr))
       return tb_fail(TB_UNSUPPORTED_FORMAT, "the decode kernel's shared-memory plan does not fit this shape");
     DecodeArgs d{};
@@ -677,7 +677,6 @@ extern "C" tb_status tb_stack_forward_dev(tb_stack* st, const void* x, tb_dtype 
   const size_t n_layers = st->layers.size();
   if (y_last && st->group_of[n_layers - 1] >= 0)
     return tb_fail(TB_INVALID_INPUT, "the last layer belongs to a grouped run: its output is read with tb_stack_read_output, y_last must be NULL");
-  const bool x_aligned = (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
   for (size_t i = 0; i < n_layers; ++i) {
     const int gi = st->group_of[i];
     if (gi >= 0) {
@@ -704,7 +703,7 @@ extern "C" tb_status tb_stack_forward_dev(tb_stack* st, const void* x, tb_dtype 
           d.x = static_cast<const uint8_t*>(x) + size_t(m0) * w->k * dtype_size(xd);
           d.y = static_cast<uint8_t*>(g.y) + size_t(m0) * w->n * 2;
           d.status = b->d_status; d.pdl = (flags & TB_FWD_PDL) != 0 || m0 > 0;
-          d.fused = x_aligned;
+          d.fused = tb_decode_builds_tables(w, mc, d.x);
           d.scratch = b->d_prep; d.scratch_bytes = b->d_prep_cap;
           d.layers = g.d_descs; d.layer_count = uint32_t(g.count); d.y_layer_stride = uint32_t(size_t(m) * w->n);
           if (!tb_decode_supported(w, mc, b->max_smem_optin, nullptr))

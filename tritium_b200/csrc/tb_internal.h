@@ -126,6 +126,10 @@ struct DecodeArgs {
   uint32_t inject_missing_tx;   // test hook (non-fused launches): the table barrier expects this many bytes too many
 };
 cudaError_t tb_launch_prepare(const DecodeArgs& a, cudaStream_t stream);
+// Whether a decode launch of `m` tokens should build its activation tables itself (one launch)
+// rather than read them from scratch that tb_launch_prepare filled.  Every CTA repeats the
+// construction, so this pays only for small tables; x must be 16-byte aligned.
+bool tb_decode_builds_tables(const tb_weights* w, uint32_t m, const void* x);
 size_t tb_decode_scratch_bytes(const tb_weights* w, uint32_t m);
 // Returns false (and leaves *err untouched) when the layout/shape does not fit the kernel.
 bool tb_decode_supported(const tb_weights* w, uint32_t m, int max_smem, size_t* smem_bytes);
