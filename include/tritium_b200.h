@@ -79,6 +79,11 @@ typedef struct tb_weights_info {
 /* ------------------------------------------------------------------ library */
 uint32_t tb_abi_version(void);
 const char* tb_last_error(void);
+/* The two lengths of the calling thread's last failure when it was a TB_SHAPE_MISMATCH that knows
+ * them (BackendError::ShapeMismatch { expected, got }, crates/tritium-spec/src/lib.rs:384-391;
+ * callers such as crates/tritium-nn/src/layers/projection.rs:207-209 match on the variant).
+ * Returns TB_INVALID_INPUT when the last failure carries no lengths. */
+tb_status tb_last_shape_mismatch(uint64_t* expected, uint64_t* got);
 
 /* ------------------------------------------------------------------ backend
  * Replaces CudaBackend::new / the BackendEntry init function
@@ -107,6 +112,16 @@ tb_status tb_salt_v2_upload(tb_backend* backend, tb_codec codec, uint32_t group,
  * whole package bytes plus a tensor name. */
 tb_status tb_salt_v2_upload_package(tb_backend* backend, const uint8_t* package, size_t len,
                                     const char* tensor_name, tb_weights** out);
+/* The same from a byte source that is read at arbitrary offsets (a seekable file), so that a
+ * multi-gigabyte package is never held in memory: SaltV2PackageReader::new_strict / tensor_info /
+ * visit_packed_tensor (crates/tritium-format/src/salt_v2_package/reader.rs:333,790,841) as used by
+ * upload_salt_v2_from_reader (crates/tritium-cuda/src/cuda/backend/salt_v2_reader_upload.rs:32).  The
+ * header table is walked with small reads; only the named tensor's payload, scales and its slice of
+ * the presence map are fetched.  `read_at` copies `len` bytes at `offset` into `dst` and returns 0,
+ * or non-zero on failure (reported as TB_INVALID_INPUT).  `package_len` is the source's length. */
+typedef int (*tb_read_at_fn)(void* user, uint64_t offset, void* dst, size_t len);
+tb_status tb_salt_v2_upload_reader(tb_backend* backend, tb_read_at_fn read_at, void* user, uint64_t package_len,
+                                   const char* tensor_name, tb_weights** out);
 tb_status tb_weights_info_get(const tb_weights* weights, tb_weights_info* out);
 void tb_weights_free(tb_weights* weights);
 
@@ -294,6 +309,21 @@ tb_status tb_fmt_resident_build(tb_codec codec, uint32_t group, uint64_t n, uint
 int64_t tb_fmt_package_write(tb_codec codec, const char* name, uint32_t group, uint64_t n,
                              uint64_t k, const uint8_t* plane_count, const int8_t* trits,
                              const uint16_t* scales, uint8_t* out, size_t cap);
+/* write_salt_v2_package for several matrix tensors in the given order (salt_v2_package.rs:1526-1668):
+ * one presence map over the full tiles of all tensors behind the last one, its trailing bits in the
+ * tensor-count word, version 2 as soon as one tensor uses 64-wide scale groups.  Arrays hold `count`
+ * entries; trits / scales / plane_count are laid out per tensor as for tb_fmt_resident_build. */
+int64_t tb_fmt_package_write_multi(tb_codec codec, uint32_t count, const char* const* names, const uint32_t* groups,
+                                   const uint64_t* n, const uint64_t* k, const uint8_t* const* plane_count,
+                                   const int8_t* const* trits, const uint16_t* const* scales, uint8_t* out, size_t cap);
+/* Host-only twin of tb_salt_v2_upload_reader: fetches the resident arenas of one tensor from a byte
+ * source.  Call with NULL buffers to learn the sizes, then with buffers of those sizes. */
+typedef struct tb_package_tensor {
+  uint32_t codec, group, terminal_map_value, planes_uniform;
+  uint64_t n, k, payload_bytes, scale_count, map_bytes;
+} tb_package_tensor;
+tb_status tb_fmt_package_extract(tb_read_at_fn read_at, void* user, uint64_t package_len, const char* tensor_name,
+                                 tb_package_tensor* info, uint8_t* payload, uint16_t* scales, uint8_t* plane_map);
 /* pack_tq2_0_row (crates/tritium-format/src/rows.rs:61-77) with unit block scales. */
 tb_status tb_fmt_tq2_pack_rows(const int8_t* trits, uint64_t n, uint64_t k, uint8_t* out);
 /* quantize_act_int8 (crates/tritium-spec/src/lib.rs:351-378), host. */

@@ -183,3 +183,27 @@ def test_bounded_wait_runs_out_and_the_context_stays_usable(backend):
     static_call()                       # the hook disarmed itself
     backend.check(stream)
     assert rel_l2(y_dev.cpu().numpy(), orc.a8_linear(orac, x, dump=False)[0]) <= 1e-5
+
+
+# ------------------------------------------------------------------ package file -> device through seeks
+def test_upload_from_seekable_package_file(backend, tmp_path):
+    """upload_salt_v2_from_reader: a multi-tensor package on disk, one tensor uploaded through seeks,
+    forward bit-identical to the upload from arenas."""
+    from tritium_b200 import format as fmt
+    a, oa = uniform_pair(48, 512, 2, seed=61)
+    b2, ob = uniform_pair(32, 768, 3, seed=62)
+    a.name, b2.name = "blk.0.attn_q", "blk.0.ffn_up"
+    path = tmp_path / "two.tslt2"
+    path.write_bytes(fmt.write_salt_v2_package_multi([a, b2], SaltV2Codec.B3))
+    x = make_activations(2, 768, seed=6)
+    with open(path, "rb") as f:
+        streamed = backend.upload_salt_v2_from_reader(f, "blk.0.ffn_up")
+    want = np.stack([orc.matvec(ob, x[i]) for i in range(2)])
+    got = backend.salt_v2_forward_exact(streamed, x, 2).output
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    y, acc, _ = backend.linear_forward_a8(streamed, x, 2, dump=True)
+    want_y, want_acc, _ = orc.a8_linear(ob, x)
+    assert np.array_equal(acc, want_acc) and rel_l2(y, want_y) <= 1e-5
+    with open(path, "rb") as f:
+        with pytest.raises(errors.InvalidInput):
+            backend.upload_salt_v2_from_reader(f, "blk.9.none")

@@ -107,6 +107,52 @@ def test_resident_arenas_and_package_bytes_match_oracle(codec, ocodec, shape):
     assert fmt.write_salt_v2_package(prod, codec) == orc.package_write(ocodec, [("w", orac)])
 
 
+@pytest.mark.parametrize("codec,ocodec", CODECS)
+def test_multi_tensor_package_and_seek_reader(codec, ocodec, tmp_path):
+    """Several tensors in one package (ragged last tiles, 64- and 128-wide groups, map bits that end in
+    the tensor-count word): the writer's bytes equal the oracle's; the seek-backed reader returns, for
+    every tensor, the arenas the oracle builds, and touches only the header table and that tensor."""
+    s34 = codec == SaltV2Codec.S34
+    specs = [("blk.0.q", 3, 173, [1, 3, 2], 128), ("blk.0.k", 4, 576, [1, 2, 3, 1, 2, 3, 1, 2, 3], 64),
+             ("blk.1.ffn", 2, 640, [3, 1, 2, 2, 1], 128), ("tiny", 1, 1, [1], 128)]
+    pairs = [ragged_pair(r, c, counts, group, s34=s34, seed=10 + i) for i, (_, r, c, counts, group) in enumerate(specs)]
+    prods = []
+    for (name, *_), (prod, _) in zip(specs, pairs):
+        prod.name = name
+        prods.append(prod)
+    package = fmt.write_salt_v2_package_multi(prods, codec)
+    assert package == orc.package_write(ocodec, [(name, orac) for (name, *_), (_, orac) in zip(specs, pairs)])
+    path = tmp_path / "model.tslt2"
+    path.write_bytes(package)
+
+    class Counting:
+        def __init__(self, f): self.f, self.bytes_read = f, 0
+        def seek(self, *a): return self.f.seek(*a)
+        def tell(self): return self.f.tell()
+        def read(self, n):
+            self.bytes_read += n
+            return self.f.read(n)
+
+    for (name, rows, cols, counts, group), (_, orac) in zip(specs, pairs):
+        with open(path, "rb") as f:
+            src = Counting(f)
+            info, payload, scales, pmap = fmt.package_extract(src, name)
+        o_payload, o_scales, o_meta, o_terminal, plan = orc.resident_build(orac, ocodec)
+        assert (info["n"], info["k"], info["group"]) == (rows, cols, group)
+        assert payload.tobytes() == o_payload.tobytes() and scales.tobytes() == o_scales.tobytes()
+        assert pmap.tobytes() == o_meta[: plan["map_bytes"]].tobytes() and info["terminal_map_value"] == o_terminal
+        # two passes (sizes, then data): each reads the header table and this tensor's sections only
+        others = sum(len(orc.resident_build(o, ocodec)[0]) for (n2, *_), (_, o) in zip(specs, pairs) if n2 != name)
+        assert src.bytes_read < 2 * (len(package) - others) + 64
+    with open(path, "rb") as f:
+        with pytest.raises(errors.InvalidInput, match="no tensor named"):
+            fmt.package_extract(f, "absent")
+    (tmp_path / "short.tslt2").write_bytes(package[:-8])
+    with open(tmp_path / "short.tslt2", "rb") as f:
+        with pytest.raises(errors.InvalidInput):
+            fmt.package_extract(f, "tiny")
+
+
 def test_semantic_validation_matches_reference_rules():
     prod, _ = ragged_pair(1, 256, [1])
     for bits in (0x7C00, 0x7E00, 0xBC00, 0x8000):

@@ -28,6 +28,7 @@ EXPORTS = [
     "tb_tp_shard_sizes", "tb_tp_shard", "tb_fmt_pack", "tb_fmt_unpack", "tb_fmt_plane_bytes",
     "tb_fmt_resident_sizes", "tb_fmt_resident_build", "tb_fmt_package_write", "tb_fmt_tq2_pack_rows",
     "tb_fmt_quantize_act_int8", "tb_linear_forward_a8_static", "tb_backend_inject_wait_timeout",
+    "tb_salt_v2_upload_reader", "tb_fmt_package_write_multi", "tb_fmt_package_extract", "tb_last_shape_mismatch",
 ]
 
 
@@ -58,6 +59,30 @@ class ForwardArgs(C.Structure):
                 ("row_scale", C.c_void_p), ("flags", C.c_uint32), ("stream", C.c_void_p)]
 
 
+READ_AT_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_uint64, C.c_void_p, C.c_size_t)
+
+
+class PackageTensor(C.Structure):
+    _fields_ = [("codec", C.c_uint32), ("group", C.c_uint32), ("terminal_map_value", C.c_uint32), ("planes_uniform", C.c_uint32),
+                ("n", C.c_uint64), ("k", C.c_uint64), ("payload_bytes", C.c_uint64), ("scale_count", C.c_uint64),
+                ("map_bytes", C.c_uint64)]
+
+
+def file_read_at(fileobj):
+    """A tb_read_at_fn over a seekable binary file object; keep the returned object alive while it is in use."""
+    def read_at(_user, offset, dst, length):
+        try:
+            fileobj.seek(offset)
+            data = fileobj.read(length)
+            if len(data) != length:
+                return 1
+            C.memmove(dst, data, length)
+            return 0
+        except Exception:
+            return 2
+    return READ_AT_FN(read_at)
+
+
 class ShardSizes(C.Structure):
     _fields_ = [("n", C.c_uint32), ("k", C.c_uint32), ("payload_bytes", C.c_uint64),
                 ("scale_count", C.c_uint64), ("map_bytes", C.c_uint64)]
@@ -78,6 +103,7 @@ _ST = C.c_int
 _SIGNATURES = {
     "tb_abi_version": (C.c_uint32, []),
     "tb_last_error": (C.c_char_p, []),
+    "tb_last_shape_mismatch": (_ST, [_P, _P]),
     "tb_backend_create": (_ST, [_I, _P]),
     "tb_backend_free": (None, [_P]),
     "tb_backend_caps": (_ST, [_P, _P]),
@@ -121,6 +147,9 @@ _SIGNATURES = {
     "tb_fmt_resident_build": (_ST, [_I, _U32, _U64, _U64, _P, _P, _P, _P, _P, _P, _P]),
     "tb_fmt_package_write": (C.c_int64, [_I, C.c_char_p, _U32, _U64, _U64, _P, _P, _P, _P, _SZ]),
     "tb_fmt_tq2_pack_rows": (_ST, [_P, _U64, _U64, _P]),
+    "tb_salt_v2_upload_reader": (_ST, [_P, _P, _P, _U64, C.c_char_p, _P]),
+    "tb_fmt_package_write_multi": (C.c_int64, [_I, _U32, _P, _P, _P, _P, _P, _P, _P, _P, _SZ]),
+    "tb_fmt_package_extract": (_ST, [_P, _P, _U64, C.c_char_p, _P, _P, _P, _P]),
     "tb_fmt_quantize_act_int8": (None, [_P, _U64, _U64, _P, _P]),
 }
 

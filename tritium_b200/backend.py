@@ -222,6 +222,16 @@ class B200Backend:
         check(self._L.tb_salt_v2_upload_package(self._h, _ptr(buf), C.c_size_t(buf.size), name.encode(), C.byref(h)))
         return SaltV2ResidentTensor(self, h.value)
 
+    def upload_salt_v2_from_reader(self, fileobj, name: str) -> SaltV2ResidentTensor:
+        """upload_salt_v2_from_reader (crates/tritium-cuda/src/cuda/backend/salt_v2_reader_upload.rs:32): the
+        package is a seekable binary file object; only the header table and the named tensor's sections are read."""
+        fileobj.seek(0, 2)
+        length = fileobj.tell()
+        cb = _lib.file_read_at(fileobj)
+        h = C.c_void_p(None)
+        check(self._L.tb_salt_v2_upload_reader(self._h, cb, None, C.c_uint64(length), name.encode(), C.byref(h)))
+        return SaltV2ResidentTensor(self, h.value)
+
     def _receipt(self, r: _lib.Receipt, mode: str) -> SaltV2ForwardReceipt:
         out = SaltV2ForwardReceipt(**{k: int(getattr(r, k)) for k, _ in _lib.Receipt._fields_})
         out.mode = mode

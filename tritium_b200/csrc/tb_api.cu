@@ -13,10 +13,18 @@
 namespace {
 thread_local std::string g_last_error;
 thread_local bool g_has_error = false;
+thread_local bool g_has_shape = false;          // the last error carries the two lengths of a shape mismatch
+thread_local uint64_t g_shape_expected = 0, g_shape_got = 0;
 }  // namespace
 
-void tb_set_error(const std::string& message) { g_last_error = message; g_has_error = true; }
-void tb_clear_error() { g_has_error = false; }
+void tb_set_error(const std::string& message) { g_last_error = message; g_has_error = true; g_has_shape = false; }
+void tb_clear_error() { g_has_error = false; g_has_shape = false; }
+// BackendError::ShapeMismatch { expected, got } (crates/tritium-spec/src/lib.rs:384-391)
+static tb_status fail_shape(uint64_t expected, uint64_t got) {
+  tb_set_error("shape mismatch: expected " + std::to_string(expected) + ", got " + std::to_string(got));
+  g_has_shape = true; g_shape_expected = expected; g_shape_got = got;
+  return TB_SHAPE_MISMATCH;
+}
 static void clear_error() { tb_clear_error(); }
 tb_status tb_fail(tb_status code, const std::string& message) { tb_set_error(message); return code; }
 tb_status tb_cuda_fail(cudaError_t err, const char* what) {
@@ -35,6 +43,12 @@ static tb_status from_fmt(const tbf::Err& e) {
 
 extern "C" uint32_t tb_abi_version(void) { return TB_ABI_VERSION; }
 extern "C" const char* tb_last_error(void) { return g_has_error ? g_last_error.c_str() : nullptr; }
+extern "C" tb_status tb_last_shape_mismatch(uint64_t* expected, uint64_t* got) {
+  if (!expected || !got) return TB_NULL_ARG;
+  if (!g_has_error || !g_has_shape) return TB_INVALID_INPUT;
+  *expected = g_shape_expected; *got = g_shape_got;
+  return TB_OK;
+}
 
 // ---------------------------------------------------------------- backend
 namespace {
@@ -243,6 +257,16 @@ extern "C" tb_status tb_salt_v2_upload_package(tb_backend* b, const uint8_t* pac
   *out = nullptr;
   tbf::Resident r;
   if (tbf::Err e = tbf::resident_from_package(package, len, name, &r)) return from_fmt(e);
+  return upload_resident(b, r, r.payload.size(), false, r.k, out);
+}
+
+extern "C" tb_status tb_salt_v2_upload_reader(tb_backend* b, tb_read_at_fn read_at, void* user, uint64_t package_len, const char* name,
+                                              tb_weights** out) {
+  clear_error();
+  if (!b || !out || !read_at || !name) return tb_fail(TB_NULL_ARG, "null argument");
+  *out = nullptr;
+  tbf::Resident r;
+  if (tbf::Err e = tbf::resident_from_reader(read_at, user, package_len, name, &r)) return from_fmt(e);
   return upload_resident(b, r, r.payload.size(), false, r.k, out);
 }
 
@@ -523,7 +547,7 @@ namespace {
 tb_status check_trait_shape(const tb_weights* w, uint32_t n, uint32_t k) {
   if (!w->is_tq2) return tb_fail(TB_INVALID_INPUT, "buffer is not a TQ2_0 upload");
   if (w->n != n || w->logical_k != k)
-    return tb_fail(TB_SHAPE_MISMATCH, "shape mismatch: expected " + std::to_string(w->n * w->logical_k) + ", got " + std::to_string(uint64_t(n) * k));
+    return fail_shape(w->n * w->logical_k, uint64_t(n) * k);
   return TB_OK;
 }
 // Rows are stored padded to whole 256-trit blocks; widen [m,k] to [m,kp] with zeros.
@@ -875,6 +899,38 @@ extern "C" int64_t tb_fmt_package_write(tb_codec codec, const char* name, uint32
   if (cap < bytes.size()) { tb_fail(TB_SHAPE_MISMATCH, "output buffer too small"); return -TB_SHAPE_MISMATCH; }
   std::copy(bytes.begin(), bytes.end(), out);
   return int64_t(bytes.size());
+}
+
+extern "C" int64_t tb_fmt_package_write_multi(tb_codec codec, uint32_t count, const char* const* names, const uint32_t* groups,
+                                              const uint64_t* n, const uint64_t* k, const uint8_t* const* pc, const int8_t* const* trits,
+                                              const uint16_t* const* scales, uint8_t* out, size_t cap) {
+  clear_error();
+  if (!names || !groups || !n || !k || !pc || !trits || !scales) { tb_fail(TB_NULL_ARG, "null argument"); return -TB_NULL_ARG; }
+  std::vector<tbf::PackageTensorIn> ts(count);
+  for (uint32_t i = 0; i < count; ++i) {
+    if (!names[i] || !pc[i] || !trits[i] || !scales[i]) { tb_fail(TB_NULL_ARG, "null tensor argument"); return -TB_NULL_ARG; }
+    ts[i] = tbf::PackageTensorIn{names[i], groups[i], n[i], k[i], pc[i], trits[i], scales[i]};
+  }
+  std::vector<uint8_t> bytes;
+  if (tbf::Err e = tbf::package_write_multi(int(codec), ts.data(), ts.size(), &bytes)) return -int64_t(from_fmt(e));
+  if (!out) return int64_t(bytes.size());
+  if (cap < bytes.size()) { tb_fail(TB_SHAPE_MISMATCH, "output buffer too small"); return -TB_SHAPE_MISMATCH; }
+  std::copy(bytes.begin(), bytes.end(), out);
+  return int64_t(bytes.size());
+}
+
+extern "C" tb_status tb_fmt_package_extract(tb_read_at_fn read_at, void* user, uint64_t package_len, const char* name,
+                                            tb_package_tensor* info, uint8_t* payload, uint16_t* scales, uint8_t* plane_map) {
+  clear_error();
+  if (!read_at || !name || !info) return tb_fail(TB_NULL_ARG, "null argument");
+  tbf::Resident r;
+  if (tbf::Err e = tbf::resident_from_reader(read_at, user, package_len, name, &r)) return from_fmt(e);
+  info->codec = uint32_t(r.codec); info->group = r.group; info->terminal_map_value = r.terminal_map; info->planes_uniform = r.uniform_planes;
+  info->n = r.n; info->k = r.k; info->payload_bytes = r.payload.size(); info->scale_count = r.scales.size(); info->map_bytes = r.map.size();
+  if (payload) std::copy(r.payload.begin(), r.payload.end(), payload);
+  if (scales) std::copy(r.scales.begin(), r.scales.end(), scales);
+  if (plane_map) std::copy(r.map.begin(), r.map.end(), plane_map);
+  return TB_OK;
 }
 
 extern "C" tb_status tb_fmt_tq2_pack_rows(const int8_t* trits, uint64_t n, uint64_t k, uint8_t* out) {

@@ -386,52 +386,215 @@ struct RawTensor {
 
 }  // namespace
 
-Err package_write(int codec, const char* name, uint32_t group, uint64_t n, uint64_t k,
-                  const uint8_t* pc, const int8_t* trits, const uint16_t* scales, std::vector<uint8_t>* out) {
-  if (!name || !*name) return invalid("tensor name is empty");
-  Resident r;
-  if (Err e = resident_from_planes(codec, group, n, k, pc, trits, scales, &r)) return e;
-  const uint64_t coeffs = n * k, full = coeffs / kTile;
-  std::vector<uint8_t> map(size_t(full * 2 / 8), 0);
-  unsigned embedded = 0;
-  for (uint64_t t = 0; t < full; ++t) {
-    const unsigned bits = presence_bits(pc[t]);
-    for (unsigned b = 0; b < 2; ++b)
-      if (bits >> b & 1u) {
-        const uint64_t bit = t * 2 + b;
-        if (bit < map.size() * 8) map[bit >> 3] |= uint8_t(1u << (bit & 7));
-        else embedded |= 1u << (bit - map.size() * 8);
-      }
+// write_salt_v2_package (crates/tritium-format/src/salt_v2_package.rs:1526-1668): tensors in the
+// given order, one presence map over the full tiles of all of them behind the last tensor, its
+// trailing bits in the tensor-count word, version 2 as soon as one tensor uses 64-wide groups.
+Err package_write_multi(int codec, const PackageTensorIn* ts, size_t count, std::vector<uint8_t>* out) {
+  if (count == 0 || count >= (1u << 26)) return shape("a package holds 1 .. 2^26 - 1 tensors");
+  std::vector<Resident> rs(count);
+  uint64_t full_total = 0, raw = 24;
+  bool any64 = false;
+  for (size_t i = 0; i < count; ++i) {
+    const PackageTensorIn& t = ts[i];
+    if (!t.name || !*t.name) return invalid("tensor name is empty");
+    for (size_t j = 0; j < i; ++j)
+      if (std::strcmp(ts[j].name, t.name) == 0) return invalid(std::string("duplicate tensor name ") + t.name);
+    if (Err e = resident_from_planes(codec, t.group, t.n, t.k, t.plane_count, t.trits, t.scales, &rs[i])) return e;
+    any64 |= t.group == 64;
+    full_total += t.n * t.k / kTile;
+    raw += 64 + std::strlen(t.name) + 16 + rs[i].payload.size() + rs[i].scales.size() * 2;
   }
-  const size_t name_len = std::strlen(name);
-  const uint64_t raw = 24 + 64 + name_len + 16 + r.payload.size() + r.scales.size() * 2 + map.size();
+  std::vector<uint8_t> map(size_t(full_total * 2 / 8), 0);
+  unsigned embedded = 0;
+  uint64_t g = 0;
+  for (size_t i = 0; i < count; ++i) {
+    const uint64_t full = ts[i].n * ts[i].k / kTile;
+    for (uint64_t t = 0; t < full; ++t, ++g) {
+      const unsigned bits = presence_bits(ts[i].plane_count[t]);
+      for (unsigned b = 0; b < 2; ++b)
+        if (bits >> b & 1u) {
+          const uint64_t bit = g * 2 + b;
+          if (bit < map.size() * 8) map[bit >> 3] |= uint8_t(1u << (bit & 7));
+          else embedded |= 1u << (bit - map.size() * 8);
+        }
+    }
+  }
+  raw += map.size();
   const uint64_t total = (raw + 7) / 8 * 8;
   std::vector<uint8_t>& o = *out;
   o.clear();
   o.reserve(size_t(total));
   o.insert(o.end(), {'T', 'S', 'L', 'T', '2', 'P', 'K', 'G'});
-  put(&o, group == 128 ? 1 : 2, 2);
+  put(&o, any64 ? 2 : 1, 2);
   o.push_back(uint8_t(codec));
   o.push_back(0);
-  put(&o, 1u | (embedded << 26), 4);
+  put(&o, uint32_t(count) | (embedded << 26), 4);
   put(&o, total, 8);
-  put(&o, name_len, 4);
-  put(&o, 2, 4);
-  put(&o, coeffs, 8);
-  put(&o, r.tiles | (uint64_t(coeffs % kTile ? presence_bits(pc[r.tiles - 1]) : 0u) << 62), 8);
-  put(&o, r.payload.size(), 8);
-  put(&o, r.scales.size() * 2, 8);
-  o.push_back(0);
-  o.push_back(group == 64 ? 1 : 0);
-  o.insert(o.end(), 6 + 16, 0);
-  o.insert(o.end(), name, name + name_len);
-  put(&o, n, 8);
-  put(&o, k, 8);
-  o.insert(o.end(), r.payload.begin(), r.payload.end());
-  for (uint16_t s : r.scales) put(&o, s, 2);
+  for (size_t i = 0; i < count; ++i) {
+    const PackageTensorIn& t = ts[i];
+    const Resident& r = rs[i];
+    const uint64_t coeffs = t.n * t.k;
+    const size_t name_len = std::strlen(t.name);
+    put(&o, name_len, 4);
+    put(&o, 2, 4);
+    put(&o, coeffs, 8);
+    put(&o, r.tiles | (uint64_t(coeffs % kTile ? presence_bits(t.plane_count[r.tiles - 1]) : 0u) << 62), 8);
+    put(&o, r.payload.size(), 8);
+    put(&o, r.scales.size() * 2, 8);
+    o.push_back(0);
+    o.push_back(t.group == 64 ? 1 : 0);
+    o.insert(o.end(), 6 + 16, 0);
+    o.insert(o.end(), t.name, t.name + name_len);
+    put(&o, t.n, 8);
+    put(&o, t.k, 8);
+    o.insert(o.end(), r.payload.begin(), r.payload.end());
+    for (uint16_t s : r.scales) put(&o, s, 2);
+  }
   o.insert(o.end(), map.begin(), map.end());
   o.resize(size_t(total), 0);
   return ok();
+}
+
+Err package_write(int codec, const char* name, uint32_t group, uint64_t n, uint64_t k,
+                  const uint8_t* pc, const int8_t* trits, const uint16_t* scales, std::vector<uint8_t>* out) {
+  const PackageTensorIn one{name, group, n, k, pc, trits, scales};
+  return package_write_multi(codec, &one, 1, out);
+}
+
+// ---------------------------------------------------------------- package reader over a byte source
+// SaltV2PackageReader (crates/tritium-format/src/salt_v2_package/reader.rs:333,790,841): the
+// header table is walked with small reads, the sections of other tensors are skipped, and only the
+// named tensor's payload, scales and its slice of the presence map are fetched.
+namespace {
+struct SourceReader {
+  ReadAtFn read_at; void* user; uint64_t len; uint64_t pos = 0; bool fail = false;
+  bool fetch(uint64_t off, void* dst, size_t n) {
+    if (off > len || len - off < n) { fail = true; return false; }
+    if (n && read_at(user, off, dst, n) != 0) { fail = true; return false; }
+    return true;
+  }
+  bool take(void* dst, size_t n) { if (!fetch(pos, dst, n)) return false; pos += n; return true; }
+  uint64_t le(size_t n) { uint8_t b[8] = {0}; take(b, n); uint64_t v = 0; for (size_t i = 0; i < n; ++i) v |= uint64_t(b[i]) << (8 * i); return v; }
+  void skip(uint64_t n) { if (len - pos < n) fail = true; else pos += n; }
+};
+}  // namespace
+
+Err resident_from_reader(ReadAtFn read_at, void* user, uint64_t len, const char* want, Resident* out) {
+  if (!read_at || !want) return invalid("null reader or tensor name");
+  SourceReader rd{read_at, user, len};
+  uint8_t magic[8];
+  if (!rd.take(magic, 8) || std::memcmp(magic, "TSLT2PKG", 8)) return invalid("bad package magic");
+  const unsigned version = unsigned(rd.le(2));
+  if (rd.fail || (version != 1 && version != 2)) return invalid("unsupported package version " + std::to_string(version));
+  const int codec = int(rd.le(1));
+  if (rd.fail || codec < kD2 || codec > kS34) return Err{3, "unsupported package codec tag " + std::to_string(codec)};
+  if (rd.le(1) != 0 || rd.fail) return invalid("package flags must be zero");
+  const uint32_t word = uint32_t(rd.le(4));
+  const uint32_t count = word & ((1u << 26) - 1), embedded = word >> 26;
+  const uint64_t declared_total = rd.le(8);
+  if (rd.fail) return invalid("truncated package header");
+  if (declared_total != len) return invalid("package declares " + std::to_string(declared_total) + " bytes but holds " + std::to_string(len));
+  if (count == 0) return invalid("package holds no tensor");
+  RawTensor hit;
+  uint64_t hit_payload_off = 0, hit_scales_off = 0, full_total = 0;
+  bool found = false, any64 = false;
+  std::vector<std::string> names;
+  for (uint32_t i = 0; i < count; ++i) {
+    RawTensor t;
+    const uint32_t name_len = uint32_t(rd.le(4)), rank = uint32_t(rd.le(4));
+    const uint64_t declared_coeffs = rd.le(8), tile_word = rd.le(8);
+    t.payload_len = rd.le(8); t.scales_len = rd.le(8);
+    const unsigned tag = unsigned(rd.le(1)), geom = unsigned(rd.le(1));
+    uint8_t zero6[6] = {1, 1, 1, 1, 1, 1};
+    rd.take(zero6, 6);
+    const uint64_t seed = rd.le(8), domain = rd.le(8);
+    if (rd.fail) return invalid("truncated tensor header");
+    if (std::any_of(zero6, zero6 + 6, [](uint8_t v) { return v != 0; })) return invalid("noncanonical transform metadata");
+    if (version == 1 ? geom != 0 : geom > 1) return invalid("unsupported scale geometry tag " + std::to_string(geom));
+    t.group = geom ? 64 : 128;
+    any64 |= geom != 0;
+    if (tag == 0 && (seed || domain)) return invalid("noncanonical transform metadata");
+    if (tag > 1) return invalid("unsupported transform tag " + std::to_string(tag));
+    if (!name_len) return invalid("empty tensor name");
+    if (name_len > rd.len - rd.pos) return invalid("truncated tensor name");
+    t.name.resize(name_len);
+    if (!rd.take(&t.name[0], name_len)) return invalid("truncated tensor name");
+    if (std::find(names.begin(), names.end(), t.name) != names.end()) return invalid("duplicate tensor name " + t.name);
+    names.push_back(t.name);
+    if (rank == 0) return invalid("tensor has no dimensions");
+    uint64_t prod = 1, last = 1;
+    for (uint32_t d = 0; d < rank; ++d) {
+      last = rd.le(8);
+      if (rd.fail) return invalid("truncated tensor dimensions");
+      if (!last || (prod && last > UINT64_MAX / prod)) return invalid("invalid tensor dimensions");
+      prod *= last;
+    }
+    t.cols = last; t.rows = prod / last; t.coeffs = prod;
+    if (declared_coeffs != prod) return invalid("declared coefficient count disagrees with the dimensions");
+    t.tiles = (prod + kTile - 1) / kTile;
+    if ((tile_word & ((1ull << 62) - 1)) != t.tiles) return invalid("declared tile count disagrees with the dimensions");
+    const unsigned ragged = unsigned(tile_word >> 62);
+    t.full_tiles = prod / kTile;
+    if (prod % kTile == 0) { if (ragged) return invalid("noncanonical map padding"); }
+    else { if (ragged == 2) return invalid("plane map is not nested"); t.ragged_planes = 1 + int(ragged & 1) + int(ragged >> 1); }
+    const bool is_hit = t.name == want;
+    if (tag == 1 && is_hit) return invalid("tensor transform SignedRht is not implemented; only None is accepted");
+    if (rank != 2 && is_hit) return invalid("SALT V2 forward requires rank 2, got rank " + std::to_string(rank));
+    if (t.payload_len > rd.len - rd.pos || t.scales_len > rd.len - rd.pos - t.payload_len) return invalid("truncated tensor sections");
+    t.first_full = full_total;
+    if (is_hit) { hit = t; hit_payload_off = rd.pos; hit_scales_off = rd.pos + t.payload_len; found = true; }
+    rd.skip(t.payload_len + t.scales_len);
+    full_total += t.full_tiles;
+  }
+  if (version != (any64 ? 2u : 1u)) return invalid("noncanonical package version");
+  const uint64_t map_off = rd.pos, map_len = full_total * 2 / 8;
+  rd.skip(map_len);
+  if (rd.fail) return invalid("truncated presence map");
+  if (full_total * 2 % 8 < 6 && (embedded >> (full_total * 2 % 8))) return invalid("noncanonical map padding");
+  const uint64_t pad = (8 - rd.pos % 8) % 8;
+  if (rd.len - rd.pos != pad) return invalid("unexpected trailing data");
+  uint8_t padding[8] = {0};
+  if (pad && !rd.take(padding, size_t(pad))) return invalid("truncated file padding");
+  for (uint64_t i = 0; i < pad; ++i) if (padding[i]) return invalid("noncanonical file padding");
+  if (!found) return invalid(std::string("package holds no tensor named ") + want);
+  // the tensor's slice of the presence map
+  const uint64_t bit0 = hit.first_full * 2, bit1 = (hit.first_full + hit.full_tiles) * 2;
+  const uint64_t byte0 = bit0 / 8, byte1 = std::min<uint64_t>((bit1 + 7) / 8, map_len);
+  std::vector<uint8_t> map(size_t(byte1 > byte0 ? byte1 - byte0 : 0));
+  if (!map.empty() && !rd.fetch(map_off + byte0, map.data(), map.size())) return invalid("presence map cannot be read");
+  auto planes_at = [&](uint64_t gtile) -> int {
+    unsigned bits = 0;
+    for (unsigned b = 0; b < 2; ++b) {
+      const uint64_t bit = gtile * 2 + b;
+      bits |= (bit < map_len * 8 ? (map[size_t((bit >> 3) - byte0)] >> (bit & 7)) & 1u : (embedded >> (bit - map_len * 8)) & 1u) << b;
+    }
+    return bits == 2 ? -1 : 1 + int(bits & 1) + int(bits >> 1);
+  };
+  std::vector<uint8_t> counts(size_t(hit.tiles));
+  for (uint64_t i = 0; i < hit.tiles; ++i) {
+    const int pcount = i < hit.full_tiles ? planes_at(hit.first_full + i) : hit.ragged_planes;
+    if (pcount < 0) return invalid("plane map is not nested");
+    counts[i] = uint8_t(pcount);
+  }
+  Sizes sz;
+  if (Err e = resident_sizes(codec, hit.group, hit.rows, hit.cols, counts.data(), &sz)) return e;
+  if (sz.payload_bytes != hit.payload_len || sz.scale_count * 2 != hit.scales_len)
+    return invalid("declared section sizes of tensor " + hit.name + " disagree with the derived sizes");
+  std::vector<uint8_t> payload(size_t(hit.payload_len)), scale_bytes(size_t(hit.scales_len));
+  if (!payload.empty() && !rd.fetch(hit_payload_off, payload.data(), payload.size())) return invalid("tensor payload cannot be read");
+  if (!scale_bytes.empty() && !rd.fetch(hit_scales_off, scale_bytes.data(), scale_bytes.size())) return invalid("tensor scales cannot be read");
+  std::vector<uint16_t> sc(scale_bytes.size() / 2);
+  for (size_t i = 0; i < sc.size(); ++i) sc[i] = uint16_t(scale_bytes[2 * i] | (scale_bytes[2 * i + 1] << 8));
+  std::vector<uint8_t> rmap(size_t(hit.tiles * 2 / 8), 0);
+  uint32_t terminal = 0;
+  for (uint64_t i = 0; i < hit.tiles; ++i) {
+    const uint64_t bit = i * 2;
+    const unsigned code = counts[i] - 1u;
+    if (bit < rmap.size() * 8) rmap[bit >> 3] |= uint8_t(code << (bit & 7));
+    else terminal |= code << (bit - rmap.size() * 8);
+  }
+  return resident_from_arenas(codec, hit.group, hit.rows, hit.cols, payload.data(), payload.size(), sc.data(), sc.size(),
+                              rmap.data(), rmap.size(), terminal, out);
 }
 
 Err resident_from_package(const uint8_t* bytes, size_t len, const char* want, Resident* out) {

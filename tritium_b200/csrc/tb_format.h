@@ -65,6 +65,17 @@ Err resident_from_arenas(int codec, uint32_t group, uint64_t n, uint64_t k, cons
                          const uint8_t* map, size_t map_len, uint32_t terminal, Resident* out);
 // From package bytes (whole-package validation), tensor selected by name.
 Err resident_from_package(const uint8_t* bytes, size_t len, const char* name, Resident* out);
+// From a byte source read at arbitrary offsets (a seekable file): the header table is walked, the
+// named tensor's sections and its slice of the presence map are fetched, nothing else is read.
+// `read_at` returns 0 on success.
+using ReadAtFn = int (*)(void* user, uint64_t offset, void* dst, size_t len);
+Err resident_from_reader(ReadAtFn read_at, void* user, uint64_t len, const char* name, Resident* out);
+// Package bytes for matrix tensors in the given order.
+struct PackageTensorIn {
+  const char* name; uint32_t group; uint64_t n, k;
+  const uint8_t* plane_count; const int8_t* trits; const uint16_t* scales;
+};
+Err package_write_multi(int codec, const PackageTensorIn* tensors, size_t count, std::vector<uint8_t>* out);
 // Package bytes for one matrix tensor.
 Err package_write(int codec, const char* name, uint32_t group, uint64_t n, uint64_t k,
                   const uint8_t* plane_count, const int8_t* trits, const uint16_t* scales,

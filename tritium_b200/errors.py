@@ -13,7 +13,11 @@ class NullArg(BackendError):
 
 
 class ShapeMismatch(BackendError):
-    pass
+    """BackendError::ShapeMismatch { expected, got }; the two lengths are attributes when known."""
+
+    def __init__(self, message="", expected=None, got=None):
+        super().__init__(message)
+        self.expected, self.got = expected, got
 
 
 class UnsupportedFormat(BackendError):
@@ -44,5 +48,13 @@ _BY_STATUS = {
 
 
 def check(status: int) -> None:
-    if status != _lib.TB_OK:
-        raise _BY_STATUS.get(int(status), BackendError)(_lib.last_error())
+    if status == _lib.TB_OK:
+        return
+    message = _lib.last_error()
+    if int(status) == _lib.TB_SHAPE_MISMATCH:
+        import ctypes as C
+        expected, got = C.c_uint64(0), C.c_uint64(0)
+        if _lib.load().tb_last_shape_mismatch(C.byref(expected), C.byref(got)) == _lib.TB_OK:
+            raise ShapeMismatch(message, expected.value, got.value)
+        raise ShapeMismatch(message)
+    raise _BY_STATUS.get(int(status), BackendError)(message)

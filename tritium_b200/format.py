@@ -140,6 +140,45 @@ def write_salt_v2_package(tensor: SaltV2Tensor, codec: SaltV2Codec) -> bytes:
     return out.tobytes()
 
 
+def write_salt_v2_package_multi(tensors, codec: SaltV2Codec) -> bytes:
+    """write_salt_v2_package for several matrix tensors in the given order (salt_v2_package.rs:1526-1668)."""
+    L = _lib.load()
+    count = len(tensors)
+    names = (C.c_char_p * count)(*[t.name.encode() for t in tensors])
+    groups = (C.c_uint32 * count)(*[t.scale_group_size for t in tensors])
+    ns = (C.c_uint64 * count)(*[t.rows for t in tensors])
+    ks = (C.c_uint64 * count)(*[t.cols for t in tensors])
+    pcs = (C.c_void_p * count)(*[t.plane_count.ctypes.data for t in tensors])
+    trits = (C.c_void_p * count)(*[t.trits.ctypes.data for t in tensors])
+    scales = (C.c_void_p * count)(*[t.scales.ctypes.data for t in tensors])
+    args = (int(codec), C.c_uint32(count), names, groups, ns, ks, pcs, trits, scales)
+    n = L.tb_fmt_package_write_multi(*args, None, C.c_size_t(0))
+    if n < 0:
+        check(-n)
+    out = np.zeros(int(n), np.uint8)
+    n = L.tb_fmt_package_write_multi(*args, _ptr(out), C.c_size_t(out.size))
+    if n < 0:
+        check(-n)
+    return out.tobytes()
+
+
+def package_extract(fileobj, name: str):
+    """The resident arenas of one tensor of a package file, read through seeks (the header table and
+    that tensor's sections only): (info dict, payload u8, scales u16, plane_map u8)."""
+    L = _lib.load()
+    fileobj.seek(0, 2)
+    length = fileobj.tell()
+    cb = _lib.file_read_at(fileobj)
+    info = _lib.PackageTensor()
+    check(L.tb_fmt_package_extract(cb, None, C.c_uint64(length), name.encode(), C.byref(info), None, None, None))
+    payload = np.zeros(max(info.payload_bytes, 1), np.uint8)
+    scales = np.zeros(max(info.scale_count, 1), np.uint16)
+    pmap = np.zeros(max(info.map_bytes, 1), np.uint8)
+    check(L.tb_fmt_package_extract(cb, None, C.c_uint64(length), name.encode(), C.byref(info), _ptr(payload), _ptr(scales), _ptr(pmap)))
+    meta = {k: getattr(info, k) for k, _ in _lib.PackageTensor._fields_}
+    return meta, payload[: info.payload_bytes], scales[: info.scale_count], pmap[: info.map_bytes]
+
+
 def pack_tq2_0_rows(trits: np.ndarray) -> bytes:
     """pack_tq2_0_row over [n, k] trits with unit block scales (rows.rs:61-77)."""
     t = np.ascontiguousarray(trits, dtype=np.int8)
