@@ -100,6 +100,21 @@ tb_status tb_backend_synchronize(tb_backend* backend);
  * crates/tritium-cuda/src/cuda/backend.rs:8581-8650).  `len` must equal n*ceil(k/256)*66. */
 tb_status tb_tq2_upload(tb_backend* backend, const uint8_t* packed, size_t len, uint32_t n,
                         uint32_t k, tb_weights** out);
+/* The same for TernaryFormat::Tq1_0 (54-byte blocks, crates/tritium-format/src/tq1.rs:16-122; the
+ * reference's kernels for it: crates/tritium-cuda/kernels/tq2_0_add.cu:796-913).  `len` must equal
+ * n*ceil(k/256)*54.  The handle runs through tb_mpgemm / tb_mpgemm_with_act_quant like a TQ2_0 one. */
+tb_status tb_tq1_upload(tb_backend* backend, const uint8_t* packed, size_t len, uint32_t n,
+                        uint32_t k, tb_weights** out);
+/* SALT V1 multi-plane weights: `t_planes` (1..3) plane-major TQ2_0 planes [t][n][ceil(k/256)*66]
+ * whose f16 block scale is the plane's scale for that block; W = sum_p scale_p * trit_p.  Replaces
+ * the upload behind salt_mpgemm_tiled_f32 (crates/tritium-cuda/kernels/tq2_0_add.cu:640-719, host
+ * crates/tritium-cuda/src/cuda/backend.rs:7807-7811) and PackedSaltMatrix
+ * (crates/tritium-nn/src/layers/packed_salt.rs:612-678).  The handle then runs through the same
+ * forward entry points: tb_linear_forward_a8 is SaltLinear::forward (layers/salt.rs:114-147: quantise,
+ * project, scale), tb_linear_forward_f32 the kernel's fp32-activation form.  Rows are padded to whole
+ * 256-blocks with zero trits: activations and info.k use the padded width. */
+tb_status tb_salt_v1_upload(tb_backend* backend, const uint8_t* planes, size_t len, uint32_t t_planes,
+                            uint32_t n, uint32_t k, tb_weights** out);
 /* CudaBackend::upload_salt_v2 (crates/tritium-cuda/src/cuda/backend.rs:7463-7651), taking the
  * resident arenas: payload (tile-major then plane), f16 scale bits, the runtime plane map
  * (2 bits per tile, value planes-1) and its terminal partial byte.  Sizes are re-derived from

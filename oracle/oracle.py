@@ -382,6 +382,66 @@ def tq2_unpack_rows(packed: bytes, n: int, k: int) -> np.ndarray:
     return out
 
 
+def tq1_pack_rows(trits: np.ndarray, block_scale_bits: int = 0x3C00) -> bytes:
+    """[n, k] int8 -> n rows of ceil(k/256)*54 bytes (TQ1_0; block scale defaults to f16 1.0)."""
+    trits = np.ascontiguousarray(trits, dtype=np.int8)
+    n, k = trits.shape
+    nb = (k + 255) // 256
+    out = np.zeros((n, nb * 54), np.uint8)
+    sc = np.full(nb, block_scale_bits, np.uint16)
+    for r in range(n):
+        rc = lib().or_tq1_pack_row(_p(trits[r]), C.c_uint64(k), _p(sc), _p(out[r]))
+        if rc:
+            raise OracleError(rc)
+    return out.tobytes()
+
+
+def tq1_unpack_rows(packed: bytes, n: int, k: int) -> np.ndarray:
+    nb = (k + 255) // 256
+    b = np.frombuffer(packed, np.uint8).reshape(n, nb * 54).copy()
+    out = np.zeros((n, k), np.int8)
+    for r in range(n):
+        rc = lib().or_tq1_unpack_row(_p(b[r]), C.c_uint64(k), _p(out[r]), None)
+        if rc:
+            raise OracleError(rc)
+    return out
+
+
+def salt_v1_pack(trits: np.ndarray, block_scales: np.ndarray) -> bytes:
+    """trits[T, n, k] int8 and block_scales[T, n, ceil(k/256)] f16 bits -> plane-major TQ2_0 rows."""
+    trits = np.ascontiguousarray(trits, np.int8)
+    t, n, k = trits.shape
+    nb = (k + 255) // 256
+    out = np.zeros((t, n, nb * 66), np.uint8)
+    for p in range(t):
+        for r in range(n):
+            sc = np.ascontiguousarray(block_scales[p, r], np.uint16)
+            rc = lib().or_tq2_pack_row(_p(trits[p, r]), C.c_uint64(k), _p(sc), _p(out[p, r]))
+            if rc:
+                raise OracleError(rc)
+    return out.tobytes()
+
+
+def salt_v1_matmul(planes: bytes, t_planes: int, n: int, k: int, act) -> np.ndarray:
+    """PackedSaltMatrix::row_dot over every row (packed_salt.rs:612-661); act [m, k] f32."""
+    act = np.ascontiguousarray(act, np.float32).reshape(-1, k)
+    m = act.shape[0]
+    buf = np.frombuffer(planes, np.uint8)
+    out = np.zeros((m, n), np.float32)
+    rc = lib().or_salt_v1_matmul(_p(buf), C.c_uint32(t_planes), C.c_uint64(n), C.c_uint64(k), _p(act), C.c_uint64(m), _p(out))
+    if rc:
+        raise OracleError(rc)
+    return out
+
+
+def salt_v1_forward_a8(planes: bytes, t_planes: int, n: int, k: int, act) -> np.ndarray:
+    """SaltLinear::forward (crates/tritium-nn/src/layers/salt.rs:114-147): quantise, project, scale."""
+    act = np.ascontiguousarray(act, np.float32).reshape(-1, k)
+    q, s = quantize_act_int8(act, act.shape[0], k)
+    y = salt_v1_matmul(planes, t_planes, n, k, q)
+    return y * s[:, None]
+
+
 def reference_mpgemm(act, w, scales, m, n, k) -> np.ndarray:
     act = np.ascontiguousarray(act, np.float32)
     w = np.ascontiguousarray(w, np.int8)

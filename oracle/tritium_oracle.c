@@ -967,6 +967,77 @@ int or_tq2_unpack_row(const uint8_t* packed, uint64_t k, int8_t* trits_out, uint
   return OR_OK;
 }
 
+/* TQ1_0 block (54 bytes = 48 qs + 4 qh + f16 scale): pack_tq1_0_block / unpack_tq1_0_block,
+ * crates/tritium-format/src/tq1.rs:16-122.  Five trits per byte in ggml's fixed-point base-3 code:
+ * encode = ceil(acc * 256 / 243), decode digit n = (((byte * 3^n) mod 256) * 3) >> 8. */
+static uint8_t tq1_encode(unsigned acc) { return (uint8_t)((acc * 256u + 242u) / 243u); }
+static int8_t tq1_decode(uint8_t byte, int n) {
+  static const uint8_t pow3[6] = {1, 3, 9, 27, 81, 243};
+  uint8_t q = (uint8_t)(byte * pow3[n]);
+  return (int8_t)((((unsigned)q * 3u) >> 8) - 1);
+}
+int or_tq1_pack_row(const int8_t* trits, uint64_t k, const uint16_t* block_scales, uint8_t* out) {
+  uint64_t nb = (k + 255) / 256;
+  for (uint64_t b = 0; b < nb; b++) {
+    int8_t blk[256];
+    for (int i = 0; i < 256; i++) blk[i] = b * 256 + i < k ? trits[b * 256 + i] : 0;
+    uint8_t* o = out + b * 54;
+    for (int m = 0; m < 32; m++) { unsigned acc = 0; for (int n = 0; n < 5; n++) acc = acc * 3 + (unsigned)(blk[m + n * 32] + 1); o[m] = tq1_encode(acc); }
+    for (int m = 0; m < 16; m++) { unsigned acc = 0; for (int n = 0; n < 5; n++) acc = acc * 3 + (unsigned)(blk[160 + m + n * 16] + 1); o[32 + m] = tq1_encode(acc); }
+    for (int j = 0; j < 4; j++) { unsigned acc = 0; for (int m = 0; m < 4; m++) acc = acc * 3 + (unsigned)(blk[240 + j + m * 4] + 1); acc *= 3; o[48 + j] = tq1_encode(acc); }
+    put16(o + 52, block_scales ? block_scales[b] : 0x3C00);
+  }
+  return OR_OK;
+}
+int or_tq1_unpack_row(const uint8_t* packed, uint64_t k, int8_t* trits_out, uint16_t* scales_out) {
+  uint64_t nb = (k + 255) / 256;
+  for (uint64_t b = 0; b < nb; b++) {
+    const uint8_t* qs = packed + b * 54;
+    int8_t blk[256];
+    for (int n = 0; n < 5; n++) for (int m = 0; m < 32; m++) blk[n * 32 + m] = tq1_decode(qs[m], n);
+    for (int n = 0; n < 5; n++) for (int m = 0; m < 16; m++) blk[160 + n * 16 + m] = tq1_decode(qs[32 + m], n);
+    for (int n = 0; n < 4; n++) for (int j = 0; j < 4; j++) blk[240 + n * 4 + j] = tq1_decode(qs[48 + j], n);
+    uint64_t len = k - b * 256 < 256 ? k - b * 256 : 256;
+    memcpy(trits_out + b * 256, blk, (size_t)len);
+    if (scales_out) scales_out[b] = get16(qs + 52);
+  }
+  return OR_OK;
+}
+
+/* SALT V1 multi-plane forward.  PackedSaltMatrix::row_dot with reconstruct_block over dense planes
+ * (crates/tritium-nn/src/layers/packed_salt.rs:612-661): per 256-block the weights are rebuilt in
+ * f32 as w[i] = sum over planes (plane order) of scale_p * trit_p[i], then acc += act[i] * w[i] in
+ * ascending k.  `planes` is plane-major [t_planes][n][ceil(k/256) * 66] TQ2_0 rows whose block
+ * scale carries the plane's per-block scale (kernel twin: tq2_0_add.cu:661-719). */
+int or_salt_v1_matmul(const uint8_t* planes, uint32_t t_planes, uint64_t n, uint64_t k, const float* act,
+                      uint64_t m, float* out) {
+  uint64_t nb = (k + 255) / 256, row_bytes = nb * 66;
+  for (uint64_t mi = 0; mi < m; mi++)
+    for (uint64_t ni = 0; ni < n; ni++) {
+      float acc = 0.0f;
+      for (uint64_t b = 0; b < nb; b++) {
+        float weight[256];
+        for (int i = 0; i < 256; i++) weight[i] = 0.0f;
+        uint64_t len = k - b * 256 < 256 ? k - b * 256 : 256;
+        for (uint32_t p = 0; p < t_planes; p++) {
+          const uint8_t* qs = planes + ((uint64_t)p * n + ni) * row_bytes + b * 66;
+          float scale = or_f16_to_f32(get16(qs + 64));
+          for (int c = 0; c < 2; c++)
+            for (int l = 0; l < 4; l++)
+              for (int mm = 0; mm < 32; mm++) {
+                int qv = (qs[c * 32 + mm] >> (2 * l)) & 3;
+                if (qv == 3) return OR_ERR_INVALID_CODE;
+                int idx = c * 128 + l * 32 + mm;
+                if ((uint64_t)idx < len) weight[idx] += scale * (float)(qv - 1);
+              }
+        }
+        for (uint64_t i = 0; i < len; i++) acc += act[mi * k + b * 256 + i] * weight[i];
+      }
+      out[mi * n + ni] = acc;
+    }
+  return OR_OK;
+}
+
 /* reference_mpgemm: crates/tritium-core/src/reference.rs:25-55 */
 void or_reference_mpgemm(const float* act, const int8_t* w, const float* scale_n, uint64_t m,
                          uint64_t n, uint64_t k, float* out) {

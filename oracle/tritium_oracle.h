@@ -152,6 +152,10 @@ int or_a8_linear(const or_tensor* t, const float* x, uint64_t m, float* y, int32
 int or_tq2_pack_row(const int8_t* trits, uint64_t k, const uint16_t* block_scales, uint8_t* out);
 int or_tq2_unpack_row(const uint8_t* packed, uint64_t k, int8_t* trits_out, uint16_t* scales_out);
 /* crates/tritium-core/src/reference.rs:25-55 */
+int or_tq1_pack_row(const int8_t* trits, uint64_t k, const uint16_t* block_scales, uint8_t* out);
+int or_tq1_unpack_row(const uint8_t* packed, uint64_t k, int8_t* trits_out, uint16_t* scales_out);
+int or_salt_v1_matmul(const uint8_t* planes, uint32_t t_planes, uint64_t n, uint64_t k, const float* act,
+                      uint64_t m, float* out);
 void or_reference_mpgemm(const float* act, const int8_t* w, const float* scale_n, uint64_t m,
                          uint64_t n, uint64_t k, float* out);
 /* crates/tritium-spec/src/lib.rs:266-318 (default host path) */

@@ -393,6 +393,15 @@ def test_trait_path_conformance(backend):
         out_q = np.zeros((m, n), np.float32)
         backend.mpgemm(MpGemm(q, buf, scales, GemmShape(m, n, k), TernaryFormat.Tq2_0, out_q))
         assert np.array_equal(out_q, orc.reference_mpgemm(q, w, scales, m, n, k)), vid
+        # the same weights as TQ1_0 rows give the same bits (crates/tritium-cuda/src/cuda/tests.rs:5520)
+        buf1 = backend.upload_weights(orc.tq1_pack_rows(w), GemmShape(0, n, k), TernaryFormat.Tq1_0)
+        assert buf1.len_bytes() == n * (k // 256) * 54
+        out_1 = np.zeros((m, n), np.float32)
+        backend.mpgemm(MpGemm(q, buf1, scales, GemmShape(m, n, k), TernaryFormat.Tq1_0, out_1))
+        assert np.array_equal(out_1, out_q), vid
+        out_1f = np.zeros((m, n), np.float32)
+        backend.mpgemm_with_act_quant(MpGemm(act, buf1, scales, GemmShape(m, n, k), TernaryFormat.Tq1_0, out_1f))
+        assert np.array_equal(out_1f, out_f), vid
 
 
 def test_trait_path_errors(backend):
@@ -401,7 +410,9 @@ def test_trait_path_errors(backend):
     with pytest.raises(errors.InvalidInput):
         backend.upload_weights(fmt.pack_tq2_0_rows(w)[:-1], GemmShape(0, 2, 256), TernaryFormat.Tq2_0)
     with pytest.raises(errors.UnsupportedFormat):
-        backend.upload_weights(b"", GemmShape(0, 2, 256), TernaryFormat.Tq1_0)
+        backend.upload_weights(b"", GemmShape(0, 2, 256), TernaryFormat.I2sInt8)
+    with pytest.raises(errors.InvalidInput):
+        backend.upload_weights(b"\x80" * 53, GemmShape(0, 1, 256), TernaryFormat.Tq1_0)
     buf = backend.upload_weights(fmt.pack_tq2_0_rows(w), GemmShape(0, 2, 256), TernaryFormat.Tq2_0)
     out = np.zeros((1, 2), np.float32)
     with pytest.raises(errors.ShapeMismatch):

@@ -207,3 +207,34 @@ def test_upload_from_seekable_package_file(backend, tmp_path):
     with open(path, "rb") as f:
         with pytest.raises(errors.InvalidInput):
             backend.upload_salt_v2_from_reader(f, "blk.9.none")
+
+
+# ------------------------------------------------------------------ SALT V1 multi-plane operator
+@pytest.mark.parametrize("t_planes", [1, 2, 3])
+@pytest.mark.parametrize("m", [1, 4, 24])
+def test_salt_v1_planes_match_the_reference_row_dot(backend, t_planes, m):
+    """Plane-major TQ2_0 planes with per-block f16 scales (tq2_0_add.cu:640-719): the int8 path against
+    SaltLinear::forward (quantise, PackedSaltMatrix::row_dot, scale), the fp32 path against row_dot on
+    the raw activations, both under the reference's own 1e-4 rule (crates/tritium-testkit/src/vector.rs:113-126)."""
+    rng = np.random.default_rng(100 + t_planes)
+    n, k = 72, 700                                       # k is not a multiple of 256: rows are padded with zero trits
+    trits = rng.integers(-1, 2, (t_planes, n, k)).astype(np.int8)
+    nb = (k + 255) // 256
+    block_scales = (0.01 + 0.05 * rng.random((t_planes, n, nb))).astype(np.float16).view(np.uint16)
+    planes = orc.salt_v1_pack(trits, block_scales)
+    handle = backend.upload_salt_v1(planes, t_planes, n, k)
+    assert handle.rows == n and handle.columns == nb * 256
+    x = make_activations(m, k, seed=40 + m)
+    xp = np.zeros((m, nb * 256), np.float32)
+    xp[:, :k] = x
+    want = orc.salt_v1_forward_a8(planes, t_planes, n, k, x)
+    _, s = orc.quantize_act_int8(x, m, k)
+    y, _, receipt = backend.linear_forward_a8(handle, xp, m)
+    assert receipt.kernel == (1 if m <= 16 else 2)
+    for r in range(m):
+        assert np.all(np.abs(y[r] - want[r]) <= 1e-4 * np.maximum(max(float(s[r]), 1e-30), np.abs(want[r])))
+    want_f32 = orc.salt_v1_matmul(planes, t_planes, n, k, x)
+    got_f32 = backend.salt_v2_forward_fast(handle, xp, m).output
+    assert np.all(np.abs(got_f32 - want_f32) <= 1e-4 * np.maximum(1.0, np.abs(want_f32)))
+    with pytest.raises(errors.UnsupportedFormat):
+        backend.upload_salt_v1(planes + planes[: len(planes) // t_planes], t_planes + 3, n, k)

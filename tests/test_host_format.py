@@ -186,6 +186,12 @@ def test_host_quantiser_matches_oracle():
     assert list(q[0]) == [64, -127, 32, -32, 127, -64]
 
 
+def test_tq1_rows_match_oracle():
+    rng = np.random.default_rng(6)
+    w = rng.integers(-1, 2, (7, 700)).astype(np.int8)
+    assert fmt.pack_tq1_0_rows(w) == orc.tq1_pack_rows(w)
+
+
 def test_tq2_rows_match_oracle():
     rng = np.random.default_rng(4)
     w = rng.integers(-1, 2, (7, 768)).astype(np.int8)
@@ -223,6 +229,15 @@ def test_tensor_parallel_shards_reassemble(codec, ocodec, world):
         xs[:kv] = x[r * kv:(r + 1) * kv]
         total += orc.forward_packed(ocodec, 128, sn, sk, sp, ss, sm, len(sm), term, xs)[0].astype(np.float64)
     assert np.allclose(total, dense @ x.astype(np.float64), rtol=1e-5, atol=1e-3)
+
+
+def test_library_loads_with_full_signatures():
+    """Every export carries ctypes argument types, so a call with the wrong arity fails in Python."""
+    L = _lib.load()
+    for name in _lib.EXPORTS:
+        assert getattr(L, name).argtypes is not None, name
+    with pytest.raises(TypeError):
+        L.tb_fmt_plane_bytes(1)
 
 
 def test_backend_reports_missing_device_without_aborting():

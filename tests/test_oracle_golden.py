@@ -479,3 +479,41 @@ def test_gather_rows_reconstructs_weights():
     w = dense_weights(t)
     got = orc.gather_rows(t, [2, 0])
     assert np.allclose(got, w[[2, 0]], rtol=0, atol=1e-6)
+
+
+def test_salt_v1_restatement_against_dense_math():
+    """SALT V1 (packed_salt.rs:612-661, tq2_0_add.cu:640-719): W = sum_p scale_p[block] * trit_p.  The
+    reference holds no stored answers for this operator; its own contract is agreement with the dense
+    fp32 matmul within 1e-4 (tq2_0_add.cu:650-653), which pins the restatement here."""
+    rng = np.random.default_rng(5)
+    t, n, k, m = 3, 9, 700, 4
+    trits = rng.integers(-1, 2, (t, n, k)).astype(np.int8)
+    nb = (k + 255) // 256
+    block_scales = (0.01 + 0.05 * rng.random((t, n, nb))).astype(np.float16)
+    planes = orc.salt_v1_pack(trits, block_scales.view(np.uint16))
+    assert len(planes) == t * n * nb * 66
+    act = rng.standard_normal((m, k)).astype(np.float32)
+    got = orc.salt_v1_matmul(planes, t, n, k, act)
+    dense = np.zeros((n, k), np.float64)
+    for p in range(t):
+        dense += trits[p].astype(np.float64) * np.repeat(block_scales[p].astype(np.float64), 256, axis=1)[:, :k]
+    want = act.astype(np.float64) @ dense.T
+    assert np.all(np.abs(got - want) <= 1e-4 * np.maximum(1.0, np.abs(want)))
+    # SaltLinear::forward: quantise, project, scale
+    q, s_ = orc.quantize_act_int8(act, m, k)
+    want_a8 = (q.astype(np.float64) @ dense.T) * s_[:, None].astype(np.float64)
+    got_a8 = orc.salt_v1_forward_a8(planes, t, n, k, act)
+    assert np.all(np.abs(got_a8 - want_a8) <= 1e-4 * np.maximum(1.0, np.abs(want_a8)))
+
+
+def test_tq1_block_goldens():
+    """crates/tritium-format/src/tq1.rs:130-163: all-zero trits -> qs 0x80, qh 0x7F; all +1 -> qs 0xFF,
+    qh 0xFD; all -1 -> 0x00; f16 1.0 scale in the last two bytes; decode of the zero block is zero."""
+    for value, qs, qh in ((0, 0x80, 0x7F), (1, 0xFF, 0xFD), (-1, 0x00, 0x00)):
+        block = np.frombuffer(orc.tq1_pack_rows(np.full((1, 256), value, np.int8)), np.uint8)
+        assert np.all(block[:48] == qs) and np.all(block[48:52] == qh) and bytes(block[52:]) == b"\x00\x3c"
+    zero = bytes([0x80] * 48 + [0x7F] * 4 + [0x00, 0x3C])
+    assert np.all(orc.tq1_unpack_rows(zero, 1, 256) == 0)
+    rng = np.random.default_rng(8)
+    w = rng.integers(-1, 2, (5, 700)).astype(np.int8)
+    assert np.array_equal(orc.tq1_unpack_rows(orc.tq1_pack_rows(w), 5, 700), w)

@@ -28,7 +28,7 @@ EXPORTS = [
     "tb_tp_shard_sizes", "tb_tp_shard", "tb_fmt_pack", "tb_fmt_unpack", "tb_fmt_plane_bytes",
     "tb_fmt_resident_sizes", "tb_fmt_resident_build", "tb_fmt_package_write", "tb_fmt_tq2_pack_rows",
     "tb_fmt_quantize_act_int8", "tb_linear_forward_a8_static", "tb_backend_inject_wait_timeout",
-    "tb_salt_v2_upload_reader", "tb_fmt_package_write_multi", "tb_fmt_package_extract", "tb_last_shape_mismatch",
+    "tb_salt_v2_upload_reader", "tb_fmt_package_write_multi", "tb_fmt_package_extract", "tb_last_shape_mismatch", "tb_salt_v1_upload", "tb_tq1_upload",
 ]
 
 
@@ -109,6 +109,8 @@ _SIGNATURES = {
     "tb_backend_caps": (_ST, [_P, _P]),
     "tb_backend_synchronize": (_ST, [_P]),
     "tb_tq2_upload": (_ST, [_P, _P, _SZ, _U32, _U32, _P]),
+    "tb_tq1_upload": (_ST, [_P, _P, _SZ, _U32, _U32, _P]),
+    "tb_salt_v1_upload": (_ST, [_P, _P, _SZ, _U32, _U32, _U32, _P]),
     "tb_salt_v2_upload": (_ST, [_P, _I, _U32, _U32, _U32, _P, _SZ, _P, _SZ, _P, _SZ, _U32, _P]),
     "tb_salt_v2_upload_package": (_ST, [_P, _P, _SZ, C.c_char_p, _P]),
     "tb_weights_info_get": (_ST, [_P, _P]),

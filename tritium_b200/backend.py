@@ -162,18 +162,21 @@ class B200Backend:
                           int(c.total_memory_bytes), bool(c.supports_imma), bool(c.supports_fp8), int(c.sm_count))
 
     def upload_weights(self, packed: bytes, shape: GemmShape, format: TernaryFormat) -> DeviceBuffer:
-        if format != TernaryFormat.Tq2_0:
+        if format not in (TernaryFormat.Tq2_0, TernaryFormat.Tq1_0):
             raise UnsupportedFormat(f"unsupported ternary format: {format}")
         buf = np.frombuffer(bytes(packed), np.uint8)
         h = C.c_void_p(None)
-        check(self._L.tb_tq2_upload(self._h, _ptr(buf), C.c_size_t(buf.size), C.c_uint32(shape.n), C.c_uint32(shape.k), C.byref(h)))
-        return DeviceBuffer(self, h.value)
+        upload = self._L.tb_tq2_upload if format == TernaryFormat.Tq2_0 else self._L.tb_tq1_upload
+        check(upload(self._h, _ptr(buf), C.c_size_t(buf.size), C.c_uint32(shape.n), C.c_uint32(shape.k), C.byref(h)))
+        out = DeviceBuffer(self, h.value)
+        out.format = format
+        return out
 
     def _check_mpgemm(self, p: MpGemm):
         m, n, k = p.shape.m, p.shape.n, p.shape.k
         if not isinstance(p.weights, DeviceBuffer) or p.weights._backend is not self:
             raise InvalidInput("buffer is not a B200 buffer of this backend")
-        if p.format != TernaryFormat.Tq2_0:
+        if p.format not in (TernaryFormat.Tq2_0, TernaryFormat.Tq1_0) or getattr(p.weights, "format", p.format) != p.format:
             raise UnsupportedFormat(f"unsupported ternary format: {p.format}")
         for arr, want in ((p.act, m * k), (p.scales, n), (p.out, m * n)):
             if arr.size != want:
@@ -214,6 +217,14 @@ class B200Backend:
                                         C.c_size_t(payload.size), _ptr(scales), C.c_size_t(scales.size),
                                         _ptr(plane_map) if plane_map.size else None, C.c_size_t(plane_map.size),
                                         C.c_uint32(terminal), C.byref(h)))
+        return SaltV2ResidentTensor(self, h.value)
+
+    def upload_salt_v1(self, planes: bytes, t_planes: int, n: int, k: int) -> SaltV2ResidentTensor:
+        """SALT V1 plane-major TQ2_0 planes with per-block f16 scales (tq2_0_add.cu:640-719,
+        packed_salt.rs:612-678); the handle's K is k rounded up to whole 256-blocks."""
+        buf = np.frombuffer(bytes(planes), np.uint8)
+        h = C.c_void_p(None)
+        check(self._L.tb_salt_v1_upload(self._h, _ptr(buf), C.c_size_t(buf.size), C.c_uint32(t_planes), C.c_uint32(n), C.c_uint32(k), C.byref(h)))
         return SaltV2ResidentTensor(self, h.value)
 
     def upload_salt_v2_from_package(self, package: bytes, name: str) -> SaltV2ResidentTensor:

@@ -239,6 +239,27 @@ extern "C" tb_status tb_tq2_upload(tb_backend* b, const uint8_t* packed, size_t 
   return upload_resident(b, r, len, true, k, out);
 }
 
+extern "C" tb_status tb_tq1_upload(tb_backend* b, const uint8_t* packed, size_t len, uint32_t n, uint32_t k, tb_weights** out) {
+  clear_error();
+  if (!b || !out || (!packed && len)) return tb_fail(TB_NULL_ARG, "null argument");
+  *out = nullptr;
+  if (n == 0 || k == 0) return tb_fail(TB_INVALID_INPUT, "packed len 0: shape must be positive");
+  tbf::Resident r;
+  if (tbf::Err e = tbf::resident_from_tq1(packed, len, n, k, &r)) return from_fmt(e);
+  return upload_resident(b, r, len, true, k, out);
+}
+
+extern "C" tb_status tb_salt_v1_upload(tb_backend* b, const uint8_t* planes, size_t len, uint32_t t_planes, uint32_t n, uint32_t k,
+                                       tb_weights** out) {
+  clear_error();
+  if (!b || !out || (!planes && len)) return tb_fail(TB_NULL_ARG, "null argument");
+  *out = nullptr;
+  if (n == 0 || k == 0) return tb_fail(TB_INVALID_INPUT, "shape must be positive");
+  tbf::Resident r;
+  if (tbf::Err e = tbf::resident_from_salt_v1(planes, len, t_planes, n, k, &r)) return from_fmt(e);
+  return upload_resident(b, r, len, false, k, out);
+}
+
 extern "C" tb_status tb_salt_v2_upload(tb_backend* b, tb_codec codec, uint32_t group, uint32_t n, uint32_t k,
                                        const uint8_t* payload, size_t payload_len, const uint16_t* scales, size_t scale_count,
                                        const uint8_t* plane_map, size_t map_len, uint32_t terminal, tb_weights** out) {

@@ -758,6 +758,74 @@ Err resident_from_tq2(const uint8_t* packed, size_t len, uint64_t n, uint64_t k,
   return ok();
 }
 
+// TQ1_0 rows (54-byte blocks: 48 + 4 bytes of five / four trits in ggml's fixed-point base-3 code,
+// f16 scale; crates/tritium-format/src/tq1.rs:16-122) -> a 1-plane D2 tensor with unit group scales,
+// like resident_from_tq2.  Digit n of a byte: (((byte * 3^n) mod 256) * 3) >> 8.
+Err resident_from_tq1(const uint8_t* packed, size_t len, uint64_t n, uint64_t k, Resident* out) {
+  if (Err e = check_geometry(kD2, 128, std::max<uint64_t>(n, 1), std::max<uint64_t>(k, 1))) return e;
+  const uint64_t nb = (k + 255) / 256;
+  if (len != n * nb * 54)
+    return invalid("packed len " + std::to_string(len) + " != expected " + std::to_string(n * nb * 54));
+  Resident r;
+  r.codec = kD2; r.group = 128; r.n = n; r.k = nb * 256;
+  r.payload.assign(size_t(n * nb * 64), 0);
+  r.scales.assign(size_t(n * nb * 2), 0x3c00);
+  static const uint8_t pow3[5] = {1, 3, 9, 27, 81};
+  auto digit = [](uint8_t byte, unsigned d) { return unsigned((unsigned(uint8_t(byte * pow3[d])) * 3u) >> 8); };
+  for (uint64_t blk = 0; blk < n * nb; ++blk) {
+    const uint8_t* qs = packed + blk * 54;
+    uint8_t* o = r.payload.data() + blk * 64;
+    auto put_code = [&](unsigned e, unsigned code) { o[e >> 2] = uint8_t(o[e >> 2] | (code << (2 * (e & 3)))); };
+    for (unsigned d = 0; d < 5; ++d) for (unsigned m = 0; m < 32; ++m) put_code(d * 32 + m, digit(qs[m], d));
+    for (unsigned d = 0; d < 5; ++d) for (unsigned m = 0; m < 16; ++m) put_code(160 + d * 16 + m, digit(qs[32 + m], d));
+    for (unsigned d = 0; d < 4; ++d) for (unsigned j = 0; j < 4; ++j) put_code(240 + d * 4 + j, digit(qs[48 + j], d));
+  }
+  finish_index(&r, std::vector<uint8_t>(size_t(n * nb), 1));
+  *out = std::move(r);
+  return ok();
+}
+
+// SALT V1: `planes` plane-major TQ2_0 rows [t][n][ceil(k/256) * 66] whose f16 block scale is that
+// plane's scale for the block (crates/tritium-cuda/kernels/tq2_0_add.cu:640-660,
+// crates/tritium-nn/src/layers/packed_salt.rs:630-645).  Re-laid as a t-plane D2 tensor whose two
+// 128-wide groups of a tile both carry the block scale.
+Err resident_from_salt_v1(const uint8_t* packed, size_t len, uint32_t t_planes, uint64_t n, uint64_t k, Resident* out) {
+  if (t_planes < 1 || t_planes > kMaxPlanes) return Err{3, "SALT V1 upload takes 1..3 planes, got " + std::to_string(t_planes)};
+  if (Err e = check_geometry(kD2, 128, std::max<uint64_t>(n, 1), std::max<uint64_t>(k, 1))) return e;
+  const uint64_t nb = (k + 255) / 256;
+  if (len != uint64_t(t_planes) * n * nb * 66)
+    return invalid("packed len " + std::to_string(len) + " != expected " + std::to_string(uint64_t(t_planes) * n * nb * 66));
+  Resident r;
+  r.codec = kD2; r.group = 128; r.n = n; r.k = nb * 256;
+  r.payload.assign(size_t(n * nb * t_planes * 64), 0x55);
+  r.scales.assign(size_t(n * nb * t_planes * 2), 0);
+  for (uint64_t row = 0; row < n; ++row)
+    for (uint64_t b = 0; b < nb; ++b)
+      for (uint32_t p = 0; p < t_planes; ++p) {
+        const uint8_t* qs = packed + ((uint64_t(p) * n + row) * nb + b) * 66;
+        const uint64_t tile_plane = (row * nb + b) * t_planes + p;
+        uint8_t* o = r.payload.data() + tile_plane * 64;
+        bool any = false;
+        for (unsigned byte = 0; byte < 64; ++byte) {
+          if (qs[byte] & (qs[byte] >> 1) & 0x55) return invalid("TQ2_0 block holds the reserved code 11");
+          for (unsigned s = 0; s < 4; ++s) {
+            const unsigned e = (byte / 32) * 128 + s * 32 + byte % 32, code = (qs[byte] >> (2 * s)) & 3u;
+            any |= code != 1u;
+            o[e >> 2] = uint8_t((o[e >> 2] & ~(3u << (2 * (e & 3)))) | (code << (2 * (e & 3))));
+          }
+        }
+        const uint16_t bits = uint16_t(qs[64] | (qs[65] << 8));
+        const bool finite = (bits & 0x7c00) != 0x7c00, negative = (bits & 0x8000) != 0;
+        if (!finite || negative) return invalid("SALT V1 block scale must be a finite, non-negative f16");
+        if ((bits & 0x7fff) == 0 && any) return invalid("SALT V1 block scale is zero over a block that holds trits");
+        r.scales[size_t(tile_plane * 2)] = bits;
+        r.scales[size_t(tile_plane * 2 + 1)] = bits;
+      }
+  finish_index(&r, std::vector<uint8_t>(size_t(n * nb), uint8_t(t_planes)));
+  *out = std::move(r);
+  return ok();
+}
+
 // ---------------------------------------------------------------- tensor-parallel shards
 Err shard_sizes(int codec, uint32_t group, uint32_t n, uint32_t k, uint32_t planes, bool row_parallel,
                 uint32_t world, uint32_t rank, ShardSizes* out) {

@@ -84,6 +84,10 @@ Err package_write(int codec, const char* name, uint32_t group, uint64_t n, uint6
 // TQ2_0 rows (66-byte blocks) -> a 1-plane D2 resident tensor with unit group scales.
 Err resident_from_tq2(const uint8_t* packed, size_t len, uint64_t n, uint64_t k, Resident* out);
 Err tq2_pack_rows(const int8_t* trits, uint64_t n, uint64_t k, uint8_t* out);
+// TQ1_0 rows (54-byte blocks) -> a 1-plane D2 resident tensor with unit group scales.
+Err resident_from_tq1(const uint8_t* packed, size_t len, uint64_t n, uint64_t k, Resident* out);
+// SALT V1 plane-major TQ2_0 planes (per-block f16 scales inside the blocks) -> a t-plane D2 resident tensor.
+Err resident_from_salt_v1(const uint8_t* packed, size_t len, uint32_t t_planes, uint64_t n, uint64_t k, Resident* out);
 
 // Tensor-parallel shard of a uniform-plane tensor.
 struct ShardSizes { uint32_t n = 0, k = 0; uint64_t payload_bytes = 0, scale_count = 0, map_bytes = 0; };

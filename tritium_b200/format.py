@@ -188,6 +188,33 @@ def pack_tq2_0_rows(trits: np.ndarray) -> bytes:
     return out.tobytes()
 
 
+def pack_tq1_0_rows(trits: np.ndarray) -> bytes:
+    """pack_tq1_0_block over [n, k] trits with unit block scales (crates/tritium-format/src/tq1.rs:36-78).
+    Test vectors only: the product consumes TQ1_0 rows, it never has to produce them on the hot path."""
+    trits = np.ascontiguousarray(trits, np.int8)
+    n, k = trits.shape
+    nb = (k + 255) // 256
+    out = np.zeros((n, nb, 54), np.uint8)
+    padded = np.zeros((n, nb * 256), np.int64)
+    padded[:, :k] = trits
+    x = (padded + 1).reshape(n, nb, 256)
+    enc = lambda acc: ((acc * 256 + 242) // 243).astype(np.uint8)
+    acc = np.zeros((n, nb, 32), np.int64)
+    for d in range(5):
+        acc = acc * 3 + x[:, :, d * 32:(d + 1) * 32]
+    out[:, :, :32] = enc(acc)
+    acc = np.zeros((n, nb, 16), np.int64)
+    for d in range(5):
+        acc = acc * 3 + x[:, :, 160 + d * 16:160 + (d + 1) * 16]
+    out[:, :, 32:48] = enc(acc)
+    acc = np.zeros((n, nb, 4), np.int64)
+    for d in range(4):
+        acc = acc * 3 + x[:, :, 240 + d * 4:240 + (d + 1) * 4]
+    out[:, :, 48:52] = enc(acc * 3)
+    out[:, :, 52], out[:, :, 53] = 0x00, 0x3C
+    return out.tobytes()
+
+
 def quantize_act_int8(act: np.ndarray, m: int, k: int):
     """quantize_act_int8 (crates/tritium-spec/src/lib.rs:351-378), host side."""
     a = np.ascontiguousarray(act, dtype=np.float32)
