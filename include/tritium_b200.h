@@ -188,6 +188,33 @@ typedef struct tb_forward_args {
 } tb_forward_args;
 tb_status tb_linear_forward_dev(tb_backend* backend, const tb_weights* weights,
                                 const tb_forward_args* args, tb_receipt* receipt);
+/* The decode block's fused step around a packed linear, on device pointers: RMSNorm in front of
+ * the int8 quantiser and `residual + y` behind the token scale.  Replaces the reference's
+ * rmsnorm_quant_i8 launch in front of its int8 GEMV (crates/tritium-cuda/kernels/decode.cu:533-640;
+ * arithmetic of crates/tritium-nn/src/ops/rmsnorm.rs:20-94, including the canonical 256-slot
+ * reduction order, so the int8 codes equal the reference's) and the residual epilogue of its
+ * TQ2_0 kernels (crates/tritium-cuda/kernels/tq2_0_add.cu:577-637: one rounding for
+ * residual + acc * scale).  Up to four tokens with small activation tables run as ONE launch
+ * (the norm happens inside the decode kernel's table builder); other shapes normalise with a
+ * kernel of their own into backend scratch, which the first such call of a size allocates.
+ *   norm_weight NULL = no norm (residual epilogue only); residual NULL = none.
+ *   x fp32 or bf16 (bf16 is widened exactly); norm_weight fp32 [k]; residual fp32 [m][n]. */
+#define TB_NORM_ZERO_CENTERED 1u   /* scale by (1 + w): rmsnorm_zero_centered, rmsnorm.rs:49-63 */
+typedef struct tb_norm_linear_args {
+  const void* x;             /* [m,k] device */
+  tb_dtype x_dtype;
+  const float* norm_weight;  /* [k] device, nullable */
+  float norm_eps;
+  uint32_t norm_flags;
+  const float* residual;     /* [m,n] device fp32, nullable; may alias y only when y is fp32 */
+  uint32_t m;
+  void* y;                   /* [m,n] device */
+  tb_dtype y_dtype;
+  uint32_t flags;            /* TB_FWD_PDL, TB_FWD_FORCE_DECODE, TB_FWD_FORCE_PREFILL */
+  void* stream;
+} tb_norm_linear_args;
+tb_status tb_norm_linear_forward_dev(tb_backend* backend, const tb_weights* weights,
+                                     const tb_norm_linear_args* args, tb_receipt* receipt);
 /* No counterpart in the reference: an int8-path forward (1..4 tokens, device pointers) for
  * callers that are not allowed to allocate device memory while they run — a serving loop whose
  * memory is fully planned up front, a latency-critical thread that must not enter the driver's

@@ -442,6 +442,27 @@ def salt_v1_forward_a8(planes: bytes, t_planes: int, n: int, k: int, act) -> np.
     return y * s[:, None]
 
 
+def rmsnorm(x, w, eps: float, zero_centered: bool = False) -> np.ndarray:
+    """rmsnorm / rmsnorm_zero_centered row by row (crates/tritium-nn/src/ops/rmsnorm.rs:43-94); x [m, k] f32."""
+    w = np.ascontiguousarray(w, np.float32)
+    x = np.ascontiguousarray(x, np.float32).reshape(-1, w.size)
+    out = np.zeros_like(x)
+    L = lib()
+    for t in range(x.shape[0]):
+        L.or_rmsnorm(_p(x[t]), _p(w), C.c_float(eps), C.c_int(int(zero_centered)), C.c_uint64(w.size), _p(out[t]))
+    return out
+
+
+def norm_a8_linear(tensor, x, norm_weight, eps: float, zero_centered: bool = False, residual=None):
+    """The decode block's fused step: rmsnorm, per-token int8 quantisation, packed linear, then
+    ``residual + y`` in one rounding (crates/tritium-cuda/kernels/decode.cu:533-640 for the
+    prologue, crates/tritium-cuda/kernels/tq2_0_add.cu:577-637 for the residual epilogue)."""
+    y = a8_linear(tensor, rmsnorm(x, norm_weight, eps, zero_centered), dump=False)[0]
+    if residual is not None:
+        y = (np.ascontiguousarray(residual, np.float32).reshape(y.shape) + y).astype(np.float32)
+    return y
+
+
 def reference_mpgemm(act, w, scales, m, n, k) -> np.ndarray:
     act = np.ascontiguousarray(act, np.float32)
     w = np.ascontiguousarray(w, np.int8)

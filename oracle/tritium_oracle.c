@@ -1038,6 +1038,29 @@ int or_salt_v1_matmul(const uint8_t* planes, uint32_t t_planes, uint64_t n, uint
   return OR_OK;
 }
 
+/* sum_squares_canonical: crates/tritium-nn/src/ops/rmsnorm.rs:20-34 (256 slots, slot t folds
+ * x[t], x[t+256], ... in ascending order; then a power-of-two tree part[t] += part[t+off]) */
+float or_sum_squares_canonical(const float* x, uint64_t n) {
+  float part[256];
+  for (int t = 0; t < 256; t++) part[t] = 0.0f;
+  for (uint64_t i = 0; i < n; i++) part[i % 256] += x[i] * x[i];
+  for (int off = 128; off > 0; off >>= 1)
+    for (int t = 0; t < off; t++) part[t] += part[t + off];
+  return part[0];
+}
+
+/* rmsnorm / rmsnorm_zero_centered: crates/tritium-nn/src/ops/rmsnorm.rs:43-94.  One row of n
+ * values; zero_centered selects the (1 + w) scale. */
+void or_rmsnorm(const float* x, const float* w, float eps, int zero_centered, uint64_t n, float* out) {
+  if (!n) return;
+  float mean_sq = or_sum_squares_canonical(x, n) / (float)n;
+  float inv = 1.0f / sqrtf(mean_sq + eps);
+  for (uint64_t i = 0; i < n; i++) {
+    float scale = zero_centered ? 1.0f + w[i] : w[i];
+    out[i] = x[i] * inv * scale;
+  }
+}
+
 /* reference_mpgemm: crates/tritium-core/src/reference.rs:25-55 */
 void or_reference_mpgemm(const float* act, const int8_t* w, const float* scale_n, uint64_t m,
                          uint64_t n, uint64_t k, float* out) {

@@ -156,6 +156,9 @@ int or_tq1_pack_row(const int8_t* trits, uint64_t k, const uint16_t* block_scale
 int or_tq1_unpack_row(const uint8_t* packed, uint64_t k, int8_t* trits_out, uint16_t* scales_out);
 int or_salt_v1_matmul(const uint8_t* planes, uint32_t t_planes, uint64_t n, uint64_t k, const float* act,
                       uint64_t m, float* out);
+/* crates/tritium-nn/src/ops/rmsnorm.rs:20-94 */
+float or_sum_squares_canonical(const float* x, uint64_t n);
+void or_rmsnorm(const float* x, const float* w, float eps, int zero_centered, uint64_t n, float* out);
 void or_reference_mpgemm(const float* act, const int8_t* w, const float* scale_n, uint64_t m,
                          uint64_t n, uint64_t k, float* out);
 /* crates/tritium-spec/src/lib.rs:266-318 (default host path) */

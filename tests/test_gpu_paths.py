@@ -238,3 +238,81 @@ def test_salt_v1_planes_match_the_reference_row_dot(backend, t_planes, m):
     assert np.all(np.abs(got_f32 - want_f32) <= 1e-4 * np.maximum(1.0, np.abs(want_f32)))
     with pytest.raises(errors.UnsupportedFormat):
         backend.upload_salt_v1(planes + planes[: len(planes) // t_planes], t_planes + 3, n, k)
+
+
+# ------------------------------------------------------------------ RMSNorm prologue, residual epilogue
+@pytest.mark.parametrize("codec", [SaltV2Codec.B3, SaltV2Codec.D2])
+@pytest.mark.parametrize("n,k,planes,m,x_bf16,zero_centered,with_residual", [
+    (192, 2560, 3, 1, False, False, True),     # one launch: the norm runs inside the decode kernel's table builder
+    (192, 2560, 2, 2, True, True, False),
+    (200, 768, 1, 3, False, True, True),
+    (192, 1280, 3, 4, True, False, True),
+    (96, 8192, 2, 4, False, False, True),      # large tables: norm kernel, preparation kernel, decode kernel
+    (160, 2560, 3, 6, False, True, True),      # two passes
+    (256, 1024, 2, 40, False, False, True),    # tensor-core kernel behind the norm kernel
+])
+def test_norm_linear_matches_the_reference_arithmetic(backend, codec, n, k, planes, m, x_bf16, zero_centered, with_residual):
+    """RMSNorm in the canonical reduction order, the int8 quantiser, the packed linear and
+    ``residual + y`` in one rounding.  Every float operation of the prologue is the reference's, so
+    the result must equal, bit for bit, the plain int8 forward of rows the oracle normalised, with
+    the residual added once in fp32; and it must agree with the oracle's whole chain."""
+    import torch
+    prod, orac = uniform_pair(n, k, planes, seed=91)
+    resident = backend.upload_salt_v2(prod, codec)
+    backend.reserve(resident, m)
+    rng = np.random.default_rng(5 + m)
+    x = make_activations(m, k, seed=17, bf16=x_bf16) * np.float32(3.7)
+    if x_bf16:
+        x = bf16_bits_to_f32(f32_to_bf16_bits(x))
+    w_norm = (rng.standard_normal(k) * 0.3 + (0.0 if zero_centered else 1.0)).astype(np.float32)
+    residual = rng.standard_normal((m, n)).astype(np.float32) if with_residual else None
+    eps = 1e-6
+    normed = orc.rmsnorm(x, w_norm, eps, zero_centered)
+    stream = torch.cuda.Stream()
+    x_dev = torch.from_numpy(x).cuda()
+    if x_bf16:
+        x_dev = x_dev.to(torch.bfloat16)
+    plain = torch.zeros(m, n, dtype=torch.float32, device="cuda")
+    got = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+    got_bf16 = torch.zeros(m, n, dtype=torch.bfloat16, device="cuda")
+    w_dev = torch.from_numpy(w_norm).cuda()
+    r_dev = torch.from_numpy(residual).cuda() if with_residual else None
+    with torch.cuda.stream(stream):
+        backend.forward_dev(resident, torch.from_numpy(normed).cuda(), plain, a8=True, stream=stream)
+        backend.norm_linear_forward_dev(resident, x_dev, got, norm_weight=w_dev, eps=eps, zero_centered=zero_centered,
+                                        residual=r_dev, stream=stream)
+        backend.norm_linear_forward_dev(resident, x_dev, got_bf16, norm_weight=w_dev, eps=eps, zero_centered=zero_centered,
+                                        residual=r_dev, stream=stream)
+    stream.synchronize()
+    backend.check(stream)
+    want = plain.cpu().numpy()
+    if with_residual:
+        want = (residual + want).astype(np.float32)
+    assert np.array_equal(got.cpu().numpy(), want)
+    assert np.array_equal(got_bf16.view(torch.int16).cpu().numpy().view(np.uint16), f32_to_bf16_bits(want))
+    chain = orc.norm_a8_linear(orac, x, w_norm, eps, zero_centered, residual)
+    plain_chain = orc.norm_a8_linear(orac, x, w_norm, eps, zero_centered, None)
+    # the tolerance belongs to the linear's output; the residual is added exactly once on both sides
+    assert rel_l2(got.cpu().numpy() - (residual if with_residual else 0), plain_chain) <= 1e-5
+    assert np.allclose(got.cpu().numpy(), chain, rtol=0, atol=1e-4 * float(np.abs(plain_chain).max()))
+
+
+def test_residual_epilogue_alone_and_argument_checks(backend):
+    import torch
+    n, k, m = 128, 1024, 2
+    prod, orac = uniform_pair(n, k, 3, seed=8)
+    resident = backend.upload_salt_v2(prod, SaltV2Codec.B3)
+    x = make_activations(m, k, seed=3, bf16=True)
+    residual = np.random.default_rng(1).standard_normal((m, n)).astype(np.float32)
+    x_dev = torch.from_numpy(x).cuda().to(torch.bfloat16)
+    y = torch.from_numpy(residual).cuda()          # residual aliases the fp32 output: x = x + linear(h)
+    plain = torch.zeros(m, n, dtype=torch.float32, device="cuda")
+    backend.forward_dev(resident, x_dev, plain, a8=True)
+    backend.norm_linear_forward_dev(resident, x_dev, y, residual=y)
+    torch.cuda.synchronize()
+    backend.check()
+    assert np.array_equal(y.cpu().numpy(), (residual + plain.cpu().numpy()).astype(np.float32))
+    with pytest.raises(errors.InvalidInput, match="non-negative"):
+        backend.norm_linear_forward_dev(resident, x_dev, y, norm_weight=torch.ones(k, device="cuda"), eps=float("nan"))
+    with pytest.raises(KeyError):
+        backend.norm_linear_forward_dev(resident, torch.zeros(m, k, dtype=torch.int8, device="cuda"), y)

@@ -517,3 +517,26 @@ def test_tq1_block_goldens():
     rng = np.random.default_rng(8)
     w = rng.integers(-1, 2, (5, 700)).astype(np.int8)
     assert np.array_equal(orc.tq1_unpack_rows(orc.tq1_pack_rows(w), 5, 700), w)
+
+
+def test_rmsnorm_known_answers_and_canonical_order():
+    """crates/tritium-nn/src/ops/rmsnorm.rs:101-110 (x = [3, 4], unit weights, eps 0: x / sqrt(12.5))
+    and the canonical reduction order of rmsnorm.rs:20-34 restated here in numpy, slot by slot."""
+    out = orc.rmsnorm(np.array([[3.0, 4.0]], np.float32), np.ones(2, np.float32), 0.0)
+    inv = np.float32(1.0) / np.sqrt(np.float32(12.5))
+    assert abs(out[0, 0] - np.float32(3.0) * inv) < 1e-6 and abs(out[0, 1] - np.float32(4.0) * inv) < 1e-6
+    rng = np.random.default_rng(12)
+    for n in (1, 255, 256, 257, 1000, 2560):
+        x = (rng.standard_normal(n) * 5).astype(np.float32)
+        w = rng.standard_normal(n).astype(np.float32)
+        part = np.zeros(256, np.float32)
+        for start in range(0, n, 256):                      # slot t folds x[t], x[t+256], ... ascending
+            chunk = x[start:start + 256]
+            part[:chunk.size] = part[:chunk.size] + chunk * chunk
+        off = 128
+        while off:
+            part[:off] = part[:off] + part[off:2 * off]
+            off >>= 1
+        inv = np.float32(1.0) / np.sqrt(part[0] / np.float32(n) + np.float32(1e-5))
+        assert np.array_equal(orc.rmsnorm(x[None], w, 1e-5)[0], x * inv * w)
+        assert np.array_equal(orc.rmsnorm(x[None], w, 1e-5, zero_centered=True)[0], x * inv * (np.float32(1.0) + w))

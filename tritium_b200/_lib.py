@@ -22,7 +22,7 @@ EXPORTS = [
     "tb_backend_synchronize", "tb_backend_reserve", "tb_backend_check", "tb_tq2_upload",
     "tb_salt_v2_upload", "tb_salt_v2_upload_package", "tb_weights_info_get", "tb_weights_free",
     "tb_salt_v2_forward_exact", "tb_linear_forward_f32", "tb_linear_forward_a8",
-    "tb_salt_v2_gather_rows", "tb_linear_forward_dev", "tb_act_absmax_dev",
+    "tb_salt_v2_gather_rows", "tb_linear_forward_dev", "tb_norm_linear_forward_dev", "tb_act_absmax_dev",
     "tb_linear_forward_tp_dev", "tb_comm_create", "tb_comm_export", "tb_comm_connect", "tb_comm_slot", "tb_comm_allreduce_f32", "tb_comm_free", "tb_mpgemm", "tb_mpgemm_with_act_quant",
     "tb_stack_create", "tb_stack_forward_dev", "tb_stack_forward_host", "tb_stack_bytes_per_step", "tb_stack_read_output", "tb_stack_free",
     "tb_tp_shard_sizes", "tb_tp_shard", "tb_fmt_pack", "tb_fmt_unpack", "tb_fmt_plane_bytes",
@@ -58,6 +58,14 @@ class ForwardArgs(C.Structure):
                 ("m", C.c_uint32), ("y", C.c_void_p), ("y_dtype", C.c_int), ("acc_dump", C.c_void_p),
                 ("row_scale", C.c_void_p), ("flags", C.c_uint32), ("stream", C.c_void_p)]
 
+
+class NormLinearArgs(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("x_dtype", C.c_int), ("norm_weight", C.c_void_p), ("norm_eps", C.c_float),
+                ("norm_flags", C.c_uint32), ("residual", C.c_void_p), ("m", C.c_uint32), ("y", C.c_void_p),
+                ("y_dtype", C.c_int), ("flags", C.c_uint32), ("stream", C.c_void_p)]
+
+
+TB_NORM_ZERO_CENTERED = 1
 
 READ_AT_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_uint64, C.c_void_p, C.c_size_t)
 
@@ -120,6 +128,7 @@ _SIGNATURES = {
     "tb_linear_forward_a8": (_ST, [_P, _P, _P, _I, _U32, _P, _I, _P, _P]),
     "tb_salt_v2_gather_rows": (_ST, [_P, _P, _P, _SZ, _P]),
     "tb_linear_forward_dev": (_ST, [_P, _P, _P, _P]),
+    "tb_norm_linear_forward_dev": (_ST, [_P, _P, _P, _P]),
     "tb_linear_forward_a8_static": (_ST, [_P, _P, _P, _I, _P, _U32, _P, _I, _P]),
     "tb_act_absmax_dev": (_ST, [_P, _P, _I, _U32, _U32, _P, _P]),
     "tb_backend_reserve": (_ST, [_P, _P, _U32]),

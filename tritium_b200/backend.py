@@ -319,6 +319,29 @@ class B200Backend:
         args.stream = s.cuda_stream
         check(self._L.tb_linear_forward_dev(self._h, t._h, C.byref(args), None))
 
+    def norm_linear_forward_dev(self, t, x, y, *, norm_weight=None, eps: float = 0.0, zero_centered: bool = False,
+                                residual=None, flags: int = 0, stream=None) -> None:
+        """RMSNorm -> int8 quantiser -> packed linear -> ``residual + y`` on device tensors, without synchronising.
+
+        The decode block's fused step (crates/tritium-cuda/kernels/decode.cu:533-640 in front,
+        crates/tritium-cuda/kernels/tq2_0_add.cu:577-637 behind).  ``norm_weight`` fp32 [k] or None,
+        ``residual`` fp32 [m, n] or None.
+        """
+        import torch
+        dt = {torch.float32: _lib.TB_F32, torch.bfloat16: _lib.TB_BF16}
+        args = _lib.NormLinearArgs()
+        args.x = x.data_ptr(); args.x_dtype = dt[x.dtype]
+        args.norm_weight = norm_weight.data_ptr() if norm_weight is not None else None
+        args.norm_eps = eps
+        args.norm_flags = _lib.TB_NORM_ZERO_CENTERED if zero_centered else 0
+        args.residual = residual.data_ptr() if residual is not None else None
+        args.m = x.shape[0] if x.dim() > 1 else 1
+        args.y = y.data_ptr(); args.y_dtype = dt[y.dtype]
+        args.flags = flags
+        s = stream if stream is not None else torch.cuda.current_stream()
+        args.stream = s.cuda_stream
+        check(self._L.tb_norm_linear_forward_dev(self._h, t._h, C.byref(args), None))
+
     def act_absmax_dev(self, x, out, stream=None) -> None:
         """Per-token max|x| of a [m, k] fp32/bf16 CUDA tensor into ``out`` (fp32 [m]); no sync."""
         import torch

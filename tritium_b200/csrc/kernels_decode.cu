@@ -51,7 +51,7 @@ constexpr int kConsumerThreads = kWarps * 32;
 constexpr int kMaxStages = 4;
 constexpr int kPartBufs = 4;   // row blocks whose partial sums may wait for the combiner
 constexpr int kMaxGroupLayers = 128;   // layers of one grouped launch (descriptors live in shared memory)
-constexpr uint32_t kBuildStagingBytes = 32 * 272 + 8 * 16;   // fused prologue: quantised activations of one pass of pairs, absmax partials
+constexpr uint32_t kBuildStagingBytes = 32 * 272 + 8 * 16 + 16;   // fused prologue: quantised activations of one pass of pairs, absmax partials, 1/rms per token
 
 struct DecodeParams {
   const uint8_t* payload; const uint16_t* scales;   // single layer (layers == nullptr)
@@ -59,6 +59,10 @@ struct DecodeParams {
   const uint8_t* tables; uint32_t table_bytes;   // z tables | accumulator start values | token scales
   // fused prologue (fused != 0): the CTA quantises x and builds its tables itself
   const void* x; const float* act_scale_in; const float* act_absmax_in; uint32_t x_dtype, fused;
+  // fused RMSNorm in front of the quantiser (fused launches only; null = none) and `residual + y`
+  // behind the token scale (fp32, indexed like y; null = none)
+  const float* norm_weight; float norm_eps; uint32_t norm_zero_centered;
+  const float* residual;
   void* y; int32_t* acc_dump; const float* row_scale;
   uint32_t* status;
   uint32_t m, n, k, planes, tpr;            // m: valid tokens; tpr = k / 256
@@ -503,6 +507,18 @@ __device__ __forceinline__ int sbyte(uint32_t w, int b) { return int(int8_t(w >>
 // aligned 32-bit words of the staged codes, every one of them inside a single scale group; their
 // transformed values z = x_t - 3 x_(t-1) (B3; x_t for D2), split as 4*high + low, are the table
 // words of that position.  Items are independent, so the whole CTA works on them at once.
+// y = (x * inv) * w (or (1 + w)) for eight consecutive columns: the reference's rmsnorm expression
+// (crates/tritium-nn/src/ops/rmsnorm.rs:88-91), one rounding per operation.
+__device__ __forceinline__ void apply_norm(const DecodeParams& p, float inv, uint32_t col, float (&v)[8]) {
+  float w[8];
+  load8(p.norm_weight, TB_F32, col, w);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const float scale = p.norm_zero_centered ? __fadd_rn(1.0f, w[e]) : w[e];
+    v[e] = __fmul_rn(__fmul_rn(v[e], inv), scale);
+  }
+}
+
 template <int CODEC, bool DUAL, int M>
 __device__ __forceinline__ void build_tables(const DecodeParams& p, uint8_t* smem, uint32_t tid) {
   constexpr int kNM = MmaCount<CODEC, DUAL>::value;
@@ -515,9 +531,46 @@ __device__ __forceinline__ void build_tables(const DecodeParams& p, uint8_t* sme
   uint32_t* ztab = reinterpret_cast<uint32_t*>(smem + p.off_z);
   int* cinit = reinterpret_cast<int*>(smem + p.off_cinit);
   float* act_scale = reinterpret_cast<float*>(smem + p.off_actscale);
-  if (tid < kChunkPairs) *reinterpret_cast<uint4*>(xq + tid * kPairStride + 256) = make_uint4(0, 0, 0, 0);
-  float scale_q[M], scale_out[M];
+  float scale_q[M], scale_out[M], inv_rms[M];
   const uint32_t pairs = p.tpr * M;
+  const bool norm = p.norm_weight != nullptr;
+#pragma unroll
+  for (int t = 0; t < M; ++t) inv_rms[t] = 1.f;
+  if (norm) {
+    // RMSNorm prologue, in the reference's canonical order (crates/tritium-nn/src/ops/rmsnorm.rs:20-34,
+    // crates/tritium-cuda/kernels/decode.cu:533-640): 256 slots, slot t folds x[t], x[t+256], ...
+    // ascending; then the power-of-two tree part[t] += part[t+off].  The 256 consumer threads are
+    // the 256 slots.  The staging area is free until the quantise phase.
+    float* part = reinterpret_cast<float*>(xq);
+    float* inv_s = red + kWarps * 4;
+#pragma unroll
+    for (int t = 0; t < M; ++t) {
+      if (uint32_t(t) >= p.m) break;
+      float acc = 0.f;
+      for (uint32_t i = tid; i < p.k; i += kConsumerThreads) {
+        const size_t at = size_t(t) * p.k + i;
+        const float v = p.x_dtype == TB_F32 ? static_cast<const float*>(p.x)[at]
+                                            : __bfloat162float(static_cast<const __nv_bfloat16*>(p.x)[at]);
+        acc = __fadd_rn(acc, __fmul_rn(v, v));
+      }
+      part[tid] = acc;
+      consumer_sync();
+      if (tid < 128) part[tid] = __fadd_rn(part[tid], part[tid + 128]);
+      consumer_sync();
+      if (tid < 64) part[tid] = __fadd_rn(part[tid], part[tid + 64]);
+      consumer_sync();
+      if (tid < 32) {
+        float v = __fadd_rn(part[tid], part[tid + 32]);
+        for (int o = 16; o; o >>= 1) v = __fadd_rn(v, __shfl_down_sync(0xffffffffu, v, o));   // lane t pairs with t + o
+        if (tid == 0) inv_s[t] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(v, float(p.k)), p.norm_eps)));
+      }
+      consumer_sync();
+    }
+#pragma unroll
+    for (int t = 0; t < M; ++t) inv_rms[t] = uint32_t(t) < p.m ? inv_s[t] : 1.f;
+    consumer_sync();   // the slots turn back into staging
+  }
+  if (tid < kChunkPairs) *reinterpret_cast<uint4*>(xq + tid * kPairStride + 256) = make_uint4(0, 0, 0, 0);
   if (p.x_dtype == TB_I8) {
 #pragma unroll
     for (int t = 0; t < M; ++t) { scale_q[t] = 1.f; scale_out[t] = uint32_t(t) < p.m ? p.act_scale_in[t] : 0.f; }
@@ -529,6 +582,7 @@ __device__ __forceinline__ void build_tables(const DecodeParams& p, uint8_t* sme
         for (uint32_t i = tid * 8; i < p.k && uint32_t(t) < p.m; i += kConsumerThreads * 8) {
           float v[8];
           load8(p.x, p.x_dtype, size_t(t) * p.k + i, v);
+          if (norm) apply_norm(p, inv_rms[t], i, v);
 #pragma unroll
           for (int e = 0; e < 8; ++e) mx = fmaxf(mx, fabsf(v[e]));
         }
@@ -559,9 +613,10 @@ __device__ __forceinline__ void build_tables(const DecodeParams& p, uint8_t* sme
       if (t >= p.m) continue;   // table entries of absent tokens are never read for an output
       float v[8];
       load8(p.x, p.x_dtype, size_t(t) * p.k + j * 256 + lane * 8, v);
-      float sq = scale_q[0];
+      float sq = scale_q[0], inv = inv_rms[0];
 #pragma unroll
-      for (int tt = 1; tt < M; ++tt) sq = t == uint32_t(tt) ? scale_q[tt] : sq;
+      for (int tt = 1; tt < M; ++tt) { sq = t == uint32_t(tt) ? scale_q[tt] : sq; inv = t == uint32_t(tt) ? inv_rms[tt] : inv; }
+      if (norm) apply_norm(p, inv, j * 256 + lane * 8, v);
       int q[8];
       bool bad = false;
 #pragma unroll
@@ -763,6 +818,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
         float out = __fmul_rn(sum, act_scale[t]);
         if (p.row_scale) out = __fmul_rn(out, p.row_scale[row0 + r]);
         const size_t idx = size_t(layer) * p.y_layer_stride + size_t(t) * p.y_row_stride + row0 + r;
+        if (p.residual) out = __fadd_rn(p.residual[idx], out);   // crates/tritium-cuda/kernels/tq2_0_add.cu:577-637
         if (p.y_dtype == TB_F32) static_cast<float*>(p.y)[idx] = out;
         else static_cast<__nv_bfloat16*>(p.y)[idx] = __float2bfloat16_rn(out);
       }
@@ -1146,9 +1202,14 @@ cudaError_t tb_launch_decode(const DecodeArgs& a, int sm_count, int max_smem, cu
     if (!a.x || (reinterpret_cast<uintptr_t>(a.x) & 15u) || a.comm_absmax) return cudaErrorInvalidValue;
     if (a.x_dtype == TB_I8 && !a.act_scale_in) return cudaErrorInvalidValue;
     p.fused = 1; p.x = a.x; p.act_scale_in = a.act_scale_in; p.act_absmax_in = a.act_absmax_in; p.x_dtype = uint32_t(a.x_dtype);
-  } else if (!a.scratch || a.scratch_bytes < tl.total) {
-    return cudaErrorInvalidValue;
+    if (a.norm_weight) {
+      if (a.x_dtype == TB_I8 || (reinterpret_cast<uintptr_t>(a.norm_weight) & 15u)) return cudaErrorInvalidValue;
+      p.norm_weight = a.norm_weight; p.norm_eps = a.norm_eps; p.norm_zero_centered = a.norm_zero_centered ? 1u : 0u;
+    }
+  } else if (!a.scratch || a.scratch_bytes < tl.total || a.norm_weight) {
+    return cudaErrorInvalidValue;   // the norm prologue lives in the fused builder; other launches take normalised input
   }
+  p.residual = a.residual;
   cudaLaunchAttribute attr[2];
   unsigned num_attrs = 0;
   if (a.pdl) {

@@ -237,6 +237,39 @@ __global__ void __launch_bounds__(256) row_absmax_kernel(const void* x, uint32_t
   }
 }
 
+// RMSNorm of one token's row per CTA, in the reference's canonical order
+// (crates/tritium-nn/src/ops/rmsnorm.rs:20-94): the 256 threads are the 256 slots, slot t folds
+// x[t], x[t+256], ... ascending, then the power-of-two tree; out = (x * inv) * w, or (1 + w).
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const void* x, uint32_t dtype, const float* weight, float eps,
+                                                      uint32_t zero_centered, uint32_t k, float* out) {
+  __shared__ float part[256];
+  __shared__ float inv_s;
+  const uint32_t t = blockIdx.x, tid = threadIdx.x;
+  const auto at = [&](uint32_t i) {
+    const size_t idx = size_t(t) * k + i;
+    return dtype == TB_F32 ? static_cast<const float*>(x)[idx] : __bfloat162float(static_cast<const __nv_bfloat16*>(x)[idx]);
+  };
+  float acc = 0.f;
+  for (uint32_t i = tid; i < k; i += 256) { const float v = at(i); acc = __fadd_rn(acc, __fmul_rn(v, v)); }
+  part[tid] = acc;
+  __syncthreads();
+  for (uint32_t off = 128; off >= 32; off >>= 1) {
+    if (tid < off) part[tid] = __fadd_rn(part[tid], part[tid + off]);
+    __syncthreads();
+  }
+  if (tid < 32) {
+    float v = part[tid];
+    for (int o = 16; o; o >>= 1) v = __fadd_rn(v, __shfl_down_sync(0xffffffffu, v, o));
+    if (tid == 0) inv_s = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(v, float(k)), eps)));
+  }
+  __syncthreads();
+  const float inv = inv_s;
+  for (uint32_t i = tid; i < k; i += 256) {
+    const float scale = zero_centered ? __fadd_rn(1.0f, weight[i]) : weight[i];
+    out[size_t(t) * k + i] = __fmul_rn(__fmul_rn(at(i), inv), scale);
+  }
+}
+
 ExactParams make_params(const tb_weights* w) {
   ExactParams p{};
   p.payload = w->d_payload; p.scales = w->d_scales; p.meta = w->d_meta; p.tile_rank = w->d_tile_rank;
@@ -270,6 +303,13 @@ cudaError_t tb_launch_gather_rows(const tb_weights* w, const uint32_t* rows, uin
 cudaError_t tb_launch_row_absmax(const void* x, tb_dtype dtype, uint32_t m, uint32_t k, float* out, cudaStream_t stream) {
   if (!m) return cudaSuccess;
   row_absmax_kernel<<<m, 256, 0, stream>>>(x, uint32_t(dtype), k, out);
+  return cudaGetLastError();
+}
+
+cudaError_t tb_launch_rmsnorm(const void* x, tb_dtype dtype, const float* weight, float eps, bool zero_centered, uint32_t m,
+                              uint32_t k, float* out, cudaStream_t stream) {
+  if (!m) return cudaSuccess;
+  rmsnorm_kernel<<<m, 256, 0, stream>>>(x, uint32_t(dtype), weight, eps, zero_centered ? 1u : 0u, k, out);
   return cudaGetLastError();
 }
 

@@ -51,7 +51,7 @@ constexpr uint32_t kTileABytes = kRows * 128;
 struct PrefillParams {
   const uint8_t* payload; const uint16_t* scales;
   const int8_t* qperm; const int32_t* qinit; const float* ascale;   // scratch from the pre-pass
-  void* y; int32_t* acc_dump; const float* row_scale;
+  void* y; int32_t* acc_dump; const float* row_scale; const float* residual;
   uint32_t* status;
   uint32_t m, m_pad, n, k, tpr, y_dtype;
   uint32_t n_tiles, m_tiles;
@@ -574,6 +574,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
                       float out = __fmul_rn(__uint_as_float(yv[i]), __ldg(p.ascale + mtok));
                       if (p.row_scale) out = __fmul_rn(out, rs);
                       const size_t idx = size_t(mtok) * p.n + n;
+                      if (p.residual) out = __fadd_rn(__ldg(p.residual + idx), out);
                       if (p.y_dtype == TB_F32) static_cast<float*>(p.y)[idx] = out;
                       else static_cast<__nv_bfloat16*>(p.y)[idx] = __float2bfloat16_rn(out);
                     }
@@ -694,7 +695,7 @@ cudaError_t tb_launch_prefill(const PrefillArgs& a, int sm_count, cudaStream_t s
   PrefillParams pp{};
   pp.payload = w->d_payload; pp.scales = w->d_scales;
   pp.qperm = sc.qperm; pp.qinit = sc.qinit; pp.ascale = sc.ascale;
-  pp.y = a.y; pp.acc_dump = a.acc_dump; pp.row_scale = a.row_scale; pp.status = a.status;
+  pp.y = a.y; pp.acc_dump = a.acc_dump; pp.row_scale = a.row_scale; pp.status = a.status; pp.residual = a.residual;
   pp.m = a.m; pp.m_pad = m_pad; pp.n = uint32_t(w->n); pp.k = k; pp.tpr = k / 256; pp.y_dtype = uint32_t(a.y_dtype);
   pp.n_tiles = (pp.n + kRows - 1) / kRows; pp.m_tiles = m_pad / tile_tokens;
   const size_t smem = 1024 + size_t(kStagesA) * kTileABytes + size_t(kStagesB) * 2 * tile_tokens * 128 + size_t(kStagesB) * 2 * tile_tokens * 4 +

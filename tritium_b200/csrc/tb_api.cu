@@ -114,7 +114,7 @@ extern "C" void tb_backend_free(tb_backend* b) {
   cudaSetDevice(b->ordinal);
   if (b->stream) { cudaStreamSynchronize(b->stream); cudaStreamDestroy(b->stream); }
   cudaFree(b->d_status); cudaFreeHost(b->h_status);
-  cudaFree(b->d_x); cudaFree(b->d_y); cudaFree(b->d_aux); cudaFree(b->d_q); cudaFree(b->d_prep); cudaFreeHost(b->h_pin);
+  cudaFree(b->d_x); cudaFree(b->d_y); cudaFree(b->d_aux); cudaFree(b->d_q); cudaFree(b->d_prep); cudaFree(b->d_norm); cudaFreeHost(b->h_pin);
   delete b;
 }
 
@@ -329,11 +329,21 @@ tb_status check_handles(const tb_backend* b, const tb_weights* w) {
   return TB_OK;
 }
 
+// What a decode block wraps around the linear: RMSNorm in front of the quantiser, residual behind.
+struct BlockExtras {
+  const float* norm_weight = nullptr; float norm_eps = 0.f; bool norm_zero_centered = false;
+  const float* residual = nullptr;
+};
+
 // Device-pointer dispatch shared by every entry point.  Returns the kernel family used.
-tb_status forward_dev(tb_backend* b, const tb_weights* w, const tb_forward_args& a, cudaStream_t st, tb_receipt* receipt) {
+tb_status forward_dev(tb_backend* b, const tb_weights* w, const tb_forward_args& a_in, cudaStream_t st, tb_receipt* receipt,
+                      const BlockExtras& ex = BlockExtras{}) {
+  tb_forward_args a = a_in;
   if (a.m == 0 || w->n == 0) { fill_receipt(w, 0, 0, 0, 0, 0, receipt); return TB_OK; }
   if (!a.x || !a.y) return tb_fail(TB_NULL_ARG, "null activation or output pointer");
   const bool a8 = (a.flags & TB_FWD_A8) != 0 || a.x_dtype == TB_I8;
+  if ((ex.norm_weight || ex.residual) && !a8) return tb_fail(TB_INVALID_INPUT, "the norm and residual steps belong to the int8 path");
+  if (ex.norm_weight && a.x_dtype == TB_I8) return tb_fail(TB_INVALID_INPUT, "RMSNorm takes fp32 or bf16 activations");
   if (!a8) {
     if (a.x_dtype != TB_F32 || a.y_dtype != TB_F32) return tb_fail(TB_INVALID_INPUT, "the fp32 path takes fp32 activations and outputs");
     ExactArgs e{w, static_cast<const float*>(a.x), static_cast<float*>(a.y), a.m, a.row_scale, b->d_status};
@@ -347,13 +357,31 @@ tb_status forward_dev(tb_backend* b, const tb_weights* w, const tb_forward_args&
   if (!w->fast) return tb_fail(TB_UNSUPPORTED_FORMAT, "the int8 path needs uniform plane counts, k % 256 == 0, group 128 and codec D2 or B3");
   // measured crossover on C2: four chained 4-token decode passes (about 51 us) still beat one tensor-core call (67 us)
   const bool want_prefill = (a.flags & TB_FWD_FORCE_PREFILL) || (a.m > 16 && !(a.flags & TB_FWD_FORCE_DECODE));
+  uint32_t extra_launches = 0;
+  // The decode kernel normalises inside its table builder.  Every other route (the tensor-core
+  // kernel, tables from the preparation kernel) takes rows normalised by a kernel of its own; the
+  // arithmetic is the same, so the codes are too.
+  const auto normalise = [&](uint32_t m0, uint32_t mc) -> tb_status {
+    if (tb_status s = ensure(&b->d_norm, &b->d_norm_cap, size_t(a.m) * w->k * 4)) return s;
+    float* dst = static_cast<float*>(b->d_norm) + size_t(m0) * w->k;
+    const uint8_t* src = static_cast<const uint8_t*>(a_in.x) + size_t(m0) * w->k * dtype_size(a_in.x_dtype);
+    TB_CUDA(tb_launch_rmsnorm(src, a_in.x_dtype, ex.norm_weight, ex.norm_eps, ex.norm_zero_centered, mc, uint32_t(w->k), dst, st),
+            "launch rmsnorm");
+    ++extra_launches;
+    return TB_OK;
+  };
   if (want_prefill && tb_prefill_supported(w, a.m)) {
     const size_t need = tb_prefill_scratch_bytes(w, a.m);
     if (b->d_q_cap < need) return tb_fail(TB_OUT_OF_MEMORY, "prefill scratch is not reserved; call through a host entry point or tb_stack first");
+    if (ex.norm_weight) {
+      if (tb_status s = normalise(0, a.m)) return s;
+      a.x = b->d_norm; a.x_dtype = TB_F32;
+    }
     PrefillArgs pa{w, a.x, a.x_dtype, a.act_scale, a.act_absmax, a.m, a.y, a.y_dtype, a.acc_dump, a.row_scale,
                    b->d_q, b->d_q_cap, b->d_status};
+    pa.residual = ex.residual;
     TB_CUDA(tb_launch_prefill(pa, b->prop.multiProcessorCount, st), "launch prefill");
-    fill_receipt(w, a.m, dtype_size(a.x_dtype), dtype_size(a.y_dtype), 2, 2, receipt);
+    fill_receipt(w, a.m, dtype_size(a_in.x_dtype), dtype_size(a.y_dtype), 2, 2 + extra_launches, receipt);
     return TB_OK;
   }
   if (a.flags & TB_FWD_FORCE_PREFILL) return tb_fail(TB_UNSUPPORTED_FORMAT, "the prefill kernel does not take this shape");
@@ -363,12 +391,22 @@ tb_status forward_dev(tb_backend* b, const tb_weights* w, const tb_forward_args&
   // kernel into the backend's scratch (see tb_decode_builds_tables).
   for (uint32_t m0 = 0; m0 < a.m; m0 += 4) {
     const uint32_t mc = std::min<uint32_t>(4, a.m - m0);
-    const bool fused = tb_decode_builds_tables(w, mc, a.x);
+    const bool fused = tb_decode_builds_tables(w, mc, a.x) &&
+                       (!ex.norm_weight || (reinterpret_cast<uintptr_t>(ex.norm_weight) & 15u) == 0);
     if (!tb_decode_supported(w, mc, b->max_smem_optin, nullptr))
       return tb_fail(TB_UNSUPPORTED_FORMAT, "the decode kernel's shared-memory plan does not fit this shape");
     DecodeArgs d{};
     d.w = w; d.x_dtype = a.x_dtype; d.m = mc; d.y_dtype = a.y_dtype; d.y_row_stride = uint32_t(w->n);
     d.x = static_cast<const uint8_t*>(a.x) + size_t(m0) * w->k * dtype_size(a.x_dtype);
+    if (ex.norm_weight) {
+      if (fused) {
+        d.norm_weight = ex.norm_weight; d.norm_eps = ex.norm_eps; d.norm_zero_centered = ex.norm_zero_centered;
+      } else {
+        if (tb_status s = normalise(m0, mc)) return s;
+        d.x = static_cast<const float*>(b->d_norm) + size_t(m0) * w->k; d.x_dtype = TB_F32;
+      }
+    }
+    d.residual = ex.residual ? ex.residual + size_t(m0) * w->n : nullptr;
     d.act_scale_in = a.act_scale ? a.act_scale + m0 : nullptr;
     d.act_absmax_in = a.act_absmax ? a.act_absmax + m0 : nullptr;
     d.y = static_cast<uint8_t*>(a.y) + size_t(m0) * w->n * dtype_size(a.y_dtype);
@@ -383,7 +421,7 @@ tb_status forward_dev(tb_backend* b, const tb_weights* w, const tb_forward_args&
     TB_CUDA(tb_launch_decode(d, b->prop.multiProcessorCount, b->max_smem_optin, st), "launch decode");
     ++launches;
   }
-  fill_receipt(w, a.m, dtype_size(a.x_dtype), dtype_size(a.y_dtype), 1, launches, receipt);
+  fill_receipt(w, a.m, dtype_size(a.x_dtype), dtype_size(a.y_dtype), 1, launches + extra_launches, receipt);
   return TB_OK;
 }
 
@@ -479,6 +517,25 @@ extern "C" tb_status tb_linear_forward_dev(tb_backend* b, const tb_weights* w, c
   if (tb_status s = use_device(b)) return s;
   cudaStream_t st = args->stream ? static_cast<cudaStream_t>(args->stream) : b->stream;
   return forward_dev(b, w, *args, st, receipt);
+}
+
+extern "C" tb_status tb_norm_linear_forward_dev(tb_backend* b, const tb_weights* w, const tb_norm_linear_args* args, tb_receipt* receipt) {
+  clear_error();
+  if (tb_status s = check_handles(b, w)) return s;
+  if (!args) return tb_fail(TB_NULL_ARG, "args is null");
+  if (args->x_dtype != TB_F32 && args->x_dtype != TB_BF16) return tb_fail(TB_INVALID_INPUT, "activations must be fp32 or bf16");
+  if (args->norm_flags & ~TB_NORM_ZERO_CENTERED) return tb_fail(TB_INVALID_INPUT, "unknown norm flag");
+  if (args->norm_weight && !(args->norm_eps >= 0.f)) return tb_fail(TB_INVALID_INPUT, "norm_eps must be a non-negative number");
+  if (tb_status s = use_device(b)) return s;
+  cudaStream_t st = args->stream ? static_cast<cudaStream_t>(args->stream) : b->stream;
+  tb_forward_args a{};
+  a.x = args->x; a.x_dtype = args->x_dtype; a.m = args->m; a.y = args->y; a.y_dtype = args->y_dtype;
+  a.flags = args->flags | TB_FWD_A8; a.stream = args->stream;
+  if (a.m > 16 && !(a.flags & TB_FWD_FORCE_DECODE)) if (tb_status s = reserve_prefill(b, w, a.m)) return s;
+  BlockExtras ex;
+  ex.norm_weight = args->norm_weight; ex.norm_eps = args->norm_eps;
+  ex.norm_zero_centered = (args->norm_flags & TB_NORM_ZERO_CENTERED) != 0; ex.residual = args->residual;
+  return forward_dev(b, w, a, st, receipt, ex);
 }
 
 extern "C" tb_status tb_act_absmax_dev(tb_backend* b, const void* x, tb_dtype x_dtype, uint32_t m, uint32_t k, float* out, void* stream) {

@@ -39,6 +39,8 @@ struct tb_backend {
   void* d_q = nullptr; size_t d_q_cap = 0;
   // scratch for the decode path: activation tables built by the prepare kernel
   void* d_prep = nullptr; size_t d_prep_cap = 0;
+  // normalised activations, for norm+linear calls whose tables the decode kernel does not build itself
+  void* d_norm = nullptr; size_t d_norm_cap = 0;
   int max_smem_optin = 0;
   uint32_t inject_missing_tx = 0;   // test hook: armed by tb_backend_inject_wait_timeout, used once
 };
@@ -85,6 +87,9 @@ struct ExactArgs {
 cudaError_t tb_launch_exact(const ExactArgs& a, cudaStream_t stream);
 cudaError_t tb_launch_gather_rows(const tb_weights* w, const uint32_t* rows, uint32_t count, float* out,
                                   cudaStream_t stream);
+// RMSNorm of m rows of k values into fp32 `out` (canonical 256-slot reduction order).
+cudaError_t tb_launch_rmsnorm(const void* x, tb_dtype dtype, const float* weight, float eps, bool zero_centered, uint32_t m,
+                              uint32_t k, float* out, cudaStream_t stream);
 cudaError_t tb_launch_row_absmax(const void* x, tb_dtype dtype, uint32_t m, uint32_t k, float* out, cudaStream_t stream);
 cudaError_t tb_launch_check_finite(const float* x, uint64_t count, uint32_t* status, cudaStream_t stream);
 
@@ -124,6 +129,10 @@ struct DecodeArgs {
   // through `comm_absmax`.  Null = no peers.
   const TbCommView* comm_absmax;
   uint32_t inject_missing_tx;   // test hook (non-fused launches): the table barrier expects this many bytes too many
+  // fused launches: RMSNorm over each token's row in front of the quantiser (weight [k] fp32,
+  // 16-byte aligned; null = none).  Any launch: out = residual + y (fp32, indexed like y).
+  const float* norm_weight; float norm_eps; bool norm_zero_centered;
+  const float* residual;
 };
 cudaError_t tb_launch_prepare(const DecodeArgs& a, cudaStream_t stream);
 // Whether a decode launch of `m` tokens should build its activation tables itself (one launch)
@@ -145,6 +154,7 @@ struct PrefillArgs {
   const float* row_scale;
   void* scratch; size_t scratch_bytes;   // permuted int8 activations, slab start values, token scales
   uint32_t* status;
+  const float* residual = nullptr;       // [m][n] fp32, nullable: out = residual + y
 };
 bool tb_prefill_supported(const tb_weights* w, uint32_t m);
 size_t tb_prefill_scratch_bytes(const tb_weights* w, uint32_t m);
