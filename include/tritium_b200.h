@@ -301,14 +301,36 @@ tb_status tb_comm_export(const tb_comm* comm, uint8_t* handle_out /* TB_COMM_HAN
 tb_status tb_comm_connect(tb_comm* comm, const uint8_t* all_handles /* world x TB_COMM_HANDLE_BYTES */);
 void* tb_comm_slot(const tb_comm* comm, uint32_t slot);
 tb_status tb_comm_allreduce_f32(tb_comm* comm, uint32_t slot, uint32_t count, int op_max, float* out, void* stream);
-/* Row-parallel int8 forward (1..8 tokens): the activation-preparation kernel exchanges the
- * per-token absmax through `slot_absmax` (so that every shard quantises with the scale of the whole
- * row), the GEMV kernel writes its fp32 partial rows into `slot_y`, and one tb_comm_allreduce_f32
- * launch adds the ranks' rows in rank order into `y` (fp32; every rank ends with the full
- * result).  `flags` must be 0.  The two slots belong to this linear alone. */
+/* Row-parallel int8 forward (1..8 tokens, at most four per launch), with both exchanges inside
+ * the kernels:
+ *   - the per-token absmax, so that every shard quantises with the scale of the whole row: each
+ *     rank pushes its slice's value, tagged with the round number, into the peers' copies of
+ *     `slot_absmax` and finds the peers' values in its own memory (small activation tables: inside
+ *     the decode kernel's table builder; large ones: in the preparation kernel);
+ *   - the output sum: every CTA pushes its fp32 partial rows into all ranks' copies of `slot_y`,
+ *     signals the row block's arrival counter on each peer, and, once the peers' partials of the
+ *     block have arrived, adds them in rank order and stores `y` (fp32 or bf16; every rank ends
+ *     with the same bits of the full result).
+ * So a row-parallel linear with small tables is ONE launch.  Only plain peer stores and loads
+ * are used.  `slot_y` must hold 2 x world x min(m,4) x n fp32 values, `slot_absmax` 1 KiB, and
+ * the communicator 4 + (row blocks of the tensor) counters per slot.  flags: 0 or TB_FWD_PDL.
+ * Every rank must make the same call (same m) on its shard; the two slots belong to this linear
+ * alone; use tb_comm_allreduce_f32 on them only after every rank has gone idle (a host barrier).  After a TB_TIMEOUT the
+ * round counters of the ranks no longer agree: free the communicator and build a new one. */
 tb_status tb_linear_forward_tp_dev(tb_backend* backend, const tb_weights* weights, tb_comm* comm, uint32_t slot_absmax,
                                    uint32_t slot_y, const void* x, tb_dtype x_dtype, uint32_t m, void* y, tb_dtype y_dtype,
                                    uint32_t flags, void* stream);
+/* Bound of every wait on a peer, in SM clock cycles (default 4e9, about two seconds).  A wait
+ * that runs out sets the backend's status word (TB_TIMEOUT at the next tb_backend_check) and the
+ * kernel returns; nothing traps. */
+tb_status tb_comm_set_wait_limit(tb_comm* comm, uint64_t sm_cycles);
+/* Teardown across ranks, in this order: (1) every rank synchronises its device and meets the
+ * others at a host barrier, so that no kernel anywhere still reads or writes peer memory;
+ * (2) every rank calls tb_comm_disconnect, which unmaps the peers' buffers; (3) a second host
+ * barrier; (4) tb_comm_free releases this rank's buffer.  Freeing a buffer that a peer still has
+ * mapped, or is still reading, is an error the library cannot detect.  tb_comm_free alone
+ * performs (2) and (4) for this rank and is enough for world == 1. */
+tb_status tb_comm_disconnect(tb_comm* comm);
 void tb_comm_free(tb_comm* comm);
 
 /* ------------------------------------------------------------------ tensor-parallel sharding (host)

@@ -37,11 +37,13 @@ def rank_main(rank, world, port, codec_value, use_peer, results):
     try:
         codec = SaltV2Codec(codec_value)
         backend = B200Backend(rank)
-        comm = tp.PeerComm(backend, rank, world, slot_bytes=64 * 384 * 4, slots=8) if use_peer else None
-        ex = tp.CudaExecutor(backend, comm=comm)
+        from tritium_b200 import _lib
+        comm = tp.PeerComm(backend, rank, world, slot_bytes=64 * 384 * 4, slots=10) if use_peer else None
+        ex = tp.CudaExecutor(backend, comm=comm, flags=_lib.TB_FWD_PDL if use_peer == 3 else 0)
         stream = torch.cuda.Stream()
         out = {}
-        for m, n, k, planes in [(3, 256, 1024, 2), (7, 200, 1536, 3), (40, 384, 2048, 1)]:   # decode kernel (one and two passes), tensor-core kernel
+        # decode kernel with its own tables (one and two passes), tables from the preparation kernel, tensor-core kernel
+        for m, n, k, planes in [(3, 256, 1024, 2), (7, 200, 1536, 3), (4, 256, 8192, 2), (40, 384, 2048, 1)]:
             tensor = make_tensor("w", n, k, planes, seed=11 + m)
             x = make_activations(m, k, seed=5, bf16=True)
             otensor = orc.Tensor(n, k, 128, tensor.plane_count.copy(), tensor.trits.copy(), tensor.scales.copy())
@@ -54,21 +56,90 @@ def rank_main(rank, world, port, codec_value, use_peer, results):
                 g = row.geometry
                 row.input_view(m).copy_(torch.from_numpy(np.ascontiguousarray(x[:, g.k_offset:g.k_offset + g.k_valid])).to(torch.bfloat16))
                 assert (row.comm is not None) == bool(use_peer)
-                row.fused = use_peer == 2
+                row.fused = use_peer >= 2
                 for _ in range(3):          # repeated rounds on the same slots
                     y_row = row.forward(m)
                 stream.synchronize()
                 backend.check(stream)
+                # every rank must hold the same bits of the reduced rows
+                bits = [torch.zeros_like(y_row) for _ in range(world)]
+                dist.all_gather(bits, y_row.contiguous())
+                stream.synchronize()
+                assert all(torch.equal(bits[0], b) for b in bits), (m, "ranks disagree on the reduced rows")
             gc = col.geometry
             # the in-kernel exchange keeps the row absmax to itself; the output parity covers it
             absmax_ok = (use_peer >= 2 and m <= 8) or bool(np.array_equal(row.absmax[:m].cpu().numpy(), np.abs(x).max(axis=1)))
             out[m] = (rel_l2(y_col.cpu().numpy(), want[:, gc.n_offset:gc.n_offset + gc.n]), rel_l2(y_row.cpu().numpy(), want), absmax_ok)
         results[rank] = out
+        if comm is not None:
+            comm.close()
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("use_peer", [0, 1, 2], ids=["nccl", "peer_one_shot", "peer_absmax_in_kernel"])
+def timeout_main(rank, world, port, in_kernel, results):
+    """Rank 1 leaves one exchange out.  Rank 0's wait has a short limit: its kernel returns by
+    itself, the status word says so, and both contexts stay usable.  Nothing is in flight on the
+    rank that stays away, and nothing traps or faults."""
+    import torch.distributed as dist
+    from tritium_b200 import B200Backend, errors, tp
+    from tritium_b200.format import SaltV2Codec
+    from tritium_b200.synth import make_activations, make_tensor
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        backend = B200Backend(rank)
+        comm = tp.PeerComm(backend, rank, world, slot_bytes=64 * 256 * 4, slots=4)
+        comm.set_wait_limit(200_000_000)             # about a tenth of a second of SM clocks
+        ex = tp.CudaExecutor(backend, comm=comm)
+        m, n, k = 2, 256, 1024
+        tensor = make_tensor("w", n, k, 2, seed=3)
+        x = make_activations(m, k, seed=5, bf16=True)
+        row = tp.TPLinear(ex, tensor, SaltV2Codec.B3, "row", rank, world, max_m=m)
+        g = row.geometry
+        row.input_view(m).copy_(torch.from_numpy(np.ascontiguousarray(x[:, g.k_offset:g.k_offset + g.k_valid])).to(torch.bfloat16))
+        row.fused = bool(in_kernel)
+        first = row.forward(m).clone()                # a complete round on both ranks
+        torch.cuda.synchronize()
+        backend.check()
+        dist.barrier()
+        outcome = "ok"
+        if rank == 0:
+            row.forward(m)                            # the peer never joins this round
+            torch.cuda.synchronize()
+            try:
+                backend.check()
+            except errors.Timeout:
+                outcome = "timeout"
+        dist.barrier()
+        # the context still runs kernels: a linear without peers gives the same result twice
+        single = tp.TPLinear(tp.CudaExecutor(backend), tensor, SaltV2Codec.B3, "column", 0, 1, max_m=m)
+        single.input_view(m).copy_(torch.from_numpy(x).to(torch.bfloat16))
+        a = single.forward(m).clone()
+        b = single.forward(m)
+        torch.cuda.synchronize()
+        backend.check()
+        results[rank] = (outcome, bool(torch.equal(a, b)), bool(torch.isfinite(first).all()))
+        comm.close()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("in_kernel", [0, 1], ids=["one_shot_reduce", "in_kernel_exchange"])
+def test_two_gpu_wait_on_an_absent_peer_runs_out(in_kernel):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    with mp.Manager() as manager:
+        results = manager.dict()
+        mp.spawn(timeout_main, args=(2, free_port(), in_kernel, results), nprocs=2, join=True)
+        assert results[0] == ("timeout", True, True), results[0]
+        assert results[1] == ("ok", True, True), results[1]
+
+
+@pytest.mark.parametrize("use_peer", [0, 1, 2, 3], ids=["nccl", "peer_one_shot", "peer_in_kernel", "peer_in_kernel_pdl"])
 @pytest.mark.parametrize("codec", [2, 1], ids=["b3", "d2"])
 def test_two_gpu_tensor_parallel_matches_unsharded_reference(codec, use_peer):
     if torch.cuda.device_count() < 2:

@@ -34,6 +34,7 @@ struct ReduceParams {
   float* out;
   uint32_t* status;
   uint32_t rank, world, count, op;   // op: 0 sum, 1 max
+  long long wait_cycles;
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
@@ -70,7 +71,7 @@ __global__ void __launch_bounds__(256) oneshot_reduce_kernel(const ReduceParams 
     for (uint32_t i = 0;; ++i) {
       // flags only grow; a peer that is already one round ahead has passed this one
       if (int32_t(ld_acquire_sys(p.my_flags + tid) - seq) >= 0) break;
-      if ((i & 255u) == 255u && clock64() - t0 > kCommWaitCycles) {
+      if ((i & 63u) == 63u && clock64() - t0 > p.wait_cycles) {
         failed = 1;
         if (atomicOr(&p.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) { p.status[TBS_INFO0] = tid; p.status[TBS_INFO1] = 400; }
         break;
@@ -117,6 +118,7 @@ struct tb_comm {
   size_t slot_bytes = 0, data_bytes = 0, total_bytes = 0;
   uint8_t* base[kMaxWorld] = {};   // base[rank] is the local allocation, the others are IPC mappings
   bool connected = false;
+  long long wait_cycles = kCommWaitCycles;
 };
 
 namespace {
@@ -199,6 +201,7 @@ extern "C" tb_status tb_comm_allreduce_f32(tb_comm* c, uint32_t slot, uint32_t c
   p.my_flags = mine; p.epoch = mine + kMaxWorld; p.done = mine + kMaxWorld + 1;
   p.out = out; p.status = c->owner->d_status;
   p.rank = c->rank; p.world = c->world; p.count = count; p.op = op_max ? 1u : 0u;
+  p.wait_cycles = c->wait_cycles;
   const uint32_t blocks = std::min<uint32_t>(32, (count / 4 + 255) / 256 + 1);
   cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : c->owner->stream;
   oneshot_reduce_kernel<<<blocks, 256, 0, st>>>(p);
@@ -214,19 +217,37 @@ bool tb_comm_view(const tb_comm* c, uint32_t slot, TbCommView* out) {
     out->flags[r] = flag_row(c->base[r], c, slot);
   }
   out->world = c->world; out->rank = c->rank; out->counters = c->flag_words - kCommCounters;
+  out->wait_cycles = c->wait_cycles;
   return true;
 }
 size_t tb_comm_slot_bytes(const tb_comm* c) { return c ? c->slot_bytes : 0; }
 const tb_backend* tb_comm_owner(const tb_comm* c) { return c ? c->owner : nullptr; }
 
+extern "C" tb_status tb_comm_set_wait_limit(tb_comm* c, uint64_t sm_cycles) {
+  if (!c) return tb_fail(TB_NULL_ARG, "null argument");
+  if (sm_cycles == 0 || sm_cycles > (uint64_t(1) << 40)) return tb_fail(TB_INVALID_INPUT, "the wait limit must be between 1 and 2^40 SM cycles");
+  c->wait_cycles = static_cast<long long>(sm_cycles);
+  return TB_OK;
+}
+
+extern "C" tb_status tb_comm_disconnect(tb_comm* c) {
+  if (!c) return tb_fail(TB_NULL_ARG, "null argument");
+  if (cudaSetDevice(c->owner->ordinal) != cudaSuccess) return tb_fail(TB_BACKEND, "select device");
+  cudaError_t err = cudaDeviceSynchronize();   // none of this rank's kernels may still read a peer
+  for (uint32_t r = 0; r < c->world; ++r) {
+    if (r == c->rank || !c->base[r]) continue;
+    const cudaError_t e = cudaIpcCloseMemHandle(c->base[r]);
+    if (err == cudaSuccess) err = e;
+    c->base[r] = nullptr;
+  }
+  c->connected = c->world == 1;
+  if (err != cudaSuccess) return tb_cuda_fail(err, "unmap the peers' communicator memory");
+  return TB_OK;
+}
+
 extern "C" void tb_comm_free(tb_comm* c) {
   if (!c) return;
-  cudaSetDevice(c->owner->ordinal);
-  cudaDeviceSynchronize();
-  for (uint32_t r = 0; r < c->world; ++r) {
-    if (!c->base[r]) continue;
-    if (r == c->rank) cudaFree(c->base[r]);
-    else cudaIpcCloseMemHandle(c->base[r]);
-  }
+  tb_comm_disconnect(c);
+  cudaFree(c->base[c->rank]);
   delete c;
 }

@@ -51,7 +51,7 @@ constexpr int kConsumerThreads = kWarps * 32;
 constexpr int kMaxStages = 4;
 constexpr int kPartBufs = 4;   // row blocks whose partial sums may wait for the combiner
 constexpr int kMaxGroupLayers = 128;   // layers of one grouped launch (descriptors live in shared memory)
-constexpr uint32_t kBuildStagingBytes = 32 * 272 + 8 * 16 + 16;   // fused prologue: quantised activations of one pass of pairs, absmax partials, 1/rms per token
+constexpr uint32_t kBuildStagingBytes = 32 * 272 + 8 * 16 + 16 + 128;   // fused prologue: quantised activations of one pass of pairs, absmax partials, 1/rms per token, the peers' absmax
 
 struct DecodeParams {
   const uint8_t* payload; const uint16_t* scales;   // single layer (layers == nullptr)
@@ -63,6 +63,8 @@ struct DecodeParams {
   // behind the token scale (fp32, indexed like y; null = none)
   const float* norm_weight; float norm_eps; uint32_t norm_zero_centered;
   const float* residual;
+  // tensor-parallel row shard (tp != 0): absmax exchange of the fused prologue, output sum over the ranks
+  TbCommView comm_absmax, comm_y; uint32_t tp;
   void* y; int32_t* acc_dump; const float* row_scale;
   uint32_t* status;
   uint32_t m, n, k, planes, tpr;            // m: valid tokens; tpr = k / 256
@@ -92,12 +94,24 @@ __device__ __forceinline__ float peer_load(const float* p) {
   return v;
 }
 // Waits (bounded) until `counter` has received `target` arrivals since the slot was created.
-__device__ __forceinline__ bool peer_wait(const uint32_t* counter, uint32_t target) {
+__device__ __forceinline__ bool peer_wait(const uint32_t* counter, uint32_t target, long long limit = kPeerWaitCycles) {
   const long long t0 = clock64();
   for (uint32_t i = 0;; ++i) {
     if (int32_t(peer_poll(counter) - target) >= 0) return true;
-    if ((i & 255u) == 255u && clock64() - t0 > kPeerWaitCycles) return false;
+    if ((i & 63u) == 63u && clock64() - t0 > limit) return false;
   }
+}
+// One 8-byte word carries a value and the round it belongs to: a single store publishes both.
+__device__ __forceinline__ void peer_store_u64(uint64_t* p, uint64_t v) {
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ uint64_t peer_load_u64(const uint64_t* p) {
+  uint64_t v;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void peer_store_f32(float* p, float v) {
+  asm volatile("st.relaxed.sys.global.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
 }
 
 template <int CODEC> struct Traits;
@@ -398,7 +412,7 @@ __global__ void __launch_bounds__(256) prepare_kernel(const PrepareParams p) {
             }
         }
         float gmax = gamma;
-        if (peer_wait(mine + kCommCounters + t, (p.comm.world - 1) * comm_seq)) {
+        if (peer_wait(mine + kCommCounters + t, (p.comm.world - 1) * comm_seq, p.comm.wait_cycles)) {
           for (uint32_t r = 0; r < p.comm.world; ++r)
             if (r != p.comm.rank) gmax = fmaxf(gmax, peer_load(p.comm.data[r] + t));
         } else if (atomicOr(&p.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) {
@@ -520,7 +534,7 @@ __device__ __forceinline__ void apply_norm(const DecodeParams& p, float inv, uin
 }
 
 template <int CODEC, bool DUAL, int M>
-__device__ __forceinline__ void build_tables(const DecodeParams& p, uint8_t* smem, uint32_t tid) {
+__device__ __forceinline__ void build_tables(const DecodeParams& p, uint8_t* smem, uint32_t tid, uint32_t tp_seq) {
   constexpr int kNM = MmaCount<CODEC, DUAL>::value;
   constexpr uint32_t ncol = (DUAL ? 4 : 2) * M;
   constexpr bool B3 = CODEC == tbf::kB3;
@@ -591,12 +605,50 @@ __device__ __forceinline__ void build_tables(const DecodeParams& p, uint8_t* sme
       }
       consumer_sync();
     }
+    float* peer_gamma = red + kWarps * 4 + 4;   // [rank][token]
+    if (p.tp && !p.act_absmax_in) {
+      // Row shard: the row's absmax is the maximum over the ranks' slices.  CTA 0 pushes this
+      // slice's value, tagged with the round, into every peer's copy of the slot; every CTA then
+      // finds the peers' values in its own GPU's memory.  Two parities alternate, so a rank that
+      // is one round ahead cannot overwrite a value still being read.
+      const TbCommView& cv = p.comm_absmax;
+      const uint32_t par = tp_seq & 1u;
+      if (tid < cv.world && tid != cv.rank) {
+        if (blockIdx.x == 0) {
+          uint64_t* dst = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(cv.data[tid]) + kCommAbsmaxWords) + (par * kCommMaxWorld + cv.rank) * 4;
+          for (uint32_t t = 0; t < p.m; ++t) {
+            float mine = 0.f;
+            for (uint32_t w2 = 0; w2 < uint32_t(kWarps); ++w2) mine = fmaxf(mine, red[w2 * 4 + t]);
+            peer_store_u64(dst + t, (uint64_t(tp_seq) << 32) | __float_as_uint(mine));
+          }
+        }
+        const uint64_t* src = reinterpret_cast<const uint64_t*>(reinterpret_cast<const uint8_t*>(cv.data[cv.rank]) + kCommAbsmaxWords) + (par * kCommMaxWorld + tid) * 4;
+        const long long t0 = clock64();
+        for (uint32_t t = 0; t < p.m; ++t) {
+          float got = 0.f;
+          for (uint32_t i = 0;; ++i) {
+            const uint64_t v = peer_load_u64(src + t);
+            if (uint32_t(v >> 32) == tp_seq) { got = __uint_as_float(uint32_t(v)); break; }
+            if ((i & 63u) == 63u && clock64() - t0 > cv.wait_cycles) {
+              if (atomicOr(&p.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) { p.status[TBS_INFO0] = tid; p.status[TBS_INFO1] = 600 + t; }
+              break;
+            }
+          }
+          peer_gamma[tid * 4 + t] = got;
+        }
+      }
+      consumer_sync();
+    }
 #pragma unroll
     for (int t = 0; t < M; ++t) {
       float gamma = 0.f;
       if (p.act_absmax_in) gamma = uint32_t(t) < p.m ? p.act_absmax_in[t] : 0.f;   // absmax over the full (unsharded) row, supplied by the caller
-      else
+      else {
         for (uint32_t w2 = 0; w2 < uint32_t(kWarps); ++w2) gamma = fmaxf(gamma, red[w2 * 4 + t]);
+        if (p.tp && uint32_t(t) < p.m)
+          for (uint32_t r = 0; r < p.comm_absmax.world; ++r)
+            if (r != p.comm_absmax.rank) gamma = fmaxf(gamma, peer_gamma[r * 4 + t]);
+      }
       scale_q[t] = gamma > 0.f ? __fdiv_rn(127.0f, gamma) : 0.f;
       scale_out[t] = __fdiv_rn(gamma, 127.0f);
     }
@@ -720,7 +772,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
   constexpr uint32_t kSliceFloats = YN * 16 * NC;   // one consumer warp's partial sums of a row block
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ uint64_t full_bar[kMaxStages], empty_bar[kMaxStages], table_bar, part_full[kPartBufs], part_empty[kPartBufs];
-  __shared__ uint32_t abort_flag;
+  __shared__ uint32_t abort_flag, tp_round;
   __shared__ TbLayerDesc layer_desc[kMaxGroupLayers];
 
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -787,6 +839,14 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
     // ------------------------------------------------ combiner: adds the eight consumer warps'
     // partial sums of a finished row block (fixed order: plane, scale-group cell, warp), applies
     // the token scale and stores the outputs, while the consumers work on later blocks.
+    // Round of the exchanges between the ranks: one more than the rounds this slot has completed.
+    // The word lives in device memory, so a replayed CUDA graph counts on by itself; the previous
+    // launch on the stream may be the one that completes the round before, so wait for it first.
+    uint32_t tp_seq = 0;
+    if (p.tp) {
+      if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
+      tp_seq = *reinterpret_cast<volatile uint32_t*>(p.comm_y.flags[p.comm_y.rank] + kCommDecodeEpoch) + 1u;
+    }
     if (!mbar_wait(&table_bar, 0, &abort_flag)) return;   // token scales live in the tables
     uint32_t buf = 0, parity = 0;
     uint32_t layer = blockIdx.x / p.blocks, blk = blockIdx.x - layer * p.blocks;
@@ -817,15 +877,72 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
         }
         float out = __fmul_rn(sum, act_scale[t]);
         if (p.row_scale) out = __fmul_rn(out, p.row_scale[row0 + r]);
+        if (p.tp) {
+          // this rank's partial goes into every rank's copy of the slot: [round parity][source rank][token][row]
+          const size_t at = (size_t((tp_seq & 1u) * p.comm_y.world + p.comm_y.rank) * p.m + t) * p.n + row0 + r;
+          for (uint32_t dst = 0; dst < p.comm_y.world; ++dst) peer_store_f32(p.comm_y.data[dst] + at, out);
+          continue;
+        }
         const size_t idx = size_t(layer) * p.y_layer_stride + size_t(t) * p.y_row_stride + row0 + r;
         if (p.residual) out = __fadd_rn(p.residual[idx], out);   // crates/tritium-cuda/kernels/tq2_0_add.cu:577-637
         if (p.y_dtype == TB_F32) static_cast<float*>(p.y)[idx] = out;
         else static_cast<__nv_bfloat16*>(p.y)[idx] = __float2bfloat16_rn(out);
       }
+      if (p.tp) {
+        // the stores above must be visible before the arrival that announces them
+        __threadfence_system();
+        __syncwarp();
+        if (lane < p.comm_y.world && lane != p.comm_y.rank) peer_signal(p.comm_y.flags[lane] + kCommCounters + kCommBlockCounter0 + blk);
+      }
       __syncwarp();
       if (lane == 0) mbar_arrive(&part_empty[buf]);
       if (++buf == kPartBufs) { buf = 0; parity ^= 1; }
       for (blk += gridDim.x; blk >= p.blocks; blk -= p.blocks) ++layer;
+    }
+    if (p.tp) {
+      // Second pass over this CTA's row blocks: once every peer's partial of a block has arrived
+      // (each peer's CTA of the same index pushed it at about the same time), add the ranks'
+      // partials in rank order, so that every rank stores the same bits.
+      const TbCommView& cv = p.comm_y;
+      const uint32_t* mine = cv.flags[cv.rank] + kCommCounters + kCommBlockCounter0;
+      const float* base = cv.data[cv.rank] + size_t((tp_seq & 1u) * cv.world) * p.m * p.n;
+      const size_t src_stride = size_t(p.m) * p.n;
+      bool ok = true;
+      blk = blockIdx.x;
+      for (uint32_t it = 0; it < my_blocks && ok; ++it, blk += gridDim.x) {
+        uint32_t arrived = 1;
+        if (lane == 0) arrived = peer_wait(mine + blk, (cv.world - 1) * tp_seq, cv.wait_cycles) ? 1u : 0u;
+        arrived = __shfl_sync(0xffffffffu, arrived, 0);
+        asm volatile("fence.acq_rel.sys;" ::: "memory");   // the other lanes' loads stay behind lane 0's acquire
+        if (!arrived) {
+          if (lane == 0 && atomicOr(&p.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) { p.status[TBS_INFO0] = blk; p.status[TBS_INFO1] = 700; }
+          ok = false;
+          break;
+        }
+        const uint32_t row0 = blk * p.rows_per_stage;
+        for (uint32_t e = lane; e < p.rows_per_stage * p.m; e += 32) {
+          const uint32_t t = e / p.rows_per_stage, r = e - t * p.rows_per_stage;
+          if (row0 + r >= p.n) continue;
+          const float* src = base + size_t(t) * p.n + row0 + r;
+          float out = peer_load(src);
+          for (uint32_t q = 1; q < cv.world; ++q) out = __fadd_rn(out, peer_load(src + q * src_stride));
+          const size_t idx = size_t(t) * p.y_row_stride + row0 + r;
+          if (p.residual) out = __fadd_rn(p.residual[idx], out);
+          if (p.y_dtype == TB_F32) static_cast<float*>(p.y)[idx] = out;
+          else static_cast<__nv_bfloat16*>(p.y)[idx] = __float2bfloat16_rn(out);
+        }
+      }
+      // the last CTA to get here closes the round (also after a wait that ran out: the next
+      // launch must not wait for a round that was given up)
+      __syncwarp();
+      if (lane == 0) {
+        __threadfence();
+        uint32_t* flags = cv.flags[cv.rank];
+        if (atomicAdd(flags + kCommDecodeDone, 1u) == gridDim.x - 1) {
+          flags[kCommDecodeDone] = 0;
+          *reinterpret_cast<volatile uint32_t*>(flags + kCommDecodeEpoch) = tp_seq;
+        }
+      }
     }
     return;
   }
@@ -834,7 +951,11 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
   if (p.fused) {
     // x may be the previous kernel's output: wait for it (the weight stream is already running)
     if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
-    build_tables<CODEC, DUAL, M>(p, smem, tid);
+    if (p.tp) {
+      if (tid == 0) tp_round = *reinterpret_cast<volatile uint32_t*>(p.comm_y.flags[p.comm_y.rank] + kCommDecodeEpoch) + 1u;
+      consumer_sync();
+    }
+    build_tables<CODEC, DUAL, M>(p, smem, tid, p.tp ? tp_round : 0u);
     consumer_sync();
     if (tid == 0) mbar_arrive(&table_bar);   // releases the combiner
   } else {
@@ -1199,7 +1320,10 @@ cudaError_t tb_launch_decode(const DecodeArgs& a, int sm_count, int max_smem, cu
   const TableLayout tl = table_layout(w, a.m);
   if (a.fused) {
     // the prologue reads x with 16-byte loads
-    if (!a.x || (reinterpret_cast<uintptr_t>(a.x) & 15u) || a.comm_absmax) return cudaErrorInvalidValue;
+    if (!a.x || (reinterpret_cast<uintptr_t>(a.x) & 15u)) return cudaErrorInvalidValue;
+    // a row shard that builds its own tables exchanges the absmax in the same launch, which needs the output slot's round
+    if (a.comm_absmax && !a.comm_y) return cudaErrorInvalidValue;
+    if (a.comm_y && a.comm_y->world > 1 && !a.comm_absmax && !a.act_absmax_in && a.x_dtype != TB_I8) return cudaErrorInvalidValue;
     if (a.x_dtype == TB_I8 && !a.act_scale_in) return cudaErrorInvalidValue;
     p.fused = 1; p.x = a.x; p.act_scale_in = a.act_scale_in; p.act_absmax_in = a.act_absmax_in; p.x_dtype = uint32_t(a.x_dtype);
     if (a.norm_weight) {
@@ -1210,6 +1334,12 @@ cudaError_t tb_launch_decode(const DecodeArgs& a, int sm_count, int max_smem, cu
     return cudaErrorInvalidValue;   // the norm prologue lives in the fused builder; other launches take normalised input
   }
   p.residual = a.residual;
+  if (a.comm_y && a.comm_y->world > 1) {
+    if (a.layers || a.layer_count > 1 || a.acc_dump) return cudaErrorInvalidValue;
+    if (a.comm_y->counters < kCommBlockCounter0 + w->plan.blocks) return cudaErrorInvalidValue;
+    p.tp = 1; p.comm_y = *a.comm_y;
+    if (a.fused && a.comm_absmax) p.comm_absmax = *a.comm_absmax;
+  }
   cudaLaunchAttribute attr[2];
   unsigned num_attrs = 0;
   if (a.pdl) {

@@ -562,37 +562,46 @@ extern "C" tb_status tb_linear_forward_tp_dev(tb_backend* b, const tb_weights* w
   if (x_dtype == TB_I8) return tb_fail(TB_INVALID_INPUT, "the tensor-parallel path quantises fp32 or bf16 activations itself");
   if (y_dtype == TB_I8) return tb_fail(TB_INVALID_INPUT, "output dtype must be fp32 or bf16");
   if (m > 8) return tb_fail(TB_INVALID_INPUT, "the fused tensor-parallel path takes at most 8 tokens per call");
-  if (flags != 0) return tb_fail(TB_INVALID_INPUT, "unknown flag bits");
-  if (y_dtype != TB_F32) return tb_fail(TB_INVALID_INPUT, "the one-shot reduce writes fp32 outputs");
+  if (flags & ~TB_FWD_PDL) return tb_fail(TB_INVALID_INPUT, "unknown flag bits");
   if (!w->fast) return tb_fail(TB_UNSUPPORTED_FORMAT, "the int8 path needs uniform plane counts, k % 256 == 0, group 128 and codec D2 or B3");
   if (slot_absmax == slot_y) return tb_fail(TB_INVALID_INPUT, "the absmax and the output slot must differ");
   TbCommView va{}, vy{};
   if (!tb_comm_view(comm, slot_absmax, &va) || !tb_comm_view(comm, slot_y, &vy))
     return tb_fail(TB_INVALID_INPUT, "communicator is not connected or a slot index is out of range");
-  if (size_t(m) * w->n * 4 > tb_comm_slot_bytes(comm)) return tb_fail(TB_INVALID_INPUT, "the output slot is smaller than m x n fp32 values");
-  if (va.counters < 4)
-    return tb_fail(TB_INVALID_INPUT, "the communicator holds " + std::to_string(va.counters) + " arrival counters per slot, four are needed");
   if (tb_status s = use_device(b)) return s;
   cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : b->stream;
+  if (va.world <= 1) {
+    tb_forward_args a{};
+    a.x = x; a.x_dtype = x_dtype; a.m = m; a.y = y; a.y_dtype = y_dtype; a.flags = TB_FWD_A8 | TB_FWD_FORCE_DECODE | flags;
+    return forward_dev(b, w, a, st, nullptr);
+  }
+  // every rank's partial rows of one pass, in two alternating copies
+  const size_t need_y = size_t(2) * va.world * std::min<uint32_t>(4, m) * w->n * 4;
+  if (need_y > tb_comm_slot_bytes(comm))
+    return tb_fail(TB_INVALID_INPUT, "the output slot holds " + std::to_string(tb_comm_slot_bytes(comm)) + " bytes, 2 x world x tokens x n fp32 values need " +
+                                         std::to_string(need_y));
+  if (tb_comm_slot_bytes(comm) < kCommAbsmaxBytes) return tb_fail(TB_INVALID_INPUT, "the absmax slot is smaller than 1 KiB");
+  if (vy.counters < kCommBlockCounter0 + w->plan.blocks)
+    return tb_fail(TB_INVALID_INPUT, "the communicator holds " + std::to_string(vy.counters) + " arrival counters per slot, this tensor needs " +
+                                         std::to_string(kCommBlockCounter0 + w->plan.blocks));
   for (uint32_t m0 = 0; m0 < m; m0 += 4) {
     const uint32_t mc = std::min<uint32_t>(4, m - m0);
     if (!tb_decode_supported(w, mc, b->max_smem_optin, nullptr))
       return tb_fail(TB_UNSUPPORTED_FORMAT, "the decode kernel's shared-memory plan does not fit this shape");
-    TbCommView ca = va;
-    for (uint32_t r = 0; r < va.world; ++r) ca.data[r] += m0;
     DecodeArgs d{};
     d.w = w; d.x_dtype = x_dtype; d.m = mc; d.y_row_stride = uint32_t(w->n);
     d.x = static_cast<const uint8_t*>(x) + size_t(m0) * w->k * dtype_size(x_dtype);
-    d.status = b->d_status; d.pdl = false;
+    d.y = static_cast<uint8_t*>(y) + size_t(m0) * w->n * dtype_size(y_dtype); d.y_dtype = y_dtype;
+    d.status = b->d_status; d.pdl = (flags & TB_FWD_PDL) != 0 || m0 > 0;
     d.scratch = b->d_prep; d.scratch_bytes = b->d_prep_cap;
-    d.comm_absmax = va.world > 1 ? &ca : nullptr;
-    // fp32 partial rows straight into this rank's slot; one reduce kernel after the last pass
-    d.y = vy.data[vy.rank] + size_t(m0) * w->n;
-    d.y_dtype = TB_F32;
-    TB_CUDA(tb_launch_prepare(d, st), "launch prepare");
+    d.comm_absmax = &va; d.comm_y = &vy;
+    // Small tables: ONE launch (absmax exchange in the table builder, output sum in the epilogue).
+    // Large tables: the preparation kernel exchanges the absmax, the decode kernel sums the outputs.
+    d.fused = tb_decode_builds_tables(w, mc, d.x);
+    if (!d.fused) TB_CUDA(tb_launch_prepare(d, st), "launch prepare");
     TB_CUDA(tb_launch_decode(d, b->prop.multiProcessorCount, b->max_smem_optin, st), "launch decode");
   }
-  return tb_comm_allreduce_f32(comm, slot_y, uint32_t(size_t(m) * w->n), 0, static_cast<float*>(y), st);
+  return TB_OK;
 }
 
 extern "C" tb_status tb_backend_reserve(tb_backend* b, const tb_weights* w, uint32_t max_m) {

@@ -97,11 +97,18 @@ cudaError_t tb_launch_check_finite(const float* x, uint64_t count, uint32_t* sta
 // its flag words (this rank's own pointers at index `rank`).  world <= 1 means "no peers".
 // Flag words of a slot: [0,8) one-shot flags, 8 epoch, 9 block counter (one-shot reduce);
 // 10 epoch, 11 block counter (fused kernels); 16.. arrival counters, one per token or row block.
-constexpr uint32_t kCommMaxWorld = 8, kCommFusedEpoch = 10, kCommFusedDone = 11, kCommCounters = 16;
+// 12 epoch, 13 block counter (exchanges inside the decode kernel); counters 0..3 belong to the
+// preparation kernel's tokens, counters 4.. to the decode kernel's row blocks.
+constexpr uint32_t kCommMaxWorld = 8, kCommFusedEpoch = 10, kCommFusedDone = 11, kCommDecodeEpoch = 12, kCommDecodeDone = 13,
+                   kCommCounters = 16, kCommBlockCounter0 = 4;
+// Byte offset, inside the absmax slot, of the words the decode kernel's absmax exchange uses:
+// uint64 [round parity][source rank][token] = (round << 32) | float bits.
+constexpr uint32_t kCommAbsmaxWords = 64, kCommAbsmaxBytes = kCommAbsmaxWords + 2 * kCommMaxWorld * 4 * 8;
 struct TbCommView {
   float* data[kCommMaxWorld];
   uint32_t* flags[kCommMaxWorld];
   uint32_t world, rank, counters;   // counters: arrival counters the slot's flag area holds
+  long long wait_cycles;            // bound of every wait on a peer, in SM clocks
 };
 
 // Device-resident descriptor of one layer of a grouped launch.
@@ -128,6 +135,11 @@ struct DecodeArgs {
   // tensor-parallel row shard (single layer): the prepare kernel exchanges the per-token absmax
   // through `comm_absmax`.  Null = no peers.
   const TbCommView* comm_absmax;
+  // Row shard whose outputs are summed over the ranks inside the decode kernel: every CTA pushes
+  // its partial rows into all ranks' copies of this slot, signals the row block's counter, and sums
+  // the block once all ranks' partials have arrived.  Fused launches exchange the absmax the same
+  // way (through comm_absmax).  Null = no peers.  Every rank must make the same launch.
+  const TbCommView* comm_y;
   uint32_t inject_missing_tx;   // test hook (non-fused launches): the table barrier expects this many bytes too many
   // fused launches: RMSNorm over each token's row in front of the quantiser (weight [k] fp32,
   // 16-byte aligned; null = none).  Any launch: out = residual + y (fp32, indexed like y).

@@ -103,7 +103,7 @@ class PeerComm:
         from .errors import check
         self._L, self._check, self.backend = _lib.load(), check, backend
         self.rank, self.world, self.slots, self.slot_bytes = rank, world, slots, (slot_bytes + 255) // 256 * 256
-        self._next = 0
+        self._next, self._group = 0, group
         h = C.c_void_p(None)
         check(self._L.tb_comm_create(backend._h, C.c_uint32(world), C.c_uint32(rank), C.c_size_t(slot_bytes), C.c_uint32(slots),
                                      C.c_uint32(counters_per_slot), C.byref(h)))
@@ -142,10 +142,10 @@ class PeerComm:
         self._check(self._L.tb_comm_allreduce_f32(self._h, C.c_uint32(slot), C.c_uint32(count), int(op_max),
                                                   C.c_void_p(out.data_ptr()), C.c_void_p(s.cuda_stream)))
 
-    def linear_fused(self, handle, slot_absmax: int, slot_y: int, x, y, stream=None) -> None:
-        """Row-parallel forward of up to 8 tokens (`tb_linear_forward_tp_dev`): the prepare kernel
-        exchanges the row absmax; the output all-reduce is one reduce kernel behind the decode
-        kernel."""
+    def linear_fused(self, handle, slot_absmax: int, slot_y: int, x, y, stream=None, flags: int = 0) -> None:
+        """Row-parallel forward of up to 8 tokens (`tb_linear_forward_tp_dev`): the absmax exchange
+        and the output sum over the ranks both happen inside the kernels (one launch per four
+        tokens when the activation tables are small)."""
         import ctypes as C
         import torch
         from . import _lib
@@ -153,17 +153,36 @@ class PeerComm:
         s = stream if stream is not None else torch.cuda.current_stream()
         self._check(self._L.tb_linear_forward_tp_dev(self.backend._h, handle._h, self._h, C.c_uint32(slot_absmax), C.c_uint32(slot_y),
                                                      C.c_void_p(x.data_ptr()), dt[x.dtype], C.c_uint32(x.shape[0]),
-                                                     C.c_void_p(y.data_ptr()), dt[y.dtype], C.c_uint32(0),
+                                                     C.c_void_p(y.data_ptr()), dt[y.dtype], C.c_uint32(flags),
                                                      C.c_void_p(s.cuda_stream)))
 
+    def set_wait_limit(self, sm_cycles: int) -> None:
+        """Bound of every wait on a peer, in SM clock cycles (default about two seconds)."""
+        import ctypes as C
+        self._check(self._L.tb_comm_set_wait_limit(self._h, C.c_uint64(sm_cycles)))
+
     def close(self) -> None:
-        if self._h:
-            self._L.tb_comm_free(self._h)
-            self._h = None
+        """Collective teardown: every rank must call it.  No rank frees its buffer while a peer may
+        still have it mapped or a kernel may still touch it: quiesce, barrier, unmap, barrier, free."""
+        if not self._h:
+            return
+        h, self._h = self._h, None
+        if self.world > 1:
+            import torch
+            import torch.distributed as dist
+            torch.cuda.synchronize(self.backend.ordinal)
+            dist.barrier(group=self._group)
+            self._L.tb_comm_disconnect(h)
+            dist.barrier(group=self._group)
+        self._L.tb_comm_free(h)
 
     def __del__(self):
+        # A collective cannot run from a finaliser (the peers may be gone): a communicator that was
+        # never closed only releases this rank's side.
         try:
-            self.close()
+            if self._h:
+                h, self._h = self._h, None
+                self._L.tb_comm_free(h)
         except Exception:
             pass
 
@@ -205,8 +224,8 @@ class TPLinear:
         # communicator: the kernels write their partials straight into its slots
         comm = getattr(executor, "comm", None) if mode == "row" and world > 1 else None
         # `fused` (decode-sized batches): False = separate absmax and one-shot reduce kernels around
-        # the ordinary forward; True = the prepare kernel exchanges the row absmax itself and one
-        # reduce kernel follows the decode kernel
+        # the ordinary forward; True = both exchanges happen inside the linear's own kernels.
+        # Switch only while every rank is idle (a barrier): the two ways share the slots.
         self.comm, self.peer_m, self.fused = comm, 0, False
         if comm is not None:
             self.peer_m = min(max_m, comm.slot_bytes // (4 * self.geometry.n))
@@ -232,8 +251,9 @@ class TPLinear:
             self.executor.linear(self.handle, x, y, None)
             return y
         absmax = self.absmax[:m]
-        if self.comm is not None and m <= min(self.peer_m, 8) and self.fused:
-            self.comm.linear_fused(self.handle, self.slot_absmax, self.slot_y, x, y)
+        if self.comm is not None and self.fused and m <= 8 and \
+                2 * self.world * min(m, 4) * self.geometry.n * 4 <= self.comm.slot_bytes:
+            self.comm.linear_fused(self.handle, self.slot_absmax, self.slot_y, x, y, flags=getattr(self.executor, "flags", 0))
             return y
         if self.comm is not None and m <= self.peer_m:
             self.executor.row_absmax(x, self.peer_absmax[:m])
