@@ -292,7 +292,8 @@ def measure_tp(torch, dist, backend, rank: int, world: int, codec, codec_name: s
     comm = None
     if world > 1:
         # two slots (row absmax, partial outputs) per row-parallel linear, sized for decode batches up to 32
-        comm = tp.PeerComm(backend, rank, world, slot_bytes=32 * shape.hidden * 4, slots=4 * built)
+        # (the in-kernel exchange keeps every rank's partial rows of a four-token pass in two alternating copies)
+        comm = tp.PeerComm(backend, rank, world, slot_bytes=max(32, 2 * world * 4 * 2) * shape.hidden * 4, slots=4 * built)
     ex = tp.CudaExecutor(backend, flags=0 if args.no_pdl else _lib.TB_FWD_PDL, comm=comm)
     t0 = time.perf_counter()
     stack = tp.TPDecoderStack(ex, shape, codec, rank, world, max_m=max_m, distinct_layers=built, synthetic_shards=True)
@@ -342,17 +343,22 @@ def measure_tp(torch, dist, backend, rank: int, world: int, codec, codec_name: s
                 "weight_gbs_all_ranks": world * bytes_rank / (ms * 1e-3) / 1e9, "cuda_graph": graphed,
                 "all_reduces_per_timed_step": 4 * built if world > 1 else 0, "reduce": reduce_kind}
 
+    # row-parallel linears exchange the absmax and sum their outputs inside their own kernels
+    # (batches up to 8 tokens; larger ones use the separate one-shot kernels or NCCL)
+    stack.use_fused_reduce(True)
     ms, graphed = timed(1, not args.no_graph)
-    out["decode_m1"] = decode_entry(ms, graphed, "separate absmax and one-shot reduce kernels over peer memory" if world > 1 else "none")
+    out["decode_m1"] = decode_entry(ms, graphed, "absmax exchange and output sum inside the linear's kernels (pushes into peer memory)" if world > 1 else "none")
     if world > 1 and reduce_variants:
-        stack.use_fused_reduce(True)
-        ms, graphed = timed(1, not args.no_graph)
-        out["decode_m1_absmax_in_kernel"] = decode_entry(ms, graphed, "absmax exchange inside the prepare kernel + one reduce kernel over peer memory")
         stack.use_fused_reduce(False)
+        dist.barrier()
+        ms, graphed = timed(1, not args.no_graph)
+        out["decode_m1_one_shot"] = decode_entry(ms, graphed, "separate absmax and one-shot reduce kernels over peer memory")
         stack.use_peer_reduce(False)
         ms, graphed = timed(1, not args.no_graph)
         out["decode_m1_nccl"] = decode_entry(ms, graphed, "nccl all_reduce")
         stack.use_peer_reduce(True)
+        stack.use_fused_reduce(True)
+        dist.barrier()
     for mb in batches:
         if mb == 1:
             continue

@@ -307,13 +307,13 @@ tb_status tb_comm_allreduce_f32(tb_comm* comm, uint32_t slot, uint32_t count, in
  *     rank pushes its slice's value, tagged with the round number, into the peers' copies of
  *     `slot_absmax` and finds the peers' values in its own memory (small activation tables: inside
  *     the decode kernel's table builder; large ones: in the preparation kernel);
- *   - the output sum: every CTA pushes its fp32 partial rows into all ranks' copies of `slot_y`,
- *     signals the row block's arrival counter on each peer, and, once the peers' partials of the
- *     block have arrived, adds them in rank order and stores `y` (fp32 or bf16; every rank ends
- *     with the same bits of the full result).
- * So a row-parallel linear with small tables is ONE launch.  Only plain peer stores and loads
- * are used.  `slot_y` must hold 2 x world x min(m,4) x n fp32 values, `slot_absmax` 1 KiB, and
- * the communicator 4 + (row blocks of the tensor) counters per slot.  flags: 0 or TB_FWD_PDL.
+ *   - the output sum: every CTA pushes its fp32 partial rows into all ranks' copies of `slot_y`
+ *     and, once the peers' partials of a row block have arrived, adds them in rank order and
+ *     stores `y` (fp32 or bf16; every rank ends with the same bits of the full result).
+ * Every value travels with its round number in one 8-byte word, so the exchanges need no flag,
+ * no fence and no second kernel: a row-parallel linear with small tables is ONE launch.  Only
+ * plain peer stores (and loads of the rank's own memory) are used.  `slot_y` must hold
+ * 2 x world x min(m,4) x n 8-byte words, `slot_absmax` 2 KiB.  flags: 0 or TB_FWD_PDL.
  * Every rank must make the same call (same m) on its shard; the two slots belong to this linear
  * alone; use tb_comm_allreduce_f32 on them only after every rank has gone idle (a host barrier).  After a TB_TIMEOUT the
  * round counters of the ranks no longer agree: free the communicator and build a new one. */

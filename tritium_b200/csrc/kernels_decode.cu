@@ -79,28 +79,6 @@ struct DecodeParams {
 
 
 // ---- peer-memory helpers (tensor-parallel row shards)
-constexpr long long kPeerWaitCycles = 4000000000ll;   // about two seconds of SM clocks
-__device__ __forceinline__ void peer_signal(uint32_t* counter) {
-  asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(counter) : "memory");
-}
-__device__ __forceinline__ uint32_t peer_poll(const uint32_t* counter) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
-  return v;
-}
-__device__ __forceinline__ float peer_load(const float* p) {
-  float v;
-  asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
-  return v;
-}
-// Waits (bounded) until `counter` has received `target` arrivals since the slot was created.
-__device__ __forceinline__ bool peer_wait(const uint32_t* counter, uint32_t target, long long limit = kPeerWaitCycles) {
-  const long long t0 = clock64();
-  for (uint32_t i = 0;; ++i) {
-    if (int32_t(peer_poll(counter) - target) >= 0) return true;
-    if ((i & 63u) == 63u && clock64() - t0 > limit) return false;
-  }
-}
 // One 8-byte word carries a value and the round it belongs to: a single store publishes both.
 __device__ __forceinline__ void peer_store_u64(uint64_t* p, uint64_t v) {
   asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
@@ -110,9 +88,7 @@ __device__ __forceinline__ uint64_t peer_load_u64(const uint64_t* p) {
   asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ void peer_store_f32(float* p, float v) {
-  asm volatile("st.relaxed.sys.global.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
-}
+
 
 template <int CODEC> struct Traits;
 // kMmas: MMAs per (16 row-planes x tile-plane) when the two scale groups use separate
@@ -399,24 +375,28 @@ __global__ void __launch_bounds__(256) prepare_kernel(const PrepareParams p) {
       if (tid == 0) {
         uint32_t* mine = p.comm.flags[p.comm.rank];
         comm_seq = *reinterpret_cast<volatile uint32_t*>(mine + kCommFusedEpoch) + 1u;
-        if (j == 0) {
-          p.comm.data[p.comm.rank][t] = gamma;
-          __threadfence_system();
-          // a launch of fewer than four tokens still advances all four token counters, so that
-          // "arrivals = peers x rounds" holds for every counter whatever the token counts were
+        // value and round number travel in one 8-byte word ([round parity][source rank][token]):
+        // no flag, no fence; a word tagged with this round holds this round's value
+        const uint32_t par = comm_seq & 1u;
+        if (j == 0)
           for (uint32_t r = 0; r < p.comm.world; ++r)
-            if (r != p.comm.rank) {
-              peer_signal(p.comm.flags[r] + kCommCounters + t);
-              if (t == 0)
-                for (uint32_t unused = p.m; unused < 4; ++unused) peer_signal(p.comm.flags[r] + kCommCounters + unused);
-            }
-        }
+            if (r != p.comm.rank)
+              peer_store_u64(reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(p.comm.data[r]) + kCommAbsmaxWordsPrepare) +
+                                 (par * kCommMaxWorld + p.comm.rank) * 4 + t,
+                             (uint64_t(comm_seq) << 32) | __float_as_uint(gamma));
         float gmax = gamma;
-        if (peer_wait(mine + kCommCounters + t, (p.comm.world - 1) * comm_seq, p.comm.wait_cycles)) {
-          for (uint32_t r = 0; r < p.comm.world; ++r)
-            if (r != p.comm.rank) gmax = fmaxf(gmax, peer_load(p.comm.data[r] + t));
-        } else if (atomicOr(&p.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) {
-          p.status[TBS_INFO0] = t; p.status[TBS_INFO1] = 500;
+        const uint64_t* own = reinterpret_cast<const uint64_t*>(reinterpret_cast<const uint8_t*>(p.comm.data[p.comm.rank]) + kCommAbsmaxWordsPrepare);
+        const long long t0 = clock64();
+        for (uint32_t r = 0; r < p.comm.world; ++r) {
+          if (r == p.comm.rank) continue;
+          for (uint32_t i = 0;; ++i) {
+            const uint64_t word = peer_load_u64(own + (par * kCommMaxWorld + r) * 4 + t);
+            if (uint32_t(word >> 32) == comm_seq) { gmax = fmaxf(gmax, __uint_as_float(uint32_t(word))); break; }
+            if ((i & 63u) == 63u && clock64() - t0 > p.comm.wait_cycles) {
+              if (atomicOr(&p.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) { p.status[TBS_INFO0] = t; p.status[TBS_INFO1] = 500 + r; }
+              break;
+            }
+          }
         }
         gamma_all = gmax;
       }
@@ -879,8 +859,11 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
         if (p.row_scale) out = __fmul_rn(out, p.row_scale[row0 + r]);
         if (p.tp) {
           // this rank's partial goes into every rank's copy of the slot: [round parity][source rank][token][row]
+          // Each value travels with the round number in one 8-byte word, so the receiver needs no
+          // flag, no counter and no fence: a word whose tag is this round is this round's value.
           const size_t at = (size_t((tp_seq & 1u) * p.comm_y.world + p.comm_y.rank) * p.m + t) * p.n + row0 + r;
-          for (uint32_t dst = 0; dst < p.comm_y.world; ++dst) peer_store_f32(p.comm_y.data[dst] + at, out);
+          const uint64_t word = (uint64_t(tp_seq) << 32) | __float_as_uint(out);
+          for (uint32_t dst = 0; dst < p.comm_y.world; ++dst) peer_store_u64(reinterpret_cast<uint64_t*>(p.comm_y.data[dst]) + at, word);
           continue;
         }
         const size_t idx = size_t(layer) * p.y_layer_stride + size_t(t) * p.y_row_stride + row0 + r;
@@ -888,49 +871,53 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
         if (p.y_dtype == TB_F32) static_cast<float*>(p.y)[idx] = out;
         else static_cast<__nv_bfloat16*>(p.y)[idx] = __float2bfloat16_rn(out);
       }
-      if (p.tp) {
-        // the stores above must be visible before the arrival that announces them
-        __threadfence_system();
-        __syncwarp();
-        if (lane < p.comm_y.world && lane != p.comm_y.rank) peer_signal(p.comm_y.flags[lane] + kCommCounters + kCommBlockCounter0 + blk);
-      }
       __syncwarp();
       if (lane == 0) mbar_arrive(&part_empty[buf]);
       if (++buf == kPartBufs) { buf = 0; parity ^= 1; }
       for (blk += gridDim.x; blk >= p.blocks; blk -= p.blocks) ++layer;
     }
     if (p.tp) {
-      // Second pass over this CTA's row blocks: once every peer's partial of a block has arrived
-      // (each peer's CTA of the same index pushed it at about the same time), add the ranks'
-      // partials in rank order, so that every rank stores the same bits.
+      // Second pass over this CTA's row blocks: wait until every rank's word of an output carries
+      // this round's tag (each peer's CTA of the same index pushed it at about the same time), then
+      // add the ranks' partials in rank order, so that every rank stores the same bits.
       const TbCommView& cv = p.comm_y;
-      const uint32_t* mine = cv.flags[cv.rank] + kCommCounters + kCommBlockCounter0;
-      const float* base = cv.data[cv.rank] + size_t((tp_seq & 1u) * cv.world) * p.m * p.n;
+      const uint64_t* base = reinterpret_cast<const uint64_t*>(cv.data[cv.rank]) + size_t((tp_seq & 1u) * cv.world) * p.m * p.n;
       const size_t src_stride = size_t(p.m) * p.n;
+      const long long t0 = clock64();
       bool ok = true;
       blk = blockIdx.x;
       for (uint32_t it = 0; it < my_blocks && ok; ++it, blk += gridDim.x) {
-        uint32_t arrived = 1;
-        if (lane == 0) arrived = peer_wait(mine + blk, (cv.world - 1) * tp_seq, cv.wait_cycles) ? 1u : 0u;
-        arrived = __shfl_sync(0xffffffffu, arrived, 0);
-        asm volatile("fence.acq_rel.sys;" ::: "memory");   // the other lanes' loads stay behind lane 0's acquire
-        if (!arrived) {
-          if (lane == 0 && atomicOr(&p.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) { p.status[TBS_INFO0] = blk; p.status[TBS_INFO1] = 700; }
-          ok = false;
-          break;
-        }
         const uint32_t row0 = blk * p.rows_per_stage;
-        for (uint32_t e = lane; e < p.rows_per_stage * p.m; e += 32) {
+        for (uint32_t e = lane; e < p.rows_per_stage * p.m && ok; e += 32) {
           const uint32_t t = e / p.rows_per_stage, r = e - t * p.rows_per_stage;
           if (row0 + r >= p.n) continue;
-          const float* src = base + size_t(t) * p.n + row0 + r;
-          float out = peer_load(src);
-          for (uint32_t q = 1; q < cv.world; ++q) out = __fadd_rn(out, peer_load(src + q * src_stride));
+          const uint64_t* src = base + size_t(t) * p.n + row0 + r;
+          float part_of[kCommMaxWorld];
+          uint32_t pending = (1u << cv.world) - 1u;
+          for (uint32_t spin = 0; pending; ++spin) {
+#pragma unroll
+            for (uint32_t q = 0; q < kCommMaxWorld; ++q)
+              if (pending & (1u << q)) {
+                const uint64_t word = peer_load_u64(src + q * src_stride);
+                if (uint32_t(word >> 32) == tp_seq) { part_of[q] = __uint_as_float(uint32_t(word)); pending &= ~(1u << q); }
+              }
+            if (pending && (spin & 63u) == 63u && clock64() - t0 > cv.wait_cycles) {
+              if (atomicOr(&p.status[TBS_FLAGS], TBF_WAIT_TIMEOUT) == 0) { p.status[TBS_INFO0] = blk; p.status[TBS_INFO1] = 700 + pending; }
+              ok = false;
+              break;
+            }
+          }
+          if (!ok) break;
+          float out = part_of[0];
+#pragma unroll
+          for (uint32_t q = 1; q < kCommMaxWorld; ++q)
+            if (q < cv.world) out = __fadd_rn(out, part_of[q]);
           const size_t idx = size_t(t) * p.y_row_stride + row0 + r;
           if (p.residual) out = __fadd_rn(p.residual[idx], out);
           if (p.y_dtype == TB_F32) static_cast<float*>(p.y)[idx] = out;
           else static_cast<__nv_bfloat16*>(p.y)[idx] = __float2bfloat16_rn(out);
         }
+        ok = __all_sync(0xffffffffu, ok);
       }
       // the last CTA to get here closes the round (also after a wait that ran out: the next
       // launch must not wait for a round that was given up)
@@ -1285,10 +1272,7 @@ cudaError_t tb_launch_prepare(const DecodeArgs& a, cudaStream_t stream) {
   pp.m = a.m; pp.mk = layout_tokens(a.m); pp.k = uint32_t(w->k); pp.tpr = uint32_t(w->k / 256); pp.x_dtype = uint32_t(a.x_dtype);
   pp.off_cinit = tl.off_cinit; pp.off_actscale = tl.off_actscale; pp.pdl = a.pdl ? 1u : 0u;
   pp.status = a.status;
-  if (a.comm_absmax) {
-    if (a.comm_absmax->counters < a.m) return cudaErrorInvalidValue;
-    pp.comm = *a.comm_absmax;
-  }
+  if (a.comm_absmax) pp.comm = *a.comm_absmax;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(pp.tpr, a.m);
   cfg.blockDim = dim3(256);
@@ -1336,7 +1320,6 @@ cudaError_t tb_launch_decode(const DecodeArgs& a, int sm_count, int max_smem, cu
   p.residual = a.residual;
   if (a.comm_y && a.comm_y->world > 1) {
     if (a.layers || a.layer_count > 1 || a.acc_dump) return cudaErrorInvalidValue;
-    if (a.comm_y->counters < kCommBlockCounter0 + w->plan.blocks) return cudaErrorInvalidValue;
     p.tp = 1; p.comm_y = *a.comm_y;
     if (a.fused && a.comm_absmax) p.comm_absmax = *a.comm_absmax;
   }

@@ -97,13 +97,14 @@ cudaError_t tb_launch_check_finite(const float* x, uint64_t count, uint32_t* sta
 // its flag words (this rank's own pointers at index `rank`).  world <= 1 means "no peers".
 // Flag words of a slot: [0,8) one-shot flags, 8 epoch, 9 block counter (one-shot reduce);
 // 10 epoch, 11 block counter (fused kernels); 16.. arrival counters, one per token or row block.
-// 12 epoch, 13 block counter (exchanges inside the decode kernel); counters 0..3 belong to the
-// preparation kernel's tokens, counters 4.. to the decode kernel's row blocks.
+// 12 epoch, 13 block counter (exchanges inside the decode kernel).
 constexpr uint32_t kCommMaxWorld = 8, kCommFusedEpoch = 10, kCommFusedDone = 11, kCommDecodeEpoch = 12, kCommDecodeDone = 13,
-                   kCommCounters = 16, kCommBlockCounter0 = 4;
+                   kCommCounters = 16;
 // Byte offset, inside the absmax slot, of the words the decode kernel's absmax exchange uses:
 // uint64 [round parity][source rank][token] = (round << 32) | float bits.
-constexpr uint32_t kCommAbsmaxWords = 64, kCommAbsmaxBytes = kCommAbsmaxWords + 2 * kCommMaxWorld * 4 * 8;
+// (the decode kernel's words first, then the preparation kernel's: the two count rounds separately)
+constexpr uint32_t kCommAbsmaxWords = 64, kCommAbsmaxWordsPrepare = kCommAbsmaxWords + 2 * kCommMaxWorld * 4 * 8,
+                   kCommAbsmaxBytes = kCommAbsmaxWordsPrepare + 2 * kCommMaxWorld * 4 * 8;
 struct TbCommView {
   float* data[kCommMaxWorld];
   uint32_t* flags[kCommMaxWorld];
@@ -136,8 +137,8 @@ struct DecodeArgs {
   // through `comm_absmax`.  Null = no peers.
   const TbCommView* comm_absmax;
   // Row shard whose outputs are summed over the ranks inside the decode kernel: every CTA pushes
-  // its partial rows into all ranks' copies of this slot, signals the row block's counter, and sums
-  // the block once all ranks' partials have arrived.  Fused launches exchange the absmax the same
+  // its partial rows, each value tagged with the round, into all ranks' copies of this slot, and
+  // sums a row block once all ranks' values of this round have arrived.  Fused launches exchange the absmax the same
   // way (through comm_absmax).  Null = no peers.  Every rank must make the same launch.
   const TbCommView* comm_y;
   uint32_t inject_missing_tx;   // test hook (non-fused launches): the table barrier expects this many bytes too many

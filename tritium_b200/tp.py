@@ -252,7 +252,7 @@ class TPLinear:
             return y
         absmax = self.absmax[:m]
         if self.comm is not None and self.fused and m <= 8 and \
-                2 * self.world * min(m, 4) * self.geometry.n * 4 <= self.comm.slot_bytes:
+                2 * self.world * min(m, 4) * self.geometry.n * 8 <= self.comm.slot_bytes:
             self.comm.linear_fused(self.handle, self.slot_absmax, self.slot_y, x, y, flags=getattr(self.executor, "flags", 0))
             return y
         if self.comm is not None and m <= self.peer_m:
