@@ -298,6 +298,11 @@ def measure_tp(torch, dist, backend, rank: int, world: int, codec, codec_name: s
     t0 = time.perf_counter()
     stack = tp.TPDecoderStack(ex, shape, codec, rank, world, max_m=max_m, distinct_layers=built, synthetic_shards=True)
     out["build_seconds"] = time.perf_counter() - t0
+    if args.tp_reduce_chunk:
+        for row in stack.layers:
+            for lin in row:
+                lin.reduce_chunk_tokens = args.tp_reduce_chunk
+        out["prefill_reduce_chunk_tokens"] = args.tp_reduce_chunk
     bytes_rank = stack.weight_bytes()
     steps = max(3, min(args.steps, 20))
 
@@ -573,6 +578,7 @@ def main() -> None:
     ap.add_argument("--no-tp", action="store_true", help="skip the tensor-parallel decoder-stack leg")
     ap.add_argument("--tp-prefill-m", type=int, default=4096, help="tokens of the tensor-parallel prefill pass (0 = skip)")
     ap.add_argument("--tp-shape", default="27b", choices=["27b", "2b"], help="decoder whose linears the tensor-parallel leg runs")
+    ap.add_argument("--tp-reduce-chunk", type=int, default=0, help="tensor-parallel prefill: reduce chunks of this many tokens on a second stream (0 = one reduce per linear)")
     ap.add_argument("--tp-batches", default="1,32", help="comma-separated decode batch sizes of the tensor-parallel leg")
     ap.add_argument("--quick", action="store_true", help="headline legs only (no single-layer, per-linear, INT8-peak and 2B-stack legs)")
     args = ap.parse_args()

@@ -57,6 +57,7 @@ def rank_main(rank, world, port, codec_value, use_peer, results):
                 row.input_view(m).copy_(torch.from_numpy(np.ascontiguousarray(x[:, g.k_offset:g.k_offset + g.k_valid])).to(torch.bfloat16))
                 assert (row.comm is not None) == bool(use_peer)
                 row.fused = use_peer >= 2
+                row.reduce_chunk_tokens = 16      # m = 40 without a communicator: three chunks, reduced on the second stream
                 for _ in range(3):          # repeated rounds on the same slots
                     y_row = row.forward(m)
                 stream.synchronize()
