@@ -272,6 +272,72 @@ def measure_int8_peak(torch) -> dict | None:
         return {"tops": None, "how": f"torch._int_mm unavailable: {type(exc).__name__}: {exc}"[:200]}
 
 
+def measure_reference_gpu_kernels(torch, backend, stream) -> dict:
+    """The reference's own CUDA kernels (built from its sources into oracle/_ref) beside this
+    library's kernels, on the same GPU, the same 1-plane TQ2_0-class weights with a per-channel
+    scale, the same int8 activations.  Decode: tq2_0_add_mpgemm_tiled_i8_scaled against the decode
+    kernel; many tokens: tq2_0_imma_mpgemm (the ahead-of-time tile; the reference's autotuned tiles
+    are rendered by its Rust host and cannot be built here) against the tensor-core kernel.
+    A set of distinct weight copies larger than L2 rotates under both."""
+    from oracle import ref_kernels
+    from tritium_b200.backend import GemmShape, TernaryFormat
+    from tritium_b200.format import pack_tq2_0_rows
+    if not ref_kernels.available():
+        return {"unavailable": "oracle/_ref holds no built reference kernels"}
+    ref = ref_kernels.ReferenceKernels()
+    out = {"weights": "1 plane, TQ2_0 rows (66 bytes per 256 trits), per-channel fp32 scale; int8 activations resident",
+           "timing": "CUDA events over back-to-back launches on one stream, rotating weight copies > 126 MB L2"}
+    rng = np.random.default_rng(3)
+
+    def timed(fn, iters):
+        for _ in range(3):
+            fn(0)
+        stream.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(iters):
+            fn(i)
+        e1.record(stream)
+        stream.synchronize()
+        return e0.elapsed_time(e1) / iters * 1e3      # microseconds per launch
+
+    for name, m, n, k in [("c2_shape_m1", 1, 6912, 2560), ("gate_up_27b_m1", 1, 34816, 5120), ("c2_shape_m2048", 2048, 6912, 2560)]:
+        trits = rng.integers(-1, 2, (n, k)).astype(np.int8)
+        rows = pack_tq2_0_rows(trits)
+        copies = max(2, int(np.ceil(300e6 / len(rows)))) if m == 1 else 2
+        with torch.cuda.stream(stream):
+            w_rows = [torch.from_numpy(np.frombuffer(rows, np.uint8).copy()).cuda() for _ in range(copies)]
+            handles = [backend.upload_weights(rows, GemmShape(m, n, k), TernaryFormat.Tq2_0) for _ in range(copies)]
+            backend.reserve(handles[0], m)
+            q = torch.randint(-127, 128, (m, k), dtype=torch.int8, device="cuda")
+            a_s = torch.rand(m, device="cuda") + 0.5
+            w_s = torch.rand(n, device="cuda") + 0.5
+            y_ref = torch.zeros(m, n, device="cuda")
+            y_own = torch.zeros(m, n, device="cuda")
+            entry = {"m": m, "n": n, "k": k, "weight_copies": copies, "packed_row_bytes": len(rows)}
+            if m == 1:
+                us_ref = timed(lambda i: ref.decode_gemv(q, w_rows[i % copies], w_s, a_s, y_ref, m, n, k, stream), 20 * copies)
+                entry["reference_kernel"] = "tq2_0_add_mpgemm_tiled_i8_scaled"
+            else:
+                w_tiles = [torch.from_numpy(ref_kernels.pack_i2s_int8(trits)).cuda() for _ in range(copies)]
+                us_ref = timed(lambda i: ref.imma_gemm(q, w_tiles[i % copies], a_s, w_s, y_ref, m, n, k, stream), 4)
+                entry["reference_kernel"] = "tq2_0_imma_mpgemm (ahead-of-time tile)"
+            us_own = timed(lambda i: backend.forward_dev(handles[i % copies], q, y_own, a8=True, act_scale=a_s, row_scale=w_s,
+                                                         stream=stream), 20 * copies if m == 1 else 10)
+            backend.check(stream)
+            entry["same_result"] = bool(torch.allclose(y_ref, y_own, rtol=3e-7, atol=0))
+        entry.update({"reference_us": us_ref, "this_library_us": us_own, "speedup": us_ref / us_own})
+        if m == 1:
+            entry["reference_gbs"] = len(rows) / us_ref / 1e3
+            entry["this_library_gbs"] = len(rows) / us_own / 1e3
+        else:
+            entry["reference_tops"] = 2.0 * m * n * k / us_ref / 1e6
+            entry["this_library_tops"] = 2.0 * m * n * k / us_own / 1e6
+        out[name] = entry
+        del w_rows, handles
+    return out
+
+
 def measure_tp(torch, dist, backend, rank: int, world: int, codec, codec_name: str, args, stream,
                shape_name: str = "27b", batches=(1,), m_prefill: int = 0, reduce_variants: bool = True) -> dict:
     """Tensor-parallel leg: the linears of the 27B-class decoder (64 layers x {QKV 5120->7168,
@@ -500,6 +566,13 @@ def run_b200(args) -> None:
                 prefill["roofline"]["int8_gemm_peak_measured"] = int8_peak
                 prefill["roofline"]["frac_of_measured_int8_gemm"] = prefill["roofline"]["achieved"] / int8_peak["tops"]
 
+    ref_gpu = None
+    if world == 1 and not args.quick:
+        try:
+            ref_gpu = measure_reference_gpu_kernels(torch, backend, stream)
+        except Exception as exc:  # a measuring stick must not take the benchmark down with it
+            ref_gpu = {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
+
     tp_leg = stack_2b = None
     if not args.no_tp:
         batches = [int(v) for v in args.tp_batches.split(",") if v]
@@ -549,6 +622,7 @@ def run_b200(args) -> None:
             "single_layer": single,
             "e2e_per_linear": e2e_linear,
             "prefill": prefill,
+            "reference_gpu_kernels": ref_gpu,
             "tp": tp_leg,
             "stack_2b": stack_2b,
         }

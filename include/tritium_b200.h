@@ -90,6 +90,10 @@ tb_status tb_last_shape_mismatch(uint64_t* expected, uint64_t* got);
  * (crates/tritium-cuda/src/cuda/backend.rs:9087-9100, crates/tritium-runtime/src/lib.rs:74-86).
  * Returns TB_BACKEND (never aborts) when no device exists. */
 tb_status tb_backend_create(int ordinal, tb_backend** out);
+/* Handles may be dropped in any order (a Rust binding's Drop order is the owner's, not ours):
+ * while weights, stacks or communicators of this backend are alive, tb_backend_free only marks
+ * the context released (every later call on it fails with TB_INVALID_INPUT, except the free calls
+ * of its objects) and the last of those objects to be freed destroys it. */
 void tb_backend_free(tb_backend* backend);
 /* TernaryBackend::capabilities (crates/tritium-spec/src/lib.rs:166-185). */
 tb_status tb_backend_caps(const tb_backend* backend, tb_caps* out);

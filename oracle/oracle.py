@@ -31,6 +31,18 @@ def build(force: bool = False) -> str:
     return _LIB_PATH
 
 
+_REF_ROOT = os.environ.get("TRITIUM_REFERENCE", "/root/reference")
+
+
+def build_reference_kernels() -> list:
+    """Compile the reference's own TQ2_0 CUDA kernels into ``_ref/*.fatbin`` with the committed
+    Makefile, where the reference checkout exists; otherwise return whatever was built before."""
+    ref_dir = os.path.join(_HERE, "_ref")
+    if os.path.isdir(os.path.join(_REF_ROOT, "crates", "tritium-cuda", "kernels")):
+        subprocess.check_call(["make", "-C", _HERE, f"REF={_REF_ROOT}", "ref-kernels"], stdout=subprocess.DEVNULL)
+    return sorted(f for f in (os.listdir(ref_dir) if os.path.isdir(ref_dir) else []) if f.endswith(".fatbin"))
+
+
 class _CTensor(C.Structure):
     _fields_ = [
         ("rows", C.c_uint64), ("cols", C.c_uint64), ("rank", C.c_uint32), ("group", C.c_uint32),

@@ -316,3 +316,30 @@ def test_residual_epilogue_alone_and_argument_checks(backend):
         backend.norm_linear_forward_dev(resident, x_dev, y, norm_weight=torch.ones(k, device="cuda"), eps=float("nan"))
     with pytest.raises(KeyError):
         backend.norm_linear_forward_dev(resident, torch.zeros(m, k, dtype=torch.int8, device="cuda"), y)
+
+
+def test_backend_freed_before_its_weights():
+    """Handles may be dropped in any order: freeing the backend first leaves the weights' free call
+    valid, refuses further work on the released context, and poisons nothing for the next context."""
+    import torch
+    from tritium_b200 import B200Backend
+    first = B200Backend(0)
+    prod, orac = uniform_pair(64, 512, 2, seed=3)
+    resident = first.upload_salt_v2(prod, SaltV2Codec.B3)
+    released = C.c_void_p(first._h.value)
+    first.close()                                   # the context is only marked released
+    x_dev = torch.zeros(1, 512, dtype=torch.bfloat16, device="cuda")
+    y_dev = torch.zeros(1, 64, dtype=torch.float32, device="cuda")
+    args = _lib.ForwardArgs()
+    args.x, args.x_dtype, args.m, args.y, args.y_dtype, args.flags = x_dev.data_ptr(), _lib.TB_BF16, 1, y_dev.data_ptr(), _lib.TB_F32, _lib.TB_FWD_A8
+    # the pointer stays valid while the weights live, and work on it is refused
+    assert _lib.load().tb_linear_forward_dev(released, resident._h, C.byref(args), None) == _lib.TB_INVALID_INPUT
+    assert "freed" in _lib.last_error()
+    resident.free()                                 # the last dependant destroys the released context
+    second = B200Backend(0)
+    prod2, orac2 = uniform_pair(64, 512, 2, seed=4)
+    again = second.upload_salt_v2(prod2, SaltV2Codec.B3)
+    x = make_activations(40, 512, seed=1, bf16=True)   # the tensor-core route checks the runtime's last error first
+    y, _, _ = second.linear_forward_a8(again, x, 40, x_is_bf16=False)
+    assert rel_l2(y, orc.a8_linear(orac2, x, dump=False)[0]) <= 1e-5
+    second.close()

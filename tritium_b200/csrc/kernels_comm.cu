@@ -131,6 +131,7 @@ extern "C" tb_status tb_comm_create(tb_backend* b, uint32_t world, uint32_t rank
                                     uint32_t counters_per_slot, tb_comm** out) {
   if (!b || !out) return tb_fail(TB_NULL_ARG, "null argument");
   *out = nullptr;
+  if (b->released.load()) return tb_fail(TB_INVALID_INPUT, "the backend context was freed");
   if (world == 0 || world > kMaxWorld || rank >= world) return tb_fail(TB_INVALID_INPUT, "world must be 1..8 and rank below it");
   if (slots == 0 || slot_bytes == 0) return tb_fail(TB_INVALID_INPUT, "a communicator needs at least one slot of at least one byte");
   if (cudaSetDevice(b->ordinal) != cudaSuccess) return tb_fail(TB_BACKEND, "select device");
@@ -149,6 +150,7 @@ extern "C" tb_status tb_comm_create(tb_backend* b, uint32_t world, uint32_t rank
   }
   c->base[rank] = static_cast<uint8_t*>(mem);
   c->connected = world == 1;
+  tb_backend_retain(b);
   *out = c;
   return TB_OK;
 }
@@ -249,5 +251,7 @@ extern "C" void tb_comm_free(tb_comm* c) {
   if (!c) return;
   tb_comm_disconnect(c);
   cudaFree(c->base[c->rank]);
+  tb_backend* owner = c->owner;
   delete c;
+  tb_backend_release(owner);
 }

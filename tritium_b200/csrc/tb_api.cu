@@ -109,14 +109,28 @@ extern "C" tb_status tb_backend_create(int ordinal, tb_backend** out) {
   return TB_OK;
 }
 
+namespace {
+void destroy_backend(tb_backend* b);
+}
+void tb_backend_retain(tb_backend* b) { if (b) b->dependants.fetch_add(1); }
+void tb_backend_release(tb_backend* b) {
+  if (b && b->dependants.fetch_sub(1) == 1 && b->released.load()) destroy_backend(b);
+}
+
 extern "C" void tb_backend_free(tb_backend* b) {
-  if (!b) return;
+  if (!b || b->released.exchange(true)) return;
+  if (b->dependants.load() == 0) destroy_backend(b);   // otherwise the last dependant does it
+}
+
+namespace {
+void destroy_backend(tb_backend* b) {
   cudaSetDevice(b->ordinal);
   if (b->stream) { cudaStreamSynchronize(b->stream); cudaStreamDestroy(b->stream); }
   cudaFree(b->d_status); cudaFreeHost(b->h_status);
   cudaFree(b->d_x); cudaFree(b->d_y); cudaFree(b->d_aux); cudaFree(b->d_q); cudaFree(b->d_prep); cudaFree(b->d_norm); cudaFreeHost(b->h_pin);
   delete b;
 }
+}  // namespace
 
 extern "C" tb_status tb_backend_caps(const tb_backend* b, tb_caps* out) {
   clear_error();
@@ -183,7 +197,7 @@ tb_status upload_resident(tb_backend* b, const tbf::Resident& r, uint64_t source
   if (tb_status s = use_device(b)) return s;
   tb_weights* w = new (std::nothrow) tb_weights();
   if (!w) return tb_fail(TB_OUT_OF_MEMORY, "host allocation failed");
-  w->owner = b; w->codec = r.codec; w->group = r.group; w->uniform_planes = r.uniform_planes;
+  w->owner = b; tb_backend_retain(b); w->codec = r.codec; w->group = r.group; w->uniform_planes = r.uniform_planes;
   w->n = r.n; w->k = r.k; w->tiles = r.tiles; w->present_planes = r.present_planes;
   w->payload_bytes = r.payload.size(); w->scale_count = r.scales.size();
   w->map_bytes = r.map.size(); w->rank_prefix_bytes = r.rank_prefix.size() * 4;
@@ -306,7 +320,9 @@ extern "C" void tb_weights_free(tb_weights* w) {
   if (!w) return;
   if (w->owner) cudaSetDevice(w->owner->ordinal);
   cudaFree(w->d_payload); cudaFree(w->d_scales); cudaFree(w->d_meta); cudaFree(w->d_tile_rank);
+  tb_backend* owner = w->owner;
   delete w;
+  tb_backend_release(owner);
 }
 
 // ---------------------------------------------------------------- forward
@@ -325,6 +341,7 @@ size_t dtype_size(tb_dtype t) { return t == TB_F32 ? 4 : t == TB_BF16 ? 2 : 1; }
 
 tb_status check_handles(const tb_backend* b, const tb_weights* w) {
   if (!b || !w) return tb_fail(TB_NULL_ARG, "null argument");
+  if (b->released.load()) return tb_fail(TB_INVALID_INPUT, "the backend context was freed; only its objects' free calls are still valid");
   if (w->owner != b) return tb_fail(TB_INVALID_INPUT, "weights handle belongs to another backend context");
   return TB_OK;
 }
@@ -721,6 +738,7 @@ extern "C" tb_status tb_stack_create(tb_backend* b, const tb_weights* const* wei
   clear_error();
   if (!b || !weights || !out) return tb_fail(TB_NULL_ARG, "null argument");
   *out = nullptr;
+  if (b->released.load()) return tb_fail(TB_INVALID_INPUT, "the backend context was freed");
   if (!layers || !max_m) return tb_fail(TB_INVALID_INPUT, "a stack needs at least one layer and one token");
   if (tb_status s = use_device(b)) return s;
   tb_stack* st = new (std::nothrow) tb_stack();
@@ -738,6 +756,7 @@ extern "C" tb_status tb_stack_create(tb_backend* b, const tb_weights* const* wei
     widest = std::max<uint64_t>(widest, w->n);
     if (tb_status s = reserve_prefill(b, w, max_m)) { delete st; return s; }
   }
+  tb_backend_retain(b);   // from here on every exit goes through tb_stack_free
   st->group_of.assign(layers, -1);
   auto same_geometry = [](const tb_weights* p, const tb_weights* q) {
     return p->k == q->k && p->n == q->n && p->codec == q->codec && p->uniform_planes == q->uniform_planes &&
@@ -902,7 +921,9 @@ extern "C" void tb_stack_free(tb_stack* st) {
   if (st->backend) cudaSetDevice(st->backend->ordinal);
   for (StackGroup& g : st->groups) { cudaFree(g.d_descs); cudaFree(g.y); }
   cudaFree(st->buf[0]); cudaFree(st->buf[1]);
+  tb_backend* owner = st->backend;
   delete st;
+  tb_backend_release(owner);
 }
 
 // ---------------------------------------------------------------- tensor-parallel shards (host)

@@ -3,6 +3,8 @@
 
 #include <cuda_runtime.h>
 
+#include <atomic>
+
 #include <cstdint>
 #include <string>
 
@@ -42,6 +44,11 @@ struct tb_backend {
   // normalised activations, for norm+linear calls whose tables the decode kernel does not build itself
   void* d_norm = nullptr; size_t d_norm_cap = 0;
   int max_smem_optin = 0;
+  // Weights, stacks and communicators point back at their backend.  tb_backend_free only marks
+  // the context released while such objects are alive; the last of them to go destroys it, so that
+  // a caller may drop its handles in any order.
+  std::atomic<uint32_t> dependants{0};
+  std::atomic<bool> released{false};
   uint32_t inject_missing_tx = 0;   // test hook: armed by tb_backend_inject_wait_timeout, used once
 };
 
@@ -74,6 +81,9 @@ struct tb_weights {
 
 void tb_set_error(const std::string& message);
 void tb_clear_error();
+// An object that keeps a pointer to `b` calls retain when it is created and release when it is freed.
+void tb_backend_retain(tb_backend* b);
+void tb_backend_release(tb_backend* b);
 tb_status tb_fail(tb_status code, const std::string& message);
 tb_status tb_cuda_fail(cudaError_t err, const char* what);
 
