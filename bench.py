@@ -280,6 +280,7 @@ def measure_reference_gpu_kernels(torch, backend, stream) -> dict:
     are rendered by its Rust host and cannot be built here) against the tensor-core kernel.
     A set of distinct weight copies larger than L2 rotates under both."""
     from oracle import ref_kernels
+    from tritium_b200 import _lib
     from tritium_b200.backend import GemmShape, TernaryFormat
     from tritium_b200.format import pack_tq2_0_rows
     if not ref_kernels.available():
@@ -325,6 +326,12 @@ def measure_reference_gpu_kernels(torch, backend, stream) -> dict:
             us_own = timed(lambda i: backend.forward_dev(handles[i % copies], q, y_own, a8=True, act_scale=a_s, row_scale=w_s,
                                                          stream=stream), 20 * copies if m == 1 else 10)
             backend.check(stream)
+            if m == 1:
+                # what a caller of this library gets on a stream of dependent launches: the weight
+                # stream of a launch starts under the previous launch's tail
+                entry["this_library_pdl_us"] = timed(lambda i: backend.forward_dev(
+                    handles[i % copies], q, y_own, a8=True, act_scale=a_s, row_scale=w_s, flags=_lib.TB_FWD_PDL, stream=stream), 20 * copies)
+                backend.check(stream)
             entry["same_result"] = bool(torch.allclose(y_ref, y_own, rtol=3e-7, atol=0))
         entry.update({"reference_us": us_ref, "this_library_us": us_own, "speedup": us_ref / us_own})
         if m == 1:
@@ -601,6 +608,19 @@ def run_b200(args) -> None:
             sec = cpu_forward_time(tensor, x, 1, reps)
             cpu = {"value": layer_bytes / sec / 1e9, "unit": UNIT, "cores": 1, "kind": "port",
                    "sample": f"best of {reps} single-thread oracle forwards of one C2 layer (M={m}), {sec * 1e3:.0f} ms each"}
+            # the reference's default host path for TQ2_0 weights (mpgemm_with_act_quant,
+            # crates/tritium-spec/src/lib.rs:266-318) on the same shape, one plane
+            from oracle import oracle as orc
+            rng = np.random.default_rng(9)
+            trits1 = rng.integers(-1, 2, (N_ROWS, K_COLS)).astype(np.int8)
+            ch_scale = rng.uniform(0.5, 2.0, N_ROWS).astype(np.float32)
+            t_best = float("inf")
+            for _ in range(reps):
+                t0 = time.perf_counter()
+                orc.mpgemm_with_act_quant(x[:1], trits1, ch_scale, 1, N_ROWS, K_COLS)
+                t_best = min(t_best, time.perf_counter() - t0)
+            cpu["tq2_0_trait_path"] = {"ms_per_forward": t_best * 1e3, "packed_gbs": N_ROWS * (K_COLS // 256) * 66 / t_best / 1e9,
+                                       "what": "oracle port of mpgemm_with_act_quant, 1 plane, per-channel scale, M=1, single thread"}
         line = {
             "metric": METRIC if m == 1 else f"ternary linear HBM GB/s (M={m})", "value": value, "unit": UNIT,
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,

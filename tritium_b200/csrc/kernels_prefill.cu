@@ -36,17 +36,26 @@
 namespace {
 
 constexpr int kRows = 128;        // weight rows per tile (UMMA M)
-constexpr int kStagesA = 4;       // expanded slabs in flight
+// Expanded slabs in flight.  With several expander groups working on consecutive tile-planes at
+// once, a group's wait on a ring slot must never be more than one phase ahead of the slot's
+// barrier: eight slots for three groups (six slabs in flight) keep it so.
+__host__ __device__ constexpr int stages_a(int exp_groups) { return exp_groups > 1 ? 8 : 4; }
 constexpr int kStagesB = 2;       // tile columns of activations in flight (two slabs each)
-constexpr int kEpilogueWarps = 16, kExpandWarps = 4;   // epilogue: two column parts per accumulator half and lane quadrant
-constexpr int kFirstEpilogueWarp = 4, kFirstExpandWarp = kFirstEpilogueWarp + kEpilogueWarps;
-constexpr int kThreads = 32 * (kFirstExpandWarp + kExpandWarps);   // warps: 0 TMA, 1-2 MMA issue (1 owns TMEM), 3 idle, then epilogue, then expanders
+// Warps: 0 TMA, 1-2 MMA issue (1 owns TMEM), 3 idle, then EPI epilogue warps, then 4 x EXP expander
+// warps (a group of four warps expands one 128-row slab).  Two configurations, both 768 threads:
+//   many tokens (tiles of 128 or 256): EPI = 16 (two column parts per accumulator half and lane
+//     quadrant: the drain bounds the kernel), EXP = 1;
+//   few tokens (tiles of 32 or 64):    EPI = 8 (the drain is small), EXP = 3 (the kernel is bound by
+//     how fast the weights can be expanded, which has to keep up with HBM).
+constexpr int kFirstEpilogueWarp = 4, kGroupWarps = 4;
+__host__ __device__ constexpr int threads_of(int epi, int exp_groups) { return 32 * (kFirstEpilogueWarp + epi + kGroupWarps * exp_groups); }
 constexpr uint32_t kSpin = 1u << 22;
 constexpr uint32_t kBarFull = 1, kBarEmpty = 3;                 // named barriers kBarFull + half, kBarEmpty + half
-constexpr uint32_t kHandoffThreads = 32 + 32 * kEpilogueWarps / 2;   // one MMA warp + the epilogue warps of its half
+constexpr uint32_t kBarEpilogue = 5;                              // all epilogue warps (split-K combine)
 constexpr long long kWaitCycles = 2000000000ll;
 constexpr uint32_t kMagicBits = 0x4B400000u;   // float 12582912 = 2^23 + 2^22
 constexpr uint32_t kTileABytes = kRows * 128;
+constexpr uint32_t kMaxSplitTiles = 256;   // arrival counters the backend keeps for split output tiles
 
 struct PrefillParams {
   const uint8_t* payload; const uint16_t* scales;
@@ -55,6 +64,11 @@ struct PrefillParams {
   uint32_t* status;
   uint32_t m, m_pad, n, k, tpr, y_dtype;
   uint32_t n_tiles, m_tiles;
+  // Split K: `splits` CTAs share an output tile, each walks a range of tile columns and leaves its
+  // fp32 running sums in `partial` [split][m_pad][n]; the last of them to finish (a counter per
+  // tile) adds the parts in split order and finishes the outputs.  splits == 1: none of this.
+  uint32_t splits;
+  float* partial; uint32_t* tile_counters;
 };
 
 // ---------------------------------------------------------------- PTX helpers
@@ -121,13 +135,14 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(saddr(bar)) : "memory");
 }
-// D[tmem] += A[smem] * B[smem], int8 operands, int32 accumulate (accumulate flag always set: the
-// accumulator was pre-loaded by the epilogue).
-__device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
+// D[tmem] (+)= A[smem] * B[smem], int8 operands, int32 accumulate.  The many-token kernel always
+// accumulates (its epilogue pre-loads the accumulator); the few-token kernel overwrites with the
+// first K step of a slab.
+__device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate = 1u) {
   asm volatile(
       "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
       " tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n"
-      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(1u), "r"(0u) : "memory");
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
 }
 #define TB_R16(a, o) "=r"(a[o+0]), "=r"(a[o+1]), "=r"(a[o+2]), "=r"(a[o+3]), "=r"(a[o+4]), "=r"(a[o+5]), "=r"(a[o+6]), "=r"(a[o+7]), \
                      "=r"(a[o+8]), "=r"(a[o+9]), "=r"(a[o+10]), "=r"(a[o+11]), "=r"(a[o+12]), "=r"(a[o+13]), "=r"(a[o+14]), "=r"(a[o+15])
@@ -293,52 +308,29 @@ __device__ __forceinline__ void lds128(uint32_t addr, uint32_t* v) {
   asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "r"(addr));
 }
 
-// HW = tokens per accumulator half (64 or 128); a CTA tile is 128 weight rows x 2*HW tokens.
-template <int CODEC, int PLANES, int HW, bool DUMP>
-__global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map_q) {
-  constexpr uint32_t kTileTokens = 2 * HW;
-  constexpr uint32_t kTileBBytes = kTileTokens * 128;          // one slab of activations
-  constexpr uint32_t kParts = kEpilogueWarps / 8;              // epilogue warps per (half, lane quadrant)
-  constexpr uint32_t kCW = HW / kParts;                        // columns per epilogue thread
-  constexpr int kChunk = 16;
-  constexpr uint32_t kSlabsPerCol = 2 * PLANES;
-  constexpr uint32_t kPlaneBytes = CODEC == tbf::kB3 ? 52 : 64;
-  constexpr uint32_t kIdesc = instr_desc_n(HW);
-  extern __shared__ __align__(1024) uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* tile_a = smem;                                       // kStagesA * 16 KB
-  uint8_t* tile_b = tile_a + kStagesA * kTileABytes;            // kStagesB * 2 slabs
-  int32_t* qinit_s = reinterpret_cast<int32_t*>(tile_b + kStagesB * 2 * kTileBBytes);   // kStagesB * 2 * kTileTokens
-  uint32_t* stage_s = reinterpret_cast<uint32_t*>(qinit_s + kStagesB * 2 * kTileTokens);   // kExpandWarps * 32 rows * 16 words
-  __shared__ uint64_t a_full[kStagesA], a_empty[kStagesA], b_full[kStagesB], b_empty[kStagesB], acc_full[2];
-  __shared__ uint32_t tmem_base_s, abort_flag;
+// work item = (row tile, token tile, K split); a split walks tile columns [j0, j1)
+__device__ __forceinline__ void split_range(const PrefillParams& p, uint32_t tile, uint32_t& j0, uint32_t& j1) {
+  const uint32_t sp = tile % p.splits;
+  j0 = uint32_t(uint64_t(p.tpr) * sp / p.splits);
+  j1 = uint32_t(uint64_t(p.tpr) * (sp + 1) / p.splits);
+}
 
-  const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  if (tid == 0) {
-    abort_flag = 0;
-    for (int s = 0; s < kStagesA; ++s) { mbar_init(&a_full[s], kExpandWarps); mbar_init(&a_empty[s], 2); }
-    for (int s = 0; s < kStagesB; ++s) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 2 + kEpilogueWarps); }
-    for (int s = 0; s < 2; ++s) mbar_init(&acc_full[s], 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(saddr(&tmem_base_s)), "r"(4u * HW) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = tmem_base_s;
-  const uint32_t tiles = p.n_tiles * p.m_tiles;
-
-  const WaitCtx wctx{&abort_flag, p.status};
-  if (warp == 0) {
+// ---------------------------------------------------------------- roles shared by the two kernels
+// Copy warp: the int8 activations of a tile column (two slabs of TILE_TOKENS x 128 bytes) and the
+// per-token start values of its two slabs, into a ring of STAGES_B columns.
+template <uint32_t TILE_TOKENS, int STAGES_B>
+__device__ __forceinline__ void tma_role(const PrefillParams& p, const CUtensorMap& map_q, uint32_t tiles, uint8_t* tile_b, int32_t* qinit_s,
+                                         uint64_t* b_full, uint64_t* b_empty, const WaitCtx& wctx, uint32_t lane) {
+  constexpr uint32_t kTileTokens = TILE_TOKENS, kTileBBytes = TILE_TOKENS * 128;
+  constexpr int kStagesB = STAGES_B;
     // ------------------------------------------------ TMA: activations + start values of a tile column
     if (lane == 0) {
       uint32_t fill = 0;
       for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
-        const uint32_t mt = tile % p.m_tiles;
-        for (uint32_t j = 0; j < p.tpr; ++j, ++fill) {
+        const uint32_t mt = (tile / p.splits) % p.m_tiles;
+        uint32_t j0, j1;
+        split_range(p, tile, j0, j1);
+        for (uint32_t j = j0; j < j1; ++j, ++fill) {
           const uint32_t s = fill % kStagesB, round = fill / kStagesB;
           if (round > 0) mbar_wait(&b_empty[s], (round - 1) & 1, wctx, 300, 400);
           mbar_expect_tx(&b_full[s], 2 * kTileBBytes + 2 * kTileTokens * 4);
@@ -355,42 +347,14 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
         for (uint32_t i = 0; i < kSpin && !mbar_try(&b_full[f % kStagesB], (f / kStagesB) & 1); ++i) {}
       }
     }
-  } else if (warp == 1 || warp == 2) {
-    // ------------------------------------------------ MMA issuers, one warp per accumulator half (issuing a
-    // tcgen05.mma keeps the thread busy for about as long as the MMA runs, so one thread cannot
-    // keep the tensor core fed and also do the waiting); the whole warp walks the loop (so
-    // that addresses and descriptors stay in uniform registers); one elected lane issues
-    const uint32_t h = warp - 1;
-    uint32_t slab = 0, colfill = 0;
-    const uint64_t a_desc0 = smem_desc(saddr(tile_a), 0), b_desc0 = smem_desc(saddr(tile_b), 0);
-    for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
-      for (uint32_t j = 0; j < p.tpr; ++j, ++colfill) {
-        const uint32_t sb = colfill % kStagesB;
-        mbar_wait(&b_full[sb], (colfill / kStagesB) & 1, wctx, 301);
-        for (uint32_t q = 0; q < kSlabsPerCol; ++q, ++slab) {
-          const uint32_t sa = slab % kStagesA, gsel = q & 1;
-          mbar_wait(&a_full[sa], (slab / kStagesA) & 1, wctx, 301);
-          // descriptor start addresses are in 16-byte units
-          const uint64_t a_desc = a_desc0 + uint64_t(sa * (kTileABytes >> 4));
-          const uint64_t b_desc = b_desc0 + uint64_t((sb * 2 + gsel) * (kTileBBytes >> 4)) + uint64_t(h * (HW * 128u >> 4));
-          named_sync(kBarEmpty + h, kHandoffThreads);   // the epilogue has stored the start values
-          tc_fence_after();
-          if (elect_one()) {
-#pragma unroll
-            for (uint32_t kc = 0; kc < 4; ++kc) tc_mma_i8(tmem_base + h * HW, a_desc + 2 * kc, b_desc + 2 * kc, kIdesc);
-            tc_commit(&acc_full[h]);
-            tc_commit(&a_empty[sa]);
-          }
-          __syncwarp();
-          mbar_wait(&acc_full[h], slab & 1, wctx, 301);
-          tc_fence_before();
-          named_arrive(kBarFull + h, kHandoffThreads);
-        }
-        if (elect_one()) tc_commit(&b_empty[sb]);
-        __syncwarp();
-      }
-    }
-  } else if (warp >= kFirstExpandWarp) {
+}
+
+// Expander warps (groups of four: one lane per weight row of the 128-row slab).
+template <int CODEC, int PLANES, int EXP, int STAGES_A>
+__device__ __forceinline__ void expander_role(const PrefillParams& p, uint32_t tiles, uint32_t wexp_all, uint32_t lane, uint8_t* tile_a,
+                                              uint32_t* stage_s, uint64_t* a_full, uint64_t* a_empty, const WaitCtx& wctx) {
+  constexpr int kStagesA = STAGES_A;
+  constexpr uint32_t kPlaneBytes = CODEC == tbf::kB3 ? 52 : 64;
     // ------------------------------------------------ expanders: one weight row per thread
     // Rows are 1.5 KB apart in the arena, so a lane that fetched its own row word by word would
     // touch one sector per load.  Instead the warp fetches its 32 rows' words of a tile-plane as a
@@ -398,32 +362,61 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
     // per-warp staging area, and every lane picks up its own row from there (stride kWords words:
     // odd for B3, conflict-free).  The next tile-plane's words are requested before the current
     // one is expanded.
+    // With EXP > 1 groups, group g expands the tile-planes whose running number is g modulo EXP:
+    // consecutive slabs are then built by different groups at the same time, and the MMA warps
+    // still consume them in order from the ring.
     constexpr uint32_t kWords = kPlaneBytes / 4;
-    const uint32_t wexp = warp - kFirstExpandWarp, r = wexp * 32 + lane;
-    uint32_t* stage = stage_s + wexp * 32 * kWords;
+    const uint32_t grp = wexp_all / kGroupWarps, wexp = wexp_all % kGroupWarps;
+    const uint32_t r = wexp * 32 + lane;
+    uint32_t* stage = stage_s + wexp_all * 32 * kWords;
     const uint32_t row_stride = p.tpr * PLANES * kWords;   // words per weight row
-    uint32_t slab = 0;
+    uint32_t tp_seq = 0;                                   // tile-planes handed to the ring so far (all groups count alike)
     for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
-      const uint32_t nt = tile / p.m_tiles;
+      const uint32_t nt = tile / (p.m_tiles * p.splits);
+      uint32_t j0, j1;
+      split_range(p, tile, j0, j1);
+      const uint32_t count = (j1 - j0) * PLANES, tp0 = j0 * PLANES;   // this item's tile-planes: tp0 .. tp0 + count - 1 of the row
+      const uint32_t first = (grp + EXP - tp_seq % EXP) % EXP;        // the group's first one among them
       const uint32_t* tile_words = reinterpret_cast<const uint32_t*>(p.payload);
       const uint32_t row0 = nt * kRows + wexp * 32;
-      uint32_t pf[kWords];
+      // One load instruction brings the words of kRowsPerIt whole rows (lane -> (row, word) is fixed,
+      // so the address of iteration `it` is a lane constant plus it x a launch constant; lanes past
+      // the last whole row idle: 26 of 32 for B3, all for D2).
+      constexpr uint32_t kRowsPerIt = 32 / kWords, kLanesUsed = kRowsPerIt * kWords, kIts = 32 / kRowsPerIt;
+      const uint32_t lrow = lane / kWords, lwd = lane - lrow * kWords;
+      const bool lane_used = lane < kLanesUsed;
+      const bool whole = row0 + 31 < p.n;   // otherwise rows past the end repeat the last row; never stored
+      const uint32_t* lane_words = tile_words + size_t(min(row0 + lrow, p.n - 1)) * row_stride + lwd;
+      uint32_t pf[kIts];
       auto fetch = [&](uint32_t tp) {
 #pragma unroll
-        for (uint32_t it = 0; it < kWords; ++it) {
-          const uint32_t f = it * 32 + lane, rl = f / kWords, wd = f - rl * kWords;
-          const uint32_t n = min(row0 + rl, p.n - 1);   // rows past the end repeat the last row; never stored
-          pf[it] = __ldg(tile_words + size_t(n) * row_stride + tp * kWords + wd);
+        for (uint32_t it = 0; it < kIts; ++it) {
+          if (!lane_used) continue;
+          const uint32_t* at = whole ? lane_words + size_t(it * kRowsPerIt) * row_stride
+                                     : tile_words + size_t(min(row0 + it * kRowsPerIt + lrow, p.n - 1)) * row_stride + lwd;
+          pf[it] = __ldg(at + tp * kWords);
         }
       };
-      fetch(0);
-      for (uint32_t j = 0; j < p.tpr; ++j) {
-        for (uint32_t pl = 0; pl < PLANES; ++pl, slab += 2) {
+      if (EXP > 1 && grp == 0) {
+        // Few-token kernel: the expansion is bound by how fast the words arrive.  Ask for this item's
+        // whole share of the lane's row (contiguous in the arena) to be brought into L2 now, so that
+        // the loads below meet L2 latency, not HBM latency.
+        const uint32_t n = min(row0 + lane, p.n - 1);
+        const uint8_t* from = reinterpret_cast<const uint8_t*>(tile_words + size_t(n) * row_stride + tp0 * kWords);
+        const uint32_t bytes = count * kWords * 4;
+        for (uint32_t off = 0; off < bytes + 127; off += 128)
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(from + min(off, bytes - 4)));
+      }
+      if (first < count) fetch(tp0 + first);
+      {
+        for (uint32_t i = first; i < count; i += EXP) {
+          const uint32_t slab = 2 * (tp_seq + i);
           uint32_t w[kWords];
 #pragma unroll
-          for (uint32_t it = 0; it < kWords; ++it) stage[it * 32 + lane] = pf[it];
+          for (uint32_t it = 0; it < kIts; ++it)
+            if (lane_used) stage[it * kLanesUsed + lane] = pf[it];
           __syncwarp();
-          if (j * PLANES + pl + 1 < p.tpr * PLANES) fetch(j * PLANES + pl + 1);
+          if (i + EXP < count) fetch(tp0 + i + EXP);
 #pragma unroll
           for (uint32_t i = 0; i < kWords; ++i) w[i] = stage[lane * kWords + i];
           __syncwarp();
@@ -486,7 +479,95 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
           }
         }
       }
+      tp_seq += count;
     }
+}
+
+// HW = tokens per accumulator half (64 or 128); a CTA tile is 128 weight rows x 2*HW tokens.
+template <int CODEC, int PLANES, int HW, bool DUMP, int EPI, int EXP>
+__global__ void __launch_bounds__(threads_of(EPI, EXP), 1) prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map_q) {
+  constexpr int kStagesA = stages_a(EXP);
+  constexpr int kEpilogueWarps = EPI, kFirstExpandWarp = kFirstEpilogueWarp + EPI;
+  constexpr uint32_t kHandoffThreads = 32 + 32 * EPI / 2;      // one MMA warp + the epilogue warps of its half
+  constexpr uint32_t kTileTokens = 2 * HW;
+  constexpr uint32_t kTileBBytes = kTileTokens * 128;          // one slab of activations
+  constexpr uint32_t kParts = kEpilogueWarps / 8;              // epilogue warps per (half, lane quadrant)
+  constexpr uint32_t kCW = HW / kParts;                        // columns per epilogue thread
+  constexpr int kChunk = 16;
+  static_assert(kCW % kChunk == 0, "an epilogue thread drains whole 16-column chunks");
+  constexpr uint32_t kSlabsPerCol = 2 * PLANES;
+  constexpr uint32_t kPlaneBytes = CODEC == tbf::kB3 ? 52 : 64;
+  constexpr uint32_t kIdesc = instr_desc_n(HW);
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* tile_a = smem;                                       // kStagesA * 16 KB
+  uint8_t* tile_b = tile_a + kStagesA * kTileABytes;            // kStagesB * 2 slabs
+  int32_t* qinit_s = reinterpret_cast<int32_t*>(tile_b + kStagesB * 2 * kTileBBytes);   // kStagesB * 2 * kTileTokens
+  uint32_t* stage_s = reinterpret_cast<uint32_t*>(qinit_s + kStagesB * 2 * kTileTokens);   // kExpandWarps * 32 rows * 16 words
+  __shared__ uint64_t a_full[kStagesA], a_empty[kStagesA], b_full[kStagesB], b_empty[kStagesB], acc_full[2];
+  __shared__ uint32_t tmem_base_s, abort_flag, combine_flag;
+
+  const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < kStagesA; ++s) { mbar_init(&a_full[s], kGroupWarps); mbar_init(&a_empty[s], 2); }
+    for (int s = 0; s < kStagesB; ++s) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 2 + kEpilogueWarps); }
+    for (int s = 0; s < 2; ++s) mbar_init(&acc_full[s], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(saddr(&tmem_base_s)), "r"(4u * HW) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+  // work item = (row tile, token tile, K split); a split walks tile columns [j0, j1)
+  const uint32_t tiles = p.n_tiles * p.m_tiles * p.splits;
+
+  const WaitCtx wctx{&abort_flag, p.status};
+  if (warp == 0) {
+    tma_role<kTileTokens, kStagesB>(p, map_q, tiles, tile_b, qinit_s, b_full, b_empty, wctx, lane);
+  } else if (warp == 1 || warp == 2) {
+    // ------------------------------------------------ MMA issuers, one warp per accumulator half (issuing a
+    // tcgen05.mma keeps the thread busy for about as long as the MMA runs, so one thread cannot
+    // keep the tensor core fed and also do the waiting); the whole warp walks the loop (so
+    // that addresses and descriptors stay in uniform registers); one elected lane issues
+    const uint32_t h = warp - 1;
+    uint32_t slab = 0, colfill = 0;
+    const uint64_t a_desc0 = smem_desc(saddr(tile_a), 0), b_desc0 = smem_desc(saddr(tile_b), 0);
+    for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+      uint32_t j0, j1;
+      split_range(p, tile, j0, j1);
+      for (uint32_t j = j0; j < j1; ++j, ++colfill) {
+        const uint32_t sb = colfill % kStagesB;
+        mbar_wait(&b_full[sb], (colfill / kStagesB) & 1, wctx, 301);
+        for (uint32_t q = 0; q < kSlabsPerCol; ++q, ++slab) {
+          const uint32_t sa = slab % kStagesA, gsel = q & 1;
+          mbar_wait(&a_full[sa], (slab / kStagesA) & 1, wctx, 301);
+          // descriptor start addresses are in 16-byte units
+          const uint64_t a_desc = a_desc0 + uint64_t(sa * (kTileABytes >> 4));
+          const uint64_t b_desc = b_desc0 + uint64_t((sb * 2 + gsel) * (kTileBBytes >> 4)) + uint64_t(h * (HW * 128u >> 4));
+          named_sync(kBarEmpty + h, kHandoffThreads);   // the epilogue has stored the start values
+          tc_fence_after();
+          if (elect_one()) {
+#pragma unroll
+            for (uint32_t kc = 0; kc < 4; ++kc) tc_mma_i8(tmem_base + h * HW, a_desc + 2 * kc, b_desc + 2 * kc, kIdesc);
+            tc_commit(&acc_full[h]);
+            tc_commit(&a_empty[sa]);
+          }
+          __syncwarp();
+          mbar_wait(&acc_full[h], slab & 1, wctx, 301);
+          tc_fence_before();
+          named_arrive(kBarFull + h, kHandoffThreads);
+        }
+        if (elect_one()) tc_commit(&b_empty[sb]);
+        __syncwarp();
+      }
+    }
+  } else if (warp >= kFirstExpandWarp) {
+    expander_role<CODEC, PLANES, EXP, kStagesA>(p, tiles, warp - kFirstExpandWarp, lane, tile_a, stage_s, a_full, a_empty, wctx);
   } else if (warp >= kFirstEpilogueWarp) {
     // ------------------------------------------------ epilogue: TMEM lane = weight row; a warp owns one
     // accumulator half, one lane quadrant and a column range of it
@@ -516,18 +597,20 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
       }
     }
     for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
-      const uint32_t nt = tile / p.m_tiles, mt = tile % p.m_tiles;
+      const uint32_t sp = tile % p.splits, out_tile = tile / p.splits, nt = out_tile / p.m_tiles, mt = out_tile % p.m_tiles;
+      uint32_t j0, j1;
+      split_range(p, tile, j0, j1);
       const uint32_t n = nt * kRows + r;
       const uint32_t nc = min(n, p.n - 1);
       const uint16_t* srow = p.scales + size_t(nc) * p.tpr * PLANES * 2;
       const bool more_tiles = tile + gridDim.x < tiles;
-      for (uint32_t j = 0; j < p.tpr; ++j, ++colfill) {
+      for (uint32_t j = j0; j < j1; ++j, ++colfill) {
         const uint32_t sb = colfill % kStagesB;
         for (uint32_t q = 0; q < kSlabsPerCol; ++q, ++slab) {
           const uint32_t gsel = q & 1, pl = q >> 1;
           const float sv = __half2float(__ushort_as_half(srow[(j * PLANES + pl) * 2 + gsel]));
           const float2 scale2 = make_float2(sv, sv), neg_magic2 = make_float2(-12582912.0f, -12582912.0f);
-          const bool last = (j + 1 == p.tpr && q + 1 == kSlabsPerCol);
+          const bool last = (j + 1 == j1 && q + 1 == kSlabsPerCol);
           // where the next slab's start values are
           const bool next_col = q + 1 == kSlabsPerCol;
           const bool has_next = !(last && !more_tiles);
@@ -565,7 +648,16 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
               }
               if (!last) tmem_stn(y_addr + c, yv);
               else {
-                if (n < p.n) {
+                if (p.splits > 1) {
+                  // this split's running sums; the last split of the tile to finish adds them up
+                  if (n < p.n) {
+#pragma unroll
+                    for (int i = 0; i < kChunk; ++i) {
+                      const uint32_t mtok = tok0 + c + i;
+                      if (mtok < p.m) p.partial[(size_t(sp) * p.m_pad + mtok) * p.n + n] = __uint_as_float(yv[i]);
+                    }
+                  }
+                } else if (n < p.n) {
                   const float rs = p.row_scale ? p.row_scale[n] : 1.0f;
 #pragma unroll
                   for (int i = 0; i < kChunk; ++i) {
@@ -592,6 +684,35 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
           }
           // the column's start values and activations are no longer needed by this warp
           if (lane == 0 && next_col) mbar_arrive(&b_empty[sb]);
+          if (last && p.splits > 1) {
+            // Split K: count this split in; whoever completes the count adds the splits' sums in
+            // split order (every run gives the same bits) and finishes the tile's outputs.
+            __threadfence();
+            named_sync(kBarEpilogue, 32 * EPI);
+            if (warp == kFirstEpilogueWarp && lane == 0) {
+              const uint32_t arrived = atomicAdd(p.tile_counters + out_tile, 1u);
+              combine_flag = arrived == p.splits - 1 ? 1u : 0u;
+              if (combine_flag) p.tile_counters[out_tile] = 0u;   // ready for the next launch
+            }
+            named_sync(kBarEpilogue, 32 * EPI);
+            if (combine_flag && n < p.n) {
+              __threadfence();
+              const float rs = p.row_scale ? p.row_scale[n] : 1.0f;
+              const uint32_t tok0 = mt * kTileTokens + wh * HW + part * kCW;
+              for (uint32_t c = 0; c < kCW; ++c) {
+                const uint32_t mtok = tok0 + c;
+                if (mtok >= p.m) break;
+                float sum = __ldcg(p.partial + size_t(mtok) * p.n + n);
+                for (uint32_t s2 = 1; s2 < p.splits; ++s2) sum = __fadd_rn(sum, __ldcg(p.partial + (size_t(s2) * p.m_pad + mtok) * p.n + n));
+                float out = __fmul_rn(sum, __ldg(p.ascale + mtok));
+                if (p.row_scale) out = __fmul_rn(out, rs);
+                const size_t idx = size_t(mtok) * p.n + n;
+                if (p.residual) out = __fadd_rn(__ldg(p.residual + idx), out);
+                if (p.y_dtype == TB_F32) static_cast<float*>(p.y)[idx] = out;
+                else static_cast<__nv_bfloat16*>(p.y)[idx] = __float2bfloat16_rn(out);
+              }
+            }
+          }
         }
       }
     }
@@ -599,6 +720,232 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
   tc_fence_before();
   __syncthreads();
   if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(4u * HW) : "memory");
+}
+
+// ---------------------------------------------------------------- few tokens (up to 64): fewtok_kernel
+// With few tokens the drain is small and the fixed cost of handing an accumulator back and forth
+// once per slab would bound the kernel.  So here: one token tile (TT = 32 or 64 tokens, N of the MMA),
+// a ring of four accumulators in TMEM that the single MMA warp fills without waiting for the
+// epilogue, the first MMA of a slab overwrites (no start values are stored), the running sums live
+// in the epilogue threads' registers (no TMEM traffic but the accumulator loads), and three
+// expander groups build consecutive slabs at once, because what bounds this kernel is how fast the
+// packed weights can be expanded: that has to keep up with HBM.  K is split over CTAs when there
+// are fewer output tiles than SMs.
+//   int -> float of an accumulator: bits(D + (0x4B400000 - sum of the slab's activations)) is the
+//   float 12582912 + I, as in the many-token kernel, but the addend meets D in the epilogue.
+// Warps: 0 copy, 1-2 MMA issue (alternate slabs; 1 owns TMEM), 3 idle, 4..11 epilogue (lane quadrant =
+// warp % 4; warps 4-7 take the first half of the tokens, 8-11 the second), 12..23 expanders.
+constexpr int kFewEpilogueWarps = 8, kFewExpGroups = 3, kFewStagesA = stages_a(kFewExpGroups), kFewStagesB = 4, kFewAccBufs = 4;
+constexpr int kFewFirstExpandWarp = kFirstEpilogueWarp + kFewEpilogueWarps;
+constexpr int kFewThreads = threads_of(kFewEpilogueWarps, kFewExpGroups);
+
+template <int CODEC, int PLANES, int TT, bool DUMP>
+__global__ void __launch_bounds__(kFewThreads, 1) fewtok_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map_q) {
+  constexpr uint32_t kTileBBytes = TT * 128;
+  constexpr uint32_t kCW = TT / 2;                  // columns (tokens) per epilogue thread
+  constexpr uint32_t kChunks = kCW / 16;
+  constexpr uint32_t kSlabsPerCol = 2 * PLANES;
+  constexpr uint32_t kIdesc = instr_desc_n(TT);
+  constexpr uint32_t kTmemCols = kFewAccBufs * TT;  // 128 or 256
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* tile_a = smem;
+  uint8_t* tile_b = tile_a + kFewStagesA * kTileABytes;
+  int32_t* qinit_s = reinterpret_cast<int32_t*>(tile_b + kFewStagesB * 2 * kTileBBytes);
+  uint32_t* stage_s = reinterpret_cast<uint32_t*>(qinit_s + kFewStagesB * 2 * TT);
+  __shared__ uint64_t a_full[kFewStagesA], a_empty[kFewStagesA], b_full[kFewStagesB], b_empty[kFewStagesB];
+  __shared__ uint64_t acc_full[kFewAccBufs], acc_empty[kFewAccBufs];
+  __shared__ uint32_t tmem_base_s, abort_flag, combine_flag;
+
+  const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < kFewStagesA; ++s) { mbar_init(&a_full[s], kGroupWarps); mbar_init(&a_empty[s], 1); }
+    for (int s = 0; s < kFewStagesB; ++s) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 2 + kFewEpilogueWarps); }
+    for (int s = 0; s < kFewAccBufs; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], kFewEpilogueWarps); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(saddr(&tmem_base_s)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+  const uint32_t tiles = p.n_tiles * p.m_tiles * p.splits;
+  const WaitCtx wctx{&abort_flag, p.status};
+
+  // Registers follow the work.  The pool is what the CTA got at launch, 768 x 80: the first
+  // warpgroup (copy, MMA issue, idle) gives back 40 per thread, the two epilogue warpgroups take
+  // 16 more each; 128 x 40 + 256 x 96 + 384 x 80 fits, so no request can block.
+  if (warp == 0) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    tma_role<TT, kFewStagesB>(p, map_q, tiles, tile_b, qinit_s, b_full, b_empty, wctx, lane);
+  } else if (warp == 1 || warp == 2) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    // ------------------------------------------------ MMA issue: two warps take alternate slabs (issuing the four
+    // MMAs of a slab occupies the issuing thread for several hundred clocks, more than the
+    // slab's share of the weight stream allows), each up to two slabs ahead of the epilogue
+    const uint32_t mine = warp - 1;
+    uint32_t slab = 0, colfill = 0;
+    const uint64_t a_desc0 = smem_desc(saddr(tile_a), 0), b_desc0 = smem_desc(saddr(tile_b), 0);
+    for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+      uint32_t j0, j1;
+      split_range(p, tile, j0, j1);
+      for (uint32_t j = j0; j < j1; ++j, ++colfill) {
+        const uint32_t sb = colfill % kFewStagesB;
+        mbar_wait(&b_full[sb], (colfill / kFewStagesB) & 1, wctx, 311);
+        for (uint32_t q = 0; q < kSlabsPerCol; ++q, ++slab) {
+          if ((slab & 1u) != mine) continue;
+          const uint32_t sa = slab % kFewStagesA, gsel = q & 1, buf = slab % kFewAccBufs;
+          mbar_wait(&a_full[sa], (slab / kFewStagesA) & 1, wctx, 312, 32);
+          if (slab >= uint32_t(kFewAccBufs)) mbar_wait(&acc_empty[buf], ((slab / kFewAccBufs) - 1) & 1, wctx, 313);
+          tc_fence_after();
+          const uint64_t a_desc = a_desc0 + uint64_t(sa * (kTileABytes >> 4));
+          const uint64_t b_desc = b_desc0 + uint64_t((sb * 2 + gsel) * (kTileBBytes >> 4));
+          if (elect_one()) {
+#pragma unroll
+            for (uint32_t kc = 0; kc < 4; ++kc) tc_mma_i8(tmem_base + buf * TT, a_desc + 2 * kc, b_desc + 2 * kc, kIdesc, kc > 0 ? 1u : 0u);
+            tc_commit(&acc_full[buf]);
+            tc_commit(&a_empty[sa]);
+          }
+          __syncwarp();
+        }
+        if (elect_one()) tc_commit(&b_empty[sb]);
+        __syncwarp();
+      }
+    }
+  } else if (warp >= kFewFirstExpandWarp) {
+    expander_role<CODEC, PLANES, kFewExpGroups, kFewStagesA>(p, tiles, warp - kFewFirstExpandWarp, lane, tile_a, stage_s, a_full, a_empty, wctx);
+  } else if (warp >= kFirstEpilogueWarp) {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 96;");
+    // ------------------------------------------------ epilogue: TMEM lane = weight row, running sums in registers
+    const uint32_t quad = warp & 3, colhalf = (warp - kFirstEpilogueWarp) >> 2, r = quad * 32 + lane;
+    const uint32_t lane_addr = tmem_base + ((quad * 32u) << 16) + colhalf * kCW;
+    float y[kCW];
+#pragma unroll
+    for (uint32_t i = 0; i < kCW; ++i) y[i] = 0.f;
+    uint32_t slab = 0, colfill = 0;
+    for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+      const uint32_t sp = tile % p.splits, out_tile = tile / p.splits, nt = out_tile / p.m_tiles, mt = out_tile % p.m_tiles;
+      uint32_t j0, j1;
+      split_range(p, tile, j0, j1);
+      const uint32_t n = nt * kRows + r;
+      const uint32_t nc = min(n, p.n - 1);
+      const uint16_t* srow = p.scales + size_t(nc) * p.tpr * PLANES * 2;
+      const uint32_t tok0 = mt * TT + colhalf * kCW;
+      // The row's group scales of a tile column (two f16 per plane) are fetched one column ahead:
+      // a load issued where the scale is needed would stall every slab for a trip to L2.
+      const uint32_t* srow2 = reinterpret_cast<const uint32_t*>(srow);
+      uint32_t sc_next[PLANES];
+#pragma unroll
+      for (int pl = 0; pl < PLANES; ++pl) sc_next[pl] = __ldg(srow2 + j0 * PLANES + pl);
+      for (uint32_t j = j0; j < j1; ++j, ++colfill) {
+        const uint32_t sb = colfill % kFewStagesB;
+        uint32_t sc[PLANES];
+#pragma unroll
+        for (int pl = 0; pl < PLANES; ++pl) {
+          sc[pl] = sc_next[pl];
+          if (j + 1 < j1) sc_next[pl] = __ldg(srow2 + (j + 1) * PLANES + pl);
+        }
+        mbar_wait(&b_full[sb], (colfill / kFewStagesB) & 1, wctx, 314, 64);   // the column's start values are in shared memory
+#pragma unroll
+        for (uint32_t q = 0; q < kSlabsPerCol; ++q, ++slab) {
+          const uint32_t gsel = q & 1, pl = q >> 1, buf = slab % kFewAccBufs;
+          const float sv = __half2float(__ushort_as_half(uint16_t(gsel ? sc[pl] >> 16 : sc[pl] & 0xffffu)));
+          const float2 scale2 = make_float2(sv, sv), neg_magic2 = make_float2(-12582912.0f, -12582912.0f);
+          mbar_wait(&acc_full[buf], (slab / kFewAccBufs) & 1, wctx, 315, 64);   // sleeps between polls: the issue slots belong to the expanders
+          tc_fence_after();
+          uint32_t dv[kChunks][16];
+#pragma unroll
+          for (uint32_t c = 0; c < kChunks; ++c) tmem_ldn(lane_addr + buf * TT + c * 16, dv[c]);
+          tmem_wait_ld();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&acc_empty[buf]);   // the MMA warp may overwrite this accumulator
+          const uint32_t qi = saddr(qinit_s + (sb * 2 + gsel) * TT + colhalf * kCW);
+#pragma unroll
+          for (uint32_t c = 0; c < kChunks; ++c) {
+            uint32_t iv[16];
+#pragma unroll
+            for (int i = 0; i < 16; i += 4) lds128(qi + (c * 16 + i) * 4u, &iv[i]);
+#pragma unroll
+            for (int i = 0; i < 16; i += 2) {
+              const uint32_t b0 = dv[c][i] + iv[i], b1 = dv[c][i + 1] + iv[i + 1];   // bits of 12582912 + I
+              const float2 d = __fadd2_rn(make_float2(__uint_as_float(b0), __uint_as_float(b1)), neg_magic2);
+              const float2 acc = __ffma2_rn(d, scale2, make_float2(y[c * 16 + i], y[c * 16 + i + 1]));
+              y[c * 16 + i] = acc.x; y[c * 16 + i + 1] = acc.y;
+              if (DUMP) {
+                if (n < p.n) {
+                  const uint32_t mtok = tok0 + c * 16 + i;
+                  if (mtok < p.m) p.acc_dump[((size_t(mtok) * p.n + n) * (p.tpr * 2) + 2 * j + gsel) * PLANES + pl] = int(b0) - int(kMagicBits);
+                  if (mtok + 1 < p.m) p.acc_dump[((size_t(mtok + 1) * p.n + n) * (p.tpr * 2) + 2 * j + gsel) * PLANES + pl] = int(b1) - int(kMagicBits);
+                }
+              }
+            }
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&b_empty[sb]);
+      }
+      // ---- the tile (or this split of it) is complete
+      if (n < p.n) {
+        const float rs = p.row_scale ? p.row_scale[n] : 1.0f;
+#pragma unroll
+        for (uint32_t i = 0; i < kCW; ++i) {
+          const uint32_t mtok = tok0 + i;
+          if (mtok < p.m) {
+            if (p.splits > 1) {
+              p.partial[(size_t(sp) * p.m_pad + mtok) * p.n + n] = y[i];
+            } else {
+              float out = __fmul_rn(y[i], __ldg(p.ascale + mtok));
+              if (p.row_scale) out = __fmul_rn(out, rs);
+              const size_t idx = size_t(mtok) * p.n + n;
+              if (p.residual) out = __fadd_rn(__ldg(p.residual + idx), out);
+              if (p.y_dtype == TB_F32) static_cast<float*>(p.y)[idx] = out;
+              else static_cast<__nv_bfloat16*>(p.y)[idx] = __float2bfloat16_rn(out);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (uint32_t i = 0; i < kCW; ++i) y[i] = 0.f;
+      if (p.splits > 1) {
+        // Split K: count this split in; whoever completes the count adds the splits' sums in split
+        // order (every run gives the same bits) and finishes the tile's outputs.
+        __threadfence();
+        named_sync(kBarEpilogue, 32 * kFewEpilogueWarps);
+        if (warp == kFirstEpilogueWarp && lane == 0) {
+          const uint32_t arrived = atomicAdd(p.tile_counters + out_tile, 1u);
+          combine_flag = arrived == p.splits - 1 ? 1u : 0u;
+          if (combine_flag) p.tile_counters[out_tile] = 0u;   // ready for the next launch
+        }
+        named_sync(kBarEpilogue, 32 * kFewEpilogueWarps);
+        if (combine_flag && n < p.n) {
+          __threadfence();
+          const float rs = p.row_scale ? p.row_scale[n] : 1.0f;
+          for (uint32_t c = 0; c < kCW; ++c) {
+            const uint32_t mtok = tok0 + c;
+            if (mtok >= p.m) break;
+            float sum = __ldcg(p.partial + size_t(mtok) * p.n + n);
+            for (uint32_t s2 = 1; s2 < p.splits; ++s2) sum = __fadd_rn(sum, __ldcg(p.partial + (size_t(s2) * p.m_pad + mtok) * p.n + n));
+            float out = __fmul_rn(sum, __ldg(p.ascale + mtok));
+            if (p.row_scale) out = __fmul_rn(out, rs);
+            const size_t idx = size_t(mtok) * p.n + n;
+            if (p.residual) out = __fadd_rn(__ldg(p.residual + idx), out);
+            if (p.y_dtype == TB_F32) static_cast<float*>(p.y)[idx] = out;
+            else static_cast<__nv_bfloat16*>(p.y)[idx] = __float2bfloat16_rn(out);
+          }
+        }
+      }
+    }
+  } else {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");   // the idle warp of the first warpgroup
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
 }
 
 // ---------------------------------------------------------------- host side
@@ -617,11 +964,22 @@ EncodeTiled encode_tiled_fn() {
   return fn;
 }
 
-// tokens per accumulator half: 64 for up to 128 tokens (one 128-token tile), else 128
-uint32_t half_width(uint32_t m) { return m <= 128 ? 64 : 128; }
+// tokens per accumulator half: one token tile of 32, 64 or 128 tokens for that many tokens, else
+// tiles of 256.  Tiles of 32 and 64 tokens run the few-token configuration of the kernel.
+uint32_t half_width(uint32_t m) { return m <= 32 ? 16 : m <= 64 ? 32 : m <= 128 ? 64 : 128; }
 uint32_t pad_tokens(uint32_t m) { const uint32_t t = 2 * half_width(m); return (m + t - 1) / t * t; }
+// K splits of an output tile: as many as keep every CTA of one wave busy, at most one per tile column.
+uint32_t k_splits(uint32_t out_tiles, uint32_t tpr, uint32_t sm_count, uint32_t hw) {
+  if (hw > 32 || out_tiles >= sm_count || out_tiles > kMaxSplitTiles) return 1;
+  return std::max(1u, std::min(std::min(sm_count / out_tiles, tpr), 8u));
+}
+uint32_t splits_of(const tb_weights* w, uint32_t m, uint32_t sm_count) {
+  const uint32_t hw = half_width(m), tile_tokens = 2 * hw;
+  const uint32_t out_tiles = uint32_t((w->n + kRows - 1) / kRows) * (pad_tokens(m) / tile_tokens);
+  return k_splits(out_tiles, uint32_t(w->k / 256), sm_count, hw);
+}
 
-struct Scratch { int8_t* qperm; int32_t* qinit; float* ascale; };
+struct Scratch { int8_t* qperm; int32_t* qinit; float* ascale; float* partial; };
 Scratch carve(void* base, uint32_t m_pad, uint32_t k) {
   uint8_t* b = static_cast<uint8_t*>(base);
   Scratch s;
@@ -630,29 +988,55 @@ Scratch carve(void* base, uint32_t m_pad, uint32_t k) {
   s.qinit = reinterpret_cast<int32_t*>(b + off);
   off += (size_t(k / 128) * m_pad * 4 + 255) & ~size_t(255);
   s.ascale = reinterpret_cast<float*>(b + off);
+  off += (size_t(m_pad) * 4 + 255) & ~size_t(255);
+  s.partial = reinterpret_cast<float*>(b + off);   // [splits][m_pad][n], only when K is split
   return s;
+}
+
+size_t smem_of(uint32_t hw) {
+  const uint32_t tile_tokens = 2 * hw;
+  if (hw <= 32)   // few-token kernel
+    return 1024 + size_t(kFewStagesA) * kTileABytes + size_t(kFewStagesB) * 2 * tile_tokens * 128 + size_t(kFewStagesB) * 2 * tile_tokens * 4 +
+           size_t(kGroupWarps * kFewExpGroups) * 32 * 16 * 4;
+  return 1024 + size_t(stages_a(1)) * kTileABytes + size_t(kStagesB) * 2 * tile_tokens * 128 + size_t(kStagesB) * 2 * tile_tokens * 4 +
+         size_t(kGroupWarps) * 32 * 16 * 4;
+}
+
+template <typename Kernel>
+cudaError_t launch_kernel(Kernel kernel, dim3 grid, int threads, size_t smem, cudaStream_t st, const PrefillParams& pp, const CUtensorMap& map) {
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+  if (e != cudaSuccess) return e;
+  kernel<<<grid, threads, smem, st>>>(pp, map);
+  return cudaGetLastError();
 }
 
 template <int CODEC, int HW, bool DUMP>
 cudaError_t launch_planes(uint32_t planes, dim3 grid, size_t smem, cudaStream_t st, const PrefillParams& pp, const CUtensorMap& map) {
-  auto go = [&](auto kernel) -> cudaError_t {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-    if (e != cudaSuccess) return e;
-    kernel<<<grid, kThreads, smem, st>>>(pp, map);
-    return cudaGetLastError();
-  };
-  if (planes == 1) return go(prefill_kernel<CODEC, 1, HW, DUMP>);
-  if (planes == 2) return go(prefill_kernel<CODEC, 2, HW, DUMP>);
-  return go(prefill_kernel<CODEC, 3, HW, DUMP>);
+  if constexpr (HW <= 32) {
+    constexpr int TT = 2 * HW;
+    if (planes == 1) return launch_kernel(fewtok_kernel<CODEC, 1, TT, DUMP>, grid, kFewThreads, smem, st, pp, map);
+    if (planes == 2) return launch_kernel(fewtok_kernel<CODEC, 2, TT, DUMP>, grid, kFewThreads, smem, st, pp, map);
+    return launch_kernel(fewtok_kernel<CODEC, 3, TT, DUMP>, grid, kFewThreads, smem, st, pp, map);
+  } else {
+    constexpr int EPI = 16, EXP = 1;
+    if (planes == 1) return launch_kernel(prefill_kernel<CODEC, 1, HW, DUMP, EPI, EXP>, grid, threads_of(EPI, EXP), smem, st, pp, map);
+    if (planes == 2) return launch_kernel(prefill_kernel<CODEC, 2, HW, DUMP, EPI, EXP>, grid, threads_of(EPI, EXP), smem, st, pp, map);
+    return launch_kernel(prefill_kernel<CODEC, 3, HW, DUMP, EPI, EXP>, grid, threads_of(EPI, EXP), smem, st, pp, map);
+  }
 }
 
 template <int CODEC>
 cudaError_t launch_shape(uint32_t hw, bool dump, uint32_t planes, dim3 grid, size_t smem, cudaStream_t st, const PrefillParams& pp,
                          const CUtensorMap& map) {
-  if (hw == 64) return dump ? launch_planes<CODEC, 64, true>(planes, grid, smem, st, pp, map)
-                            : launch_planes<CODEC, 64, false>(planes, grid, smem, st, pp, map);
-  return dump ? launch_planes<CODEC, 128, true>(planes, grid, smem, st, pp, map)
-              : launch_planes<CODEC, 128, false>(planes, grid, smem, st, pp, map);
+#define TB_HW_CASE(W) \
+  if (hw == W) return dump ? launch_planes<CODEC, W, true>(planes, grid, smem, st, pp, map) \
+                           : launch_planes<CODEC, W, false>(planes, grid, smem, st, pp, map)
+  TB_HW_CASE(16);
+  TB_HW_CASE(32);
+  TB_HW_CASE(64);
+  TB_HW_CASE(128);
+#undef TB_HW_CASE
+  return cudaErrorInvalidValue;
 }
 
 }  // namespace
@@ -663,8 +1047,10 @@ bool tb_prefill_supported(const tb_weights* w, uint32_t m) {
 
 size_t tb_prefill_scratch_bytes(const tb_weights* w, uint32_t m) {
   const uint32_t m_pad = pad_tokens(m);
+  const uint32_t sm_count = w->owner ? uint32_t(w->owner->prop.multiProcessorCount) : 148u;
+  const uint32_t splits = splits_of(w, m, sm_count);
   return ((size_t(m_pad) * w->k + 255) & ~size_t(255)) + ((size_t(w->k / 128) * m_pad * 4 + 255) & ~size_t(255)) +
-         size_t(m_pad) * 4 + 256;
+         ((size_t(m_pad) * 4 + 255) & ~size_t(255)) + (splits > 1 ? size_t(splits) * m_pad * w->n * 4 : 0) + 256;
 }
 
 cudaError_t tb_launch_prefill(const PrefillArgs& a, int sm_count, cudaStream_t stream) {
@@ -698,9 +1084,13 @@ cudaError_t tb_launch_prefill(const PrefillArgs& a, int sm_count, cudaStream_t s
   pp.y = a.y; pp.acc_dump = a.acc_dump; pp.row_scale = a.row_scale; pp.status = a.status; pp.residual = a.residual;
   pp.m = a.m; pp.m_pad = m_pad; pp.n = uint32_t(w->n); pp.k = k; pp.tpr = k / 256; pp.y_dtype = uint32_t(a.y_dtype);
   pp.n_tiles = (pp.n + kRows - 1) / kRows; pp.m_tiles = m_pad / tile_tokens;
-  const size_t smem = 1024 + size_t(kStagesA) * kTileABytes + size_t(kStagesB) * 2 * tile_tokens * 128 + size_t(kStagesB) * 2 * tile_tokens * 4 +
-                      size_t(kExpandWarps) * 32 * 16 * 4;
-  const dim3 grid(std::min<uint32_t>(pp.n_tiles * pp.m_tiles, uint32_t(sm_count)));
+  pp.splits = splits_of(w, a.m, uint32_t(sm_count));
+  if (pp.splits > 1) {
+    if (!a.tile_counters) return cudaErrorInvalidValue;
+    pp.partial = sc.partial; pp.tile_counters = a.tile_counters;
+  }
+  const size_t smem = smem_of(hw);
+  const dim3 grid(std::min<uint32_t>(pp.n_tiles * pp.m_tiles * pp.splits, uint32_t(sm_count)));
   const bool dump = a.acc_dump != nullptr;
   return w->codec == tbf::kB3 ? launch_shape<tbf::kB3>(hw, dump, w->uniform_planes, grid, smem, stream, pp, map)
                               : launch_shape<tbf::kD2>(hw, dump, w->uniform_planes, grid, smem, stream, pp, map);

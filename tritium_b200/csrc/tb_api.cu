@@ -101,6 +101,9 @@ extern "C" tb_status tb_backend_create(int ordinal, tb_backend** out) {
   cudaDeviceGetAttribute(&b->max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, ordinal);
   b->d_prep_cap = 2u << 20;   // activation tables of the decode path: up to 4 tokens x k = 32768
   if ((err = cudaMalloc(&b->d_prep, b->d_prep_cap)) != cudaSuccess) return bail(err, "allocate decode scratch");
+  if ((err = cudaMalloc(reinterpret_cast<void**>(&b->d_tile_counters), 256 * sizeof(uint32_t))) != cudaSuccess ||
+      (err = cudaMemset(b->d_tile_counters, 0, 256 * sizeof(uint32_t))) != cudaSuccess)
+    return bail(err, "allocate tile counters");
   const unsigned char* u = reinterpret_cast<const unsigned char*>(b->prop.uuid.bytes);
   std::snprintf(b->physical_id, sizeof b->physical_id,
                 "b200:%d:GPU-%02x%02x%02x%02x-%02x%02x-%02x%02x-%02x%02x-%02x%02x%02x%02x%02x%02x", ordinal, u[0], u[1],
@@ -127,7 +130,7 @@ void destroy_backend(tb_backend* b) {
   cudaSetDevice(b->ordinal);
   if (b->stream) { cudaStreamSynchronize(b->stream); cudaStreamDestroy(b->stream); }
   cudaFree(b->d_status); cudaFreeHost(b->h_status);
-  cudaFree(b->d_x); cudaFree(b->d_y); cudaFree(b->d_aux); cudaFree(b->d_q); cudaFree(b->d_prep); cudaFree(b->d_norm); cudaFreeHost(b->h_pin);
+  cudaFree(b->d_x); cudaFree(b->d_y); cudaFree(b->d_aux); cudaFree(b->d_q); cudaFree(b->d_prep); cudaFree(b->d_norm); cudaFree(b->d_tile_counters); cudaFreeHost(b->h_pin);
   delete b;
 }
 }  // namespace
@@ -372,8 +375,9 @@ tb_status forward_dev(tb_backend* b, const tb_weights* w, const tb_forward_args&
   if (a.x_dtype == TB_I8 && !a.act_scale) return tb_fail(TB_NULL_ARG, "int8 activations need act_scale");
   if (a.y_dtype == TB_I8) return tb_fail(TB_INVALID_INPUT, "output dtype must be fp32 or bf16");
   if (!w->fast) return tb_fail(TB_UNSUPPORTED_FORMAT, "the int8 path needs uniform plane counts, k % 256 == 0, group 128 and codec D2 or B3");
-  // measured crossover on C2: four chained 4-token decode passes (about 51 us) still beat one tensor-core call (67 us)
-  const bool want_prefill = (a.flags & TB_FWD_FORCE_PREFILL) || (a.m > 16 && !(a.flags & TB_FWD_FORCE_DECODE));
+  // measured crossover (C2, 27B and 2B linears alike): three chained 4-token decode passes are level with
+  // one call of the few-token tensor-core kernel (about 33 us on C2), four passes are slower
+  const bool want_prefill = (a.flags & TB_FWD_FORCE_PREFILL) || (a.m > 12 && !(a.flags & TB_FWD_FORCE_DECODE));
   uint32_t extra_launches = 0;
   // The decode kernel normalises inside its table builder.  Every other route (the tensor-core
   // kernel, tables from the preparation kernel) takes rows normalised by a kernel of its own; the
@@ -396,7 +400,7 @@ tb_status forward_dev(tb_backend* b, const tb_weights* w, const tb_forward_args&
     }
     PrefillArgs pa{w, a.x, a.x_dtype, a.act_scale, a.act_absmax, a.m, a.y, a.y_dtype, a.acc_dump, a.row_scale,
                    b->d_q, b->d_q_cap, b->d_status};
-    pa.residual = ex.residual;
+    pa.residual = ex.residual; pa.tile_counters = b->d_tile_counters;
     TB_CUDA(tb_launch_prefill(pa, b->prop.multiProcessorCount, st), "launch prefill");
     fill_receipt(w, a.m, dtype_size(a_in.x_dtype), dtype_size(a.y_dtype), 2, 2 + extra_launches, receipt);
     return TB_OK;
@@ -444,7 +448,12 @@ tb_status forward_dev(tb_backend* b, const tb_weights* w, const tb_forward_args&
 
 tb_status reserve_prefill(tb_backend* b, const tb_weights* w, uint32_t m) {
   if (!w->fast || !tb_prefill_supported(w, m)) return TB_OK;
-  return ensure(&b->d_q, &b->d_q_cap, tb_prefill_scratch_bytes(w, m));
+  // batches of up to 64 tokens split K and keep partial sums in the scratch as well, so the need
+  // does not grow monotonically with m: reserve for the largest of the kernel's token-tile classes
+  size_t need = tb_prefill_scratch_bytes(w, m);
+  for (uint32_t edge : {32u, 64u})
+    if (m > edge) need = std::max(need, tb_prefill_scratch_bytes(w, edge));
+  return ensure(&b->d_q, &b->d_q_cap, need);
 }
 
 // Host-pointer wrapper: stage in, run, check, stage out.  `y` is written only on success.
@@ -548,7 +557,7 @@ extern "C" tb_status tb_norm_linear_forward_dev(tb_backend* b, const tb_weights*
   tb_forward_args a{};
   a.x = args->x; a.x_dtype = args->x_dtype; a.m = args->m; a.y = args->y; a.y_dtype = args->y_dtype;
   a.flags = args->flags | TB_FWD_A8; a.stream = args->stream;
-  if (a.m > 16 && !(a.flags & TB_FWD_FORCE_DECODE)) if (tb_status s = reserve_prefill(b, w, a.m)) return s;
+  if (a.m > 12 && !(a.flags & TB_FWD_FORCE_DECODE)) if (tb_status s = reserve_prefill(b, w, a.m)) return s;
   BlockExtras ex;
   ex.norm_weight = args->norm_weight; ex.norm_eps = args->norm_eps;
   ex.norm_zero_centered = (args->norm_flags & TB_NORM_ZERO_CENTERED) != 0; ex.residual = args->residual;

@@ -43,6 +43,7 @@ struct tb_backend {
   void* d_prep = nullptr; size_t d_prep_cap = 0;
   // normalised activations, for norm+linear calls whose tables the decode kernel does not build itself
   void* d_norm = nullptr; size_t d_norm_cap = 0;
+  uint32_t* d_tile_counters = nullptr;   // 256 words, zero between launches (the tensor-core kernel's K splits)
   int max_smem_optin = 0;
   // Weights, stacks and communicators point back at their backend.  tb_backend_free only marks
   // the context released while such objects are alive; the last of them to go destroys it, so that
@@ -178,6 +179,7 @@ struct PrefillArgs {
   void* scratch; size_t scratch_bytes;   // permuted int8 activations, slab start values, token scales
   uint32_t* status;
   const float* residual = nullptr;       // [m][n] fp32, nullable: out = residual + y
+  uint32_t* tile_counters = nullptr;     // 256 zeroed words (few-token launches split K and count the splits of a tile in)
 };
 bool tb_prefill_supported(const tb_weights* w, uint32_t m);
 size_t tb_prefill_scratch_bytes(const tb_weights* w, uint32_t m);
