@@ -272,6 +272,51 @@ def measure_int8_peak(torch) -> dict | None:
         return {"tops": None, "how": f"torch._int_mm unavailable: {type(exc).__name__}: {exc}"[:200]}
 
 
+def measure_few_tokens(torch, backend, codec, stream, shapes=None, batches=(16, 32, 64), copies_cap: int = 0) -> dict:
+    """Batches of 13 to 64 tokens (batched decode): one call of the few-token tensor-core kernel per
+    linear against chained 4-token decode passes, on the benchmark's layer and on a 27B-class gate/up
+    linear, weights rotating over copies larger than L2, eager calls (quantisation pre-pass included)."""
+    from tritium_b200 import _lib
+    from tritium_b200.synth import make_activations, make_tensor
+    shapes = shapes or [("c2_3plane", N_ROWS, K_COLS, PLANES), ("gate_up_27b_2plane", 34816, 5120, 2)]
+    out = {"timing": "CUDA events over back-to-back calls on one stream, bf16 in and out, weight copies > 126 MB L2"}
+    for name, n, k, planes in shapes:
+        t = make_tensor(name, n, k, planes, seed=1)
+        payload, scales, pmap, terminal, _ = t.resident(codec)
+        layer = len(payload) + len(scales)
+        copies = max(2, int(np.ceil(300e6 / layer)))
+        if copies_cap:
+            copies = min(copies, copies_cap)
+        hs = [backend.upload_salt_v2_arenas(codec, 128, n, k, payload, scales, pmap, terminal) for _ in range(copies)]
+        backend.reserve(hs[0], max(batches))
+        entry = {"n": n, "k": k, "planes": planes, "packed_bytes": layer, "weight_copies": copies}
+        for m in batches:
+            x = torch.from_numpy(make_activations(m, k, seed=2, bf16=True)).cuda().to(torch.bfloat16)
+            y = torch.zeros(m, n, dtype=torch.bfloat16, device="cuda")
+            res = {}
+            for label, flags in (("tensor_core_us", _lib.TB_FWD_FORCE_PREFILL), ("decode_passes_us", _lib.TB_FWD_FORCE_DECODE | _lib.TB_FWD_PDL)):
+                if label == "decode_passes_us" and m > 32:
+                    continue
+                with torch.cuda.stream(stream):
+                    for i in range(3):
+                        backend.forward_dev(hs[i % copies], x, y, a8=True, flags=flags, stream=stream)
+                    stream.synchronize()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    iters = 2 * copies
+                    e0.record(stream)
+                    for i in range(iters):
+                        backend.forward_dev(hs[i % copies], x, y, a8=True, flags=flags, stream=stream)
+                    e1.record(stream)
+                    stream.synchronize()
+                    backend.check(stream)
+                res[label] = e0.elapsed_time(e1) / iters * 1e3
+            res["tensor_core_weight_gbs"] = layer / res["tensor_core_us"] / 1e3
+            entry[f"m{m}"] = res
+        out[name] = entry
+        del hs
+    return out
+
+
 def measure_reference_gpu_kernels(torch, backend, stream) -> dict:
     """The reference's own CUDA kernels (built from its sources into oracle/_ref) beside this
     library's kernels, on the same GPU, the same 1-plane TQ2_0-class weights with a per-channel
@@ -481,6 +526,11 @@ def run_b200(args) -> None:
     stack = LinearStack(backend, weights, [0] * copies, max_m=max(m, 1))
 
     stream = torch.cuda.Stream()
+    if args.only_few_tokens:
+        # profiling aid: the few-token tensor-core kernel alone, on the 27B-class gate/up linear
+        print(json.dumps(measure_few_tokens(torch, backend, codec, stream, shapes=[("gate_up_27b_2plane", 34816, 5120, 2)],
+                                            batches=(args.only_few_tokens,), copies_cap=3)), flush=True)
+        return
     if args.only_prefill:
         # profiling aid: the tensor-core leg alone (no decode leg, no CPU leg)
         print(json.dumps(measure_prefill(torch, backend, weights[:2], args.prefill_m, codec_name, args.steps, args.warmup, stream)), flush=True)
@@ -573,6 +623,10 @@ def run_b200(args) -> None:
                 prefill["roofline"]["int8_gemm_peak_measured"] = int8_peak
                 prefill["roofline"]["frac_of_measured_int8_gemm"] = prefill["roofline"]["achieved"] / int8_peak["tops"]
 
+    few_tokens = None
+    if world == 1 and not args.quick:
+        few_tokens = measure_few_tokens(torch, backend, codec, stream)
+
     ref_gpu = None
     if world == 1 and not args.quick:
         try:
@@ -642,6 +696,7 @@ def run_b200(args) -> None:
             "single_layer": single,
             "e2e_per_linear": e2e_linear,
             "prefill": prefill,
+            "few_tokens": few_tokens,
             "reference_gpu_kernels": ref_gpu,
             "tp": tp_leg,
             "stack_2b": stack_2b,
@@ -669,6 +724,7 @@ def main() -> None:
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--prefill-m", type=int, default=2048, help="tokens of the tensor-core leg (0 = skip)")
     ap.add_argument("--only-prefill", action="store_true")
+    ap.add_argument("--only-few-tokens", type=int, default=0, metavar="M", help="profiling aid: only the few-token kernel at M tokens (13..64)")
     ap.add_argument("--no-tp", action="store_true", help="skip the tensor-parallel decoder-stack leg")
     ap.add_argument("--tp-prefill-m", type=int, default=4096, help="tokens of the tensor-parallel prefill pass (0 = skip)")
     ap.add_argument("--tp-shape", default="27b", choices=["27b", "2b"], help="decoder whose linears the tensor-parallel leg runs")
