@@ -463,3 +463,33 @@ def test_stack_host_call_matches_per_layer_calls(backend):
         want, _, _ = backend.linear_forward_a8(r, f32_to_bf16_bits(x), m, y_dtype="bf16", x_is_bf16=True)
         assert np.array_equal(got[i], want)
     stack.close()
+
+
+# ------------------------------------------------------------------ int8 path of layouts without a fast kernel
+@pytest.mark.parametrize("codec,ocodec", CODECS)
+@pytest.mark.parametrize("layout", ["ragged_3x173", "g64_4x576", "mixed_planes_8x256"])
+def test_int8_path_of_other_layouts_is_bit_identical_to_cpu(backend, codec, ocodec, layout):
+    """Ragged shapes, scale groups of 64, S34 and mixed plane counts have no fast kernel: their int8
+    path quantises to codes kept as fp32 values and runs the bit-exact kernel on them.  Group sums
+    of small integers are exact and the order is the reference's, so the output equals the CPU
+    composition (quantise, matvec, token scale) bit for bit."""
+    if layout == "ragged_3x173":
+        t = cuda_test_tensor(3, 173, [1, 3, 2])
+    elif layout == "g64_4x576":
+        tiles = []
+        for ti in range(9):
+            trits = [{0: 0, 1: 1, 2: 1, 3: -1}[(i + ti) % 4] for i in range(256)]
+            tiles.append([(trits, [f16(np.float32(0.125) + np.float32(ti * 4 + g) / np.float32(64.0)) for g in range(4)])])
+        t = orc.tensor_from_planes(4, 576, tiles, group=64)
+    else:
+        t = cuda_test_tensor(8, 256, [1, 3, 2, 1, 2, 3, 3, 1])
+    m = 3
+    x = seeded_f32(0xA8 + t.rows, m * t.cols, -2.5, 2.5).reshape(m, t.cols)
+    want, _, scale = orc.a8_linear(t, x, dump=False)
+    resident = backend.upload_salt_v2(as_product(t), codec)
+    assert not resident.info["fast_path"]
+    y, _, receipt = backend.linear_forward_a8(resident, x, m)
+    assert receipt.kernel == 0
+    assert np.array_equal(y.view(np.uint32), want.view(np.uint32))
+    with pytest.raises(errors.UnsupportedFormat, match="accumulator dump"):
+        backend.linear_forward_a8(resident, x, m, dump=True)

@@ -270,6 +270,45 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const void* x, uint32_t dt
   }
 }
 
+// Per-token absmax int8 quantisation with the codes kept as fp32 values (quantize_act_int8,
+// crates/tritium-spec/src/lib.rs:239-264): the input of the exact kernel when a layout without a
+// fast kernel takes the int8 path.  One CTA per token.
+__global__ void __launch_bounds__(256) quantize_to_float_kernel(const void* x, uint32_t dtype, uint32_t k, float* q, float* act_scale,
+                                                                uint32_t* status) {
+  __shared__ float red[8];
+  const uint32_t t = blockIdx.x, tid = threadIdx.x;
+  const auto at = [&](uint32_t i) {
+    const size_t idx = size_t(t) * k + i;
+    return dtype == TB_F32 ? static_cast<const float*>(x)[idx] : __bfloat162float(static_cast<const __nv_bfloat16*>(x)[idx]);
+  };
+  float mx = 0.f;
+  bool bad = false;
+  for (uint32_t i = tid; i < k; i += 256) { const float v = at(i); bad |= !(fabsf(v) <= 3.402823466e+38f); mx = fmaxf(mx, fabsf(v)); }
+  if (bad && atomicOr(&status[TBS_FLAGS], TBF_NONFINITE_ACT) == 0) { status[TBS_INFO0] = t * k; status[TBS_INFO1] = 0x7fc00000u; }
+  for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if ((tid & 31) == 0) red[tid >> 5] = mx;
+  __syncthreads();
+  float gamma = 0.f;
+  for (int w = 0; w < 8; ++w) gamma = fmaxf(gamma, red[w]);
+  const float scale_q = gamma > 0.f ? __fdiv_rn(127.0f, gamma) : 0.f;
+  if (tid == 0) act_scale[t] = __fdiv_rn(gamma, 127.0f);
+  for (uint32_t i = tid; i < k; i += 256) q[size_t(t) * k + i] = fminf(127.f, fmaxf(-128.f, rintf(__fmul_rn(at(i), scale_q))));
+}
+
+// y_out[t][i] = y[t][i] * act_scale[t] (one rounding), fp32 or bf16
+__global__ void __launch_bounds__(256) scale_tokens_kernel(const float* y, const float* act_scale, const float* residual, uint32_t n,
+                                                           void* out, uint32_t out_dtype) {
+  const uint32_t t = blockIdx.y;
+  const float a = act_scale[t];
+  for (uint32_t i = blockIdx.x * 256 + threadIdx.x; i < n; i += gridDim.x * 256) {
+    const size_t idx = size_t(t) * n + i;
+    float v = __fmul_rn(y[idx], a);
+    if (residual) v = __fadd_rn(residual[idx], v);
+    if (out_dtype == TB_F32) static_cast<float*>(out)[idx] = v;
+    else static_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16_rn(v);
+  }
+}
+
 ExactParams make_params(const tb_weights* w) {
   ExactParams p{};
   p.payload = w->d_payload; p.scales = w->d_scales; p.meta = w->d_meta; p.tile_rank = w->d_tile_rank;
@@ -310,6 +349,20 @@ cudaError_t tb_launch_rmsnorm(const void* x, tb_dtype dtype, const float* weight
                               uint32_t k, float* out, cudaStream_t stream) {
   if (!m) return cudaSuccess;
   rmsnorm_kernel<<<m, 256, 0, stream>>>(x, uint32_t(dtype), weight, eps, zero_centered ? 1u : 0u, k, out);
+  return cudaGetLastError();
+}
+
+cudaError_t tb_launch_quantize_to_float(const void* x, tb_dtype dtype, uint32_t m, uint32_t k, float* q, float* act_scale, uint32_t* status,
+                                        cudaStream_t stream) {
+  if (!m) return cudaSuccess;
+  quantize_to_float_kernel<<<m, 256, 0, stream>>>(x, uint32_t(dtype), k, q, act_scale, status);
+  return cudaGetLastError();
+}
+
+cudaError_t tb_launch_scale_tokens(const float* y, const float* act_scale, const float* residual, uint32_t m, uint32_t n, void* out,
+                                   tb_dtype out_dtype, cudaStream_t stream) {
+  if (!m || !n) return cudaSuccess;
+  scale_tokens_kernel<<<dim3(std::min<uint32_t>((n + 255) / 256, 64), m), 256, 0, stream>>>(y, act_scale, residual, n, out, uint32_t(out_dtype));
   return cudaGetLastError();
 }
 

@@ -374,7 +374,32 @@ tb_status forward_dev(tb_backend* b, const tb_weights* w, const tb_forward_args&
   }
   if (a.x_dtype == TB_I8 && !a.act_scale) return tb_fail(TB_NULL_ARG, "int8 activations need act_scale");
   if (a.y_dtype == TB_I8) return tb_fail(TB_INVALID_INPUT, "output dtype must be fp32 or bf16");
-  if (!w->fast) return tb_fail(TB_UNSUPPORTED_FORMAT, "the int8 path needs uniform plane counts, k % 256 == 0, group 128 and codec D2 or B3");
+  if (!w->fast) {
+    // Scale groups of 64, ragged shapes, S34 and mixed plane counts have no fast kernel: quantise
+    // to int8 codes kept as fp32 values, run the bit-exact kernel on them (its group sums of small
+    // integers are exact and it keeps the reference's order, so the result equals the CPU path bit
+    // for bit), apply the token scale.  Slow by design; the accumulator dump is not offered here.
+    if (a.acc_dump) return tb_fail(TB_UNSUPPORTED_FORMAT, "the accumulator dump needs uniform plane counts, k % 256 == 0, group 128 and codec D2 or B3");
+    if (a.x_dtype == TB_I8 || a.act_absmax) return tb_fail(TB_UNSUPPORTED_FORMAT, "this layout takes fp32 or bf16 activations without a supplied absmax");
+    const size_t qf = (size_t(a.m) * w->k * 4 + 255) & ~size_t(255), yf = (size_t(a.m) * w->n * 4 + 255) & ~size_t(255);
+    if (tb_status s = ensure(&b->d_norm, &b->d_norm_cap, 2 * qf + yf + size_t(a.m) * 4 + 256)) return s;
+    uint8_t* base = static_cast<uint8_t*>(b->d_norm);
+    float* q = reinterpret_cast<float*>(base + qf);           // the first qf bytes may hold normalised rows
+    float* y32 = reinterpret_cast<float*>(base + 2 * qf);
+    float* scale = reinterpret_cast<float*>(base + 2 * qf + yf);
+    const void* src = a.x; tb_dtype src_dtype = a.x_dtype;
+    if (ex.norm_weight) {
+      TB_CUDA(tb_launch_rmsnorm(a.x, a.x_dtype, ex.norm_weight, ex.norm_eps, ex.norm_zero_centered, a.m, uint32_t(w->k),
+                                reinterpret_cast<float*>(base), st), "launch rmsnorm");
+      src = base; src_dtype = TB_F32;
+    }
+    TB_CUDA(tb_launch_quantize_to_float(src, src_dtype, a.m, uint32_t(w->k), q, scale, b->d_status, st), "launch quantise");
+    ExactArgs e{w, q, y32, a.m, a.row_scale, b->d_status};
+    TB_CUDA(tb_launch_exact(e, st), "launch salt_v2_exact");
+    TB_CUDA(tb_launch_scale_tokens(y32, scale, ex.residual, a.m, uint32_t(w->n), a.y, a.y_dtype, st), "launch token scale");
+    fill_receipt(w, a.m, dtype_size(a.x_dtype), dtype_size(a.y_dtype), 0, ex.norm_weight ? 4 : 3, receipt);
+    return TB_OK;
+  }
   // measured crossover (C2, 27B and 2B linears alike): three chained 4-token decode passes are level with
   // one call of the few-token tensor-core kernel (about 33 us on C2), four passes are slower
   const bool want_prefill = (a.flags & TB_FWD_FORCE_PREFILL) || (a.m > 12 && !(a.flags & TB_FWD_FORCE_DECODE));

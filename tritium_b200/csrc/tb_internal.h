@@ -101,6 +101,12 @@ cudaError_t tb_launch_gather_rows(const tb_weights* w, const uint32_t* rows, uin
 // RMSNorm of m rows of k values into fp32 `out` (canonical 256-slot reduction order).
 cudaError_t tb_launch_rmsnorm(const void* x, tb_dtype dtype, const float* weight, float eps, bool zero_centered, uint32_t m,
                               uint32_t k, float* out, cudaStream_t stream);
+// The int8 path of layouts without a fast kernel: codes as fp32 values for the exact kernel, and
+// the token scale (and residual) applied to its output.
+cudaError_t tb_launch_quantize_to_float(const void* x, tb_dtype dtype, uint32_t m, uint32_t k, float* q, float* act_scale, uint32_t* status,
+                                        cudaStream_t stream);
+cudaError_t tb_launch_scale_tokens(const float* y, const float* act_scale, const float* residual, uint32_t m, uint32_t n, void* out,
+                                   tb_dtype out_dtype, cudaStream_t stream);
 cudaError_t tb_launch_row_absmax(const void* x, tb_dtype dtype, uint32_t m, uint32_t k, float* out, cudaStream_t stream);
 cudaError_t tb_launch_check_finite(const float* x, uint64_t count, uint32_t* status, cudaStream_t stream);
 
