@@ -151,7 +151,10 @@ void tb_weights_free(tb_weights* weights);
  * as TB_INVALID_INPUT and `y` is left untouched on any error. */
 tb_status tb_salt_v2_forward_exact(tb_backend* backend, const tb_weights* weights, const float* x,
                                    uint32_t m, float* y, tb_receipt* receipt);
-/* CudaBackend::salt_v2_forward_fast (backend.rs:7672-7687): same contract, reassociated sums. */
+/* CudaBackend::salt_v2_forward_fast (backend.rs:7672-7687): same contract, reassociated sums; not
+ * bit-exact but within 1e-5 relative L2.  Tensors with a fast kernel run every fp32 activation as
+ * four int8 limbs relative to its token's absmax (representation error below 2e-9 of the absmax)
+ * through the int8 kernels, exact int32 sums per limb; other layouts run the bit-exact kernel. */
 tb_status tb_linear_forward_f32(tb_backend* backend, const tb_weights* weights, const float* x,
                                 uint32_t m, float* y, tb_receipt* receipt);
 /* The fused W1.58A8 path (TernaryBackend::mpgemm_with_act_quant, crates/tritium-spec/src/lib.rs:266-318,

@@ -232,3 +232,27 @@ def test_c5_decoder_27b_prefill_4096(backend, decoder_27b_tensors, name):
     q, s = orc.quantize_act_int8(x[tok], len(tok), k)
     want = orc.matmul(oracle_rows(prod, rows), q, threads=THREADS) * s[:, None]
     assert rel_l2(bf16_bits_to_f32(y_bits)[np.ix_(tok, rows)], want) <= 1e-2
+
+
+# ------------------------------------------------------------------ C1 as stated: fp32 activations on the fast entry point
+@pytest.mark.parametrize("m", [1, 32])
+@pytest.mark.parametrize("codec", [SaltV2Codec.B3, SaltV2Codec.D2], ids=["b3", "d2"])
+def test_c1_fp32_fast_entry_point_full_size(backend, codec, m):
+    """C1 (K=2048, N=8192, one plane, fp32 activations): the fast fp32 entry point runs the int8
+    kernels on four int8 limbs per activation; the exact entry point stays bit-identical."""
+    n, k = 8192, 2048
+    prod, orac = uniform_pair(n, k, 1, seed=0)
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    x[:, 7] *= 50.0                                   # an outlier channel: limbs are relative to the row's absmax
+    want = np.stack([orc.matvec(orac, x[i]) for i in range(m)])
+    resident = backend.upload_salt_v2(prod, codec)
+    fast = backend.salt_v2_forward_fast(resident, x, m)
+    assert rel_l2(fast.output, want) <= 1e-5
+    assert fast.receipt.kernel in (1, 2)              # a fast kernel ran, not the scalar exact one
+    exact = backend.salt_v2_forward_exact(resident, x, m)
+    assert np.array_equal(exact.output.view(np.uint32), want.view(np.uint32))
+    # tiny activations against one huge one still resolve: 31 bits below the absmax
+    x2 = np.full((1, k), 1e-6, np.float32); x2[0, 0] = 1.0
+    want2 = orc.matvec(orac, x2[0])[None]
+    assert rel_l2(backend.salt_v2_forward_fast(resident, x2, 1).output, want2) <= 1e-5

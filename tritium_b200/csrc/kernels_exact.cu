@@ -295,6 +295,50 @@ __global__ void __launch_bounds__(256) quantize_to_float_kernel(const void* x, u
   for (uint32_t i = tid; i < k; i += 256) q[size_t(t) * k + i] = fminf(127.f, fmaxf(-128.f, rintf(__fmul_rn(at(i), scale_q))));
 }
 
+// fp32 activations as four int8 limbs per element, for the int8 kernels: with gamma = max |x| of
+// the token and u = x * 127 / gamma, q0 = rint(u), then three times r <- (r - q) * 128, q = rint(r):
+//   x = (gamma / 127) * (q0 + q1 / 128 + q2 / 128^2 + q3 / 128^3) + e,  |e| <= gamma * 2e-9,
+// every step after u exact in fp32.  Limb l of token t becomes pseudo-token 4 t + l with the
+// dequantisation multiplier gamma / 127 / 128^l; the four outputs are added afterwards.
+__global__ void __launch_bounds__(256) limb_split_kernel(const float* x, uint32_t k, int8_t* q, float* act_scale, uint32_t* status) {
+  __shared__ float red[8];
+  const uint32_t t = blockIdx.x, tid = threadIdx.x;
+  const float* row = x + size_t(t) * k;
+  float mx = 0.f;
+  bool bad = false;
+  for (uint32_t i = tid; i < k; i += 256) { const float v = row[i]; bad |= !(fabsf(v) <= 3.402823466e+38f); mx = fmaxf(mx, fabsf(v)); }
+  if (bad && atomicOr(&status[TBS_FLAGS], TBF_NONFINITE_ACT) == 0) { status[TBS_INFO0] = t * k; status[TBS_INFO1] = 0x7fc00000u; }
+  for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if ((tid & 31) == 0) red[tid >> 5] = mx;
+  __syncthreads();
+  float gamma = 0.f;
+  for (int w = 0; w < 8; ++w) gamma = fmaxf(gamma, red[w]);
+  const float scale_q = gamma > 0.f ? __fdiv_rn(127.0f, gamma) : 0.f;
+  if (tid < 4) {
+    float a = __fdiv_rn(gamma, 127.0f);
+    for (uint32_t l = 0; l < tid; ++l) a = __fmul_rn(a, 0.0078125f);   // exact: a power of two
+    act_scale[4 * t + tid] = a;
+  }
+  for (uint32_t i = tid; i < k; i += 256) {
+    float r = __fmul_rn(row[i], scale_q);
+#pragma unroll
+    for (uint32_t l = 0; l < 4; ++l) {
+      const float ql = fminf(127.f, fmaxf(-127.f, rintf(r)));
+      q[(size_t(4 * t + l)) * k + i] = int8_t(int(ql));
+      r = __fmul_rn(__fsub_rn(r, ql), 128.0f);
+    }
+  }
+}
+
+// y[t][i] = ((y4[4t][i] + y4[4t+1][i]) + y4[4t+2][i]) + y4[4t+3][i]
+__global__ void __launch_bounds__(256) limb_sum_kernel(const float* y4, uint32_t n, float* y) {
+  const uint32_t t = blockIdx.y;
+  for (uint32_t i = blockIdx.x * 256 + threadIdx.x; i < n; i += gridDim.x * 256) {
+    const float* src = y4 + size_t(4 * t) * n + i;
+    y[size_t(t) * n + i] = __fadd_rn(__fadd_rn(__fadd_rn(src[0], src[n]), src[2 * size_t(n)]), src[3 * size_t(n)]);
+  }
+}
+
 // y_out[t][i] = y[t][i] * act_scale[t] (one rounding), fp32 or bf16
 __global__ void __launch_bounds__(256) scale_tokens_kernel(const float* y, const float* act_scale, const float* residual, uint32_t n,
                                                            void* out, uint32_t out_dtype) {
@@ -356,6 +400,18 @@ cudaError_t tb_launch_quantize_to_float(const void* x, tb_dtype dtype, uint32_t 
                                         cudaStream_t stream) {
   if (!m) return cudaSuccess;
   quantize_to_float_kernel<<<m, 256, 0, stream>>>(x, uint32_t(dtype), k, q, act_scale, status);
+  return cudaGetLastError();
+}
+
+cudaError_t tb_launch_limb_split(const float* x, uint32_t m, uint32_t k, int8_t* q, float* act_scale, uint32_t* status, cudaStream_t stream) {
+  if (!m) return cudaSuccess;
+  limb_split_kernel<<<m, 256, 0, stream>>>(x, k, q, act_scale, status);
+  return cudaGetLastError();
+}
+
+cudaError_t tb_launch_limb_sum(const float* y4, uint32_t m, uint32_t n, float* y, cudaStream_t stream) {
+  if (!m || !n) return cudaSuccess;
+  limb_sum_kernel<<<dim3(std::min<uint32_t>((n + 255) / 256, 64), m), 256, 0, stream>>>(y4, n, y);
   return cudaGetLastError();
 }
 

@@ -130,7 +130,7 @@ void destroy_backend(tb_backend* b) {
   cudaSetDevice(b->ordinal);
   if (b->stream) { cudaStreamSynchronize(b->stream); cudaStreamDestroy(b->stream); }
   cudaFree(b->d_status); cudaFreeHost(b->h_status);
-  cudaFree(b->d_x); cudaFree(b->d_y); cudaFree(b->d_aux); cudaFree(b->d_q); cudaFree(b->d_prep); cudaFree(b->d_norm); cudaFree(b->d_tile_counters); cudaFreeHost(b->h_pin);
+  cudaFree(b->d_x); cudaFree(b->d_y); cudaFree(b->d_aux); cudaFree(b->d_q); cudaFree(b->d_prep); cudaFree(b->d_norm); cudaFree(b->d_limb); cudaFree(b->d_tile_counters); cudaFreeHost(b->h_pin);
   delete b;
 }
 }  // namespace
@@ -349,6 +349,8 @@ tb_status check_handles(const tb_backend* b, const tb_weights* w) {
   return TB_OK;
 }
 
+tb_status reserve_prefill(tb_backend* b, const tb_weights* w, uint32_t m);
+
 // What a decode block wraps around the linear: RMSNorm in front of the quantiser, residual behind.
 struct BlockExtras {
   const float* norm_weight = nullptr; float norm_eps = 0.f; bool norm_zero_centered = false;
@@ -366,6 +368,28 @@ tb_status forward_dev(tb_backend* b, const tb_weights* w, const tb_forward_args&
   if (ex.norm_weight && a.x_dtype == TB_I8) return tb_fail(TB_INVALID_INPUT, "RMSNorm takes fp32 or bf16 activations");
   if (!a8) {
     if (a.x_dtype != TB_F32 || a.y_dtype != TB_F32) return tb_fail(TB_INVALID_INPUT, "the fp32 path takes fp32 activations and outputs");
+    if (!(a.flags & TB_FWD_EXACT) && w->fast && a.m <= (1u << 20)) {
+      // Not bit-exact, but fast: every activation as four int8 limbs relative to its token's
+      // absmax (error below 2e-9 of the absmax), the limbs as pseudo-tokens through the int8
+      // kernels (exact int32 sums per limb), the four outputs of a token added in a fixed order.
+      const uint32_t m4 = a.m * 4;
+      const size_t qb = (size_t(m4) * w->k + 255) & ~size_t(255), sb = (size_t(m4) * 4 + 255) & ~size_t(255);
+      if (tb_status s = ensure(&b->d_limb, &b->d_limb_cap, qb + sb + size_t(m4) * w->n * 4 + 256)) return s;
+      if (m4 > 12) if (tb_status s = reserve_prefill(b, w, m4)) return s;
+      uint8_t* base = static_cast<uint8_t*>(b->d_limb);
+      int8_t* q = reinterpret_cast<int8_t*>(base);
+      float* scales = reinterpret_cast<float*>(base + qb);
+      float* y4 = reinterpret_cast<float*>(base + qb + sb);
+      TB_CUDA(tb_launch_limb_split(static_cast<const float*>(a.x), a.m, uint32_t(w->k), q, scales, b->d_status, st), "launch limb split");
+      tb_forward_args l{};
+      l.x = q; l.x_dtype = TB_I8; l.act_scale = scales; l.m = m4; l.y = y4; l.y_dtype = TB_F32; l.row_scale = a.row_scale;
+      l.flags = TB_FWD_A8 | (a.flags & (TB_FWD_PDL | TB_FWD_FORCE_DECODE | TB_FWD_FORCE_PREFILL));
+      tb_receipt inner{};
+      if (tb_status s = forward_dev(b, w, l, st, &inner)) return s;
+      TB_CUDA(tb_launch_limb_sum(y4, a.m, uint32_t(w->n), static_cast<float*>(a.y), st), "launch limb sum");
+      fill_receipt(w, a.m, 4, 4, inner.kernel, inner.launches + 2, receipt);
+      return TB_OK;
+    }
     ExactArgs e{w, static_cast<const float*>(a.x), static_cast<float*>(a.y), a.m, a.row_scale, b->d_status};
     TB_CUDA(tb_launch_check_finite(e.x, uint64_t(a.m) * w->k, b->d_status, st), "launch finite check");
     TB_CUDA(tb_launch_exact(e, st), "launch salt_v2_exact");

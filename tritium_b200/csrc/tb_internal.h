@@ -43,6 +43,8 @@ struct tb_backend {
   void* d_prep = nullptr; size_t d_prep_cap = 0;
   // normalised activations, for norm+linear calls whose tables the decode kernel does not build itself
   void* d_norm = nullptr; size_t d_norm_cap = 0;
+  // fp32 activations split into int8 limbs, their multipliers and the limbs' outputs
+  void* d_limb = nullptr; size_t d_limb_cap = 0;
   uint32_t* d_tile_counters = nullptr;   // 256 words, zero between launches (the tensor-core kernel's K splits)
   int max_smem_optin = 0;
   // Weights, stacks and communicators point back at their backend.  tb_backend_free only marks
@@ -105,6 +107,10 @@ cudaError_t tb_launch_rmsnorm(const void* x, tb_dtype dtype, const float* weight
 // the token scale (and residual) applied to its output.
 cudaError_t tb_launch_quantize_to_float(const void* x, tb_dtype dtype, uint32_t m, uint32_t k, float* q, float* act_scale, uint32_t* status,
                                         cudaStream_t stream);
+// fp32 activations through the int8 kernels: four int8 limbs per element (pseudo-tokens 4t..4t+3
+// with their own dequantisation multipliers), and the sum of the four outputs of a token.
+cudaError_t tb_launch_limb_split(const float* x, uint32_t m, uint32_t k, int8_t* q, float* act_scale, uint32_t* status, cudaStream_t stream);
+cudaError_t tb_launch_limb_sum(const float* y4, uint32_t m, uint32_t n, float* y, cudaStream_t stream);
 cudaError_t tb_launch_scale_tokens(const float* y, const float* act_scale, const float* residual, uint32_t m, uint32_t n, void* out,
                                    tb_dtype out_dtype, cudaStream_t stream);
 cudaError_t tb_launch_row_absmax(const void* x, tb_dtype dtype, uint32_t m, uint32_t k, float* out, cudaStream_t stream);
