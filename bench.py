@@ -317,6 +317,47 @@ def measure_few_tokens(torch, backend, codec, stream, shapes=None, batches=(16, 
     return out
 
 
+def measure_c1_fp32(torch, backend, codec, stream, peak: float, peak_kind: str) -> dict:
+    """BASELINE config 1 as stated: one-plane linear, K=2048, N=8192, fp32 activations, M=1 and 32, on
+    the fast fp32 entry point (four int8 limbs per activation through the int8 kernels) and on the
+    bit-exact entry point, device pointers, weights rotating over copies larger than L2."""
+    from tritium_b200 import _lib
+    from tritium_b200.synth import make_tensor
+    n, k = 8192, 2048
+    t = make_tensor("c1", n, k, 1, seed=0)
+    payload, scales, pmap, terminal, _ = t.resident(codec)
+    layer = len(payload) + len(scales)
+    copies = max(2, int(np.ceil(300e6 / layer)))
+    hs = [backend.upload_salt_v2_arenas(codec, 128, n, k, payload, scales, pmap, terminal) for _ in range(copies)]
+    out = {"workload": "c1_1plane_k2048_n8192_fp32", "weight_copies": copies, "packed_bytes": layer,
+           "timing": "CUDA events over back-to-back eager calls on one stream"}
+    for m in (1, 32):
+        x = torch.randn(m, k, device="cuda", dtype=torch.float32)
+        y = torch.zeros(m, n, device="cuda", dtype=torch.float32)
+        res = {}
+        for label, flags in (("fast", _lib.TB_FWD_PDL), ("exact", _lib.TB_FWD_EXACT)):
+            with torch.cuda.stream(stream):
+                for i in range(3):
+                    backend.forward_dev(hs[i % copies], x, y, a8=False, flags=flags, stream=stream)
+                stream.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                iters = copies if label == "fast" else min(copies, 8)
+                e0.record(stream)
+                for i in range(iters):
+                    backend.forward_dev(hs[i % copies], x, y, a8=False, flags=flags, stream=stream)
+                e1.record(stream)
+                stream.synchronize()
+                backend.check(stream)
+            us = e0.elapsed_time(e1) / iters * 1e3
+            algorithmic = layer + m * k * 4 + m * n * 4
+            res[label] = {"us_per_call": us, "gbs": algorithmic / us / 1e3}
+        res["roofline"] = {"bound": "hbm", "achieved": res["fast"]["gbs"], "peak": peak, "unit": UNIT, "frac": res["fast"]["gbs"] / peak,
+                           "peak_kind": peak_kind, "note": "one 3.7 MB layer per call: bound by launches, not bytes"}
+        out[f"m{m}"] = res
+    del hs
+    return out
+
+
 def measure_reference_gpu_kernels(torch, backend, stream) -> dict:
     """The reference's own CUDA kernels (built from its sources into oracle/_ref) beside this
     library's kernels, on the same GPU, the same 1-plane TQ2_0-class weights with a per-channel
@@ -623,9 +664,10 @@ def run_b200(args) -> None:
                 prefill["roofline"]["int8_gemm_peak_measured"] = int8_peak
                 prefill["roofline"]["frac_of_measured_int8_gemm"] = prefill["roofline"]["achieved"] / int8_peak["tops"]
 
-    few_tokens = None
+    few_tokens = c1_fp32 = None
     if world == 1 and not args.quick:
         few_tokens = measure_few_tokens(torch, backend, codec, stream)
+        c1_fp32 = measure_c1_fp32(torch, backend, codec, stream, peak, peak_kind)
 
     ref_gpu = None
     if world == 1 and not args.quick:
@@ -697,6 +739,7 @@ def run_b200(args) -> None:
             "e2e_per_linear": e2e_linear,
             "prefill": prefill,
             "few_tokens": few_tokens,
+            "c1_fp32": c1_fp32,
             "reference_gpu_kernels": ref_gpu,
             "tp": tp_leg,
             "stack_2b": stack_2b,
