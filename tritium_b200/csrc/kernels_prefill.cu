@@ -604,11 +604,24 @@ __global__ void __launch_bounds__(threads_of(EPI, EXP), 1) prefill_kernel(const 
       const uint32_t nc = min(n, p.n - 1);
       const uint16_t* srow = p.scales + size_t(nc) * p.tpr * PLANES * 2;
       const bool more_tiles = tile + gridDim.x < tiles;
+      // the row's group scales of a tile column (two f16 per plane) are fetched one column ahead,
+      // so that no slab's drain waits for a load
+      const uint32_t* srow2 = reinterpret_cast<const uint32_t*>(srow);
+      uint32_t sc_next[PLANES];
+#pragma unroll
+      for (int pl2 = 0; pl2 < PLANES; ++pl2) sc_next[pl2] = __ldg(srow2 + j0 * PLANES + pl2);
       for (uint32_t j = j0; j < j1; ++j, ++colfill) {
         const uint32_t sb = colfill % kStagesB;
+        uint32_t sc[PLANES];
+#pragma unroll
+        for (int pl2 = 0; pl2 < PLANES; ++pl2) {
+          sc[pl2] = sc_next[pl2];
+          if (j + 1 < j1) sc_next[pl2] = __ldg(srow2 + (j + 1) * PLANES + pl2);
+        }
+#pragma unroll
         for (uint32_t q = 0; q < kSlabsPerCol; ++q, ++slab) {
           const uint32_t gsel = q & 1, pl = q >> 1;
-          const float sv = __half2float(__ushort_as_half(srow[(j * PLANES + pl) * 2 + gsel]));
+          const float sv = __half2float(__ushort_as_half(uint16_t(gsel ? sc[pl] >> 16 : sc[pl] & 0xffffu)));
           const float2 scale2 = make_float2(sv, sv), neg_magic2 = make_float2(-12582912.0f, -12582912.0f);
           const bool last = (j + 1 == j1 && q + 1 == kSlabsPerCol);
           // where the next slab's start values are
