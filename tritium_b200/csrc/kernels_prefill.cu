@@ -207,6 +207,9 @@ struct QuantParams {
 
 __global__ void __launch_bounds__(256) prefill_quant_kernel(const QuantParams p) {
   __shared__ float red[8];
+  // The tensor-core kernel behind this one may start now: its expanders do not depend on the
+  // activations, only its copy warp waits (griddepcontrol.wait) for this grid to complete.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const uint32_t t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const uint32_t slabs = p.k / 128;
   int8_t* qrow = p.qperm + size_t(t) * p.k;
@@ -323,6 +326,9 @@ __device__ __forceinline__ void tma_role(const PrefillParams& p, const CUtensorM
                                          uint64_t* b_full, uint64_t* b_empty, const WaitCtx& wctx, uint32_t lane) {
   constexpr uint32_t kTileTokens = TILE_TOKENS, kTileBBytes = TILE_TOKENS * 128;
   constexpr int kStagesB = STAGES_B;
+  // launched with programmatic stream serialisation: everything this warp loads was written by
+  // the quantisation pre-pass, the previous grid on the stream
+  asm volatile("griddepcontrol.wait;" ::: "memory");
     // ------------------------------------------------ TMA: activations + start values of a tile column
     if (lane == 0) {
       uint32_t fill = 0;
@@ -1019,8 +1025,14 @@ template <typename Kernel>
 cudaError_t launch_kernel(Kernel kernel, dim3 grid, int threads, size_t smem, cudaStream_t st, const PrefillParams& pp, const CUtensorMap& map) {
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
   if (e != cudaSuccess) return e;
-  kernel<<<grid, threads, smem, st>>>(pp, map);
-  return cudaGetLastError();
+  // may start under the tail of the quantisation pre-pass (see tma_role)
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid; cfg.blockDim = dim3(unsigned(threads)); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, pp, map);
 }
 
 template <int CODEC, int HW, bool DUMP>
