@@ -273,7 +273,7 @@ def measure_int8_peak(torch) -> dict | None:
 
 
 def measure_few_tokens(torch, backend, codec, stream, shapes=None, batches=(16, 32, 64), copies_cap: int = 0) -> dict:
-    """Batches of 13 to 64 tokens (batched decode): one call of the few-token tensor-core kernel per
+    """Batches of 9 to 64 tokens (batched decode): one call of the few-token tensor-core kernel per
     linear against chained 4-token decode passes, on the benchmark's layer and on a 27B-class gate/up
     linear, weights rotating over copies larger than L2, eager calls (quantisation pre-pass included)."""
     from tritium_b200 import _lib
@@ -767,7 +767,7 @@ def main() -> None:
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--prefill-m", type=int, default=2048, help="tokens of the tensor-core leg (0 = skip)")
     ap.add_argument("--only-prefill", action="store_true")
-    ap.add_argument("--only-few-tokens", type=int, default=0, metavar="M", help="profiling aid: only the few-token kernel at M tokens (13..64)")
+    ap.add_argument("--only-few-tokens", type=int, default=0, metavar="M", help="profiling aid: only the few-token kernel at M tokens (9..64)")
     ap.add_argument("--no-tp", action="store_true", help="skip the tensor-parallel decoder-stack leg")
     ap.add_argument("--tp-prefill-m", type=int, default=4096, help="tokens of the tensor-parallel prefill pass (0 = skip)")
     ap.add_argument("--tp-shape", default="27b", choices=["27b", "2b"], help="decoder whose linears the tensor-parallel leg runs")

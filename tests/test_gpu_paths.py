@@ -230,7 +230,7 @@ def test_salt_v1_planes_match_the_reference_row_dot(backend, t_planes, m):
     want = orc.salt_v1_forward_a8(planes, t_planes, n, k, x)
     _, s = orc.quantize_act_int8(x, m, k)
     y, _, receipt = backend.linear_forward_a8(handle, xp, m)
-    assert receipt.kernel == (1 if m <= 12 else 2)
+    assert receipt.kernel == (1 if m <= 8 else 2)
     for r in range(m):
         assert np.all(np.abs(y[r] - want[r]) <= 1e-4 * np.maximum(max(float(s[r]), 1e-30), np.abs(want[r])))
     want_f32 = orc.salt_v1_matmul(planes, t_planes, n, k, x)
@@ -345,10 +345,10 @@ def test_backend_freed_before_its_weights():
     second.close()
 
 
-# ------------------------------------------------------------------ few tokens on the tensor cores (13..64 tokens)
+# ------------------------------------------------------------------ few tokens on the tensor cores (9..64 tokens)
 @pytest.mark.parametrize("codec", [SaltV2Codec.B3, SaltV2Codec.D2])
 @pytest.mark.parametrize("m,n,k,planes", [
-    (13, 200, 768, 3),      # smallest batch that takes the tensor-core route; K split four ways; ragged rows
+    (9, 200, 768, 3),       # smallest batch that takes the tensor-core route; K split three ways; ragged rows
     (20, 256, 1024, 2),
     (32, 6912, 2560, 3),    # the benchmark's layer: 54 row tiles, two K splits
     (33, 384, 2560, 3),     # 64-token tile
@@ -356,7 +356,7 @@ def test_backend_freed_before_its_weights():
     (48, 19200, 512, 2),    # more row tiles than SMs: no split, several tiles per CTA
 ])
 def test_few_token_tensor_core_kernel_is_exact(backend, codec, m, n, k, planes):
-    """Batches of 13 to 64 tokens run one pass of the few-token tensor-core kernel (accumulator ring,
+    """Batches of 9 to 64 tokens run one pass of the few-token tensor-core kernel (accumulator ring,
     sums in registers, K split over CTAs with a fixed-order combine).  The int32 group sums must be
     the oracle's bit for bit, with and without the dump, and two runs must give the same bits."""
     import torch

@@ -375,7 +375,7 @@ tb_status forward_dev(tb_backend* b, const tb_weights* w, const tb_forward_args&
       const uint32_t m4 = a.m * 4;
       const size_t qb = (size_t(m4) * w->k + 255) & ~size_t(255), sb = (size_t(m4) * 4 + 255) & ~size_t(255);
       if (tb_status s = ensure(&b->d_limb, &b->d_limb_cap, qb + sb + size_t(m4) * w->n * 4 + 256)) return s;
-      if (m4 > 12) if (tb_status s = reserve_prefill(b, w, m4)) return s;
+      if (m4 > 8) if (tb_status s = reserve_prefill(b, w, m4)) return s;
       uint8_t* base = static_cast<uint8_t*>(b->d_limb);
       int8_t* q = reinterpret_cast<int8_t*>(base);
       float* scales = reinterpret_cast<float*>(base + qb);
@@ -424,9 +424,9 @@ tb_status forward_dev(tb_backend* b, const tb_weights* w, const tb_forward_args&
     fill_receipt(w, a.m, dtype_size(a.x_dtype), dtype_size(a.y_dtype), 0, ex.norm_weight ? 4 : 3, receipt);
     return TB_OK;
   }
-  // measured crossover (C2, 27B and 2B linears alike): three chained 4-token decode passes are level with
-  // one call of the few-token tensor-core kernel (about 33 us on C2), four passes are slower
-  const bool want_prefill = (a.flags & TB_FWD_FORCE_PREFILL) || (a.m > 12 && !(a.flags & TB_FWD_FORCE_DECODE));
+  // measured crossover (C2, 27B and 2B linears alike): two chained 4-token decode passes are level with
+  // one call of the few-token tensor-core kernel (about 25 us on C2), three passes are slower
+  const bool want_prefill = (a.flags & TB_FWD_FORCE_PREFILL) || (a.m > 8 && !(a.flags & TB_FWD_FORCE_DECODE));
   uint32_t extra_launches = 0;
   // The decode kernel normalises inside its table builder.  Every other route (the tensor-core
   // kernel, tables from the preparation kernel) takes rows normalised by a kernel of its own; the
@@ -606,7 +606,7 @@ extern "C" tb_status tb_norm_linear_forward_dev(tb_backend* b, const tb_weights*
   tb_forward_args a{};
   a.x = args->x; a.x_dtype = args->x_dtype; a.m = args->m; a.y = args->y; a.y_dtype = args->y_dtype;
   a.flags = args->flags | TB_FWD_A8; a.stream = args->stream;
-  if (a.m > 12 && !(a.flags & TB_FWD_FORCE_DECODE)) if (tb_status s = reserve_prefill(b, w, a.m)) return s;
+  if (a.m > 8 && !(a.flags & TB_FWD_FORCE_DECODE)) if (tb_status s = reserve_prefill(b, w, a.m)) return s;
   BlockExtras ex;
   ex.norm_weight = args->norm_weight; ex.norm_eps = args->norm_eps;
   ex.norm_zero_centered = (args->norm_flags & TB_NORM_ZERO_CENTERED) != 0; ex.residual = args->residual;
