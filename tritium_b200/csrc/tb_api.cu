@@ -171,6 +171,9 @@ extern "C" tb_status tb_backend_check(tb_backend* b, void* stream) {
   if (!flags) return TB_OK;
   char msg[192];
   if (flags & TBF_WAIT_TIMEOUT) {
+    // a tensor-core launch that gave up may have left the arrival counters of its K splits part
+    // way: the next launch must find them at zero again
+    cudaMemsetAsync(b->d_tile_counters, 0, 256 * sizeof(uint32_t), st);
     std::snprintf(msg, sizeof msg, "a bounded device wait gave up (stage %u, barrier %u)", b->h_status[TBS_INFO0], b->h_status[TBS_INFO1]);
     return tb_fail(TB_TIMEOUT, msg);
   }
