@@ -204,7 +204,8 @@ tb_status tb_linear_forward_dev(tb_backend* backend, const tb_weights* weights,
  * residual + acc * scale).  Up to four tokens with small activation tables run as ONE launch
  * (the norm happens inside the decode kernel's table builder); other shapes normalise with a
  * kernel of their own into backend scratch, which the first such call of a size allocates.
- *   norm_weight NULL = no norm (residual epilogue only); residual NULL = none.
+ *   norm_weight NULL = no norm (residual epilogue only); residual NULL = none; relu2_up: the MLP's
+ *   squared-ReLU gate in front of the down projection (see the field).
  *   x fp32 or bf16 (bf16 is widened exactly); norm_weight fp32 [k]; residual fp32 [m][n]. */
 #define TB_NORM_ZERO_CENTERED 1u   /* scale by (1 + w): rmsnorm_zero_centered, rmsnorm.rs:49-63 */
 typedef struct tb_norm_linear_args {
@@ -219,6 +220,12 @@ typedef struct tb_norm_linear_args {
   tb_dtype y_dtype;
   uint32_t flags;            /* TB_FWD_PDL, TB_FWD_FORCE_DECODE, TB_FWD_FORCE_PREFILL */
   void* stream;
+  const float* relu2_up;     /* [m,k] device fp32, nullable: squared-ReLU gate in front of the quantiser.
+                                x then holds the gate projection's fp32 output, relu2_up the up
+                                projection's, and the linear's input is (max(x,0)^2) * relu2_up, the
+                                reference's relu2_gate_f32 (crates/tritium-cuda/kernels/decode.cu:772-780),
+                                computed where the activations are quantised: no launch of its own.
+                                Not together with norm_weight. */
 } tb_norm_linear_args;
 tb_status tb_norm_linear_forward_dev(tb_backend* backend, const tb_weights* weights,
                                      const tb_norm_linear_args* args, tb_receipt* receipt);

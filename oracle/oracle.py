@@ -465,6 +465,15 @@ def rmsnorm(x, w, eps: float, zero_centered: bool = False) -> np.ndarray:
     return out
 
 
+def relu2_gate(gate, up) -> np.ndarray:
+    """tritium_nn::layers::mlp gating loop = relu2_gate_f32 (crates/tritium-cuda/kernels/decode.cu:764-780):
+    r = max(g, 0); out = (r * r) * u, left-associated single-precision products."""
+    g = np.ascontiguousarray(gate, np.float32)
+    u = np.ascontiguousarray(up, np.float32)
+    r = np.maximum(g, np.float32(0.0))
+    return ((r * r).astype(np.float32) * u).astype(np.float32)
+
+
 def norm_a8_linear(tensor, x, norm_weight, eps: float, zero_centered: bool = False, residual=None):
     """The decode block's fused step: rmsnorm, per-token int8 quantisation, packed linear, then
     ``residual + y`` in one rounding (crates/tritium-cuda/kernels/decode.cu:533-640 for the

@@ -388,3 +388,36 @@ def test_few_token_tensor_core_kernel_is_exact(backend, codec, m, n, k, planes):
     assert torch.equal(y, y2)
     assert rel_l2(y.cpu().numpy()[:, sample], want) <= 1e-5
     assert np.array_equal(y3.cpu().numpy(), (residual + y.cpu().numpy()).astype(np.float32))
+
+
+# ------------------------------------------------------------------ squared-ReLU gate in front of the down projection
+@pytest.mark.parametrize("codec", [SaltV2Codec.B3, SaltV2Codec.D2])
+@pytest.mark.parametrize("n,k,planes,m", [
+    (192, 1024, 2, 1),      # tables built in the decode kernel
+    (160, 6912, 1, 4),      # the 2B-class down projection's width: preparation kernel
+    (256, 2560, 3, 6),      # two passes
+    (256, 1536, 2, 40),     # few-token tensor-core kernel
+    (128, 1024, 1, 200),    # many-token kernel
+])
+def test_relu2_gate_prologue_is_bit_identical(backend, codec, n, k, planes, m):
+    """(max(gate, 0)^2) * up is computed where the activations are quantised; elementwise and
+    association-preserving, so the result equals the plain int8 forward of gated rows bit for bit."""
+    import torch
+    prod, orac = uniform_pair(n, k, planes, seed=21)
+    resident = backend.upload_salt_v2(prod, codec)
+    backend.reserve(resident, m)
+    rng = np.random.default_rng(m)
+    gate = rng.standard_normal((m, k)).astype(np.float32)
+    up = rng.standard_normal((m, k)).astype(np.float32)
+    gated = orc.relu2_gate(gate, up)
+    plain = torch.zeros(m, n, dtype=torch.float32, device="cuda")
+    got = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+    backend.forward_dev(resident, torch.from_numpy(gated).cuda(), plain, a8=True)
+    backend.norm_linear_forward_dev(resident, torch.from_numpy(gate).cuda(), got, relu2_up=torch.from_numpy(up).cuda())
+    torch.cuda.synchronize()
+    backend.check()
+    assert torch.equal(got, plain)
+    assert rel_l2(got.cpu().numpy(), orc.a8_linear(orac, gated, dump=False)[0]) <= 1e-5
+    with pytest.raises(errors.InvalidInput, match="not combined"):
+        backend.norm_linear_forward_dev(resident, torch.from_numpy(gate).cuda(), got, relu2_up=torch.from_numpy(up).cuda(),
+                                        norm_weight=torch.ones(k, device="cuda"))

@@ -62,7 +62,7 @@ class ForwardArgs(C.Structure):
 class NormLinearArgs(C.Structure):
     _fields_ = [("x", C.c_void_p), ("x_dtype", C.c_int), ("norm_weight", C.c_void_p), ("norm_eps", C.c_float),
                 ("norm_flags", C.c_uint32), ("residual", C.c_void_p), ("m", C.c_uint32), ("y", C.c_void_p),
-                ("y_dtype", C.c_int), ("flags", C.c_uint32), ("stream", C.c_void_p)]
+                ("y_dtype", C.c_int), ("flags", C.c_uint32), ("stream", C.c_void_p), ("relu2_up", C.c_void_p)]
 
 
 TB_NORM_ZERO_CENTERED = 1

@@ -320,7 +320,7 @@ class B200Backend:
         check(self._L.tb_linear_forward_dev(self._h, t._h, C.byref(args), None))
 
     def norm_linear_forward_dev(self, t, x, y, *, norm_weight=None, eps: float = 0.0, zero_centered: bool = False,
-                                residual=None, flags: int = 0, stream=None) -> None:
+                                residual=None, relu2_up=None, flags: int = 0, stream=None) -> None:
         """RMSNorm -> int8 quantiser -> packed linear -> ``residual + y`` on device tensors, without synchronising.
 
         The decode block's fused step (crates/tritium-cuda/kernels/decode.cu:533-640 in front,
@@ -335,6 +335,8 @@ class B200Backend:
         args.norm_eps = eps
         args.norm_flags = _lib.TB_NORM_ZERO_CENTERED if zero_centered else 0
         args.residual = residual.data_ptr() if residual is not None else None
+        # squared-ReLU gate (crates/tritium-cuda/kernels/decode.cu:772-780): x = gate projection, relu2_up = up projection
+        args.relu2_up = relu2_up.data_ptr() if relu2_up is not None else None
         args.m = x.shape[0] if x.dim() > 1 else 1
         args.y = y.data_ptr(); args.y_dtype = dt[y.dtype]
         args.flags = flags

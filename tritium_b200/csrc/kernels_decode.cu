@@ -63,6 +63,10 @@ struct DecodeParams {
   // behind the token scale (fp32, indexed like y; null = none)
   const float* norm_weight; float norm_eps; uint32_t norm_zero_centered;
   const float* residual;
+  // squared-ReLU gate in front of the quantiser (null = none): x holds the gate projection's fp32
+  // output, relu2_up the up projection's, and the activation is (max(x, 0)^2) * up, the
+  // reference's relu2_gate_f32 (crates/tritium-cuda/kernels/decode.cu:772-780)
+  const float* relu2_up;
   // tensor-parallel row shard (tp != 0): absmax exchange of the fused prologue, output sum over the ranks
   TbCommView comm_absmax, comm_y; uint32_t tp;
   void* y; int32_t* acc_dump; const float* row_scale;
@@ -329,11 +333,17 @@ __device__ __forceinline__ uint2 z_bytewise(const int8_t* xq_tile, const Slot<CO
 // int[m][tpr][2] (padded to 16) | token scales float[m] (padded to 16).
 struct PrepareParams {
   const void* x; const float* act_scale_in; const float* act_absmax_in;
+  const float* relu2_up;   // squared-ReLU gate: activation = (max(x, 0)^2) * relu2_up (x fp32); null = none
   uint8_t* tables; uint32_t* status;
   uint32_t m, mk, k, tpr, x_dtype, off_cinit, off_actscale, pdl;   // m valid tokens (grid.y), tables laid out for mk
   TbCommView comm;   // world > 1: the per-token absmax is the maximum over the ranks' slices
 };
 
+// (max(g, 0)^2) * u with the reference's association and no contraction
+__device__ __forceinline__ float relu2_gate(float g, float u) {
+  const float r = fmaxf(g, 0.0f);
+  return __fmul_rn(__fmul_rn(r, r), u);
+}
 __device__ __forceinline__ float load_act(const void* x, uint32_t dtype, size_t i) {
   return dtype == TB_F32 ? static_cast<const float*>(x)[i] : __bfloat162float(static_cast<const __nv_bfloat16*>(x)[i]);
 }
@@ -360,7 +370,12 @@ __global__ void __launch_bounds__(256) prepare_kernel(const PrepareParams p) {
       gamma = p.act_absmax_in[t];   // absmax over the full (unsharded) row, supplied by the caller
     } else {
       float mx = 0.f;
-      for (uint32_t i = tid; i < p.k; i += 256) mx = fmaxf(mx, fabsf(load_act(p.x, p.x_dtype, size_t(t) * p.k + i)));
+      for (uint32_t i = tid; i < p.k; i += 256) {
+        const size_t at = size_t(t) * p.k + i;
+        float v = load_act(p.x, p.x_dtype, at);
+        if (p.relu2_up) v = relu2_gate(v, p.relu2_up[at]);
+        mx = fmaxf(mx, fabsf(v));
+      }
       for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
       if (lane == 0) red[warp] = mx;
       __syncthreads();
@@ -405,7 +420,8 @@ __global__ void __launch_bounds__(256) prepare_kernel(const PrepareParams p) {
     }
     const float scale_q = gamma > 0.f ? __fdiv_rn(127.0f, gamma) : 0.f;
     scale_out = __fdiv_rn(gamma, 127.0f);
-    const float v = load_act(p.x, p.x_dtype, size_t(t) * p.k + j * 256 + tid);
+    float v = load_act(p.x, p.x_dtype, size_t(t) * p.k + j * 256 + tid);
+    if (p.relu2_up) v = relu2_gate(v, p.relu2_up[size_t(t) * p.k + j * 256 + tid]);
     if (!(fabsf(v) <= FLT_MAX) && atomicOr(&p.status[TBS_FLAGS], TBF_NONFINITE_ACT) == 0) {
       p.status[TBS_INFO0] = t * p.k + j * 256 + tid; p.status[TBS_INFO1] = __float_as_uint(v);
     }
@@ -513,6 +529,14 @@ __device__ __forceinline__ void apply_norm(const DecodeParams& p, float inv, uin
   }
 }
 
+// squared-ReLU gate for eight consecutive activations (see relu2_gate)
+__device__ __forceinline__ void apply_gate(const DecodeParams& p, size_t at, float (&v)[8]) {
+  float u[8];
+  load8(p.relu2_up, TB_F32, at, u);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) v[e] = relu2_gate(v[e], u[e]);
+}
+
 template <int CODEC, bool DUAL, int M>
 __device__ __forceinline__ void build_tables(const DecodeParams& p, uint8_t* smem, uint32_t tid, uint32_t tp_seq) {
   constexpr int kNM = MmaCount<CODEC, DUAL>::value;
@@ -576,6 +600,7 @@ __device__ __forceinline__ void build_tables(const DecodeParams& p, uint8_t* sme
         for (uint32_t i = tid * 8; i < p.k && uint32_t(t) < p.m; i += kConsumerThreads * 8) {
           float v[8];
           load8(p.x, p.x_dtype, size_t(t) * p.k + i, v);
+          if (p.relu2_up) apply_gate(p, size_t(t) * p.k + i, v);
           if (norm) apply_norm(p, inv_rms[t], i, v);
 #pragma unroll
           for (int e = 0; e < 8; ++e) mx = fmaxf(mx, fabsf(v[e]));
@@ -648,6 +673,7 @@ __device__ __forceinline__ void build_tables(const DecodeParams& p, uint8_t* sme
       float sq = scale_q[0], inv = inv_rms[0];
 #pragma unroll
       for (int tt = 1; tt < M; ++tt) { sq = t == uint32_t(tt) ? scale_q[tt] : sq; inv = t == uint32_t(tt) ? inv_rms[tt] : inv; }
+      if (p.relu2_up) apply_gate(p, size_t(t) * p.k + j * 256 + lane * 8, v);
       if (norm) apply_norm(p, inv, j * 256 + lane * 8, v);
       int q[8];
       bool bad = false;
@@ -1268,6 +1294,10 @@ cudaError_t tb_launch_prepare(const DecodeArgs& a, cudaStream_t stream) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   PrepareParams pp{};
   pp.x = a.x; pp.act_scale_in = a.act_scale_in; pp.act_absmax_in = a.act_absmax_in;
+  if (a.relu2_up) {
+    if (a.x_dtype != TB_F32) return cudaErrorInvalidValue;
+    pp.relu2_up = a.relu2_up;
+  }
   pp.tables = static_cast<uint8_t*>(a.scratch);
   pp.m = a.m; pp.mk = layout_tokens(a.m); pp.k = uint32_t(w->k); pp.tpr = uint32_t(w->k / 256); pp.x_dtype = uint32_t(a.x_dtype);
   pp.off_cinit = tl.off_cinit; pp.off_actscale = tl.off_actscale; pp.pdl = a.pdl ? 1u : 0u;
@@ -1310,6 +1340,10 @@ cudaError_t tb_launch_decode(const DecodeArgs& a, int sm_count, int max_smem, cu
     if (a.comm_y && a.comm_y->world > 1 && !a.comm_absmax && !a.act_absmax_in && a.x_dtype != TB_I8) return cudaErrorInvalidValue;
     if (a.x_dtype == TB_I8 && !a.act_scale_in) return cudaErrorInvalidValue;
     p.fused = 1; p.x = a.x; p.act_scale_in = a.act_scale_in; p.act_absmax_in = a.act_absmax_in; p.x_dtype = uint32_t(a.x_dtype);
+    if (a.relu2_up) {
+      if (a.x_dtype != TB_F32 || (reinterpret_cast<uintptr_t>(a.relu2_up) & 15u) || a.norm_weight) return cudaErrorInvalidValue;
+      p.relu2_up = a.relu2_up;
+    }
     if (a.norm_weight) {
       if (a.x_dtype == TB_I8 || (reinterpret_cast<uintptr_t>(a.norm_weight) & 15u)) return cudaErrorInvalidValue;
       p.norm_weight = a.norm_weight; p.norm_eps = a.norm_eps; p.norm_zero_centered = a.norm_zero_centered ? 1u : 0u;

@@ -200,6 +200,7 @@ __host__ __device__ inline uint32_t d2_slot(uint32_t t) {
 // ---------------------------------------------------------------- quantisation pre-pass
 struct QuantParams {
   const void* x; const float* act_scale_in; const float* act_absmax_in;
+  const float* relu2_up;   // squared-ReLU gate (x fp32): activation = (max(x, 0)^2) * relu2_up; null = none
   int8_t* qperm; int32_t* qinit; float* ascale;
   uint32_t m, m_pad, k, x_dtype, codec;
   uint32_t* status;
@@ -226,8 +227,9 @@ __global__ void __launch_bounds__(256) prefill_quant_kernel(const QuantParams p)
     else {
       float mx = 0.f;
       for (uint32_t i = tid; i < p.k; i += 256) {
-        const float v = p.x_dtype == TB_F32 ? static_cast<const float*>(p.x)[size_t(t) * p.k + i]
-                                            : __bfloat162float(static_cast<const __nv_bfloat16*>(p.x)[size_t(t) * p.k + i]);
+        float v = p.x_dtype == TB_F32 ? static_cast<const float*>(p.x)[size_t(t) * p.k + i]
+                                      : __bfloat162float(static_cast<const __nv_bfloat16*>(p.x)[size_t(t) * p.k + i]);
+        if (p.relu2_up) { const float r = fmaxf(v, 0.0f); v = __fmul_rn(__fmul_rn(r, r), p.relu2_up[size_t(t) * p.k + i]); }
         mx = fmaxf(mx, fabsf(v));
       }
       for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
@@ -249,8 +251,9 @@ __global__ void __launch_bounds__(256) prefill_quant_kernel(const QuantParams p)
       int q;
       if (p.x_dtype == TB_I8) q = static_cast<const int8_t*>(p.x)[size_t(t) * p.k + i];
       else {
-        const float v = p.x_dtype == TB_F32 ? static_cast<const float*>(p.x)[size_t(t) * p.k + i]
-                                            : __bfloat162float(static_cast<const __nv_bfloat16*>(p.x)[size_t(t) * p.k + i]);
+        float v = p.x_dtype == TB_F32 ? static_cast<const float*>(p.x)[size_t(t) * p.k + i]
+                                      : __bfloat162float(static_cast<const __nv_bfloat16*>(p.x)[size_t(t) * p.k + i]);
+        if (p.relu2_up) { const float r = fmaxf(v, 0.0f); v = __fmul_rn(__fmul_rn(r, r), p.relu2_up[size_t(t) * p.k + i]); }
         // a NaN would clamp to a finite code: report non-finite activations instead
         if (!(fabsf(v) <= 3.402823466e+38f) && atomicOr(&p.status[TBS_FLAGS], TBF_NONFINITE_ACT) == 0) {
           p.status[TBS_INFO0] = t * p.k + i; p.status[TBS_INFO1] = __float_as_uint(v);
@@ -1086,6 +1089,10 @@ cudaError_t tb_launch_prefill(const PrefillArgs& a, int sm_count, cudaStream_t s
 
   QuantParams qp{};
   qp.x = a.x; qp.act_scale_in = a.act_scale_in; qp.act_absmax_in = a.act_absmax_in;
+  if (a.relu2_up) {
+    if (a.x_dtype != TB_F32) return cudaErrorInvalidValue;
+    qp.relu2_up = a.relu2_up;
+  }
   qp.qperm = sc.qperm; qp.qinit = sc.qinit; qp.ascale = sc.ascale;
   qp.m = a.m; qp.m_pad = m_pad; qp.k = k; qp.x_dtype = uint32_t(a.x_dtype); qp.codec = uint32_t(w->codec); qp.status = a.status;
   prefill_quant_kernel<<<m_pad, 256, 0, stream>>>(qp);

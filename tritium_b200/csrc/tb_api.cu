@@ -358,6 +358,7 @@ tb_status reserve_prefill(tb_backend* b, const tb_weights* w, uint32_t m);
 struct BlockExtras {
   const float* norm_weight = nullptr; float norm_eps = 0.f; bool norm_zero_centered = false;
   const float* residual = nullptr;
+  const float* relu2_up = nullptr;   // squared-ReLU gate: activation = (max(x, 0)^2) * relu2_up
 };
 
 // Device-pointer dispatch shared by every entry point.  Returns the kernel family used.
@@ -369,6 +370,11 @@ tb_status forward_dev(tb_backend* b, const tb_weights* w, const tb_forward_args&
   const bool a8 = (a.flags & TB_FWD_A8) != 0 || a.x_dtype == TB_I8;
   if ((ex.norm_weight || ex.residual) && !a8) return tb_fail(TB_INVALID_INPUT, "the norm and residual steps belong to the int8 path");
   if (ex.norm_weight && a.x_dtype == TB_I8) return tb_fail(TB_INVALID_INPUT, "RMSNorm takes fp32 or bf16 activations");
+  if (ex.relu2_up) {
+    if (a.x_dtype != TB_F32) return tb_fail(TB_INVALID_INPUT, "the squared-ReLU gate takes the fp32 outputs of the gate and up projections");
+    if (ex.norm_weight || a.act_absmax) return tb_fail(TB_INVALID_INPUT, "the squared-ReLU gate is not combined with RMSNorm or a supplied absmax");
+    if (!w->fast) return tb_fail(TB_UNSUPPORTED_FORMAT, "the squared-ReLU gate needs uniform plane counts, k % 256 == 0, group 128 and codec D2 or B3");
+  }
   if (!a8) {
     if (a.x_dtype != TB_F32 || a.y_dtype != TB_F32) return tb_fail(TB_INVALID_INPUT, "the fp32 path takes fp32 activations and outputs");
     if (!(a.flags & TB_FWD_EXACT) && w->fast && a.m <= (1u << 20)) {
@@ -452,7 +458,7 @@ tb_status forward_dev(tb_backend* b, const tb_weights* w, const tb_forward_args&
     }
     PrefillArgs pa{w, a.x, a.x_dtype, a.act_scale, a.act_absmax, a.m, a.y, a.y_dtype, a.acc_dump, a.row_scale,
                    b->d_q, b->d_q_cap, b->d_status};
-    pa.residual = ex.residual; pa.tile_counters = b->d_tile_counters;
+    pa.residual = ex.residual; pa.tile_counters = b->d_tile_counters; pa.relu2_up = ex.relu2_up;
     TB_CUDA(tb_launch_prefill(pa, b->prop.multiProcessorCount, st), "launch prefill");
     fill_receipt(w, a.m, dtype_size(a_in.x_dtype), dtype_size(a.y_dtype), 2, 2 + extra_launches, receipt);
     return TB_OK;
@@ -465,7 +471,8 @@ tb_status forward_dev(tb_backend* b, const tb_weights* w, const tb_forward_args&
   for (uint32_t m0 = 0; m0 < a.m; m0 += 4) {
     const uint32_t mc = std::min<uint32_t>(4, a.m - m0);
     const bool fused = tb_decode_builds_tables(w, mc, a.x) &&
-                       (!ex.norm_weight || (reinterpret_cast<uintptr_t>(ex.norm_weight) & 15u) == 0);
+                       (!ex.norm_weight || (reinterpret_cast<uintptr_t>(ex.norm_weight) & 15u) == 0) &&
+                       (!ex.relu2_up || (reinterpret_cast<uintptr_t>(ex.relu2_up) & 15u) == 0);
     if (!tb_decode_supported(w, mc, b->max_smem_optin, nullptr))
       return tb_fail(TB_UNSUPPORTED_FORMAT, "the decode kernel's shared-memory plan does not fit this shape");
     DecodeArgs d{};
@@ -480,6 +487,7 @@ tb_status forward_dev(tb_backend* b, const tb_weights* w, const tb_forward_args&
       }
     }
     d.residual = ex.residual ? ex.residual + size_t(m0) * w->n : nullptr;
+    d.relu2_up = ex.relu2_up ? ex.relu2_up + size_t(m0) * w->k : nullptr;
     d.act_scale_in = a.act_scale ? a.act_scale + m0 : nullptr;
     d.act_absmax_in = a.act_absmax ? a.act_absmax + m0 : nullptr;
     d.y = static_cast<uint8_t*>(a.y) + size_t(m0) * w->n * dtype_size(a.y_dtype);
@@ -613,6 +621,7 @@ extern "C" tb_status tb_norm_linear_forward_dev(tb_backend* b, const tb_weights*
   BlockExtras ex;
   ex.norm_weight = args->norm_weight; ex.norm_eps = args->norm_eps;
   ex.norm_zero_centered = (args->norm_flags & TB_NORM_ZERO_CENTERED) != 0; ex.residual = args->residual;
+  ex.relu2_up = args->relu2_up;
   return forward_dev(b, w, a, st, receipt, ex);
 }
 

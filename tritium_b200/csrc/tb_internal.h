@@ -169,6 +169,9 @@ struct DecodeArgs {
   // 16-byte aligned; null = none).  Any launch: out = residual + y (fp32, indexed like y).
   const float* norm_weight; float norm_eps; bool norm_zero_centered;
   const float* residual;
+  // squared-ReLU gate in front of the quantiser (fp32 x = gate projection, relu2_up = up
+  // projection, both [m][k]; 16-byte aligned for fused launches; not together with the norm)
+  const float* relu2_up;
 };
 cudaError_t tb_launch_prepare(const DecodeArgs& a, cudaStream_t stream);
 // Whether a decode launch of `m` tokens should build its activation tables itself (one launch)
@@ -191,6 +194,7 @@ struct PrefillArgs {
   void* scratch; size_t scratch_bytes;   // permuted int8 activations, slab start values, token scales
   uint32_t* status;
   const float* residual = nullptr;       // [m][n] fp32, nullable: out = residual + y
+  const float* relu2_up = nullptr;       // squared-ReLU gate: activation = (max(x, 0)^2) * relu2_up (x fp32)
   uint32_t* tile_counters = nullptr;     // 256 zeroed words (few-token launches split K and count the splits of a tile in)
 };
 bool tb_prefill_supported(const tb_weights* w, uint32_t m);
