@@ -358,6 +358,62 @@ def measure_c1_fp32(torch, backend, codec, stream, peak: float, peak_kind: str) 
     return out
 
 
+def measure_mlp_block(torch, backend, codec, stream) -> dict:
+    """A decoder's MLP block at M=1 on the 2B-class shapes (hidden 2560, ffn 6912, one plane), chained
+    through 30 distinct blocks (> L2): RMSNorm -> gate+up projection (one launch, the norm runs in the
+    kernel's table builder), then squared-ReLU gate -> down projection -> + residual (preparation kernel
+    + decode kernel, gate and residual fused).  Three launches per block, none of them elementwise."""
+    from tritium_b200 import _lib
+    from tritium_b200.synth import make_tensor
+    hidden, ffn, blocks = 2560, 6912, 30
+    ws = []
+    total = 0
+    for i in range(blocks):
+        row = []
+        for name, n, k in (("gate_up", 2 * ffn, hidden), ("down", hidden, ffn)):
+            t = make_tensor(f"b{i}.{name}", n, k, 1, seed=2 * i + (name == "down"))
+            payload, scales, pmap, terminal, _ = t.resident(codec)
+            total += len(payload) + len(scales)
+            row.append(backend.upload_salt_v2_arenas(codec, 128, n, k, payload, scales, pmap, terminal))
+        ws.append(row)
+    norm_w = torch.ones(hidden, device="cuda") + 0.01 * torch.randn(hidden, device="cuda")
+    xs = [torch.zeros(1, hidden, device="cuda") for _ in range(2)]
+    xs[0].normal_()
+    y_gu = torch.zeros(1, 2 * ffn, device="cuda")
+    gate, up = y_gu[:, :ffn], y_gu[:, ffn:]
+    flags = _lib.TB_FWD_PDL
+
+    def step():
+        for i, (w_gu, w_down) in enumerate(ws):
+            src, dst = xs[i & 1], xs[(i + 1) & 1]
+            backend.norm_linear_forward_dev(w_gu, src, y_gu, norm_weight=norm_w, eps=1e-6, flags=flags, stream=stream)
+            backend.norm_linear_forward_dev(w_down, gate, dst, relu2_up=up, residual=src, flags=flags, stream=stream)
+
+    out = {"workload": "mlp_block_2b_1plane_m1", "blocks": blocks, "packed_bytes_per_block": total // blocks, "launches_per_block": 3}
+    with torch.cuda.stream(stream):
+        step()
+        stream.synchronize()
+        backend.check(stream)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            step()
+        for label, fn in (("eager", step), ("graph_pdl", graph.replay)):
+            for _ in range(3):
+                fn()
+            stream.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(5):
+                fn()
+            e1.record(stream)
+            stream.synchronize()
+            backend.check(stream)
+            us = e0.elapsed_time(e1) / 5 / blocks * 1e3
+            out[label] = {"us_per_block": us, "weight_gbs": (total / blocks) / us / 1e3}
+    out["finite"] = bool(torch.isfinite(xs[0]).all() and torch.isfinite(xs[1]).all())
+    return out
+
+
 def measure_reference_gpu_kernels(torch, backend, stream) -> dict:
     """The reference's own CUDA kernels (built from its sources into oracle/_ref) beside this
     library's kernels, on the same GPU, the same 1-plane TQ2_0-class weights with a per-channel
@@ -664,10 +720,14 @@ def run_b200(args) -> None:
                 prefill["roofline"]["int8_gemm_peak_measured"] = int8_peak
                 prefill["roofline"]["frac_of_measured_int8_gemm"] = prefill["roofline"]["achieved"] / int8_peak["tops"]
 
-    few_tokens = c1_fp32 = None
+    few_tokens = c1_fp32 = mlp_block = None
     if world == 1 and not args.quick:
         few_tokens = measure_few_tokens(torch, backend, codec, stream)
         c1_fp32 = measure_c1_fp32(torch, backend, codec, stream, peak, peak_kind)
+        try:
+            mlp_block = measure_mlp_block(torch, backend, codec, stream)
+        except Exception as exc:  # an extra leg must not take the benchmark down with it
+            mlp_block = {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
 
     ref_gpu = None
     if world == 1 and not args.quick:
@@ -740,6 +800,7 @@ def run_b200(args) -> None:
             "prefill": prefill,
             "few_tokens": few_tokens,
             "c1_fp32": c1_fp32,
+            "mlp_block": mlp_block,
             "reference_gpu_kernels": ref_gpu,
             "tp": tp_leg,
             "stack_2b": stack_2b,
