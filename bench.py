@@ -251,7 +251,7 @@ def measure_e2e_per_linear(torch, backend, weights, x_bits, m: int, layer_bytes:
 
 def measure_int8_peak(torch) -> dict | None:
     """Dense INT8 GEMM rate of the library GEMM on this GPU (torch._int_mm, 8192^3, best of 10):
-    the denominator SURVEY-style rooflines ask for when no INT8 figure was measured beforehand."""
+    the INT8 denominator of the tensor-core leg's roofline, measured in the same run."""
     try:
         n = 8192
         a = torch.randint(-8, 8, (n, n), dtype=torch.int8, device="cuda")

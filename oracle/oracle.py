@@ -31,7 +31,8 @@ def build(force: bool = False) -> str:
     return _LIB_PATH
 
 
-_REF_ROOT = os.environ.get("TRITIUM_REFERENCE", "/root/reference")
+# root of the reference checkout: the TRITIUM_REFERENCE variable, else a `reference` folder beside this repository
+_REF_ROOT = os.environ.get("TRITIUM_REFERENCE", os.path.normpath(os.path.join(_HERE, "..", "..", "reference")))
 
 
 def build_reference_kernels() -> list:
