@@ -203,21 +203,7 @@ __device__ __forceinline__ void mma_u8s8_first(int (&d)[4], uint32_t a0, uint32_
 constexpr uint32_t kC3 = 0x35533553u, kK3 = 0x61566156u;
 constexpr uint32_t kC9 = 0x2f192f19u, kK9 = 0x631e631eu;
 constexpr uint32_t kC9b = 0x2f1f2f1fu, kK9b = 0x631d631du;
-__device__ __forceinline__ void b3_quads(uint32_t w, uint32_t (&q)[5]) {
-  const uint32_t h01 = prmt(w, 0x64646464u, 0x4140u);  // halves 1024+b0, 1024+b1
-  const uint32_t h23 = prmt(w, 0x64646464u, 0x4342u);  // halves 1024+b2, 1024+b3
-  const uint32_t a1 = hfma2_bits(h01, kC3, kK3), b1 = hfma2_bits(h23, kC3, kK3);
-  const uint32_t a2 = hfma2_bits(h01, kC9, kK9), b2 = hfma2_bits(h23, kC9, kK9);
-  const uint32_t a3 = hfma2_bits(a1, kC9, kK9), b3 = hfma2_bits(b1, kC9, kK9);
-  const uint32_t a4 = hfma2_bits(a2, kC9b, kK9b), b4 = hfma2_bits(b2, kC9b, kK9b);
-  q[0] = w;
-  q[1] = prmt(a1, b1, 0x6420u);
-  q[2] = prmt(a2, b2, 0x6420u);
-  q[3] = prmt(a3, b3, 0x6420u);
-  q[4] = prmt(a4, b4, 0x6420u);
-}
-
-// The same for the packed words of two rows, in MMA operand order: A[2i] = q_i of row a,
+// For the packed words of two rows, in MMA operand order: A[2i] = q_i of row a,
 // A[2i+1] = q_i of row b.  A[10] and A[11] pad the third MMA; they meet zero B entries, so their
 // value does not matter and they are left unwritten.
 __device__ __forceinline__ void b3_quads2(uint32_t wa, uint32_t wb, uint32_t (&A)[12]) {

@@ -505,7 +505,6 @@ __global__ void __launch_bounds__(threads_of(EPI, EXP), 1) prefill_kernel(const 
   constexpr int kChunk = 16;
   static_assert(kCW % kChunk == 0, "an epilogue thread drains whole 16-column chunks");
   constexpr uint32_t kSlabsPerCol = 2 * PLANES;
-  constexpr uint32_t kPlaneBytes = CODEC == tbf::kB3 ? 52 : 64;
   constexpr uint32_t kIdesc = instr_desc_n(HW);
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
