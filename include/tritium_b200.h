@@ -172,6 +172,9 @@ tb_status tb_salt_v2_gather_rows(tb_backend* backend, const tb_weights* weights,
 /* ------------------------------------------------------------------ forward, device pointers
  * Same operators on device memory, launched on `stream` (a cudaStream_t, NULL = the backend's
  * stream) without any host synchronisation or allocation beyond the backend's own scratch.
+ * The backend's stream is non-blocking: work on it is NOT ordered with the legacy default stream.
+ * A caller whose tensors are produced on the default stream passes cudaStreamLegacy (the handle
+ * 0x1), not NULL, and keeps every buffer of a call alive until the stream has run it.
  * flags: */
 #define TB_FWD_A8 1u          /* int8-quantise activations (x_dtype F32 or BF16), or consume int8 */
 #define TB_FWD_EXACT 2u       /* force the bit-exact kernel (fp32 activations only) */

@@ -67,6 +67,15 @@ class NormLinearArgs(C.Structure):
 
 TB_NORM_ZERO_CENTERED = 1
 
+
+def stream_handle(stream) -> int:
+    """cudaStream_t of a torch stream for the C ABI.  The ABI reads NULL as "the backend's own
+    stream", which is non-blocking and therefore not ordered with anything torch does; torch's
+    default stream has the handle 0, so it is passed as cudaStreamLegacy (0x1), which names the
+    legacy default stream explicitly."""
+    handle = int(stream.cuda_stream)
+    return handle if handle else 1
+
 READ_AT_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_uint64, C.c_void_p, C.c_size_t)
 
 

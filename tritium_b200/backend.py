@@ -316,7 +316,7 @@ class B200Backend:
         args.row_scale = row_scale.data_ptr() if row_scale is not None else None
         args.flags = flags | (_lib.TB_FWD_A8 if a8 else 0)
         s = stream if stream is not None else torch.cuda.current_stream()
-        args.stream = s.cuda_stream
+        args.stream = _lib.stream_handle(s)
         check(self._L.tb_linear_forward_dev(self._h, t._h, C.byref(args), None))
 
     def norm_linear_forward_dev(self, t, x, y, *, norm_weight=None, eps: float = 0.0, zero_centered: bool = False,
@@ -341,7 +341,7 @@ class B200Backend:
         args.y = y.data_ptr(); args.y_dtype = dt[y.dtype]
         args.flags = flags
         s = stream if stream is not None else torch.cuda.current_stream()
-        args.stream = s.cuda_stream
+        args.stream = _lib.stream_handle(s)
         check(self._L.tb_norm_linear_forward_dev(self._h, t._h, C.byref(args), None))
 
     def act_absmax_dev(self, x, out, stream=None) -> None:
@@ -350,14 +350,14 @@ class B200Backend:
         dt = {torch.float32: _lib.TB_F32, torch.bfloat16: _lib.TB_BF16}
         s = stream if stream is not None else torch.cuda.current_stream()
         check(self._L.tb_act_absmax_dev(self._h, C.c_void_p(x.data_ptr()), dt[x.dtype], C.c_uint32(x.shape[0]),
-                                        C.c_uint32(x.shape[1]), C.c_void_p(out.data_ptr()), C.c_void_p(s.cuda_stream)))
+                                        C.c_uint32(x.shape[1]), C.c_void_p(out.data_ptr()), C.c_void_p(_lib.stream_handle(s))))
 
     def reserve(self, t, max_m: int) -> None:
         check(self._L.tb_backend_reserve(self._h, t._h, C.c_uint32(max_m)))
 
     def check(self, stream=None) -> None:
         """Reads the device status word (bounded-wait timeouts, non-finite values); synchronises."""
-        check(self._L.tb_backend_check(self._h, C.c_void_p(stream.cuda_stream) if stream is not None else None))
+        check(self._L.tb_backend_check(self._h, C.c_void_p(_lib.stream_handle(stream)) if stream is not None else None))
 
     def synchronize(self) -> None:
         check(self._L.tb_backend_synchronize(self._h))
@@ -393,7 +393,7 @@ class LinearStack:
         check(self._backend._L.tb_stack_forward_dev(
             self._h, C.c_void_p(x.data_ptr()), dt[x.dtype], C.c_uint32(x.shape[0]),
             C.c_void_p(y_last.data_ptr()) if y_last is not None else None,
-            dt[y_last.dtype] if y_last is not None else _lib.TB_BF16, C.c_uint32(flags), C.c_void_p(s.cuda_stream)))
+            dt[y_last.dtype] if y_last is not None else _lib.TB_BF16, C.c_uint32(flags), C.c_void_p(_lib.stream_handle(s))))
 
     def forward_host(self, x: np.ndarray, m: int, x_is_bf16: bool = False, flags: int = 0) -> np.ndarray:
         """Host buffers in and out: every layer's bf16 output bits as [layers, m, n] (uint16); the

@@ -146,9 +146,10 @@ class PeerComm:
     def all_reduce(self, slot: int, count: int, out, op_max: bool = False, stream=None) -> None:
         import ctypes as C
         import torch
+        from . import _lib
         s = stream if stream is not None else torch.cuda.current_stream()
         self._check(self._L.tb_comm_allreduce_f32(self._h, C.c_uint32(slot), C.c_uint32(count), int(op_max),
-                                                  C.c_void_p(out.data_ptr()), C.c_void_p(s.cuda_stream)))
+                                                  C.c_void_p(out.data_ptr()), C.c_void_p(_lib.stream_handle(s))))
 
     def linear_fused(self, handle, slot_absmax: int, slot_y: int, x, y, stream=None, flags: int = 0) -> None:
         """Row-parallel forward of up to 8 tokens (`tb_linear_forward_tp_dev`): the absmax exchange
@@ -162,7 +163,7 @@ class PeerComm:
         self._check(self._L.tb_linear_forward_tp_dev(self.backend._h, handle._h, self._h, C.c_uint32(slot_absmax), C.c_uint32(slot_y),
                                                      C.c_void_p(x.data_ptr()), dt[x.dtype], C.c_uint32(x.shape[0]),
                                                      C.c_void_p(y.data_ptr()), dt[y.dtype], C.c_uint32(flags),
-                                                     C.c_void_p(s.cuda_stream)))
+                                                     C.c_void_p(_lib.stream_handle(s))))
 
     def set_wait_limit(self, sm_cycles: int) -> None:
         """Bound of every wait on a peer, in SM clock cycles (default about two seconds)."""
