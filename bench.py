@@ -720,14 +720,19 @@ def run_b200(args) -> None:
                 prefill["roofline"]["int8_gemm_peak_measured"] = int8_peak
                 prefill["roofline"]["frac_of_measured_int8_gemm"] = prefill["roofline"]["achieved"] / int8_peak["tops"]
 
+    def extra_leg(fn, *leg_args, **leg_kwargs):
+        """An explanatory leg beside the headline must not take the benchmark line down with it."""
+        try:
+            return fn(*leg_args, **leg_kwargs)
+        except Exception as exc:
+            torch.cuda.synchronize()
+            return {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
+
     few_tokens = c1_fp32 = mlp_block = None
     if world == 1 and not args.quick:
-        few_tokens = measure_few_tokens(torch, backend, codec, stream)
-        c1_fp32 = measure_c1_fp32(torch, backend, codec, stream, peak, peak_kind)
-        try:
-            mlp_block = measure_mlp_block(torch, backend, codec, stream)
-        except Exception as exc:  # an extra leg must not take the benchmark down with it
-            mlp_block = {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
+        few_tokens = extra_leg(measure_few_tokens, torch, backend, codec, stream)
+        c1_fp32 = extra_leg(measure_c1_fp32, torch, backend, codec, stream, peak, peak_kind)
+        mlp_block = extra_leg(measure_mlp_block, torch, backend, codec, stream)
 
     ref_gpu = None
     if world == 1 and not args.quick:
@@ -743,8 +748,10 @@ def run_b200(args) -> None:
             # the same decoder unsharded on this rank's GPU: the baseline of the efficiency figures below
             base = measure_tp(torch, None, backend, 0, 1, codec, codec_name, args, stream, shape_name=args.tp_shape, batches=batches,
                               m_prefill=args.tp_prefill_m, reduce_variants=False)
-        tp_leg = measure_tp(torch, dist, backend, rank, world, codec, codec_name, args, stream, shape_name=args.tp_shape,
-                            batches=batches, m_prefill=args.tp_prefill_m)
+        # (on several GPUs a leg that raised on one rank would leave the others in a collective: no guard there)
+        tp_leg = (measure_tp if world > 1 else lambda *a2, **k2: extra_leg(measure_tp, *a2, **k2))(
+            torch, dist, backend, rank, world, codec, codec_name, args, stream, shape_name=args.tp_shape,
+            batches=batches, m_prefill=args.tp_prefill_m)
         if world > 1:
             eff = {}
             for key, entry in tp_leg.items():
@@ -755,7 +762,7 @@ def run_b200(args) -> None:
             tp_leg["one_gpu_same_run"] = {k2: v for k2, v in base.items() if isinstance(v, dict) and "tokens_per_s" in v}
             tp_leg["efficiency_vs_one_gpu"] = eff
         if world == 1 and not args.quick and args.tp_shape == "27b":
-            stack_2b = measure_tp(torch, dist, backend, rank, world, codec, codec_name, args, stream, shape_name="2b", batches=[1, 16, 64])
+            stack_2b = extra_leg(measure_tp, torch, dist, backend, rank, world, codec, codec_name, args, stream, shape_name="2b", batches=[1, 16, 64])
 
     if rank == 0:
         cpu = None
