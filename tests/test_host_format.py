@@ -248,3 +248,36 @@ def test_backend_reports_missing_device_without_aborting():
     with pytest.raises(errors.Backend):
         B200Backend(0)
     assert Registry.init().names() == []
+
+
+def test_stream_handle_names_the_default_stream_explicitly():
+    """torch's default stream has the handle 0, which the C ABI reads as "the backend's own stream":
+    the wrapper must pass the legacy-stream handle instead, and any other handle unchanged."""
+    from types import SimpleNamespace
+    from tritium_b200 import _lib
+    assert _lib.stream_handle(SimpleNamespace(cuda_stream=0)) == 1
+    assert _lib.stream_handle(SimpleNamespace(cuda_stream=0x7F00DEAD)) == 0x7F00DEAD
+
+
+def test_reference_kernel_weight_layout_and_gate_restatement():
+    """The I2sInt8 packer used to feed the reference's own tensor-core kernel (8 x 32 tiles of 2-bit
+    codes, n-tile-major then k-tile-major, row-major inside a tile, tq2_0_imma.cu:36-55) and the
+    squared-ReLU gate restatement (decode.cu:764-780)."""
+    from oracle import oracle as orc
+    from oracle import ref_kernels
+    rng = np.random.default_rng(4)
+    trits = rng.integers(-1, 2, (24, 96)).astype(np.int8)
+    packed = ref_kernels.pack_i2s_int8(trits)
+    assert packed.size == (24 // 8) * (96 // 32) * 64
+    num_kt = 96 // 32
+    for nt in range(3):
+        for kt in range(num_kt):
+            tile = packed[(nt * num_kt + kt) * 64:(nt * num_kt + kt + 1) * 64]
+            for e in range(256):
+                code = (int(tile[e // 4]) >> (2 * (e % 4))) & 3
+                assert code - 1 == int(trits[nt * 8 + e // 32, kt * 32 + e % 32])
+    with pytest.raises(ValueError):
+        ref_kernels.pack_i2s_int8(trits[:23])
+    g = np.array([-2.0, 0.0, 0.5, 3.0], np.float32)
+    u = np.array([7.0, 7.0, -4.0, 0.25], np.float32)
+    assert np.array_equal(orc.relu2_gate(g, u), np.array([0.0, 0.0, -1.0, 2.25], np.float32))
