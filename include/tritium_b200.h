@@ -337,6 +337,13 @@ tb_status tb_comm_allreduce_f32(tb_comm* comm, uint32_t slot, uint32_t count, in
 tb_status tb_linear_forward_tp_dev(tb_backend* backend, const tb_weights* weights, tb_comm* comm, uint32_t slot_absmax,
                                    uint32_t slot_y, const void* x, tb_dtype x_dtype, uint32_t m, void* y, tb_dtype y_dtype,
                                    uint32_t flags, void* stream);
+/* The same with the block's fused steps of tb_norm_linear_args: `relu2_up` (the squared-ReLU gate
+ * acts on this rank's slice of the row: x and relu2_up are the local shards of the gate and up
+ * projections' outputs) and `residual` (added once, behind the sum over the ranks, so every rank
+ * stores the same bits).  `norm_weight` must be NULL: RMSNorm acts on the whole row and belongs in
+ * front of the column-parallel linear.  At most 8 tokens; flags: 0 or TB_FWD_PDL. */
+tb_status tb_block_linear_forward_tp_dev(tb_backend* backend, const tb_weights* weights, tb_comm* comm, uint32_t slot_absmax,
+                                         uint32_t slot_y, const tb_norm_linear_args* args);
 /* Bound of every wait on a peer, in SM clock cycles (default 4e9, about two seconds).  A wait
  * that runs out sets the backend's status word (TB_TIMEOUT at the next tb_backend_check) and the
  * kernel returns; nothing traps. */

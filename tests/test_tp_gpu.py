@@ -128,6 +128,63 @@ def timeout_main(rank, world, port, in_kernel, results):
         dist.destroy_process_group()
 
 
+def block_main(rank, world, port, results):
+    """Down-projection shape of an MLP block on two GPUs: squared-ReLU gate on each rank's slice in
+    front of the row-parallel linear, residual behind the sum over the ranks, one call."""
+    import torch.distributed as dist
+    from oracle import oracle as orc
+    from tritium_b200 import B200Backend, tp
+    from tritium_b200.format import SaltV2Codec
+    from tritium_b200.synth import make_tensor
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        backend = B200Backend(rank)
+        comm = tp.PeerComm(backend, rank, world, slot_bytes=64 * 512 * 4, slots=8)
+        ex = tp.CudaExecutor(backend, comm=comm)
+        out = {}
+        for m, n, k, planes in [(1, 256, 1024, 2), (4, 320, 6912, 1), (7, 200, 1536, 3)]:   # in-kernel tables, preparation kernel, two passes
+            tensor = make_tensor("down", n, k, planes, seed=3 + m)
+            rng = np.random.default_rng(m)
+            gate = rng.standard_normal((m, k)).astype(np.float32)
+            up = rng.standard_normal((m, k)).astype(np.float32)
+            residual = rng.standard_normal((m, n)).astype(np.float32)
+            otensor = orc.Tensor(n, k, 128, tensor.plane_count.copy(), tensor.trits.copy(), tensor.scales.copy())
+            want = (residual + orc.a8_linear(otensor, orc.relu2_gate(gate, up), dump=False)[0]).astype(np.float32)
+            row = tp.TPLinear(ex, tensor, SaltV2Codec.B3, "row", rank, world, max_m=m, act_dtype=torch.float32)
+            g = row.geometry
+            up_dev = torch.zeros_like(row.x)
+            row.input_view(m).copy_(torch.from_numpy(np.ascontiguousarray(gate[:, g.k_offset:g.k_offset + g.k_valid])))
+            up_dev[:m, :g.k_valid].copy_(torch.from_numpy(np.ascontiguousarray(up[:, g.k_offset:g.k_offset + g.k_valid])))
+            r_dev = torch.from_numpy(residual).cuda()
+            for _ in range(2):
+                comm.block_linear_fused(row.handle, row.slot_absmax, row.slot_y, row.x[:m], row.y[:m], relu2_up=up_dev[:m], residual=r_dev)
+            torch.cuda.synchronize()
+            backend.check()
+            bits = [torch.zeros_like(row.y[:m]) for _ in range(world)]
+            dist.all_gather(bits, row.y[:m].contiguous())
+            torch.cuda.synchronize()
+            out[m] = (rel_l2(row.y[:m].cpu().numpy() - residual, want - residual), bool(all(torch.equal(bits[0], b2) for b2 in bits)))
+        results[rank] = out
+        comm.close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpu_block_linear_with_gate_and_residual():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    with mp.Manager() as manager:
+        results = manager.dict()
+        mp.spawn(block_main, args=(2, free_port(), results), nprocs=2, join=True)
+        for rank in range(2):
+            for m, (err, same) in results[rank].items():
+                assert err <= 1e-5 and same, (rank, m, err, same)
+
+
 @pytest.mark.parametrize("in_kernel", [0, 1], ids=["one_shot_reduce", "in_kernel_exchange"])
 def test_two_gpu_wait_on_an_absent_peer_runs_out(in_kernel):
     if torch.cuda.device_count() < 2:

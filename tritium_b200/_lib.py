@@ -23,7 +23,7 @@ EXPORTS = [
     "tb_salt_v2_upload", "tb_salt_v2_upload_package", "tb_weights_info_get", "tb_weights_free",
     "tb_salt_v2_forward_exact", "tb_linear_forward_f32", "tb_linear_forward_a8",
     "tb_salt_v2_gather_rows", "tb_linear_forward_dev", "tb_norm_linear_forward_dev", "tb_act_absmax_dev",
-    "tb_linear_forward_tp_dev", "tb_comm_create", "tb_comm_export", "tb_comm_connect", "tb_comm_slot", "tb_comm_allreduce_f32", "tb_comm_set_wait_limit", "tb_comm_disconnect", "tb_comm_free", "tb_mpgemm", "tb_mpgemm_with_act_quant",
+    "tb_linear_forward_tp_dev", "tb_block_linear_forward_tp_dev", "tb_comm_create", "tb_comm_export", "tb_comm_connect", "tb_comm_slot", "tb_comm_allreduce_f32", "tb_comm_set_wait_limit", "tb_comm_disconnect", "tb_comm_free", "tb_mpgemm", "tb_mpgemm_with_act_quant",
     "tb_stack_create", "tb_stack_forward_dev", "tb_stack_forward_host", "tb_stack_bytes_per_step", "tb_stack_read_output", "tb_stack_free",
     "tb_tp_shard_sizes", "tb_tp_shard", "tb_fmt_pack", "tb_fmt_unpack", "tb_fmt_plane_bytes",
     "tb_fmt_resident_sizes", "tb_fmt_resident_build", "tb_fmt_package_write", "tb_fmt_tq2_pack_rows",
@@ -151,6 +151,7 @@ _SIGNATURES = {
     "tb_stack_bytes_per_step": (C.c_uint64, [_P, _U32]),
     "tb_stack_read_output": (_ST, [_P, _U32, _U32, _P]),
     "tb_stack_free": (None, [_P]),
+    "tb_block_linear_forward_tp_dev": (_ST, [_P, _P, _P, _U32, _U32, _P]),
     "tb_comm_create": (_ST, [_P, _U32, _U32, _SZ, _U32, _U32, _P]),
     "tb_comm_export": (_ST, [_P, _P]),
     "tb_comm_connect": (_ST, [_P, _P]),

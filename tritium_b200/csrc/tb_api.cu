@@ -637,10 +637,31 @@ extern "C" tb_status tb_act_absmax_dev(tb_backend* b, const void* x, tb_dtype x_
   return TB_OK;
 }
 
+namespace {
+tb_status forward_tp(tb_backend* b, const tb_weights* w, tb_comm* comm, uint32_t slot_absmax, uint32_t slot_y, const void* x,
+                     tb_dtype x_dtype, uint32_t m, void* y, tb_dtype y_dtype, uint32_t flags, void* stream, const BlockExtras& ex);
+}
+
 extern "C" tb_status tb_linear_forward_tp_dev(tb_backend* b, const tb_weights* w, tb_comm* comm, uint32_t slot_absmax, uint32_t slot_y,
                                                const void* x, tb_dtype x_dtype, uint32_t m, void* y, tb_dtype y_dtype, uint32_t flags,
                                                void* stream) {
   clear_error();
+  return forward_tp(b, w, comm, slot_absmax, slot_y, x, x_dtype, m, y, y_dtype, flags, stream, BlockExtras{});
+}
+
+extern "C" tb_status tb_block_linear_forward_tp_dev(tb_backend* b, const tb_weights* w, tb_comm* comm, uint32_t slot_absmax,
+                                                     uint32_t slot_y, const tb_norm_linear_args* args) {
+  clear_error();
+  if (!args) return tb_fail(TB_NULL_ARG, "args is null");
+  if (args->norm_weight) return tb_fail(TB_INVALID_INPUT, "RMSNorm acts on the whole row: apply it in front of the column-parallel linear, not on a row shard");
+  BlockExtras ex;
+  ex.residual = args->residual; ex.relu2_up = args->relu2_up;
+  return forward_tp(b, w, comm, slot_absmax, slot_y, args->x, args->x_dtype, args->m, args->y, args->y_dtype, args->flags, args->stream, ex);
+}
+
+namespace {
+tb_status forward_tp(tb_backend* b, const tb_weights* w, tb_comm* comm, uint32_t slot_absmax, uint32_t slot_y, const void* x,
+                     tb_dtype x_dtype, uint32_t m, void* y, tb_dtype y_dtype, uint32_t flags, void* stream, const BlockExtras& ex) {
   if (tb_status s = check_handles(b, w)) return s;
   if (!comm) return tb_fail(TB_NULL_ARG, "communicator is null");
   if (tb_comm_owner(comm) != b) return tb_fail(TB_INVALID_INPUT, "communicator belongs to another backend context");
@@ -650,6 +671,7 @@ extern "C" tb_status tb_linear_forward_tp_dev(tb_backend* b, const tb_weights* w
   if (y_dtype == TB_I8) return tb_fail(TB_INVALID_INPUT, "output dtype must be fp32 or bf16");
   if (m > 8) return tb_fail(TB_INVALID_INPUT, "the fused tensor-parallel path takes at most 8 tokens per call");
   if (flags & ~TB_FWD_PDL) return tb_fail(TB_INVALID_INPUT, "unknown flag bits");
+  if (ex.relu2_up && x_dtype != TB_F32) return tb_fail(TB_INVALID_INPUT, "the squared-ReLU gate takes the fp32 outputs of the gate and up projections");
   if (!w->fast) return tb_fail(TB_UNSUPPORTED_FORMAT, "the int8 path needs uniform plane counts, k % 256 == 0, group 128 and codec D2 or B3");
   if (slot_absmax == slot_y) return tb_fail(TB_INVALID_INPUT, "the absmax and the output slot must differ");
   TbCommView va{}, vy{};
@@ -660,7 +682,7 @@ extern "C" tb_status tb_linear_forward_tp_dev(tb_backend* b, const tb_weights* w
   if (va.world <= 1) {
     tb_forward_args a{};
     a.x = x; a.x_dtype = x_dtype; a.m = m; a.y = y; a.y_dtype = y_dtype; a.flags = TB_FWD_A8 | TB_FWD_FORCE_DECODE | flags;
-    return forward_dev(b, w, a, st, nullptr);
+    return forward_dev(b, w, a, st, nullptr, ex);
   }
   // every rank's partial rows of one pass (8-byte words: value and round), in two alternating copies
   const size_t need_y = size_t(2) * va.world * std::min<uint32_t>(4, m) * w->n * 8;
@@ -679,6 +701,9 @@ extern "C" tb_status tb_linear_forward_tp_dev(tb_backend* b, const tb_weights* w
     d.status = b->d_status; d.pdl = (flags & TB_FWD_PDL) != 0 || m0 > 0;
     d.scratch = b->d_prep; d.scratch_bytes = b->d_prep_cap;
     d.comm_absmax = &va; d.comm_y = &vy;
+    // the gate acts on this rank's slice of the row; the residual is added once, behind the sum over the ranks
+    d.relu2_up = ex.relu2_up ? ex.relu2_up + size_t(m0) * w->k : nullptr;
+    d.residual = ex.residual ? ex.residual + size_t(m0) * w->n : nullptr;
     // Small tables: ONE launch (absmax exchange in the table builder, output sum in the epilogue).
     // Large tables: the preparation kernel exchanges the absmax, the decode kernel sums the outputs.
     d.fused = tb_decode_builds_tables(w, mc, d.x);
@@ -687,6 +712,7 @@ extern "C" tb_status tb_linear_forward_tp_dev(tb_backend* b, const tb_weights* w
   }
   return TB_OK;
 }
+}  // namespace
 
 extern "C" tb_status tb_backend_reserve(tb_backend* b, const tb_weights* w, uint32_t max_m) {
   clear_error();

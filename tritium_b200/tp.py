@@ -165,6 +165,26 @@ class PeerComm:
                                                      C.c_void_p(y.data_ptr()), dt[y.dtype], C.c_uint32(flags),
                                                      C.c_void_p(_lib.stream_handle(s))))
 
+    def block_linear_fused(self, handle, slot_absmax: int, slot_y: int, x, y, *, relu2_up=None, residual=None, stream=None,
+                           flags: int = 0) -> None:
+        """`linear_fused` with the block's fused steps (`tb_block_linear_forward_tp_dev`): the
+        squared-ReLU gate on this rank's slice in front, the residual behind the sum over the ranks."""
+        import ctypes as C
+        import torch
+        from . import _lib
+        dt = {torch.float32: _lib.TB_F32, torch.bfloat16: _lib.TB_BF16}
+        s = stream if stream is not None else torch.cuda.current_stream()
+        args = _lib.NormLinearArgs()
+        args.x = x.data_ptr(); args.x_dtype = dt[x.dtype]
+        args.relu2_up = relu2_up.data_ptr() if relu2_up is not None else None
+        args.residual = residual.data_ptr() if residual is not None else None
+        args.m = x.shape[0]
+        args.y = y.data_ptr(); args.y_dtype = dt[y.dtype]
+        args.flags = flags
+        args.stream = _lib.stream_handle(s)
+        self._check(self._L.tb_block_linear_forward_tp_dev(self.backend._h, handle._h, self._h, C.c_uint32(slot_absmax),
+                                                           C.c_uint32(slot_y), C.byref(args)))
+
     def set_wait_limit(self, sm_cycles: int) -> None:
         """Bound of every wait on a peer, in SM clock cycles (default about two seconds)."""
         import ctypes as C
