@@ -69,7 +69,9 @@ typedef struct tb_receipt {
 } tb_receipt;
 
 typedef struct tb_weights_info {
-  uint32_t codec, group, planes_uniform; /* planes_uniform: 1..3, or 0 when plane counts vary */
+  uint32_t codec, group, planes_uniform; /* planes_uniform: plane slots per tile as stored on the device, 1..3
+                                            (tiles with fewer planes on a 256-aligned B3/D2 g128 shape are padded
+                                            with zero planes to the largest count), or 0 for the ragged layout */
   uint64_t n, k, tiles, present_planes;
   uint64_t payload_bytes, scale_bytes, map_bytes, rank_prefix_bytes;
   uint64_t source_len_bytes; /* DeviceBuffer::len_bytes(): the caller's packed input length */

@@ -465,11 +465,47 @@ def test_stack_host_call_matches_per_layer_calls(backend):
     stack.close()
 
 
+@pytest.mark.parametrize("codec", [SaltV2Codec.B3, SaltV2Codec.D2])
+@pytest.mark.parametrize("m", [1, 6, 24, 200])
+def test_mixed_plane_counts_on_aligned_shapes_take_the_fast_kernels(backend, codec, m):
+    """A tensor whose tiles hold one to three planes (a plane map with varying counts), on a shape
+    the fast kernels take, is stored padded to three plane slots per tile with all-zero planes.
+    The int8 path then runs the decode, few-token and many-token kernels with the same exact
+    group sums (zero for a padded plane); the fp32 exact kernel still adds only each tile's true
+    planes and returns the reference's bits."""
+    n, k = 64, 768
+    prod, orac = uniform_pair(n, k, 3, seed=91)
+    tiles = n * k // 256
+    counts = (1 + (np.arange(tiles) * 7 + 2) % 3).astype(np.uint8)
+    for t in (prod, orac):
+        t.plane_count[:] = counts
+        for ti in range(tiles):
+            t.trits[ti, counts[ti]:, :] = 0
+            t.scales[ti, counts[ti]:, :] = 0
+    resident = backend.upload_salt_v2(prod, codec)
+    assert resident.info["fast_path"] and resident.info["planes_uniform"] == 3
+    slot = 52 if codec == SaltV2Codec.B3 else 64
+    assert resident.allocation_receipt()["payload_bytes"] == tiles * 3 * slot
+    x = make_activations(m, k, seed=m)
+    want_y, want_acc, _ = orc.a8_linear(orac, x)
+    y, acc, receipt = backend.linear_forward_a8(resident, x, m, dump=True)
+    assert receipt.kernel == (1 if m <= 8 else 2)
+    assert np.array_equal(acc, want_acc[:, :, :, :3])
+    assert rel_l2(y, want_y) <= 1e-5
+    xe = seeded_f32(0x77 + m, min(m, 3) * k, -0.75, 0.75).reshape(min(m, 3), k)
+    want = np.stack([orc.matvec(orac, row) for row in xe])
+    exact = backend.salt_v2_forward_exact(resident, xe, xe.shape[0])
+    assert np.array_equal(exact.output.view(np.uint32), want.view(np.uint32))
+    streamed = backend.upload_salt_v2_from_package(fmt.write_salt_v2_package(prod, codec), prod.name)
+    again = backend.salt_v2_forward_exact(streamed, xe, xe.shape[0])
+    assert np.array_equal(again.output.view(np.uint32), want.view(np.uint32))
+
+
 # ------------------------------------------------------------------ int8 path of layouts without a fast kernel
 @pytest.mark.parametrize("codec,ocodec", CODECS)
 @pytest.mark.parametrize("layout", ["ragged_3x173", "g64_4x576", "mixed_planes_8x256"])
 def test_int8_path_of_other_layouts_is_bit_identical_to_cpu(backend, codec, ocodec, layout):
-    """Ragged shapes, scale groups of 64, S34 and mixed plane counts have no fast kernel: their int8
+    """Ragged shapes, scale groups of 64, S34 and mixed plane counts on small shapes have no fast kernel: their int8
     path quantises to codes kept as fp32 values and runs the bit-exact kernel on them.  Group sums
     of small integers are exact and the order is the reference's, so the output equals the CPU
     composition (quantise, matvec, token scale) bit for bit."""

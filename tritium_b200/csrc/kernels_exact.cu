@@ -24,6 +24,7 @@ struct ExactParams {
   const uint8_t* payload; const uint16_t* scales; const uint8_t* meta; const uint32_t* tile_rank;
   uint64_t map_bytes, coeffs, tiles;
   uint32_t terminal, uniform_planes, codec, group, m, n, k;
+  uint32_t pad_planes;   // != 0: every tile occupies this many plane slots; its true count comes from the map
   const float* x; float* y; const float* row_scale;
   uint32_t* status;
 };
@@ -43,6 +44,7 @@ __device__ __forceinline__ uint32_t planes_of(const ExactParams& p, uint64_t til
 }
 
 __device__ __forceinline__ uint64_t rank_of(const ExactParams& p, uint64_t tile) {
+  if (p.pad_planes) return tile * p.pad_planes;
   return p.uniform_planes ? tile * p.uniform_planes : p.tile_rank[tile];
 }
 
@@ -357,7 +359,9 @@ ExactParams make_params(const tb_weights* w) {
   ExactParams p{};
   p.payload = w->d_payload; p.scales = w->d_scales; p.meta = w->d_meta; p.tile_rank = w->d_tile_rank;
   p.map_bytes = w->map_bytes; p.coeffs = w->n * w->k; p.tiles = w->tiles;
-  p.terminal = w->terminal_map; p.uniform_planes = w->uniform_planes;
+  p.terminal = w->terminal_map;
+  p.uniform_planes = w->map_counts ? 0u : w->uniform_planes;
+  p.pad_planes = w->map_counts ? w->uniform_planes : 0u;
   p.codec = uint32_t(w->codec); p.group = w->group; p.n = uint32_t(w->n); p.k = uint32_t(w->k);
   return p;
 }

@@ -198,12 +198,39 @@ extern "C" tb_status tb_backend_inject_wait_timeout(tb_backend* b, uint32_t enab
 // ---------------------------------------------------------------- weights
 namespace {
 
-tb_status upload_resident(tb_backend* b, const tbf::Resident& r, uint64_t source_len, bool is_tq2, uint64_t logical_k,
+// Tiles with different plane counts, on a shape the fast kernels take: the same tensor with every
+// tile padded to the largest count by all-zero planes (zero-trit bytes, zero scales).  The 2-bit
+// map keeps the true counts.
+bool pad_to_uniform(const tbf::Resident& r, tbf::Resident* out) {
+  if (r.uniform_planes || r.k % 256 || r.group != 128 || (r.codec != tbf::kB3 && r.codec != tbf::kD2)) return false;
+  if (r.n < 16 || r.k > 65536) return false;   // odd shapes stay on the general route
+  uint32_t most = 1;
+  for (uint64_t t = 0; t < r.tiles; ++t) most = std::max<uint32_t>(most, r.planes_of(t));
+  const size_t pb = r.codec == tbf::kB3 ? 52 : 64;
+  *out = r;
+  out->payload.assign(size_t(r.tiles) * most * pb, uint8_t(r.codec == tbf::kB3 ? 121 : 0x55));
+  out->scales.assign(size_t(r.tiles) * most * 2, 0);
+  size_t src = 0;
+  for (uint64_t t = 0; t < r.tiles; ++t) {
+    const uint32_t have = r.planes_of(t);
+    std::memcpy(out->payload.data() + size_t(t) * most * pb, r.payload.data() + src * pb, size_t(have) * pb);
+    std::memcpy(out->scales.data() + size_t(t) * most * 2, r.scales.data() + src * 2, size_t(have) * 2 * sizeof(uint16_t));
+    src += have;
+  }
+  out->uniform_planes = most;
+  return true;
+}
+
+tb_status upload_resident(tb_backend* b, const tbf::Resident& r_in, uint64_t source_len, bool is_tq2, uint64_t logical_k,
                           tb_weights** out) {
   if (tb_status s = use_device(b)) return s;
+  tbf::Resident padded;
+  const bool map_counts = pad_to_uniform(r_in, &padded);
+  const tbf::Resident& r = map_counts ? padded : r_in;
   tb_weights* w = new (std::nothrow) tb_weights();
   if (!w) return tb_fail(TB_OUT_OF_MEMORY, "host allocation failed");
   w->owner = b; tb_backend_retain(b); w->codec = r.codec; w->group = r.group; w->uniform_planes = r.uniform_planes;
+  w->map_counts = map_counts;
   w->n = r.n; w->k = r.k; w->tiles = r.tiles; w->present_planes = r.present_planes;
   w->payload_bytes = r.payload.size(); w->scale_count = r.scales.size();
   w->map_bytes = r.map.size(); w->rank_prefix_bytes = r.rank_prefix.size() * 4;

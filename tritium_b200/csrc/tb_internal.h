@@ -68,6 +68,11 @@ struct tb_weights {
   tb_backend* owner = nullptr;
   int codec = 0;                 // tbf::Codec
   uint32_t group = 128, uniform_planes = 0;
+  // Tiles with different plane counts (aligned shapes only) are stored padded to the largest
+  // count with all-zero planes, so that the fast kernels see a uniform tensor: uniform_planes is
+  // then that count, and map_counts tells the bit-exact kernel to take each tile's true count
+  // from the 2-bit map (a zero plane would add +0.0, which can flip the sign of a zero sum).
+  bool map_counts = false;
   uint64_t n = 0, k = 0, tiles = 0, present_planes = 0;
   uint64_t payload_bytes = 0, scale_count = 0, map_bytes = 0, rank_prefix_bytes = 0;
   uint32_t terminal_map = 0;
