@@ -181,8 +181,11 @@ tb_status tb_salt_v2_gather_rows(tb_backend* backend, const tb_weights* weights,
 #define TB_FWD_A8 1u          /* int8-quantise activations (x_dtype F32 or BF16), or consume int8 */
 #define TB_FWD_EXACT 2u       /* force the bit-exact kernel (fp32 activations only) */
 #define TB_FWD_PDL 4u         /* launch with programmatic dependent launch (weights prefetch early) */
-#define TB_FWD_FORCE_DECODE 8u
-#define TB_FWD_FORCE_PREFILL 16u
+#define TB_FWD_FORCE_DECODE 8u   /* streaming kernel whatever m; TB_UNSUPPORTED_FORMAT when a row block does not fit */
+#define TB_FWD_FORCE_PREFILL 16u /* tensor-core kernel whatever m */
+/* Without a force flag: up to 8 tokens take the streaming (decode) kernel, more the tensor-core
+ * kernels; a tensor whose rows are too long for the streaming kernel's shared-memory ring takes the
+ * tensor-core kernel at every m (so a device-pointer caller reserves with tb_backend_reserve). */
 typedef struct tb_forward_args {
   const void* x;            /* [m,k] device */
   tb_dtype x_dtype;

@@ -501,6 +501,25 @@ def test_mixed_plane_counts_on_aligned_shapes_take_the_fast_kernels(backend, cod
     assert np.array_equal(again.output.view(np.uint32), want.view(np.uint32))
 
 
+@pytest.mark.parametrize("m", [1, 5])
+def test_rows_too_long_for_the_decode_kernel_run_on_tensor_cores(backend, m):
+    """Three planes at k = 17408 (a 27B-class down projection): two row blocks of the decode
+    kernel's ring do not fit in shared memory, so the tensor-core kernel takes the call at every
+    token count, with the same exact group sums."""
+    n, k, planes = 48, 17408, 3
+    prod, orac = uniform_pair(n, k, planes, seed=17)
+    x = make_activations(m, k, seed=40 + m)
+    want_y, want_acc, _ = orc.a8_linear(orac, x)
+    resident = backend.upload_salt_v2(prod, SaltV2Codec.B3)
+    y, acc, receipt = backend.linear_forward_a8(resident, x, m, dump=True)
+    assert receipt.kernel == 2
+    assert np.array_equal(acc, want_acc[:, :, :, :planes])
+    assert rel_l2(y, want_y) <= 1e-5
+    y32 = backend.salt_v2_forward_fast(resident, x, m)           # fp32 entry: int8 limbs, same route
+    want32 = np.stack([orc.matvec(orac, row) for row in x])
+    assert rel_l2(y32.output, want32) <= 1e-5
+
+
 # ------------------------------------------------------------------ int8 path of layouts without a fast kernel
 @pytest.mark.parametrize("codec,ocodec", CODECS)
 @pytest.mark.parametrize("layout", ["ragged_3x173", "g64_4x576", "mixed_planes_8x256"])

@@ -381,6 +381,18 @@ tb_status check_handles(const tb_backend* b, const tb_weights* w) {
 
 tb_status reserve_prefill(tb_backend* b, const tb_weights* w, uint32_t m);
 
+// The decode kernel keeps two row blocks of a tensor in shared memory at least.  Rows too long for
+// that (three planes beyond k of about 9 K, two planes beyond about 28 K) go to the tensor-core
+// kernel at every token count.
+bool decode_fits(const tb_backend* b, const tb_weights* w, uint32_t m) {
+  return tb_decode_supported(w, std::min<uint32_t>(std::max<uint32_t>(m, 1u), 4u), b->max_smem_optin, nullptr);
+}
+bool takes_tensor_cores(const tb_backend* b, const tb_weights* w, uint32_t m, uint32_t flags, uint32_t decode_limit = 8) {
+  if (flags & TB_FWD_FORCE_PREFILL) return true;
+  if (flags & TB_FWD_FORCE_DECODE) return false;
+  return m > decode_limit || (w->fast && !decode_fits(b, w, m));
+}
+
 // What a decode block wraps around the linear: RMSNorm in front of the quantiser, residual behind.
 struct BlockExtras {
   const float* norm_weight = nullptr; float norm_eps = 0.f; bool norm_zero_centered = false;
@@ -411,7 +423,7 @@ tb_status forward_dev(tb_backend* b, const tb_weights* w, const tb_forward_args&
       const uint32_t m4 = a.m * 4;
       const size_t qb = (size_t(m4) * w->k + 255) & ~size_t(255), sb = (size_t(m4) * 4 + 255) & ~size_t(255);
       if (tb_status s = ensure(&b->d_limb, &b->d_limb_cap, qb + sb + size_t(m4) * w->n * 4 + 256)) return s;
-      if (m4 > 8) if (tb_status s = reserve_prefill(b, w, m4)) return s;
+      if (takes_tensor_cores(b, w, m4, a.flags)) if (tb_status s = reserve_prefill(b, w, m4)) return s;
       uint8_t* base = static_cast<uint8_t*>(b->d_limb);
       int8_t* q = reinterpret_cast<int8_t*>(base);
       float* scales = reinterpret_cast<float*>(base + qb);
@@ -462,7 +474,7 @@ tb_status forward_dev(tb_backend* b, const tb_weights* w, const tb_forward_args&
   }
   // measured crossover (C2, 27B and 2B linears alike): two chained 4-token decode passes are level with
   // one call of the few-token tensor-core kernel (about 25 us on C2), three passes are slower
-  const bool want_prefill = (a.flags & TB_FWD_FORCE_PREFILL) || (a.m > 8 && !(a.flags & TB_FWD_FORCE_DECODE));
+  const bool want_prefill = takes_tensor_cores(b, w, a.m, a.flags);
   uint32_t extra_launches = 0;
   // The decode kernel normalises inside its table builder.  Every other route (the tensor-core
   // kernel, tables from the preparation kernel) takes rows normalised by a kernel of its own; the
@@ -644,7 +656,7 @@ extern "C" tb_status tb_norm_linear_forward_dev(tb_backend* b, const tb_weights*
   tb_forward_args a{};
   a.x = args->x; a.x_dtype = args->x_dtype; a.m = args->m; a.y = args->y; a.y_dtype = args->y_dtype;
   a.flags = args->flags | TB_FWD_A8; a.stream = args->stream;
-  if (a.m > 8 && !(a.flags & TB_FWD_FORCE_DECODE)) if (tb_status s = reserve_prefill(b, w, a.m)) return s;
+  if (takes_tensor_cores(b, w, a.m, a.flags)) if (tb_status s = reserve_prefill(b, w, a.m)) return s;
   BlockExtras ex;
   ex.norm_weight = args->norm_weight; ex.norm_eps = args->norm_eps;
   ex.norm_zero_centered = (args->norm_flags & TB_NORM_ZERO_CENTERED) != 0; ex.residual = args->residual;
@@ -934,7 +946,7 @@ extern "C" tb_status tb_stack_forward_dev(tb_stack* st, const void* x, tb_dtype 
       // [layer][m][n] bf16, whichever kernel family runs.
       const StackGroup& g = st->groups[gi];
       const tb_weights* w = st->layers[i];
-      const bool prefill = (flags & TB_FWD_FORCE_PREFILL) || (m > 16 && !(flags & TB_FWD_FORCE_DECODE));
+      const bool prefill = takes_tensor_cores(b, w, m, flags, 16);
       if (prefill) {
         for (size_t l = 0; l < g.count; ++l) {
           tb_forward_args a{};
