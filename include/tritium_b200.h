@@ -69,7 +69,9 @@ typedef struct tb_receipt {
 } tb_receipt;
 
 typedef struct tb_weights_info {
-  uint32_t codec, group, planes_uniform; /* planes_uniform: plane slots per tile as stored on the device, 1..3
+  uint32_t codec, group, planes_uniform; /* codec: the codec resident on the device (an S34 artifact on a
+                                            256-aligned g128 shape is stored as B3 with the same trits);
+                                            planes_uniform: plane slots per tile as stored on the device, 1..3
                                             (tiles with fewer planes on a 256-aligned B3/D2 g128 shape are padded
                                             with zero planes to the largest count), or 0 for the ragged layout */
   uint64_t n, k, tiles, present_planes;

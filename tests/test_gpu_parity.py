@@ -520,6 +520,46 @@ def test_rows_too_long_for_the_decode_kernel_run_on_tensor_cores(backend, m):
     assert rel_l2(y32.output, want32) <= 1e-5
 
 
+def s34_pair(n, k, planes, seed):
+    """Planes with exactly one zero in every four trits (what S34 can hold), random signs and scales."""
+    rng = np.random.default_rng(seed)
+    prod, orac = uniform_pair(n, k, planes, seed=seed)
+    tiles = n * k // 256
+    trits = rng.choice(np.array([-1, 1], np.int8), size=(tiles, 3, 64, 4))
+    zero_at = rng.integers(0, 4, size=(tiles, 3, 64))
+    np.put_along_axis(trits, zero_at[..., None], 0, axis=3)
+    trits = trits.reshape(tiles, 3, 256)
+    trits[:, planes:, :] = 0
+    for t in (prod, orac):
+        t.trits[:] = trits
+    return prod, orac
+
+
+@pytest.mark.parametrize("planes,m", [(1, 1), (2, 4), (3, 7), (2, 40), (3, 300)])
+def test_s34_tensors_on_aligned_shapes_take_the_fast_kernels(backend, planes, m):
+    """An S34 artifact on a shape the fast kernels take is stored as B3 with the same trits: the
+    int8 path runs the decode and tensor-core kernels with exact group sums, and the fp32 exact
+    kernel still returns the reference's bits.  The package route gives the same resident tensor."""
+    n, k = 80, 1024
+    prod, orac = s34_pair(n, k, planes, seed=planes * 100 + m)
+    resident = backend.upload_salt_v2(prod, SaltV2Codec.S34)
+    assert resident.info["fast_path"] and resident.info["planes_uniform"] == planes
+    assert resident.allocation_receipt()["payload_bytes"] == (n * k // 256) * planes * 52
+    x = make_activations(m, k, seed=m)
+    want_y, want_acc, _ = orc.a8_linear(orac, x)
+    y, acc, receipt = backend.linear_forward_a8(resident, x, m, dump=True)
+    assert receipt.kernel == (1 if m <= 8 else 2)
+    assert np.array_equal(acc, want_acc[:, :, :, :planes])
+    assert rel_l2(y, want_y) <= 1e-5
+    rows = min(m, 2)
+    xe = seeded_f32(0x534 + m, rows * k, -0.75, 0.75).reshape(rows, k)
+    want = np.stack([orc.matvec(orac, row) for row in xe])
+    streamed = backend.upload_salt_v2_from_package(fmt.write_salt_v2_package(prod, SaltV2Codec.S34), prod.name)
+    for r in (resident, streamed):
+        got = backend.salt_v2_forward_exact(r, xe, rows)
+        assert np.array_equal(got.output.view(np.uint32), want.view(np.uint32))
+
+
 # ------------------------------------------------------------------ int8 path of layouts without a fast kernel
 @pytest.mark.parametrize("codec,ocodec", CODECS)
 @pytest.mark.parametrize("layout", ["ragged_3x173", "g64_4x576", "mixed_planes_8x256"])

@@ -201,9 +201,13 @@ namespace {
 // Tiles with different plane counts, on a shape the fast kernels take: the same tensor with every
 // tile padded to the largest count by all-zero planes (zero-trit bytes, zero scales).  The 2-bit
 // map keeps the true counts.
+// Shapes on which a tensor with varying plane counts is padded to uniform plane slots.
+bool pads_to_uniform(const tbf::Resident& r) {
+  return !r.uniform_planes && r.k % 256 == 0 && r.group == 128 && r.n >= 16 && r.k <= 65536;   // odd shapes stay on the general route
+}
+
 bool pad_to_uniform(const tbf::Resident& r, tbf::Resident* out) {
-  if (r.uniform_planes || r.k % 256 || r.group != 128 || (r.codec != tbf::kB3 && r.codec != tbf::kD2)) return false;
-  if (r.n < 16 || r.k > 65536) return false;   // odd shapes stay on the general route
+  if (!pads_to_uniform(r) || (r.codec != tbf::kB3 && r.codec != tbf::kD2)) return false;
   uint32_t most = 1;
   for (uint64_t t = 0; t < r.tiles; ++t) most = std::max<uint32_t>(most, r.planes_of(t));
   const size_t pb = r.codec == tbf::kB3 ? 52 : 64;
@@ -221,10 +225,33 @@ bool pad_to_uniform(const tbf::Resident& r, tbf::Resident* out) {
   return true;
 }
 
-tb_status upload_resident(tb_backend* b, const tbf::Resident& r_in, uint64_t source_len, bool is_tq2, uint64_t logical_k,
+// S34 (one 5-bit code per four trits) has no kernel of its own on the fast path.  On a shape the
+// fast kernels take, the same trits are stored as B3 (52 instead of 40 bytes per plane of a tile):
+// every kernel, the bit-exact one included, then sees the trits the artifact holds.
+bool s34_to_b3(const tbf::Resident& r, tbf::Resident* out, tbf::Err* err) {
+  if (r.codec != tbf::kS34 || r.k % 256 || r.group != 128) return false;
+  if (!r.uniform_planes && !pads_to_uniform(r)) return false;   // no fast kernel either way: keep the artifact's bytes
+  const size_t slots = size_t(r.present_planes), from = tbf::plane_bytes(tbf::kS34, 256), to = tbf::plane_bytes(tbf::kB3, 256);
+  if (r.payload.size() != slots * from) return false;
+  *out = r;
+  out->codec = tbf::kB3;
+  out->payload.assign(slots * to, 0);
+  int8_t trits[256];
+  for (size_t i = 0; i < slots; ++i) {
+    if ((*err = tbf::unpack(tbf::kS34, r.payload.data() + i * from, from, 256, trits))) return false;
+    if ((*err = tbf::pack(tbf::kB3, trits, 256, out->payload.data() + i * to))) return false;
+  }
+  return true;
+}
+
+tb_status upload_resident(tb_backend* b, const tbf::Resident& r_artifact, uint64_t source_len, bool is_tq2, uint64_t logical_k,
                           tb_weights** out) {
   if (tb_status s = use_device(b)) return s;
-  tbf::Resident padded;
+  tbf::Resident recoded, padded;
+  tbf::Err recode_err;
+  const bool was_s34 = s34_to_b3(r_artifact, &recoded, &recode_err);
+  if (recode_err) return from_fmt(recode_err);
+  const tbf::Resident& r_in = was_s34 ? recoded : r_artifact;
   const bool map_counts = pad_to_uniform(r_in, &padded);
   const tbf::Resident& r = map_counts ? padded : r_in;
   tb_weights* w = new (std::nothrow) tb_weights();
