@@ -399,6 +399,22 @@ tb_status tb_fmt_resident_build(tb_codec codec, uint32_t group, uint64_t n, uint
                                 const uint8_t* plane_count, const int8_t* trits,
                                 const uint16_t* scales, uint8_t* payload, uint16_t* scale_out,
                                 uint8_t* plane_map, uint32_t* terminal_map_value);
+/* Host-only twin of the re-layout the uploads apply: the payload and scale arenas as the device
+ * holds them.  They are the artifact's own, except that (a) an S34 tensor on a shape the fast
+ * kernels take (k % 256 == 0, groups of 128) is stored as B3 with the same trits, and (b) a
+ * tensor whose tiles hold different plane counts on such a shape (n >= 16, k <= 65536) has
+ * every tile padded to the largest count by all-zero planes (zero-trit bytes, zero scales; the
+ * plane map keeps the true counts).  Call with NULL output buffers to learn the sizes. */
+typedef struct tb_device_layout {
+  uint32_t codec, planes_uniform; /* as resident: codec tag; plane slots per tile, 0 for the ragged layout */
+  uint32_t recoded;               /* 1 when S34 was stored as B3 */
+  uint32_t counts_from_map;       /* 1 when tiles were padded: true plane counts live in the map */
+  uint64_t payload_bytes, scale_count;
+} tb_device_layout;
+tb_status tb_fmt_device_layout(tb_codec codec, uint32_t group, uint32_t n, uint32_t k, const uint8_t* payload,
+                               size_t payload_len, const uint16_t* scales, size_t scale_count,
+                               const uint8_t* plane_map, size_t map_len, uint32_t terminal_map_value,
+                               tb_device_layout* info, uint8_t* payload_out, uint16_t* scales_out);
 /* write_salt_v2_package for one matrix tensor (salt_v2_package.rs:1526-1668); returns total
  * bytes (negative tb_status on error; out may be NULL to size). */
 int64_t tb_fmt_package_write(tb_codec codec, const char* name, uint32_t group, uint64_t n,

@@ -281,3 +281,69 @@ def test_reference_kernel_weight_layout_and_gate_restatement():
     g = np.array([-2.0, 0.0, 0.5, 3.0], np.float32)
     u = np.array([7.0, 7.0, -4.0, 0.25], np.float32)
     assert np.array_equal(orc.relu2_gate(g, u), np.array([0.0, 0.0, -1.0, 2.25], np.float32))
+
+
+# ------------------------------------------------------------------ arenas as stored on the device
+def _tensor(n, k, counts, rng, s34=False):
+    tiles = n * k // 256
+    trits = np.zeros((tiles, 3, 256), np.int8)
+    scales = np.zeros((tiles, 3, 4), np.uint16)
+    for t in range(tiles):
+        for p in range(counts[t]):
+            trits[t, p] = s34_trits(rng, 256) if s34 else rng.integers(-1, 2, 256)
+            scales[t, p, :2] = fmt.f16_bits(rng.uniform(0.01, 1.0, 2).astype(np.float32))
+    return SaltV2Tensor("w", n, k, np.asarray(counts, np.uint8), trits, scales, 128)
+
+
+def test_device_layout_keeps_the_artifact_arenas_of_uniform_tensors():
+    rng = np.random.default_rng(3)
+    t = _tensor(16, 512, [2] * 32, rng)
+    for codec in (SaltV2Codec.B3, SaltV2Codec.D2):
+        payload, scales, _, _, _ = t.resident(codec)
+        got_p, got_s, info = t.device_layout(codec)
+        assert np.array_equal(got_p, payload) and np.array_equal(got_s, scales)
+        assert info == dict(codec=int(codec), planes_uniform=2, recoded=0, counts_from_map=0,
+                            payload_bytes=payload.size, scale_count=scales.size)
+
+
+def test_device_layout_stores_s34_as_b3_with_the_same_trits():
+    rng = np.random.default_rng(4)
+    t = _tensor(16, 512, [3] * 32, rng, s34=True)
+    got_p, got_s, info = t.device_layout(SaltV2Codec.S34)
+    want_p, want_s, _, _, _ = t.resident(SaltV2Codec.B3)          # the same planes encoded as B3
+    assert info["codec"] == int(SaltV2Codec.B3) and info["recoded"] == 1 and info["planes_uniform"] == 3
+    assert np.array_equal(got_p, want_p) and np.array_equal(got_s, want_s)
+    first = fmt.unpack(SaltV2Codec.B3, bytes(got_p[:52]), 256)
+    assert np.array_equal(first, t.trits[0, 0])
+
+
+@pytest.mark.parametrize("codec", [SaltV2Codec.B3, SaltV2Codec.D2, SaltV2Codec.S34])
+def test_device_layout_pads_varying_plane_counts_with_zero_planes(codec):
+    rng = np.random.default_rng(5)
+    n, k = 16, 512
+    counts = [1 + (7 * i + 2) % 3 for i in range(n * k // 256)]
+    t = _tensor(n, k, counts, rng, s34=(codec == SaltV2Codec.S34))
+    got_p, got_s, info = t.device_layout(codec)
+    stored = SaltV2Codec.B3 if codec == SaltV2Codec.S34 else codec
+    pb = 52 if stored == SaltV2Codec.B3 else 64
+    assert info["counts_from_map"] == 1 and info["planes_uniform"] == 3 and info["codec"] == int(stored)
+    assert info["recoded"] == (1 if codec == SaltV2Codec.S34 else 0)
+    assert got_p.size == len(counts) * 3 * pb and got_s.size == len(counts) * 3 * 2
+    for tile, have in enumerate(counts):
+        for p in range(3):
+            plane = fmt.unpack(stored, bytes(got_p[(tile * 3 + p) * pb:(tile * 3 + p + 1) * pb]), 256)
+            sc = got_s[(tile * 3 + p) * 2:(tile * 3 + p) * 2 + 2]
+            if p < have:
+                assert np.array_equal(plane, t.trits[tile, p]) and np.array_equal(sc, t.scales[tile, p, :2])
+            else:
+                assert not plane.any() and not sc.any()
+
+
+def test_device_layout_leaves_small_and_unaligned_shapes_alone():
+    rng = np.random.default_rng(6)
+    mixed_small = _tensor(8, 256, [1, 3, 2, 1, 2, 3, 3, 1], rng, s34=True)       # fewer than 16 rows
+    for codec in (SaltV2Codec.B3, SaltV2Codec.S34):
+        payload, scales, _, _, _ = mixed_small.resident(codec)
+        got_p, got_s, info = mixed_small.device_layout(codec)
+        assert np.array_equal(got_p, payload) and np.array_equal(got_s, scales)
+        assert info["codec"] == int(codec) and not info["recoded"] and not info["counts_from_map"] and info["planes_uniform"] == 0

@@ -29,6 +29,7 @@ EXPORTS = [
     "tb_fmt_resident_sizes", "tb_fmt_resident_build", "tb_fmt_package_write", "tb_fmt_tq2_pack_rows",
     "tb_fmt_quantize_act_int8", "tb_linear_forward_a8_static", "tb_backend_inject_wait_timeout",
     "tb_salt_v2_upload_reader", "tb_fmt_package_write_multi", "tb_fmt_package_extract", "tb_last_shape_mismatch", "tb_salt_v1_upload", "tb_tq1_upload",
+    "tb_fmt_device_layout",
 ]
 
 
@@ -83,6 +84,11 @@ class PackageTensor(C.Structure):
     _fields_ = [("codec", C.c_uint32), ("group", C.c_uint32), ("terminal_map_value", C.c_uint32), ("planes_uniform", C.c_uint32),
                 ("n", C.c_uint64), ("k", C.c_uint64), ("payload_bytes", C.c_uint64), ("scale_count", C.c_uint64),
                 ("map_bytes", C.c_uint64)]
+
+
+class DeviceLayout(C.Structure):
+    _fields_ = [("codec", C.c_uint32), ("planes_uniform", C.c_uint32), ("recoded", C.c_uint32), ("counts_from_map", C.c_uint32),
+                ("payload_bytes", C.c_uint64), ("scale_count", C.c_uint64)]
 
 
 def file_read_at(fileobj):
@@ -174,6 +180,7 @@ _SIGNATURES = {
     "tb_fmt_package_write_multi": (C.c_int64, [_I, _U32, _P, _P, _P, _P, _P, _P, _P, _P, _SZ]),
     "tb_fmt_package_extract": (_ST, [_P, _P, _U64, C.c_char_p, _P, _P, _P, _P]),
     "tb_fmt_quantize_act_int8": (None, [_P, _U64, _U64, _P, _P]),
+    "tb_fmt_device_layout": (_ST, [_I, _U32, _U32, _U32, _P, _SZ, _P, _SZ, _P, _SZ, _U32, _P, _P, _P]),
 }
 
 

@@ -198,62 +198,14 @@ extern "C" tb_status tb_backend_inject_wait_timeout(tb_backend* b, uint32_t enab
 // ---------------------------------------------------------------- weights
 namespace {
 
-// Tiles with different plane counts, on a shape the fast kernels take: the same tensor with every
-// tile padded to the largest count by all-zero planes (zero-trit bytes, zero scales).  The 2-bit
-// map keeps the true counts.
-// Shapes on which a tensor with varying plane counts is padded to uniform plane slots.
-bool pads_to_uniform(const tbf::Resident& r) {
-  return !r.uniform_planes && r.k % 256 == 0 && r.group == 128 && r.n >= 16 && r.k <= 65536;   // odd shapes stay on the general route
-}
-
-bool pad_to_uniform(const tbf::Resident& r, tbf::Resident* out) {
-  if (!pads_to_uniform(r) || (r.codec != tbf::kB3 && r.codec != tbf::kD2)) return false;
-  uint32_t most = 1;
-  for (uint64_t t = 0; t < r.tiles; ++t) most = std::max<uint32_t>(most, r.planes_of(t));
-  const size_t pb = r.codec == tbf::kB3 ? 52 : 64;
-  *out = r;
-  out->payload.assign(size_t(r.tiles) * most * pb, uint8_t(r.codec == tbf::kB3 ? 121 : 0x55));
-  out->scales.assign(size_t(r.tiles) * most * 2, 0);
-  size_t src = 0;
-  for (uint64_t t = 0; t < r.tiles; ++t) {
-    const uint32_t have = r.planes_of(t);
-    std::memcpy(out->payload.data() + size_t(t) * most * pb, r.payload.data() + src * pb, size_t(have) * pb);
-    std::memcpy(out->scales.data() + size_t(t) * most * 2, r.scales.data() + src * 2, size_t(have) * 2 * sizeof(uint16_t));
-    src += have;
-  }
-  out->uniform_planes = most;
-  return true;
-}
-
-// S34 (one 5-bit code per four trits) has no kernel of its own on the fast path.  On a shape the
-// fast kernels take, the same trits are stored as B3 (52 instead of 40 bytes per plane of a tile):
-// every kernel, the bit-exact one included, then sees the trits the artifact holds.
-bool s34_to_b3(const tbf::Resident& r, tbf::Resident* out, tbf::Err* err) {
-  if (r.codec != tbf::kS34 || r.k % 256 || r.group != 128) return false;
-  if (!r.uniform_planes && !pads_to_uniform(r)) return false;   // no fast kernel either way: keep the artifact's bytes
-  const size_t slots = size_t(r.present_planes), from = tbf::plane_bytes(tbf::kS34, 256), to = tbf::plane_bytes(tbf::kB3, 256);
-  if (r.payload.size() != slots * from) return false;
-  *out = r;
-  out->codec = tbf::kB3;
-  out->payload.assign(slots * to, 0);
-  int8_t trits[256];
-  for (size_t i = 0; i < slots; ++i) {
-    if ((*err = tbf::unpack(tbf::kS34, r.payload.data() + i * from, from, 256, trits))) return false;
-    if ((*err = tbf::pack(tbf::kB3, trits, 256, out->payload.data() + i * to))) return false;
-  }
-  return true;
-}
-
 tb_status upload_resident(tb_backend* b, const tbf::Resident& r_artifact, uint64_t source_len, bool is_tq2, uint64_t logical_k,
                           tb_weights** out) {
   if (tb_status s = use_device(b)) return s;
-  tbf::Resident recoded, padded;
-  tbf::Err recode_err;
-  const bool was_s34 = s34_to_b3(r_artifact, &recoded, &recode_err);
-  if (recode_err) return from_fmt(recode_err);
-  const tbf::Resident& r_in = was_s34 ? recoded : r_artifact;
-  const bool map_counts = pad_to_uniform(r_in, &padded);
-  const tbf::Resident& r = map_counts ? padded : r_in;
+  // the arenas as the device holds them: S34 recoded as B3, varying plane counts padded (tb_format.h)
+  tbf::Resident relaid;
+  bool recoded = false, map_counts = false;
+  if (tbf::Err e = tbf::device_layout(r_artifact, &relaid, &recoded, &map_counts)) return from_fmt(e);
+  const tbf::Resident& r = (recoded || map_counts) ? relaid : r_artifact;
   tb_weights* w = new (std::nothrow) tb_weights();
   if (!w) return tb_fail(TB_OUT_OF_MEMORY, "host allocation failed");
   w->owner = b; tb_backend_retain(b); w->codec = r.codec; w->group = r.group; w->uniform_planes = r.uniform_planes;
@@ -1153,6 +1105,25 @@ extern "C" tb_status tb_fmt_resident_build(tb_codec codec, uint32_t group, uint6
   std::copy(r.scales.begin(), r.scales.end(), scale_out);
   if (plane_map) std::copy(r.map.begin(), r.map.end(), plane_map);
   *terminal = r.terminal_map;
+  return TB_OK;
+}
+
+extern "C" tb_status tb_fmt_device_layout(tb_codec codec, uint32_t group, uint32_t n, uint32_t k, const uint8_t* payload,
+                                          size_t payload_len, const uint16_t* scales, size_t scale_count, const uint8_t* plane_map,
+                                          size_t map_len, uint32_t terminal, tb_device_layout* info, uint8_t* payload_out,
+                                          uint16_t* scales_out) {
+  clear_error();
+  if (!payload || !scales || !info || (!plane_map && map_len)) return tb_fail(TB_NULL_ARG, "null argument");
+  tbf::Resident r, relaid;
+  if (tbf::Err e = tbf::resident_from_arenas(int(codec), group, n, k, payload, payload_len, scales, scale_count, plane_map, map_len, terminal, &r))
+    return from_fmt(e);
+  bool recoded = false, map_counts = false;
+  if (tbf::Err e = tbf::device_layout(r, &relaid, &recoded, &map_counts)) return from_fmt(e);
+  const tbf::Resident& d = (recoded || map_counts) ? relaid : r;
+  info->codec = uint32_t(d.codec); info->planes_uniform = d.uniform_planes; info->counts_from_map = map_counts ? 1u : 0u;
+  info->recoded = recoded ? 1u : 0u; info->payload_bytes = d.payload.size(); info->scale_count = d.scales.size();
+  if (payload_out) std::copy(d.payload.begin(), d.payload.end(), payload_out);
+  if (scales_out) std::copy(d.scales.begin(), d.scales.end(), scales_out);
   return TB_OK;
 }
 

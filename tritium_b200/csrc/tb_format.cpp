@@ -306,6 +306,53 @@ Err resident_from_planes(int codec, uint32_t group, uint64_t n, uint64_t k, cons
   return ok();
 }
 
+namespace {
+// Shapes on which a tensor with varying plane counts is padded to uniform plane slots; odd shapes
+// (a single row, very long rows) stay on the general route.
+bool pads_to_uniform(const Resident& r) {
+  return !r.uniform_planes && r.k % 256 == 0 && r.group == 128 && r.n >= 16 && r.k <= 65536;
+}
+}  // namespace
+
+Err device_layout(const Resident& in, Resident* out, bool* recoded, bool* map_counts) {
+  *recoded = *map_counts = false;
+  const Resident* cur = &in;
+  if (in.codec == kS34 && in.k % 256 == 0 && in.group == 128 && (in.uniform_planes || pads_to_uniform(in))) {
+    const size_t slots = size_t(in.present_planes), from = plane_bytes(kS34, 256), to = plane_bytes(kB3, 256);
+    if (in.payload.size() == slots * from) {
+      *out = in;
+      out->codec = kB3;
+      out->payload.assign(slots * to, 0);
+      int8_t trits[256];
+      for (size_t i = 0; i < slots; ++i) {
+        if (Err e = unpack(kS34, in.payload.data() + i * from, from, 256, trits)) return e;
+        if (Err e = pack(kB3, trits, 256, out->payload.data() + i * to)) return e;
+      }
+      *recoded = true;
+      cur = out;
+    }
+  }
+  if (pads_to_uniform(*cur) && (cur->codec == kB3 || cur->codec == kD2)) {
+    const Resident src = *cur;   // `out` may be the source
+    uint32_t most = 1;
+    for (uint64_t t = 0; t < src.tiles; ++t) most = std::max<uint32_t>(most, src.planes_of(t));
+    const size_t pb = plane_bytes(src.codec, 256);
+    *out = src;
+    out->payload.assign(size_t(src.tiles) * most * pb, uint8_t(src.codec == kB3 ? 121 : 0x55));
+    out->scales.assign(size_t(src.tiles) * most * 2, 0);
+    size_t at = 0;
+    for (uint64_t t = 0; t < src.tiles; ++t) {
+      const uint32_t have = src.planes_of(t);
+      std::memcpy(out->payload.data() + size_t(t) * most * pb, src.payload.data() + at * pb, size_t(have) * pb);
+      std::memcpy(out->scales.data() + size_t(t) * most * 2, src.scales.data() + at * 2, size_t(have) * 2 * sizeof(uint16_t));
+      at += have;
+    }
+    out->uniform_planes = most;
+    *map_counts = true;
+  }
+  return ok();
+}
+
 Err resident_from_arenas(int codec, uint32_t group, uint64_t n, uint64_t k, const uint8_t* payload,
                          size_t payload_len, const uint16_t* scales, size_t scale_count,
                          const uint8_t* map, size_t map_len, uint32_t terminal, Resident* out) {

@@ -63,6 +63,17 @@ Err resident_from_planes(int codec, uint32_t group, uint64_t n, uint64_t k,
 Err resident_from_arenas(int codec, uint32_t group, uint64_t n, uint64_t k, const uint8_t* payload,
                          size_t payload_len, const uint16_t* scales, size_t scale_count,
                          const uint8_t* map, size_t map_len, uint32_t terminal, Resident* out);
+// The arenas as the device holds them.  Two re-layouts let the fast kernels (uniform plane
+// counts, k % 256 == 0, groups of 128, B3 or D2) take more artifacts:
+//  * S34 (one 5-bit code per four trits) has no tile expander of its own: on such a shape the
+//    same trits are stored as B3 (52 instead of 40 bytes per plane of a tile), so every kernel,
+//    the bit-exact one included, sees the trits the artifact holds;
+//  * a tensor whose tiles hold different plane counts (n >= 16, k <= 65536) gets every tile
+//    padded to the largest count by all-zero planes (zero-trit bytes, zero scales); the 2-bit map
+//    keeps the true counts (*map_counts), which the bit-exact kernel follows: a zero plane would
+//    add +0.0, and that can flip the sign of a zero sum.
+// `out` is filled only when *recoded or *map_counts is set; otherwise the input is the layout.
+Err device_layout(const Resident& in, Resident* out, bool* recoded, bool* map_counts);
 // From package bytes (whole-package validation), tensor selected by name.
 Err resident_from_package(const uint8_t* bytes, size_t len, const char* name, Resident* out);
 // From a byte source read at arbitrary offsets (a seekable file): the header table is walked, the

@@ -124,6 +124,24 @@ class SaltV2Tensor:
         return (payload[: sz.payload_bytes], scales[: sz.scale_count], pmap[: sz.map_bytes], term.value,
                 {k: getattr(sz, k) for k, _ in _lib.ResidentSizes._fields_})
 
+    def device_layout(self, codec: SaltV2Codec):
+        """The payload and scale arenas as the uploads store them on the device (host-only twin):
+        the artifact's own, except that S34 on a shape the fast kernels take is stored as B3 and
+        that tiles with different plane counts on such a shape are padded to uniform plane slots
+        with all-zero planes.  Returns (payload u8, scales u16, info dict)."""
+        L = _lib.load()
+        payload, scales, pmap, term, _ = self.resident(codec)
+        args = (int(codec), C.c_uint32(self.scale_group_size), C.c_uint32(self.rows), C.c_uint32(self.cols),
+                _ptr(payload), C.c_size_t(payload.size), _ptr(scales), C.c_size_t(scales.size),
+                _ptr(pmap) if pmap.size else None, C.c_size_t(pmap.size), C.c_uint32(term))
+        info = _lib.DeviceLayout()
+        check(L.tb_fmt_device_layout(*args, C.byref(info), None, None))
+        out_p = np.zeros(max(info.payload_bytes, 1), np.uint8)
+        out_s = np.zeros(max(info.scale_count, 1), np.uint16)
+        check(L.tb_fmt_device_layout(*args, C.byref(info), _ptr(out_p), _ptr(out_s)))
+        return (out_p[: info.payload_bytes], out_s[: info.scale_count],
+                {k: getattr(info, k) for k, _ in _lib.DeviceLayout._fields_})
+
 
 def write_salt_v2_package(tensor: SaltV2Tensor, codec: SaltV2Codec) -> bytes:
     """write_salt_v2_package for a one-tensor package (salt_v2_package.rs:1526-1668)."""
